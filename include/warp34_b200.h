@@ -1,0 +1,182 @@
+/*
+ * warp34_b200 -- C ABI of the B200 (sm_100a) TQ4 paged-KV hot path.
+ *
+ * The three descriptor structs, the enums and the first group of entry points
+ * are binary-compatible with the reference project's FFI seam
+ * (crates/warp34-kernels/csrc/warp34_cuda.h:11-101 and :353-373, mirrored in
+ * crates/warp34-kernels/src/ffi.rs), so a host built against that seam can
+ * load this library in place of the reference kernels for the KV-cache write
+ * and paged-attention calls.  Every pointer is borrowed; no call allocates,
+ * frees or synchronises with the host unless its comment says otherwise; all
+ * work is enqueued on `ex->stream`; the caller has already made the target
+ * device current.  Return value: 0 on success, otherwise a cudaError_t value
+ * (cudaErrorInvalidValue = 1 for ill-formed arguments,
+ * cudaErrorNotSupported = 801 for a combination this library does not
+ * implement).
+ */
+#ifndef WARP34_B200_H
+#define WARP34_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- enums (reference: warp34_cuda.h:20-48) -------------------------------- */
+enum {
+    WARP34_KV_NAMESPACE_TARGET_FULL_ATTN = 0,
+    WARP34_KV_NAMESPACE_MTP_FULL_ATTN    = 1,
+    WARP34_KV_NAMESPACE_DFLASH_DRAFT_CTX = 2,
+};
+enum {
+    WARP34_KV_FORMAT_FP16     = 0,
+    WARP34_KV_FORMAT_BF16     = 1,
+    WARP34_KV_FORMAT_TQ4      = 2,
+    WARP34_KV_FORMAT_Q8_0     = 3,
+    WARP34_KV_FORMAT_FP8_E4M3 = 4,
+};
+enum {
+    WARP34_KV_TRANSFORM_IDENTITY          = 0,
+    WARP34_KV_TRANSFORM_RADEMACHER_WHT256 = 1,
+};
+enum {
+    WARP34_ATTN_MASK_CAUSAL           = 0,
+    WARP34_ATTN_MASK_SYMMETRIC_WINDOW = 1,
+    WARP34_ATTN_MASK_NONCAUSAL_WINDOW = 1,
+};
+
+/* ---- descriptors (reference: warp34_cuda.h:50-101) -------------------------- */
+typedef struct {
+    uintptr_t stream;       /* cudaStream_t */
+    uint64_t  scratch_ptr;  /* device workspace, 16-byte aligned */
+    size_t    scratch_size; /* bytes */
+    uint64_t  flags;
+} warp34_exec;
+
+typedef struct {
+    uint64_t k_base;
+    uint64_t v_base;
+    uint64_t k_page_stride_bytes;
+    uint64_t k_head_stride_bytes;
+    uint64_t k_token_stride_bytes;
+    uint64_t v_page_stride_bytes;
+    uint64_t v_head_stride_bytes;
+    uint64_t v_token_stride_bytes;
+    int32_t  namespace_id;
+    int32_t  layer_id;
+    int32_t  local_kv_heads;
+    int32_t  head_dim;
+    int32_t  block_size;
+    int32_t  k_format;
+    int32_t  v_format;
+    int32_t  k_transform;
+    int32_t  v_transform;
+    int32_t  reserved;
+} warp34_kv_layer_layout;
+
+typedef struct {
+    const int32_t* query_start_loc;     /* [num_reqs + 1]  device */
+    const int32_t* context_lens_before; /* [num_reqs]      device, may be NULL */
+    const int32_t* seq_lens_after;      /* [num_reqs]      device */
+    const int32_t* block_tables;        /* [num_reqs, max_blocks_per_req] device */
+    const int32_t* write_slot_mapping;  /* [total_tokens]  device: page*16 + offset, < 0 = skip */
+    const uint8_t* valid_token_mask;    /* [total_tokens]  device, may be NULL */
+    const uint8_t* valid_req_mask;      /* [num_reqs]      device, may be NULL */
+    int32_t        num_reqs;
+    int32_t        total_tokens;
+    int32_t        max_blocks_per_req;
+    int32_t        max_q_len;
+    int32_t        max_seq_len;
+    int32_t        mask_mode;
+    int32_t        sliding_window;
+    float          sm_scale;
+    int32_t        reserved;
+} warp34_attention_batch;
+
+#if defined(__cplusplus)
+static_assert(sizeof(warp34_exec) == 32, "warp34_exec ABI size");
+static_assert(sizeof(warp34_kv_layer_layout) == 104, "warp34_kv_layer_layout ABI size");
+static_assert(sizeof(warp34_attention_batch) == 96, "warp34_attention_batch ABI size");
+#else
+_Static_assert(sizeof(warp34_exec) == 32, "warp34_exec ABI size");
+_Static_assert(sizeof(warp34_kv_layer_layout) == 104, "warp34_kv_layer_layout ABI size");
+_Static_assert(sizeof(warp34_attention_batch) == 96, "warp34_attention_batch ABI size");
+#endif
+
+/* ======================================================================== *
+ * 1. Drop-in entry points (same names, argument meaning and error behaviour
+ *    as the reference).
+ * ======================================================================== */
+
+/*
+ * Quantize-and-append: encodes one fp16 K row and one fp16 V row of 256
+ * values per (token, kv head) into the paged pool at
+ * write_slot_mapping[token].  Replaces warp34_kv_cache_write
+ * (warp34_cuda.h:354-356, op_kv_cache.cu:852-858); k_in / v_in are
+ * [total_tokens, local_kv_heads * head_dim] contiguous.
+ */
+int warp34_kv_cache_write(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
+                          const warp34_attention_batch* batch,
+                          const void* k_in, const void* v_in);
+
+/*
+ * Same with an explicit row stride (in elements) for K and V, so K and V can
+ * be slices of a packed QKV activation.  Replaces
+ * warp34_kv_cache_write_strided (warp34_cuda.h:357-360,
+ * op_kv_cache.cu:828-850).  Strides below local_kv_heads * head_dim are
+ * rejected with cudaErrorInvalidValue; an empty batch returns 0 without a
+ * launch.  Tokens with valid_token_mask == 0, requests with
+ * valid_req_mask == 0 and slots < 0 have no side effects.
+ */
+int warp34_kv_cache_write_strided(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
+                                  const warp34_attention_batch* batch,
+                                  const void* k_in, const void* v_in,
+                                  int k_row_stride, int v_row_stride);
+
+/*
+ * Paged attention over the pool: q_in and attn_out are fp16
+ * [total_tokens, num_q_heads, head_dim].  Replaces warp34_paged_attention_f16
+ * (warp34_cuda.h:370-373, op_paged_attn.cu:1266-1448).  Split-KV partials
+ * live in ex->scratch_ptr; warp34_paged_attention_scratch_bytes() says how
+ * much a batch geometry can use, and any 16-byte-aligned scratch of at least
+ * 1 MiB is accepted (less scratch means fewer, longer KV partitions).
+ * Masked rows of attn_out are left untouched.
+ */
+int warp34_paged_attention_f16(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
+                               const warp34_attention_batch* batch,
+                               const void* q_in, void* attn_out,
+                               int num_q_heads);
+
+/*
+ * The literal dequant-then-attend kernel (one warp per query row, fp32
+ * throughout, no scratch).  Replaces warp34_paged_attention_scalar_f16
+ * (op_kv_cache.cu:1244), which the reference keeps as its fallback and test
+ * selector; accepts any strides in the layout.
+ */
+int warp34_paged_attention_scalar_f16(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
+                                      const warp34_attention_batch* batch,
+                                      const void* q_in, void* attn_out,
+                                      int num_q_heads);
+
+/* ======================================================================== *
+ * 2. Additive entry points (no reference symbol changes meaning).
+ * ======================================================================== */
+
+/*
+ * Upper bound of the scratch the split-KV path can use for a batch geometry
+ * (only host-known fields of `batch` are read).  The reference sizes the same
+ * buffer inline (op_paged_attn.cu:1301-1338).
+ */
+size_t warp34_paged_attention_scratch_bytes(const warp34_kv_layer_layout* layout,
+                                            const warp34_attention_batch* batch,
+                                            int num_q_heads);
+
+/* Library identification: returns a static string "warp34_b200 <version> sm_100a". */
+const char* warp34_b200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* WARP34_B200_H */

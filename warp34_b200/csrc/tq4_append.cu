@@ -1,0 +1,368 @@
+// TQ4 quantize-and-append for sm_100a.
+//
+// Replaces kv_cache_write_kernel / write_kv_row of the reference
+// (crates/warp34-kernels/csrc/ops/op_kv_cache.cu:152-218, :325-368) for
+// head_dim 256, TQ4 storage and the sign-diagonal + WHT-256 rotation.
+//
+// Per (token, kv head) and per K / V row:
+//   v = sign * x  ->  WHT-256  ->  per 128-half: s = sum v^2,
+//   inv = 0.70710678 * rsqrt(s)  ->  code = #{i : v*inv > boundary_i}
+//   ->  d = sum(v * c[code]) / sum(c[code]^2)  ->  fp16(d) + 64 packed bytes.
+//
+// The packed bytes and scales are bit-identical to the reference because every
+// fp32 operation is issued in the same association order:
+//   * the WHT is the same butterfly network (stage order 1..128);
+//   * each of the 24 sums is the reference's 32-lane xor butterfly (levels over
+//     column bits 4,3,2,1,0) followed by a sequential sum over the four
+//     32-column groups of a half.
+// The thread layout is different: 8 lanes hold one row (column bits 0..2 select
+// the lane, bits 3..7 the register), so the first two butterfly levels and five
+// of the eight WHT stages are register-only, and the three cross-lane levels of
+// the eight per-group sums are done with a halving exchange (7 shuffles instead
+// of 40 per quantity).  A warp encodes 4 rows at once.
+//
+// This translation unit is compiled with -use_fast_math like the reference
+// build (crates/warp34-kernels/build.rs:56-59), so rsqrtf() and '/' lower to the
+// same approximate instructions and denormals flush the same way.
+#include "tq4_common.cuh"
+
+namespace w34 {
+
+// The reference computes warp_reduce_sum(a * b); nvcc contracts the first butterfly add
+// with the product into an fma (the product that is shuffled is still rounded).  Lanes
+// with column bit 4 clear ("lo class") then hold fma(a_lo, b_lo, rn(a_hi*b_hi)) while
+// lanes with bit 4 set hold fma(a_hi, b_hi, rn(a_lo*b_lo)): two different sums that
+// stay separate through the remaining symmetric levels.  kContract* say, per quantity,
+// whether that contraction is emulated; with it off both classes are the plain sum.
+#ifndef W34_CONTRACT_SQ
+#define W34_CONTRACT_SQ 1
+#endif
+#ifndef W34_CONTRACT_VC
+#define W34_CONTRACT_VC 1
+#endif
+#ifndef W34_CONTRACT_CC
+#define W34_CONTRACT_CC 1
+#endif
+
+// code = #{i : rv > boundary_i} for the 15 ascending, symmetric boundaries (b[7] = 0).
+__device__ __forceinline__ int tq4_bucket(float rv, const float (&bpos)[7]) {
+    // bpos[k] = boundary[8 + k] > 0.  For rv > 0 all of b[0..7] are below rv; for rv <= 0
+    // none of b[7..14] is, and rv > -B  <=>  |rv| < B.
+    const float a = fabsf(rv);
+    int gt = 0, lt = 0;
+#pragma unroll
+    for (int k = 0; k < 7; ++k) {
+        gt += (a > bpos[k]) ? 1 : 0;
+        lt += (a < bpos[k]) ? 1 : 0;
+    }
+    return (rv > 0.0f) ? (8 + gt) : lt;
+}
+
+// One level of the halving exchange: the lane keeps the N/2 values whose index bit
+// matches its own lane bit and adds the partner's copies of the same indices.
+template <int N>
+__device__ __forceinline__ void halve_level(float (&x)[8], int lane_bit_set, int xor_mask) {
+#pragma unroll
+    for (int i = 0; i < N / 2; ++i) {
+        const float keep = lane_bit_set ? x[i + N / 2] : x[i];
+        const float send = lane_bit_set ? x[i] : x[i + N / 2];
+        const float got = __shfl_xor_sync(0xffffffffu, send, xor_mask);
+        x[i] = __fadd_rn(keep, got);
+    }
+}
+
+// Cross-lane part of eight butterfly sums at once.  In: x[j] = this lane's partial of
+// group j after the register-only levels.  Out: total of group (lane & 7) for the
+// lane's row, levels applied in the order column bit 2, 1, 0.
+__device__ __forceinline__ float group_totals(float (&x)[8], int sub) {
+    halve_level<8>(x, sub & 4, 4);
+    halve_level<4>(x, sub & 2, 2);
+    halve_level<2>(x, sub & 1, 1);
+    return x[0];
+}
+
+// Sequential sum (((0 + t0) + t1) + t2) + t3 of the group totals held by lanes base+g0..g0+3.
+__device__ __forceinline__ float seq4(float t, int lane_base, int g0) {
+    // The reference starts from 0.0f (0 + (-0) = +0 matters for all-zero rows).
+    float s = __fadd_rn(0.0f, __shfl_sync(0xffffffffu, t, lane_base + g0));
+    s = __fadd_rn(s, __shfl_sync(0xffffffffu, t, lane_base + g0 + 1));
+    s = __fadd_rn(s, __shfl_sync(0xffffffffu, t, lane_base + g0 + 2));
+    s = __fadd_rn(s, __shfl_sync(0xffffffffu, t, lane_base + g0 + 3));
+    return s;
+}
+
+// Register-only levels (column bits 4 then 3) of the butterfly over products a*b for one
+// group; r indexes column bits 3,4 as (bit3 = r & 1, bit4 = r >> 1).
+template <bool CONTRACT>
+__device__ __forceinline__ void reg_levels(const float (&a)[4], const float (&b)[4], float& lo, float& hi) {
+    float p[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) p[r] = __fmul_rn(a[r], b[r]);
+    if (CONTRACT) {
+        const float l0 = __fmaf_rn(a[0], b[0], p[2]);
+        const float l1 = __fmaf_rn(a[1], b[1], p[3]);
+        const float h0 = __fmaf_rn(a[2], b[2], p[0]);
+        const float h1 = __fmaf_rn(a[3], b[3], p[1]);
+        lo = __fadd_rn(l0, l1);
+        hi = __fadd_rn(h0, h1);
+    } else {
+        lo = __fadd_rn(__fadd_rn(p[0], p[2]), __fadd_rn(p[1], p[3]));
+        hi = lo;
+    }
+}
+
+struct AppendParams {
+    warp34_kv_layer_layout layout;
+    warp34_attention_batch batch;
+    const __half* k_in;
+    const __half* v_in;
+    int k_row_stride;
+    int v_row_stride;
+    int total_rows;  // total_tokens * local_kv_heads * 2
+};
+
+__global__ void __launch_bounds__(128) tq4_append_kernel(const AppendParams p) {
+    __shared__ float s_centroid[16];
+    if (threadIdx.x < 16) s_centroid[threadIdx.x] = tq4_centroid(threadIdx.x);
+    __syncthreads();
+
+    const int lane = threadIdx.x & 31;
+    const int sub = lane & 7;
+    const int lane_base = lane & ~7;
+    const int warp_global = blockIdx.x * 4 + (threadIdx.x >> 5);
+    const int row_id = warp_global * 4 + (lane >> 3);
+
+    // ---- resolve the row: (token, head, K or V), masks, destination ------------------
+    const int heads = p.layout.local_kv_heads;
+    bool active = row_id < p.total_rows;
+    const int which = row_id & 1;
+    const int th = row_id >> 1;
+    const int tok = active ? th / heads : 0;
+    const int head = th - tok * heads;
+    int slot = -1;
+    if (active) {
+        if (p.batch.valid_token_mask != nullptr && p.batch.valid_token_mask[tok] == 0) active = false;
+    }
+    if (active && p.batch.valid_req_mask != nullptr && p.batch.query_start_loc != nullptr &&
+        p.batch.num_reqs > 0) {
+        const int req = find_request(p.batch.query_start_loc, p.batch.num_reqs, tok);
+        if (req < 0 || p.batch.valid_req_mask[req] == 0) active = false;
+    }
+    if (active) {
+        slot = p.batch.write_slot_mapping[tok];
+        if (slot < 0) active = false;
+    }
+    // All 8 lanes of a row agree on `active`; rows of a warp may differ, and every lane
+    // still takes part in the shuffles below.
+    const __half* src = nullptr;
+    uint8_t* dst = nullptr;
+    if (active) {
+        const int page = slot >> 4, off = slot & 15;
+        if (which == 0) {
+            src = p.k_in + (size_t)tok * p.k_row_stride + (size_t)head * kHeadDim;
+            dst = (uint8_t*)(uintptr_t)p.layout.k_base + (size_t)page * p.layout.k_page_stride_bytes +
+                  (size_t)head * p.layout.k_head_stride_bytes + (size_t)off * p.layout.k_token_stride_bytes;
+        } else {
+            src = p.v_in + (size_t)tok * p.v_row_stride + (size_t)head * kHeadDim;
+            dst = (uint8_t*)(uintptr_t)p.layout.v_base + (size_t)page * p.layout.v_page_stride_bytes +
+                  (size_t)head * p.layout.v_head_stride_bytes + (size_t)off * p.layout.v_token_stride_bytes;
+        }
+    }
+
+    // ---- load: v[r] = sign * x[sub + 8 r] -------------------------------------------
+    float v[32];
+#pragma unroll
+    for (int r = 0; r < 32; ++r) {
+        const int col = sub + 8 * r;
+        const float x = active ? __half2float(src[col]) : 0.0f;
+        v[r] = apply_sign(x, col);
+    }
+
+    // ---- WHT-256: stages 1,2,4 across lanes, 8..128 in registers ----------------------
+#pragma unroll
+    for (int h = 1; h < 8; h <<= 1) {
+        const bool upper = (sub & h) != 0;
+#pragma unroll
+        for (int r = 0; r < 32; ++r) {
+            const float o = __shfl_xor_sync(0xffffffffu, v[r], h);
+            v[r] = upper ? __fsub_rn(o, v[r]) : __fadd_rn(v[r], o);
+        }
+    }
+#pragma unroll
+    for (int s = 1; s < 32; s <<= 1) {
+#pragma unroll
+        for (int r = 0; r < 32; ++r) {
+            if ((r & s) == 0) {
+                const float a = v[r], b = v[r | s];
+                v[r] = __fadd_rn(a, b);
+                v[r | s] = __fsub_rn(a, b);
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < 32; ++r) v[r] = __fmul_rn(v[r], 0.0625f);
+
+    // ---- s_sq per half, in both lane classes -------------------------------------------
+    float inv_lo[2], inv_hi[2];
+    {
+        float xl[8], xh[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float a[4] = {v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]};
+            reg_levels<W34_CONTRACT_SQ != 0>(a, a, xl[j], xh[j]);
+        }
+        const float tl = group_totals(xl, sub);
+        const float s0l = seq4(tl, lane_base, 0), s1l = seq4(tl, lane_base, 4);
+        inv_lo[0] = (s0l > 1e-20f) ? (0.7071067811865475f * rsqrtf(s0l)) : 0.0f;
+        inv_lo[1] = (s1l > 1e-20f) ? (0.7071067811865475f * rsqrtf(s1l)) : 0.0f;
+        if (W34_CONTRACT_SQ != 0) {
+            const float thh = group_totals(xh, sub);
+            const float s0h = seq4(thh, lane_base, 0), s1h = seq4(thh, lane_base, 4);
+            inv_hi[0] = (s0h > 1e-20f) ? (0.7071067811865475f * rsqrtf(s0h)) : 0.0f;
+            inv_hi[1] = (s1h > 1e-20f) ? (0.7071067811865475f * rsqrtf(s1h)) : 0.0f;
+        } else {
+            inv_hi[0] = inv_lo[0];
+            inv_hi[1] = inv_lo[1];
+        }
+    }
+
+    // ---- codes, centroids, least-squares sums ------------------------------------------
+    float bpos[7];
+#pragma unroll
+    for (int k = 0; k < 7; ++k) bpos[k] = tq4_boundary(8 + k);
+
+    uint32_t nib[4] = {0u, 0u, 0u, 0u};  // nibble r at nib[r >> 3] bits 4 (r & 7)
+    float vcl[8], ccl[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        float c[4];
+        const float a[4] = {v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]};
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+            const int r = 4 * j + q4;
+            const float inv = (q4 & 2) ? inv_hi[j >> 2] : inv_lo[j >> 2];
+            const int q = tq4_bucket(__fmul_rn(a[q4], inv), bpos);
+            nib[r >> 3] |= (uint32_t)q << (4 * (r & 7));
+            c[q4] = s_centroid[q];
+        }
+        float hi_unused;
+        reg_levels<W34_CONTRACT_VC != 0>(a, c, vcl[j], hi_unused);
+        reg_levels<W34_CONTRACT_CC != 0>(c, c, ccl[j], hi_unused);
+    }
+    // Only lane 0 of the reference warp (a lo-class lane) uses these sums.
+    const float vct = group_totals(vcl, sub);
+    const float cct = group_totals(ccl, sub);
+    const float vc0 = seq4(vct, lane_base, 0), vc1 = seq4(vct, lane_base, 4);
+    const float cc0 = seq4(cct, lane_base, 0), cc1 = seq4(cct, lane_base, 4);
+    const float d0 = (cc0 > 1e-10f) ? (vc0 / cc0) : 0.0f;
+    const float d1 = (cc1 > 1e-10f) ? (vc1 / cc1) : 0.0f;
+    const uint32_t d0h = __half_as_ushort(__float2half_rn(d0));
+    const uint32_t d1h = __half_as_ushort(__float2half_rn(d1));
+
+    // ---- 8x8 nibble transpose inside the 8-lane group -----------------------------------
+    // Before: lane `sub`, register m, nibble t  = code of column sub + 8 (8 m + t).
+    // After : lane t,     register m, nibble s  = code of column s   + 8 (8 m + t),
+    //         i.e. the 4 packed bytes of columns [8 (8 m + t), +8).
+#pragma unroll
+    for (int m = 0; m < 4; ++m) {
+        uint32_t w = nib[m];
+        {
+            const uint32_t o = __shfl_xor_sync(0xffffffffu, w, 4);
+            w = (sub & 4) ? ((w & 0xffff0000u) | (o >> 16)) : ((w & 0x0000ffffu) | (o << 16));
+        }
+        {
+            const uint32_t o = __shfl_xor_sync(0xffffffffu, w, 2);
+            w = (sub & 2) ? ((w & 0xff00ff00u) | ((o >> 8) & 0x00ff00ffu))
+                          : ((w & 0x00ff00ffu) | ((o << 8) & 0xff00ff00u));
+        }
+        {
+            const uint32_t o = __shfl_xor_sync(0xffffffffu, w, 1);
+            w = (sub & 1) ? ((w & 0xf0f0f0f0u) | ((o >> 4) & 0x0f0f0f0fu))
+                          : ((w & 0x0f0f0f0fu) | ((o << 4) & 0xf0f0f0f0u));
+        }
+        nib[m] = w;
+    }
+    // Lane t now holds qs-words: block 0 words t (nib[0]) and 8 + t (nib[1]);
+    // block 1 words t (nib[2]) and 8 + t (nib[3]).
+    //
+    // The row as 33 aligned 32-bit words W0..W32: W0 = d0 | qs0[0..1] << 16,
+    // Wk = hi16(qs0 word k-1) | lo16(qs0 word k) << 16 (k = 1..15),
+    // W16 = hi16(qs0 word 15) | d1 << 16, W(17 + k) = qs1 word k.
+    const uint32_t a_prev = __shfl_sync(0xffffffffu, nib[0], lane_base + ((sub + 7) & 7));
+    const uint32_t b_prev = __shfl_sync(0xffffffffu, nib[1], lane_base + ((sub + 7) & 7));
+    if (active) {
+        const bool word_ok = ((((uintptr_t)dst) & 3u) == 0u);
+        if (word_ok) {
+            uint32_t* w = reinterpret_cast<uint32_t*>(dst);
+            const uint32_t w_a = (sub == 0) ? (d0h | (nib[0] << 16)) : ((a_prev >> 16) | (nib[0] << 16));
+            const uint32_t prev_for_b = (sub == 0) ? a_prev : b_prev;  // lane 0: qs0 word 7 (from lane 7)
+            const uint32_t w_b = (prev_for_b >> 16) | (nib[1] << 16);
+            w[sub] = w_a;
+            w[8 + sub] = w_b;
+            w[17 + sub] = nib[2];
+            w[25 + sub] = nib[3];
+            if (sub == 7) w[16] = (nib[1] >> 16) | (d1h << 16);
+        } else {
+            // Row base not 4-byte aligned: 16-bit stores (rows are always 2-byte aligned).
+            uint16_t* h = reinterpret_cast<uint16_t*>(dst);
+            if (sub == 0) { h[0] = (uint16_t)d0h; h[33] = (uint16_t)d1h; }
+            h[1 + 2 * sub] = (uint16_t)nib[0];
+            h[2 + 2 * sub] = (uint16_t)(nib[0] >> 16);
+            h[17 + 2 * sub] = (uint16_t)nib[1];
+            h[18 + 2 * sub] = (uint16_t)(nib[1] >> 16);
+            h[34 + 2 * sub] = (uint16_t)nib[2];
+            h[35 + 2 * sub] = (uint16_t)(nib[2] >> 16);
+            h[50 + 2 * sub] = (uint16_t)nib[3];
+            h[51 + 2 * sub] = (uint16_t)(nib[3] >> 16);
+        }
+    }
+}
+
+}  // namespace w34
+
+extern "C" int warp34_kv_cache_write_strided(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
+                                             const warp34_attention_batch* batch, const void* k_in,
+                                             const void* v_in, int k_row_stride, int v_row_stride) {
+    if (ex == nullptr || layout == nullptr || batch == nullptr || k_in == nullptr || v_in == nullptr) {
+        return (int)cudaErrorInvalidValue;
+    }
+    if (batch->total_tokens <= 0 || layout->local_kv_heads <= 0) return 0;
+    if (layout->head_dim != w34::kHeadDim || layout->block_size != w34::kPageTokens ||
+        layout->k_format != WARP34_KV_FORMAT_TQ4 || layout->v_format != WARP34_KV_FORMAT_TQ4 ||
+        layout->k_transform != WARP34_KV_TRANSFORM_RADEMACHER_WHT256 ||
+        layout->v_transform != WARP34_KV_TRANSFORM_RADEMACHER_WHT256) {
+        return (int)cudaErrorNotSupported;
+    }
+    const int min_stride = layout->local_kv_heads * layout->head_dim;
+    if (k_row_stride < min_stride || v_row_stride < min_stride) return (int)cudaErrorInvalidValue;
+    if (batch->write_slot_mapping == nullptr || layout->k_base == 0 || layout->v_base == 0) {
+        return (int)cudaErrorInvalidValue;
+    }
+    // Scales are stored with 16-bit accesses: every row must be 2-byte aligned.
+    if ((layout->k_base | layout->v_base | layout->k_page_stride_bytes | layout->k_head_stride_bytes |
+         layout->k_token_stride_bytes | layout->v_page_stride_bytes | layout->v_head_stride_bytes |
+         layout->v_token_stride_bytes) & 1u) {
+        return (int)cudaErrorInvalidValue;
+    }
+    w34::AppendParams p;
+    p.layout = *layout;
+    p.batch = *batch;
+    p.k_in = static_cast<const __half*>(k_in);
+    p.v_in = static_cast<const __half*>(v_in);
+    p.k_row_stride = k_row_stride;
+    p.v_row_stride = v_row_stride;
+    const long long rows = 2ll * batch->total_tokens * layout->local_kv_heads;
+    if (rows > 0x7fffffffll) return (int)cudaErrorInvalidValue;
+    p.total_rows = (int)rows;
+    const unsigned blocks = (unsigned)((rows + 15) / 16);  // 4 warps x 4 rows per block
+    w34::tq4_append_kernel<<<blocks, 128, 0, (cudaStream_t)ex->stream>>>(p);
+    return (int)cudaGetLastError();
+}
+
+extern "C" int warp34_kv_cache_write(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
+                                     const warp34_attention_batch* batch, const void* k_in,
+                                     const void* v_in) {
+    if (layout == nullptr) return (int)cudaErrorInvalidValue;
+    const int stride = layout->local_kv_heads * layout->head_dim;
+    return warp34_kv_cache_write_strided(ex, layout, batch, k_in, v_in, stride, stride);
+}

@@ -1,0 +1,899 @@
+// Paged attention over TQ4 pages for sm_100a: decode, MTP verify and (slowly) anything else
+// the descriptor ABI can express.
+//
+// Replaces, for TQ4 + sign/WHT-256 layers, the reference's
+//   paged_attention_gqa_mma_f16_kernel            (crates/warp34-kernels/csrc/ops/op_paged_attn.cu:186-588)
+//   paged_attention_split_kv_reduce_f16_kernel    (op_paged_attn.cu:1132-1218)
+//   warp34_paged_attention_f16 (dispatcher)       (op_paged_attn.cu:1266-1448)
+//   paged_attention_kernel<__half> (scalar path)  (op_kv_cache.cu:373-461, :619-792)
+//
+// Three launches per call:
+//   plan   : per request page range, item count and prefix sums -> scratch header.
+//   stream : persistent grid, one CTA per SM.  The work list is the flattened sequence of
+//            (request, kv head, row group, page) units, cut into equal contiguous shares, one
+//            per warp.  A warp streams its pages through a private ring of shared-memory
+//            stages filled by cp.async.bulk (one 2112-byte run for K and one for V per page
+//            and head, completion on an mbarrier), dequantises the 4-bit codes in registers
+//            through a conflict-free byte-pair lookup table, and runs S^T = K Q'^T and
+//            O^T += V^T P^T as m16n8k16 tensor-core MMAs with fp32 accumulators (M = 16 keys or
+//            16 channels, N = 8 query rows = GQA heads x query tokens of one row group).
+//            Warps never synchronise with each other inside the page loop.
+//   merge  : per (token, q head) combine the (m, l, acc[256]) partials of every warp share
+//            that touched the row, one inverse WHT, sign diagonal, fp16 store.
+//
+// Scales never touch the operands: scores are d0 * (q . c)[0:128] + d1 * (q . c)[128:256]
+// with one accumulator per 128-half, and P is multiplied by the V scales of its key before
+// the PV product (the same factoring as op_kv_cache.cu:653-656 and :695-705).
+#include "tq4_common.cuh"
+
+#include <cuda_fp16.h>
+
+namespace w34 {
+
+// ---------------------------------------------------------------------------------------
+// Request geometry shared by all kernels (op_paged_attn.cu:266-280 / op_kv_cache.cu:405-422)
+// ---------------------------------------------------------------------------------------
+struct ReqGeom {
+    int q_start, q_len, ctx_before, seq_after;
+    bool valid;
+};
+
+__device__ __forceinline__ ReqGeom load_req(const warp34_attention_batch& b, int r) {
+    ReqGeom g;
+    g.q_start = b.query_start_loc[r];
+    g.q_len = b.query_start_loc[r + 1] - g.q_start;
+    g.seq_after = b.seq_lens_after[r];
+    g.ctx_before = (b.context_lens_before != nullptr) ? b.context_lens_before[r] : (g.seq_after - g.q_len);
+    g.valid = g.q_len > 0 && (b.valid_req_mask == nullptr || b.valid_req_mask[r] != 0);
+    return g;
+}
+
+__device__ __forceinline__ int row_max_kv(const warp34_attention_batch& b, const ReqGeom& g, int q_off) {
+    int m = (b.mask_mode == WARP34_ATTN_MASK_SYMMETRIC_WINDOW) ? (g.seq_after - 1) : (g.ctx_before + q_off);
+    if (m >= g.seq_after) m = g.seq_after - 1;
+    return m;
+}
+
+__device__ __forceinline__ int row_min_kv(const warp34_attention_batch& b, const ReqGeom& g, int q_off) {
+    int m = 0;
+    if (b.sliding_window > 0) {
+        const int w = g.ctx_before + q_off - b.sliding_window + 1;
+        if (w > m) m = w;
+    }
+    return m;
+}
+
+// ---------------------------------------------------------------------------------------
+// Scalar dequant-then-attend: one warp per (token, q head), fp32, any strides.
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) tq4_attention_scalar_kernel(
+    const warp34_kv_layer_layout layout, const warp34_attention_batch batch,
+    const __half* __restrict__ q_in, __half* __restrict__ attn_out, int num_q_heads) {
+    __shared__ float s_x[4][kHeadDim];
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const long long row = (long long)blockIdx.x * 4 + wid;
+    if (row >= (long long)batch.total_tokens * num_q_heads) return;
+    const int tok = (int)(row / num_q_heads), q_head = (int)(row % num_q_heads);
+    if (batch.valid_token_mask != nullptr && batch.valid_token_mask[tok] == 0) return;
+    const int req = find_request(batch.query_start_loc, batch.num_reqs, tok);
+    if (req < 0) return;
+    const ReqGeom g = load_req(batch, req);
+    if (!g.valid) return;
+    const int gqa = num_q_heads / layout.local_kv_heads;
+    const int kv_head = q_head / gqa;
+    const int q_off = tok - g.q_start;
+    const int max_kv = row_max_kv(batch, g, q_off);
+    const int min_kv = row_min_kv(batch, g, q_off);
+
+    const __half* q_row = q_in + ((size_t)tok * num_q_heads + q_head) * kHeadDim;
+    __half* out_row = attn_out + ((size_t)tok * num_q_heads + q_head) * kHeadDim;
+
+    // Q' = WHT(sign * q); then re-distribute so that lane L owns rotated columns [8 L, 8 L + 8).
+    float t[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) t[j] = apply_sign(__half2float(q_row[lane + 32 * j]), lane + 32 * j);
+    wht256_lanes(t, lane);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s_x[wid][lane + 32 * j] = t[j];
+    __syncwarp();
+    float qv[8], acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) { qv[e] = s_x[wid][8 * lane + e]; acc[e] = 0.0f; }
+    __syncwarp();
+
+    const int blk = lane >> 4;                       // which 128-half this lane reads
+    const int byte_off = kTq4BlockBytes * blk + 2 + 4 * (lane & 15);
+    const int32_t* blocks = batch.block_tables + (size_t)req * batch.max_blocks_per_req;
+    float m_i = -1e30f, l_i = 0.0f;
+    for (int pos = min_kv; pos <= max_kv; ++pos) {
+        const int page = blocks[pos >> 4], off = pos & 15;
+        const uint8_t* kp = (const uint8_t*)(uintptr_t)layout.k_base + (size_t)page * layout.k_page_stride_bytes +
+                            (size_t)kv_head * layout.k_head_stride_bytes + (size_t)off * layout.k_token_stride_bytes;
+        const uint8_t* vp = (const uint8_t*)(uintptr_t)layout.v_base + (size_t)page * layout.v_page_stride_bytes +
+                            (size_t)kv_head * layout.v_head_stride_bytes + (size_t)off * layout.v_token_stride_bytes;
+        const float dk = __half2float(*reinterpret_cast<const __half*>(kp + kTq4BlockBytes * blk));
+        const uint32_t kw = (uint32_t)*reinterpret_cast<const uint16_t*>(kp + byte_off) |
+                            ((uint32_t)*reinterpret_cast<const uint16_t*>(kp + byte_off + 2) << 16);
+        float dot = 0.0f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) dot += qv[e] * tq4_centroid((kw >> (4 * e)) & 15u);
+        const float score = warp_sum(dot * dk) * batch.sm_scale;
+        const float m_new = fmaxf(m_i, score);
+        const float alpha = __expf(m_i - m_new);
+        const float pr = __expf(score - m_new);
+        l_i = l_i * alpha + pr;
+        m_i = m_new;
+        const float pd = pr * __half2float(*reinterpret_cast<const __half*>(vp + kTq4BlockBytes * blk));
+        const uint32_t vw = (uint32_t)*reinterpret_cast<const uint16_t*>(vp + byte_off) |
+                            ((uint32_t)*reinterpret_cast<const uint16_t*>(vp + byte_off + 2) << 16);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = acc[e] * alpha + pd * tq4_centroid((vw >> (4 * e)) & 15u);
+    }
+    const float inv_l = (l_i > 0.0f) ? (1.0f / l_i) : 0.0f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) s_x[wid][8 * lane + e] = acc[e] * inv_l;
+    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < 8; ++j) t[j] = s_x[wid][lane + 32 * j];
+    wht256_lanes(t, lane);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) out_row[lane + 32 * j] = __float2half_rn(apply_sign(t[j], lane + 32 * j));
+}
+
+// ---------------------------------------------------------------------------------------
+// Split-KV streaming path
+// ---------------------------------------------------------------------------------------
+constexpr int kRowsPerGroup = 8;            // N of the MMA: query rows per work item
+constexpr int kStageBytes = 2 * kTq4PageHeadBytes;  // K run then V run of one (page, head)
+constexpr int kLutBytes = 256 * 32 * 4;     // byte-pair table, one copy per lane
+constexpr int kPartialFloats = kRowsPerGroup * kHeadDim + 2 * kRowsPerGroup;
+constexpr long long kWaitCycleLimit = 1ll << 31;  // about one second of SM clocks
+constexpr int kMinUnitsPerWarp = 4;
+
+// Scratch header written by the plan kernel.
+struct PlanHeader {
+    int32_t status;        // 0 ok; bit 0: an mbarrier wait gave up
+    int32_t total_items;
+    int32_t total_units;
+    int32_t units_per_warp;
+};
+// Per request (num_reqs + 1 entries where it is a prefix sum), all int32, after the header:
+//   unit_prefix[r], item_prefix[r], page_lo[r], npages[r], ngroups[r]
+constexpr int kPlanArrays = 5;
+
+__host__ __device__ inline size_t plan_bytes(int num_reqs) {
+    size_t b = sizeof(PlanHeader) + (size_t)kPlanArrays * (size_t)(num_reqs + 1) * sizeof(int32_t);
+    return (b + 255) & ~(size_t)255;
+}
+
+struct StreamParams {
+    warp34_kv_layer_layout layout;
+    warp34_attention_batch batch;
+    const __half* q_in;
+    __half* attn_out;
+    uint8_t* scratch;      // plan header, arrays, then partial slots
+    int num_q_heads;
+    int gqa;
+    int num_warps;         // worker warps over the whole grid
+    int max_slots;
+    float q_scale;         // sm_scale * log2(e), folded into Q'
+};
+
+__device__ __forceinline__ int32_t* plan_array(uint8_t* scratch, int which, int num_reqs) {
+    return reinterpret_cast<int32_t*>(scratch + sizeof(PlanHeader)) + (size_t)which * (num_reqs + 1);
+}
+
+__global__ void __launch_bounds__(32) tq4_attention_plan_kernel(const StreamParams p) {
+    const int lane = threadIdx.x;
+    const int R = p.batch.num_reqs;
+    int32_t* unit_prefix = plan_array(p.scratch, 0, R);
+    int32_t* item_prefix = plan_array(p.scratch, 1, R);
+    int32_t* page_lo = plan_array(p.scratch, 2, R);
+    int32_t* npages_a = plan_array(p.scratch, 3, R);
+    int32_t* ngroups_a = plan_array(p.scratch, 4, R);
+    const int hkv = p.layout.local_kv_heads;
+    int unit_carry = 0, item_carry = 0;
+    for (int base = 0; base < R; base += 32) {
+        const int r = base + lane;
+        int npages = 0, ngroups = 0, plo = 0;
+        if (r < R) {
+            const ReqGeom g = load_req(p.batch, r);
+            if (g.valid) {
+                const int lo = row_min_kv(p.batch, g, 0);
+                const int hi = row_max_kv(p.batch, g, g.q_len - 1);
+                if (hi >= lo) { plo = lo >> 4; npages = (hi >> 4) - plo + 1; }
+                ngroups = (g.q_len * p.gqa + kRowsPerGroup - 1) / kRowsPerGroup;
+            }
+        }
+        const int items = hkv * ngroups;
+        int units = items * npages;
+        int iu = units, ii = items;  // inclusive scans
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int a = __shfl_up_sync(0xffffffffu, iu, d);
+            const int c = __shfl_up_sync(0xffffffffu, ii, d);
+            if (lane >= d) { iu += a; ii += c; }
+        }
+        if (r < R) {
+            unit_prefix[r] = unit_carry + iu - units;
+            item_prefix[r] = item_carry + ii - items;
+            page_lo[r] = plo;
+            npages_a[r] = npages;
+            ngroups_a[r] = ngroups;
+        }
+        unit_carry += __shfl_sync(0xffffffffu, iu, 31);
+        item_carry += __shfl_sync(0xffffffffu, ii, 31);
+    }
+    if (lane == 0) {
+        unit_prefix[R] = unit_carry;
+        item_prefix[R] = item_carry;
+        page_lo[R] = 0; npages_a[R] = 0; ngroups_a[R] = 0;
+        PlanHeader* h = reinterpret_cast<PlanHeader*>(p.scratch);
+        h->status = 0;
+        h->total_items = item_carry;
+        h->total_units = unit_carry;
+        int per = (unit_carry + p.num_warps - 1) / (p.num_warps > 0 ? p.num_warps : 1);
+        if (unit_carry > 0 && per < kMinUnitsPerWarp) per = kMinUnitsPerWarp;
+        h->units_per_warp = per;
+    }
+}
+
+// ---- PTX wrappers ---------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait; returns false when it gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (;;) {
+#pragma unroll 1
+        for (int spin = 0; spin < 256; ++spin) {
+            if (mbar_try_wait(bar, parity)) return true;
+        }
+        if (clock64() - t0 > kWaitCycleLimit) return false;
+    }
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
+    uint32_t y;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
+    return y;
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// A 132-byte row is 33 aligned words W0..W32.  Codes of the first 128-half sit at bytes 2..65,
+// i.e. shifted by half a word.  "Virtual word" vw (0..15) of half 0 is W[vw] for vw >= 1 and the
+// splice {bytes 2,3 | bytes 64,65} = (W0 >> 16) | (W16 << 16) for vw = 0; of half 1 it is
+// W[17 + vw].  Rotated columns covered by virtual word vw, element e (0..7):
+__device__ __forceinline__ int vword_col(int half, int vw, int e) {
+    if (half == 1) return 128 + 8 * vw + e;
+    if (vw == 0) return (e < 4) ? e : (120 + e);
+    return 8 * vw - 4 + e;
+}
+
+template <int STAGES>
+__global__ void __launch_bounds__(384, 1) tq4_attention_stream_kernel(const StreamParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    // [lut 32 KB][per warp: STAGES x 4224 B][per warp: STAGES mbarriers]
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int warps_per_cta = blockDim.x >> 5;
+    const uint32_t lut_base = smem_u32(smem);
+    uint8_t* ring_gen = smem + kLutBytes + (size_t)wid * STAGES * kStageBytes;
+    const uint32_t ring = smem_u32(ring_gen);
+    const uint32_t bars = smem_u32(smem + kLutBytes + (size_t)warps_per_cta * STAGES * kStageBytes) +
+                          (uint32_t)wid * STAGES * 8u;
+
+    // Byte-pair table: entry (byte, lane) = half2(centroid[byte & 15], centroid[byte >> 4]).
+    for (int i = threadIdx.x; i < 256 * 32; i += blockDim.x) {
+        const int byte = i >> 5;
+        reinterpret_cast<uint32_t*>(smem)[i] = pack_half2(tq4_centroid(byte & 15), tq4_centroid(byte >> 4));
+    }
+    if (lane == 0) {
+        for (int s = 0; s < STAGES; ++s) mbar_init(bars + 8u * s, 1u);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    const int R = p.batch.num_reqs;
+    PlanHeader* hdr = reinterpret_cast<PlanHeader*>(p.scratch);
+    const int32_t* unit_prefix = plan_array(p.scratch, 0, R);
+    const int32_t* item_prefix = plan_array(p.scratch, 1, R);
+    const int32_t* page_lo_a = plan_array(p.scratch, 2, R);
+    const int32_t* npages_a = plan_array(p.scratch, 3, R);
+    const int32_t* ngroups_a = plan_array(p.scratch, 4, R);
+    float* partials = reinterpret_cast<float*>(p.scratch + plan_bytes(R));
+
+    const int w_global = blockIdx.x * warps_per_cta + wid;
+    const int per = hdr->units_per_warp;
+    const int total_units = hdr->total_units;
+    long long u_ll = (long long)w_global * per;
+    if (per <= 0 || u_ll >= total_units) return;
+    int u = (int)u_ll;
+    const int u_end = min(u + per, total_units);
+
+    const int gid = lane >> 2, tig = lane & 3;
+    // MMA row m (0..7) <-> key pk within the page; row m + 8 <-> key pk + 8.  The permutation
+    // gives thread tig the keys {tig, tig+4, tig+8, tig+12} in the PV product.
+    const int pk = (gid >> 1) + 4 * (gid & 1);
+    const uint32_t lut_lane = lut_base + 4u * lane;
+    uint32_t phase_bits = 0;   // bit s = parity to wait for on stage s
+    uint32_t pending = 0;      // bit s = a copy into stage s has been issued and not yet awaited
+    bool failed = false;
+
+    // locate the request containing unit u
+    int r;
+    {
+        int lo = 0, hi = R;  // unit_prefix[lo] <= u < unit_prefix[hi]
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (unit_prefix[mid] <= u) lo = mid; else hi = mid;
+        }
+        r = lo;
+    }
+
+    while (u < u_end && !failed) {
+        while (unit_prefix[r + 1] <= u) ++r;  // skips requests without units
+        const int npages = npages_a[r];
+        const int ngroups = ngroups_a[r];
+        const int in_req = u - unit_prefix[r];
+        const int item = in_req / npages;
+        const int page_in_item = in_req - item * npages;
+        const int n_here = min(u_end - u, npages - page_in_item);
+        const int kv_head = item / ngroups;
+        const int group = item - kv_head * ngroups;
+        const int pg0 = page_lo_a[r] + page_in_item;  // first logical page of this segment
+        const int slot = w_global + item_prefix[r] + item;
+        const ReqGeom g = load_req(p.batch, r);
+        const int rows_in_req = g.q_len * p.gqa;
+
+        // ---- per-row limits for this lane's two query rows (2 tig, 2 tig + 1) ----------
+        int rmax[2], rmin[2];
+        bool rvalid[2];
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+            const int row = group * kRowsPerGroup + 2 * tig + x;
+            const int q_off = row / p.gqa;
+            rvalid[x] = row < rows_in_req &&
+                        (p.batch.valid_token_mask == nullptr || p.batch.valid_token_mask[g.q_start + q_off] != 0);
+            rmax[x] = rvalid[x] ? row_max_kv(p.batch, g, q_off) : -1;
+            rmin[x] = rvalid[x] ? row_min_kv(p.batch, g, q_off) : 0x7fffffff;
+        }
+        // keys in [safe_lo, safe_hi] are visible to every valid row of the group
+        int safe_hi = min(rvalid[0] ? rmax[0] : 0x7fffffff, rvalid[1] ? rmax[1] : 0x7fffffff);
+        int safe_lo = max(rvalid[0] ? rmin[0] : 0, rvalid[1] ? rmin[1] : 0);
+#pragma unroll
+        for (int d = 1; d < 4; d <<= 1) {
+            safe_hi = min(safe_hi, __shfl_xor_sync(0xffffffffu, safe_hi, d));
+            safe_lo = max(safe_lo, __shfl_xor_sync(0xffffffffu, safe_lo, d));
+        }
+
+        // ---- stage Q' for the group's rows: ring memory is idle here ---------------------
+        // layout: fp16 [8 rows][256 rotated columns], pre-multiplied by sm_scale * log2(e)
+        __half* q_stage = reinterpret_cast<__half*>(ring_gen);
+        for (int row8 = 0; row8 < kRowsPerGroup; ++row8) {
+            const int row = group * kRowsPerGroup + row8;
+            const int q_off = row / p.gqa;
+            const int q_head = kv_head * p.gqa + (row - q_off * p.gqa);
+            const bool ok = row < rows_in_req &&
+                            (p.batch.valid_token_mask == nullptr || p.batch.valid_token_mask[g.q_start + q_off] != 0);
+            float t[8];
+            if (ok) {
+                const __half* q_row = p.q_in + ((size_t)(g.q_start + q_off) * p.num_q_heads + q_head) * kHeadDim;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) t[j] = apply_sign(__half2float(q_row[lane + 32 * j]), lane + 32 * j);
+                wht256_lanes(t, lane);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) t[j] = 0.0f;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) q_stage[row8 * kHeadDim + lane + 32 * j] = __float2half_rn(t[j] * p.q_scale);
+        }
+        __syncwarp();
+        // B fragments of Q'^T: step s (0..7) covers half s >> 2, virtual word 4 tig + (s & 3);
+        // k-step 2 s uses elements 0..3 of the word, k-step 2 s + 1 elements 4..7.
+        uint32_t qb[16][2];
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+            const int half = s >> 2, vw = 4 * tig + (s & 3);
+#pragma unroll
+            for (int hk = 0; hk < 2; ++hk) {
+#pragma unroll
+                for (int x = 0; x < 2; ++x) {
+                    const int e = 4 * hk + 2 * x;
+                    const __half lo = q_stage[gid * kHeadDim + vword_col(half, vw, e)];
+                    const __half hi = q_stage[gid * kHeadDim + vword_col(half, vw, e + 1)];
+                    qb[2 * s + hk][x] = (uint32_t)__half_as_ushort(lo) | ((uint32_t)__half_as_ushort(hi) << 16);
+                }
+            }
+        }
+        __syncwarp();
+
+        // ---- accumulators ----------------------------------------------------------------
+        float o[16][4];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
+        float m_run[2] = {-1e30f, -1e30f};
+        float l_run[2] = {0.0f, 0.0f};
+
+        // ---- page pipeline ---------------------------------------------------------------
+        const int32_t* blocks = p.batch.block_tables + (size_t)r * p.batch.max_blocks_per_req;
+        const uint8_t* k_head_base = (const uint8_t*)(uintptr_t)p.layout.k_base + (size_t)kv_head * p.layout.k_head_stride_bytes;
+        const uint8_t* v_head_base = (const uint8_t*)(uintptr_t)p.layout.v_base + (size_t)kv_head * p.layout.v_head_stride_bytes;
+        int32_t my_page = (lane < n_here) ? blocks[pg0 + lane] : 0;  // page ids of units [0, 32)
+        int32_t next_page = (32 + lane < n_here) ? blocks[pg0 + 32 + lane] : 0;
+
+        fence_proxy_async();  // the staging writes above precede async-proxy writes to the ring
+        auto issue = [&](int idx) {  // called by all lanes; lane 0 issues the two copies
+            const int32_t page = __shfl_sync(0xffffffffu, (idx & 32) ? next_page : my_page, idx & 31);
+            pending |= 1u << (idx % STAGES);
+            if (lane == 0) {
+                const int s = idx % STAGES;
+                const uint32_t bar = bars + 8u * s;
+                const uint32_t dst = ring + (uint32_t)s * kStageBytes;
+                mbar_expect_tx(bar, kStageBytes);
+                bulk_g2s(dst, k_head_base + (size_t)page * p.layout.k_page_stride_bytes, kTq4PageHeadBytes, bar);
+                bulk_g2s(dst + kTq4PageHeadBytes, v_head_base + (size_t)page * p.layout.v_page_stride_bytes,
+                         kTq4PageHeadBytes, bar);
+            }
+        };
+        // `my_page` holds ids for units [64 c, 64 c + 32), `next_page` for [64 c + 32, 64 c + 64).
+#pragma unroll 1
+        for (int i = 0; i < STAGES - 1 && i < n_here; ++i) issue(i);
+
+#pragma unroll 1
+        for (int i = 0; i < n_here; ++i) {
+            // refill page-id registers every 32 units, one window ahead
+            if ((i & 31) == 0 && i > 0) {
+                const int base = i + 32;  // ids for [i+32, i+64) replace the window just consumed
+                const int32_t fresh = (base + lane < n_here) ? blocks[pg0 + base + lane] : 0;
+                if (i & 32) my_page = fresh; else next_page = fresh;
+            }
+            {
+                const int ahead = i + STAGES - 1;
+                if (ahead < n_here) issue(ahead);
+            }
+            const int s = i % STAGES;
+            if (!mbar_wait(bars + 8u * s, (phase_bits >> s) & 1u)) { failed = true; break; }
+            phase_bits ^= 1u << s;
+            pending &= ~(1u << s);
+
+            const uint32_t kst = ring + (uint32_t)s * kStageBytes;
+            const uint32_t vst = kst + kTq4PageHeadBytes;
+            const int kv_base = (pg0 + i) << 4;
+            const bool full = (kv_base >= safe_lo) && (kv_base + 15 <= safe_hi);
+
+            // ---- S^T = K Q'^T, one accumulator per 128-half ------------------------------
+            float sa[2][4];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) { sa[h][0] = sa[h][1] = sa[h][2] = sa[h][3] = 0.0f; }
+            const uint32_t krow_a = kst + (uint32_t)pk * kTq4RowBytes;
+            const uint32_t krow_b = krow_a + 8u * kTq4RowBytes;
+            const uint32_t ka0 = lds32(krow_a), ka16 = lds32(krow_a + 64);
+            const uint32_t kb0 = lds32(krow_b), kb16 = lds32(krow_b + 64);
+#pragma unroll
+            for (int s8 = 0; s8 < 8; ++s8) {
+                const int half = s8 >> 2;
+                uint32_t wa, wb;
+                if (half == 0) {
+                    const uint32_t off = 4u * (4u * tig + (s8 & 3));
+                    wa = lds32(krow_a + off);
+                    wb = lds32(krow_b + off);
+                    if ((s8 & 3) == 0 && tig == 0) {
+                        wa = (ka0 >> 16) | (ka16 << 16);
+                        wb = (kb0 >> 16) | (kb16 << 16);
+                    }
+                } else {
+                    const uint32_t off = 4u * (17u + 4u * tig + (s8 & 3));
+                    wa = lds32(krow_a + off);
+                    wb = lds32(krow_b + off);
+                }
+#pragma unroll
+                for (int hk = 0; hk < 2; ++hk) {
+                    const uint32_t a0 = lds32(lut_lane + (__byte_perm(wa, 0, 0x4440 + 2 * hk) << 7));
+                    const uint32_t a1 = lds32(lut_lane + (__byte_perm(wb, 0, 0x4440 + 2 * hk) << 7));
+                    const uint32_t a2 = lds32(lut_lane + (__byte_perm(wa, 0, 0x4441 + 2 * hk) << 7));
+                    const uint32_t a3 = lds32(lut_lane + (__byte_perm(wb, 0, 0x4441 + 2 * hk) << 7));
+                    mma16816(sa[half], a0, a1, a2, a3, qb[2 * s8 + hk][0], qb[2 * s8 + hk][1]);
+                }
+            }
+            // scales of this lane's two keys
+            const float dka0 = __half2float(__ushort_as_half((unsigned short)(ka0 & 0xffffu)));
+            const float dka1 = __half2float(__ushort_as_half((unsigned short)(ka16 >> 16)));
+            const float dkb0 = __half2float(__ushort_as_half((unsigned short)(kb0 & 0xffffu)));
+            const float dkb1 = __half2float(__ushort_as_half((unsigned short)(kb16 >> 16)));
+            // sc[0],sc[1]: key pk, rows 2tig, 2tig+1;  sc[2],sc[3]: key pk+8
+            float sc[4];
+            sc[0] = dka0 * sa[0][0] + dka1 * sa[1][0];
+            sc[1] = dka0 * sa[0][1] + dka1 * sa[1][1];
+            sc[2] = dkb0 * sa[0][2] + dkb1 * sa[1][2];
+            sc[3] = dkb0 * sa[0][3] + dkb1 * sa[1][3];
+
+            const uint32_t vrow = vst + (uint32_t)pk * kTq4RowBytes;  // V rows of the same two keys
+            const uint32_t va0 = lds32(vrow), va16 = lds32(vrow + 64);
+            const uint32_t vb0 = lds32(vrow + 8u * kTq4RowBytes), vb16 = lds32(vrow + 8u * kTq4RowBytes + 64);
+            float dva0 = __half2float(__ushort_as_half((unsigned short)(va0 & 0xffffu)));
+            float dva1 = __half2float(__ushort_as_half((unsigned short)(va16 >> 16)));
+            float dvb0 = __half2float(__ushort_as_half((unsigned short)(vb0 & 0xffffu)));
+            float dvb1 = __half2float(__ushort_as_half((unsigned short)(vb16 >> 16)));
+
+            bool msk[4] = {false, false, false, false};
+            if (!full) {
+                const int pos_a = kv_base + pk, pos_b = pos_a + 8;
+                msk[0] = !(pos_a >= rmin[0] && pos_a <= rmax[0]);
+                msk[1] = !(pos_a >= rmin[1] && pos_a <= rmax[1]);
+                msk[2] = !(pos_b >= rmin[0] && pos_b <= rmax[0]);
+                msk[3] = !(pos_b >= rmin[1] && pos_b <= rmax[1]);
+#pragma unroll
+                for (int x = 0; x < 4; ++x) if (msk[x]) sc[x] = -1e30f;
+            }
+            // ---- online softmax over the 16 keys, per query row -----------------------------
+            float mx0 = fmaxf(sc[0], sc[2]), mx1 = fmaxf(sc[1], sc[3]);
+#pragma unroll
+            for (int d = 4; d < 32; d <<= 1) {
+                mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, d));
+                mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, d));
+            }
+            const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
+            const bool grew = (mn0 > m_run[0]) || (mn1 > m_run[1]);
+            if (__any_sync(0xffffffffu, grew)) {
+                const float al0 = ex2(m_run[0] - mn0), al1 = ex2(m_run[1] - mn1);
+                l_run[0] *= al0;
+                l_run[1] *= al1;
+#pragma unroll
+                for (int t = 0; t < 16; ++t) {
+                    o[t][0] *= al0; o[t][1] *= al1; o[t][2] *= al0; o[t][3] *= al1;
+                }
+                m_run[0] = mn0;
+                m_run[1] = mn1;
+            }
+            float pr[4];
+            pr[0] = ex2(sc[0] - mn0);
+            pr[1] = ex2(sc[1] - mn1);
+            pr[2] = ex2(sc[2] - mn0);
+            pr[3] = ex2(sc[3] - mn1);
+            if (!full) {
+#pragma unroll
+                for (int x = 0; x < 4; ++x) if (msk[x]) pr[x] = 0.0f;
+                // a key no row can see may hold never-written bytes: keep its scale finite
+                if (msk[0] && msk[1]) { dva0 = 0.0f; dva1 = 0.0f; }
+                if (msk[2] && msk[3]) { dvb0 = 0.0f; dvb1 = 0.0f; }
+            }
+            l_run[0] += pr[0] + pr[2];
+            l_run[1] += pr[1] + pr[3];
+            // P * d_v per half, as B fragments (k = key, n = query row)
+            uint32_t pb[2][2];
+            pb[0][0] = movmatrix_trans(pack_half2(pr[0] * dva0, pr[1] * dva0));
+            pb[0][1] = movmatrix_trans(pack_half2(pr[2] * dvb0, pr[3] * dvb0));
+            pb[1][0] = movmatrix_trans(pack_half2(pr[0] * dva1, pr[1] * dva1));
+            pb[1][1] = movmatrix_trans(pack_half2(pr[2] * dvb1, pr[3] * dvb1));
+
+            // ---- O^T += V^T P^T -----------------------------------------------------------
+            // step i4: half i4 >> 1, virtual word 2 gid + (i4 & 1); rows tig, tig+4, tig+8, tig+12
+            const uint32_t vr = vst + (uint32_t)tig * kTq4RowBytes;
+#pragma unroll
+            for (int i4 = 0; i4 < 4; ++i4) {
+                const int half = i4 >> 1;
+                uint32_t w[4];
+                if (half == 0) {
+                    const uint32_t off = 4u * (2u * gid + (i4 & 1));
+#pragma unroll
+                    for (int kq = 0; kq < 4; ++kq) w[kq] = lds32(vr + 4u * kq * kTq4RowBytes + off);
+                    if ((i4 & 1) == 0 && gid == 0) {
+#pragma unroll
+                        for (int kq = 0; kq < 4; ++kq) {
+                            const uint32_t x0 = w[kq];  // W0 of that row
+                            const uint32_t x16 = lds32(vr + 4u * kq * kTq4RowBytes + 64);
+                            w[kq] = (x0 >> 16) | (x16 << 16);
+                        }
+                    }
+                } else {
+                    const uint32_t off = 4u * (17u + 2u * gid + (i4 & 1));
+#pragma unroll
+                    for (int kq = 0; kq < 4; ++kq) w[kq] = lds32(vr + 4u * kq * kTq4RowBytes + off);
+                }
+                // byte t of lo_ab -> (V[ka][e=2t], V[kb][e=2t]); of hi_ab -> e = 2t+1
+                const uint32_t lo_ab = (w[0] & 0x0f0f0f0fu) | ((w[1] << 4) & 0xf0f0f0f0u);
+                const uint32_t hi_ab = ((w[0] >> 4) & 0x0f0f0f0fu) | (w[1] & 0xf0f0f0f0u);
+                const uint32_t lo_cd = (w[2] & 0x0f0f0f0fu) | ((w[3] << 4) & 0xf0f0f0f0u);
+                const uint32_t hi_cd = ((w[2] >> 4) & 0x0f0f0f0fu) | (w[3] & 0xf0f0f0f0u);
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    const uint32_t a0 = lds32(lut_lane + (__byte_perm(lo_ab, 0, 0x4440 + t) << 7));
+                    const uint32_t a1 = lds32(lut_lane + (__byte_perm(hi_ab, 0, 0x4440 + t) << 7));
+                    const uint32_t a2 = lds32(lut_lane + (__byte_perm(lo_cd, 0, 0x4440 + t) << 7));
+                    const uint32_t a3 = lds32(lut_lane + (__byte_perm(hi_cd, 0, 0x4440 + t) << 7));
+                    mma16816(o[4 * i4 + t], a0, a1, a2, a3, pb[half][0], pb[half][1]);
+                }
+            }
+            __syncwarp();  // every lane is done with stage s before it is refilled
+        }
+
+        // ---- drain: nothing of this segment may still be in flight ------------------------
+        // (every issued stage was waited for above unless a wait gave up)
+        if (failed) {
+            // wait, bounded, for copies already issued so the CTA does not exit under them
+            for (int s = 0; s < STAGES; ++s) {
+                if (pending & (1u << s)) (void)mbar_wait(bars + 8u * s, (phase_bits >> s) & 1u);
+            }
+            if (lane == 0) atomicOr(&hdr->status, 1);
+            break;
+        }
+
+        // ---- write the partial: natural column order, through the idle ring ------------------
+        // l: add the 8 lanes (gid) that share a query row
+#pragma unroll
+        for (int d = 4; d < 32; d <<= 1) {
+            l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], d);
+            l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], d);
+        }
+        float* stage_o = reinterpret_cast<float*>(ring_gen);  // [8 rows][256]
+#pragma unroll
+        for (int i4 = 0; i4 < 4; ++i4) {
+            const int half = i4 >> 1, vw = 2 * gid + (i4 & 1);
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                const int ca = vword_col(half, vw, 2 * t), cb = vword_col(half, vw, 2 * t + 1);
+                stage_o[(2 * tig) * kHeadDim + ca] = o[4 * i4 + t][0];
+                stage_o[(2 * tig + 1) * kHeadDim + ca] = o[4 * i4 + t][1];
+                stage_o[(2 * tig) * kHeadDim + cb] = o[4 * i4 + t][2];
+                stage_o[(2 * tig + 1) * kHeadDim + cb] = o[4 * i4 + t][3];
+            }
+        }
+        __syncwarp();
+        if (slot < p.max_slots) {
+            float* dst = partials + (size_t)slot * kPartialFloats;
+            const float4* src4 = reinterpret_cast<const float4*>(stage_o);
+            float4* dst4 = reinterpret_cast<float4*>(dst);
+#pragma unroll
+            for (int k = 0; k < (kRowsPerGroup * kHeadDim / 4) / 32; ++k) dst4[k * 32 + lane] = src4[k * 32 + lane];
+            if (gid == 0) {
+                dst[kRowsPerGroup * kHeadDim + 2 * tig] = m_run[0];
+                dst[kRowsPerGroup * kHeadDim + 2 * tig + 1] = m_run[1];
+                dst[kRowsPerGroup * kHeadDim + kRowsPerGroup + 2 * tig] = l_run[0];
+                dst[kRowsPerGroup * kHeadDim + kRowsPerGroup + 2 * tig + 1] = l_run[1];
+            }
+        }
+        __syncwarp();
+        u += n_here;
+    }
+}
+
+// One warp per (token, q head): combine partials, inverse rotation, store.
+__global__ void __launch_bounds__(128) tq4_attention_merge_kernel(const StreamParams p) {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const long long row_ll = (long long)blockIdx.x * 4 + wid;
+    if (row_ll >= (long long)p.batch.total_tokens * p.num_q_heads) return;
+    const int tok = (int)(row_ll / p.num_q_heads), q_head = (int)(row_ll % p.num_q_heads);
+    if (p.batch.valid_token_mask != nullptr && p.batch.valid_token_mask[tok] == 0) return;
+    const int R = p.batch.num_reqs;
+    const int r = find_request(p.batch.query_start_loc, R, tok);
+    if (r < 0) return;
+    if (p.batch.valid_req_mask != nullptr && p.batch.valid_req_mask[r] == 0) return;
+
+    const PlanHeader* hdr = reinterpret_cast<const PlanHeader*>(p.scratch);
+    const int32_t* unit_prefix = plan_array(p.scratch, 0, R);
+    const int32_t* item_prefix = plan_array(p.scratch, 1, R);
+    const int32_t* npages_a = plan_array(p.scratch, 3, R);
+    const int32_t* ngroups_a = plan_array(p.scratch, 4, R);
+    const float* partials = reinterpret_cast<const float*>(p.scratch + plan_bytes(R));
+
+    const int kv_head = q_head / p.gqa;
+    const int row_in_req = (tok - p.batch.query_start_loc[r]) * p.gqa + (q_head - kv_head * p.gqa);
+    const int group = row_in_req / kRowsPerGroup, row8 = row_in_req - group * kRowsPerGroup;
+    const int item = kv_head * ngroups_a[r] + group;
+    const int npages = npages_a[r];
+    const int per = hdr->units_per_warp;
+
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    float l_tot = 0.0f;
+    if (npages > 0 && per > 0) {
+        const int us = unit_prefix[r] + item * npages;
+        const int w_first = us / per, w_last = (us + npages - 1) / per;
+        const int slot0 = item_prefix[r] + item;
+        float m_tot = -1e30f;
+        for (int w = w_first; w <= w_last; ++w) {
+            const float* ps = partials + (size_t)(w + slot0) * kPartialFloats + kRowsPerGroup * kHeadDim;
+            if (ps[kRowsPerGroup + row8] > 0.0f) m_tot = fmaxf(m_tot, ps[row8]);
+        }
+        for (int w = w_first; w <= w_last; ++w) {
+            const float* pa = partials + (size_t)(w + slot0) * kPartialFloats;
+            const float ls = pa[kRowsPerGroup * kHeadDim + kRowsPerGroup + row8];
+            if (ls > 0.0f) {
+                const float wgt = ex2(pa[kRowsPerGroup * kHeadDim + row8] - m_tot);
+                l_tot += ls * wgt;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[j] += pa[row8 * kHeadDim + lane + 32 * j] * wgt;
+            }
+        }
+    }
+    const float inv_l = (l_tot > 0.0f) ? (1.0f / l_tot) : 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] *= inv_l;
+    wht256_lanes(acc, lane);
+    __half* out_row = p.attn_out + ((size_t)tok * p.num_q_heads + q_head) * kHeadDim;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) out_row[lane + 32 * j] = __float2half_rn(apply_sign(acc[j], lane + 32 * j));
+}
+
+// ---- host side ---------------------------------------------------------------------------
+constexpr int kStages = 3;
+constexpr int kWarpsPerCta = 12;
+
+struct DeviceInfo {
+    int sm_count;
+    bool configured;
+};
+
+static DeviceInfo* device_info(int* rc) {
+    static DeviceInfo info[64];
+    int dev = 0;
+    *rc = (int)cudaGetDevice(&dev);
+    if (*rc != 0) return nullptr;
+    if (dev < 0 || dev >= 64) { *rc = (int)cudaErrorInvalidDevice; return nullptr; }
+    DeviceInfo* d = &info[dev];
+    if (!d->configured) {
+        int sms = 0;
+        *rc = (int)cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (*rc != 0) return nullptr;
+        const size_t smem = kLutBytes + (size_t)kWarpsPerCta * kStages * (kStageBytes + 8);
+        *rc = (int)cudaFuncSetAttribute(tq4_attention_stream_kernel<kStages>,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (*rc != 0) return nullptr;
+        d->sm_count = sms;
+        d->configured = true;
+    }
+    return d;
+}
+
+static bool tq4_layout_ok(const warp34_kv_layer_layout* l) {
+    return l->head_dim == kHeadDim && l->block_size == kPageTokens && l->local_kv_heads > 0 &&
+           l->k_format == WARP34_KV_FORMAT_TQ4 && l->v_format == WARP34_KV_FORMAT_TQ4 &&
+           l->k_transform == WARP34_KV_TRANSFORM_RADEMACHER_WHT256 &&
+           l->v_transform == WARP34_KV_TRANSFORM_RADEMACHER_WHT256 && l->k_base != 0 && l->v_base != 0;
+}
+
+// The streaming path needs the canonical packing: 132-byte rows, 16 rows contiguous per
+// (page, head), every run 16-byte aligned (bulk-copy granularity).
+static bool stream_layout_ok(const warp34_kv_layer_layout* l) {
+    return l->k_token_stride_bytes == kTq4RowBytes && l->v_token_stride_bytes == kTq4RowBytes &&
+           ((l->k_base | l->v_base | l->k_page_stride_bytes | l->v_page_stride_bytes |
+             l->k_head_stride_bytes | l->v_head_stride_bytes) & 15u) == 0 &&
+           l->k_head_stride_bytes >= (uint64_t)kTq4PageHeadBytes &&
+           l->v_head_stride_bytes >= (uint64_t)kTq4PageHeadBytes;
+}
+
+static long long items_bound(const warp34_kv_layer_layout* l, const warp34_attention_batch* b, int hq) {
+    const long long gqa = hq / l->local_kv_heads;
+    const long long rows = (long long)b->total_tokens * gqa;
+    return (long long)l->local_kv_heads * ((rows + kRowsPerGroup - 1) / kRowsPerGroup + b->num_reqs);
+}
+
+}  // namespace w34
+
+extern "C" int warp34_paged_attention_scalar_f16(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
+                                                 const warp34_attention_batch* batch, const void* q_in,
+                                                 void* attn_out, int num_q_heads) {
+    if (ex == nullptr || layout == nullptr || batch == nullptr || q_in == nullptr || attn_out == nullptr) {
+        return (int)cudaErrorInvalidValue;
+    }
+    if (batch->total_tokens <= 0 || num_q_heads <= 0) return 0;
+    if (!w34::tq4_layout_ok(layout)) return (int)cudaErrorNotSupported;
+    if (num_q_heads % layout->local_kv_heads != 0 || batch->num_reqs <= 0) return (int)cudaErrorInvalidValue;
+    const long long rows = (long long)batch->total_tokens * num_q_heads;
+    const unsigned blocks = (unsigned)((rows + 3) / 4);
+    w34::tq4_attention_scalar_kernel<<<blocks, 128, 0, (cudaStream_t)ex->stream>>>(
+        *layout, *batch, static_cast<const __half*>(q_in), static_cast<__half*>(attn_out), num_q_heads);
+    return (int)cudaGetLastError();
+}
+
+extern "C" size_t warp34_paged_attention_scratch_bytes(const warp34_kv_layer_layout* layout,
+                                                       const warp34_attention_batch* batch, int num_q_heads) {
+    if (layout == nullptr || batch == nullptr || num_q_heads <= 0 || layout->local_kv_heads <= 0) return 0;
+    int rc = 0;
+    w34::DeviceInfo* d = w34::device_info(&rc);
+    const int sms = d ? d->sm_count : 148;
+    const long long slots = (long long)sms * w34::kWarpsPerCta + w34::items_bound(layout, batch, num_q_heads);
+    return w34::plan_bytes(batch->num_reqs) + (size_t)slots * w34::kPartialFloats * sizeof(float);
+}
+
+extern "C" int warp34_paged_attention_f16(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
+                                          const warp34_attention_batch* batch, const void* q_in,
+                                          void* attn_out, int num_q_heads) {
+    if (ex == nullptr || layout == nullptr || batch == nullptr || q_in == nullptr || attn_out == nullptr) {
+        return (int)cudaErrorInvalidValue;
+    }
+    if (batch->total_tokens <= 0 || num_q_heads <= 0) return 0;
+    if (!w34::tq4_layout_ok(layout)) return (int)cudaErrorNotSupported;
+    if (num_q_heads % layout->local_kv_heads != 0 || batch->num_reqs <= 0) return (int)cudaErrorInvalidValue;
+
+    int rc = 0;
+    w34::DeviceInfo* dev = w34::device_info(&rc);
+    if (dev == nullptr) return rc;
+
+    // Streaming path: canonical layout, scratch that holds the plan plus at least one partial
+    // per item and per worker warp, unit count within int32.
+    const long long items = w34::items_bound(layout, batch, num_q_heads);
+    const long long units_bound = items * (long long)(batch->max_blocks_per_req > 0 ? batch->max_blocks_per_req : 1);
+    const size_t plan = w34::plan_bytes(batch->num_reqs);
+    const size_t slot_bytes = (size_t)w34::kPartialFloats * sizeof(float);
+    bool stream = w34::stream_layout_ok(layout) && ex->scratch_ptr != 0 && (ex->scratch_ptr & 15u) == 0u &&
+                  units_bound < 0x7fffffffll && batch->max_blocks_per_req > 0;
+    int grid = dev->sm_count;
+    if (stream) {
+        const size_t avail = ex->scratch_size > plan ? ex->scratch_size - plan : 0;
+        const long long slots_avail = (long long)(avail / slot_bytes);
+        long long warps = slots_avail - items;
+        if (warps < w34::kWarpsPerCta) {
+            stream = false;
+        } else {
+            const long long max_ctas = warps / w34::kWarpsPerCta;
+            if (max_ctas < grid) grid = (int)max_ctas;
+        }
+    }
+    if (!stream) {
+        return warp34_paged_attention_scalar_f16(ex, layout, batch, q_in, attn_out, num_q_heads);
+    }
+
+    w34::StreamParams p;
+    p.layout = *layout;
+    p.batch = *batch;
+    p.q_in = static_cast<const __half*>(q_in);
+    p.attn_out = static_cast<__half*>(attn_out);
+    p.scratch = reinterpret_cast<uint8_t*>((uintptr_t)ex->scratch_ptr);
+    p.num_q_heads = num_q_heads;
+    p.gqa = num_q_heads / layout->local_kv_heads;
+    p.num_warps = grid * w34::kWarpsPerCta;
+    p.max_slots = (int)(p.num_warps + items);
+    p.q_scale = batch->sm_scale * 1.4426950408889634f;
+    cudaStream_t st = (cudaStream_t)ex->stream;
+    const size_t smem = w34::kLutBytes + (size_t)w34::kWarpsPerCta * w34::kStages * (w34::kStageBytes + 8);
+    w34::tq4_attention_plan_kernel<<<1, 32, 0, st>>>(p);
+    w34::tq4_attention_stream_kernel<w34::kStages><<<grid, w34::kWarpsPerCta * 32, smem, st>>>(p);
+    const long long rows = (long long)batch->total_tokens * num_q_heads;
+    w34::tq4_attention_merge_kernel<<<(unsigned)((rows + 3) / 4), 128, 0, st>>>(p);
+    return (int)cudaGetLastError();
+}

@@ -1,0 +1,276 @@
+"""Host-side mirror of the reference's KV cache interface for this path, over the C ABIs.
+
+Reference counterparts: KvPool / PageBitmap / KvFormatPolicy (crates/warp34-host/src/cache.rs),
+ReqRadixState page vectors and rollback (crates/warp34-host/src/radix.rs:1070-1245), the step
+metadata packers (crates/warp34-host/src/model/graph_io.rs:368-420, execution.rs:7-127) and the
+two kernel calls of run_attention_block (crates/warp34-host/src/model/forward.rs:1141-1188).
+
+torch is used only to own device memory and streams.
+"""
+import ctypes as C
+
+import numpy as np
+import torch
+
+from . import ffi
+
+
+class PagePool:
+    """Logical page allocator (lowest-free-first, or a seeded shuffled free list)."""
+
+    def __init__(self, num_pages, block_size=16):
+        self._h = ffi.host()
+        self.handle = self._h.w34_pool_create(num_pages, block_size)
+        if not self.handle:
+            raise ValueError("w34_pool_create failed")
+        self.block_size = block_size
+
+    def close(self):
+        if self.handle:
+            self._h.w34_pool_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    num_pages = property(lambda s: s._h.w34_pool_num_pages(s.handle))
+    free_count = property(lambda s: s._h.w34_pool_free_count(s.handle))
+
+    def alloc_page(self):
+        p = self._h.w34_pool_alloc_page(self.handle)
+        return None if p < 0 else p
+
+    def free_page(self, page):
+        return self._h.w34_pool_free_page(self.handle, int(page))
+
+    def ref_page(self, page):
+        return self._h.w34_pool_ref_page(self.handle, int(page))
+
+    def refcount(self, page):
+        return self._h.w34_pool_refcount(self.handle, int(page))
+
+    def reset(self):
+        self._h.w34_pool_reset(self.handle)
+
+    def truncate(self, max_pages):
+        self._h.w34_pool_truncate(self.handle, max_pages)
+
+    def shuffle_free_list(self, seed, reserve_page0=True):
+        return self._h.w34_pool_shuffle_free_list(self.handle, seed, 1 if reserve_page0 else 0)
+
+    def stats(self):
+        st = ffi.PoolStats()
+        self._h.w34_pool_get_stats(self.handle, C.byref(st))
+        return {"capacity": st.capacity, "free": st.free_pages, "shared": st.shared_pages,
+                "active": st.active_pages}
+
+
+class Sequence:
+    """Block table and committed length of one request."""
+
+    def __init__(self, pool):
+        self._h = ffi.host()
+        self.pool = pool
+        self.handle = self._h.w34_seq_create(pool.handle)
+
+    def close(self):
+        if self.handle:
+            self._h.w34_seq_destroy(self.handle)
+            self.handle = None
+
+    def attach_prefix(self, pages, num_tokens):
+        arr = (C.c_int32 * len(pages))(*pages)
+        return self._h.w34_seq_attach_prefix(self.handle, arr, len(pages), num_tokens)
+
+    def reserve(self, total_tokens):
+        return self._h.w34_seq_reserve(self.handle, total_tokens)
+
+    def prepare_append(self):
+        """Returns None, or (src_page, dst_page, rows) when a shared tail page must be copied."""
+        s, d, r = C.c_int32(), C.c_int32(), C.c_int32()
+        rc = self._h.w34_seq_prepare_append(self.handle, C.byref(s), C.byref(d), C.byref(r))
+        if rc < 0:
+            raise RuntimeError(f"w34_seq_prepare_append: {rc}")
+        return (s.value, d.value, r.value) if rc == 1 else None
+
+    def commit(self, n):
+        return self._h.w34_seq_commit(self.handle, n)
+
+    def set_committed(self, n):
+        return self._h.w34_seq_set_committed(self.handle, n)
+
+    def rollback(self):
+        cap = max(self.num_pages, 1)
+        buf = (C.c_int32 * cap)()
+        n = self._h.w34_seq_rollback(self.handle, buf, cap)
+        if n < 0:
+            raise RuntimeError(f"w34_seq_rollback: {n}")
+        return list(buf[:n])
+
+    committed_len = property(lambda s: s._h.w34_seq_committed_len(s.handle))
+    num_pages = property(lambda s: s._h.w34_seq_num_pages(s.handle))
+    protected_pages = property(lambda s: s._h.w34_seq_protected_pages(s.handle))
+
+    @property
+    def pages(self):
+        n = self.num_pages
+        p = self._h.w34_seq_pages(self.handle)
+        return [p[i] for i in range(n)]
+
+    def set_pages_unchecked(self, pages, protected_pages=0):
+        arr = (C.c_int32 * len(pages))(*pages)
+        return self._h.w34_seq_set_pages_unchecked(self.handle, arr, len(pages), protected_pages)
+
+
+def resolve_layer(policy, ordinal, num_layers, supports_fp8=False):
+    out = (C.c_int32 * 4)()
+    rc = ffi.host().w34_kv_policy_resolve_layer(policy, ordinal, num_layers, int(supports_fp8), out)
+    if rc != 0:
+        raise ValueError("bad policy")
+    return tuple(out)
+
+
+class KvLayer:
+    """One layer's K and V slabs plus its descriptor (KvLayerBuffer, cache.rs:168-177)."""
+
+    def __init__(self, num_pages, local_kv_heads, head_dim=256, block_size=16,
+                 formats=(ffi.KV_FORMAT_TQ4, ffi.KV_FORMAT_TQ4,
+                          ffi.KV_TRANSFORM_RADEMACHER_WHT256, ffi.KV_TRANSFORM_RADEMACHER_WHT256),
+                 device="cuda", namespace_id=0, layer_id=0, fill=None):
+        self.layout = ffi.KvLayerLayout()
+        f = (C.c_int32 * 4)(*formats)
+        kb, vb = C.c_uint64(), C.c_uint64()
+        rc = ffi.host().w34_kv_layout_init(C.byref(self.layout), 0, 0, namespace_id, layer_id,
+                                           local_kv_heads, head_dim, block_size, f, num_pages,
+                                           C.byref(kb), C.byref(vb))
+        if rc != 0:
+            raise ValueError("w34_kv_layout_init failed")
+        if fill is None:
+            self.k = torch.zeros(kb.value, dtype=torch.uint8, device=device)
+            self.v = torch.zeros(vb.value, dtype=torch.uint8, device=device)
+        else:
+            self.k = torch.full((kb.value,), fill, dtype=torch.uint8, device=device)
+            self.v = torch.full((vb.value,), fill, dtype=torch.uint8, device=device)
+        self.layout.k_base = self.k.data_ptr()
+        self.layout.v_base = self.v.data_ptr()
+        self.num_pages = num_pages
+
+
+class StepBatch:
+    """Device-resident metadata of one step plus the warp34_attention_batch descriptor."""
+
+    def __init__(self, query_start_loc, context_lens_before, seq_lens_after, block_tables,
+                 write_slot_mapping, max_blocks_per_req, sm_scale, device="cuda", mask_mode=0,
+                 sliding_window=0, valid_token_mask=None, valid_req_mask=None, max_q_len=None,
+                 max_seq_len=None):
+        i32 = lambda a: torch.as_tensor(np.ascontiguousarray(a, dtype=np.int32)).to(device)  # noqa: E731
+        self.host = dict(query_start_loc=np.asarray(query_start_loc, np.int32),
+                         context_lens_before=np.asarray(context_lens_before, np.int32),
+                         seq_lens_after=np.asarray(seq_lens_after, np.int32),
+                         block_tables=np.asarray(block_tables, np.int32),
+                         write_slot_mapping=np.asarray(write_slot_mapping, np.int32),
+                         valid_token_mask=None if valid_token_mask is None else np.asarray(valid_token_mask, np.uint8),
+                         valid_req_mask=None if valid_req_mask is None else np.asarray(valid_req_mask, np.uint8))
+        self.qsl = i32(query_start_loc)
+        self.ctx = i32(context_lens_before)
+        self.seq = i32(seq_lens_after)
+        self.bt = i32(block_tables)
+        self.slots = i32(write_slot_mapping)
+        self.vtm = None if valid_token_mask is None else torch.as_tensor(np.asarray(valid_token_mask, np.uint8)).to(device)
+        self.vrm = None if valid_req_mask is None else torch.as_tensor(np.asarray(valid_req_mask, np.uint8)).to(device)
+        q = np.asarray(query_start_loc, np.int64)
+        b = ffi.AttentionBatch()
+        b.query_start_loc = self.qsl.data_ptr()
+        b.context_lens_before = self.ctx.data_ptr()
+        b.seq_lens_after = self.seq.data_ptr()
+        b.block_tables = self.bt.data_ptr()
+        b.write_slot_mapping = self.slots.data_ptr()
+        b.valid_token_mask = None if self.vtm is None else self.vtm.data_ptr()
+        b.valid_req_mask = None if self.vrm is None else self.vrm.data_ptr()
+        b.num_reqs = len(q) - 1
+        b.total_tokens = int(q[-1])
+        b.max_blocks_per_req = int(max_blocks_per_req)
+        b.max_q_len = int(max_q_len if max_q_len is not None else (np.diff(q).max() if len(q) > 1 else 0))
+        b.max_seq_len = int(max_seq_len if max_seq_len is not None else (np.max(seq_lens_after) if len(q) > 1 else 0))
+        b.mask_mode = mask_mode
+        b.sliding_window = sliding_window
+        b.sm_scale = sm_scale
+        self.desc = b
+
+    def host_desc(self):
+        """The same descriptor over HOST arrays (for the CPU oracle)."""
+        h = self.host
+        b = ffi.AttentionBatch()
+        C.memmove(C.byref(b), C.byref(self.desc), C.sizeof(b))
+        b.query_start_loc = h["query_start_loc"].ctypes.data
+        b.context_lens_before = h["context_lens_before"].ctypes.data
+        b.seq_lens_after = h["seq_lens_after"].ctypes.data
+        b.block_tables = h["block_tables"].ctypes.data
+        b.write_slot_mapping = h["write_slot_mapping"].ctypes.data
+        b.valid_token_mask = None if h["valid_token_mask"] is None else h["valid_token_mask"].ctypes.data
+        b.valid_req_mask = None if h["valid_req_mask"] is None else h["valid_req_mask"].ctypes.data
+        return b
+
+
+def build_step(seqs, q_lens, max_blocks_per_req, sm_scale, device="cuda", **kw):
+    """Packs the step metadata of `seqs` (each already reserved) through the C++ builder."""
+    n = len(seqs)
+    total = int(sum(q_lens))
+    handles = (C.c_void_p * n)(*[s.handle for s in seqs])
+    ql = (C.c_int32 * n)(*q_lens)
+    qsl = np.zeros(n + 1, np.int32)
+    ctx = np.zeros(n, np.int32)
+    seq = np.zeros(n, np.int32)
+    bt = np.zeros((n, max_blocks_per_req), np.int32)
+    slots = np.zeros(max(total, 1), np.int32)
+    mq, ms = C.c_int32(), C.c_int32()
+    ip = lambda a: a.ctypes.data_as(C.POINTER(C.c_int32))  # noqa: E731
+    rc = ffi.host().w34_build_step_metadata(handles, ql, n, max_blocks_per_req, ip(qsl), ip(ctx),
+                                            ip(seq), ip(bt), ip(slots), C.byref(mq), C.byref(ms))
+    if rc < 0:
+        raise RuntimeError(f"w34_build_step_metadata: {rc}")
+    return StepBatch(qsl, ctx, seq, bt, slots[:total], max_blocks_per_req, sm_scale, device=device,
+                     max_q_len=mq.value, max_seq_len=ms.value, **kw)
+
+
+class Executor:
+    """warp34_exec: a stream and a scratch buffer."""
+
+    def __init__(self, scratch_bytes=64 << 20, device="cuda", stream=None):
+        self.scratch = torch.empty(scratch_bytes, dtype=torch.uint8, device=device)
+        self.ex = ffi.Exec()
+        self.ex.scratch_ptr = self.scratch.data_ptr()
+        self.ex.scratch_size = scratch_bytes
+        self.ex.flags = 0
+        self.set_stream(stream)
+
+    def set_stream(self, stream=None):
+        s = stream if stream is not None else torch.cuda.current_stream()
+        self.ex.stream = s.cuda_stream
+
+
+def _check(rc, what):
+    if rc != 0:
+        raise RuntimeError(f"{what} failed with CUDA error {rc}")
+
+
+def kv_cache_write(ex, layer, batch, k, v, k_row_stride=None, v_row_stride=None, lib=None):
+    """warp34_kv_cache_write_strided: fp16 k/v [tokens, heads*256] (or strided views)."""
+    lib = lib or ffi.kernels()
+    ks = k_row_stride if k_row_stride is not None else k.stride(0)
+    vs = v_row_stride if v_row_stride is not None else v.stride(0)
+    rc = lib.warp34_kv_cache_write_strided(C.byref(ex.ex), C.byref(layer.layout), C.byref(batch.desc),
+                                           k.data_ptr(), v.data_ptr(), ks, vs)
+    _check(rc, "warp34_kv_cache_write_strided")
+
+
+def paged_attention(ex, layer, batch, q, out, num_q_heads, lib=None, scalar=False):
+    """warp34_paged_attention_f16 (or the scalar dequant-then-attend entry point)."""
+    lib = lib or ffi.kernels()
+    fn = lib.warp34_paged_attention_scalar_f16 if scalar else lib.warp34_paged_attention_f16
+    rc = fn(C.byref(ex.ex), C.byref(layer.layout), C.byref(batch.desc), q.data_ptr(), out.data_ptr(),
+            num_q_heads)
+    _check(rc, "warp34_paged_attention_f16")
