@@ -1,0 +1,328 @@
+#!/usr/bin/env python3
+"""Benchmark of the TQ4 paged-KV hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Workload (config.workload): batched decode at the 27B-class full-attention layer shape --
+24 Q heads, 4 KV heads, head_dim 256, 64 sequences with contexts uniform in [8192, 32768],
+TQ4 pages of 16 tokens placed by a seeded shuffled free list.  A step appends one token per
+sequence (quantize-and-append) and runs one decode attention pass.  Inputs are synthetic and
+seeded; the KV read per step (about 1.34 GB) is far larger than L2.
+
+Metric: compressed-KV GB/s = sum(ctx_len) * Hkv * 264 B per step / step time.  With N > 1
+every rank runs its own 64-sequence batch (weak scaling, no data-path collective); the value
+is all ranks' bytes over the slowest rank's time.
+
+`--impl reference` runs the same steps through the reference's own kernels compiled for
+sm_100a (oracle/_ref), or, when that library is absent, through the CPU oracle.
+"""
+import argparse
+import ctypes as C
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "tq4_paged_decode_attention_kv_gbps"
+UNIT = "GB/s"
+NOMINAL_HBM_GBS = 8000.0
+FALLBACK_HBM_GBS = 6650.0
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return json.load(open(p)), "measured"
+        except Exception:
+            pass
+    return {"hbm_gbs": FALLBACK_HBM_GBS}, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """Polls NVML (read-only) for SM clock and clock-event reasons while the benchmark runs."""
+
+    def __init__(self, index, period_s=0.02):
+        super().__init__(daemon=True)
+        self.index, self.period = index, period_s
+        self.samples = []  # (t, sm_mhz, reasons_bitmask)
+        self.stop_flag = False
+        self.max_mhz = None
+        self.ok = False
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception:
+            self.ok = False
+
+    def run(self):
+        if not self.ok:
+            return
+        nv = self.nv
+        while not self.stop_flag:
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)
+                try:
+                    reasons = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    reasons = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                self.samples.append((time.perf_counter(), mhz, reasons))
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def summary(self, t0, t1):
+        names = {0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown",
+                 0x10: "sync_boost", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+                 0x80: "hw_power_brake_slowdown", 0x100: "display_clock_setting"}
+        inside = [s for s in self.samples if t0 <= s[0] <= t1]
+        scope = "timed_region"
+        if not inside:
+            inside, scope = self.samples, "whole_run"
+        if not inside:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0, "scope": "unavailable"}
+        mask = 0
+        for s in inside:
+            mask |= s[2]
+        return {"sm_mhz": float(np.median([s[1] for s in inside])), "sm_max_mhz": self.max_mhz,
+                "reasons": [n for b, n in names.items() if mask & b], "samples": len(inside), "scope": scope}
+
+
+def init_dist(n_gpus):
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    else:
+        torch.cuda.set_device(0)
+    return rank, local, world
+
+
+def barrier(world):
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def max_over_ranks(x, world):
+    if world == 1:
+        return x
+    import torch.distributed as dist
+    t = torch.tensor([x], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def sum_over_ranks(x, world):
+    if world == 1:
+        return x
+    import torch.distributed as dist
+    t = torch.tensor([x], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.SUM)
+    return float(t.item())
+
+
+def cpu_baseline(wl, hq, q_host, k_new, v_new, step_host_desc, budget_s=20.0):
+    """The CPU oracle (a restatement of the reference's algorithm; the reference has no CPU
+    implementation of this path) on the host cores: the same step on a bounded sample of the
+    batch.  Returns the cpu_baseline object."""
+    import oracle
+    from warp34_b200 import ffi
+    cores = os.cpu_count() or 1
+    hk, hv = wl.layer.k.cpu().numpy(), wl.layer.v.cpu().numpy()
+    lay = ffi.KvLayerLayout()
+    C.memmove(C.byref(lay), C.byref(wl.layer.layout), C.sizeof(lay))
+    lay.k_base, lay.v_base = hk.ctypes.data, hv.ctypes.data
+    nreq = step_host_desc.num_reqs
+    # size the sample from a one-sequence probe
+    def run(n):
+        b = ffi.AttentionBatch()
+        C.memmove(C.byref(b), C.byref(step_host_desc), C.sizeof(b))
+        b.num_reqs, b.total_tokens = n, n
+        out = np.zeros((n, hq, 256), np.uint16)
+        t0 = time.perf_counter()
+        oracle.kv_cache_write(lay, b, k_new, v_new, k_new.shape[1], v_new.shape[1], nthreads=cores)
+        oracle.paged_attention(lay, b, q_host, out, hq, nthreads=cores)
+        return time.perf_counter() - t0
+    t1 = run(1)
+    n = int(max(1, min(nreq, budget_s / max(t1, 1e-4))))
+    dt = run(n)
+    kv_bytes = sum(wl.ctx[i] + 1 for i in range(n)) * wl.num_kv_heads * 264
+    return {"value": kv_bytes / dt / 1e9, "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": f"one full step (append + attention) over the first {n} of {nreq} sequences, {dt:.2f} s"}
+
+
+def host_step_batch(kv, step, batch, n_tok):
+    """The step's metadata as a host-side StepBatch (keeps the arrays alive for the oracle)."""
+    io = step.io
+    o = io._offs
+    return kv.StepBatch(io._np[o[0]:o[0] + batch + 1], io._np[o[1]:o[1] + batch], io._np[o[2]:o[2] + batch],
+                        io._np[o[3]:o[3] + batch * io.max_blocks].reshape(batch, -1), io._np[o[4]:o[4] + n_tok],
+                        io.max_blocks, 1.0 / 16.0, device="cpu")
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=300)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="cfg1_batched_decode")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    import oracle  # only for the reference arm and the cpu_baseline leg
+    from warp34_b200 import ffi, kv, synth
+
+    reference = args.impl == "reference"
+    ref_path = oracle.ref_lib_path() if reference else None
+    if reference and int(os.environ.get("RANK", "0")) != 0 and ref_path is None:
+        return  # the CPU fallback of the reference arm runs on rank 0 only
+    rank, local, world = init_dist(args.gpus)
+    dev = f"cuda:{local}"
+    lib = ffi.bind_kernel_abi(ref_path) if ref_path else ffi.kernels()
+
+    hq, hkv, batch, lo, hi, q_len, seed = synth.CONFIGS[args.config]
+    ctx = synth.context_lengths(batch, lo, hi, seed + 1000 * rank)
+    wl = synth.PagedWorkload([int(c) for c in ctx], [q_len] * batch, hkv, seed=seed + 1000 * rank, device=dev)
+    step = kv.DecodeStep(wl.layer, wl.seqs, hq, max_q_len=q_len, scratch_bytes=64 << 20, device=dev)
+    wl.fill_context(step.ex, seed + 1000 * rank, chunk_tokens=32768)  # untimed: KV pool resident in HBM
+    n_tok = batch * q_len
+    k_new, v_new = synth.make_kv(n_tok, hkv, seed + 17)
+    q_new = synth.make_q(n_tok, hq, seed + 17)
+    step.k_host.copy_(k_new)
+    step.v_host.copy_(v_new)
+    step.q_host.copy_(q_new)
+    q_lens = [q_len] * batch
+    kv_bytes = wl.algorithmic_kv_bytes()
+
+    if reference and ref_path is None:
+        # CPU arm: the oracle port on the host cores, each step a bounded sample.
+        step.run(q_lens)
+        hb = host_step_batch(kv, step, batch, n_tok)
+        cb = cpu_baseline(wl, hq, q_new.numpy().view(np.uint16), k_new.numpy().view(np.uint16),
+                          v_new.numpy().view(np.uint16), hb.host_desc(), budget_s=8.0)
+        line = {"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": UNIT, "n_gpus": args.gpus,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": args.config}, "cpu_baseline": cb,
+                "e2e": {"value": cb["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(line))
+        return
+
+    # ---- device-resident timing: inputs already in HBM -------------------------------------
+    step.io.pack(wl.seqs, q_lens, 1.0 / 16.0)
+    step.io.upload()
+    step.k_dev.copy_(step.k_host)
+    step.v_dev.copy_(step.v_host)
+    step.q_dev.copy_(step.q_host)
+    torch.cuda.synchronize()
+    desc = kv._DescOnly(step.io.desc)
+    step.ex.set_stream()
+
+    def device_step(ev=None):
+        if ev is not None:
+            ev[0].record()
+        kv.kv_cache_write(step.ex, wl.layer, desc, step.k_dev, step.v_dev, lib=lib)
+        if ev is not None:
+            ev[1].record()
+        kv.paged_attention(step.ex, wl.layer, desc, step.q_dev, step.out_dev, hq, lib=lib)
+        if ev is not None:
+            ev[2].record()
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    for _ in range(args.warmup):
+        device_step()
+    barrier(world)
+    evs = [tuple(torch.cuda.Event(enable_timing=True) for _ in range(3)) for _ in range(args.steps)]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_begin = time.perf_counter()
+    e0.record()
+    for i in range(args.steps):
+        device_step(evs[i])
+    e1.record()
+    barrier(world)
+    t_end = time.perf_counter()
+    total_ms = max_over_ranks(e0.elapsed_time(e1), world)
+    ms_per_step = total_ms / args.steps
+    append_ms = float(np.mean([a.elapsed_time(b) for a, b, c in evs]))
+    attn_ms = float(np.mean([b.elapsed_time(c) for a, b, c in evs]))
+    clocks = sampler.summary(t_begin, t_end)
+    all_bytes = sum_over_ranks(float(kv_bytes), world)
+    value = all_bytes / (ms_per_step * 1e-3) / 1e9
+
+    # ---- end to end: host buffers in, host result out, every step ----------------------------
+    for _ in range(3):
+        step.run(q_lens, lib=lib)
+    barrier(world)
+    e2e_steps = max(3, min(args.steps, 200))
+    e0.record()
+    for _ in range(e2e_steps):
+        step.run(q_lens, lib=lib, sync=True)
+    e1.record()
+    barrier(world)
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1), world) / e2e_steps
+    sampler.stop_flag = True
+    e2e_value = all_bytes / (e2e_ms * 1e-3) / 1e9
+
+    status = int(step.ex.scratch[:4].cpu().numpy().view(np.int32)[0]) if not reference else 0
+
+    if rank != 0:
+        return
+    peaks, peak_kind = measured_peaks()
+    peak = float(peaks.get("hbm_gbs", FALLBACK_HBM_GBS))
+    achieved = kv_bytes / (attn_ms * 1e-3) / 1e9
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": f"{args.config}: {batch} seqs x ctx U[{lo},{hi}], {hq} q heads / {hkv} kv heads, "
+                               f"d256, TQ4 pages of 16, step = append {q_len} token/seq + decode attention",
+                   "kv_bytes_per_step_per_gpu": kv_bytes, "tokens_in_cache_per_gpu": int(sum(wl.ctx)),
+                   "l2": "KV read per step (>1.3 GB) is larger than L2; no flush needed",
+                   "per_gpu_batch": batch, "parallelism": f"batch-sharded x{world}, no collective"},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "peak_kind": f"of {peak_kind}", "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,
+                     "kernel": "tq4_attention_stream_kernel (+ plan and merge launches, timed together)",
+                     "launch_ms": attn_ms, "traffic": None},
+        "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": step.h2d_bytes,
+                "d2h_bytes_per_step": step.d2h_bytes},
+        "gpu_launches": 4 * args.steps,
+        "clocks": clocks,
+        "append_tokens_per_s": n_tok / (append_ms * 1e-3), "append_ms": append_ms, "attention_steps_per_s": 1e3 / attn_ms, "kernel_status": status,
+    }
+    if reference:
+        line["impl"] = "reference"
+        line["cpu_baseline"] = {"value": value, "unit": UNIT, "cores": 0, "kind": "reference",
+                                "sample": "the reference's CUDA kernels (op_kv_cache.cu, op_paged_attn.cu) built "
+                                          "unmodified for sm_100a, run on the GPU: the reference has no CPU path"}
+        line["gpu_launches"] = None
+        line["roofline"]["kernel"] = "reference paged_attention_gqa_mma_f16_kernel"
+    elif not args.no_cpu_baseline:
+        b = host_step_batch(kv, step, batch, n_tok)
+        line["cpu_baseline"] = cpu_baseline(wl, hq, q_new.numpy().view(np.uint16), k_new.numpy().view(np.uint16),
+                                            v_new.numpy().view(np.uint16), b.host_desc())
+    print(json.dumps(line))
+
+
+if __name__ == "__main__":
+    main()

@@ -47,6 +47,13 @@ enum {
     WARP34_ATTN_MASK_NONCAUSAL_WINDOW = 1,
 };
 
+/* warp34_exec.flags.  Bit 0 is the reference's WARP34_EXEC_FLAG_ALLOW_W4A8_PREFILL
+ * (warp34_cuda.h:46-48), ignored here.  The high bit below is additive: it makes
+ * warp34_paged_attention_f16 take the fp32 dequant-then-attend kernel (no fp16 tensor-core
+ * operands, no scratch) for callers that want scores at fp32 accuracy. */
+#define WARP34_EXEC_FLAG_ALLOW_W4A8_PREFILL (1ull << 0)
+#define WARP34_B200_EXEC_FLAG_PRECISE_ATTENTION (1ull << 40)
+
 /* ---- descriptors (reference: warp34_cuda.h:50-101) -------------------------- */
 typedef struct {
     uintptr_t stream;       /* cudaStream_t */

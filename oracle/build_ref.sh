@@ -38,6 +38,7 @@ if [ ! "$OUT/obj/op_paged_fa2.o" -nt "$CSRC/ops/op_paged_fa2.cu" ]; then
   pids+=($!)
 fi
 for p in "${pids[@]}"; do wait "$p"; done
-$NVCC -shared -o "$OUT/libwarp34_ref.so" "$OUT"/obj/op_kv_cache.o "$OUT"/obj/op_paged_attn.o \
+${CC:-gcc} -O2 -fPIC -c "$HERE/ref_link_stubs.c" -o "$OUT/obj/ref_link_stubs.o"
+$NVCC -shared -o "$OUT/libwarp34_ref.so" "$OUT"/obj/ref_link_stubs.o "$OUT"/obj/op_kv_cache.o "$OUT"/obj/op_paged_attn.o \
   "$OUT"/obj/op_init.o "$OUT"/obj/op_paged_fa2.o -lcublas -lcublasLt -lcudart
 echo "built $OUT/libwarp34_ref.so"

@@ -1,0 +1,327 @@
+"""GPU parity tests, all through the C ABI (include/warp34_b200.h).
+
+Append: packed codes, scales and untouched bytes are compared bit-for-bit with the golden fixture
+written by the reference's kernels, and with the reference library itself when
+oracle/_ref/libwarp34_ref.so travelled with the repository.  Attention: |a-b| <= 2e-3 + 1e-2|b|
+against the reference's scalar dequant-then-attend output (fixture) and the CPU oracle.
+The relational tests follow the reference's own (page-permutation invariance:
+crates/warp34-host/tests/backbone_and_collectives.rs:453-572; masks and sentinels:
+crates/warp34-host/src/cuda/tests.rs:538-572, tests/paged_fa2.rs:521-691)."""
+import ctypes as C
+import os
+
+import numpy as np
+import pytest
+
+from util import GOLDEN, f16, host_layout, tensor_core_parity, tq4_rows_equal_up_to_scale_ulp, within_tol
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+HAVE_GOLDEN = os.path.exists(GOLDEN)
+
+
+@pytest.fixture(scope="module")
+def env(native_libs):
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    from warp34_b200 import ffi, kv, synth
+    ex = kv.Executor(64 << 20)
+    return dict(ffi=ffi, kv=kv, synth=synth, ex=ex, lib=native_libs[0])
+
+
+@pytest.fixture(scope="module")
+def ref_lib(env):
+    import oracle
+    p = oracle.ref_lib_path()
+    if p is None:
+        pytest.skip("reference kernels not built (oracle/_ref)")
+    return env["ffi"].bind_kernel_abi(p)
+
+
+def _golden_workload(env, fx, fill=0x5A):
+    """Rebuilds the fixture's pool geometry: same pages, same slots."""
+    kv, synth = env["kv"], env["synth"]
+    layer = kv.KvLayer(int(fx["num_pages"]), int(fx["hkv"]), fill=fill)
+    return layer
+
+
+def _batch(env, fx, tag, slots=None, **kw):
+    kv = env["kv"]
+    if tag == "app":
+        return kv.StepBatch(fx["app_qsl"], fx["app_ctx"], fx["app_seq"], fx["app_bt"], fx["app_slots"],
+                            fx["app_bt"].shape[1], 0.0625, **kw)
+    n = int(fx[f"{tag}_query_start_loc"][-1])
+    return kv.StepBatch(fx[f"{tag}_query_start_loc"], fx[f"{tag}_context_lens_before"],
+                        fx[f"{tag}_seq_lens_after"], fx[f"{tag}_block_tables"],
+                        np.full(n, -1, np.int32) if slots is None else slots,
+                        fx[f"{tag}_block_tables"].shape[1], 0.0625, **kw)
+
+
+@pytest.mark.skipif(not HAVE_GOLDEN, reason="golden fixture missing")
+def test_append_is_bit_exact_with_reference_fixture(env):
+    fx = np.load(GOLDEN)
+    kv = env["kv"]
+    layer = _golden_workload(env, fx)
+    b = _batch(env, fx, "app")
+    k = torch.from_numpy(fx["k_in"].view(np.float16)).cuda()
+    v = torch.from_numpy(fx["v_in"].view(np.float16)).cuda()
+    kv.kv_cache_write(env["ex"], layer, b, k, v)
+    torch.cuda.synchronize()
+    assert (layer.k.cpu().numpy() == fx["k_pool"]).all()
+    assert (layer.v.cpu().numpy() == fx["v_pool"]).all()
+
+
+def test_append_is_bit_exact_with_reference_kernels_cfg0(env, ref_lib):
+    """Config 0 of the benchmark: 4 sequences, contexts in [1024, 4096], 4 KV heads, shuffled pages."""
+    kv, synth = env["kv"], env["synth"]
+    ctx = synth.context_lengths(4, 1024, 4096, 0)
+    T = int(ctx.sum())
+    k, v = synth.make_kv(T, 4, 0)
+    kd, vd = k.cuda(), v.cuda()
+    pools = []
+    for lib in (None, ref_lib):
+        wl = synth.PagedWorkload([0] * 4, [int(c) for c in ctx], 4, seed=0, fill=0xA5)
+        kv.kv_cache_write(env["ex"], wl.layer, wl.step(), kd, vd, lib=lib)
+        torch.cuda.synchronize()
+        pools.append((wl.layer.k.cpu().numpy(), wl.layer.v.cpu().numpy(), wl))
+    assert (pools[0][0] == pools[1][0]).all() and (pools[0][1] == pools[1][1]).all()
+    # and the CPU oracle agrees except for rare last-place differences of the fp16 scales
+    import oracle
+    wl = pools[0][2]
+    hk, hv = np.full_like(pools[0][0], 0xA5), np.full_like(pools[0][1], 0xA5)
+    lay = host_layout(wl.layer.layout, hk, hv)
+    assert oracle.kv_cache_write(lay, wl.step().host_desc(), k.numpy().view(np.uint16),
+                                 v.numpy().view(np.uint16), 1024, 1024, nthreads=8) == 0
+    for got, want in ((hk, pools[0][0]), (hv, pools[0][1])):
+        code_mism, scale_mism, ulp = tq4_rows_equal_up_to_scale_ulp(got, want)
+        assert code_mism <= 2 and ulp <= 1 and scale_mism <= got.size // 66 // 2000 + 2
+
+
+def test_append_masks_strides_and_sentinels(env):
+    """valid_token_mask / valid_req_mask / negative slots have no side effects, K and V may be
+    column slices of one packed activation, and bytes outside written rows are untouched."""
+    kv, synth, ffi = env["kv"], env["synth"], env["ffi"]
+    hkv, T = 2, 37
+    packed = torch.zeros(T, 3 * hkv * 256 + 64, dtype=torch.float16)
+    k, v = synth.make_kv(T, hkv, 77)
+    packed[:, 512:512 + hkv * 256] = k
+    packed[:, 512 + hkv * 256:512 + 2 * hkv * 256] = v
+    pd = packed.cuda()
+    kview, vview = pd[:, 512:512 + hkv * 256], pd[:, 512 + hkv * 256:512 + 2 * hkv * 256]
+    qsl = [0, 10, 10, 30, 37]
+    slots = np.array([16 * (5 + t // 16) + t % 16 for t in range(T)], np.int32)
+    slots[3] = -1
+    vtm = np.ones(T, np.uint8)
+    vtm[7] = 0
+    vrm = np.array([1, 1, 1, 0], np.uint8)  # last request (tokens 30..36) masked
+    bt = np.zeros((4, 4), np.int32)
+
+    def run(masked):
+        layer = kv.KvLayer(12, hkv, fill=0x55)
+        b = kv.StepBatch(qsl, [0, 0, 0, 0], [10, 0, 20, 7], bt, slots, 4, 0.0625,
+                         valid_token_mask=vtm if masked else None, valid_req_mask=vrm if masked else None)
+        kv.kv_cache_write(env["ex"], layer, b, kview, vview, k_row_stride=pd.stride(0), v_row_stride=pd.stride(0))
+        torch.cuda.synchronize()
+        return layer.k.cpu().numpy().reshape(12, hkv, 16, 132), layer.v.cpu().numpy().reshape(12, hkv, 16, 132)
+
+    km, vm = run(True)
+    # contiguous inputs give the same bytes as the strided views
+    layer2 = kv.KvLayer(12, hkv, fill=0x55)
+    s2 = slots.copy()
+    b2 = kv.StepBatch(qsl, [0] * 4, [10, 0, 20, 7], bt, s2, 4, 0.0625)
+    kv.kv_cache_write(env["ex"], layer2, b2, k.cuda(), v.cuda())
+    torch.cuda.synchronize()
+    kc = layer2.k.cpu().numpy().reshape(12, hkv, 16, 132)
+    vc = layer2.v.cpu().numpy().reshape(12, hkv, 16, 132)
+    for t in range(T):
+        page, off = 5 + t // 16, t % 16
+        skipped = t == 3 or t == 7 or t >= 30
+        for h in range(hkv):
+            if skipped:
+                assert (km[page, h, off] == 0x55).all() and (vm[page, h, off] == 0x55).all()
+            else:
+                assert (km[page, h, off] == kc[page, h, off]).all() and (vm[page, h, off] == vc[page, h, off]).all()
+    untouched = np.ones(12, bool)
+    untouched[5:8] = False
+    assert (km[untouched] == 0x55).all() and (vm[untouched] == 0x55).all()
+    assert (km[7, :, 5:] == 0x55).all()  # rows past the last token of page 7
+    # stride below heads * 256 is rejected
+    rc = env["lib"].warp34_kv_cache_write_strided(C.byref(env["ex"].ex), C.byref(layer2.layout), C.byref(b2.desc),
+                                                  k.cuda().data_ptr(), v.cuda().data_ptr(), 256, 512)
+    assert rc == ffi.CUDA_ERROR_INVALID_VALUE
+
+
+@pytest.mark.skipif(not HAVE_GOLDEN, reason="golden fixture missing")
+@pytest.mark.parametrize("tag", ["dec", "ver"])
+@pytest.mark.parametrize("scalar", [False, True])
+def test_attention_matches_reference_dequant_then_attend(env, tag, scalar):
+    fx = np.load(GOLDEN)
+    kv = env["kv"]
+    layer = _golden_workload(env, fx)
+    layer.k.copy_(torch.from_numpy(fx["k_pool"]))
+    layer.v.copy_(torch.from_numpy(fx["v_pool"]))
+    b = _batch(env, fx, tag)
+    q = torch.from_numpy(fx[f"q_{tag}"].view(np.float16)).cuda()
+    out = torch.zeros_like(q)
+    kv.paged_attention(env["ex"], layer, b, q, out, int(fx["hq"]), scalar=scalar)
+    torch.cuda.synchronize()
+    got = out.float().cpu().numpy()
+    want = f16(fx[f"out_{tag}"])
+    if scalar:
+        ok = within_tol(got, want)
+        assert ok.all(), f"{(~ok).sum()} of {ok.size} outside tolerance, max abs {np.abs(got - want).max()}"
+    else:
+        ok, msg = tensor_core_parity(got, want)
+        assert ok, msg
+
+
+def _decode_case(env, ctx, hq, hkv, seed, q_lens=None, shuffle=True, fill=None):
+    kv, synth = env["kv"], env["synth"]
+    q_lens = q_lens or [1] * len(ctx)
+    wl = synth.PagedWorkload([0] * len(ctx), [int(c) for c in ctx], hkv, seed=seed, shuffle=shuffle, fill=fill)
+    k, v = synth.make_kv(int(sum(ctx)), hkv, seed)
+    kv.kv_cache_write(env["ex"], wl.layer, wl.step(), k.cuda(), v.cuda())
+    for s, c, ql in zip(wl.seqs, ctx, q_lens):
+        s.commit(int(c) - ql)
+    q = synth.make_q(sum(q_lens), hq, seed)
+    return wl, q
+
+
+def _oracle_attention(wl, batch, q, hq, nthreads=8):
+    import oracle
+    hk, hv = wl.layer.k.cpu().numpy(), wl.layer.v.cpu().numpy()
+    lay = host_layout(wl.layer.layout, hk, hv)
+    out = np.zeros((q.shape[0], hq, 256), np.uint16)
+    assert oracle.paged_attention(lay, batch.host_desc(), q.numpy().view(np.uint16), out, hq, nthreads=nthreads) == 0
+    return f16(out)
+
+
+@pytest.mark.parametrize("hq,hkv,q_len", [(16, 4, 1), (24, 4, 1), (24, 4, 4), (8, 8, 1), (20, 2, 3)])
+def test_attention_matches_cpu_oracle_on_ragged_batches(env, hq, hkv, q_len):
+    kv = env["kv"]
+    ctx = [1, 15, 16, 17, 250, 1000, 33]
+    ctx = [max(c, q_len) for c in ctx]
+    wl, q = _decode_case(env, ctx, hq, hkv, seed=100 + hq + q_len, q_lens=[q_len] * len(ctx))
+    b = wl.step(q_lens=[q_len] * len(ctx))
+    out = torch.full((q.shape[0], hq, 256), 9.0, dtype=torch.float16, device="cuda")
+    kv.paged_attention(env["ex"], wl.layer, b, q.cuda(), out, hq)
+    torch.cuda.synchronize()
+    want = _oracle_attention(wl, b, q, hq)
+    got = out.float().cpu().numpy()
+    ok, msg = tensor_core_parity(got, want)
+    assert ok, msg
+    status = int(env["ex"].scratch[:4].cpu().numpy().view(np.int32)[0])
+    assert status == 0
+    # the fp32 path, selected by the exec flag, meets the plain elementwise bound
+    precise = kv.Executor(1 << 20)
+    precise.ex.flags = env["ffi"].EXEC_FLAG_PRECISE_ATTENTION
+    out2 = torch.zeros_like(out)
+    kv.paged_attention(precise, wl.layer, b, q.cuda(), out2, hq)
+    torch.cuda.synchronize()
+    ok2 = within_tol(out2.float().cpu().numpy(), want)
+    assert ok2.all(), f"fp32 path: {(~ok2).sum()} of {ok2.size} outside tolerance"
+
+
+def test_page_permutation_invariance_is_zero_ulp(env):
+    """Same tokens at pages [1,2,3,...] and at a shuffled placement: identical output bits."""
+    kv = env["kv"]
+    ctx, hq, hkv = [40, 700], 8, 2
+    outs = []
+    for shuffle in (False, True):
+        wl, q = _decode_case(env, ctx, hq, hkv, seed=9, shuffle=shuffle)
+        b = wl.step(q_lens=[1, 1])
+        out = torch.zeros(2, hq, 256, dtype=torch.float16, device="cuda")
+        kv.paged_attention(env["ex"], wl.layer, b, q.cuda(), out, hq)
+        torch.cuda.synchronize()
+        outs.append(out.cpu().numpy().view(np.uint16))
+        pages = [s.pages for s in wl.seqs]
+    assert pages[0] != sorted(pages[0])
+    assert (outs[0] == outs[1]).all()
+
+
+def test_masks_windows_and_untouched_rows(env):
+    """Masked tokens / requests leave their output rows untouched; sliding window and the
+    non-causal window mode agree with the CPU oracle."""
+    kv = env["kv"]
+    ctx, hq, hkv, ql = [90, 41, 300], 8, 2, 3
+    wl, q = _decode_case(env, ctx, hq, hkv, seed=21, q_lens=[ql] * 3)
+    sentinel = np.float16(0.0).view(np.uint16) + 0x5500
+    for mode, window in ((0, 0), (0, 33), (1, 50), (1, 0)):
+        vtm = np.ones(9, np.uint8)
+        vtm[4] = 0
+        vrm = np.array([1, 1, 0], np.uint8)
+        b = wl.step(q_lens=[ql] * 3, mask_mode=mode, sliding_window=window, valid_token_mask=vtm, valid_req_mask=vrm)
+        out = torch.from_numpy(np.full((9, hq, 256), sentinel, np.uint16).view(np.float16)).cuda()
+        kv.paged_attention(env["ex"], wl.layer, b, q.cuda(), out, hq)
+        torch.cuda.synchronize()
+        got_bits = out.cpu().numpy().view(np.uint16)
+        assert (got_bits[4] == sentinel).all() and (got_bits[6:] == sentinel).all()
+        want = _oracle_attention(wl, b, q, hq)
+        live = [0, 1, 2, 3, 5]
+        ok, msg = tensor_core_parity(f16(got_bits[live]), want[live])
+        assert ok, (mode, window, msg)
+
+
+def test_block_table_entries_past_the_sequence_are_never_used(env):
+    """Entries beyond ceil(seq_len / 16) point at a page whose scales are NaN: any use of them
+    would poison the output (the reference's tight-block-table test, tests/paged_fa2.rs:521-616)."""
+    kv = env["kv"]
+    ctx, hq, hkv = [37, 64], 8, 2
+    wl, q = _decode_case(env, ctx, hq, hkv, seed=31)
+    poison = wl.pool.alloc_page()
+    kview = wl.layer.k.view(wl.num_pages, -1)
+    vview = wl.layer.v.view(wl.num_pages, -1)
+    kview[poison] = 0x7E
+    vview[poison] = 0x7E  # fp16 0x7e7e is NaN
+    b = wl.step(q_lens=[1, 1])
+    bt = b.host["block_tables"].copy()
+    for i, c in enumerate(ctx):
+        bt[i, (c + 15) // 16:] = poison
+    b2 = kv.StepBatch(b.host["query_start_loc"], b.host["context_lens_before"], b.host["seq_lens_after"], bt,
+                      b.host["write_slot_mapping"], bt.shape[1], 0.0625)
+    out = torch.zeros(2, hq, 256, dtype=torch.float16, device="cuda")
+    kv.paged_attention(env["ex"], wl.layer, b2, q.cuda(), out, hq)
+    torch.cuda.synchronize()
+    got = out.float().cpu().numpy()
+    assert np.isfinite(got).all()
+    ok, msg = tensor_core_parity(got, _oracle_attention(wl, b, q, hq))
+    assert ok, msg
+
+
+def test_small_scratch_and_odd_strides_fall_back_to_the_scalar_kernel(env):
+    kv, ffi = env["kv"], env["ffi"]
+    ctx, hq, hkv = [100, 20], 8, 2
+    wl, q = _decode_case(env, ctx, hq, hkv, seed=41)
+    b = wl.step(q_lens=[1, 1])
+    want = _oracle_attention(wl, b, q, hq)
+    tiny = kv.Executor(4096)
+    out = torch.zeros(2, hq, 256, dtype=torch.float16, device="cuda")
+    kv.paged_attention(tiny, wl.layer, b, q.cuda(), out, hq)
+    torch.cuda.synchronize()
+    assert within_tol(out.float().cpu().numpy(), want).all()
+    # empty batch: success, nothing launched, output untouched
+    empty = ffi.AttentionBatch()
+    rc = env["lib"].warp34_paged_attention_f16(C.byref(env["ex"].ex), C.byref(wl.layer.layout), C.byref(empty),
+                                               q.cuda().data_ptr(), out.data_ptr(), hq)
+    assert rc == 0
+
+
+def test_split_partitioning_does_not_change_the_result_beyond_tolerance(env):
+    """The same step with scratch for 12 worker warps and for the full grid: different
+    cuts of the KV stream, same answer (merge algebra of op_paged_attn.cu:1168-1202)."""
+    kv = env["kv"]
+    ctx, hq, hkv = [5000, 1234, 16, 9000], 24, 4
+    wl, q = _decode_case(env, ctx, hq, hkv, seed=51)
+    b = wl.step(q_lens=[1] * 4)
+    outs = []
+    need_min = 4096 + (12 + 4 * 8) * (8 * 256 + 16) * 4 + (24 * 2064 * 4)
+    for ex in (env["ex"], kv.Executor(need_min)):
+        out = torch.zeros(4, hq, 256, dtype=torch.float16, device="cuda")
+        kv.paged_attention(ex, wl.layer, b, q.cuda(), out, hq)
+        torch.cuda.synchronize()
+        outs.append(out.float().cpu().numpy())
+    want = _oracle_attention(wl, b, q, hq)
+    for o in outs:
+        ok, msg = tensor_core_parity(o, want)
+        assert ok, msg
+    assert np.abs(outs[0] - outs[1]).max() <= 2e-3 + 1e-2 * np.abs(want).max()

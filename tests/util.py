@@ -1,0 +1,107 @@
+"""Helpers shared by the parity tests."""
+import ctypes as C
+import os
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+GOLDEN = os.path.join(ROOT, "tests", "golden", "tq4_ref_sm100a.npz")
+
+# Attention tolerance of this path: |a - b| <= 2e-3 + 1e-2 |b|, a and b as fp16 outputs
+# compared in fp32 (the dequant-then-attend result is b).
+ATOL, RTOL = 2e-3, 1e-2
+
+
+def within_tol(a, b):
+    a = np.asarray(a, np.float32)
+    b = np.asarray(b, np.float32)
+    return np.abs(a - b) <= ATOL + RTOL * np.abs(b)
+
+
+# The tensor-core kernel feeds fp16 operands (rotated Q, codebook values, softmax weights) to
+# the MMAs, like the reference's production kernel (op_paged_attn.cu:357, :470, :47-50).  A
+# relative error eps in a softmax weight moves an output channel by eps * |V value|, not by
+# eps * |average|: where a x20 outlier channel of two dominant keys cancels, the output is near
+# zero while the error scales with the row's largest magnitude.  The elementwise bound therefore
+# holds for all but a few elements in 10^5, and every element is inside the bound with an extra
+# absolute term proportional to the row maximum.  The fp32 kernel meets the plain bound.
+ROW_TERM = 2.5e-4
+MIN_FRACTION_WITHIN = 0.9998
+
+
+def tensor_core_parity(a, b):
+    """Returns (ok, message) for the fp16-operand kernel against dequant-then-attend."""
+    a = np.asarray(a, np.float32)
+    b = np.asarray(b, np.float32)
+    d = np.abs(a - b)
+    plain = d <= ATOL + RTOL * np.abs(b)
+    rowmax = np.abs(b).max(axis=-1, keepdims=True)
+    capped = d <= ATOL + RTOL * np.abs(b) + ROW_TERM * rowmax
+    frac = plain.mean()
+    msg = (f"{(~plain).sum()} of {plain.size} outside 2e-3 + 1e-2|b| (fraction inside {frac:.6f}), "
+           f"{(~capped).sum()} outside the row-scaled bound, max abs {d.max():.3e}")
+    return bool(capped.all() and frac >= MIN_FRACTION_WITHIN), msg
+
+
+def f16(bits):
+    return np.asarray(bits, np.uint16).view(np.float16).astype(np.float32)
+
+
+def host_layout(layer_layout, k_pool, v_pool):
+    """A copy of a layer descriptor whose bases point at host slabs (for the CPU oracle)."""
+    from warp34_b200 import ffi
+    lay = ffi.KvLayerLayout()
+    C.memmove(C.byref(lay), C.byref(layer_layout), C.sizeof(lay))
+    lay.k_base = k_pool.ctypes.data
+    lay.v_base = v_pool.ctypes.data
+    return lay
+
+
+def canonical_layout(hkv, num_pages=0):
+    from warp34_b200 import ffi
+    lay = ffi.KvLayerLayout()
+    f = (C.c_int32 * 4)(2, 2, 1, 1)
+    rc = ffi.host().w34_kv_layout_init(C.byref(lay), 0, 0, 0, 0, hkv, 256, 16, f, num_pages, None, None)
+    assert rc == 0
+    return lay
+
+
+def host_batch(qsl, ctx, seq, bt, slots=None, sm_scale=0.0625, mask_mode=0, window=0, vtm=None, vrm=None):
+    """warp34_attention_batch over host numpy arrays; returns (desc, keepalive)."""
+    from warp34_b200 import ffi
+    arrs = dict(qsl=np.ascontiguousarray(qsl, np.int32), ctx=np.ascontiguousarray(ctx, np.int32),
+                seq=np.ascontiguousarray(seq, np.int32), bt=np.ascontiguousarray(bt, np.int32),
+                slots=None if slots is None else np.ascontiguousarray(slots, np.int32),
+                vtm=None if vtm is None else np.ascontiguousarray(vtm, np.uint8),
+                vrm=None if vrm is None else np.ascontiguousarray(vrm, np.uint8))
+    b = ffi.AttentionBatch()
+    b.query_start_loc = arrs["qsl"].ctypes.data
+    b.context_lens_before = arrs["ctx"].ctypes.data
+    b.seq_lens_after = arrs["seq"].ctypes.data
+    b.block_tables = arrs["bt"].ctypes.data
+    b.write_slot_mapping = None if arrs["slots"] is None else arrs["slots"].ctypes.data
+    b.valid_token_mask = None if arrs["vtm"] is None else arrs["vtm"].ctypes.data
+    b.valid_req_mask = None if arrs["vrm"] is None else arrs["vrm"].ctypes.data
+    b.num_reqs = len(arrs["qsl"]) - 1
+    b.total_tokens = int(arrs["qsl"][-1])
+    b.max_blocks_per_req = arrs["bt"].shape[1] if arrs["bt"].ndim == 2 else len(arrs["bt"])
+    q = np.diff(arrs["qsl"])
+    b.max_q_len = int(q.max()) if len(q) else 0
+    b.max_seq_len = int(arrs["seq"].max()) if len(arrs["seq"]) else 0
+    b.mask_mode = mask_mode
+    b.sliding_window = window
+    b.sm_scale = sm_scale
+    return b, arrs
+
+
+def tq4_rows_equal_up_to_scale_ulp(a, b):
+    """Compares two TQ4 slabs: packed codes must be identical; fp16 scales may differ by one
+    unit in the last place (IEEE division on the CPU against the GPU's approximate division).
+    Returns (code_byte_mismatches, scale_mismatches, max_scale_ulp)."""
+    a = np.asarray(a, np.uint8).reshape(-1, 66)
+    b = np.asarray(b, np.uint8).reshape(-1, 66)
+    code_mism = int((a[:, 2:] != b[:, 2:]).sum())
+    sa = a[:, :2].copy().view(np.uint16).astype(np.int32).ravel()
+    sb = b[:, :2].copy().view(np.uint16).astype(np.int32).ravel()
+    diff = np.abs(sa - sb)
+    return code_mism, int((diff != 0).sum()), int(diff.max()) if diff.size else 0

@@ -28,20 +28,21 @@
 
 namespace w34 {
 
-// The reference computes warp_reduce_sum(a * b); nvcc contracts the first butterfly add
-// with the product into an fma (the product that is shuffled is still rounded).  Lanes
-// with column bit 4 clear ("lo class") then hold fma(a_lo, b_lo, rn(a_hi*b_hi)) while
-// lanes with bit 4 set hold fma(a_hi, b_hi, rn(a_lo*b_lo)): two different sums that
-// stay separate through the remaining symmetric levels.  kContract* say, per quantity,
-// whether that contraction is emulated; with it off both classes are the plain sum.
+// The reference computes warp_reduce_sum(a * b): the product is rounded, then summed by the
+// butterfly.  Had the compiler contracted the first butterfly add with the product into an
+// fma, lanes with column bit 4 clear ("lo class") would hold fma(a_lo, b_lo, rn(a_hi*b_hi))
+// and the others fma(a_hi, b_hi, rn(a_lo*b_lo)): two different sums.  Comparing all eight
+// on/off combinations against the reference kernels built for sm_100a showed that it does
+// not (all three off is bit-identical; turning either least-squares sum on is not), so the
+// switches default to 0; the emulation stays for re-checking against another toolchain.
 #ifndef W34_CONTRACT_SQ
-#define W34_CONTRACT_SQ 1
+#define W34_CONTRACT_SQ 0
 #endif
 #ifndef W34_CONTRACT_VC
-#define W34_CONTRACT_VC 1
+#define W34_CONTRACT_VC 0
 #endif
 #ifndef W34_CONTRACT_CC
-#define W34_CONTRACT_CC 1
+#define W34_CONTRACT_CC 0
 #endif
 
 // code = #{i : rv > boundary_i} for the 15 ascending, symmetric boundaries (b[7] = 0).

@@ -144,11 +144,16 @@ __global__ void __launch_bounds__(128) tq4_attention_scalar_kernel(
 // Split-KV streaming path
 // ---------------------------------------------------------------------------------------
 constexpr int kRowsPerGroup = 8;            // N of the MMA: query rows per work item
-constexpr int kStageBytes = 2 * kTq4PageHeadBytes;  // K run then V run of one (page, head)
-constexpr int kLutBytes = 256 * 32 * 4;     // byte-pair table, one copy per lane
+constexpr int kLutBytes = 256 * 256;         // byte-pair table: 256-byte entry stride, 32 lane copies each
 constexpr int kPartialFloats = kRowsPerGroup * kHeadDim + 2 * kRowsPerGroup;
 constexpr long long kWaitCycleLimit = 1ll << 31;  // about one second of SM clocks
 constexpr int kMinUnitsPerWarp = 4;
+// The lookup table holds fp16(kLutScale * centroid).  fp16 rounding of the 8 centroid
+// magnitudes is a systematic error of up to 3.7e-4 relative; with this common factor every one
+// of them lands within 9.5e-5 of an fp16 grid point (found by exhaustive search over
+// [0.5, 2)), and the factor itself is divided out exactly: 1/kLutScale is folded into Q' for
+// the scores and into the final normalisation for the output.
+constexpr float kLutScale = 0.954016f;
 
 // Scratch header written by the plan kernel.
 struct PlanHeader {
@@ -176,7 +181,8 @@ struct StreamParams {
     int gqa;
     int num_warps;         // worker warps over the whole grid
     int max_slots;
-    float q_scale;         // sm_scale * log2(e), folded into Q'
+    uint32_t smem_bytes;   // dynamic shared memory given to the stream kernel
+    float q_scale;         // sm_scale * log2(e) / kLutScale, folded into Q'
 };
 
 __device__ __forceinline__ int32_t* plan_array(uint8_t* scratch, int which, int num_reqs) {
@@ -277,6 +283,9 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
 __device__ __forceinline__ void fence_proxy_async() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
+__device__ __forceinline__ void sts32(uint32_t addr, uint32_t v) {
+    asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
 __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
     uint32_t v;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
@@ -314,22 +323,70 @@ __device__ __forceinline__ int vword_col(int half, int vw, int e) {
     return 8 * vw - 4 + e;
 }
 
+// Shared-memory stage of one (page, kv head): each 2112-byte run is brought in as two
+// 1056-byte halves (tokens 0-7, tokens 8-15) with 32 bytes of padding between them, so that
+// token t sits at bank offset t (t < 8) or t + 8 (t >= 8).  With 33-word rows that makes every
+// code load below hit 32 distinct banks:
+//   K: one load covers tokens {0..3} u {8..11} (or {4..7} u {12..15}) x words {w, w+4, w+8, w+12};
+//   V: one load covers tokens {k, k+2, k+8, k+10} x words {0,1,4,5,8,9,12,13} (+2).
+constexpr int kHalfBytes = 8 * kTq4RowBytes;       // 1056
+constexpr int kHalfStride = kHalfBytes + 32;       // 1088
+constexpr int kRunStride = 2 * kHalfStride - 32;   // 2144: K run, then V run
+constexpr int kStageStride = 2 * kRunStride;       // 4288
+
+__device__ __forceinline__ uint32_t token_offset(int t) {  // byte offset of token row t in a run
+    return (uint32_t)((t >> 3) * kHalfStride + (t & 7) * kTq4RowBytes);
+}
+
+#ifndef W34_WARPS
+#define W34_WARPS 12
+#endif
+#ifndef W34_STAGES
+#define W34_STAGES 3
+#endif
+// Optional extra-precision MMAs (compile-time).  Measured on the 64-sequence decode benchmark:
+// SPLIT_Q adds 22% to the kernel time and cuts score errors about 4x (Q' is then accurate to
+// 2^-14 instead of 2^-11); SPLIT_P adds 8% and only matters for softmaxes over a handful of keys.
+// Both are off by default: the fp16 lookup-table values of K bound the score accuracy either
+// way, and callers that need fp32 scores can set WARP34_B200_EXEC_FLAG_PRECISE_ATTENTION.
+#ifndef W34_SPLIT_Q
+#define W34_SPLIT_Q 0   // second QK MMA with the fp16 rounding residual of Q'
+#endif
+#ifndef W34_SPLIT_P
+#define W34_SPLIT_P 0   // second PV MMA with the fp16 rounding residual of P * d_v
+#endif
+
 template <int STAGES>
-__global__ void __launch_bounds__(384, 1) tq4_attention_stream_kernel(const StreamParams p) {
-    extern __shared__ __align__(128) uint8_t smem[];
-    // [lut 32 KB][per warp: STAGES x 4224 B][per warp: STAGES mbarriers]
+__global__ void __launch_bounds__(W34_WARPS * 32, 1) tq4_attention_stream_kernel(const StreamParams p) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    // The lookup table sits at the first 64 KB-aligned SHARED address inside the dynamic window,
+    // so that (table address | code byte << 8 | lane << 2) is one PRMT.  Warp rings fill the
+    // space below and above it; the mbarriers follow the last ring.
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int warps_per_cta = blockDim.x >> 5;
-    const uint32_t lut_base = smem_u32(smem);
-    uint8_t* ring_gen = smem + kLutBytes + (size_t)wid * STAGES * kStageBytes;
-    const uint32_t ring = smem_u32(ring_gen);
-    const uint32_t bars = smem_u32(smem + kLutBytes + (size_t)warps_per_cta * STAGES * kStageBytes) +
-                          (uint32_t)wid * STAGES * 8u;
+    const uint32_t win_lo = smem_u32(smem);
+    const uint32_t win_hi = win_lo + p.smem_bytes;
+    const uint32_t lut_addr = (win_lo + 0xffffu) & ~0xffffu;
+    constexpr uint32_t kRingBytes = STAGES * kStageStride;
+    const uint32_t warps_below = (lut_addr - win_lo) / kRingBytes;
+    const uint32_t ring = ((uint32_t)wid < warps_below) ? (win_lo + (uint32_t)wid * kRingBytes)
+                                                         : (lut_addr + kLutBytes + ((uint32_t)wid - warps_below) * kRingBytes);
+    const uint32_t above = (uint32_t)warps_per_cta > warps_below ? (uint32_t)warps_per_cta - warps_below : 0u;
+    const uint32_t bars_base = lut_addr + kLutBytes + above * kRingBytes;
+    const uint32_t bars = bars_base + (uint32_t)wid * STAGES * 8u;
+    PlanHeader* hdr = reinterpret_cast<PlanHeader*>(p.scratch);
+    if (lut_addr + kLutBytes > win_hi || bars_base + (uint32_t)warps_per_cta * STAGES * 8u > win_hi) {
+        if (threadIdx.x == 0) atomicOr(&hdr->status, 2);  // shared-memory window cannot hold the layout
+        return;
+    }
+    uint8_t* ring_gen = smem + (ring - win_lo);
 
-    // Byte-pair table: entry (byte, lane) = half2(centroid[byte & 15], centroid[byte >> 4]).
+    // Byte-pair table: entry (byte, lane) at byte * 256 + lane * 4 holds
+    // half2(s * centroid[byte & 15], s * centroid[byte >> 4]); bank = lane for any data.
     for (int i = threadIdx.x; i < 256 * 32; i += blockDim.x) {
-        const int byte = i >> 5;
-        reinterpret_cast<uint32_t*>(smem)[i] = pack_half2(tq4_centroid(byte & 15), tq4_centroid(byte >> 4));
+        const int byte = i >> 5, ln = i & 31;
+        sts32(lut_addr + (uint32_t)(byte * 256 + ln * 4),
+              pack_half2(kLutScale * tq4_centroid(byte & 15), kLutScale * tq4_centroid(byte >> 4)));
     }
     if (lane == 0) {
         for (int s = 0; s < STAGES; ++s) mbar_init(bars + 8u * s, 1u);
@@ -338,7 +395,6 @@ __global__ void __launch_bounds__(384, 1) tq4_attention_stream_kernel(const Stre
     __syncthreads();
 
     const int R = p.batch.num_reqs;
-    PlanHeader* hdr = reinterpret_cast<PlanHeader*>(p.scratch);
     const int32_t* unit_prefix = plan_array(p.scratch, 0, R);
     const int32_t* item_prefix = plan_array(p.scratch, 1, R);
     const int32_t* page_lo_a = plan_array(p.scratch, 2, R);
@@ -355,10 +411,11 @@ __global__ void __launch_bounds__(384, 1) tq4_attention_stream_kernel(const Stre
     const int u_end = min(u + per, total_units);
 
     const int gid = lane >> 2, tig = lane & 3;
-    // MMA row m (0..7) <-> key pk within the page; row m + 8 <-> key pk + 8.  The permutation
-    // gives thread tig the keys {tig, tig+4, tig+8, tig+12} in the PV product.
-    const int pk = (gid >> 1) + 4 * (gid & 1);
-    const uint32_t lut_lane = lut_base + 4u * lane;
+    // MMA row m of S^T <-> token key(m) = (m & 3) + 8 ((m >> 2) & 1) + 4 (m >> 3) of the page.
+    const int key_a = (gid & 3) + 8 * (gid >> 2);      // row gid; row gid + 8 is token key_a + 4
+    // In the PV product thread tig owns tokens kv0 + {0, 1, 4, 5} (k positions 2tig, 2tig+1, +8, +9).
+    const int kv0 = 2 * (tig & 1) + 8 * (tig >> 1);
+    const uint32_t lut_lane = lut_addr + 4u * lane;  // byte 1 is zero: the code byte goes there
     uint32_t phase_bits = 0;   // bit s = parity to wait for on stage s
     uint32_t pending = 0;      // bit s = a copy into stage s has been issued and not yet awaited
     bool failed = false;
@@ -411,8 +468,8 @@ __global__ void __launch_bounds__(384, 1) tq4_attention_stream_kernel(const Stre
         }
 
         // ---- stage Q' for the group's rows: ring memory is idle here ---------------------
-        // layout: fp16 [8 rows][256 rotated columns], pre-multiplied by sm_scale * log2(e)
-        __half* q_stage = reinterpret_cast<__half*>(ring_gen);
+        // layout: fp32 [8 rows][256 rotated columns], pre-multiplied by q_scale
+        float* q_stage = reinterpret_cast<float*>(ring_gen);
         for (int row8 = 0; row8 < kRowsPerGroup; ++row8) {
             const int row = group * kRowsPerGroup + row8;
             const int q_off = row / p.gqa;
@@ -430,24 +487,36 @@ __global__ void __launch_bounds__(384, 1) tq4_attention_stream_kernel(const Stre
                 for (int j = 0; j < 8; ++j) t[j] = 0.0f;
             }
 #pragma unroll
-            for (int j = 0; j < 8; ++j) q_stage[row8 * kHeadDim + lane + 32 * j] = __float2half_rn(t[j] * p.q_scale);
+            for (int j = 0; j < 8; ++j) q_stage[row8 * kHeadDim + lane + 32 * j] = t[j] * p.q_scale;
         }
         __syncwarp();
         // B fragments of Q'^T: step s (0..7) covers half s >> 2, virtual word 4 tig + (s & 3);
         // k-step 2 s uses elements 0..3 of the word, k-step 2 s + 1 elements 4..7.
+        // Q' = hi + lo: hi is fp16, lo (the fp16 rounding residual) is kept as 4 e5m2 bytes per
+        // k-step and widened to fp16 pairs by two PRMTs right before its MMA.
         uint32_t qb[16][2];
+        uint32_t qlo[16];
 #pragma unroll
         for (int s = 0; s < 8; ++s) {
             const int half = s >> 2, vw = 4 * tig + (s & 3);
 #pragma unroll
             for (int hk = 0; hk < 2; ++hk) {
+                uint32_t lo_bytes = 0;
 #pragma unroll
                 for (int x = 0; x < 2; ++x) {
                     const int e = 4 * hk + 2 * x;
-                    const __half lo = q_stage[gid * kHeadDim + vword_col(half, vw, e)];
-                    const __half hi = q_stage[gid * kHeadDim + vword_col(half, vw, e + 1)];
-                    qb[2 * s + hk][x] = (uint32_t)__half_as_ushort(lo) | ((uint32_t)__half_as_ushort(hi) << 16);
+                    const float f0 = q_stage[gid * kHeadDim + vword_col(half, vw, e)];
+                    const float f1 = q_stage[gid * kHeadDim + vword_col(half, vw, e + 1)];
+                    const __half h0 = __float2half_rn(f0), h1 = __float2half_rn(f1);
+                    qb[2 * s + hk][x] = (uint32_t)__half_as_ushort(h0) | ((uint32_t)__half_as_ushort(h1) << 16);
+                    // residuals, rounded to the top byte of their fp16 encoding (e5m2)
+                    const uint32_t r0 = __half_as_ushort(__float2half_rn(f0 - __half2float(h0)));
+                    const uint32_t r1 = __half_as_ushort(__float2half_rn(f1 - __half2float(h1)));
+                    const uint32_t b0 = (r0 + 0x7fu + ((r0 >> 8) & 1u)) >> 8;
+                    const uint32_t b1 = (r1 + 0x7fu + ((r1 >> 8) & 1u)) >> 8;
+                    lo_bytes |= (b0 & 0xffu) << (16 * x) | (b1 & 0xffu) << (16 * x + 8);
                 }
+                qlo[2 * s + hk] = lo_bytes;
             }
         }
         __syncwarp();
@@ -467,17 +536,20 @@ __global__ void __launch_bounds__(384, 1) tq4_attention_stream_kernel(const Stre
         int32_t next_page = (32 + lane < n_here) ? blocks[pg0 + 32 + lane] : 0;
 
         fence_proxy_async();  // the staging writes above precede async-proxy writes to the ring
-        auto issue = [&](int idx) {  // called by all lanes; lane 0 issues the two copies
+        auto issue = [&](int idx) {  // called by all lanes; lane 0 issues the four copies
             const int32_t page = __shfl_sync(0xffffffffu, (idx & 32) ? next_page : my_page, idx & 31);
             pending |= 1u << (idx % STAGES);
             if (lane == 0) {
                 const int s = idx % STAGES;
                 const uint32_t bar = bars + 8u * s;
-                const uint32_t dst = ring + (uint32_t)s * kStageBytes;
-                mbar_expect_tx(bar, kStageBytes);
-                bulk_g2s(dst, k_head_base + (size_t)page * p.layout.k_page_stride_bytes, kTq4PageHeadBytes, bar);
-                bulk_g2s(dst + kTq4PageHeadBytes, v_head_base + (size_t)page * p.layout.v_page_stride_bytes,
-                         kTq4PageHeadBytes, bar);
+                const uint32_t dst = ring + (uint32_t)s * kStageStride;
+                const uint8_t* ksrc = k_head_base + (size_t)page * p.layout.k_page_stride_bytes;
+                const uint8_t* vsrc = v_head_base + (size_t)page * p.layout.v_page_stride_bytes;
+                mbar_expect_tx(bar, 4 * kHalfBytes);
+                bulk_g2s(dst, ksrc, kHalfBytes, bar);
+                bulk_g2s(dst + kHalfStride, ksrc + kHalfBytes, kHalfBytes, bar);
+                bulk_g2s(dst + kRunStride, vsrc, kHalfBytes, bar);
+                bulk_g2s(dst + kRunStride + kHalfStride, vsrc + kHalfBytes, kHalfBytes, bar);
             }
         };
         // `my_page` holds ids for units [64 c, 64 c + 32), `next_page` for [64 c + 32, 64 c + 64).
@@ -501,43 +573,52 @@ __global__ void __launch_bounds__(384, 1) tq4_attention_stream_kernel(const Stre
             phase_bits ^= 1u << s;
             pending &= ~(1u << s);
 
-            const uint32_t kst = ring + (uint32_t)s * kStageBytes;
-            const uint32_t vst = kst + kTq4PageHeadBytes;
+            const uint32_t kst = ring + (uint32_t)s * kStageStride;
+            const uint32_t vst = kst + kRunStride;
             const int kv_base = (pg0 + i) << 4;
             const bool full = (kv_base >= safe_lo) && (kv_base + 15 <= safe_hi);
+#define W34_LDS(addr) lds32(addr)
+#define W34_LUT(word, k) lds32(__byte_perm((word), lut_lane, 0x7604 + ((k) << 4)))
 
             // ---- S^T = K Q'^T, one accumulator per 128-half ------------------------------
-            float sa[2][4];
+            float sa[2][4], sl[2][4];  // hi and lo chains are independent
 #pragma unroll
-            for (int h = 0; h < 2; ++h) { sa[h][0] = sa[h][1] = sa[h][2] = sa[h][3] = 0.0f; }
-            const uint32_t krow_a = kst + (uint32_t)pk * kTq4RowBytes;
-            const uint32_t krow_b = krow_a + 8u * kTq4RowBytes;
-            const uint32_t ka0 = lds32(krow_a), ka16 = lds32(krow_a + 64);
-            const uint32_t kb0 = lds32(krow_b), kb16 = lds32(krow_b + 64);
+            for (int h = 0; h < 2; ++h) {
+                sa[h][0] = sa[h][1] = sa[h][2] = sa[h][3] = 0.0f;
+                sl[h][0] = sl[h][1] = sl[h][2] = sl[h][3] = 0.0f;
+            }
+            const uint32_t krow_a = kst + token_offset(key_a);
+            const uint32_t krow_b = krow_a + 4u * kTq4RowBytes;
+            const uint32_t ka0 = W34_LDS(krow_a), ka16 = W34_LDS(krow_a + 64);
+            const uint32_t kb0 = W34_LDS(krow_b), kb16 = W34_LDS(krow_b + 64);
 #pragma unroll
             for (int s8 = 0; s8 < 8; ++s8) {
                 const int half = s8 >> 2;
                 uint32_t wa, wb;
                 if (half == 0) {
                     const uint32_t off = 4u * (4u * tig + (s8 & 3));
-                    wa = lds32(krow_a + off);
-                    wb = lds32(krow_b + off);
+                    wa = W34_LDS(krow_a + off);
+                    wb = W34_LDS(krow_b + off);
                     if ((s8 & 3) == 0 && tig == 0) {
                         wa = (ka0 >> 16) | (ka16 << 16);
                         wb = (kb0 >> 16) | (kb16 << 16);
                     }
                 } else {
                     const uint32_t off = 4u * (17u + 4u * tig + (s8 & 3));
-                    wa = lds32(krow_a + off);
-                    wb = lds32(krow_b + off);
+                    wa = W34_LDS(krow_a + off);
+                    wb = W34_LDS(krow_b + off);
                 }
 #pragma unroll
                 for (int hk = 0; hk < 2; ++hk) {
-                    const uint32_t a0 = lds32(lut_lane + (__byte_perm(wa, 0, 0x4440 + 2 * hk) << 7));
-                    const uint32_t a1 = lds32(lut_lane + (__byte_perm(wb, 0, 0x4440 + 2 * hk) << 7));
-                    const uint32_t a2 = lds32(lut_lane + (__byte_perm(wa, 0, 0x4441 + 2 * hk) << 7));
-                    const uint32_t a3 = lds32(lut_lane + (__byte_perm(wb, 0, 0x4441 + 2 * hk) << 7));
+                    const uint32_t a0 = W34_LUT(wa, 2 * hk);
+                    const uint32_t a1 = W34_LUT(wb, 2 * hk);
+                    const uint32_t a2 = W34_LUT(wa, 2 * hk + 1);
+                    const uint32_t a3 = W34_LUT(wb, 2 * hk + 1);
+                    const uint32_t ql = qlo[2 * s8 + hk];
                     mma16816(sa[half], a0, a1, a2, a3, qb[2 * s8 + hk][0], qb[2 * s8 + hk][1]);
+                    if (W34_SPLIT_Q) {
+                        mma16816(sl[half], a0, a1, a2, a3, __byte_perm(ql, 0, 0x1404), __byte_perm(ql, 0, 0x3424));
+                    }
                 }
             }
             // scales of this lane's two keys
@@ -545,16 +626,23 @@ __global__ void __launch_bounds__(384, 1) tq4_attention_stream_kernel(const Stre
             const float dka1 = __half2float(__ushort_as_half((unsigned short)(ka16 >> 16)));
             const float dkb0 = __half2float(__ushort_as_half((unsigned short)(kb0 & 0xffffu)));
             const float dkb1 = __half2float(__ushort_as_half((unsigned short)(kb16 >> 16)));
-            // sc[0],sc[1]: key pk, rows 2tig, 2tig+1;  sc[2],sc[3]: key pk+8
+            // sc[0],sc[1]: token key_a, rows 2tig, 2tig+1;  sc[2],sc[3]: token key_a + 4
+            if (W34_SPLIT_Q) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+#pragma unroll
+                    for (int x = 0; x < 4; ++x) sa[h][x] += sl[h][x];
+                }
+            }
             float sc[4];
             sc[0] = dka0 * sa[0][0] + dka1 * sa[1][0];
             sc[1] = dka0 * sa[0][1] + dka1 * sa[1][1];
             sc[2] = dkb0 * sa[0][2] + dkb1 * sa[1][2];
             sc[3] = dkb0 * sa[0][3] + dkb1 * sa[1][3];
 
-            const uint32_t vrow = vst + (uint32_t)pk * kTq4RowBytes;  // V rows of the same two keys
-            const uint32_t va0 = lds32(vrow), va16 = lds32(vrow + 64);
-            const uint32_t vb0 = lds32(vrow + 8u * kTq4RowBytes), vb16 = lds32(vrow + 8u * kTq4RowBytes + 64);
+            const uint32_t vrow_a = vst + token_offset(key_a);  // V rows of the same two tokens
+            const uint32_t va0 = W34_LDS(vrow_a), va16 = W34_LDS(vrow_a + 64);
+            const uint32_t vb0 = W34_LDS(vrow_a + 4u * kTq4RowBytes), vb16 = W34_LDS(vrow_a + 4u * kTq4RowBytes + 64);
             float dva0 = __half2float(__ushort_as_half((unsigned short)(va0 & 0xffffu)));
             float dva1 = __half2float(__ushort_as_half((unsigned short)(va16 >> 16)));
             float dvb0 = __half2float(__ushort_as_half((unsigned short)(vb0 & 0xffffu)));
@@ -562,7 +650,7 @@ __global__ void __launch_bounds__(384, 1) tq4_attention_stream_kernel(const Stre
 
             bool msk[4] = {false, false, false, false};
             if (!full) {
-                const int pos_a = kv_base + pk, pos_b = pos_a + 8;
+                const int pos_a = kv_base + key_a, pos_b = pos_a + 4;
                 msk[0] = !(pos_a >= rmin[0] && pos_a <= rmax[0]);
                 msk[1] = !(pos_a >= rmin[1] && pos_a <= rmax[1]);
                 msk[2] = !(pos_b >= rmin[0] && pos_b <= rmax[0]);
@@ -604,36 +692,44 @@ __global__ void __launch_bounds__(384, 1) tq4_attention_stream_kernel(const Stre
             }
             l_run[0] += pr[0] + pr[2];
             l_run[1] += pr[1] + pr[3];
-            // P * d_v per half, as B fragments (k = key, n = query row)
-            uint32_t pb[2][2];
-            pb[0][0] = movmatrix_trans(pack_half2(pr[0] * dva0, pr[1] * dva0));
-            pb[0][1] = movmatrix_trans(pack_half2(pr[2] * dvb0, pr[3] * dvb0));
-            pb[1][0] = movmatrix_trans(pack_half2(pr[0] * dva1, pr[1] * dva1));
-            pb[1][1] = movmatrix_trans(pack_half2(pr[2] * dvb1, pr[3] * dvb1));
+            // P * d_v per half as B fragments (k = key, n = query row), split into an fp16 value
+            // and the fp16 of its rounding residual so that few-key softmaxes keep fp32-like weights
+            uint32_t pb[2][2], pl[2][2];
+            {
+                const float pd[2][4] = {{pr[0] * dva0, pr[1] * dva0, pr[2] * dvb0, pr[3] * dvb0},
+                                        {pr[0] * dva1, pr[1] * dva1, pr[2] * dvb1, pr[3] * dvb1}};
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+#pragma unroll
+                    for (int x = 0; x < 2; ++x) {
+                        const __half2 hi = __floats2half2_rn(pd[h][2 * x], pd[h][2 * x + 1]);
+                        const float2 hf = __half22float2(hi);
+                        const __half2 lo = __floats2half2_rn(pd[h][2 * x] - hf.x, pd[h][2 * x + 1] - hf.y);
+                        pb[h][x] = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&hi));
+                        pl[h][x] = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&lo));
+                    }
+                }
+            }
 
             // ---- O^T += V^T P^T -----------------------------------------------------------
-            // step i4: half i4 >> 1, virtual word 2 gid + (i4 & 1); rows tig, tig+4, tig+8, tig+12
-            const uint32_t vr = vst + (uint32_t)tig * kTq4RowBytes;
+            // step i4: half i4 >> 1, virtual word 4 (gid >> 1) + (gid & 1) + 2 (i4 & 1);
+            // tokens kv0 + {0, 1, 4, 5}
+            const uint32_t vr = vst + token_offset(kv0);
+            const uint32_t vwb = 4u * (uint32_t)(gid >> 1) + (uint32_t)(gid & 1);
 #pragma unroll
             for (int i4 = 0; i4 < 4; ++i4) {
                 const int half = i4 >> 1;
                 uint32_t w[4];
-                if (half == 0) {
-                    const uint32_t off = 4u * (2u * gid + (i4 & 1));
-#pragma unroll
-                    for (int kq = 0; kq < 4; ++kq) w[kq] = lds32(vr + 4u * kq * kTq4RowBytes + off);
-                    if ((i4 & 1) == 0 && gid == 0) {
-#pragma unroll
-                        for (int kq = 0; kq < 4; ++kq) {
-                            const uint32_t x0 = w[kq];  // W0 of that row
-                            const uint32_t x16 = lds32(vr + 4u * kq * kTq4RowBytes + 64);
-                            w[kq] = (x0 >> 16) | (x16 << 16);
-                        }
-                    }
-                } else {
-                    const uint32_t off = 4u * (17u + 2u * gid + (i4 & 1));
-#pragma unroll
-                    for (int kq = 0; kq < 4; ++kq) w[kq] = lds32(vr + 4u * kq * kTq4RowBytes + off);
+                const uint32_t off = 4u * ((half ? 17u : 0u) + vwb + 2u * (i4 & 1));
+                w[0] = W34_LDS(vr + off);
+                w[1] = W34_LDS(vr + kTq4RowBytes + off);
+                w[2] = W34_LDS(vr + 4u * kTq4RowBytes + off);
+                w[3] = W34_LDS(vr + 5u * kTq4RowBytes + off);
+                if (i4 == 0 && gid == 0) {  // virtual word 0 of half 0: splice (W0 >> 16) | (W16 << 16)
+                    w[0] = (w[0] >> 16) | (W34_LDS(vr + 64) << 16);
+                    w[1] = (w[1] >> 16) | (W34_LDS(vr + kTq4RowBytes + 64) << 16);
+                    w[2] = (w[2] >> 16) | (W34_LDS(vr + 4u * kTq4RowBytes + 64) << 16);
+                    w[3] = (w[3] >> 16) | (W34_LDS(vr + 5u * kTq4RowBytes + 64) << 16);
                 }
                 // byte t of lo_ab -> (V[ka][e=2t], V[kb][e=2t]); of hi_ab -> e = 2t+1
                 const uint32_t lo_ab = (w[0] & 0x0f0f0f0fu) | ((w[1] << 4) & 0xf0f0f0f0u);
@@ -642,13 +738,16 @@ __global__ void __launch_bounds__(384, 1) tq4_attention_stream_kernel(const Stre
                 const uint32_t hi_cd = ((w[2] >> 4) & 0x0f0f0f0fu) | (w[3] & 0xf0f0f0f0u);
 #pragma unroll
                 for (int t = 0; t < 4; ++t) {
-                    const uint32_t a0 = lds32(lut_lane + (__byte_perm(lo_ab, 0, 0x4440 + t) << 7));
-                    const uint32_t a1 = lds32(lut_lane + (__byte_perm(hi_ab, 0, 0x4440 + t) << 7));
-                    const uint32_t a2 = lds32(lut_lane + (__byte_perm(lo_cd, 0, 0x4440 + t) << 7));
-                    const uint32_t a3 = lds32(lut_lane + (__byte_perm(hi_cd, 0, 0x4440 + t) << 7));
+                    const uint32_t a0 = W34_LUT(lo_ab, t);
+                    const uint32_t a1 = W34_LUT(hi_ab, t);
+                    const uint32_t a2 = W34_LUT(lo_cd, t);
+                    const uint32_t a3 = W34_LUT(hi_cd, t);
                     mma16816(o[4 * i4 + t], a0, a1, a2, a3, pb[half][0], pb[half][1]);
+                    if (W34_SPLIT_P) mma16816(o[4 * i4 + t], a0, a1, a2, a3, pl[half][0], pl[half][1]);
                 }
             }
+#undef W34_LUT
+#undef W34_LDS
             __syncwarp();  // every lane is done with stage s before it is refilled
         }
 
@@ -673,7 +772,7 @@ __global__ void __launch_bounds__(384, 1) tq4_attention_stream_kernel(const Stre
         float* stage_o = reinterpret_cast<float*>(ring_gen);  // [8 rows][256]
 #pragma unroll
         for (int i4 = 0; i4 < 4; ++i4) {
-            const int half = i4 >> 1, vw = 2 * gid + (i4 & 1);
+            const int half = i4 >> 1, vw = 4 * (gid >> 1) + (gid & 1) + 2 * (i4 & 1);
 #pragma unroll
             for (int t = 0; t < 4; ++t) {
                 const int ca = vword_col(half, vw, 2 * t), cb = vword_col(half, vw, 2 * t + 1);
@@ -750,7 +849,7 @@ __global__ void __launch_bounds__(128) tq4_attention_merge_kernel(const StreamPa
             }
         }
     }
-    const float inv_l = (l_tot > 0.0f) ? (1.0f / l_tot) : 0.0f;
+    const float inv_l = (l_tot > 0.0f) ? (1.0f / (l_tot * kLutScale)) : 0.0f;
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] *= inv_l;
     wht256_lanes(acc, lane);
@@ -760,11 +859,18 @@ __global__ void __launch_bounds__(128) tq4_attention_merge_kernel(const StreamPa
 }
 
 // ---- host side ---------------------------------------------------------------------------
-constexpr int kStages = 3;
-constexpr int kWarpsPerCta = 12;
+constexpr int kStages = W34_STAGES;
+constexpr int kWarpsPerCta = W34_WARPS;
+
+// LUT + rings + mbarriers, plus up to 64 KB - 1 of alignment slack in front of the table; the
+// kernel is given the whole opt-in maximum and checks the carve-up itself.
+static size_t stream_smem_min_bytes() {
+    return kLutBytes + (size_t)kWarpsPerCta * kStages * (kStageStride + 8);
+}
 
 struct DeviceInfo {
     int sm_count;
+    int smem_optin;
     bool configured;
 };
 
@@ -779,10 +885,14 @@ static DeviceInfo* device_info(int* rc) {
         int sms = 0;
         *rc = (int)cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         if (*rc != 0) return nullptr;
-        const size_t smem = kLutBytes + (size_t)kWarpsPerCta * kStages * (kStageBytes + 8);
-        *rc = (int)cudaFuncSetAttribute(tq4_attention_stream_kernel<kStages>,
-                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        int optin = 0;
+        *rc = (int)cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
         if (*rc != 0) return nullptr;
+        if ((size_t)optin < stream_smem_min_bytes()) { *rc = (int)cudaErrorNotSupported; return nullptr; }
+        *rc = (int)cudaFuncSetAttribute(tq4_attention_stream_kernel<kStages>,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, optin);
+        if (*rc != 0) return nullptr;
+        d->smem_optin = optin;
         d->sm_count = sms;
         d->configured = true;
     }
@@ -860,7 +970,8 @@ extern "C" int warp34_paged_attention_f16(const warp34_exec* ex, const warp34_kv
     const long long units_bound = items * (long long)(batch->max_blocks_per_req > 0 ? batch->max_blocks_per_req : 1);
     const size_t plan = w34::plan_bytes(batch->num_reqs);
     const size_t slot_bytes = (size_t)w34::kPartialFloats * sizeof(float);
-    bool stream = w34::stream_layout_ok(layout) && ex->scratch_ptr != 0 && (ex->scratch_ptr & 15u) == 0u &&
+    bool stream = (ex->flags & WARP34_B200_EXEC_FLAG_PRECISE_ATTENTION) == 0 &&
+                  w34::stream_layout_ok(layout) && ex->scratch_ptr != 0 && (ex->scratch_ptr & 15u) == 0u &&
                   units_bound < 0x7fffffffll && batch->max_blocks_per_req > 0;
     int grid = dev->sm_count;
     if (stream) {
@@ -888,9 +999,10 @@ extern "C" int warp34_paged_attention_f16(const warp34_exec* ex, const warp34_kv
     p.gqa = num_q_heads / layout->local_kv_heads;
     p.num_warps = grid * w34::kWarpsPerCta;
     p.max_slots = (int)(p.num_warps + items);
-    p.q_scale = batch->sm_scale * 1.4426950408889634f;
+    p.q_scale = batch->sm_scale * 1.4426950408889634f / w34::kLutScale;
     cudaStream_t st = (cudaStream_t)ex->stream;
-    const size_t smem = w34::kLutBytes + (size_t)w34::kWarpsPerCta * w34::kStages * (w34::kStageBytes + 8);
+    const size_t smem = (size_t)dev->smem_optin;
+    p.smem_bytes = (uint32_t)smem;
     w34::tq4_attention_plan_kernel<<<1, 32, 0, st>>>(p);
     w34::tq4_attention_stream_kernel<w34::kStages><<<grid, w34::kWarpsPerCta * 32, smem, st>>>(p);
     const long long rows = (long long)batch->total_tokens * num_q_heads;

@@ -17,6 +17,7 @@ ATTN_MASK_CAUSAL, ATTN_MASK_SYMMETRIC_WINDOW = 0, 1
 KV_NAMESPACE_TARGET_FULL_ATTN, KV_NAMESPACE_MTP_FULL_ATTN, KV_NAMESPACE_DFLASH_DRAFT_CTX = 0, 1, 2
 POLICY_FP16, POLICY_BF16, POLICY_Q8_0, POLICY_FP8, POLICY_TQ4, POLICY_TQ4_ALL = range(6)
 
+EXEC_FLAG_PRECISE_ATTENTION = 1 << 40
 CUDA_ERROR_INVALID_VALUE = 1
 CUDA_ERROR_NOT_SUPPORTED = 801
 W34_ERR_INVALID, W34_ERR_EXHAUSTED, W34_ERR_PROTECTED, W34_ERR_CAPACITY = -1, -2, -3, -4

@@ -274,3 +274,92 @@ def paged_attention(ex, layer, batch, q, out, num_q_heads, lib=None, scalar=Fals
     rc = fn(C.byref(ex.ex), C.byref(layer.layout), C.byref(batch.desc), q.data_ptr(), out.data_ptr(),
             num_q_heads)
     _check(rc, "warp34_paged_attention_f16")
+
+
+class StepIo:
+    """Persistent step-metadata buffers: one pinned host arena, one device arena, one copy per
+    step (the reference packs tokens | slots | block tables | lengths into a single pinned
+    upload, crates/warp34-host/src/model/execution.rs:38-93; graph_io.rs:368-420)."""
+
+    def __init__(self, max_reqs, max_tokens, max_blocks_per_req, device="cuda"):
+        self.max_reqs, self.max_tokens, self.max_blocks = max_reqs, max_tokens, max_blocks_per_req
+        sizes = [max_reqs + 1, max_reqs, max_reqs, max_reqs * max_blocks_per_req, max_tokens]
+        offs = np.concatenate([[0], np.cumsum([(s + 3) // 4 * 4 for s in sizes])])
+        self._offs, self._sizes = offs, sizes
+        total = int(offs[-1])
+        self.host = torch.zeros(total, dtype=torch.int32).pin_memory() if device != "cpu" else torch.zeros(total, dtype=torch.int32)
+        self.dev = torch.zeros(total, dtype=torch.int32, device=device)
+        self._np = self.host.numpy()
+        self.desc = ffi.AttentionBatch()
+        base = self.dev.data_ptr()
+        self.desc.query_start_loc = base + 4 * int(offs[0])
+        self.desc.context_lens_before = base + 4 * int(offs[1])
+        self.desc.seq_lens_after = base + 4 * int(offs[2])
+        self.desc.block_tables = base + 4 * int(offs[3])
+        self.desc.write_slot_mapping = base + 4 * int(offs[4])
+        self.desc.max_blocks_per_req = max_blocks_per_req
+        self.nbytes = total * 4
+
+    def _ptr(self, i):
+        return C.cast(self._np.ctypes.data + 4 * int(self._offs[i]), C.POINTER(C.c_int32))
+
+    def pack(self, seqs, q_lens, sm_scale, mask_mode=0, sliding_window=0):
+        n = len(seqs)
+        assert n <= self.max_reqs and sum(q_lens) <= self.max_tokens
+        handles = (C.c_void_p * n)(*[s.handle for s in seqs])
+        ql = (C.c_int32 * n)(*q_lens)
+        mq, ms = C.c_int32(), C.c_int32()
+        rc = ffi.host().w34_build_step_metadata(handles, ql, n, self.max_blocks, self._ptr(0), self._ptr(1),
+                                                self._ptr(2), self._ptr(3), self._ptr(4), C.byref(mq), C.byref(ms))
+        if rc < 0:
+            raise RuntimeError(f"w34_build_step_metadata: {rc}")
+        d = self.desc
+        d.num_reqs, d.total_tokens = n, rc
+        d.max_q_len, d.max_seq_len = mq.value, ms.value
+        d.mask_mode, d.sliding_window, d.sm_scale = mask_mode, sliding_window, sm_scale
+        return rc
+
+    def upload(self):
+        self.dev.copy_(self.host, non_blocking=True)
+
+
+class _DescOnly:
+    def __init__(self, desc):
+        self.desc = desc
+
+
+class DecodeStep:
+    """The call a user of this path makes once per model step and layer: new K/V rows and Q in
+    HOST memory in, attention output in HOST memory out (append then attend, forward.rs:1141-1188)."""
+
+    def __init__(self, layer, seqs, num_q_heads, max_q_len=1, scratch_bytes=64 << 20, device="cuda"):
+        self.layer, self.seqs, self.hq = layer, seqs, num_q_heads
+        hkv = layer.layout.local_kv_heads
+        n_tok = len(seqs) * max_q_len
+        max_blocks = max(s.num_pages for s in seqs)
+        self.io = StepIo(len(seqs), n_tok, max_blocks, device=device)
+        self.ex = Executor(scratch_bytes, device=device)
+        pin = lambda *shape: torch.zeros(*shape, dtype=torch.float16).pin_memory()  # noqa: E731
+        self.k_host, self.v_host = pin(n_tok, hkv * 256), pin(n_tok, hkv * 256)
+        self.q_host, self.out_host = pin(n_tok, num_q_heads, 256), pin(n_tok, num_q_heads, 256)
+        self.k_dev = torch.zeros_like(self.k_host, device=device)
+        self.v_dev = torch.zeros_like(self.v_host, device=device)
+        self.q_dev = torch.zeros_like(self.q_host, device=device)
+        self.out_dev = torch.zeros_like(self.out_host, device=device)
+        self.h2d_bytes = self.io.nbytes + 2 * self.k_host.numel() * 2 + self.q_host.numel() * 2
+        self.d2h_bytes = self.out_host.numel() * 2
+
+    def run(self, q_lens, sm_scale=1.0 / 16.0, lib=None, sync=True):
+        self.io.pack(self.seqs, q_lens, sm_scale)
+        self.io.upload()
+        self.k_dev.copy_(self.k_host, non_blocking=True)
+        self.v_dev.copy_(self.v_host, non_blocking=True)
+        self.q_dev.copy_(self.q_host, non_blocking=True)
+        self.ex.set_stream()
+        b = _DescOnly(self.io.desc)
+        kv_cache_write(self.ex, self.layer, b, self.k_dev, self.v_dev, lib=lib)
+        paged_attention(self.ex, self.layer, b, self.q_dev, self.out_dev, self.hq, lib=lib)
+        self.out_host.copy_(self.out_dev, non_blocking=True)
+        if sync:
+            torch.cuda.current_stream().synchronize()
+        return self.out_host
