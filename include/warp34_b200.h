@@ -180,6 +180,37 @@ size_t warp34_paged_attention_scratch_bytes(const warp34_kv_layer_layout* layout
                                             const warp34_attention_batch* batch,
                                             int num_q_heads);
 
+/*
+ * Attention over a page shard of longer sequences: same arguments as
+ * warp34_paged_attention_f16, but the result is left un-normalised so that shards held by
+ * different GPUs can be merged.  triples_out is fp32 [total_tokens, num_q_heads, 258]: 256
+ * accumulator values in the rotated domain, then the running maximum m (base-2 logarithm
+ * units of the scaled scores) and the sum l.  Needs the streaming path (canonical layout and
+ * scratch); returns cudaErrorNotSupported otherwise.  The reference has no multi-GPU
+ * attention; the triple is the (acc, m, l) of its split-KV scratch (op_paged_attn.cu:1329-1338).
+ */
+int warp34_paged_attention_partial_f16(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
+                                       const warp34_attention_batch* batch,
+                                       const void* q_in, float* triples_out, int num_q_heads);
+
+/*
+ * Merges num_shards sets of triples ([num_shards, num_rows, 258], e.g. the all-gather of every
+ * GPU's warp34_paged_attention_partial_f16 output) into fp16 attention output
+ * [num_rows, 256]: w_s = 2^(m_s - max m), out = sum acc_s w_s / sum l_s w_s, inverse rotation
+ * (the algebra of op_paged_attn.cu:1168-1202).  Shards with l <= 0 are skipped.
+ */
+int warp34_paged_attention_merge_shards_f16(const warp34_exec* ex, const float* triples,
+                                            int num_shards, int64_t num_rows, void* attn_out);
+
+/*
+ * Copies the first `rows` token rows (all kv heads, K and V) of page src_page to page dst_page
+ * of one layer: the device half of copy-on-write for a shared partial tail page
+ * (docs/contracts/cache-layout.md:106-110 specifies the copy; the reference never implemented
+ * it).  Pair with w34_seq_prepare_append() of warp34_host.h.
+ */
+int warp34_kv_page_copy(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
+                        int32_t src_page, int32_t dst_page, int32_t rows);
+
 /* Library identification: returns a static string "warp34_b200 <version> sm_100a". */
 const char* warp34_b200_version(void);
 

@@ -176,6 +176,7 @@ struct StreamParams {
     warp34_attention_batch batch;
     const __half* q_in;
     __half* attn_out;
+    float* triple_out;     // [total_tokens, num_q_heads, 258] when the merge stops before normalising
     uint8_t* scratch;      // plan header, arrays, then partial slots
     int num_q_heads;
     int gqa;
@@ -349,6 +350,9 @@ __device__ __forceinline__ uint32_t token_offset(int t) {  // byte offset of tok
 // 2^-14 instead of 2^-11); SPLIT_P adds 8% and only matters for softmaxes over a handful of keys.
 // Both are off by default: the fp16 lookup-table values of K bound the score accuracy either
 // way, and callers that need fp32 scores can set WARP34_B200_EXEC_FLAG_PRECISE_ATTENTION.
+#ifndef W34_QK_CHAINS
+#define W34_QK_CHAINS 2   // independent accumulator chains of the QK product per 128-half x 2
+#endif
 #ifndef W34_SPLIT_Q
 #define W34_SPLIT_Q 0   // second QK MMA with the fp16 rounding residual of Q'
 #endif
@@ -615,7 +619,11 @@ __global__ void __launch_bounds__(W34_WARPS * 32, 1) tq4_attention_stream_kernel
                     const uint32_t a2 = W34_LUT(wa, 2 * hk + 1);
                     const uint32_t a3 = W34_LUT(wb, 2 * hk + 1);
                     const uint32_t ql = qlo[2 * s8 + hk];
-                    mma16816(sa[half], a0, a1, a2, a3, qb[2 * s8 + hk][0], qb[2 * s8 + hk][1]);
+                    if (W34_QK_CHAINS == 4 && !W34_SPLIT_Q && hk == 1) {
+                        mma16816(sl[half], a0, a1, a2, a3, qb[2 * s8 + hk][0], qb[2 * s8 + hk][1]);
+                    } else {
+                        mma16816(sa[half], a0, a1, a2, a3, qb[2 * s8 + hk][0], qb[2 * s8 + hk][1]);
+                    }
                     if (W34_SPLIT_Q) {
                         mma16816(sl[half], a0, a1, a2, a3, __byte_perm(ql, 0, 0x1404), __byte_perm(ql, 0, 0x3424));
                     }
@@ -627,7 +635,7 @@ __global__ void __launch_bounds__(W34_WARPS * 32, 1) tq4_attention_stream_kernel
             const float dkb0 = __half2float(__ushort_as_half((unsigned short)(kb0 & 0xffffu)));
             const float dkb1 = __half2float(__ushort_as_half((unsigned short)(kb16 >> 16)));
             // sc[0],sc[1]: token key_a, rows 2tig, 2tig+1;  sc[2],sc[3]: token key_a + 4
-            if (W34_SPLIT_Q) {
+            if (W34_SPLIT_Q || W34_QK_CHAINS == 4) {
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
 #pragma unroll
@@ -801,7 +809,14 @@ __global__ void __launch_bounds__(W34_WARPS * 32, 1) tq4_attention_stream_kernel
     }
 }
 
-// One warp per (token, q head): combine partials, inverse rotation, store.
+// Row triple written when the caller merges across page shards itself: 256 un-normalised
+// accumulator values in the rotated domain (in lookup-table units), then m (log2 units of the
+// pre-scaled scores) and l.
+constexpr int kRowTripleFloats = kHeadDim + 2;
+
+// One warp per (token, q head): combine partials, then either normalise + inverse rotation +
+// fp16 store, or (PARTIAL_OUT) store the merged (acc, m, l) triple for a cross-shard merge.
+template <bool PARTIAL_OUT>
 __global__ void __launch_bounds__(128) tq4_attention_merge_kernel(const StreamParams p) {
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const long long row_ll = (long long)blockIdx.x * 4 + wid;
@@ -829,11 +844,11 @@ __global__ void __launch_bounds__(128) tq4_attention_merge_kernel(const StreamPa
 
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     float l_tot = 0.0f;
+    float m_tot = -1e30f;
     if (npages > 0 && per > 0) {
         const int us = unit_prefix[r] + item * npages;
         const int w_first = us / per, w_last = (us + npages - 1) / per;
         const int slot0 = item_prefix[r] + item;
-        float m_tot = -1e30f;
         for (int w = w_first; w <= w_last; ++w) {
             const float* ps = partials + (size_t)(w + slot0) * kPartialFloats + kRowsPerGroup * kHeadDim;
             if (ps[kRowsPerGroup + row8] > 0.0f) m_tot = fmaxf(m_tot, ps[row8]);
@@ -849,6 +864,13 @@ __global__ void __launch_bounds__(128) tq4_attention_merge_kernel(const StreamPa
             }
         }
     }
+    if (PARTIAL_OUT) {
+        float* dst = p.triple_out + ((size_t)tok * p.num_q_heads + q_head) * kRowTripleFloats;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) dst[lane + 32 * j] = acc[j];
+        if (lane == 0) { dst[kHeadDim] = m_tot; dst[kHeadDim + 1] = l_tot; }
+        return;
+    }
     const float inv_l = (l_tot > 0.0f) ? (1.0f / (l_tot * kLutScale)) : 0.0f;
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] *= inv_l;
@@ -856,6 +878,58 @@ __global__ void __launch_bounds__(128) tq4_attention_merge_kernel(const StreamPa
     __half* out_row = p.attn_out + ((size_t)tok * p.num_q_heads + q_head) * kHeadDim;
 #pragma unroll
     for (int j = 0; j < 8; ++j) out_row[lane + 32 * j] = __float2half_rn(apply_sign(acc[j], lane + 32 * j));
+}
+
+// Cross-shard merge: parts is [num_parts][rows][258]; one warp per row.
+__global__ void __launch_bounds__(128) tq4_attention_merge_shards_kernel(
+    const float* __restrict__ parts, int num_parts, long long rows, __half* __restrict__ attn_out) {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const long long row = (long long)blockIdx.x * 4 + wid;
+    if (row >= rows) return;
+    float m_tot = -1e30f;
+    for (int s = 0; s < num_parts; ++s) {
+        const float* t = parts + ((size_t)s * rows + row) * kRowTripleFloats;
+        if (t[kHeadDim + 1] > 0.0f) m_tot = fmaxf(m_tot, t[kHeadDim]);
+    }
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    float l_tot = 0.0f;
+    for (int s = 0; s < num_parts; ++s) {
+        const float* t = parts + ((size_t)s * rows + row) * kRowTripleFloats;
+        const float ls = t[kHeadDim + 1];
+        if (ls > 0.0f) {
+            const float wgt = ex2(t[kHeadDim] - m_tot);
+            l_tot += ls * wgt;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] += t[lane + 32 * j] * wgt;
+        }
+    }
+    const float inv_l = (l_tot > 0.0f) ? (1.0f / (l_tot * kLutScale)) : 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] *= inv_l;
+    wht256_lanes(acc, lane);
+    __half* out_row = attn_out + (size_t)row * kHeadDim;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) out_row[lane + 32 * j] = __float2half_rn(apply_sign(acc[j], lane + 32 * j));
+}
+
+// Copies the first `rows` token rows of every kv head of one page to another page of the same
+// slabs (copy-on-write of a shared partial tail page).  One block per (kv head, K or V).
+__global__ void __launch_bounds__(128) kv_page_copy_kernel(const warp34_kv_layer_layout layout, int src_page,
+                                                           int dst_page, int rows) {
+    const int head = blockIdx.x >> 1;
+    const bool is_v = blockIdx.x & 1;
+    const uint64_t base = is_v ? layout.v_base : layout.k_base;
+    const uint64_t ps = is_v ? layout.v_page_stride_bytes : layout.k_page_stride_bytes;
+    const uint64_t hs = is_v ? layout.v_head_stride_bytes : layout.k_head_stride_bytes;
+    const uint64_t ts = is_v ? layout.v_token_stride_bytes : layout.k_token_stride_bytes;
+    const uint16_t* src = (const uint16_t*)(uintptr_t)(base + (uint64_t)src_page * ps + (uint64_t)head * hs);
+    uint16_t* dst = (uint16_t*)(uintptr_t)(base + (uint64_t)dst_page * ps + (uint64_t)head * hs);
+    const int halves_per_row = kTq4RowBytes / 2;
+    for (int i = threadIdx.x; i < rows * halves_per_row; i += blockDim.x) {
+        const int row = i / halves_per_row, c = i - row * halves_per_row;
+        const size_t off = ((size_t)row * ts) / 2 + c;
+        dst[off] = src[off];
+    }
 }
 
 // ---- host side ---------------------------------------------------------------------------
@@ -950,62 +1024,121 @@ extern "C" size_t warp34_paged_attention_scratch_bytes(const warp34_kv_layer_lay
     return w34::plan_bytes(batch->num_reqs) + (size_t)slots * w34::kPartialFloats * sizeof(float);
 }
 
-extern "C" int warp34_paged_attention_f16(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
-                                          const warp34_attention_batch* batch, const void* q_in,
-                                          void* attn_out, int num_q_heads) {
-    if (ex == nullptr || layout == nullptr || batch == nullptr || q_in == nullptr || attn_out == nullptr) {
+namespace w34 {
+
+// Shared body of the attention entry points.  triple_out != nullptr: stop after the split-KV
+// merge and write per-row (acc, m, l) instead of attn_out (streaming path only).
+static int launch_attention(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
+                            const warp34_attention_batch* batch, const void* q_in, void* attn_out,
+                            float* triple_out, int num_q_heads) {
+    if (ex == nullptr || layout == nullptr || batch == nullptr || q_in == nullptr ||
+        (attn_out == nullptr && triple_out == nullptr)) {
         return (int)cudaErrorInvalidValue;
     }
     if (batch->total_tokens <= 0 || num_q_heads <= 0) return 0;
-    if (!w34::tq4_layout_ok(layout)) return (int)cudaErrorNotSupported;
+    if (!tq4_layout_ok(layout)) return (int)cudaErrorNotSupported;
     if (num_q_heads % layout->local_kv_heads != 0 || batch->num_reqs <= 0) return (int)cudaErrorInvalidValue;
 
     int rc = 0;
-    w34::DeviceInfo* dev = w34::device_info(&rc);
+    DeviceInfo* dev = device_info(&rc);
     if (dev == nullptr) return rc;
 
     // Streaming path: canonical layout, scratch that holds the plan plus at least one partial
     // per item and per worker warp, unit count within int32.
-    const long long items = w34::items_bound(layout, batch, num_q_heads);
+    const long long items = items_bound(layout, batch, num_q_heads);
     const long long units_bound = items * (long long)(batch->max_blocks_per_req > 0 ? batch->max_blocks_per_req : 1);
-    const size_t plan = w34::plan_bytes(batch->num_reqs);
-    const size_t slot_bytes = (size_t)w34::kPartialFloats * sizeof(float);
+    const size_t plan = plan_bytes(batch->num_reqs);
+    const size_t slot_bytes = (size_t)kPartialFloats * sizeof(float);
     bool stream = (ex->flags & WARP34_B200_EXEC_FLAG_PRECISE_ATTENTION) == 0 &&
-                  w34::stream_layout_ok(layout) && ex->scratch_ptr != 0 && (ex->scratch_ptr & 15u) == 0u &&
+                  stream_layout_ok(layout) && ex->scratch_ptr != 0 && (ex->scratch_ptr & 15u) == 0u &&
                   units_bound < 0x7fffffffll && batch->max_blocks_per_req > 0;
     int grid = dev->sm_count;
     if (stream) {
         const size_t avail = ex->scratch_size > plan ? ex->scratch_size - plan : 0;
         const long long slots_avail = (long long)(avail / slot_bytes);
         long long warps = slots_avail - items;
-        if (warps < w34::kWarpsPerCta) {
+        if (warps < kWarpsPerCta) {
             stream = false;
         } else {
-            const long long max_ctas = warps / w34::kWarpsPerCta;
+            const long long max_ctas = warps / kWarpsPerCta;
             if (max_ctas < grid) grid = (int)max_ctas;
         }
     }
     if (!stream) {
+        if (triple_out != nullptr) return (int)cudaErrorNotSupported;
         return warp34_paged_attention_scalar_f16(ex, layout, batch, q_in, attn_out, num_q_heads);
     }
 
-    w34::StreamParams p;
+    StreamParams p;
     p.layout = *layout;
     p.batch = *batch;
     p.q_in = static_cast<const __half*>(q_in);
     p.attn_out = static_cast<__half*>(attn_out);
+    p.triple_out = triple_out;
     p.scratch = reinterpret_cast<uint8_t*>((uintptr_t)ex->scratch_ptr);
     p.num_q_heads = num_q_heads;
     p.gqa = num_q_heads / layout->local_kv_heads;
-    p.num_warps = grid * w34::kWarpsPerCta;
+    p.num_warps = grid * kWarpsPerCta;
     p.max_slots = (int)(p.num_warps + items);
-    p.q_scale = batch->sm_scale * 1.4426950408889634f / w34::kLutScale;
+    p.q_scale = batch->sm_scale * 1.4426950408889634f / kLutScale;
     cudaStream_t st = (cudaStream_t)ex->stream;
     const size_t smem = (size_t)dev->smem_optin;
     p.smem_bytes = (uint32_t)smem;
-    w34::tq4_attention_plan_kernel<<<1, 32, 0, st>>>(p);
-    w34::tq4_attention_stream_kernel<w34::kStages><<<grid, w34::kWarpsPerCta * 32, smem, st>>>(p);
+    tq4_attention_plan_kernel<<<1, 32, 0, st>>>(p);
+    tq4_attention_stream_kernel<kStages><<<grid, kWarpsPerCta * 32, smem, st>>>(p);
     const long long rows = (long long)batch->total_tokens * num_q_heads;
-    w34::tq4_attention_merge_kernel<<<(unsigned)((rows + 3) / 4), 128, 0, st>>>(p);
+    if (triple_out != nullptr) {
+        tq4_attention_merge_kernel<true><<<(unsigned)((rows + 3) / 4), 128, 0, st>>>(p);
+    } else {
+        tq4_attention_merge_kernel<false><<<(unsigned)((rows + 3) / 4), 128, 0, st>>>(p);
+    }
+    return (int)cudaGetLastError();
+}
+
+}  // namespace w34
+
+extern "C" int warp34_paged_attention_f16(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
+                                          const warp34_attention_batch* batch, const void* q_in,
+                                          void* attn_out, int num_q_heads) {
+    if (attn_out == nullptr) return (int)cudaErrorInvalidValue;
+    return w34::launch_attention(ex, layout, batch, q_in, attn_out, nullptr, num_q_heads);
+}
+
+extern "C" int warp34_paged_attention_partial_f16(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
+                                                  const warp34_attention_batch* batch, const void* q_in,
+                                                  float* triples_out, int num_q_heads) {
+    if (triples_out == nullptr) return (int)cudaErrorInvalidValue;
+    return w34::launch_attention(ex, layout, batch, q_in, nullptr, triples_out, num_q_heads);
+}
+
+extern "C" int warp34_paged_attention_merge_shards_f16(const warp34_exec* ex, const float* triples,
+                                                       int num_shards, int64_t num_rows, void* attn_out) {
+    if (ex == nullptr || triples == nullptr || attn_out == nullptr || num_shards <= 0 || num_rows < 0) {
+        return (int)cudaErrorInvalidValue;
+    }
+    if (num_rows == 0) return 0;
+    w34::tq4_attention_merge_shards_kernel<<<(unsigned)((num_rows + 3) / 4), 128, 0, (cudaStream_t)ex->stream>>>(
+        triples, num_shards, (long long)num_rows, static_cast<__half*>(attn_out));
+    return (int)cudaGetLastError();
+}
+
+extern "C" int warp34_kv_page_copy(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
+                                   int32_t src_page, int32_t dst_page, int32_t rows) {
+    if (ex == nullptr || layout == nullptr || src_page < 0 || dst_page < 0 || rows < 0 ||
+        rows > layout->block_size) {
+        return (int)cudaErrorInvalidValue;
+    }
+    if (rows == 0 || src_page == dst_page || layout->local_kv_heads <= 0) return 0;
+    if (layout->k_format != WARP34_KV_FORMAT_TQ4 || layout->v_format != WARP34_KV_FORMAT_TQ4 ||
+        layout->head_dim != w34::kHeadDim) {
+        return (int)cudaErrorNotSupported;
+    }
+    if ((layout->k_base | layout->v_base | layout->k_page_stride_bytes | layout->k_head_stride_bytes |
+         layout->k_token_stride_bytes | layout->v_page_stride_bytes | layout->v_head_stride_bytes |
+         layout->v_token_stride_bytes) & 1u) {
+        return (int)cudaErrorInvalidValue;
+    }
+    w34::kv_page_copy_kernel<<<2 * layout->local_kv_heads, 128, 0, (cudaStream_t)ex->stream>>>(
+        *layout, src_page, dst_page, rows);
     return (int)cudaGetLastError();
 }

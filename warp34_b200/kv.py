@@ -276,6 +276,28 @@ def paged_attention(ex, layer, batch, q, out, num_q_heads, lib=None, scalar=Fals
     _check(rc, "warp34_paged_attention_f16")
 
 
+def paged_attention_partial(ex, layer, batch, q, triples, num_q_heads, lib=None):
+    """warp34_paged_attention_partial_f16: triples is fp32 [tokens, heads, 258]."""
+    lib = lib or ffi.kernels()
+    rc = lib.warp34_paged_attention_partial_f16(C.byref(ex.ex), C.byref(layer.layout), C.byref(batch.desc),
+                                                q.data_ptr(), triples.data_ptr(), num_q_heads)
+    _check(rc, "warp34_paged_attention_partial_f16")
+
+
+def merge_shards(ex, triples, out, lib=None):
+    """warp34_paged_attention_merge_shards_f16: triples fp32 [shards, rows, 258] -> out fp16 [rows, 256]."""
+    lib = lib or ffi.kernels()
+    shards, rows = triples.shape[0], triples[0].numel() // 258
+    rc = lib.warp34_paged_attention_merge_shards_f16(C.byref(ex.ex), triples.data_ptr(), shards, rows, out.data_ptr())
+    _check(rc, "warp34_paged_attention_merge_shards_f16")
+
+
+def kv_page_copy(ex, layer, src_page, dst_page, rows, lib=None):
+    lib = lib or ffi.kernels()
+    _check(lib.warp34_kv_page_copy(C.byref(ex.ex), C.byref(layer.layout), src_page, dst_page, rows),
+           "warp34_kv_page_copy")
+
+
 class StepIo:
     """Persistent step-metadata buffers: one pinned host arena, one device arena, one copy per
     step (the reference packs tokens | slots | block tables | lengths into a single pinned
