@@ -211,6 +211,39 @@ int warp34_paged_attention_merge_shards_f16(const warp34_exec* ex, const float* 
 int warp34_kv_page_copy(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
                         int32_t src_page, int32_t dst_page, int32_t rows);
 
+/*
+ * warp34_paged_attention_f16 for callers that have no workspace to offer and may not allocate
+ * one.  This entry point has no counterpart in the reference, whose engine always passes an
+ * 8 MiB scratch arena in warp34_exec.  It exists for hosts where that is not possible: the
+ * process has already committed all the device memory it was allowed (KV pool, weights) before
+ * this library is reached, the caller is a plugin that receives only tensors and a stream, or
+ * allocator calls are banned on the serving path.  The split-KV workspace is a 16 MiB array
+ * built into the library image (each GPU that loads the library holds it until the process
+ * exits); nothing is allocated or freed by this call, by the CUDA runtime on its behalf, or by
+ * any other library.
+ *
+ *  - Same inputs, outputs, masks and result as warp34_paged_attention_f16; `stream` replaces
+ *    the warp34_exec.
+ *  - Limit: the batch must fit the built-in workspace (plan + one 8256-byte partial per work
+ *    item, i.e. per (request, kv head, group of 8 query rows), + 12): 64 decode requests x 24
+ *    heads use the whole grid, about 1900 work items is the ceiling.  Larger batches, and
+ *    layouts that are not the canonical 132-byte-row packing, are refused with
+ *    cudaErrorInvalidValue / cudaErrorNotSupported and nothing is launched; when
+ *    `scratch_needed` is not NULL it receives the bytes the batch would have needed, so the
+ *    caller can tell "too large" from a malformed argument.
+ *  - The first call on each device looks up the array's device address
+ *    (cudaGetSymbolAddress, with that device current) and configures the kernel's shared
+ *    memory; make that first call outside any stream capture.
+ *  - All calls on a device share the one array, and it keeps whatever the previous call left.
+ *    Every call rewrites the plan and each partial before reading it, so no clearing is needed,
+ *    but two calls whose kernels overlap on the GPU (different streams without an event
+ *    between them) race on it.  Serialise them.
+ */
+int warp34_paged_attention_f16_static_scratch(uintptr_t stream, const warp34_kv_layer_layout* layout,
+                                              const warp34_attention_batch* batch,
+                                              const void* q_in, void* attn_out, int num_q_heads,
+                                              size_t* scratch_needed);
+
 /* Library identification: returns a static string "warp34_b200 <version> sm_100a". */
 const char* warp34_b200_version(void);
 

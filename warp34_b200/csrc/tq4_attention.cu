@@ -1104,6 +1104,66 @@ extern "C" int warp34_paged_attention_f16(const warp34_exec* ex, const warp34_kv
     return w34::launch_attention(ex, layout, batch, q_in, attn_out, nullptr, num_q_heads);
 }
 
+// ---- attention without any caller-provided or allocated workspace ---------------------------
+// Some hosts cannot hand this library a scratch buffer: an engine that has already given every
+// byte of HBM it could reserve to the KV pool and the weights, a plugin that is only passed
+// tensors and a stream, or a serving loop whose rules forbid allocator calls on the hot path.
+// For them the split-KV workspace lives in this array, which every GPU that loads the library
+// keeps for the life of the process.
+constexpr size_t kStaticScratchBytes = (size_t)16 << 20;  // 16 MiB: 64 decode requests x 24 heads at full grid
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+namespace w34 {
+// Device address of g_static_scratch per device.  In host code the array's name is only a
+// host-side handle; the address the kernels can use comes from cudaGetSymbolAddress, asked once
+// per device while that device is current.
+static int static_scratch_address(uint64_t* out) {
+    static uint64_t addr[64];
+    static bool known[64];
+    int dev = 0;
+    int rc = (int)cudaGetDevice(&dev);
+    if (rc != 0) return rc;
+    if (dev < 0 || dev >= 64) return (int)cudaErrorInvalidDevice;
+    if (!known[dev]) {
+        void* ptr = nullptr;
+        rc = (int)cudaGetSymbolAddress(&ptr, g_static_scratch);
+        if (rc != 0) return rc;
+        addr[dev] = (uint64_t)(uintptr_t)ptr;
+        known[dev] = true;
+    }
+    *out = addr[dev];
+    return 0;
+}
+}  // namespace w34
+
+extern "C" int warp34_paged_attention_f16_static_scratch(uintptr_t stream, const warp34_kv_layer_layout* layout,
+                                                         const warp34_attention_batch* batch, const void* q_in,
+                                                         void* attn_out, int num_q_heads,
+                                                         size_t* scratch_needed) {
+    if (scratch_needed != nullptr) *scratch_needed = 0;
+    if (layout == nullptr || batch == nullptr || q_in == nullptr || attn_out == nullptr) {
+        return (int)cudaErrorInvalidValue;
+    }
+    if (batch->total_tokens <= 0 || num_q_heads <= 0) return 0;
+    if (!w34::tq4_layout_ok(layout)) return (int)cudaErrorNotSupported;
+    if (!w34::stream_layout_ok(layout)) return (int)cudaErrorNotSupported;  // this entry point has no scratch-free fallback
+    if (num_q_heads % layout->local_kv_heads != 0 || batch->num_reqs <= 0) return (int)cudaErrorInvalidValue;
+    // Smallest workspace the streaming path accepts: the plan plus one partial per work item
+    // and per warp of a single CTA.
+    const size_t needed = w34::plan_bytes(batch->num_reqs) +
+                          (size_t)(w34::items_bound(layout, batch, num_q_heads) + w34::kWarpsPerCta) *
+                              w34::kPartialFloats * sizeof(float);
+    if (scratch_needed != nullptr) *scratch_needed = needed;
+    if (needed > kStaticScratchBytes) return (int)cudaErrorInvalidValue;  // batch too large for the built-in workspace
+    warp34_exec ex;
+    ex.stream = stream;
+    ex.scratch_size = kStaticScratchBytes;
+    ex.flags = 0;
+    const int rc = w34::static_scratch_address(&ex.scratch_ptr);
+    if (rc != 0) return rc;
+    return w34::launch_attention(&ex, layout, batch, q_in, attn_out, nullptr, num_q_heads);
+}
+
 extern "C" int warp34_paged_attention_partial_f16(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
                                                   const warp34_attention_batch* batch, const void* q_in,
                                                   float* triples_out, int num_q_heads) {

@@ -69,6 +69,8 @@ _KERNEL_SIGS = {
     "warp34_paged_attention_partial_f16": (C.c_int, [_P(Exec), _P(KvLayerLayout), _P(AttentionBatch),
                                                       C.c_void_p, C.c_void_p, C.c_int]),
     "warp34_paged_attention_merge_shards_f16": (C.c_int, [_P(Exec), C.c_void_p, C.c_int, C.c_int64, C.c_void_p]),
+    "warp34_paged_attention_f16_static_scratch": (C.c_int, [C.c_size_t, _P(KvLayerLayout), _P(AttentionBatch),
+                                                             C.c_void_p, C.c_void_p, C.c_int, _P(C.c_size_t)]),
     "warp34_kv_page_copy": (C.c_int, [_P(Exec), _P(KvLayerLayout), C.c_int32, C.c_int32, C.c_int32]),
     "warp34_paged_attention_scratch_bytes": (C.c_size_t, [_P(KvLayerLayout), _P(AttentionBatch), C.c_int]),
     "warp34_b200_version": (C.c_char_p, []),
