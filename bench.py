@@ -139,7 +139,7 @@ def sum_over_ranks(x, world):
     return float(t.item())
 
 
-def cpu_baseline(wl, hq, q_host, k_new, v_new, step_host_desc, budget_s=20.0):
+def cpu_baseline(wl, hq, q_host, k_new, v_new, step_host_desc, budget_s=20.0, q_len=1):
     """The CPU oracle (a restatement of the reference's algorithm; the reference has no CPU
     implementation of this path) on the host cores: the same step on a bounded sample of the
     batch.  Returns the cpu_baseline object."""
@@ -155,8 +155,8 @@ def cpu_baseline(wl, hq, q_host, k_new, v_new, step_host_desc, budget_s=20.0):
     def run(n):
         b = ffi.AttentionBatch()
         C.memmove(C.byref(b), C.byref(step_host_desc), C.sizeof(b))
-        b.num_reqs, b.total_tokens = n, n
-        out = np.zeros((n, hq, 256), np.uint16)
+        b.num_reqs, b.total_tokens = n, n * q_len
+        out = np.zeros((n * q_len, hq, 256), np.uint16)
         t0 = time.perf_counter()
         oracle.kv_cache_write(lay, b, k_new, v_new, k_new.shape[1], v_new.shape[1], nthreads=cores)
         oracle.paged_attention(lay, b, q_host, out, hq, nthreads=cores)
@@ -164,7 +164,7 @@ def cpu_baseline(wl, hq, q_host, k_new, v_new, step_host_desc, budget_s=20.0):
     t1 = run(1)
     n = int(max(1, min(nreq, budget_s / max(t1, 1e-4))))
     dt = run(n)
-    kv_bytes = sum(wl.ctx[i] + 1 for i in range(n)) * wl.num_kv_heads * 264
+    kv_bytes = sum(wl.ctx[i] + q_len for i in range(n)) * wl.num_kv_heads * 264
     return {"value": kv_bytes / dt / 1e9, "unit": UNIT, "cores": cores, "kind": "port",
             "sample": f"one full step (append + attention) over the first {n} of {nreq} sequences, {dt:.2f} s"}
 
@@ -186,6 +186,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="cfg1_batched_decode")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--append-tokens", type=int, default=32768, help="tokens of the bulk-append measurement")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -201,9 +202,20 @@ def main():
     lib = ffi.bind_kernel_abi(ref_path) if ref_path else ffi.kernels()
 
     hq, hkv, batch, lo, hi, q_len, seed = synth.CONFIGS[args.config]
+    sharded = args.config == "cfg4_long_context" and world > 1 and not reference
+    if sharded:
+        # one sequence, pages split across ranks: rank r holds tokens [r L / N, (r + 1) L / N)
+        lo = hi = (hi // world) // 16 * 16
     ctx = synth.context_lengths(batch, lo, hi, seed + 1000 * rank)
+    if sharded:
+        ctx = ctx - q_len  # every shard plays "context + the query token" so all its keys are visible
     wl = synth.PagedWorkload([int(c) for c in ctx], [q_len] * batch, hkv, seed=seed + 1000 * rank, device=dev)
     step = kv.DecodeStep(wl.layer, wl.seqs, hq, max_q_len=q_len, scratch_bytes=64 << 20, device=dev)
+    triples = gathered = None
+    if sharded:
+        import torch.distributed as dist
+        triples = torch.zeros(batch * q_len * hq, 258, dtype=torch.float32, device=dev)
+        gathered = torch.zeros(world * batch * q_len * hq, 258, dtype=torch.float32, device=dev)  # rank-major
     wl.fill_context(step.ex, seed + 1000 * rank, chunk_tokens=32768)  # untimed: KV pool resident in HBM
     n_tok = batch * q_len
     k_new, v_new = synth.make_kv(n_tok, hkv, seed + 17)
@@ -219,7 +231,7 @@ def main():
         step.run(q_lens)
         hb = host_step_batch(kv, step, batch, n_tok)
         cb = cpu_baseline(wl, hq, q_new.numpy().view(np.uint16), k_new.numpy().view(np.uint16),
-                          v_new.numpy().view(np.uint16), hb.host_desc(), budget_s=8.0)
+                          v_new.numpy().view(np.uint16), hb.host_desc(), budget_s=8.0, q_len=q_len)
         line = {"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": UNIT, "n_gpus": args.gpus,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True,
                 "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
@@ -238,13 +250,21 @@ def main():
     desc = kv._DescOnly(step.io.desc)
     step.ex.set_stream()
 
+    def attend(desc_):
+        if sharded:
+            kv.paged_attention_partial(step.ex, wl.layer, desc_, step.q_dev, triples, hq)
+            dist.all_gather_into_tensor(gathered, triples)
+            kv.merge_shards(step.ex, gathered.view(world, -1, 258), step.out_dev)
+        else:
+            kv.paged_attention(step.ex, wl.layer, desc_, step.q_dev, step.out_dev, hq, lib=lib)
+
     def device_step(ev=None):
         if ev is not None:
             ev[0].record()
         kv.kv_cache_write(step.ex, wl.layer, desc, step.k_dev, step.v_dev, lib=lib)
         if ev is not None:
             ev[1].record()
-        kv.paged_attention(step.ex, wl.layer, desc, step.q_dev, step.out_dev, hq, lib=lib)
+        attend(desc)
         if ev is not None:
             ev[2].record()
 
@@ -272,12 +292,12 @@ def main():
 
     # ---- end to end: host buffers in, host result out, every step ----------------------------
     for _ in range(3):
-        step.run(q_lens, lib=lib)
+        step.run(q_lens, lib=lib, attend=attend)
     barrier(world)
     e2e_steps = max(3, min(args.steps, 200))
     e0.record()
     for _ in range(e2e_steps):
-        step.run(q_lens, lib=lib, sync=True)
+        step.run(q_lens, lib=lib, sync=True, attend=attend)
     e1.record()
     barrier(world)
     e2e_ms = max_over_ranks(e0.elapsed_time(e1), world) / e2e_steps
@@ -286,6 +306,23 @@ def main():
 
     status = int(step.ex.scratch[:4].cpu().numpy().view(np.int32)[0]) if not reference else 0
 
+    # ---- bulk append (prefill-sized): the "appended tokens/s" half of the metric ----------------
+    bulk_tokens = args.append_tokens
+    wl2 = synth.PagedWorkload([0], [bulk_tokens], hkv, seed=seed + 5 + 1000 * rank, device=dev)
+    kb, vb = synth.make_kv(bulk_tokens, hkv, seed + 5, device=dev)   # 2 x 67 MB at 32768 tokens: > L2 together with the pool
+    b2 = wl2.step()
+    for _ in range(3):
+        kv.kv_cache_write(step.ex, wl2.layer, b2, kb, vb, lib=lib)
+    barrier(world)
+    n_bulk = 20
+    e0.record()
+    for _ in range(n_bulk):
+        kv.kv_cache_write(step.ex, wl2.layer, b2, kb, vb, lib=lib)
+    e1.record()
+    barrier(world)
+    bulk_ms = max_over_ranks(e0.elapsed_time(e1), world) / n_bulk
+    bulk_tok_s = world * bulk_tokens / (bulk_ms * 1e-3)
+
     if rank != 0:
         return
     peaks, peak_kind = measured_peaks()
@@ -293,13 +330,15 @@ def main():
     achieved = kv_bytes / (attn_ms * 1e-3) / 1e9
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "strong" if sharded else "weak",
         "vs_baseline": None, "dtype": "f16", "data": "synthetic",
         "config": {"workload": f"{args.config}: {batch} seqs x ctx U[{lo},{hi}], {hq} q heads / {hkv} kv heads, "
                                f"d256, TQ4 pages of 16, step = append {q_len} token/seq + decode attention",
                    "kv_bytes_per_step_per_gpu": kv_bytes, "tokens_in_cache_per_gpu": int(sum(wl.ctx)),
                    "l2": "KV read per step (>1.3 GB) is larger than L2; no flush needed",
-                   "per_gpu_batch": batch, "parallelism": f"batch-sharded x{world}, no collective"},
+                   "per_gpu_batch": batch, "parallelism": (f"pages of one sequence sharded x{world}, (m, l, acc) triples all-gathered over NCCL"
+                                   if sharded else f"batch-sharded x{world}, no collective")},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "peak_kind": f"of {peak_kind}", "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,
                      "kernel": "tq4_attention_stream_kernel (+ plan and merge launches, timed together)",
@@ -308,7 +347,11 @@ def main():
                 "d2h_bytes_per_step": step.d2h_bytes},
         "gpu_launches": 4 * args.steps,
         "clocks": clocks,
-        "append_tokens_per_s": n_tok / (append_ms * 1e-3), "append_ms": append_ms, "attention_steps_per_s": 1e3 / attn_ms, "kernel_status": status,
+        "append_tokens_per_s": n_tok / (append_ms * 1e-3), "append_ms": append_ms,
+        "append_bulk": {"tokens": bulk_tokens, "ms": bulk_ms, "tokens_per_s": bulk_tok_s,
+                        "algorithmic_GBps": bulk_tok_s * hkv * 1288 / 1e9,
+                        "frac_of_peak": bulk_tok_s * hkv * 1288 / 1e9 / (world * float(measured_peaks()[0].get("hbm_gbs", FALLBACK_HBM_GBS)))},
+        "attention_steps_per_s": 1e3 / attn_ms, "kernel_status": status,
     }
     if reference:
         line["impl"] = "reference"
@@ -320,7 +363,7 @@ def main():
     elif not args.no_cpu_baseline:
         b = host_step_batch(kv, step, batch, n_tok)
         line["cpu_baseline"] = cpu_baseline(wl, hq, q_new.numpy().view(np.uint16), k_new.numpy().view(np.uint16),
-                                            v_new.numpy().view(np.uint16), b.host_desc())
+                                            v_new.numpy().view(np.uint16), b.host_desc(), q_len=q_len)
     print(json.dumps(line))
 
 

@@ -31,6 +31,10 @@ def lib():
         L.w34o_kv_cache_write_strided.argtypes = [vp, vp, vp, vp, i, i, i]
         L.w34o_paged_attention_f16.restype = i
         L.w34o_paged_attention_f16.argtypes = [vp, vp, vp, vp, i, i]
+        L.w34o_paged_attention_partial.restype = i
+        L.w34o_paged_attention_partial.argtypes = [vp, vp, vp, vp, i, i]
+        L.w34o_merge_shards.restype = i
+        L.w34o_merge_shards.argtypes = [vp, i, C.c_long, vp]
         L.w34o_tq4_encode_row.restype = None
         L.w34o_tq4_encode_row.argtypes = [vp, vp, vp, vp]
         L.w34o_tq4_decode_row.restype = None
@@ -80,3 +84,13 @@ def kv_cache_write(layout, batch_host, k_f16, v_f16, k_stride, v_stride, nthread
 def paged_attention(layout, batch_host, q_f16, out_f16, num_q_heads, nthreads=1):
     return lib().w34o_paged_attention_f16(C.addressof(layout), C.addressof(batch_host),
                                           q_f16.ctypes.data, out_f16.ctypes.data, num_q_heads, nthreads)
+
+
+def paged_attention_partial(layout, batch_host, q_f16, triples_f32, num_q_heads, nthreads=1):
+    return lib().w34o_paged_attention_partial(C.addressof(layout), C.addressof(batch_host), q_f16.ctypes.data,
+                                              triples_f32.ctypes.data, num_q_heads, nthreads)
+
+
+def merge_shards(triples_f32, out_f16):
+    shards, rows = triples_f32.shape[0], triples_f32[0].size // 258
+    return lib().w34o_merge_shards(triples_f32.ctypes.data, shards, rows, out_f16.ctypes.data)

@@ -285,6 +285,7 @@ typedef struct {
     const warp34_attention_batch* b;
     const uint16_t* q; uint16_t* out;
     int hq;
+    float* triples;  /* when non-NULL: write (acc[256], m, l) per row instead of the output */
 } attn_ctx;
 
 static void attn_one(void* p, long idx) {
@@ -375,6 +376,17 @@ static void attn_one(void* p, long idx) {
         if (l_w[w] > 0.0f) { ws[w] = expf(m_w[w] - m_tot); l_tot += l_w[w] * ws[w]; }
         else ws[w] = 0.0f;
     }
+    if (c->triples) {
+        /* un-normalised, still rotated: what a page shard hands to the cross-shard merge
+         * (the partial layout of op_paged_attn.cu:1329-1338, m in natural-log units here) */
+        float* t = c->triples + ((size_t)tok * hq + q_head) * 258;
+        for (int i = 0; i < 256; ++i) {
+            t[i] = acc[0][i] * ws[0] + acc[1][i] * ws[1] + acc[2][i] * ws[2] + acc[3][i] * ws[3];
+        }
+        t[256] = m_tot;
+        t[257] = l_tot;
+        return;
+    }
     const float inv_l = (l_tot > 0.0f) ? (1.0f / l_tot) : 0.0f;
     float o[256];
     for (int i = 0; i < 256; ++i) {
@@ -393,8 +405,48 @@ int w34o_paged_attention_f16(const warp34_kv_layer_layout* l, const warp34_atten
         l->k_transform != WARP34_KV_TRANSFORM_RADEMACHER_WHT256 ||
         l->v_transform != WARP34_KV_TRANSFORM_RADEMACHER_WHT256) return 801;
     if (l->local_kv_heads <= 0 || num_q_heads % l->local_kv_heads) return 1;
-    attn_ctx c = {l, b, q_in, attn_out, num_q_heads};
+    attn_ctx c = {l, b, q_in, attn_out, num_q_heads, NULL};
     parallel_for((long)b->total_tokens * num_q_heads, nthreads, attn_one, &c);
+    return 0;
+}
+
+/* Attention over a page shard, stopped before normalisation: triples is fp32
+ * [total_tokens, num_q_heads, 258] = 256 rotated accumulator values, m, l. */
+int w34o_paged_attention_partial(const warp34_kv_layer_layout* l, const warp34_attention_batch* b,
+                                 const uint16_t* q_in, float* triples, int num_q_heads, int nthreads) {
+    if (!l || !b || !q_in || !triples) return 1;
+    if (b->total_tokens <= 0 || num_q_heads <= 0) return 0;
+    if (l->local_kv_heads <= 0 || num_q_heads % l->local_kv_heads) return 1;
+    attn_ctx c = {l, b, q_in, NULL, num_q_heads, triples};
+    parallel_for((long)b->total_tokens * num_q_heads, nthreads, attn_one, &c);
+    return 0;
+}
+
+/* Cross-shard merge (algebra of op_paged_attn.cu:1168-1202): triples is
+ * [num_shards, rows, 258]; out is fp16 [rows, 256]. */
+int w34o_merge_shards(const float* triples, int num_shards, long rows, uint16_t* out) {
+    if (!triples || !out || num_shards <= 0 || rows < 0) return 1;
+    for (long r = 0; r < rows; ++r) {
+        float m_tot = -3.402823466e+38f;
+        for (int s = 0; s < num_shards; ++s) {
+            const float* t = triples + ((size_t)s * rows + r) * 258;
+            if (t[257] > 0.0f) m_tot = fmaxf(m_tot, t[256]);
+        }
+        float o[256], l_tot = 0.0f;
+        for (int i = 0; i < 256; ++i) o[i] = 0.0f;
+        for (int s = 0; s < num_shards; ++s) {
+            const float* t = triples + ((size_t)s * rows + r) * 258;
+            if (t[257] > 0.0f) {
+                const float w = expf(t[256] - m_tot);
+                l_tot += t[257] * w;
+                for (int i = 0; i < 256; ++i) o[i] += t[i] * w;
+            }
+        }
+        const float inv_l = (l_tot > 0.0f) ? (1.0f / l_tot) : 0.0f;
+        for (int i = 0; i < 256; ++i) o[i] *= inv_l;
+        w34o_wht256(o);
+        for (int i = 0; i < 256; ++i) out[r * 256 + i] = w34o_float_to_half(o[i] * sign_of(i));
+    }
     return 0;
 }
 

@@ -1,0 +1,77 @@
+"""Multi-rank host logic on CPU (gloo, world size 2): page-sharded attention over one sequence.
+Each rank holds half of the pages, computes un-normalised (acc, m, l) triples with the CPU oracle,
+the triples are all-gathered in the [world, rows, 258] layout the GPU entry points use, and the merge
+must reproduce the unsharded result.  Also covers the sharding helpers."""
+import os
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_sharding_helpers():
+    from warp34_b200 import sharding
+    assert [sharding.split_batch(64, 8, r) for r in range(8)] == [(8 * r, 8 * r + 8) for r in range(8)]
+    parts = [sharding.split_batch(10, 4, r) for r in range(4)]
+    assert parts == [(0, 3), (3, 6), (6, 8), (8, 10)]
+    assert sharding.split_kv_heads(4, 24, 2, 1) == ((2, 4), (12, 24), 1)
+    assert sharding.split_kv_heads(4, 24, 8, 5) == ((2, 3), (12, 18), 2)
+    cuts = [sharding.split_pages(262144, 8, r) for r in range(8)]
+    assert cuts[0] == (0, 32768) and cuts[-1] == (229376, 262144)
+    assert all(a[1] == b[0] for a, b in zip(cuts, cuts[1:]))
+    odd = [sharding.split_pages(100, 4, r) for r in range(4)]
+    assert odd == [(0, 32), (32, 64), (64, 96), (96, 100)]
+    assert [sharding.split_pages(20, 4, r) for r in range(4)] == [(0, 16), (16, 20), (20, 20), (20, 20)]
+
+
+def _worker(rank, world, port, tmp):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import torch
+    import torch.distributed as dist
+    import oracle
+    from util import canonical_layout, host_batch
+    from warp34_b200 import sharding, synth
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    hq, hkv, T = 8, 2, 200
+    k, v = synth.make_kv(T, hkv, 3)
+    q = synth.make_q(1, hq, 3).numpy().view(np.uint16)
+    lay = canonical_layout(hkv)
+    npages = (T + 15) // 16
+    perm = np.random.RandomState(7).permutation(npages) + 1
+    k_pool = np.zeros((npages + 1) * hkv * 2112, np.uint8)
+    v_pool = np.zeros_like(k_pool)
+    lay.k_base, lay.v_base = k_pool.ctypes.data, v_pool.ctypes.data
+    slots = [int(perm[t // 16]) * 16 + t % 16 for t in range(T)]
+    ab, keep = host_batch([0, T], [0], [T], [perm.tolist()], slots)
+    assert oracle.kv_cache_write(lay, ab, k.numpy().view(np.uint16), v.numpy().view(np.uint16), hkv * 256, hkv * 256) == 0
+    lo, hi = sharding.split_pages(T, world, rank)
+    bt = np.zeros((1, npages), np.int32)
+    bt[0, :(hi - lo + 15) // 16] = perm[lo // 16:(hi + 15) // 16]
+    sb, keep2 = host_batch([0, 1], [hi - lo - 1], [hi - lo], bt)
+    triples = np.zeros((hq, 258), np.float32)
+    assert oracle.paged_attention_partial(lay, sb, q, triples, hq) == 0
+    gathered = torch.zeros(world * hq, 258)  # rank-major concatenation = [world, rows, 258]
+    dist.all_gather_into_tensor(gathered, torch.from_numpy(triples))
+    merged = np.zeros((hq, 256), np.uint16)
+    assert oracle.merge_shards(np.ascontiguousarray(gathered.numpy()).reshape(world, hq, 258), merged) == 0
+    fb, keep3 = host_batch([0, 1], [T - 1], [T], [perm.tolist()])
+    whole = np.zeros((1, hq, 256), np.uint16)
+    assert oracle.paged_attention(lay, fb, q, whole, hq) == 0
+    a = merged.view(np.float16).astype(np.float32)
+    w = whole.view(np.float16).astype(np.float32)[0]
+    np.save(os.path.join(tmp, f"err{rank}.npy"), np.array([np.abs(a - w).max(), np.abs(w).max()]))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_page_sharded_merge_over_gloo(tmp_path, oracle_lib):
+    import torch.multiprocessing as mp
+    port = 29500 + (os.getpid() % 2000)
+    mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    for r in range(2):
+        err, scale = np.load(tmp_path / f"err{r}.npy")
+        assert err <= 1e-3 + 2e-3 * scale, (r, err, scale)

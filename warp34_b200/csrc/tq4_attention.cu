@@ -848,19 +848,39 @@ __global__ void __launch_bounds__(128) tq4_attention_merge_kernel(const StreamPa
     if (npages > 0 && per > 0) {
         const int us = unit_prefix[r] + item * npages;
         const int w_first = us / per, w_last = (us + npages - 1) / per;
-        const int slot0 = item_prefix[r] + item;
-        for (int w = w_first; w <= w_last; ++w) {
-            const float* ps = partials + (size_t)(w + slot0) * kPartialFloats + kRowsPerGroup * kHeadDim;
-            if (ps[kRowsPerGroup + row8] > 0.0f) m_tot = fmaxf(m_tot, ps[row8]);
-        }
-        for (int w = w_first; w <= w_last; ++w) {
-            const float* pa = partials + (size_t)(w + slot0) * kPartialFloats;
-            const float ls = pa[kRowsPerGroup * kHeadDim + kRowsPerGroup + row8];
-            if (ls > 0.0f) {
-                const float wgt = ex2(pa[kRowsPerGroup * kHeadDim + row8] - m_tot);
-                l_tot += ls * wgt;
+        const float* base = partials + (size_t)(w_first + item_prefix[r] + item) * kPartialFloats;
+        const int nparts = w_last - w_first + 1;
+        // Lanes fetch the (m, l) pairs of up to 32 partials at once; the accumulation then runs
+        // over independent loads instead of a chain of dependent ones.
+        for (int c0 = 0; c0 < nparts; c0 += 32) {
+            const int mine = c0 + lane;
+            float m_s = -1e30f, l_s = 0.0f;
+            if (mine < nparts) {
+                const float* ps = base + (size_t)mine * kPartialFloats + kRowsPerGroup * kHeadDim;
+                l_s = ps[kRowsPerGroup + row8];
+                m_s = (l_s > 0.0f) ? ps[row8] : -1e30f;
+            }
+            float m_chunk = m_s;
 #pragma unroll
-                for (int j = 0; j < 8; ++j) acc[j] += pa[row8 * kHeadDim + lane + 32 * j] * wgt;
+            for (int d = 16; d > 0; d >>= 1) m_chunk = fmaxf(m_chunk, __shfl_xor_sync(0xffffffffu, m_chunk, d));
+            const float m_new = fmaxf(m_tot, m_chunk);
+            const float rescale = ex2(m_tot - m_new);  // 1 for the first chunk's -1e30 -> anything: acc is 0
+            l_tot *= rescale;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] *= rescale;
+            m_tot = m_new;
+            const float w_s = (l_s > 0.0f) ? ex2(m_s - m_tot) : 0.0f;
+            float lw = l_s * w_s;
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) lw += __shfl_xor_sync(0xffffffffu, lw, d);
+            l_tot += lw;
+            const int n_here = min(32, nparts - c0);
+#pragma unroll 4
+            for (int sidx = 0; sidx < n_here; ++sidx) {
+                const float wgt = __shfl_sync(0xffffffffu, w_s, sidx);
+                const float* pa = base + (size_t)(c0 + sidx) * kPartialFloats + row8 * kHeadDim;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[j] += pa[lane + 32 * j] * wgt;
             }
         }
     }

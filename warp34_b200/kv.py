@@ -371,7 +371,7 @@ class DecodeStep:
         self.h2d_bytes = self.io.nbytes + 2 * self.k_host.numel() * 2 + self.q_host.numel() * 2
         self.d2h_bytes = self.out_host.numel() * 2
 
-    def run(self, q_lens, sm_scale=1.0 / 16.0, lib=None, sync=True):
+    def run(self, q_lens, sm_scale=1.0 / 16.0, lib=None, sync=True, attend=None):
         self.io.pack(self.seqs, q_lens, sm_scale)
         self.io.upload()
         self.k_dev.copy_(self.k_host, non_blocking=True)
@@ -380,7 +380,10 @@ class DecodeStep:
         self.ex.set_stream()
         b = _DescOnly(self.io.desc)
         kv_cache_write(self.ex, self.layer, b, self.k_dev, self.v_dev, lib=lib)
-        paged_attention(self.ex, self.layer, b, self.q_dev, self.out_dev, self.hq, lib=lib)
+        if attend is not None:
+            attend(b)  # e.g. partial attention + all-gather + merge when pages are sharded over GPUs
+        else:
+            paged_attention(self.ex, self.layer, b, self.q_dev, self.out_dev, self.hq, lib=lib)
         self.out_host.copy_(self.out_dev, non_blocking=True)
         if sync:
             torch.cuda.current_stream().synchronize()
