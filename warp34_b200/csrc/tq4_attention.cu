@@ -814,13 +814,17 @@ __global__ void __launch_bounds__(W34_WARPS * 32, 1) tq4_attention_stream_kernel
 // pre-scaled scores) and l.
 constexpr int kRowTripleFloats = kHeadDim + 2;
 
-// One warp per (token, q head): combine partials, then either normalise + inverse rotation +
-// fp16 store, or (PARTIAL_OUT) store the merged (acc, m, l) triple for a cross-shard merge.
+// One block of four warps per (token, q head): warp w combines the partials w, w+4, ... of the
+// row with an online softmax merge, the four results are combined through shared memory, then
+// either normalise + inverse rotation + fp16 store, or (PARTIAL_OUT) store the merged
+// (acc, m, l) triple for a cross-shard merge.  A long single sequence has hundreds of partials
+// per row and only a few rows, hence the split over warps.
 template <bool PARTIAL_OUT>
 __global__ void __launch_bounds__(128) tq4_attention_merge_kernel(const StreamParams p) {
+    __shared__ float s_acc[4][kHeadDim];
+    __shared__ float s_m[4], s_l[4];
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-    const long long row_ll = (long long)blockIdx.x * 4 + wid;
-    if (row_ll >= (long long)p.batch.total_tokens * p.num_q_heads) return;
+    const long long row_ll = blockIdx.x;
     const int tok = (int)(row_ll / p.num_q_heads), q_head = (int)(row_ll % p.num_q_heads);
     if (p.batch.valid_token_mask != nullptr && p.batch.valid_token_mask[tok] == 0) return;
     const int R = p.batch.num_reqs;
@@ -850,10 +854,10 @@ __global__ void __launch_bounds__(128) tq4_attention_merge_kernel(const StreamPa
         const int w_first = us / per, w_last = (us + npages - 1) / per;
         const float* base = partials + (size_t)(w_first + item_prefix[r] + item) * kPartialFloats;
         const int nparts = w_last - w_first + 1;
-        // Lanes fetch the (m, l) pairs of up to 32 partials at once; the accumulation then runs
-        // over independent loads instead of a chain of dependent ones.
-        for (int c0 = 0; c0 < nparts; c0 += 32) {
-            const int mine = c0 + lane;
+        // this warp's partials: wid, wid + 4, ...; lanes fetch up to 32 (m, l) pairs at once so
+        // that the accumulation runs over independent loads
+        for (int c0 = wid; c0 < nparts; c0 += 128) {
+            const int mine = c0 + 4 * lane;
             float m_s = -1e30f, l_s = 0.0f;
             if (mine < nparts) {
                 const float* ps = base + (size_t)mine * kPartialFloats + kRowsPerGroup * kHeadDim;
@@ -864,7 +868,7 @@ __global__ void __launch_bounds__(128) tq4_attention_merge_kernel(const StreamPa
 #pragma unroll
             for (int d = 16; d > 0; d >>= 1) m_chunk = fmaxf(m_chunk, __shfl_xor_sync(0xffffffffu, m_chunk, d));
             const float m_new = fmaxf(m_tot, m_chunk);
-            const float rescale = ex2(m_tot - m_new);  // 1 for the first chunk's -1e30 -> anything: acc is 0
+            const float rescale = ex2(m_tot - m_new);
             l_tot *= rescale;
 #pragma unroll
             for (int j = 0; j < 8; ++j) acc[j] *= rescale;
@@ -874,15 +878,32 @@ __global__ void __launch_bounds__(128) tq4_attention_merge_kernel(const StreamPa
 #pragma unroll
             for (int d = 16; d > 0; d >>= 1) lw += __shfl_xor_sync(0xffffffffu, lw, d);
             l_tot += lw;
-            const int n_here = min(32, nparts - c0);
+            const int n_here = min(32, (nparts - c0 + 3) / 4);
 #pragma unroll 4
             for (int sidx = 0; sidx < n_here; ++sidx) {
                 const float wgt = __shfl_sync(0xffffffffu, w_s, sidx);
-                const float* pa = base + (size_t)(c0 + sidx) * kPartialFloats + row8 * kHeadDim;
+                const float* pa = base + (size_t)(c0 + 4 * sidx) * kPartialFloats + row8 * kHeadDim;
 #pragma unroll
                 for (int j = 0; j < 8; ++j) acc[j] += pa[lane + 32 * j] * wgt;
             }
         }
+    }
+    // combine the four warps
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s_acc[wid][lane + 32 * j] = acc[j];
+    if (lane == 0) { s_m[wid] = m_tot; s_l[wid] = l_tot; }
+    __syncthreads();
+    if (wid != 0) return;
+    m_tot = fmaxf(fmaxf(s_m[0], s_m[1]), fmaxf(s_m[2], s_m[3]));
+    l_tot = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+        const float wgt = (s_l[w] > 0.0f) ? ex2(s_m[w] - m_tot) : 0.0f;
+        l_tot += s_l[w] * wgt;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += s_acc[w][lane + 32 * j] * wgt;
     }
     if (PARTIAL_OUT) {
         float* dst = p.triple_out + ((size_t)tok * p.num_q_heads + q_head) * kRowTripleFloats;
@@ -1108,9 +1129,9 @@ static int launch_attention(const warp34_exec* ex, const warp34_kv_layer_layout*
     tq4_attention_stream_kernel<kStages><<<grid, kWarpsPerCta * 32, smem, st>>>(p);
     const long long rows = (long long)batch->total_tokens * num_q_heads;
     if (triple_out != nullptr) {
-        tq4_attention_merge_kernel<true><<<(unsigned)((rows + 3) / 4), 128, 0, st>>>(p);
+        tq4_attention_merge_kernel<true><<<(unsigned)rows, 128, 0, st>>>(p);
     } else {
-        tq4_attention_merge_kernel<false><<<(unsigned)((rows + 3) / 4), 128, 0, st>>>(p);
+        tq4_attention_merge_kernel<false><<<(unsigned)rows, 128, 0, st>>>(p);
     }
     return (int)cudaGetLastError();
 }
