@@ -181,6 +181,20 @@ size_t warp34_paged_attention_scratch_bytes(const warp34_kv_layer_layout* layout
                                             int num_q_heads);
 
 /*
+ * bf16 activations over TQ4 pages.  The reference's TQ4 path takes fp16 activations only (its
+ * bf16 entry points, warp34_cuda.h:363-368, require BF16 *storage*: op_kv_cache.cu:860-865);
+ * these two take bf16 K / V (append) and bf16 Q / output (attention) with the same descriptors.
+ * Values representable in both types produce the same packed bytes as the fp16 entry points.
+ */
+int warp34_tq4_kv_cache_write_strided_bf16(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
+                                           const warp34_attention_batch* batch,
+                                           const void* k_in, const void* v_in,
+                                           int k_row_stride, int v_row_stride);
+int warp34_tq4_paged_attention_bf16(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
+                                    const warp34_attention_batch* batch,
+                                    const void* q_in, void* attn_out, int num_q_heads);
+
+/*
  * Attention over a page shard of longer sequences: same arguments as
  * warp34_paged_attention_f16, but the result is left un-normalised so that shards held by
  * different GPUs can be merged.  triples_out is fp32 [total_tokens, num_q_heads, 258]: 256

@@ -421,3 +421,42 @@ def test_copy_on_write_tail_page_gives_the_unshared_result(env):
     assert (outs[0] == outs[1]).all()
     assert (layer.k.view(40, -1)[donor_tail].cpu().numpy() == before).all()
     assert sharer.pages[:4] == donor.pages[:4] and sharer.pages[4] != donor_tail
+
+
+def test_bf16_activations_match_the_fp16_entry_points(env):
+    """warp34_tq4_kv_cache_write_strided_bf16 / warp34_tq4_paged_attention_bf16: inputs on the grid
+    bf16 and fp16 share give bit-identical TQ4 bytes; the attention output is the bf16 rounding of
+    the same result; bf16 values beyond the fp16 range are accepted."""
+    kv, synth, lib = env["kv"], env["synth"], env["lib"]
+    hq, hkv, ctx = 8, 2, [75, 300]
+    T = sum(ctx)
+    k, v = synth.make_kv(T, hkv, 81)
+    q = synth.make_q(2, hq, 81)
+    pools, outs = [], []
+    for bf16 in (False, True):
+        wl = synth.PagedWorkload([0] * 2, ctx, hkv, seed=81, fill=0x22)
+        b = wl.step()
+        kd, vd = (k.to(torch.bfloat16).cuda(), v.to(torch.bfloat16).cuda()) if bf16 else (k.cuda(), v.cuda())
+        fn = lib.warp34_tq4_kv_cache_write_strided_bf16 if bf16 else lib.warp34_kv_cache_write_strided
+        assert fn(C.byref(env["ex"].ex), C.byref(wl.layer.layout), C.byref(b.desc), kd.data_ptr(), vd.data_ptr(),
+                  hkv * 256, hkv * 256) == 0
+        for s, c in zip(wl.seqs, ctx):
+            s.commit(c - 1)
+        d = wl.step(q_lens=[1, 1])
+        qd = q.to(torch.bfloat16).cuda() if bf16 else q.cuda()
+        out = torch.zeros_like(qd)
+        fn = lib.warp34_tq4_paged_attention_bf16 if bf16 else lib.warp34_paged_attention_f16
+        assert fn(C.byref(env["ex"].ex), C.byref(wl.layer.layout), C.byref(d.desc), qd.data_ptr(), out.data_ptr(), hq) == 0
+        torch.cuda.synchronize()
+        pools.append((wl.layer.k.cpu().numpy(), wl.layer.v.cpu().numpy()))
+        outs.append(out.float().cpu().numpy())
+    assert (pools[0][0] == pools[1][0]).all() and (pools[0][1] == pools[1][1]).all()
+    # same fp32 result rounded to fp16 / bf16: they differ by at most one bf16 ulp
+    assert (np.abs(outs[0] - outs[1]) <= 2.0 ** -8 * np.abs(outs[0]) + 1e-6).all()
+    # a bf16 row far outside the fp16 range still encodes (scales saturate to +inf like any overflow)
+    wl = synth.PagedWorkload([0], [16], hkv, seed=82, fill=0)
+    big = torch.full((16, hkv * 256), 3.0e38, dtype=torch.bfloat16).cuda()
+    b = wl.step()
+    assert lib.warp34_tq4_kv_cache_write_strided_bf16(C.byref(env["ex"].ex), C.byref(wl.layer.layout), C.byref(b.desc),
+                                                      big.data_ptr(), big.data_ptr(), hkv * 256, hkv * 256) == 0
+    torch.cuda.synchronize()

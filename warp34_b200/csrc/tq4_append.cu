@@ -26,6 +26,8 @@
 // same approximate instructions and denormals flush the same way.
 #include "tq4_common.cuh"
 
+#include <cuda_bf16.h>
+
 namespace w34 {
 
 // The reference computes warp_reduce_sum(a * b): the product is rounded, then summed by the
@@ -45,18 +47,21 @@ namespace w34 {
 #define W34_CONTRACT_CC 0
 #endif
 
-// code = #{i : rv > boundary_i} for the 15 ascending, symmetric boundaries (b[7] = 0).
-__device__ __forceinline__ int tq4_bucket(float rv, const float (&bpos)[7]) {
-    // bpos[k] = boundary[8 + k] > 0.  For rv > 0 all of b[0..7] are below rv; for rv <= 0
-    // none of b[7..14] is, and rv > -B  <=>  |rv| < B.
-    const float a = fabsf(rv);
-    int gt = 0, lt = 0;
-#pragma unroll
-    for (int k = 0; k < 7; ++k) {
-        gt += (a > bpos[k]) ? 1 : 0;
-        lt += (a < bpos[k]) ? 1 : 0;
-    }
-    return (rv > 0.0f) ? (8 + gt) : lt;
+// code = #{i : rv > boundary_i} for the 15 ascending, symmetric boundaries (b[7] = 0), by a
+// three-level binary search on |rv| in the integer domain.  bpos[k] = bits(boundary[8 + k]) > 0.
+// For rv > 0 all of b[0..7] are below rv and the code is 8 + #{k : |rv| > B_k}; for rv <= 0 none
+// of b[7..14] is, rv > -B  <=>  |rv| < B, and the code is 7 - #{k : |rv| >= B_k}.  Positive floats
+// order like their bit patterns and ">= B" is "> B - 1 ulp", so both cases count
+// #{k : bits(|rv|) + (rv > 0 ? 0 : 1) > bits(B_k)}.  NaN gives 0 and -0 gives 7, as the
+// comparison chain does.
+__device__ __forceinline__ int tq4_bucket(float rv, const uint32_t (&bpos)[7]) {
+    const bool pos = rv > 0.0f;
+    const uint32_t x = (__float_as_uint(rv) & 0x7fffffffu) + (pos ? 0u : 1u);
+    const bool c1 = x > bpos[3];
+    const bool c2 = x > (c1 ? bpos[5] : bpos[1]);
+    const uint32_t t3 = c1 ? (c2 ? bpos[6] : bpos[4]) : (c2 ? bpos[2] : bpos[0]);
+    const int c = (c1 ? 4 : 0) + (c2 ? 2 : 0) + ((x > t3) ? 1 : 0);
+    return pos ? (8 + c) : (7 - c);
 }
 
 // One level of the halving exchange: the lane keeps the N/2 values whose index bit
@@ -115,14 +120,21 @@ __device__ __forceinline__ void reg_levels(const float (&a)[4], const float (&b)
 struct AppendParams {
     warp34_kv_layer_layout layout;
     warp34_attention_batch batch;
-    const __half* k_in;
-    const __half* v_in;
+    const uint16_t* k_in;   // fp16 or bf16 bits, see the kernel's template argument
+    const uint16_t* v_in;
     int k_row_stride;
     int v_row_stride;
     int total_rows;  // total_tokens * local_kv_heads * 2
 };
 
-__global__ void __launch_bounds__(128) tq4_append_kernel(const AppendParams p) {
+#ifndef W34_APPEND_BLOCKS_PER_SM
+#define W34_APPEND_BLOCKS_PER_SM 5
+#endif
+
+// IN_BF16: activations are bf16 instead of fp16.  Values that both types can hold encode to the
+// same bytes; bf16 values beyond the fp16 range are simply larger fp32 inputs.
+template <bool IN_BF16>
+__global__ void __launch_bounds__(128, W34_APPEND_BLOCKS_PER_SM) tq4_append_kernel(const AppendParams p) {
     __shared__ float s_centroid[16];
     if (threadIdx.x < 16) s_centroid[threadIdx.x] = tq4_centroid(threadIdx.x);
     __syncthreads();
@@ -130,11 +142,27 @@ __global__ void __launch_bounds__(128) tq4_append_kernel(const AppendParams p) {
     const int lane = threadIdx.x & 31;
     const int sub = lane & 7;
     const int lane_base = lane & ~7;
-    const int warp_global = blockIdx.x * 4 + (threadIdx.x >> 5);
-    const int row_id = warp_global * 4 + (lane >> 3);
+    // Per-lane constants, paid once per thread: the warp then loops over groups of 4 rows.
+    uint32_t sign_word = 0;   // bit r = sign of column sub + 8 r
+#pragma unroll
+    for (int r = 0; r < 32; ++r) {
+        const int col = sub + 8 * r;
+        sign_word |= ((c_sign_mask[col >> 5] >> (col & 31)) & 1u) << r;
+    }
+    uint32_t bpos[7];
+#pragma unroll
+    for (int k = 0; k < 7; ++k) bpos[k] = c_boundary_bits[8 + k];
+    // butterfly direction of the three cross-lane WHT stages: upper lanes compute o - v
+    const float dir1 = (sub & 1) ? -1.0f : 1.0f, dir2 = (sub & 2) ? -1.0f : 1.0f, dir4 = (sub & 4) ? -1.0f : 1.0f;
+
+    const int heads = p.layout.local_kv_heads;
+    const int warps_total = gridDim.x * 4;
+    const int quads = (p.total_rows + 3) >> 2;
+#pragma unroll 1
+    for (int quad = blockIdx.x * 4 + (threadIdx.x >> 5); quad < quads; quad += warps_total) {
+    const int row_id = quad * 4 + (lane >> 3);
 
     // ---- resolve the row: (token, head, K or V), masks, destination ------------------
-    const int heads = p.layout.local_kv_heads;
     bool active = row_id < p.total_rows;
     const int which = row_id & 1;
     const int th = row_id >> 1;
@@ -155,7 +183,7 @@ __global__ void __launch_bounds__(128) tq4_append_kernel(const AppendParams p) {
     }
     // All 8 lanes of a row agree on `active`; rows of a warp may differ, and every lane
     // still takes part in the shuffles below.
-    const __half* src = nullptr;
+    const uint16_t* src = nullptr;
     uint8_t* dst = nullptr;
     if (active) {
         const int page = slot >> 4, off = slot & 15;
@@ -174,21 +202,19 @@ __global__ void __launch_bounds__(128) tq4_append_kernel(const AppendParams p) {
     float v[32];
 #pragma unroll
     for (int r = 0; r < 32; ++r) {
-        const int col = sub + 8 * r;
-        const float x = active ? __half2float(src[col]) : 0.0f;
-        v[r] = apply_sign(x, col);
+        const uint16_t raw = active ? src[sub + 8 * r] : (uint16_t)0;
+        const float x = IN_BF16 ? __uint_as_float((uint32_t)raw << 16) : __half2float(__ushort_as_half(raw));
+        v[r] = __uint_as_float(__float_as_uint(x) ^ ((sign_word << (31 - r)) & 0x80000000u));
     }
 
     // ---- WHT-256: stages 1,2,4 across lanes, 8..128 in registers ----------------------
+    // lower lane: v + o, upper lane: o - v; fma(+-1, v, o) is the same single rounding.
 #pragma unroll
-    for (int h = 1; h < 8; h <<= 1) {
-        const bool upper = (sub & h) != 0;
+    for (int r = 0; r < 32; ++r) v[r] = __fmaf_rn(dir1, v[r], __shfl_xor_sync(0xffffffffu, v[r], 1));
 #pragma unroll
-        for (int r = 0; r < 32; ++r) {
-            const float o = __shfl_xor_sync(0xffffffffu, v[r], h);
-            v[r] = upper ? __fsub_rn(o, v[r]) : __fadd_rn(v[r], o);
-        }
-    }
+    for (int r = 0; r < 32; ++r) v[r] = __fmaf_rn(dir2, v[r], __shfl_xor_sync(0xffffffffu, v[r], 2));
+#pragma unroll
+    for (int r = 0; r < 32; ++r) v[r] = __fmaf_rn(dir4, v[r], __shfl_xor_sync(0xffffffffu, v[r], 4));
 #pragma unroll
     for (int s = 1; s < 32; s <<= 1) {
 #pragma unroll
@@ -228,10 +254,6 @@ __global__ void __launch_bounds__(128) tq4_append_kernel(const AppendParams p) {
     }
 
     // ---- codes, centroids, least-squares sums ------------------------------------------
-    float bpos[7];
-#pragma unroll
-    for (int k = 0; k < 7; ++k) bpos[k] = tq4_boundary(8 + k);
-
     uint32_t nib[4] = {0u, 0u, 0u, 0u};  // nibble r at nib[r >> 3] bits 4 (r & 7)
     float vcl[8], ccl[8];
 #pragma unroll
@@ -243,7 +265,7 @@ __global__ void __launch_bounds__(128) tq4_append_kernel(const AppendParams p) {
             const int r = 4 * j + q4;
             const float inv = (q4 & 2) ? inv_hi[j >> 2] : inv_lo[j >> 2];
             const int q = tq4_bucket(__fmul_rn(a[q4], inv), bpos);
-            nib[r >> 3] |= (uint32_t)q << (4 * (r & 7));
+            nib[r >> 3] += (uint32_t)q * (1u << (4 * (r & 7)));   // disjoint nibbles: add == or
             c[q4] = s_centroid[q];
         }
         float hi_unused;
@@ -317,18 +339,20 @@ __global__ void __launch_bounds__(128) tq4_append_kernel(const AppendParams p) {
             h[51 + 2 * sub] = (uint16_t)(nib[3] >> 16);
         }
     }
+    }  // row-quad loop
 }
 
 }  // namespace w34
 
-extern "C" int warp34_kv_cache_write_strided(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
-                                             const warp34_attention_batch* batch, const void* k_in,
-                                             const void* v_in, int k_row_stride, int v_row_stride) {
+namespace w34 {
+static int launch_append(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
+                         const warp34_attention_batch* batch, const void* k_in, const void* v_in,
+                         int k_row_stride, int v_row_stride, bool in_bf16) {
     if (ex == nullptr || layout == nullptr || batch == nullptr || k_in == nullptr || v_in == nullptr) {
         return (int)cudaErrorInvalidValue;
     }
     if (batch->total_tokens <= 0 || layout->local_kv_heads <= 0) return 0;
-    if (layout->head_dim != w34::kHeadDim || layout->block_size != w34::kPageTokens ||
+    if (layout->head_dim != kHeadDim || layout->block_size != kPageTokens ||
         layout->k_format != WARP34_KV_FORMAT_TQ4 || layout->v_format != WARP34_KV_FORMAT_TQ4 ||
         layout->k_transform != WARP34_KV_TRANSFORM_RADEMACHER_WHT256 ||
         layout->v_transform != WARP34_KV_TRANSFORM_RADEMACHER_WHT256) {
@@ -345,19 +369,45 @@ extern "C" int warp34_kv_cache_write_strided(const warp34_exec* ex, const warp34
          layout->v_token_stride_bytes) & 1u) {
         return (int)cudaErrorInvalidValue;
     }
-    w34::AppendParams p;
+    AppendParams p;
     p.layout = *layout;
     p.batch = *batch;
-    p.k_in = static_cast<const __half*>(k_in);
-    p.v_in = static_cast<const __half*>(v_in);
+    p.k_in = static_cast<const uint16_t*>(k_in);
+    p.v_in = static_cast<const uint16_t*>(v_in);
     p.k_row_stride = k_row_stride;
     p.v_row_stride = v_row_stride;
     const long long rows = 2ll * batch->total_tokens * layout->local_kv_heads;
     if (rows > 0x7fffffffll) return (int)cudaErrorInvalidValue;
     p.total_rows = (int)rows;
-    const unsigned blocks = (unsigned)((rows + 15) / 16);  // 4 warps x 4 rows per block
-    w34::tq4_append_kernel<<<blocks, 128, 0, (cudaStream_t)ex->stream>>>(p);
+    // 4 warps x 4 rows per block and pass; each warp then strides over the remaining row groups,
+    // so per-thread constants are set up once.  The grid is what the GPU can hold at once.
+    const long long blocks_needed = (rows + 15) / 16;
+    static int sm_count_cache[64];
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64) {
+        if (sm_count_cache[dev] == 0) {
+            int n = 0;
+            if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0) {
+                sm_count_cache[dev] = n;
+            }
+        }
+        if (sm_count_cache[dev] > 0) sms = sm_count_cache[dev];
+    }
+    const long long resident = (long long)sms * W34_APPEND_BLOCKS_PER_SM;
+    const unsigned blocks = (unsigned)(blocks_needed < resident ? blocks_needed : resident);
+    if (in_bf16) {
+        tq4_append_kernel<true><<<blocks, 128, 0, (cudaStream_t)ex->stream>>>(p);
+    } else {
+        tq4_append_kernel<false><<<blocks, 128, 0, (cudaStream_t)ex->stream>>>(p);
+    }
     return (int)cudaGetLastError();
+}
+}  // namespace w34
+
+extern "C" int warp34_kv_cache_write_strided(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
+                                             const warp34_attention_batch* batch, const void* k_in,
+                                             const void* v_in, int k_row_stride, int v_row_stride) {
+    return w34::launch_append(ex, layout, batch, k_in, v_in, k_row_stride, v_row_stride, false);
 }
 
 extern "C" int warp34_kv_cache_write(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
@@ -365,5 +415,11 @@ extern "C" int warp34_kv_cache_write(const warp34_exec* ex, const warp34_kv_laye
                                      const void* v_in) {
     if (layout == nullptr) return (int)cudaErrorInvalidValue;
     const int stride = layout->local_kv_heads * layout->head_dim;
-    return warp34_kv_cache_write_strided(ex, layout, batch, k_in, v_in, stride, stride);
+    return w34::launch_append(ex, layout, batch, k_in, v_in, stride, stride, false);
+}
+
+extern "C" int warp34_tq4_kv_cache_write_strided_bf16(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
+                                                      const warp34_attention_batch* batch, const void* k_in,
+                                                      const void* v_in, int k_row_stride, int v_row_stride) {
+    return w34::launch_append(ex, layout, batch, k_in, v_in, k_row_stride, v_row_stride, true);
 }

@@ -26,6 +26,7 @@
 // the PV product (the same factoring as op_kv_cache.cu:653-656 and :695-705).
 #include "tq4_common.cuh"
 
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
 namespace w34 {
@@ -63,12 +64,23 @@ __device__ __forceinline__ int row_min_kv(const warp34_attention_batch& b, const
     return m;
 }
 
+// Activations are fp16 (the reference ABI) or bf16 (additive entry points): 16-bit loads and
+// stores with the conversion picked at run time, outside the per-page loops.
+__device__ __forceinline__ float load_act(const void* base, size_t idx, int bf16) {
+    const uint16_t raw = static_cast<const uint16_t*>(base)[idx];
+    return bf16 ? __uint_as_float((uint32_t)raw << 16) : __half2float(__ushort_as_half(raw));
+}
+__device__ __forceinline__ void store_act(void* base, size_t idx, float x, int bf16) {
+    static_cast<uint16_t*>(base)[idx] = bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(x))
+                                             : __half_as_ushort(__float2half_rn(x));
+}
+
 // ---------------------------------------------------------------------------------------
 // Scalar dequant-then-attend: one warp per (token, q head), fp32, any strides.
 // ---------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(128) tq4_attention_scalar_kernel(
     const warp34_kv_layer_layout layout, const warp34_attention_batch batch,
-    const __half* __restrict__ q_in, __half* __restrict__ attn_out, int num_q_heads) {
+    const void* __restrict__ q_in, void* __restrict__ attn_out, int num_q_heads, int io_bf16) {
     __shared__ float s_x[4][kHeadDim];
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const long long row = (long long)blockIdx.x * 4 + wid;
@@ -85,13 +97,12 @@ __global__ void __launch_bounds__(128) tq4_attention_scalar_kernel(
     const int max_kv = row_max_kv(batch, g, q_off);
     const int min_kv = row_min_kv(batch, g, q_off);
 
-    const __half* q_row = q_in + ((size_t)tok * num_q_heads + q_head) * kHeadDim;
-    __half* out_row = attn_out + ((size_t)tok * num_q_heads + q_head) * kHeadDim;
+    const size_t row_base = ((size_t)tok * num_q_heads + q_head) * kHeadDim;
 
     // Q' = WHT(sign * q); then re-distribute so that lane L owns rotated columns [8 L, 8 L + 8).
     float t[8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) t[j] = apply_sign(__half2float(q_row[lane + 32 * j]), lane + 32 * j);
+    for (int j = 0; j < 8; ++j) t[j] = apply_sign(load_act(q_in, row_base + lane + 32 * j, io_bf16), lane + 32 * j);
     wht256_lanes(t, lane);
 #pragma unroll
     for (int j = 0; j < 8; ++j) s_x[wid][lane + 32 * j] = t[j];
@@ -137,7 +148,7 @@ __global__ void __launch_bounds__(128) tq4_attention_scalar_kernel(
     for (int j = 0; j < 8; ++j) t[j] = s_x[wid][lane + 32 * j];
     wht256_lanes(t, lane);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) out_row[lane + 32 * j] = __float2half_rn(apply_sign(t[j], lane + 32 * j));
+    for (int j = 0; j < 8; ++j) store_act(attn_out, row_base + lane + 32 * j, apply_sign(t[j], lane + 32 * j), io_bf16);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -174,8 +185,9 @@ __host__ __device__ inline size_t plan_bytes(int num_reqs) {
 struct StreamParams {
     warp34_kv_layer_layout layout;
     warp34_attention_batch batch;
-    const __half* q_in;
-    __half* attn_out;
+    const void* q_in;      // fp16 or bf16, see io_bf16
+    void* attn_out;
+    int io_bf16;
     float* triple_out;     // [total_tokens, num_q_heads, 258] when the merge stops before normalising
     uint8_t* scratch;      // plan header, arrays, then partial slots
     int num_q_heads;
@@ -183,6 +195,7 @@ struct StreamParams {
     int num_warps;         // worker warps over the whole grid
     int max_slots;
     uint32_t smem_bytes;   // dynamic shared memory given to the stream kernel
+    int rows_per_group;    // query rows per work item: 8 (one warp per item) or 8 * NT (teams)
     float q_scale;         // sm_scale * log2(e) / kLutScale, folded into Q'
 };
 
@@ -209,7 +222,7 @@ __global__ void __launch_bounds__(32) tq4_attention_plan_kernel(const StreamPara
                 const int lo = row_min_kv(p.batch, g, 0);
                 const int hi = row_max_kv(p.batch, g, g.q_len - 1);
                 if (hi >= lo) { plo = lo >> 4; npages = (hi >> 4) - plo + 1; }
-                ngroups = (g.q_len * p.gqa + kRowsPerGroup - 1) / kRowsPerGroup;
+                ngroups = (g.q_len * p.gqa + p.rows_per_group - 1) / p.rows_per_group;
             }
         }
         const int items = hkv * ngroups;
@@ -482,9 +495,9 @@ __global__ void __launch_bounds__(W34_WARPS * 32, 1) tq4_attention_stream_kernel
                             (p.batch.valid_token_mask == nullptr || p.batch.valid_token_mask[g.q_start + q_off] != 0);
             float t[8];
             if (ok) {
-                const __half* q_row = p.q_in + ((size_t)(g.q_start + q_off) * p.num_q_heads + q_head) * kHeadDim;
+                const size_t q_base = ((size_t)(g.q_start + q_off) * p.num_q_heads + q_head) * kHeadDim;
 #pragma unroll
-                for (int j = 0; j < 8; ++j) t[j] = apply_sign(__half2float(q_row[lane + 32 * j]), lane + 32 * j);
+                for (int j = 0; j < 8; ++j) t[j] = apply_sign(load_act(p.q_in, q_base + lane + 32 * j, p.io_bf16), lane + 32 * j);
                 wht256_lanes(t, lane);
             } else {
 #pragma unroll
@@ -809,6 +822,482 @@ __global__ void __launch_bounds__(W34_WARPS * 32, 1) tq4_attention_stream_kernel
     }
 }
 
+// ---------------------------------------------------------------------------------------
+// Team kernel: 8 * NT query rows (GQA heads x draft tokens of a verify step) share ONE pass
+// over the KV pages.  A team is four warps; warp t owns a quarter of the 256 channels (half
+// t >> 1 of the row, every other pair of 8-channel words), for the score product and for the
+// output alike, so every code is looked up once per page however many query rows read it and
+// each looked-up fragment feeds NT MMAs.  Per page the team meets twice: after the partial
+// scores (summed through shared memory; the warp that owns an 8-row tile then runs its online
+// softmax) and after the softmax (P fragments and rescale factors go back through shared
+// memory).  Three teams per CTA, one CTA per SM, each team with its own ring of stages.
+// ---------------------------------------------------------------------------------------
+#ifndef W34_TEAMS
+#define W34_TEAMS 3
+#endif
+#ifndef W34_TEAM_STAGES
+#define W34_TEAM_STAGES 10
+#endif
+constexpr int kTeams = W34_TEAMS;
+constexpr int kTeamWarps = 4;
+constexpr int kTeamStages = W34_TEAM_STAGES;
+
+__device__ __forceinline__ void team_barrier(int team) {
+    asm volatile("bar.sync %0, %1;" ::"r"(team + 1), "r"(kTeamWarps * 32) : "memory");
+}
+__device__ __forceinline__ float4 lds128f(uint32_t addr) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void sts128f(uint32_t addr, float4 v) {
+    asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+__device__ __forceinline__ float2 lds64f(uint32_t addr) {
+    float2 v;
+    asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void sts64f(uint32_t addr, float2 v) {
+    asm volatile("st.shared.v2.f32 [%0], {%1,%2};" ::"r"(addr), "f"(v.x), "f"(v.y) : "memory");
+}
+
+// Carves [lo, hi) minus the 64 KB table at `lut` into chunks: first fit below the table, then above.
+struct SmemCarver {
+    uint32_t a_cur, a_end, b_cur, b_end;
+    bool ok;
+    __device__ SmemCarver(uint32_t lo, uint32_t lut, uint32_t hi)
+        : a_cur(lo), a_end(lut), b_cur(lut + kLutBytes), b_end(hi), ok(lut + kLutBytes <= hi) {}
+    __device__ uint32_t take(uint32_t bytes, uint32_t align) {
+        uint32_t a = (a_cur + align - 1) & ~(align - 1);
+        if (a + bytes <= a_end) { a_cur = a + bytes; return a; }
+        uint32_t b = (b_cur + align - 1) & ~(align - 1);
+        if (b + bytes <= b_end) { b_cur = b + bytes; return b; }
+        ok = false;
+        return b_end >= bytes ? b_end - bytes : 0;
+    }
+};
+
+template <int NT>
+__global__ void __launch_bounds__(kTeams * kTeamWarps * 32, 1) tq4_attention_team_kernel(const StreamParams p) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    constexpr int RG = 8 * NT;
+    constexpr int PARTIAL = RG * kHeadDim + 2 * RG;
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int team = wid >> 2, t = wid & 3;     // warp t of its team
+    const int half = t >> 1, cset = t & 1;      // 128-half and word set owned by this warp
+    const uint32_t win_lo = smem_u32(smem);
+    const uint32_t win_hi = win_lo + p.smem_bytes;
+    const uint32_t lut_addr = (win_lo + 0xffffu) & ~0xffffu;
+    PlanHeader* hdr = reinterpret_cast<PlanHeader*>(p.scratch);
+
+    SmemCarver carve(win_lo, lut_addr, win_hi);
+    uint32_t ring = 0, sx = 0, px = 0, ax = 0, bars = 0;
+    for (int tm = 0; tm < kTeams; ++tm) {
+        const uint32_t r_ = carve.take(kTeamStages * kStageStride, 128);
+        if (tm == team) ring = r_;
+    }
+    for (int tm = 0; tm < kTeams; ++tm) {
+        const uint32_t s_ = carve.take(kTeamWarps * NT * 512, 16);   // partial scores [warp][tile][lane] float4
+        const uint32_t p_ = carve.take(NT * 2 * 2 * 128, 16);         // P fragments [tile][half][reg][lane]
+        const uint32_t a_ = carve.take(NT * 4 * 8, 8);                // rescale factors [tile][tig] float2
+        const uint32_t b_ = carve.take(kTeamStages * 8, 8);
+        if (tm == team) { sx = s_; px = p_; ax = a_; bars = b_; }
+    }
+    if (!carve.ok) {
+        if (threadIdx.x == 0) atomicOr(&hdr->status, 2);
+        return;
+    }
+    uint8_t* ring_gen = smem + (ring - win_lo);
+
+    for (int i = threadIdx.x; i < 256 * 32; i += blockDim.x) {
+        const int byte = i >> 5, ln = i & 31;
+        sts32(lut_addr + (uint32_t)(byte * 256 + ln * 4),
+              pack_half2(kLutScale * tq4_centroid(byte & 15), kLutScale * tq4_centroid(byte >> 4)));
+    }
+    if (t == 0 && lane == 0) {
+        for (int s = 0; s < kTeamStages; ++s) mbar_init(bars + 8u * s, 1u);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    const int R = p.batch.num_reqs;
+    const int32_t* unit_prefix = plan_array(p.scratch, 0, R);
+    const int32_t* item_prefix = plan_array(p.scratch, 1, R);
+    const int32_t* page_lo_a = plan_array(p.scratch, 2, R);
+    const int32_t* npages_a = plan_array(p.scratch, 3, R);
+    const int32_t* ngroups_a = plan_array(p.scratch, 4, R);
+    float* partials = reinterpret_cast<float*>(p.scratch + plan_bytes(R));
+
+    const int worker = blockIdx.x * kTeams + team;
+    const int per = hdr->units_per_warp;
+    const int total_units = hdr->total_units;
+    const long long u_ll = (long long)worker * per;
+    if (per <= 0 || u_ll >= total_units) return;   // whole team leaves together
+    int u = (int)u_ll;
+    const int u_end = min(u + per, total_units);
+
+    const int gid = lane >> 2, tig = lane & 3;
+    const int key_a = (gid & 3) + 8 * (gid >> 2);
+    const int kv0 = 2 * (tig & 1) + 8 * (tig >> 1);
+    const uint32_t lut_lane = lut_addr + 4u * lane;
+    const bool owner = t < NT;                   // runs the softmax of query tile t
+    uint32_t phase_bits = 0, pending = 0;
+    bool failed = false;
+
+    int r;
+    {
+        int lo = 0, hi = R;
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (unit_prefix[mid] <= u) lo = mid; else hi = mid;
+        }
+        r = lo;
+    }
+
+    while (u < u_end) {
+        while (unit_prefix[r + 1] <= u) ++r;
+        const int npages = npages_a[r];
+        const int ngroups = ngroups_a[r];
+        const int in_req = u - unit_prefix[r];
+        const int item = in_req / npages;
+        const int page_in_item = in_req - item * npages;
+        const int n_here = min(u_end - u, npages - page_in_item);
+        const int kv_head = item / ngroups;
+        const int group = item - kv_head * ngroups;
+        const int pg0 = page_lo_a[r] + page_in_item;
+        const int slot = worker + item_prefix[r] + item;
+        const ReqGeom g = load_req(p.batch, r);
+        const int rows_in_req = g.q_len * p.gqa;
+
+        // ---- limits: this lane's two rows of the tile it owns, and the group-wide safe range ----
+        int rmax[2] = {-1, -1}, rmin[2] = {0x7fffffff, 0x7fffffff};
+        int safe_hi = 0x7fffffff, safe_lo = 0;
+        for (int row = group * RG + lane; row < group * RG + RG; row += 32) {   // RG <= 32: one pass
+            const int q_off = row / p.gqa;
+            const bool ok = row < rows_in_req &&
+                            (p.batch.valid_token_mask == nullptr || p.batch.valid_token_mask[g.q_start + q_off] != 0);
+            if (ok) {
+                safe_hi = row_max_kv(p.batch, g, q_off);
+                safe_lo = row_min_kv(p.batch, g, q_off);
+            }
+        }
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) {
+            safe_hi = min(safe_hi, __shfl_xor_sync(0xffffffffu, safe_hi, d));
+            safe_lo = max(safe_lo, __shfl_xor_sync(0xffffffffu, safe_lo, d));
+        }
+        if (owner) {
+#pragma unroll
+            for (int x = 0; x < 2; ++x) {
+                const int row = group * RG + 8 * t + 2 * tig + x;
+                const int q_off = row / p.gqa;
+                const bool ok = row < rows_in_req &&
+                                (p.batch.valid_token_mask == nullptr || p.batch.valid_token_mask[g.q_start + q_off] != 0);
+                if (ok) { rmax[x] = row_max_kv(p.batch, g, q_off); rmin[x] = row_min_kv(p.batch, g, q_off); }
+            }
+        }
+
+        // ---- stage Q' (fp16 [RG][256], pre-scaled) in the idle ring; warp t rotates rows t, t+4, ...
+        __half* q_stage = reinterpret_cast<__half*>(ring_gen);
+        for (int row8 = t; row8 < RG; row8 += kTeamWarps) {
+            const int row = group * RG + row8;
+            const int q_off = row / p.gqa;
+            const int q_head = kv_head * p.gqa + (row - q_off * p.gqa);
+            const bool ok = row < rows_in_req &&
+                            (p.batch.valid_token_mask == nullptr || p.batch.valid_token_mask[g.q_start + q_off] != 0);
+            float tv[8];
+            if (ok) {
+                const size_t q_base = ((size_t)(g.q_start + q_off) * p.num_q_heads + q_head) * kHeadDim;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) tv[j] = apply_sign(load_act(p.q_in, q_base + lane + 32 * j, p.io_bf16), lane + 32 * j);
+                wht256_lanes(tv, lane);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) tv[j] = 0.0f;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) q_stage[row8 * kHeadDim + lane + 32 * j] = __float2half_rn(tv[j] * p.q_scale);
+        }
+        team_barrier(team);
+        // B fragments: k-step ks = 2 j + hk covers elements 4 hk .. 4 hk + 3 of virtual word
+        // vw_j = 2 cset + j + 4 tig of this warp's half.
+        uint32_t qb[4][NT][2];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const int vw = 2 * cset + j + 4 * tig;
+#pragma unroll
+            for (int hk = 0; hk < 2; ++hk) {
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+                    for (int x = 0; x < 2; ++x) {
+                        const int e = 4 * hk + 2 * x;
+                        const __half lo = q_stage[(8 * nt + gid) * kHeadDim + vword_col(half, vw, e)];
+                        const __half hi = q_stage[(8 * nt + gid) * kHeadDim + vword_col(half, vw, e + 1)];
+                        qb[2 * j + hk][nt][x] = (uint32_t)__half_as_ushort(lo) | ((uint32_t)__half_as_ushort(hi) << 16);
+                    }
+                }
+            }
+        }
+        team_barrier(team);   // everyone has its fragments before copies overwrite the staging area
+
+        float o[4][NT][4];
+#pragma unroll
+        for (int mt = 0; mt < 4; ++mt) {
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) { o[mt][nt][0] = o[mt][nt][1] = o[mt][nt][2] = o[mt][nt][3] = 0.0f; }
+        }
+        float m_run[2] = {-1e30f, -1e30f};
+        float l_run[2] = {0.0f, 0.0f};
+
+        const int32_t* blocks = p.batch.block_tables + (size_t)r * p.batch.max_blocks_per_req;
+        const uint8_t* k_head_base = (const uint8_t*)(uintptr_t)p.layout.k_base + (size_t)kv_head * p.layout.k_head_stride_bytes;
+        const uint8_t* v_head_base = (const uint8_t*)(uintptr_t)p.layout.v_base + (size_t)kv_head * p.layout.v_head_stride_bytes;
+        // page ids are only needed by the issuing warp (t == 0)
+        int32_t my_page = (t == 0 && lane < n_here) ? blocks[pg0 + lane] : 0;
+        int32_t next_page = (t == 0 && 32 + lane < n_here) ? blocks[pg0 + 32 + lane] : 0;
+
+        fence_proxy_async();
+        auto issue = [&](int idx) {
+            pending |= 1u << (idx % kTeamStages);
+            if (t == 0) {
+                const int32_t page = __shfl_sync(0xffffffffu, (idx & 32) ? next_page : my_page, idx & 31);
+                if (lane == 0) {
+                    const int s = idx % kTeamStages;
+                    const uint32_t bar = bars + 8u * s;
+                    const uint32_t dst = ring + (uint32_t)s * kStageStride;
+                    const uint8_t* ksrc = k_head_base + (size_t)page * p.layout.k_page_stride_bytes;
+                    const uint8_t* vsrc = v_head_base + (size_t)page * p.layout.v_page_stride_bytes;
+                    mbar_expect_tx(bar, 4 * kHalfBytes);
+                    bulk_g2s(dst, ksrc, kHalfBytes, bar);
+                    bulk_g2s(dst + kHalfStride, ksrc + kHalfBytes, kHalfBytes, bar);
+                    bulk_g2s(dst + kRunStride, vsrc, kHalfBytes, bar);
+                    bulk_g2s(dst + kRunStride + kHalfStride, vsrc + kHalfBytes, kHalfBytes, bar);
+                }
+            }
+        };
+#pragma unroll 1
+        for (int i = 0; i < kTeamStages - 1 && i < n_here; ++i) issue(i);
+
+#pragma unroll 1
+        for (int i = 0; i < n_here; ++i) {
+            if (t == 0 && (i & 31) == 0 && i > 0) {
+                const int base = i + 32;
+                const int32_t fresh = (base + lane < n_here) ? blocks[pg0 + base + lane] : 0;
+                if (i & 32) my_page = fresh; else next_page = fresh;
+            }
+            {
+                const int ahead = i + kTeamStages - 1;
+                if (ahead < n_here) issue(ahead);   // its stage was last read before barrier B of page i - 1
+            }
+            const int s = i % kTeamStages;
+            if (!failed && !mbar_wait(bars + 8u * s, (phase_bits >> s) & 1u)) {
+                failed = true;                      // results are void; keep meeting the team's barriers
+                if (lane == 0) atomicOr(&hdr->status, 1);
+            }
+            phase_bits ^= 1u << s;
+            pending &= ~(1u << s);
+
+            const uint32_t kst = ring + (uint32_t)s * kStageStride;
+            const uint32_t vst = kst + kRunStride;
+            const int kv_base = (pg0 + i) << 4;
+            const bool full = (kv_base >= safe_lo) && (kv_base + 15 <= safe_hi);
+#define W34_LUT(word, k) lds32(__byte_perm((word), lut_lane, 0x7604 + ((k) << 4)))
+
+            // ---- partial scores over this warp's 64 channels -------------------------------
+            float sa[NT][4];
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) { sa[nt][0] = sa[nt][1] = sa[nt][2] = sa[nt][3] = 0.0f; }
+            const uint32_t krow_a = kst + token_offset(key_a);
+            const uint32_t krow_b = krow_a + 4u * kTq4RowBytes;
+            const uint32_t sw_a = lds32(krow_a + (half ? 64u : 0u));   // word holding this half's scale
+            const uint32_t sw_b = lds32(krow_b + (half ? 64u : 0u));
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const uint32_t off = 4u * ((half ? 17u : 0u) + 2u * cset + j + 4u * tig);
+                uint32_t wa = lds32(krow_a + off);
+                uint32_t wb = lds32(krow_b + off);
+                if (j == 0 && t == 0 && tig == 0) {   // virtual word 0 of half 0: splice
+                    wa = (wa >> 16) | (lds32(krow_a + 64) << 16);
+                    wb = (wb >> 16) | (lds32(krow_b + 64) << 16);
+                }
+#pragma unroll
+                for (int hk = 0; hk < 2; ++hk) {
+                    const uint32_t a0 = W34_LUT(wa, 2 * hk);
+                    const uint32_t a1 = W34_LUT(wb, 2 * hk);
+                    const uint32_t a2 = W34_LUT(wa, 2 * hk + 1);
+                    const uint32_t a3 = W34_LUT(wb, 2 * hk + 1);
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) {
+                        mma16816(sa[nt], a0, a1, a2, a3, qb[2 * j + hk][nt][0], qb[2 * j + hk][nt][1]);
+                    }
+                }
+            }
+            {
+                const float dka = __half2float(__ushort_as_half((unsigned short)(half ? (sw_a >> 16) : (sw_a & 0xffffu))));
+                const float dkb = __half2float(__ushort_as_half((unsigned short)(half ? (sw_b >> 16) : (sw_b & 0xffffu))));
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    sts128f(sx + (uint32_t)((t * NT + nt) * 512 + lane * 16),
+                            make_float4(dka * sa[nt][0], dka * sa[nt][1], dkb * sa[nt][2], dkb * sa[nt][3]));
+                }
+            }
+
+            // ---- V look-ups do not depend on the softmax: do them before the team meets ------
+            uint32_t av[4][4];
+            {
+                const uint32_t vr = vst + token_offset(kv0);
+                const uint32_t vw = 4u * (uint32_t)(gid >> 1) + (uint32_t)(gid & 1) + 2u * cset;
+                const uint32_t off = 4u * ((half ? 17u : 0u) + vw);
+                uint32_t w[4];
+                w[0] = lds32(vr + off);
+                w[1] = lds32(vr + kTq4RowBytes + off);
+                w[2] = lds32(vr + 4u * kTq4RowBytes + off);
+                w[3] = lds32(vr + 5u * kTq4RowBytes + off);
+                if (t == 0 && gid == 0) {
+                    w[0] = (w[0] >> 16) | (lds32(vr + 64) << 16);
+                    w[1] = (w[1] >> 16) | (lds32(vr + kTq4RowBytes + 64) << 16);
+                    w[2] = (w[2] >> 16) | (lds32(vr + 4u * kTq4RowBytes + 64) << 16);
+                    w[3] = (w[3] >> 16) | (lds32(vr + 5u * kTq4RowBytes + 64) << 16);
+                }
+                const uint32_t lo_ab = (w[0] & 0x0f0f0f0fu) | ((w[1] << 4) & 0xf0f0f0f0u);
+                const uint32_t hi_ab = ((w[0] >> 4) & 0x0f0f0f0fu) | (w[1] & 0xf0f0f0f0u);
+                const uint32_t lo_cd = (w[2] & 0x0f0f0f0fu) | ((w[3] << 4) & 0xf0f0f0f0u);
+                const uint32_t hi_cd = ((w[2] >> 4) & 0x0f0f0f0fu) | (w[3] & 0xf0f0f0f0u);
+#pragma unroll
+                for (int mt = 0; mt < 4; ++mt) {
+                    av[mt][0] = W34_LUT(lo_ab, mt);
+                    av[mt][1] = W34_LUT(hi_ab, mt);
+                    av[mt][2] = W34_LUT(lo_cd, mt);
+                    av[mt][3] = W34_LUT(hi_cd, mt);
+                }
+            }
+#undef W34_LUT
+            team_barrier(team);   // A: all partial scores are in shared memory
+
+            // ---- the owner of query tile t sums the partials and runs the online softmax -------
+            if (owner) {
+                float sc[4];
+                {
+                    const float4 p0 = lds128f(sx + (uint32_t)((0 * NT + t) * 512 + lane * 16));
+                    const float4 p1 = lds128f(sx + (uint32_t)((1 * NT + t) * 512 + lane * 16));
+                    const float4 p2 = lds128f(sx + (uint32_t)((2 * NT + t) * 512 + lane * 16));
+                    const float4 p3 = lds128f(sx + (uint32_t)((3 * NT + t) * 512 + lane * 16));
+                    sc[0] = ((p0.x + p1.x) + p2.x) + p3.x;
+                    sc[1] = ((p0.y + p1.y) + p2.y) + p3.y;
+                    sc[2] = ((p0.z + p1.z) + p2.z) + p3.z;
+                    sc[3] = ((p0.w + p1.w) + p2.w) + p3.w;
+                }
+                const uint32_t vrow_a = vst + token_offset(key_a);
+                const uint32_t va0 = lds32(vrow_a), va16 = lds32(vrow_a + 64);
+                const uint32_t vb0 = lds32(vrow_a + 4u * kTq4RowBytes), vb16 = lds32(vrow_a + 4u * kTq4RowBytes + 64);
+                float dva0 = __half2float(__ushort_as_half((unsigned short)(va0 & 0xffffu)));
+                float dva1 = __half2float(__ushort_as_half((unsigned short)(va16 >> 16)));
+                float dvb0 = __half2float(__ushort_as_half((unsigned short)(vb0 & 0xffffu)));
+                float dvb1 = __half2float(__ushort_as_half((unsigned short)(vb16 >> 16)));
+                bool msk[4] = {false, false, false, false};
+                if (!full) {
+                    const int pos_a = kv_base + key_a, pos_b = pos_a + 4;
+                    msk[0] = !(pos_a >= rmin[0] && pos_a <= rmax[0]);
+                    msk[1] = !(pos_a >= rmin[1] && pos_a <= rmax[1]);
+                    msk[2] = !(pos_b >= rmin[0] && pos_b <= rmax[0]);
+                    msk[3] = !(pos_b >= rmin[1] && pos_b <= rmax[1]);
+#pragma unroll
+                    for (int x = 0; x < 4; ++x) if (msk[x]) sc[x] = -1e30f;
+                }
+                float mx0 = fmaxf(sc[0], sc[2]), mx1 = fmaxf(sc[1], sc[3]);
+#pragma unroll
+                for (int d = 4; d < 32; d <<= 1) {
+                    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, d));
+                    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, d));
+                }
+                const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
+                const float al0 = ex2(m_run[0] - mn0), al1 = ex2(m_run[1] - mn1);  // 1 when the max did not grow
+                l_run[0] *= al0;
+                l_run[1] *= al1;
+                m_run[0] = mn0;
+                m_run[1] = mn1;
+                float pr[4];
+                pr[0] = ex2(sc[0] - mn0);
+                pr[1] = ex2(sc[1] - mn1);
+                pr[2] = ex2(sc[2] - mn0);
+                pr[3] = ex2(sc[3] - mn1);
+                if (!full) {
+#pragma unroll
+                    for (int x = 0; x < 4; ++x) if (msk[x]) pr[x] = 0.0f;
+                    if (msk[0] && msk[1]) { dva0 = 0.0f; dva1 = 0.0f; }
+                    if (msk[2] && msk[3]) { dvb0 = 0.0f; dvb1 = 0.0f; }
+                }
+                l_run[0] += pr[0] + pr[2];
+                l_run[1] += pr[1] + pr[3];
+                const uint32_t pbase = px + (uint32_t)(t * 512 + lane * 4);
+                sts32(pbase + 0, movmatrix_trans(pack_half2(pr[0] * dva0, pr[1] * dva0)));
+                sts32(pbase + 128, movmatrix_trans(pack_half2(pr[2] * dvb0, pr[3] * dvb0)));
+                sts32(pbase + 256, movmatrix_trans(pack_half2(pr[0] * dva1, pr[1] * dva1)));
+                sts32(pbase + 384, movmatrix_trans(pack_half2(pr[2] * dvb1, pr[3] * dvb1)));
+                if (gid == 0) sts64f(ax + (uint32_t)((t * 4 + tig) * 8), make_float2(al0, al1));
+            }
+            team_barrier(team);   // B: P fragments and rescale factors are in shared memory
+
+            // ---- O^T += V^T P^T over this warp's 64 channels, all query tiles ----------------
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const float2 al = lds64f(ax + (uint32_t)((nt * 4 + tig) * 8));
+                const uint32_t pb0 = lds32(px + (uint32_t)(nt * 512 + half * 256 + lane * 4));
+                const uint32_t pb1 = lds32(px + (uint32_t)(nt * 512 + half * 256 + 128 + lane * 4));
+                if (__any_sync(0xffffffffu, al.x != 1.0f || al.y != 1.0f)) {
+#pragma unroll
+                    for (int mt = 0; mt < 4; ++mt) {
+                        o[mt][nt][0] *= al.x; o[mt][nt][1] *= al.y; o[mt][nt][2] *= al.x; o[mt][nt][3] *= al.y;
+                    }
+                }
+#pragma unroll
+                for (int mt = 0; mt < 4; ++mt) mma16816(o[mt][nt], av[mt][0], av[mt][1], av[mt][2], av[mt][3], pb0, pb1);
+            }
+        }
+
+        // ---- write the partial of this segment ------------------------------------------------
+        if (slot < p.max_slots) {
+            float* dst = partials + (size_t)slot * PARTIAL;
+            const int vw = 4 * (gid >> 1) + (gid & 1) + 2 * cset;
+#pragma unroll
+            for (int mt = 0; mt < 4; ++mt) {
+                const int ca = vword_col(half, vw, 2 * mt), cb = vword_col(half, vw, 2 * mt + 1);
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    const int r0 = 8 * nt + 2 * tig;
+                    dst[r0 * kHeadDim + ca] = o[mt][nt][0];
+                    dst[(r0 + 1) * kHeadDim + ca] = o[mt][nt][1];
+                    dst[r0 * kHeadDim + cb] = o[mt][nt][2];
+                    dst[(r0 + 1) * kHeadDim + cb] = o[mt][nt][3];
+                }
+            }
+            if (owner) {
+#pragma unroll
+                for (int d = 4; d < 32; d <<= 1) {
+                    l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], d);
+                    l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], d);
+                }
+                if (gid == 0) {
+                    const int r0 = 8 * t + 2 * tig;
+                    dst[RG * kHeadDim + r0] = m_run[0];
+                    dst[RG * kHeadDim + r0 + 1] = m_run[1];
+                    dst[RG * kHeadDim + RG + r0] = l_run[0];
+                    dst[RG * kHeadDim + RG + r0 + 1] = l_run[1];
+                }
+            }
+        }
+        team_barrier(team);   // the staging area is rewritten by the next segment
+        u += n_here;
+    }
+    if (failed) {
+        for (int s = 0; s < kTeamStages; ++s) {
+            if (pending & (1u << s)) (void)mbar_wait(bars + 8u * s, (phase_bits >> s) & 1u);
+        }
+    }
+}
+
 // Row triple written when the caller merges across page shards itself: 256 un-normalised
 // accumulator values in the rotated domain (in lookup-table units), then m (log2 units of the
 // pre-scaled scores) and l.
@@ -841,7 +1330,9 @@ __global__ void __launch_bounds__(128) tq4_attention_merge_kernel(const StreamPa
 
     const int kv_head = q_head / p.gqa;
     const int row_in_req = (tok - p.batch.query_start_loc[r]) * p.gqa + (q_head - kv_head * p.gqa);
-    const int group = row_in_req / kRowsPerGroup, row8 = row_in_req - group * kRowsPerGroup;
+    const int rpg = p.rows_per_group;
+    const int part_floats = rpg * kHeadDim + 2 * rpg;
+    const int group = row_in_req / rpg, row8 = row_in_req - group * rpg;
     const int item = kv_head * ngroups_a[r] + group;
     const int npages = npages_a[r];
     const int per = hdr->units_per_warp;
@@ -852,7 +1343,7 @@ __global__ void __launch_bounds__(128) tq4_attention_merge_kernel(const StreamPa
     if (npages > 0 && per > 0) {
         const int us = unit_prefix[r] + item * npages;
         const int w_first = us / per, w_last = (us + npages - 1) / per;
-        const float* base = partials + (size_t)(w_first + item_prefix[r] + item) * kPartialFloats;
+        const float* base = partials + (size_t)(w_first + item_prefix[r] + item) * part_floats;
         const int nparts = w_last - w_first + 1;
         // this warp's partials: wid, wid + 4, ...; lanes fetch up to 32 (m, l) pairs at once so
         // that the accumulation runs over independent loads
@@ -860,8 +1351,8 @@ __global__ void __launch_bounds__(128) tq4_attention_merge_kernel(const StreamPa
             const int mine = c0 + 4 * lane;
             float m_s = -1e30f, l_s = 0.0f;
             if (mine < nparts) {
-                const float* ps = base + (size_t)mine * kPartialFloats + kRowsPerGroup * kHeadDim;
-                l_s = ps[kRowsPerGroup + row8];
+                const float* ps = base + (size_t)mine * part_floats + rpg * kHeadDim;
+                l_s = ps[rpg + row8];
                 m_s = (l_s > 0.0f) ? ps[row8] : -1e30f;
             }
             float m_chunk = m_s;
@@ -882,7 +1373,7 @@ __global__ void __launch_bounds__(128) tq4_attention_merge_kernel(const StreamPa
 #pragma unroll 4
             for (int sidx = 0; sidx < n_here; ++sidx) {
                 const float wgt = __shfl_sync(0xffffffffu, w_s, sidx);
-                const float* pa = base + (size_t)(c0 + 4 * sidx) * kPartialFloats + row8 * kHeadDim;
+                const float* pa = base + (size_t)(c0 + 4 * sidx) * part_floats + row8 * kHeadDim;
 #pragma unroll
                 for (int j = 0; j < 8; ++j) acc[j] += pa[lane + 32 * j] * wgt;
             }
@@ -916,14 +1407,14 @@ __global__ void __launch_bounds__(128) tq4_attention_merge_kernel(const StreamPa
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] *= inv_l;
     wht256_lanes(acc, lane);
-    __half* out_row = p.attn_out + ((size_t)tok * p.num_q_heads + q_head) * kHeadDim;
+    const size_t out_base = ((size_t)tok * p.num_q_heads + q_head) * kHeadDim;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) out_row[lane + 32 * j] = __float2half_rn(apply_sign(acc[j], lane + 32 * j));
+    for (int j = 0; j < 8; ++j) store_act(p.attn_out, out_base + lane + 32 * j, apply_sign(acc[j], lane + 32 * j), p.io_bf16);
 }
 
 // Cross-shard merge: parts is [num_parts][rows][258]; one warp per row.
 __global__ void __launch_bounds__(128) tq4_attention_merge_shards_kernel(
-    const float* __restrict__ parts, int num_parts, long long rows, __half* __restrict__ attn_out) {
+    const float* __restrict__ parts, int num_parts, long long rows, void* __restrict__ attn_out, int io_bf16) {
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const long long row = (long long)blockIdx.x * 4 + wid;
     if (row >= rows) return;
@@ -948,9 +1439,8 @@ __global__ void __launch_bounds__(128) tq4_attention_merge_shards_kernel(
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] *= inv_l;
     wht256_lanes(acc, lane);
-    __half* out_row = attn_out + (size_t)row * kHeadDim;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) out_row[lane + 32 * j] = __float2half_rn(apply_sign(acc[j], lane + 32 * j));
+    for (int j = 0; j < 8; ++j) store_act(attn_out, (size_t)row * kHeadDim + lane + 32 * j, apply_sign(acc[j], lane + 32 * j), io_bf16);
 }
 
 // Copies the first `rows` token rows of every kv head of one page to another page of the same
@@ -1007,6 +1497,12 @@ static DeviceInfo* device_info(int* rc) {
         *rc = (int)cudaFuncSetAttribute(tq4_attention_stream_kernel<kStages>,
                                         cudaFuncAttributeMaxDynamicSharedMemorySize, optin);
         if (*rc != 0) return nullptr;
+        *rc = (int)cudaFuncSetAttribute(tq4_attention_team_kernel<2>,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, optin);
+        if (*rc != 0) return nullptr;
+        *rc = (int)cudaFuncSetAttribute(tq4_attention_team_kernel<3>,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, optin);
+        if (*rc != 0) return nullptr;
         d->smem_optin = optin;
         d->sm_count = sms;
         d->configured = true;
@@ -1031,17 +1527,38 @@ static bool stream_layout_ok(const warp34_kv_layer_layout* l) {
            l->v_head_stride_bytes >= (uint64_t)kTq4PageHeadBytes;
 }
 
-static long long items_bound(const warp34_kv_layer_layout* l, const warp34_attention_batch* b, int hq) {
+static long long items_bound(const warp34_kv_layer_layout* l, const warp34_attention_batch* b, int hq,
+                             int rows_per_group = kRowsPerGroup) {
     const long long gqa = hq / l->local_kv_heads;
     const long long rows = (long long)b->total_tokens * gqa;
-    return (long long)l->local_kv_heads * ((rows + kRowsPerGroup - 1) / kRowsPerGroup + b->num_reqs);
+    return (long long)l->local_kv_heads * ((rows + rows_per_group - 1) / rows_per_group + b->num_reqs);
+}
+
+// Query rows that share one KV pass: 8 with one warp per work item (decode), 16 or 24 with
+// four-warp teams (several draft tokens per request, or prefill chunks).
+static int pick_row_tiles(const warp34_attention_batch* b, int gqa) {
+    const long long rows = (long long)(b->max_q_len > 0 ? b->max_q_len : 1) * gqa;
+    if (rows <= 8) return 1;
+    return rows <= 16 ? 2 : 3;
 }
 
 }  // namespace w34
 
+namespace w34 {
+static int launch_scalar(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
+                         const warp34_attention_batch* batch, const void* q_in, void* attn_out,
+                         int num_q_heads, int io_bf16);
+}
+
 extern "C" int warp34_paged_attention_scalar_f16(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
                                                  const warp34_attention_batch* batch, const void* q_in,
                                                  void* attn_out, int num_q_heads) {
+    return w34::launch_scalar(ex, layout, batch, q_in, attn_out, num_q_heads, 0);
+}
+
+static int w34::launch_scalar(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
+                              const warp34_attention_batch* batch, const void* q_in, void* attn_out,
+                              int num_q_heads, int io_bf16) {
     if (ex == nullptr || layout == nullptr || batch == nullptr || q_in == nullptr || attn_out == nullptr) {
         return (int)cudaErrorInvalidValue;
     }
@@ -1051,7 +1568,7 @@ extern "C" int warp34_paged_attention_scalar_f16(const warp34_exec* ex, const wa
     const long long rows = (long long)batch->total_tokens * num_q_heads;
     const unsigned blocks = (unsigned)((rows + 3) / 4);
     w34::tq4_attention_scalar_kernel<<<blocks, 128, 0, (cudaStream_t)ex->stream>>>(
-        *layout, *batch, static_cast<const __half*>(q_in), static_cast<__half*>(attn_out), num_q_heads);
+        *layout, *batch, q_in, attn_out, num_q_heads, io_bf16);
     return (int)cudaGetLastError();
 }
 
@@ -1061,8 +1578,11 @@ extern "C" size_t warp34_paged_attention_scratch_bytes(const warp34_kv_layer_lay
     int rc = 0;
     w34::DeviceInfo* d = w34::device_info(&rc);
     const int sms = d ? d->sm_count : 148;
-    const long long slots = (long long)sms * w34::kWarpsPerCta + w34::items_bound(layout, batch, num_q_heads);
-    return w34::plan_bytes(batch->num_reqs) + (size_t)slots * w34::kPartialFloats * sizeof(float);
+    const int nt = w34::pick_row_tiles(batch, num_q_heads / layout->local_kv_heads);
+    const int rpg = 8 * nt;
+    const long long slots = (long long)sms * (nt == 1 ? w34::kWarpsPerCta : w34::kTeams) +
+                            w34::items_bound(layout, batch, num_q_heads, rpg);
+    return w34::plan_bytes(batch->num_reqs) + (size_t)slots * (size_t)(rpg * w34::kHeadDim + 2 * rpg) * sizeof(float);
 }
 
 namespace w34 {
@@ -1071,7 +1591,7 @@ namespace w34 {
 // merge and write per-row (acc, m, l) instead of attn_out (streaming path only).
 static int launch_attention(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
                             const warp34_attention_batch* batch, const void* q_in, void* attn_out,
-                            float* triple_out, int num_q_heads) {
+                            float* triple_out, int num_q_heads, int io_bf16 = 0) {
     if (ex == nullptr || layout == nullptr || batch == nullptr || q_in == nullptr ||
         (attn_out == nullptr && triple_out == nullptr)) {
         return (int)cudaErrorInvalidValue;
@@ -1085,11 +1605,16 @@ static int launch_attention(const warp34_exec* ex, const warp34_kv_layer_layout*
     if (dev == nullptr) return rc;
 
     // Streaming path: canonical layout, scratch that holds the plan plus at least one partial
-    // per item and per worker warp, unit count within int32.
-    const long long items = items_bound(layout, batch, num_q_heads);
+    // per item and per worker, unit count within int32.  Workers are warps (8 query rows per
+    // item) or four-warp teams (16 / 24 rows per item).
+    const int gqa = num_q_heads / layout->local_kv_heads;
+    const int nt = pick_row_tiles(batch, gqa);
+    const int rpg = 8 * nt;
+    const int workers_per_cta = (nt == 1) ? kWarpsPerCta : kTeams;
+    const long long items = items_bound(layout, batch, num_q_heads, rpg);
     const long long units_bound = items * (long long)(batch->max_blocks_per_req > 0 ? batch->max_blocks_per_req : 1);
     const size_t plan = plan_bytes(batch->num_reqs);
-    const size_t slot_bytes = (size_t)kPartialFloats * sizeof(float);
+    const size_t slot_bytes = (size_t)(rpg * kHeadDim + 2 * rpg) * sizeof(float);
     bool stream = (ex->flags & WARP34_B200_EXEC_FLAG_PRECISE_ATTENTION) == 0 &&
                   stream_layout_ok(layout) && ex->scratch_ptr != 0 && (ex->scratch_ptr & 15u) == 0u &&
                   units_bound < 0x7fffffffll && batch->max_blocks_per_req > 0;
@@ -1097,36 +1622,44 @@ static int launch_attention(const warp34_exec* ex, const warp34_kv_layer_layout*
     if (stream) {
         const size_t avail = ex->scratch_size > plan ? ex->scratch_size - plan : 0;
         const long long slots_avail = (long long)(avail / slot_bytes);
-        long long warps = slots_avail - items;
-        if (warps < kWarpsPerCta) {
+        long long workers = slots_avail - items;
+        if (workers < workers_per_cta) {
             stream = false;
         } else {
-            const long long max_ctas = warps / kWarpsPerCta;
+            const long long max_ctas = workers / workers_per_cta;
             if (max_ctas < grid) grid = (int)max_ctas;
         }
     }
     if (!stream) {
         if (triple_out != nullptr) return (int)cudaErrorNotSupported;
-        return warp34_paged_attention_scalar_f16(ex, layout, batch, q_in, attn_out, num_q_heads);
+        return launch_scalar(ex, layout, batch, q_in, attn_out, num_q_heads, io_bf16);
     }
 
     StreamParams p;
     p.layout = *layout;
     p.batch = *batch;
-    p.q_in = static_cast<const __half*>(q_in);
-    p.attn_out = static_cast<__half*>(attn_out);
+    p.q_in = q_in;
+    p.attn_out = attn_out;
+    p.io_bf16 = io_bf16;
     p.triple_out = triple_out;
     p.scratch = reinterpret_cast<uint8_t*>((uintptr_t)ex->scratch_ptr);
     p.num_q_heads = num_q_heads;
-    p.gqa = num_q_heads / layout->local_kv_heads;
-    p.num_warps = grid * kWarpsPerCta;
+    p.gqa = gqa;
+    p.num_warps = grid * workers_per_cta;
     p.max_slots = (int)(p.num_warps + items);
+    p.rows_per_group = rpg;
     p.q_scale = batch->sm_scale * 1.4426950408889634f / kLutScale;
     cudaStream_t st = (cudaStream_t)ex->stream;
     const size_t smem = (size_t)dev->smem_optin;
     p.smem_bytes = (uint32_t)smem;
     tq4_attention_plan_kernel<<<1, 32, 0, st>>>(p);
-    tq4_attention_stream_kernel<kStages><<<grid, kWarpsPerCta * 32, smem, st>>>(p);
+    if (nt == 1) {
+        tq4_attention_stream_kernel<kStages><<<grid, kWarpsPerCta * 32, smem, st>>>(p);
+    } else if (nt == 2) {
+        tq4_attention_team_kernel<2><<<grid, kTeams * kTeamWarps * 32, smem, st>>>(p);
+    } else {
+        tq4_attention_team_kernel<3><<<grid, kTeams * kTeamWarps * 32, smem, st>>>(p);
+    }
     const long long rows = (long long)batch->total_tokens * num_q_heads;
     if (triple_out != nullptr) {
         tq4_attention_merge_kernel<true><<<(unsigned)rows, 128, 0, st>>>(p);
@@ -1191,9 +1724,12 @@ extern "C" int warp34_paged_attention_f16_static_scratch(uintptr_t stream, const
     if (num_q_heads % layout->local_kv_heads != 0 || batch->num_reqs <= 0) return (int)cudaErrorInvalidValue;
     // Smallest workspace the streaming path accepts: the plan plus one partial per work item
     // and per warp of a single CTA.
+    const int nt = w34::pick_row_tiles(batch, num_q_heads / layout->local_kv_heads);
+    const int rpg = 8 * nt;
     const size_t needed = w34::plan_bytes(batch->num_reqs) +
-                          (size_t)(w34::items_bound(layout, batch, num_q_heads) + w34::kWarpsPerCta) *
-                              w34::kPartialFloats * sizeof(float);
+                          (size_t)(w34::items_bound(layout, batch, num_q_heads, rpg) +
+                                   (nt == 1 ? w34::kWarpsPerCta : w34::kTeams)) *
+                              (size_t)(rpg * w34::kHeadDim + 2 * rpg) * sizeof(float);
     if (scratch_needed != nullptr) *scratch_needed = needed;
     if (needed > kStaticScratchBytes) return (int)cudaErrorInvalidValue;  // batch too large for the built-in workspace
     warp34_exec ex;
@@ -1203,6 +1739,13 @@ extern "C" int warp34_paged_attention_f16_static_scratch(uintptr_t stream, const
     const int rc = w34::static_scratch_address(&ex.scratch_ptr);
     if (rc != 0) return rc;
     return w34::launch_attention(&ex, layout, batch, q_in, attn_out, nullptr, num_q_heads);
+}
+
+extern "C" int warp34_tq4_paged_attention_bf16(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
+                                               const warp34_attention_batch* batch, const void* q_in,
+                                               void* attn_out, int num_q_heads) {
+    if (attn_out == nullptr) return (int)cudaErrorInvalidValue;
+    return w34::launch_attention(ex, layout, batch, q_in, attn_out, nullptr, num_q_heads, 1);
 }
 
 extern "C" int warp34_paged_attention_partial_f16(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
@@ -1219,7 +1762,7 @@ extern "C" int warp34_paged_attention_merge_shards_f16(const warp34_exec* ex, co
     }
     if (num_rows == 0) return 0;
     w34::tq4_attention_merge_shards_kernel<<<(unsigned)((num_rows + 3) / 4), 128, 0, (cudaStream_t)ex->stream>>>(
-        triples, num_shards, (long long)num_rows, static_cast<__half*>(attn_out));
+        triples, num_shards, (long long)num_rows, attn_out, 0);
     return (int)cudaGetLastError();
 }
 

@@ -66,6 +66,10 @@ _KERNEL_SIGS = {
                                               C.c_void_p, C.c_void_p, C.c_int]),
     "warp34_paged_attention_scalar_f16": (C.c_int, [_P(Exec), _P(KvLayerLayout), _P(AttentionBatch),
                                                      C.c_void_p, C.c_void_p, C.c_int]),
+    "warp34_tq4_kv_cache_write_strided_bf16": (C.c_int, [_P(Exec), _P(KvLayerLayout), _P(AttentionBatch),
+                                                          C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
+    "warp34_tq4_paged_attention_bf16": (C.c_int, [_P(Exec), _P(KvLayerLayout), _P(AttentionBatch),
+                                                   C.c_void_p, C.c_void_p, C.c_int]),
     "warp34_paged_attention_partial_f16": (C.c_int, [_P(Exec), _P(KvLayerLayout), _P(AttentionBatch),
                                                       C.c_void_p, C.c_void_p, C.c_int]),
     "warp34_paged_attention_merge_shards_f16": (C.c_int, [_P(Exec), C.c_void_p, C.c_int, C.c_int64, C.c_void_p]),
