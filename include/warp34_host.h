@@ -141,6 +141,49 @@ const int32_t* w34_seq_pages(const w34_seq* seq);
 /* Tests only: replace the block table without touching reference counts. */
 int32_t w34_seq_set_pages_unchecked(w34_seq* seq, const int32_t* pages, int32_t n, int32_t protected_pages);
 
+/* ---- page-aligned radix prefix cache: MambaRadixCache, KV half (radix.rs:383-692, :950-980) -- */
+typedef struct w34_radix w34_radix;
+
+typedef struct {
+    int32_t nodes;            /* live nodes, root excluded */
+    int32_t cached_pages;     /* pages the tree holds a reference on */
+    int32_t protected_pages;  /* of those, on locked paths */
+    int32_t evictable_pages;
+} w34_radix_stats;
+
+w34_radix* w34_radix_create(w34_page_pool* pool);
+/* Releases the tree's page references. */
+void w34_radix_destroy(w34_radix* radix);
+
+/* Longest cached prefix of `tokens`, in whole pages (match_prefix, radix.rs:383-490).  Writes
+ * the matched page ids, the matched token count (a multiple of the block size) and the deepest
+ * matched node (0 = root = no match); refreshes recency along the path.  A node that matches
+ * only partly is split at the page boundary.  Returns the number of pages or a negative error. */
+int32_t w34_radix_match_prefix(w34_radix* radix, const int32_t* tokens, int32_t num_tokens,
+                               int32_t* out_pages, int32_t page_capacity, int32_t* matched_tokens,
+                               int32_t* last_node);
+
+/* inc_lock_ref / dec_lock_ref (radix.rs:494-550): pin / unpin the path from `node` to the
+ * root against eviction.  Unbalanced unlocks return W34_ERR_PROTECTED and change nothing. */
+int32_t w34_radix_lock(w34_radix* radix, int32_t node);
+int32_t w34_radix_unlock(w34_radix* radix, int32_t node);
+
+/* insert (radix.rs:552-692): caches a page-aligned token sequence with its pages.  The tree
+ * takes one pool reference on every page it newly stores.  Returns the number of leading
+ * tokens that were already cached (the caller may free its duplicate pages for that prefix);
+ * `last_node` receives the node that now ends the sequence. */
+int32_t w34_radix_insert(w34_radix* radix, const int32_t* tokens, int32_t num_tokens,
+                         const int32_t* pages, int32_t num_pages, int32_t* last_node);
+
+/* evict_full_pages (radix.rs:950-980): drops least-recently-used unlocked leaves until at least
+ * num_pages pages were released (or nothing evictable is left); their ids are written to
+ * `freed` and their references returned to the pool.  Returns the count. */
+int32_t w34_radix_evict(w34_radix* radix, int32_t num_pages, int32_t* freed, int32_t capacity);
+
+void w34_radix_get_stats(const w34_radix* radix, w34_radix_stats* out);
+/* 0 when the structural invariants hold (sanity_check, radix.rs:983-1041). */
+int32_t w34_radix_sanity_check(const w34_radix* radix);
+
 /* ---- step metadata (model/graph_io.rs:368-420, :505-576; execution.rs:386, :618) ----------- */
 /*
  * Packs the device-side arrays of one attention step for `num_seqs` sequences, sequence i

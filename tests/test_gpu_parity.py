@@ -460,3 +460,58 @@ def test_bf16_activations_match_the_fp16_entry_points(env):
     assert lib.warp34_tq4_kv_cache_write_strided_bf16(C.byref(env["ex"].ex), C.byref(wl.layer.layout), C.byref(b.desc),
                                                       big.data_ptr(), big.data_ptr(), hkv * 256, hkv * 256) == 0
     torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("hq", [16, 24])
+@pytest.mark.parametrize("q_len,ctx_before", [(64, 0), (65, 19), (137, 128), (256, 200)])
+def test_chunked_prefill_matches_cpu_oracle(env, hq, q_len, ctx_before):
+    """Prefill chunks through the 64-row kernel, on the shapes the reference uses to compare its
+    16- / 64- / 128-row kernels (crates/warp34-host/src/cuda/tests.rs:111-576): a chunk of q_len
+    tokens after ctx_before cached tokens, causal inside the chunk."""
+    kv, synth = env["kv"], env["synth"]
+    hkv = 4
+    total = ctx_before + q_len
+    wl = synth.PagedWorkload([0], [total], hkv, seed=200 + q_len)
+    k, v = synth.make_kv(total, hkv, 200 + q_len)
+    kv.kv_cache_write(env["ex"], wl.layer, wl.step(), k.cuda(), v.cuda())
+    wl.seqs[0].commit(ctx_before)
+    b = wl.step(q_lens=[q_len])
+    q = synth.make_q(q_len, hq, 200 + q_len)
+    out = torch.full((q_len, hq, 256), 5.0, dtype=torch.float16, device="cuda")
+    kv.paged_attention(env["ex"], wl.layer, b, q.cuda(), out, hq)
+    torch.cuda.synchronize()
+    want = _oracle_attention(wl, b, q, hq)
+    vs = channel_scale(v.numpy(), [(0, total)], [q_len], hq, hkv)
+    ok, msg = tensor_core_parity(out.float().cpu().numpy(), want, vs)
+    assert ok, msg
+
+
+def test_mixed_prefill_and_decode_batch_with_masks(env):
+    """Three requests in one call (a prefill chunk, a decode token, a second chunk with a sliding
+    window), one masked token and sentinels in the output (cuda/tests.rs:538-572)."""
+    kv, synth = env["kv"], env["synth"]
+    hq, hkv = 16, 4
+    ctx_before, q_lens = [40, 300, 7], [50, 1, 90]
+    totals = [c + q for c, q in zip(ctx_before, q_lens)]
+    wl = synth.PagedWorkload([0] * 3, totals, hkv, seed=300)
+    k, v = synth.make_kv(sum(totals), hkv, 300)
+    kv.kv_cache_write(env["ex"], wl.layer, wl.step(), k.cuda(), v.cuda())
+    for s, c in zip(wl.seqs, ctx_before):
+        s.commit(c)
+    q = synth.make_q(sum(q_lens), hq, 300)
+    starts = np.concatenate([[0], np.cumsum(totals)])
+    vs = channel_scale(v.numpy(), [(int(starts[i]), int(starts[i + 1])) for i in range(3)], q_lens, hq, hkv)
+    sentinel = np.uint16(0x5500)
+    for window in (0, 33):
+        vtm = np.ones(sum(q_lens), np.uint8)
+        vtm[60] = 0
+        b = wl.step(q_lens=q_lens, sliding_window=window, valid_token_mask=vtm)
+        out = torch.from_numpy(np.full((sum(q_lens), hq, 256), sentinel, np.uint16).view(np.float16)).cuda()
+        kv.paged_attention(env["ex"], wl.layer, b, q.cuda(), out, hq)
+        torch.cuda.synchronize()
+        bits = out.cpu().numpy().view(np.uint16)
+        assert (bits[60] == sentinel).all()
+        live = np.array([i for i in range(sum(q_lens)) if i != 60])
+        want = _oracle_attention(wl, b, q, hq)
+        ok, msg = tensor_core_parity(f16(bits[live]), want[live], vs[live])
+        assert ok, (window, msg)

@@ -23,7 +23,7 @@ CUDA_UNITS = [
     ("tq4_attention.cu", []),
     ("abi_misc.cu", []),
 ]
-HOST_UNITS = ["page_pool.cpp"]
+HOST_UNITS = ["page_pool.cpp", "prefix_cache.cpp"]
 
 
 def _stale(target, sources):

@@ -827,16 +827,17 @@ __global__ void __launch_bounds__(W34_WARPS * 32, 1) tq4_attention_stream_kernel
 // over the KV pages.  A team is four warps; warp t owns a quarter of the 256 channels (half
 // t >> 1 of the row, every other pair of 8-channel words), for the score product and for the
 // output alike, so every code is looked up once per page however many query rows read it and
-// each looked-up fragment feeds NT MMAs.  Per page the team meets twice: after the partial
-// scores (summed through shared memory; the warp that owns an 8-row tile then runs its online
-// softmax) and after the softmax (P fragments and rescale factors go back through shared
-// memory).  Three teams per CTA, one CTA per SM, each team with its own ring of stages.
+// each looked-up fragment feeds NT MMAs.  The team meets once per page, after the partial
+// scores: they are summed through shared memory by the warp that owns an 8-row tile, which
+// runs its online softmax and publishes P fragments and rescale factors (double-buffered);
+// the output product of a page runs after the next meeting, so one page's softmax overlaps the
+// next page's score product.  Three teams per CTA, one CTA per SM, each team with its own ring.
 // ---------------------------------------------------------------------------------------
 #ifndef W34_TEAMS
 #define W34_TEAMS 3
 #endif
 #ifndef W34_TEAM_STAGES
-#define W34_TEAM_STAGES 10
+#define W34_TEAM_STAGES 8
 #endif
 constexpr int kTeams = W34_TEAMS;
 constexpr int kTeamWarps = 4;
@@ -898,9 +899,10 @@ __global__ void __launch_bounds__(kTeams * kTeamWarps * 32, 1) tq4_attention_tea
         if (tm == team) ring = r_;
     }
     for (int tm = 0; tm < kTeams; ++tm) {
-        const uint32_t s_ = carve.take(kTeamWarps * NT * 512, 16);   // partial scores [warp][tile][lane] float4
-        const uint32_t p_ = carve.take(NT * 2 * 2 * 128, 16);         // P fragments [tile][half][reg][lane]
-        const uint32_t a_ = carve.take(NT * 4 * 8, 8);                // rescale factors [tile][tig] float2
+        // all three are double-buffered by page parity
+        const uint32_t s_ = carve.take(2 * kTeamWarps * NT * 512, 16);   // partial scores [buf][warp][tile][lane] float4
+        const uint32_t p_ = carve.take(2 * NT * 2 * 2 * 128, 16);         // P fragments [buf][tile][half][reg][lane]
+        const uint32_t a_ = carve.take(2 * NT * 4 * 8, 8);                // rescale factors [buf][tile][tig] float2
         const uint32_t b_ = carve.take(kTeamStages * 8, 8);
         if (tm == team) { sx = s_; px = p_; ax = a_; bars = b_; }
     }
@@ -941,7 +943,10 @@ __global__ void __launch_bounds__(kTeams * kTeamWarps * 32, 1) tq4_attention_tea
     const int key_a = (gid & 3) + 8 * (gid >> 2);
     const int kv0 = 2 * (tig & 1) + 8 * (tig >> 1);
     const uint32_t lut_lane = lut_addr + 4u * lane;
-    const bool owner = t < NT;                   // runs the softmax of query tile t
+    // Softmax owners are rotated from team to team so that the schedulers, which each host one
+    // warp of every team, share the softmax work evenly.
+    const int tile = (t + 4 - (team & 3)) & 3;   // query tile this warp owns, if < NT
+    const bool owner = tile < NT;
     uint32_t phase_bits = 0, pending = 0;
     bool failed = false;
 
@@ -990,7 +995,7 @@ __global__ void __launch_bounds__(kTeams * kTeamWarps * 32, 1) tq4_attention_tea
         if (owner) {
 #pragma unroll
             for (int x = 0; x < 2; ++x) {
-                const int row = group * RG + 8 * t + 2 * tig + x;
+                const int row = group * RG + 8 * tile + 2 * tig + x;
                 const int q_off = row / p.gqa;
                 const bool ok = row < rows_in_req &&
                                 (p.batch.valid_token_mask == nullptr || p.batch.valid_token_mask[g.q_start + q_off] != 0);
@@ -1077,21 +1082,37 @@ __global__ void __launch_bounds__(kTeams * kTeamWarps * 32, 1) tq4_attention_tea
                 }
             }
         };
+        // The page ids of units [32 c, 32 c + 32) alternate between my_page (c even) and next_page
+        // (c odd); a window is replaced once every unit in it has been issued.
 #pragma unroll 1
-        for (int i = 0; i < kTeamStages - 1 && i < n_here; ++i) issue(i);
+        for (int i = 0; i < kTeamStages && i < n_here; ++i) issue(i);
+
+        // One meeting per page.  Iteration i: partial scores of page i -> meet -> (output product
+        // of page i - 1, whose P fragments the owners published before arriving) -> owners'
+        // softmax of page i -> V look-ups of page i.  The softmax of one page thus overlaps the
+        // score product of the next in the other warps.
+        uint32_t av[4][4];
+        auto pv_product = [&](int buf) {
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const float2 al = lds64f(ax + (uint32_t)(buf * (NT * 32) + (nt * 4 + tig) * 8));
+                const uint32_t pb0 = lds32(px + (uint32_t)(buf * (NT * 512) + nt * 512 + half * 256 + lane * 4));
+                const uint32_t pb1 = lds32(px + (uint32_t)(buf * (NT * 512) + nt * 512 + half * 256 + 128 + lane * 4));
+                if (__any_sync(0xffffffffu, al.x != 1.0f || al.y != 1.0f)) {
+#pragma unroll
+                    for (int mt = 0; mt < 4; ++mt) {
+                        o[mt][nt][0] *= al.x; o[mt][nt][1] *= al.y; o[mt][nt][2] *= al.x; o[mt][nt][3] *= al.y;
+                    }
+                }
+#pragma unroll
+                for (int mt = 0; mt < 4; ++mt) mma16816(o[mt][nt], av[mt][0], av[mt][1], av[mt][2], av[mt][3], pb0, pb1);
+            }
+        };
 
 #pragma unroll 1
         for (int i = 0; i < n_here; ++i) {
-            if (t == 0 && (i & 31) == 0 && i > 0) {
-                const int base = i + 32;
-                const int32_t fresh = (base + lane < n_here) ? blocks[pg0 + base + lane] : 0;
-                if (i & 32) my_page = fresh; else next_page = fresh;
-            }
-            {
-                const int ahead = i + kTeamStages - 1;
-                if (ahead < n_here) issue(ahead);   // its stage was last read before barrier B of page i - 1
-            }
             const int s = i % kTeamStages;
+            const int buf = i & 1;
             if (!failed && !mbar_wait(bars + 8u * s, (phase_bits >> s) & 1u)) {
                 failed = true;                      // results are void; keep meeting the team's barriers
                 if (lane == 0) atomicOr(&hdr->status, 1);
@@ -1106,84 +1127,68 @@ __global__ void __launch_bounds__(kTeams * kTeamWarps * 32, 1) tq4_attention_tea
 #define W34_LUT(word, k) lds32(__byte_perm((word), lut_lane, 0x7604 + ((k) << 4)))
 
             // ---- partial scores over this warp's 64 channels -------------------------------
-            float sa[NT][4];
+            {
+                float sa[NT][4];
 #pragma unroll
-            for (int nt = 0; nt < NT; ++nt) { sa[nt][0] = sa[nt][1] = sa[nt][2] = sa[nt][3] = 0.0f; }
-            const uint32_t krow_a = kst + token_offset(key_a);
-            const uint32_t krow_b = krow_a + 4u * kTq4RowBytes;
-            const uint32_t sw_a = lds32(krow_a + (half ? 64u : 0u));   // word holding this half's scale
-            const uint32_t sw_b = lds32(krow_b + (half ? 64u : 0u));
+                for (int nt = 0; nt < NT; ++nt) { sa[nt][0] = sa[nt][1] = sa[nt][2] = sa[nt][3] = 0.0f; }
+                const uint32_t krow_a = kst + token_offset(key_a);
+                const uint32_t krow_b = krow_a + 4u * kTq4RowBytes;
+                const uint32_t sw_a = lds32(krow_a + (half ? 64u : 0u));   // word holding this half's scale
+                const uint32_t sw_b = lds32(krow_b + (half ? 64u : 0u));
 #pragma unroll
-            for (int j = 0; j < 2; ++j) {
-                const uint32_t off = 4u * ((half ? 17u : 0u) + 2u * cset + j + 4u * tig);
-                uint32_t wa = lds32(krow_a + off);
-                uint32_t wb = lds32(krow_b + off);
-                if (j == 0 && t == 0 && tig == 0) {   // virtual word 0 of half 0: splice
-                    wa = (wa >> 16) | (lds32(krow_a + 64) << 16);
-                    wb = (wb >> 16) | (lds32(krow_b + 64) << 16);
-                }
+                for (int j = 0; j < 2; ++j) {
+                    const uint32_t off = 4u * ((half ? 17u : 0u) + 2u * cset + j + 4u * tig);
+                    uint32_t wa = lds32(krow_a + off);
+                    uint32_t wb = lds32(krow_b + off);
+                    if (j == 0 && t == 0 && tig == 0) {   // virtual word 0 of half 0: splice
+                        wa = (wa >> 16) | (lds32(krow_a + 64) << 16);
+                        wb = (wb >> 16) | (lds32(krow_b + 64) << 16);
+                    }
 #pragma unroll
-                for (int hk = 0; hk < 2; ++hk) {
-                    const uint32_t a0 = W34_LUT(wa, 2 * hk);
-                    const uint32_t a1 = W34_LUT(wb, 2 * hk);
-                    const uint32_t a2 = W34_LUT(wa, 2 * hk + 1);
-                    const uint32_t a3 = W34_LUT(wb, 2 * hk + 1);
+                    for (int hk = 0; hk < 2; ++hk) {
+                        const uint32_t a0 = W34_LUT(wa, 2 * hk);
+                        const uint32_t a1 = W34_LUT(wb, 2 * hk);
+                        const uint32_t a2 = W34_LUT(wa, 2 * hk + 1);
+                        const uint32_t a3 = W34_LUT(wb, 2 * hk + 1);
 #pragma unroll
-                    for (int nt = 0; nt < NT; ++nt) {
-                        mma16816(sa[nt], a0, a1, a2, a3, qb[2 * j + hk][nt][0], qb[2 * j + hk][nt][1]);
+                        for (int nt = 0; nt < NT; ++nt) {
+                            mma16816(sa[nt], a0, a1, a2, a3, qb[2 * j + hk][nt][0], qb[2 * j + hk][nt][1]);
+                        }
                     }
                 }
-            }
-            {
                 const float dka = __half2float(__ushort_as_half((unsigned short)(half ? (sw_a >> 16) : (sw_a & 0xffffu))));
                 const float dkb = __half2float(__ushort_as_half((unsigned short)(half ? (sw_b >> 16) : (sw_b & 0xffffu))));
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) {
-                    sts128f(sx + (uint32_t)((t * NT + nt) * 512 + lane * 16),
+                    sts128f(sx + (uint32_t)(buf * (kTeamWarps * NT * 512) + (t * NT + nt) * 512 + lane * 16),
                             make_float4(dka * sa[nt][0], dka * sa[nt][1], dkb * sa[nt][2], dkb * sa[nt][3]));
                 }
             }
+            team_barrier(team);   // scores of page i are in shared memory; so is everything of page i - 1
 
-            // ---- V look-ups do not depend on the softmax: do them before the team meets ------
-            uint32_t av[4][4];
-            {
-                const uint32_t vr = vst + token_offset(kv0);
-                const uint32_t vw = 4u * (uint32_t)(gid >> 1) + (uint32_t)(gid & 1) + 2u * cset;
-                const uint32_t off = 4u * ((half ? 17u : 0u) + vw);
-                uint32_t w[4];
-                w[0] = lds32(vr + off);
-                w[1] = lds32(vr + kTq4RowBytes + off);
-                w[2] = lds32(vr + 4u * kTq4RowBytes + off);
-                w[3] = lds32(vr + 5u * kTq4RowBytes + off);
-                if (t == 0 && gid == 0) {
-                    w[0] = (w[0] >> 16) | (lds32(vr + 64) << 16);
-                    w[1] = (w[1] >> 16) | (lds32(vr + kTq4RowBytes + 64) << 16);
-                    w[2] = (w[2] >> 16) | (lds32(vr + 4u * kTq4RowBytes + 64) << 16);
-                    w[3] = (w[3] >> 16) | (lds32(vr + 5u * kTq4RowBytes + 64) << 16);
+            // page i - 1 is finished by every warp once it has passed this point's output product,
+            // which the NEXT meeting certifies: refill the stage of page i - 1 now that all warps
+            // have passed the meeting of page i (they read stage i - 1 before arriving).
+            if (i >= 1 && i - 1 + kTeamStages < n_here) {
+                if (t == 0 && ((i - 1 + kTeamStages) & 31) == 0) {
+                    // entering a new id window: the window being replaced was fully issued long ago
+                    const int base = i - 1 + kTeamStages + 32;
+                    const int32_t fresh = (base + lane < n_here) ? blocks[pg0 + base + lane] : 0;
+                    if ((i - 1 + kTeamStages) & 32) my_page = fresh; else next_page = fresh;
                 }
-                const uint32_t lo_ab = (w[0] & 0x0f0f0f0fu) | ((w[1] << 4) & 0xf0f0f0f0u);
-                const uint32_t hi_ab = ((w[0] >> 4) & 0x0f0f0f0fu) | (w[1] & 0xf0f0f0f0u);
-                const uint32_t lo_cd = (w[2] & 0x0f0f0f0fu) | ((w[3] << 4) & 0xf0f0f0f0u);
-                const uint32_t hi_cd = ((w[2] >> 4) & 0x0f0f0f0fu) | (w[3] & 0xf0f0f0f0u);
-#pragma unroll
-                for (int mt = 0; mt < 4; ++mt) {
-                    av[mt][0] = W34_LUT(lo_ab, mt);
-                    av[mt][1] = W34_LUT(hi_ab, mt);
-                    av[mt][2] = W34_LUT(lo_cd, mt);
-                    av[mt][3] = W34_LUT(hi_cd, mt);
-                }
+                issue(i - 1 + kTeamStages);
             }
-#undef W34_LUT
-            team_barrier(team);   // A: all partial scores are in shared memory
+            if (i >= 1) pv_product(buf ^ 1);
 
             // ---- the owner of query tile t sums the partials and runs the online softmax -------
             if (owner) {
                 float sc[4];
                 {
-                    const float4 p0 = lds128f(sx + (uint32_t)((0 * NT + t) * 512 + lane * 16));
-                    const float4 p1 = lds128f(sx + (uint32_t)((1 * NT + t) * 512 + lane * 16));
-                    const float4 p2 = lds128f(sx + (uint32_t)((2 * NT + t) * 512 + lane * 16));
-                    const float4 p3 = lds128f(sx + (uint32_t)((3 * NT + t) * 512 + lane * 16));
+                    const uint32_t sb = sx + (uint32_t)(buf * (kTeamWarps * NT * 512) + tile * 512 + lane * 16);
+                    const float4 p0 = lds128f(sb + 0 * NT * 512);
+                    const float4 p1 = lds128f(sb + 1 * NT * 512);
+                    const float4 p2 = lds128f(sb + 2 * NT * 512);
+                    const float4 p3 = lds128f(sb + 3 * NT * 512);
                     sc[0] = ((p0.x + p1.x) + p2.x) + p3.x;
                     sc[1] = ((p0.y + p1.y) + p2.y) + p3.y;
                     sc[2] = ((p0.z + p1.z) + p2.z) + p3.z;
@@ -1231,31 +1236,46 @@ __global__ void __launch_bounds__(kTeams * kTeamWarps * 32, 1) tq4_attention_tea
                 }
                 l_run[0] += pr[0] + pr[2];
                 l_run[1] += pr[1] + pr[3];
-                const uint32_t pbase = px + (uint32_t)(t * 512 + lane * 4);
+                const uint32_t pbase = px + (uint32_t)(buf * (NT * 512) + tile * 512 + lane * 4);
                 sts32(pbase + 0, movmatrix_trans(pack_half2(pr[0] * dva0, pr[1] * dva0)));
                 sts32(pbase + 128, movmatrix_trans(pack_half2(pr[2] * dvb0, pr[3] * dvb0)));
                 sts32(pbase + 256, movmatrix_trans(pack_half2(pr[0] * dva1, pr[1] * dva1)));
                 sts32(pbase + 384, movmatrix_trans(pack_half2(pr[2] * dvb1, pr[3] * dvb1)));
-                if (gid == 0) sts64f(ax + (uint32_t)((t * 4 + tig) * 8), make_float2(al0, al1));
+                if (gid == 0) sts64f(ax + (uint32_t)(buf * (NT * 32) + (tile * 4 + tig) * 8), make_float2(al0, al1));
             }
-            team_barrier(team);   // B: P fragments and rescale factors are in shared memory
 
-            // ---- O^T += V^T P^T over this warp's 64 channels, all query tiles ----------------
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-                const float2 al = lds64f(ax + (uint32_t)((nt * 4 + tig) * 8));
-                const uint32_t pb0 = lds32(px + (uint32_t)(nt * 512 + half * 256 + lane * 4));
-                const uint32_t pb1 = lds32(px + (uint32_t)(nt * 512 + half * 256 + 128 + lane * 4));
-                if (__any_sync(0xffffffffu, al.x != 1.0f || al.y != 1.0f)) {
-#pragma unroll
-                    for (int mt = 0; mt < 4; ++mt) {
-                        o[mt][nt][0] *= al.x; o[mt][nt][1] *= al.y; o[mt][nt][2] *= al.x; o[mt][nt][3] *= al.y;
-                    }
+            // ---- V look-ups of page i (its product runs after the next meeting) ----------------
+            {
+                const uint32_t vr = vst + token_offset(kv0);
+                const uint32_t vw = 4u * (uint32_t)(gid >> 1) + (uint32_t)(gid & 1) + 2u * cset;
+                const uint32_t off = 4u * ((half ? 17u : 0u) + vw);
+                uint32_t w[4];
+                w[0] = lds32(vr + off);
+                w[1] = lds32(vr + kTq4RowBytes + off);
+                w[2] = lds32(vr + 4u * kTq4RowBytes + off);
+                w[3] = lds32(vr + 5u * kTq4RowBytes + off);
+                if (t == 0 && gid == 0) {
+                    w[0] = (w[0] >> 16) | (lds32(vr + 64) << 16);
+                    w[1] = (w[1] >> 16) | (lds32(vr + kTq4RowBytes + 64) << 16);
+                    w[2] = (w[2] >> 16) | (lds32(vr + 4u * kTq4RowBytes + 64) << 16);
+                    w[3] = (w[3] >> 16) | (lds32(vr + 5u * kTq4RowBytes + 64) << 16);
                 }
+                const uint32_t lo_ab = (w[0] & 0x0f0f0f0fu) | ((w[1] << 4) & 0xf0f0f0f0u);
+                const uint32_t hi_ab = ((w[0] >> 4) & 0x0f0f0f0fu) | (w[1] & 0xf0f0f0f0u);
+                const uint32_t lo_cd = (w[2] & 0x0f0f0f0fu) | ((w[3] << 4) & 0xf0f0f0f0u);
+                const uint32_t hi_cd = ((w[2] >> 4) & 0x0f0f0f0fu) | (w[3] & 0xf0f0f0f0u);
 #pragma unroll
-                for (int mt = 0; mt < 4; ++mt) mma16816(o[mt][nt], av[mt][0], av[mt][1], av[mt][2], av[mt][3], pb0, pb1);
+                for (int mt = 0; mt < 4; ++mt) {
+                    av[mt][0] = W34_LUT(lo_ab, mt);
+                    av[mt][1] = W34_LUT(hi_ab, mt);
+                    av[mt][2] = W34_LUT(lo_cd, mt);
+                    av[mt][3] = W34_LUT(hi_cd, mt);
+                }
             }
+#undef W34_LUT
         }
+        team_barrier(team);   // the owners' last softmax is published
+        if (n_here > 0) pv_product((n_here - 1) & 1);
 
         // ---- write the partial of this segment ------------------------------------------------
         if (slot < p.max_slots) {
@@ -1280,7 +1300,7 @@ __global__ void __launch_bounds__(kTeams * kTeamWarps * 32, 1) tq4_attention_tea
                     l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], d);
                 }
                 if (gid == 0) {
-                    const int r0 = 8 * t + 2 * tig;
+                    const int r0 = 8 * tile + 2 * tig;
                     dst[RG * kHeadDim + r0] = m_run[0];
                     dst[RG * kHeadDim + r0 + 1] = m_run[1];
                     dst[RG * kHeadDim + RG + r0] = l_run[0];
@@ -1294,6 +1314,395 @@ __global__ void __launch_bounds__(kTeams * kTeamWarps * 32, 1) tq4_attention_tea
     if (failed) {
         for (int s = 0; s < kTeamStages; ++s) {
             if (pending & (1u << s)) (void)mbar_wait(bars + 8u * s, (phase_bits >> s) & 1u);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Chunked-prefill kernel: 64 query rows (64 / G tokens x G heads of one kv head) per CTA, four
+// warps of 16 rows.  Replaces paged_attention_prefill_mma_f16_kernel<64>
+// (op_paged_attn.cu:594-1128).  Per page the CTA dequantises K and V once into fp16 tiles in
+// shared memory (natural rotated-column order, unscaled centroids) while the previous page's
+// tiles feed the MMAs: S = Q' K^T with ldmatrix B fragments and one accumulator per 128-half
+// (scores = d0 S0 + d1 S1), online softmax in registers, O += (P d_v) V with ldmatrix.trans.
+// The 4-bit look-ups are paid once per 64 rows.  No scratch, no split: a CTA walks all pages
+// its rows can see; causal / window masks are applied per row on the pages that need them.
+// (A tcgen05 version with TMEM accumulators is the intended successor of this kernel.)
+// ---------------------------------------------------------------------------------------
+constexpr int kPfRows = 64;
+constexpr int kPfWarps = 4;
+constexpr int kPfStages = 3;                 // raw pages in flight
+constexpr int kTileStride = 264;             // halves per dequantised row: 528 B, conflict-free ldmatrix
+constexpr int kTileBytes = 16 * kTileStride * 2;
+constexpr int kPfLutBytes = 256 * 32 * 4;    // 128-byte entry stride (PRMT + LEA addressing)
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
+struct PrefillParams {
+    warp34_kv_layer_layout layout;
+    warp34_attention_batch batch;
+    const void* q_in;
+    void* attn_out;
+    int io_bf16;
+    int num_q_heads;
+    int gqa;
+    int tok_per_tile;      // 64 / gqa
+    float q_scale;         // sm_scale * log2(e) / kLutScale
+    int32_t* status;       // may be null
+};
+
+__global__ void __launch_bounds__(kPfWarps * 32, 2) tq4_attention_prefill_kernel(const PrefillParams p) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    // [lut 32 KB][K tile x2][V tile x2][raw ring][scales 2 x 64 floats][mbarriers]
+    const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    const int gid = lane >> 2, tig = lane & 3;
+    const uint32_t lut = smem_u32(smem);
+    const uint32_t ktile = lut + kPfLutBytes;
+    const uint32_t vtile = ktile + 2 * kTileBytes;
+    const uint32_t raw = vtile + 2 * kTileBytes;
+    const uint32_t scl = raw + kPfStages * kStageStride;     // [buf][K0 K1 V0 V1][16 keys] floats
+    const uint32_t bars = scl + 2 * 64 * 4;
+    float* scl_gen = reinterpret_cast<float*>(smem + (scl - lut));
+
+    for (int i = tid; i < 256 * 32; i += blockDim.x) {
+        const int byte = i >> 5, ln = i & 31;
+        sts32(lut + (uint32_t)(byte * 128 + ln * 4),
+              pack_half2(kLutScale * tq4_centroid(byte & 15), kLutScale * tq4_centroid(byte >> 4)));
+    }
+    if (tid == 0) {
+        for (int s = 0; s < kPfStages; ++s) mbar_init(bars + 8u * s, 1u);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    // ---- which (request, token tile) is this CTA? ---------------------------------------------
+    const int tpt = p.tok_per_tile;
+    const int kv_head = blockIdx.y;
+    int req = -1, tile_in_req = 0;
+    {
+        int t = blockIdx.x;
+        for (int r = 0; r < p.batch.num_reqs; ++r) {
+            const int ql = p.batch.query_start_loc[r + 1] - p.batch.query_start_loc[r];
+            const int nt = (ql + tpt - 1) / tpt;
+            if (t < nt) { req = r; tile_in_req = t; break; }
+            t -= nt;
+        }
+    }
+    if (req < 0) return;
+    const ReqGeom g = load_req(p.batch, req);
+    if (!g.valid) return;
+    const int tok0 = tile_in_req * tpt;                         // first query token of the tile (in request)
+    const int ntok = min(tpt, g.q_len - tok0);
+    const int rows_used = ntok * p.gqa;
+
+    // this lane's two rows: 16 wid + gid and + 8
+    int rmax[2], rmin[2];
+    bool rvalid[2];
+#pragma unroll
+    for (int x = 0; x < 2; ++x) {
+        const int row = 16 * wid + gid + 8 * x;
+        const int q_off = tok0 + row / p.gqa;
+        rvalid[x] = row < rows_used &&
+                    (p.batch.valid_token_mask == nullptr || p.batch.valid_token_mask[g.q_start + q_off] != 0);
+        rmax[x] = rvalid[x] ? row_max_kv(p.batch, g, q_off) : -1;
+        rmin[x] = rvalid[x] ? row_min_kv(p.batch, g, q_off) : 0x7fffffff;
+    }
+    // page range of the whole tile, and the range of keys every valid row sees
+    __shared__ int s_lo[kPfWarps], s_hi[kPfWarps], s_slo[kPfWarps], s_shi[kPfWarps];
+    {
+        int lo = min(rmin[0], rmin[1]), hi = max(rmax[0], rmax[1]);
+        int slo = max(rvalid[0] ? rmin[0] : 0, rvalid[1] ? rmin[1] : 0);
+        int shi = min(rvalid[0] ? rmax[0] : 0x7fffffff, rvalid[1] ? rmax[1] : 0x7fffffff);
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) {
+            lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, d));
+            hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, d));
+            slo = max(slo, __shfl_xor_sync(0xffffffffu, slo, d));
+            shi = min(shi, __shfl_xor_sync(0xffffffffu, shi, d));
+        }
+        if (lane == 0) { s_lo[wid] = lo; s_hi[wid] = hi; s_slo[wid] = slo; s_shi[wid] = shi; }
+    }
+    __syncthreads();
+    int kv_lo = 0x7fffffff, kv_hi = -1, safe_lo = 0, safe_hi = 0x7fffffff;
+#pragma unroll
+    for (int w = 0; w < kPfWarps; ++w) {
+        kv_lo = min(kv_lo, s_lo[w]); kv_hi = max(kv_hi, s_hi[w]);
+        safe_lo = max(safe_lo, s_slo[w]); safe_hi = min(safe_hi, s_shi[w]);
+    }
+    const int pg_lo = (kv_hi >= kv_lo) ? (kv_lo >> 4) : 0;
+    const int npages = (kv_hi >= kv_lo) ? ((kv_hi >> 4) - pg_lo + 1) : 0;
+
+    // ---- Q' rows of this warp -> A fragments (natural rotated-column order) -----------------------
+    // staging through this warp's slice of the K tiles (idle before the first page)
+    uint32_t qa[16][4];
+    {
+        __half* stage = reinterpret_cast<__half*>(smem + (ktile - lut)) + wid * 16 * kTileStride;  // [16][264]
+        for (int rr = 0; rr < 16; ++rr) {
+            const int row = 16 * wid + rr;
+            const int q_off = tok0 + row / p.gqa;
+            const int q_head = kv_head * p.gqa + row % p.gqa;
+            const bool ok = row < rows_used &&
+                            (p.batch.valid_token_mask == nullptr || p.batch.valid_token_mask[g.q_start + q_off] != 0);
+            float tv[8];
+            if (ok) {
+                const size_t q_base = ((size_t)(g.q_start + q_off) * p.num_q_heads + q_head) * kHeadDim;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) tv[j] = apply_sign(load_act(p.q_in, q_base + lane + 32 * j, p.io_bf16), lane + 32 * j);
+                wht256_lanes(tv, lane);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) tv[j] = 0.0f;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) stage[rr * kTileStride + lane + 32 * j] = __float2half_rn(tv[j] * p.q_scale);
+        }
+        __syncwarp();
+        const uint32_t* st32 = reinterpret_cast<const uint32_t*>(stage);
+#pragma unroll
+        for (int ks = 0; ks < 16; ++ks) {
+            qa[ks][0] = st32[(gid * kTileStride + 16 * ks + 2 * tig) >> 1];
+            qa[ks][1] = st32[((gid + 8) * kTileStride + 16 * ks + 2 * tig) >> 1];
+            qa[ks][2] = st32[(gid * kTileStride + 16 * ks + 8 + 2 * tig) >> 1];
+            qa[ks][3] = st32[((gid + 8) * kTileStride + 16 * ks + 8 + 2 * tig) >> 1];
+        }
+    }
+    __syncthreads();   // staging area becomes the K tile buffers
+
+    float o[32][4];
+#pragma unroll
+    for (int n = 0; n < 32; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f; }
+    float m_run[2] = {-1e30f, -1e30f}, l_run[2] = {0.0f, 0.0f};
+
+    const int32_t* blocks = p.batch.block_tables + (size_t)req * p.batch.max_blocks_per_req;
+    const uint8_t* k_head_base = (const uint8_t*)(uintptr_t)p.layout.k_base + (size_t)kv_head * p.layout.k_head_stride_bytes;
+    const uint8_t* v_head_base = (const uint8_t*)(uintptr_t)p.layout.v_base + (size_t)kv_head * p.layout.v_head_stride_bytes;
+    uint32_t phase_bits = 0;
+    bool failed = false;
+
+    auto issue = [&](int idx) {   // thread 0 only
+        const int s = idx % kPfStages;
+        const int32_t page = blocks[pg_lo + idx];
+        const uint32_t bar = bars + 8u * s;
+        const uint32_t dst = raw + (uint32_t)s * kStageStride;
+        const uint8_t* ksrc = k_head_base + (size_t)page * p.layout.k_page_stride_bytes;
+        const uint8_t* vsrc = v_head_base + (size_t)page * p.layout.v_page_stride_bytes;
+        mbar_expect_tx(bar, 4 * kHalfBytes);
+        bulk_g2s(dst, ksrc, kHalfBytes, bar);
+        bulk_g2s(dst + kHalfStride, ksrc + kHalfBytes, kHalfBytes, bar);
+        bulk_g2s(dst + kRunStride, vsrc, kHalfBytes, bar);
+        bulk_g2s(dst + kRunStride + kHalfStride, vsrc + kHalfBytes, kHalfBytes, bar);
+    };
+    // Dequantises raw page `idx` into tile buffer idx & 1: thread -> (token row, 32-column chunk).
+    auto dequant = [&](int idx) {
+        const int s = idx % kPfStages;
+        if (!failed && !mbar_wait(bars + 8u * s, (phase_bits >> s) & 1u)) {
+            failed = true;
+            if (p.status != nullptr && lane == 0) atomicOr(p.status, 1);
+        }
+        phase_bits ^= 1u << s;
+        const int buf = idx & 1;
+        const int r = tid >> 3, c = tid & 7;            // token row, chunk of 32 rotated columns
+        const int half = c >> 2;
+#pragma unroll
+        for (int kvsel = 0; kvsel < 2; ++kvsel) {
+            const uint32_t rowp = raw + (uint32_t)s * kStageStride + (kvsel ? kRunStride : 0) + token_offset(r);
+            uint32_t w[4];
+            if (half == 0) {   // codes of half 0 start at byte 2: read 5 words and shift by 16 bits
+                const uint32_t b = rowp + 16u * (c & 3);
+                uint32_t x[5];
+#pragma unroll
+                for (int j = 0; j < 5; ++j) x[j] = lds32(b + 4u * j);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) w[j] = __funnelshift_r(x[j], x[j + 1], 16);
+            } else {
+                const uint32_t b = rowp + 68u + 16u * (c & 3);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) w[j] = lds32(b + 4u * j);
+            }
+            const uint32_t dst = (kvsel ? vtile : ktile) + (uint32_t)buf * kTileBytes +
+                                 (uint32_t)(r * kTileStride + 32 * c) * 2u;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                uint32_t h[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) h[k] = lds32(lut + 4u * lane + (__byte_perm(w[j], 0, 0x4440 + k) << 7));
+                sts128(dst + 16u * j, h[0], h[1], h[2], h[3]);
+            }
+            if ((c & 3) == 0) {   // one thread per (row, half) publishes the scale
+                const uint32_t sw = lds32(rowp + (half ? 64u : 0u));
+                const float d = __half2float(__ushort_as_half((unsigned short)(half ? (sw >> 16) : (sw & 0xffffu))));
+                scl_gen[buf * 64 + (kvsel * 2 + half) * 16 + r] = d;
+            }
+        }
+    };
+
+    if (tid == 0) {
+        for (int i = 0; i < kPfStages && i < npages; ++i) issue(i);
+    }
+    if (npages > 0) dequant(0);
+    __syncthreads();
+
+#pragma unroll 1
+    for (int i = 0; i < npages; ++i) {
+        const int buf = i & 1;
+        // raw stage of page i is free (dequantised before the last barrier): refill it
+        if (tid == 0 && i + kPfStages < npages) issue(i + kPfStages);
+        if (i + 1 < npages) dequant(i + 1);   // overlaps the MMAs below
+
+        const int kv_base = (pg_lo + i) << 4;
+        const bool full = (kv_base >= safe_lo) && (kv_base + 15 <= safe_hi);
+        const uint32_t kt = ktile + (uint32_t)buf * kTileBytes, vt = vtile + (uint32_t)buf * kTileBytes;
+        const float* sc_ = scl_gen + buf * 64;
+
+        // ---- S = Q' K^T: [16 rows x 16 keys], per 128-half ------------------------------------
+        float sacc[2][2][4];   // [half][key n-tile][c]
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+#pragma unroll
+            for (int n = 0; n < 2; ++n) { sacc[h][n][0] = sacc[h][n][1] = sacc[h][n][2] = sacc[h][n][3] = 0.0f; }
+        }
+        // ldmatrix.x4: matrices (keys 0-7, cols k0..+7), (keys 0-7, cols k0+8..), (keys 8-15, k0..), (keys 8-15, k0+8..)
+        const uint32_t kaddr = kt + (uint32_t)(((lane & 7) + 8 * (lane >> 4)) * kTileStride + 8 * ((lane >> 3) & 1)) * 2u;
+#pragma unroll
+        for (int ks = 0; ks < 16; ++ks) {
+            uint32_t b[4];
+            ldmatrix_x4(b, kaddr + 32u * ks);
+            mma16816(sacc[ks >> 3][0], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b[0], b[1]);
+            mma16816(sacc[ks >> 3][1], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b[2], b[3]);
+        }
+        // this lane's keys: n-tile n -> keys 8 n + 2 tig, + 1
+        float sc[2][4];
+        float dv0[2][2], dv1[2][2];
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int key = 8 * n + 2 * tig + e;
+                const float dk0 = sc_[0 * 16 + key], dk1 = sc_[1 * 16 + key];
+                dv0[n][e] = sc_[2 * 16 + key];
+                dv1[n][e] = sc_[3 * 16 + key];
+                sc[n][e] = dk0 * sacc[0][n][e] + dk1 * sacc[1][n][e];               // row gid
+                sc[n][2 + e] = dk0 * sacc[0][n][2 + e] + dk1 * sacc[1][n][2 + e];   // row gid + 8
+            }
+        }
+        bool msk[2][4];
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) msk[n][e] = false;
+        }
+        if (!full) {
+#pragma unroll
+            for (int n = 0; n < 2; ++n) {
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int pos = kv_base + 8 * n + 2 * tig + e;
+                    msk[n][e] = !(pos >= rmin[0] && pos <= rmax[0]);
+                    msk[n][2 + e] = !(pos >= rmin[1] && pos <= rmax[1]);
+                    if (msk[n][e]) sc[n][e] = -1e30f;
+                    if (msk[n][2 + e]) sc[n][2 + e] = -1e30f;
+                    // a key beyond the sequence may hold never-written bytes: keep its V scale finite
+                    if (pos > kv_hi || pos < kv_lo) { dv0[n][e] = 0.0f; dv1[n][e] = 0.0f; }
+                }
+            }
+        }
+        // ---- online softmax: rows gid (x = 0) and gid + 8 (x = 1), 4 lanes share a row -----------
+        float mx[2];
+        mx[0] = fmaxf(fmaxf(sc[0][0], sc[0][1]), fmaxf(sc[1][0], sc[1][1]));
+        mx[1] = fmaxf(fmaxf(sc[0][2], sc[0][3]), fmaxf(sc[1][2], sc[1][3]));
+#pragma unroll
+        for (int d = 1; d < 4; d <<= 1) {
+            mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xffffffffu, mx[0], d));
+            mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xffffffffu, mx[1], d));
+        }
+        const float mn0 = fmaxf(m_run[0], mx[0]), mn1 = fmaxf(m_run[1], mx[1]);
+        if (__any_sync(0xffffffffu, mn0 > m_run[0] || mn1 > m_run[1])) {
+            const float al0 = ex2(m_run[0] - mn0), al1 = ex2(m_run[1] - mn1);
+            l_run[0] *= al0; l_run[1] *= al1;
+#pragma unroll
+            for (int n = 0; n < 32; ++n) { o[n][0] *= al0; o[n][1] *= al0; o[n][2] *= al1; o[n][3] *= al1; }
+            m_run[0] = mn0; m_run[1] = mn1;
+        }
+        float pr[2][4];
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+            pr[n][0] = msk[n][0] ? 0.0f : ex2(sc[n][0] - mn0);
+            pr[n][1] = msk[n][1] ? 0.0f : ex2(sc[n][1] - mn0);
+            pr[n][2] = msk[n][2] ? 0.0f : ex2(sc[n][2] - mn1);
+            pr[n][3] = msk[n][3] ? 0.0f : ex2(sc[n][3] - mn1);
+            l_run[0] += pr[n][0] + pr[n][1];
+            l_run[1] += pr[n][2] + pr[n][3];
+        }
+        // P d_v as A fragments (k = 16 keys of the page), one set per 128-half of V
+        uint32_t pa0[4], pa1[4];
+        pa0[0] = pack_half2(pr[0][0] * dv0[0][0], pr[0][1] * dv0[0][1]);
+        pa0[1] = pack_half2(pr[0][2] * dv0[0][0], pr[0][3] * dv0[0][1]);
+        pa0[2] = pack_half2(pr[1][0] * dv0[1][0], pr[1][1] * dv0[1][1]);
+        pa0[3] = pack_half2(pr[1][2] * dv0[1][0], pr[1][3] * dv0[1][1]);
+        pa1[0] = pack_half2(pr[0][0] * dv1[0][0], pr[0][1] * dv1[0][1]);
+        pa1[1] = pack_half2(pr[0][2] * dv1[0][0], pr[0][3] * dv1[0][1]);
+        pa1[2] = pack_half2(pr[1][0] * dv1[1][0], pr[1][1] * dv1[1][1]);
+        pa1[3] = pack_half2(pr[1][2] * dv1[1][0], pr[1][3] * dv1[1][1]);
+        // ---- O += P V: ldmatrix.trans gives (keys 0-7 | 8-15) x (cols n0..+7 | n0+8..+15) -----------
+        const uint32_t vaddr = vt + (uint32_t)(((lane & 7) + 8 * ((lane >> 3) & 1)) * kTileStride + 8 * (lane >> 4)) * 2u;
+#pragma unroll
+        for (int np = 0; np < 16; ++np) {
+            uint32_t b[4];
+            ldmatrix_x4_trans(b, vaddr + 32u * np);
+            if (np < 8) {
+                mma16816(o[2 * np], pa0[0], pa0[1], pa0[2], pa0[3], b[0], b[1]);
+                mma16816(o[2 * np + 1], pa0[0], pa0[1], pa0[2], pa0[3], b[2], b[3]);
+            } else {
+                mma16816(o[2 * np], pa1[0], pa1[1], pa1[2], pa1[3], b[0], b[1]);
+                mma16816(o[2 * np + 1], pa1[0], pa1[1], pa1[2], pa1[3], b[2], b[3]);
+            }
+        }
+        __syncthreads();   // tiles of page i + 1 are complete; tiles of page i may be overwritten
+    }
+
+    // ---- epilogue: normalise, inverse rotation, store -------------------------------------------------
+#pragma unroll
+    for (int d = 1; d < 4; d <<= 1) {
+        l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], d);
+        l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], d);
+    }
+    const float inv0 = (l_run[0] > 0.0f) ? (1.0f / (l_run[0] * kLutScale)) : 0.0f;
+    const float inv1 = (l_run[1] > 0.0f) ? (1.0f / (l_run[1] * kLutScale)) : 0.0f;
+    // each warp stages 8 rows at a time in its 8 KB slice of the (now idle) tile buffers
+    float* ostage = reinterpret_cast<float*>(smem + (ktile - lut)) + wid * 8 * kHeadDim;
+#pragma unroll
+    for (int x = 0; x < 2; ++x) {
+        __syncwarp();
+#pragma unroll
+        for (int n = 0; n < 32; ++n) {
+            ostage[gid * kHeadDim + 8 * n + 2 * tig] = o[n][2 * x] * (x ? inv1 : inv0);
+            ostage[gid * kHeadDim + 8 * n + 2 * tig + 1] = o[n][2 * x + 1] * (x ? inv1 : inv0);
+        }
+        __syncwarp();
+        for (int rr = 0; rr < 8; ++rr) {
+            const int row = 16 * wid + rr + 8 * x;
+            const int q_off = tok0 + row / p.gqa;
+            const int q_head = kv_head * p.gqa + row % p.gqa;
+            const bool ok = row < rows_used &&
+                            (p.batch.valid_token_mask == nullptr || p.batch.valid_token_mask[g.q_start + q_off] != 0);
+            if (!ok) continue;
+            float tv[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) tv[j] = ostage[rr * kHeadDim + lane + 32 * j];
+            wht256_lanes(tv, lane);
+            const size_t out_base = ((size_t)(g.q_start + q_off) * p.num_q_heads + q_head) * kHeadDim;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) store_act(p.attn_out, out_base + lane + 32 * j, apply_sign(tv[j], lane + 32 * j), p.io_bf16);
         }
     }
 }
@@ -1473,6 +1882,10 @@ static size_t stream_smem_min_bytes() {
     return kLutBytes + (size_t)kWarpsPerCta * kStages * (kStageStride + 8);
 }
 
+static size_t prefill_smem_bytes() {
+    return (size_t)kPfLutBytes + 4 * (size_t)kTileBytes + (size_t)kPfStages * kStageStride + 2 * 64 * 4 + kPfStages * 8 + 64;
+}
+
 struct DeviceInfo {
     int sm_count;
     int smem_optin;
@@ -1502,6 +1915,9 @@ static DeviceInfo* device_info(int* rc) {
         if (*rc != 0) return nullptr;
         *rc = (int)cudaFuncSetAttribute(tq4_attention_team_kernel<3>,
                                         cudaFuncAttributeMaxDynamicSharedMemorySize, optin);
+        if (*rc != 0) return nullptr;
+        *rc = (int)cudaFuncSetAttribute(tq4_attention_prefill_kernel,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)prefill_smem_bytes());
         if (*rc != 0) return nullptr;
         d->smem_optin = optin;
         d->sm_count = sms;
@@ -1604,10 +2020,33 @@ static int launch_attention(const warp34_exec* ex, const warp34_kv_layer_layout*
     DeviceInfo* dev = device_info(&rc);
     if (dev == nullptr) return rc;
 
+    const int gqa = num_q_heads / layout->local_kv_heads;
+    // Prefill chunks (more query rows per request and kv head than one team item holds): 64-row
+    // CTAs, no scratch.  Not for the partial-output mode, which is a decode-time feature.
+    if (triple_out == nullptr && (ex->flags & WARP34_B200_EXEC_FLAG_PRECISE_ATTENTION) == 0 &&
+        stream_layout_ok(layout) && batch->max_blocks_per_req > 0 && gqa <= kPfRows &&
+        (long long)batch->max_q_len * gqa > 24) {
+        PrefillParams pp;
+        pp.layout = *layout;
+        pp.batch = *batch;
+        pp.q_in = q_in;
+        pp.attn_out = attn_out;
+        pp.io_bf16 = io_bf16;
+        pp.num_q_heads = num_q_heads;
+        pp.gqa = gqa;
+        pp.tok_per_tile = kPfRows / gqa;
+        pp.q_scale = batch->sm_scale * 1.4426950408889634f / kLutScale;
+        pp.status = nullptr;
+        const long long tiles = (long long)batch->total_tokens / pp.tok_per_tile + batch->num_reqs;
+        if (tiles > 0x7fffffffll || layout->local_kv_heads > 65535) return (int)cudaErrorInvalidValue;
+        const dim3 grid((unsigned)tiles, (unsigned)layout->local_kv_heads);
+        tq4_attention_prefill_kernel<<<grid, kPfWarps * 32, prefill_smem_bytes(), (cudaStream_t)ex->stream>>>(pp);
+        return (int)cudaGetLastError();
+    }
+
     // Streaming path: canonical layout, scratch that holds the plan plus at least one partial
     // per item and per worker, unit count within int32.  Workers are warps (8 query rows per
     // item) or four-warp teams (16 / 24 rows per item).
-    const int gqa = num_q_heads / layout->local_kv_heads;
     const int nt = pick_row_tiles(batch, gqa);
     const int rpg = 8 * nt;
     const int workers_per_cta = (nt == 1) ? kWarpsPerCta : kTeams;

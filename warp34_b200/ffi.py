@@ -50,6 +50,11 @@ class AttentionBatch(C.Structure):
                 ("sliding_window", C.c_int32), ("sm_scale", C.c_float), ("reserved", C.c_int32)]
 
 
+class RadixStats(C.Structure):
+    _fields_ = [("nodes", C.c_int32), ("cached_pages", C.c_int32),
+                ("protected_pages", C.c_int32), ("evictable_pages", C.c_int32)]
+
+
 class PoolStats(C.Structure):
     _fields_ = [("capacity", C.c_int32), ("free_pages", C.c_int32),
                 ("shared_pages", C.c_int32), ("active_pages", C.c_int32)]
@@ -113,6 +118,16 @@ _HOST_SIGS = {
     "w34_seq_protected_pages": (C.c_int32, [C.c_void_p]),
     "w34_seq_pages": (_P(C.c_int32), [C.c_void_p]),
     "w34_seq_set_pages_unchecked": (C.c_int32, [C.c_void_p, _P(C.c_int32), C.c_int32, C.c_int32]),
+    "w34_radix_create": (C.c_void_p, [C.c_void_p]),
+    "w34_radix_destroy": (None, [C.c_void_p]),
+    "w34_radix_match_prefix": (C.c_int32, [C.c_void_p, _P(C.c_int32), C.c_int32, _P(C.c_int32), C.c_int32,
+                                            _P(C.c_int32), _P(C.c_int32)]),
+    "w34_radix_lock": (C.c_int32, [C.c_void_p, C.c_int32]),
+    "w34_radix_unlock": (C.c_int32, [C.c_void_p, C.c_int32]),
+    "w34_radix_insert": (C.c_int32, [C.c_void_p, _P(C.c_int32), C.c_int32, _P(C.c_int32), C.c_int32, _P(C.c_int32)]),
+    "w34_radix_evict": (C.c_int32, [C.c_void_p, C.c_int32, _P(C.c_int32), C.c_int32]),
+    "w34_radix_get_stats": (None, [C.c_void_p, _P(RadixStats)]),
+    "w34_radix_sanity_check": (C.c_int32, [C.c_void_p]),
     "w34_build_step_metadata": (C.c_int32, [_P(C.c_void_p), _P(C.c_int32), C.c_int32, C.c_int32] +
                                 [_P(C.c_int32)] * 7),
 }

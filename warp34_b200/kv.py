@@ -125,6 +125,65 @@ class Sequence:
         return self._h.w34_seq_set_pages_unchecked(self.handle, arr, len(pages), protected_pages)
 
 
+class PrefixCache:
+    """Page-aligned radix cache of token prefixes (KV half of the reference's MambaRadixCache)."""
+
+    def __init__(self, pool):
+        self._h = ffi.host()
+        self.pool = pool
+        self.handle = self._h.w34_radix_create(pool.handle)
+
+    def close(self):
+        if self.handle:
+            self._h.w34_radix_destroy(self.handle)
+            self.handle = None
+
+    def match_prefix(self, tokens):
+        """Returns (pages, matched_tokens, node)."""
+        n = len(tokens)
+        tok = (C.c_int32 * max(n, 1))(*tokens)
+        cap = n // self.pool.block_size + 1
+        out = (C.c_int32 * cap)()
+        mt, node = C.c_int32(), C.c_int32()
+        rc = self._h.w34_radix_match_prefix(self.handle, tok, n, out, cap, C.byref(mt), C.byref(node))
+        if rc < 0:
+            raise RuntimeError(f"w34_radix_match_prefix: {rc}")
+        return list(out[:rc]), mt.value, node.value
+
+    def insert(self, tokens, pages):
+        """Returns (tokens already cached, node ending the sequence)."""
+        tok = (C.c_int32 * max(len(tokens), 1))(*tokens)
+        pg = (C.c_int32 * max(len(pages), 1))(*pages)
+        node = C.c_int32()
+        rc = self._h.w34_radix_insert(self.handle, tok, len(tokens), pg, len(pages), C.byref(node))
+        if rc < 0:
+            raise RuntimeError(f"w34_radix_insert: {rc}")
+        return rc, node.value
+
+    def lock(self, node):
+        return self._h.w34_radix_lock(self.handle, node)
+
+    def unlock(self, node):
+        return self._h.w34_radix_unlock(self.handle, node)
+
+    def evict(self, num_pages):
+        cap = self.pool.num_pages
+        buf = (C.c_int32 * cap)()
+        n = self._h.w34_radix_evict(self.handle, num_pages, buf, cap)
+        if n < 0:
+            raise RuntimeError(f"w34_radix_evict: {n}")
+        return list(buf[:n])
+
+    def stats(self):
+        st = ffi.RadixStats()
+        self._h.w34_radix_get_stats(self.handle, C.byref(st))
+        return {"nodes": st.nodes, "cached": st.cached_pages, "protected": st.protected_pages,
+                "evictable": st.evictable_pages}
+
+    def sanity_check(self):
+        return self._h.w34_radix_sanity_check(self.handle)
+
+
 def resolve_layer(policy, ordinal, num_layers, supports_fp8=False):
     out = (C.c_int32 * 4)()
     rc = ffi.host().w34_kv_policy_resolve_layer(policy, ordinal, num_layers, int(supports_fp8), out)
