@@ -178,6 +178,117 @@ def host_step_batch(kv, step, batch, n_tok):
                         io.max_blocks, 1.0 / 16.0, device="cpu")
 
 
+def run_chunked_prefill(args):
+    """Config 2: 8 sequences x 16384 tokens prefilled in 2048-token chunks (quantize-and-append,
+    then causal chunk attention over everything cached so far); the first 4096 tokens are one
+    shared, reference-counted prefix that only the first sequence computes.  Sequences are split
+    over the ranks (strong scaling), each rank keeps its own copy of the shared prefix."""
+    import oracle  # noqa: F401  (reference arm only)
+    from warp34_b200 import ffi, kv, sharding, synth
+    reference = args.impl == "reference"
+    ref_path = oracle.ref_lib_path() if reference else None
+    if reference and ref_path is None:
+        if int(os.environ.get("RANK", "0")) == 0:
+            print(json.dumps({"impl": "reference", "unavailable": "reference kernels not built (oracle/_ref missing)"}))
+        return
+    rank, local, world = init_dist(args.gpus)
+    dev = f"cuda:{local}"
+    lib = ffi.bind_kernel_abi(ref_path) if ref_path else ffi.kernels()
+    hq, hkv, n_seq, seq_len, chunk, prefix = 16, 4, 8, 16384, 2048, 4096
+    lo, hi = sharding.split_batch(n_seq, world, rank)
+    my_seqs = max(hi - lo, 0)
+    pages_needed = my_seqs * (seq_len // 16) + 64
+    pool = kv.PagePool(pages_needed + 1)
+    pool.shuffle_free_list(2 + rank)
+    layer = kv.KvLayer(pages_needed + 1, hkv, device=dev)
+    cache = kv.PrefixCache(pool)
+    ex = kv.Executor(64 << 20, device=dev)
+    kc, vc = synth.make_kv(chunk, hkv, 2, device=dev)
+    qc = synth.make_q(chunk, hq, 2, device=dev)
+    out = torch.zeros(chunk, hq, 256, dtype=torch.float16, device=dev)
+    max_blocks = seq_len // 16
+    tokens = list(range(seq_len))           # every sequence has the same first `prefix` tokens
+
+    def run_job(timed):
+        pool_seqs, flops, n_tok = [], 0.0, 0
+        evs = []
+        for i in range(my_seqs):
+            s = kv.Sequence(pool)
+            pool_seqs.append(s)
+            start = 0
+            if i > 0:
+                pages, matched, node = cache.match_prefix(tokens[:prefix])
+                assert matched == prefix
+                s.attach_prefix(pages, matched)
+                start = matched
+            while start < seq_len:
+                assert s.reserve(start + chunk) >= 0
+                b = kv.build_step([s], [chunk], max_blocks, 1.0 / 16.0, device=dev)
+                if timed:
+                    e = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True),
+                         torch.cuda.Event(enable_timing=True))
+                    e[0].record()
+                kv.kv_cache_write(ex, layer, b, kc, vc, lib=lib)
+                if timed:
+                    e[1].record()
+                kv.paged_attention(ex, layer, b, qc, out, hq, lib=lib)
+                if timed:
+                    e[2].record()
+                    evs.append(e)
+                s.commit(chunk)
+                # causal: token t of the chunk sees start + t + 1 keys
+                flops += 4.0 * hq * 256 * (chunk * start + chunk * (chunk + 1) / 2)
+                n_tok += chunk
+                start += chunk
+                if i == 0 and start == prefix:
+                    cache.insert(tokens[:prefix], s.pages[:prefix // 16])
+        torch.cuda.synchronize()
+        for s in pool_seqs:
+            s.close()
+        freed = cache.evict(10 ** 9)
+        return flops, n_tok, evs, len(freed)
+
+    run_job(False)                            # warm-up pass over the whole job
+    barrier(world)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(local)
+    sampler.start()
+    t_begin = time.perf_counter()
+    e0.record()
+    flops, n_tok, evs, shared_pages = run_job(True)
+    e1.record()
+    barrier(world)
+    t_end = time.perf_counter()
+    sampler.stop_flag = True
+    ms = max_over_ranks(e0.elapsed_time(e1), world)
+    attn_ms = sum(b.elapsed_time(c) for a, b, c in evs)
+    app_ms = sum(a.elapsed_time(b) for a, b, c in evs)
+    tot_flops = sum_over_ranks(flops, world)
+    tot_tok = sum_over_ranks(float(n_tok), world)
+    if rank != 0:
+        return
+    peaks, kind = measured_peaks()
+    peak = float(peaks.get("bf16_tflops_sustained", 1400.0))
+    achieved = flops / (attn_ms * 1e-3) / 1e12 if attn_ms > 0 else 0.0
+    line = {"metric": "tq4_chunked_prefill_attention_tflops", "value": tot_flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+            "n_gpus": world, "steps": 1, "warmup": 1, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": "cfg2_chunked_prefill: 8 seqs x 16384 tokens, 2048-token chunks, first 4096 tokens a "
+                                   "shared refcounted prefix, 16 q heads / 4 kv heads, d256; a step is the whole job",
+                       "l2": "each chunk re-reads its sequence's cached KV (up to 17 MB): L2-resident by design of the workload",
+                       "parallelism": f"sequences split over {world} rank(s), no collective", "shared_prefix_pages": shared_pages},
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                         "peak_kind": f"of {kind} (sustained bf16)", "kernel": "tq4_attention_prefill_kernel", "traffic": None,
+                         "attention_ms_rank0": attn_ms},
+            "append_tokens_per_s": n_tok / (app_ms * 1e-3) if app_ms > 0 else None,
+            "prefill_tokens_per_s": tot_tok / (ms * 1e-3), "gpu_launches": 2 * len(evs),
+            "clocks": sampler.summary(t_begin, t_end)}
+    if reference:
+        line["impl"] = "reference"
+        line["roofline"]["kernel"] = "reference paged_attention_prefill_mma_f16_kernel<64>"
+    print(json.dumps(line))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -189,6 +300,8 @@ def main():
     ap.add_argument("--append-tokens", type=int, default=32768, help="tokens of the bulk-append measurement")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.config == "cfg2_chunked_prefill":
+        return run_chunked_prefill(args)
 
     import oracle  # only for the reference arm and the cpu_baseline leg
     from warp34_b200 import ffi, kv, synth

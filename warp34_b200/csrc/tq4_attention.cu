@@ -305,14 +305,38 @@ __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
     return v;
 }
+// Schedulable shared-memory loads.  A volatile asm keeps its place among all other volatile
+// asms, which chains every load and MMA of a page in source order.  These two are plain asms:
+// the compiler may move and interleave them freely.
+//  * lds32_lut: the lookup table never changes after the kernel's first barrier, and its address
+//    always derives from a code word loaded in the same page iteration.
+//  * lds32_dep: staged page data.  `token` is produced by page_token() right after the stage's
+//    mbarrier wait, so the load cannot rise above the wait, and loads of different iterations are
+//    different expressions; every result feeds an MMA of the same iteration, so it cannot sink
+//    past the stage's release either.
+__device__ __forceinline__ uint32_t lds32_lut(uint32_t addr) {
+    uint32_t v;
+    asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds32_dep(uint32_t addr, uint32_t token) {
+    uint32_t v;
+    asm("ld.shared.u32 %0, [%1+0];  // dep %2" : "=r"(v) : "r"(addr), "r"(token));
+    return v;
+}
+__device__ __forceinline__ uint32_t page_token(int i) {
+    uint32_t t;
+    asm volatile("mov.u32 %0, %1;" : "=r"(t) : "r"(i) : "memory");
+    return t;
+}
 __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
     uint32_t y;
-    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
+    asm("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
     return y;
 }
 __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
@@ -594,8 +618,9 @@ __global__ void __launch_bounds__(W34_WARPS * 32, 1) tq4_attention_stream_kernel
             const uint32_t vst = kst + kRunStride;
             const int kv_base = (pg0 + i) << 4;
             const bool full = (kv_base >= safe_lo) && (kv_base + 15 <= safe_hi);
-#define W34_LDS(addr) lds32(addr)
-#define W34_LUT(word, k) lds32(__byte_perm((word), lut_lane, 0x7604 + ((k) << 4)))
+            const uint32_t ptok = page_token(i);
+#define W34_LDS(addr) lds32_dep(addr, ptok)
+#define W34_LUT(word, k) lds32_lut(__byte_perm((word), lut_lane, 0x7604 + ((k) << 4)))
 
             // ---- S^T = K Q'^T, one accumulator per 128-half ------------------------------
             float sa[2][4], sl[2][4];  // hi and lo chains are independent
