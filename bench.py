@@ -289,6 +289,77 @@ def run_chunked_prefill(args):
     print(json.dumps(line))
 
 
+def run_bf16_kv(args):
+    """Comparison arm: the same decode step over uncompressed BF16 pages (1024 B per token and KV
+    head instead of 264), device-resident, one GPU.  `--impl reference` runs the reference's
+    own bf16 kernels when they were built."""
+    import oracle
+    from warp34_b200 import ffi, kv, synth
+    reference = args.impl == "reference"
+    ref_path = oracle.ref_lib_path() if reference else None
+    if reference and ref_path is None:
+        print(json.dumps({"impl": "reference", "unavailable": "reference kernels not built (oracle/_ref missing)"}))
+        return
+    lib = ffi.bind_kernel_abi(ref_path) if ref_path else ffi.kernels()
+    hq, hkv, batch, lo, hi, q_len, seed = synth.CONFIGS[args.config]
+    ctx = synth.context_lengths(batch, lo, hi, seed)
+    wl = synth.PagedWorkload([int(c) for c in ctx], [q_len] * batch, hkv, seed=seed, formats=kv.BF16_KV_FORMATS)
+    ex = kv.Executor(64 << 20)
+    wl.fill_context(ex, seed, chunk_tokens=32768)
+    n_tok = batch * q_len
+    k_new, v_new = (x.to(torch.bfloat16).cuda() for x in synth.make_kv(n_tok, hkv, seed + 17))
+    q = synth.make_q(n_tok, hq, seed + 17).to(torch.bfloat16).cuda()
+    out = torch.zeros_like(q)
+    b = wl.step()
+    ex.set_stream()
+
+    def one(ev=None):
+        kv.kv_cache_write_bf16(ex, wl.layer, b, k_new, v_new, lib=lib)
+        if ev is not None:
+            ev[0].record()
+        kv.paged_attention_bf16kv(ex, wl.layer, b, q, out, hq, lib=lib)
+        if ev is not None:
+            ev[1].record()
+
+    sampler = ClockSampler(0)
+    sampler.start()
+    for _ in range(args.warmup):
+        one()
+    torch.cuda.synchronize()
+    evs = [tuple(torch.cuda.Event(enable_timing=True) for _ in range(2)) for _ in range(args.steps)]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_begin = time.perf_counter()
+    e0.record()
+    for i in range(args.steps):
+        one(evs[i])
+    e1.record()
+    torch.cuda.synchronize()
+    t_end = time.perf_counter()
+    sampler.stop_flag = True
+    ms = e0.elapsed_time(e1) / args.steps
+    attn_ms = float(np.mean([a.elapsed_time(c) for a, c in evs]))
+    kv_bytes = wl.algorithmic_kv_bytes()
+    peaks, peak_kind = measured_peaks()
+    peak = float(peaks.get("hbm_gbs", FALLBACK_HBM_GBS))
+    achieved = kv_bytes / (attn_ms * 1e-3) / 1e9
+    line = {"metric": "bf16_kv_decode_GBps", "value": kv_bytes / (ms * 1e-3) / 1e9, "unit": "GB/s", "n_gpus": 1,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"{args.config} over uncompressed BF16 pages: {batch} seqs x ctx U[{lo},{hi}], "
+                                   f"{hq} q heads / {hkv} kv heads, d256, step = append {q_len} token/seq + decode attention",
+                       "kv_bytes_per_step": kv_bytes, "l2": "KV read per step is larger than L2; no flush needed"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_kind": f"of {peak_kind}", "kernel": "bf16kv_attention_stream_kernel (+ plan and merge)",
+                         "launch_ms": attn_ms, "traffic": None},
+            "attended_tokens_per_s": float(sum(wl.ctx) + n_tok) / (attn_ms * 1e-3),
+            "gpu_launches": 4 * args.steps, "clocks": sampler.summary(t_begin, t_end)}
+    if reference:
+        line["impl"] = "reference"
+        line["roofline"]["kernel"] = "reference paged_attention_gqa_bf16_kernel"
+        line["gpu_launches"] = None
+    print(json.dumps(line))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -298,8 +369,12 @@ def main():
     ap.add_argument("--config", default="cfg1_batched_decode")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--append-tokens", type=int, default=32768, help="tokens of the bulk-append measurement")
+    ap.add_argument("--kv", default="tq4", choices=["tq4", "bf16"],
+                    help="bf16: the uncompressed-storage comparison arm of the same decode step (one GPU)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.kv == "bf16":
+        return run_bf16_kv(args)
     if args.config == "cfg2_chunked_prefill":
         return run_chunked_prefill(args)
 

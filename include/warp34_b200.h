@@ -167,6 +167,29 @@ int warp34_paged_attention_scalar_f16(const warp34_exec* ex, const warp34_kv_lay
                                       const void* q_in, void* attn_out,
                                       int num_q_heads);
 
+/*
+ * Uncompressed BF16 KV storage with identity transforms (the comparison arm of the TQ4 path).
+ * Replace warp34_kv_cache_write_bf16 / warp34_kv_cache_write_strided_bf16 /
+ * warp34_paged_attention_bf16 (warp34_cuda.h:363-368; op_kv_cache.cu:1170-1241) for
+ * {BF16, BF16, IDENTITY, IDENTITY} descriptors with head_dim 256 and 16-token pages; other
+ * head sizes return cudaErrorNotSupported, descriptors of another format cudaErrorInvalidValue
+ * as in the reference (op_kv_cache.cu:860-865).  K / V / Q / output are bf16.  The append copies
+ * rows bit for bit (row_stride_elems >= heads * 256 lets packed [K, V] or [Q, K, V]
+ * activations be written without a column copy).  The attention call streams pages through
+ * the split-KV path and, unlike the reference's, needs ex->scratch_ptr
+ * (warp34_paged_attention_bf16_scratch_bytes for the full grid, less shrinks the grid) and
+ * 16-byte-aligned strides; without them it returns cudaErrorNotSupported.
+ */
+int warp34_kv_cache_write_bf16(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
+                               const warp34_attention_batch* batch,
+                               const void* k_in, const void* v_in);
+int warp34_kv_cache_write_strided_bf16(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
+                                       const warp34_attention_batch* batch,
+                                       const void* k_in, const void* v_in, int row_stride_elems);
+int warp34_paged_attention_bf16(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
+                                const warp34_attention_batch* batch,
+                                const void* q_in, void* attn_out, int num_q_heads);
+
 /* ======================================================================== *
  * 2. Additive entry points (no reference symbol changes meaning).
  * ======================================================================== */
@@ -179,6 +202,11 @@ int warp34_paged_attention_scalar_f16(const warp34_exec* ex, const warp34_kv_lay
 size_t warp34_paged_attention_scratch_bytes(const warp34_kv_layer_layout* layout,
                                             const warp34_attention_batch* batch,
                                             int num_q_heads);
+
+/* The same bound for warp34_paged_attention_bf16 (16 query rows per work item). */
+size_t warp34_paged_attention_bf16_scratch_bytes(const warp34_kv_layer_layout* layout,
+                                                 const warp34_attention_batch* batch,
+                                                 int num_q_heads);
 
 /*
  * bf16 activations over TQ4 pages.  The reference's TQ4 path takes fp16 activations only (its

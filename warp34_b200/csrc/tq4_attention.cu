@@ -197,6 +197,7 @@ struct StreamParams {
     uint32_t smem_bytes;   // dynamic shared memory given to the stream kernel
     int rows_per_group;    // query rows per work item: 8 (one warp per item) or 8 * NT (teams)
     float q_scale;         // sm_scale * log2(e) / kLutScale, folded into Q'
+    int natural;           // partials are in natural (unrotated, unscaled) coordinates: uncompressed KV
 };
 
 __device__ __forceinline__ int32_t* plan_array(uint8_t* scratch, int which, int num_reqs) {
@@ -1837,11 +1838,17 @@ __global__ void __launch_bounds__(128) tq4_attention_merge_kernel(const StreamPa
         if (lane == 0) { dst[kHeadDim] = m_tot; dst[kHeadDim + 1] = l_tot; }
         return;
     }
+    const size_t out_base = ((size_t)tok * p.num_q_heads + q_head) * kHeadDim;
+    if (p.natural) {
+        const float inv = (l_tot > 0.0f) ? (1.0f / l_tot) : 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) store_act(p.attn_out, out_base + lane + 32 * j, acc[j] * inv, p.io_bf16);
+        return;
+    }
     const float inv_l = (l_tot > 0.0f) ? (1.0f / (l_tot * kLutScale)) : 0.0f;
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] *= inv_l;
     wht256_lanes(acc, lane);
-    const size_t out_base = ((size_t)tok * p.num_q_heads + q_head) * kHeadDim;
 #pragma unroll
     for (int j = 0; j < 8; ++j) store_act(p.attn_out, out_base + lane + 32 * j, apply_sign(acc[j], lane + 32 * j), p.io_bf16);
 }
@@ -2113,6 +2120,7 @@ static int launch_attention(const warp34_exec* ex, const warp34_kv_layer_layout*
     p.max_slots = (int)(p.num_warps + items);
     p.rows_per_group = rpg;
     p.q_scale = batch->sm_scale * 1.4426950408889634f / kLutScale;
+    p.natural = 0;
     cudaStream_t st = (cudaStream_t)ex->stream;
     const size_t smem = (size_t)dev->smem_optin;
     p.smem_bytes = (uint32_t)smem;
@@ -2250,3 +2258,5 @@ extern "C" int warp34_kv_page_copy(const warp34_exec* ex, const warp34_kv_layer_
         *layout, src_page, dst_page, rows);
     return (int)cudaGetLastError();
 }
+
+#include "bf16_kv.cuh"

@@ -335,6 +335,26 @@ def paged_attention(ex, layer, batch, q, out, num_q_heads, lib=None, scalar=Fals
     _check(rc, "warp34_paged_attention_f16")
 
 
+BF16_KV_FORMATS = (ffi.KV_FORMAT_BF16, ffi.KV_FORMAT_BF16, ffi.KV_TRANSFORM_IDENTITY, ffi.KV_TRANSFORM_IDENTITY)
+
+
+def kv_cache_write_bf16(ex, layer, batch, k, v, row_stride_elems=None, lib=None):
+    """warp34_kv_cache_write_strided_bf16: bf16 k/v into a BF16-format layer (KvLayer(formats=BF16_KV_FORMATS))."""
+    lib = lib or ffi.kernels()
+    rs = row_stride_elems if row_stride_elems is not None else k.stride(0)
+    rc = lib.warp34_kv_cache_write_strided_bf16(C.byref(ex.ex), C.byref(layer.layout), C.byref(batch.desc),
+                                                k.data_ptr(), v.data_ptr(), rs)
+    _check(rc, "warp34_kv_cache_write_strided_bf16")
+
+
+def paged_attention_bf16kv(ex, layer, batch, q, out, num_q_heads, lib=None):
+    """warp34_paged_attention_bf16: bf16 q / out over a BF16-format layer."""
+    lib = lib or ffi.kernels()
+    rc = lib.warp34_paged_attention_bf16(C.byref(ex.ex), C.byref(layer.layout), C.byref(batch.desc),
+                                         q.data_ptr(), out.data_ptr(), num_q_heads)
+    _check(rc, "warp34_paged_attention_bf16")
+
+
 def paged_attention_partial(ex, layer, batch, q, triples, num_q_heads, lib=None):
     """warp34_paged_attention_partial_f16: triples is fp32 [tokens, heads, 258]."""
     lib = lib or ffi.kernels()

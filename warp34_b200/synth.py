@@ -70,7 +70,7 @@ class PagedWorkload:
     """
 
     def __init__(self, ctx, q_lens, num_kv_heads, seed, device="cuda", slack_pages=64,
-                 shuffle=True, fill=None):
+                 shuffle=True, fill=None, formats=None):
         self.ctx = [int(c) for c in ctx]
         self.q_lens = [int(q) for q in q_lens]
         n = len(self.ctx)
@@ -85,7 +85,9 @@ class PagedWorkload:
         for s, c, q in zip(self.seqs, self.ctx, self.q_lens):
             rc = s.reserve(c + q)
             assert rc >= 0, rc
-        self.layer = kvmod.KvLayer(self.num_pages, num_kv_heads, device=device, fill=fill)
+        self.bf16_storage = formats is not None and tuple(formats) == tuple(kvmod.BF16_KV_FORMATS)
+        extra = {} if formats is None else {"formats": tuple(formats)}
+        self.layer = kvmod.KvLayer(self.num_pages, num_kv_heads, device=device, fill=fill, **extra)
         self.num_kv_heads = num_kv_heads
         self.device = device
         self.max_blocks = max(s.num_pages for s in self.seqs)
@@ -112,7 +114,11 @@ class PagedWorkload:
                 n = min(chunk_tokens, c - start)
                 k, v = make_kv(n, self.num_kv_heads, seed * 1000003 + i * 1009 + start, device=self.device)
                 batch = kvmod.build_step([s], [n], self.max_blocks, 1.0 / 16.0, device=self.device)
-                kvmod.kv_cache_write(ex, self.layer, batch, k, v, lib=lib)
+                if self.bf16_storage:
+                    k, v = k.to(torch.bfloat16), v.to(torch.bfloat16)   # exact: values sit on the bf16 grid
+                    kvmod.kv_cache_write_bf16(ex, self.layer, batch, k, v, lib=lib)
+                else:
+                    kvmod.kv_cache_write(ex, self.layer, batch, k, v, lib=lib)
                 s.commit(n)
                 if keep:
                     ks.append(k.cpu())
@@ -125,5 +131,7 @@ class PagedWorkload:
         return kept
 
     def algorithmic_kv_bytes(self):
-        """Compressed KV bytes one decode / verify pass must read: sum(ctx+q) * Hkv * 264."""
-        return sum(c + q for c, q in zip(self.ctx, self.q_lens)) * self.num_kv_heads * 264
+        """KV bytes one decode / verify pass must read: sum(ctx+q) * Hkv * (K row + V row bytes):
+        264 for TQ4 storage, 1024 for uncompressed BF16."""
+        row_pair = 1024 if self.bf16_storage else 264
+        return sum(c + q for c, q in zip(self.ctx, self.q_lens)) * self.num_kv_heads * row_pair
