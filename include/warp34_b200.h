@@ -53,6 +53,9 @@ enum {
  * operands, no scratch) for callers that want scores at fp32 accuracy. */
 #define WARP34_EXEC_FLAG_ALLOW_W4A8_PREFILL (1ull << 0)
 #define WARP34_B200_EXEC_FLAG_PRECISE_ATTENTION (1ull << 40)
+/* Additive as well: chunked-prefill batches take the 64-row mma.sync kernel even where the
+ * 128-row tcgen05 kernel applies (cross-checks, A/B measurements). */
+#define WARP34_B200_EXEC_FLAG_PREFILL_MMA_SYNC (1ull << 41)
 
 /* ---- descriptors (reference: warp34_cuda.h:50-101) -------------------------- */
 typedef struct {

@@ -81,7 +81,7 @@ __global__ void __launch_bounds__(128) kv_cache_write_bf16_kernel(const warp34_k
 }
 
 __global__ void __launch_bounds__(kBfWarps * 32, 1) bf16kv_attention_stream_kernel(const StreamParams p) {
-    extern __shared__ __align__(128) uint8_t smem[];
+    extern __shared__ __align__(1024) uint8_t smem[];
     constexpr int PARTIAL = kBfRows * kHeadDim + 2 * kBfRows;
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int gid = lane >> 2, tig = lane & 3;

@@ -1733,6 +1733,10 @@ __global__ void __launch_bounds__(kPfWarps * 32, 2) tq4_attention_prefill_kernel
     }
 }
 
+}  // namespace w34
+#include "tq4_prefill_tc.cuh"
+namespace w34 {
+
 // Row triple written when the caller merges across page shards itself: 256 un-normalised
 // accumulator values in the rotated domain (in lookup-table units), then m (log2 units of the
 // pre-scaled scores) and l.
@@ -1951,6 +1955,9 @@ static DeviceInfo* device_info(int* rc) {
         *rc = (int)cudaFuncSetAttribute(tq4_attention_prefill_kernel,
                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)prefill_smem_bytes());
         if (*rc != 0) return nullptr;
+        *rc = (int)cudaFuncSetAttribute(tq4_attention_prefill_tc_kernel,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBytes);
+        if (*rc != 0) return nullptr;
         d->smem_optin = optin;
         d->sm_count = sms;
         d->configured = true;
@@ -2058,6 +2065,32 @@ static int launch_attention(const warp34_exec* ex, const warp34_kv_layer_layout*
     if (triple_out == nullptr && (ex->flags & WARP34_B200_EXEC_FLAG_PRECISE_ATTENTION) == 0 &&
         stream_layout_ok(layout) && batch->max_blocks_per_req > 0 && gqa <= kPfRows &&
         (long long)batch->max_q_len * gqa > 24) {
+        // 128-row tiles on tcgen05 once a request fills a tile; the 64-row mma.sync kernel below
+        // for shorter chunks and when the caller asks for it.
+        if ((ex->flags & WARP34_B200_EXEC_FLAG_PREFILL_MMA_SYNC) == 0 && (long long)batch->max_q_len * gqa >= kTcRows &&
+            (size_t)dev->smem_optin >= kTcSmemBytes) {
+            PrefillTcParams tp;
+            tp.layout = *layout;
+            tp.batch = *batch;
+            tp.q_in = q_in;
+            tp.attn_out = attn_out;
+            tp.io_bf16 = io_bf16;
+            tp.num_q_heads = num_q_heads;
+            tp.gqa = gqa;
+            tp.tok_per_tile = kTcRows / gqa;
+            tp.q_scale = batch->sm_scale * 1.4426950408889634f;
+            tp.status = nullptr;
+            if (ex->scratch_ptr != 0 && (ex->scratch_ptr & 3u) == 0 && ex->scratch_size >= sizeof(PlanHeader)) {
+                tp.status = reinterpret_cast<int32_t*>((uintptr_t)ex->scratch_ptr);   // PlanHeader::status
+                rc = (int)cudaMemsetAsync(tp.status, 0, sizeof(int32_t), (cudaStream_t)ex->stream);
+                if (rc != 0) return rc;
+            }
+            const long long tiles = (long long)batch->total_tokens / tp.tok_per_tile + batch->num_reqs;
+            if (tiles > 0x7fffffffll || layout->local_kv_heads > 65535) return (int)cudaErrorInvalidValue;
+            const dim3 grid((unsigned)tiles, (unsigned)layout->local_kv_heads);
+            tq4_attention_prefill_tc_kernel<<<grid, kTcThreads, kTcSmemBytes, (cudaStream_t)ex->stream>>>(tp);
+            return (int)cudaGetLastError();
+        }
         PrefillParams pp;
         pp.layout = *layout;
         pp.batch = *batch;

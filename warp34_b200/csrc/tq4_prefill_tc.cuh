@@ -1,0 +1,526 @@
+// Chunked-prefill attention over TQ4 pages on the 5th-generation tensor cores (tcgen05 + TMEM).
+// Included by tq4_attention.cu (shares the PTX wrappers, geometry helpers and the codebook).
+//
+// Replaces paged_attention_prefill_mma_f16_kernel<128> (crates/warp34-kernels/csrc/ops/
+// op_paged_attn.cu:594-1128) for head_dim 256, 16-token pages, canonical TQ4 packing.
+//
+// One CTA = 128 query rows (128 / gqa tokens x gqa heads of one KV head) and 8 warps:
+//   warps 0-3 (consumers): thread r owns query row r = TMEM lane r.  Per block of 64 keys they
+//     read the scores S from TMEM (tcgen05.ld), run the online softmax with a lazily updated
+//     reference maximum, write P as fp16 into a swizzled shared-memory tile and, rarely,
+//     rescale the output accumulator in TMEM.  Thread 0 issues every tcgen05.mma:
+//       S_h[128 x 64] = Q'_h[128 x 128] K_h^T  8 instructions (K = 16 each) per 128-half h
+//       O[128 x 256] += P[128 x 64] V          4 instructions, A = P from smem, B = V (MN-major)
+//   warps 4-7 (producers): bulk-copy the raw (page, head) runs of four pages (2112 B each for
+//     K and for V) into a staging buffer, then dequantise them once per CTA into fp16 tiles in
+//     the 128-byte-swizzled layout the MMA descriptors expect: lookup of a code byte ->
+//     half2 of table centroids, 16-byte stores; the row scales go to a small fp32 array.
+// Completion of MMAs is tracked with tcgen05.commit on mbarriers; every wait is bounded and a
+// wait that gives up raises a flag that ends all loops (no thread is ever left at a barrier).
+//
+// Shared-memory tiles (all 1024-byte aligned, rows of 128 B = 64 fp16, 16-byte chunk index
+// XOR (row & 7)):
+//   Q' [4 dim blocks][128 rows][64]  K-major A operand      64 KB
+//   K  [4 dim blocks][ 64 keys][64]  K-major B operand      32 KB
+//   V  [4 dim blocks][ 64 keys][64]  MN-major B operand     32 KB  (same physical layout as K)
+//   P  [128 rows][64 keys]           K-major A operand      16 KB
+// TMEM (512 columns allocated): O in columns [0, 256), the two per-half score accumulators in
+// [256, 320) and [320, 384), fp32, lane = query row.
+// Scales: K tiles hold unscaled (table) centroids and the two K scales of a key multiply the
+// per-half partial scores in fp32.  V tiles are scaled while they are dequantised, each element
+// being the product rounded once.  (A scale, or P times a scale, rounded to fp16 per 128-half
+// puts a different relative error on the two halves of a row; through the inverse rotation that
+// difference moves a fraction of channel c ^ 128 into channel c, which is visible next to a
+// x20 outlier channel.  Element-wise rounding has no such coherent part.)
+#pragma once
+
+namespace w34 {
+
+constexpr int kTcRows = 128;
+constexpr int kTcKeys = 64;                      // keys per block = 4 pages
+constexpr int kTcThreads = 256;
+constexpr uint32_t kTcQBytes = 4u * kTcRows * 128u;          // 65536
+constexpr uint32_t kTcKvBytes = 4u * kTcKeys * 128u;         // 32768
+constexpr uint32_t kTcPBytes = kTcRows * 128u;               // 16384
+constexpr uint32_t kTcRawStage = 2u * 4u * kTq4PageHeadBytes;  // K runs then V runs of four pages: 16896
+constexpr uint32_t kTcLutBytes = 256u * 128u;                // lane-replicated, 128-byte entry stride
+constexpr uint32_t kTcOffQ = 0;
+constexpr uint32_t kTcOffK = kTcOffQ + kTcQBytes;
+constexpr uint32_t kTcOffV = kTcOffK + kTcKvBytes;
+constexpr uint32_t kTcOffP = kTcOffV + kTcKvBytes;
+constexpr uint32_t kTcOffRaw = kTcOffP + kTcPBytes;
+constexpr uint32_t kTcOffLut = kTcOffRaw + kTcRawStage;
+constexpr uint32_t kTcOffBars = kTcOffLut + kTcLutBytes;
+constexpr uint32_t kTcOffKScale = kTcOffBars + 128u;              // [2 buffers][2 halves][64 keys] floats
+constexpr uint32_t kTcSmemBytes = kTcOffKScale + 1024u + 1024u;   // + alignment slack
+constexpr int kTcStageStride = 257;              // floats per row of the epilogue staging
+static_assert(kTcRows * kTcStageStride * 4 <= (int)kTcOffRaw, "epilogue staging must not reach the raw ring");
+constexpr uint32_t kTcTmemCols = 512;
+constexpr uint32_t kTcColO = 0, kTcColS = 256;   // S: one 64-column accumulator per 128-half of the head
+constexpr float kTcRescaleThreshold = 8.0f;      // log2 units: P stays below 2^8
+
+// barrier slots (8 bytes each)
+enum { kBarFullK = 0, kBarFullV, kBarEmptyK, kBarEmptyV, kBarS, kBarPv, kBarPReady,
+       kBarRawFull, kBarRawFree, kBarCount };
+
+// ---- tcgen05 wrappers -------------------------------------------------------------------------
+__device__ __forceinline__ void tc_alloc(uint32_t smem_dst, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tc_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// D[tmem] (+)= A[smem desc] * B[smem desc]; issued by one thread.
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                           uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+// The mbarrier receives one arrival when every MMA issued so far by this thread has completed.
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t (&r)[32], uint32_t taddr) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+                 :: "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void sts16(uint32_t addr, uint32_t v) {
+    asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle: start address, leading / stride byte
+// offsets in 16-byte units, descriptor version 1 (bits 46-47), layout type 2 (bits 61-63).
+__device__ __forceinline__ uint64_t tc_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    return (uint64_t)((saddr >> 4) & 0x3fffu) | ((uint64_t)((lbo_bytes >> 4) & 0x3fffu) << 16) |
+           ((uint64_t)((sbo_bytes >> 4) & 0x3fffu) << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor, kind::f16: fp32 accumulate (bits 4-5 = 1), fp16 A and B (formats 0),
+// A K-major, B K-major or MN-major (bit 16), N >> 3 at bit 17, M >> 4 at bit 24.
+__host__ __device__ constexpr uint32_t tc_idesc(int m, int n, int b_mn_major) {
+    return (1u << 4) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+struct PrefillTcParams {
+    warp34_kv_layer_layout layout;
+    warp34_attention_batch batch;
+    const void* q_in;
+    void* attn_out;
+    int io_bf16;
+    int num_q_heads;
+    int gqa;
+    int tok_per_tile;      // 128 / gqa
+    float q_scale;         // sm_scale * log2(e)
+    int32_t* status;       // may be null; bit 2 is set when a wait gave up
+};
+
+__global__ void __launch_bounds__(kTcThreads, 1) tq4_attention_prefill_tc_kernel(const PrefillTcParams p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t q_t = base + kTcOffQ, k_t = base + kTcOffK, v_t = base + kTcOffV, p_t = base + kTcOffP;
+    const uint32_t raw = base + kTcOffRaw, lut = base + kTcOffLut, bars = base + kTcOffBars;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + kTcOffBars + 96);
+    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(gen + kTcOffBars + 100);
+    float* kscale = reinterpret_cast<float*>(gen + kTcOffKScale);
+    auto bar = [&](int which) { return bars + 8u * (uint32_t)which; };
+    // Waits and abort checks are made warp-uniform, so that no lane leaves a loop alone and the
+    // warp-collective instructions below always see all 32 lanes.
+    auto wait_all = [&](uint32_t b, uint32_t parity) {
+        const bool ok = mbar_wait(b, parity);
+        return __all_sync(0xffffffffu, ok) != 0;
+    };
+    auto aborted_any = [&]() { return __any_sync(0xffffffffu, *abort_flag != 0u) != 0; };
+
+    // ---- one-time setup -------------------------------------------------------------------------
+    for (int i = tid; i < 256 * 32; i += kTcThreads) {
+        const int byte = i >> 5, ln = i & 31;
+        // kLutScale x centroid lands close to the fp16 grid for all eight magnitudes; the factor is
+        // divided out of the row scale before the fp16 multiply
+        sts32(lut + (uint32_t)(byte * 128 + ln * 4),
+              pack_half2(kLutScale * tq4_centroid(byte & 15), kLutScale * tq4_centroid(byte >> 4)));
+    }
+    if (tid == 0) {
+        mbar_init(bar(kBarFullK), 128u);
+        mbar_init(bar(kBarFullV), 128u);
+        mbar_init(bar(kBarEmptyK), 1u);
+        mbar_init(bar(kBarEmptyV), 1u);
+        mbar_init(bar(kBarS), 1u);
+        mbar_init(bar(kBarPv), 1u);
+        mbar_init(bar(kBarPReady), 128u);
+        mbar_init(bar(kBarRawFull), 1u);
+        mbar_init(bar(kBarRawFree), 128u);
+        *abort_flag = 0u;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (wid == 0) {
+        tc_alloc(base + kTcOffBars + 96, kTcTmemCols);
+        tc_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    // ---- which (request, token tile) is this CTA? ---------------------------------------------
+    const int tpt = p.tok_per_tile;
+    const int kv_head = blockIdx.y;
+    int req = -1, tile_in_req = 0;
+    {
+        int t = blockIdx.x;
+        for (int r = 0; r < p.batch.num_reqs; ++r) {
+            const int ql = p.batch.query_start_loc[r + 1] - p.batch.query_start_loc[r];
+            const int nt = (ql + tpt - 1) / tpt;
+            if (t < nt) { req = r; tile_in_req = t; break; }
+            t -= nt;
+        }
+    }
+    ReqGeom g;
+    g.q_start = g.q_len = g.ctx_before = g.seq_after = 0;
+    g.valid = false;
+    if (req >= 0) g = load_req(p.batch, req);
+    const bool active = req >= 0 && g.valid;     // uniform over the CTA
+    const int tok0 = tile_in_req * tpt;
+    const int ntok = active ? min(tpt, g.q_len - tok0) : 0;
+    const int rows_used = ntok * p.gqa;
+
+    // every thread evaluates the limits of row (tid & 127); consumers keep them
+    const int my_row = tid & 127;
+    const int my_qoff = tok0 + my_row / p.gqa;
+    const bool row_ok = my_row < rows_used &&
+                        (p.batch.valid_token_mask == nullptr || p.batch.valid_token_mask[g.q_start + my_qoff] != 0);
+    const int rmax = row_ok ? row_max_kv(p.batch, g, my_qoff) : -1;
+    const int rmin = row_ok ? row_min_kv(p.batch, g, my_qoff) : 0x7fffffff;
+    __shared__ int s_lo[8], s_hi[8];
+    {
+        int lo = rmin, hi = rmax;
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) {
+            lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, d));
+            hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, d));
+        }
+        if (lane == 0) { s_lo[wid] = lo; s_hi[wid] = hi; }
+    }
+    __syncthreads();
+    int kv_lo = 0x7fffffff, kv_hi = -1;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) { kv_lo = min(kv_lo, s_lo[w]); kv_hi = max(kv_hi, s_hi[w]); }
+    const bool any_keys = active && kv_hi >= kv_lo;
+    const int kb_lo = any_keys ? (kv_lo >> 6) : 0;
+    const int nblocks = any_keys ? ((kv_hi >> 6) - kb_lo + 1) : 0;
+    const int pg_hi = any_keys ? (kv_hi >> 4) : -1;
+
+    // ---- Q' -> swizzled A tile: one warp per row, natural rotated-column order -------------------
+    for (int row = wid; row < kTcRows; row += 8) {
+        const int q_off = tok0 + row / p.gqa;
+        const int q_head = kv_head * p.gqa + row % p.gqa;
+        const bool ok = row < rows_used &&
+                        (p.batch.valid_token_mask == nullptr || p.batch.valid_token_mask[g.q_start + q_off] != 0);
+        float tv[8];
+        if (ok) {
+            const size_t q_base = ((size_t)(g.q_start + q_off) * p.num_q_heads + q_head) * kHeadDim;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) tv[j] = apply_sign(load_act(p.q_in, q_base + lane + 32 * j, p.io_bf16), lane + 32 * j);
+            wht256_lanes(tv, lane);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) tv[j] = 0.0f;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int c = lane + 32 * j;                 // rotated column
+            const int db = c >> 6, cc = c & 63;
+            const uint32_t addr = q_t + (uint32_t)db * (kTcRows * 128u) + (uint32_t)row * 128u +
+                                  (uint32_t)((((cc >> 3) ^ (row & 7)) << 4) + ((cc & 7) << 1));
+            sts16(addr, (uint32_t)__half_as_ushort(__float2half_rn(tv[j] * p.q_scale)));
+        }
+    }
+    fence_proxy_async();
+    __syncthreads();
+
+    const int32_t* blocks = p.batch.block_tables + (size_t)(req >= 0 ? req : 0) * p.batch.max_blocks_per_req;
+    float l_run = 0.0f;
+
+    if (wid >= 4) {
+        // ======================= producers: raw copies + dequantisation ============================
+        const int tp = tid - 128;
+        const int key = tp & 63, half = tp >> 6;
+        const uint8_t* k_head_base = (const uint8_t*)(uintptr_t)p.layout.k_base + (size_t)kv_head * p.layout.k_head_stride_bytes;
+        const uint8_t* v_head_base = (const uint8_t*)(uintptr_t)p.layout.v_base + (size_t)kv_head * p.layout.v_head_stride_bytes;
+        auto issue = [&](int j) {   // producer thread 0: raw runs of block j
+            const uint32_t dst = raw;
+            const uint32_t fb = bar(kBarRawFull);
+            int npg = 0;
+            for (int pp = 0; pp < 4; ++pp) npg += (4 * (kb_lo + j) + pp <= pg_hi) ? 1 : 0;
+            mbar_expect_tx(fb, (uint32_t)npg * 2u * kTq4PageHeadBytes);
+            for (int pp = 0; pp < npg; ++pp) {
+                const int32_t page = blocks[4 * (kb_lo + j) + pp];
+                bulk_g2s(dst + (uint32_t)pp * kTq4PageHeadBytes,
+                         k_head_base + (size_t)page * p.layout.k_page_stride_bytes, kTq4PageHeadBytes, fb);
+                bulk_g2s(dst + (uint32_t)(4 + pp) * kTq4PageHeadBytes,
+                         v_head_base + (size_t)page * p.layout.v_page_stride_bytes, kTq4PageHeadBytes, fb);
+            }
+        };
+        // one (key, 128-half) of K or V: 16 code words -> 16 swizzled 16-byte chunks
+        auto dequant = [&](uint32_t rowp, uint32_t tile, bool key_ok, float* scale_out) {
+            uint32_t w[16];
+            uint32_t dbits;
+            if (half == 0) {
+                uint32_t x[17];
+#pragma unroll
+                for (int j = 0; j < 17; ++j) x[j] = lds32(rowp + 4u * j);
+                dbits = x[0] & 0xffffu;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) w[j] = __funnelshift_r(x[j], x[j + 1], 16);
+            } else {
+                dbits = lds_u16(rowp + 66u);
+#pragma unroll
+                for (int j = 0; j < 16; ++j) w[j] = lds32(rowp + 68u + 4u * j);
+            }
+            if (!key_ok) dbits = 0u;      // a key no row can see may hold never-written bytes
+            // K tiles hold table values: the row scale (table factor divided out) multiplies the
+            // partial scores in fp32.  V tiles are scaled here: scale = hi + lo in fp16 and
+            // v = fma(e, hi, e * lo) is the product rounded once (to within 2^-22).
+            const float dscaled = __half2float(__ushort_as_half((unsigned short)dbits)) * (1.0f / kLutScale);
+            const __half d_hi = __float2half_rn(dscaled);
+            const __half2 hi2 = __half2half2(d_hi);
+            const __half2 lo2 = __float2half2_rn(dscaled - __half2float(d_hi));
+            if (scale_out != nullptr) *scale_out = dscaled;
+            const uint32_t lut_lane = lut + 4u * (uint32_t)lane;
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+                uint32_t h[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const uint32_t e = lds32(lut_lane + (__byte_perm(w[c], 0, 0x4440 + k) << 7));
+                    if (scale_out != nullptr) {
+                        h[k] = e;
+                    } else {
+                        const __half2 e2 = *reinterpret_cast<const __half2*>(&e);
+                        const __half2 v = __hfma2(e2, hi2, __hmul2(e2, lo2));
+                        h[k] = *reinterpret_cast<const uint32_t*>(&v);
+                    }
+                }
+                const int db = 2 * half + (c >> 3), cc = c & 7;
+                sts128(tile + (uint32_t)db * (kTcKeys * 128u) + (uint32_t)key * 128u + (uint32_t)((cc ^ (key & 7)) << 4),
+                       h[0], h[1], h[2], h[3]);
+            }
+        };
+
+        if (tp == 0 && nblocks > 0) issue(0);
+#pragma unroll 1
+        for (int j = 0; j < nblocks; ++j) {
+            if (aborted_any()) break;
+            const uint32_t par = (uint32_t)(j & 1);
+            if (!wait_all(bar(kBarRawFull), par)) { *abort_flag = 1u; break; }
+            const int pos = ((kb_lo + j) << 6) + key;
+            const bool key_ok = pos >= kv_lo && pos <= kv_hi;
+            const uint32_t rowp = raw + (uint32_t)key * kTq4RowBytes;
+            float* scales = kscale + (j & 1) * 128 + half * 64 + key;
+            if (j > 0 && !wait_all(bar(kBarEmptyK), par ^ 1u)) { *abort_flag = 1u; break; }
+            dequant(rowp, k_t, key_ok, scales);
+            fence_proxy_async();
+            mbar_arrive(bar(kBarFullK));
+            if (j > 0 && !wait_all(bar(kBarEmptyV), par ^ 1u)) { *abort_flag = 1u; break; }
+            dequant(rowp + 4u * kTq4PageHeadBytes, v_t, key_ok, nullptr);
+            fence_proxy_async();
+            mbar_arrive(bar(kBarFullV));
+            // The next block's raw runs fly while this thread waits for the tiles to be consumed.
+            mbar_arrive(bar(kBarRawFree));
+            if (tp == 0 && j + 1 < nblocks) {   // the loop's next abort check ends the warp together
+                if (mbar_wait(bar(kBarRawFree), par)) issue(j + 1); else *abort_flag = 1u;
+            }
+        }
+    } else {
+        // ======================= consumers: MMA issue, softmax, P, rescale =========================
+        const int row = tid;
+        const uint32_t lane_base = (uint32_t)(32 * wid) << 16;
+        const uint32_t t_o = tmem + lane_base + kTcColO, t_s = tmem + lane_base + kTcColS;
+        constexpr uint32_t kIdescQk = tc_idesc(kTcRows, kTcKeys, 0);
+        constexpr uint32_t kIdescPv = tc_idesc(kTcRows, kHeadDim, 1);
+        float m_ref = -1e30f;
+        auto issue_qk = [&](int j) {   // thread 0
+            if (!mbar_wait(bar(kBarFullK), (uint32_t)(j & 1))) { *abort_flag = 1u; return; }
+            tc_fence_after();
+#pragma unroll
+            for (int ks = 0; ks < 16; ++ks) {
+                const uint32_t off = (uint32_t)(ks >> 2);
+                const uint64_t a = tc_smem_desc(q_t + off * (kTcRows * 128u) + 32u * (ks & 3), 16u, 1024u);
+                const uint64_t b = tc_smem_desc(k_t + off * (kTcKeys * 128u) + 32u * (ks & 3), 16u, 1024u);
+                tc_mma_f16(tmem + kTcColS + 64u * (uint32_t)(ks >> 3), a, b, kIdescQk, (ks & 7) ? 1u : 0u);
+            }
+            tc_commit(bar(kBarS));
+            tc_commit(bar(kBarEmptyK));
+        };
+        if (tid == 0 && nblocks > 0) issue_qk(0);
+#pragma unroll 1
+        for (int j = 0; j < nblocks; ++j) {
+            if (aborted_any()) break;
+            const uint32_t par = (uint32_t)(j & 1);
+            if (!wait_all(bar(kBarS), par)) { *abort_flag = 1u; break; }
+            tc_fence_after();
+            float sv[64];
+            {
+                const float4* ks0 = reinterpret_cast<const float4*>(kscale + (j & 1) * 128);
+                const float4* ks1 = ks0 + 16;
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    uint32_t r0[32], r1[32];
+                    tc_ld32(r0, t_s + 32u * hh);
+                    tc_ld32(r1, t_s + 64u + 32u * hh);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int i4 = 0; i4 < 8; ++i4) {
+                        const float4 a = ks0[8 * hh + i4], b = ks1[8 * hh + i4];
+                        sv[32 * hh + 4 * i4 + 0] = a.x * __uint_as_float(r0[4 * i4 + 0]) + b.x * __uint_as_float(r1[4 * i4 + 0]);
+                        sv[32 * hh + 4 * i4 + 1] = a.y * __uint_as_float(r0[4 * i4 + 1]) + b.y * __uint_as_float(r1[4 * i4 + 1]);
+                        sv[32 * hh + 4 * i4 + 2] = a.z * __uint_as_float(r0[4 * i4 + 2]) + b.z * __uint_as_float(r1[4 * i4 + 2]);
+                        sv[32 * hh + 4 * i4 + 3] = a.w * __uint_as_float(r0[4 * i4 + 3]) + b.w * __uint_as_float(r1[4 * i4 + 3]);
+                    }
+                }
+            }
+            const int kbase = (kb_lo + j) << 6;
+            if (!(kbase >= rmin && kbase + 63 <= rmax)) {
+#pragma unroll
+                for (int i = 0; i < 64; ++i) {
+                    const int pos = kbase + i;
+                    if (!(pos >= rmin && pos <= rmax)) sv[i] = -1e30f;
+                }
+            }
+            float mx = sv[0];
+#pragma unroll
+            for (int i = 1; i < 64; ++i) mx = fmaxf(mx, sv[i]);
+            // the reference maximum moves only when the true maximum ran ahead by more than the threshold
+            const bool need = mx > m_ref + kTcRescaleThreshold;
+            float alpha = 1.0f;
+            if (need) {
+                alpha = ex2(m_ref - mx);      // 0 when nothing was visible before
+                m_ref = mx;
+            }
+            // P(j - 1) and O are in use until the previous output product has completed
+            if (j > 0 && !wait_all(bar(kBarPv), par ^ 1u)) { *abort_flag = 1u; break; }
+            tc_fence_after();
+            if (j > 0 && __any_sync(0xffffffffu, need)) {
+#pragma unroll 1
+                for (int c = 0; c < 8; ++c) {
+                    uint32_t o[32];
+                    tc_ld32(o, t_o + 32u * c);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                    tc_st32(t_o + 32u * c, o);
+                }
+                tc_wait_st();
+            }
+            float lsum = 0.0f;
+            const uint32_t prow = p_t + (uint32_t)row * 128u;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                uint32_t h[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const float a = sv[8 * c + 2 * k], b = sv[8 * c + 2 * k + 1];
+                    const float pa = (a > -1e29f) ? ex2(a - m_ref) : 0.0f;
+                    const float pb = (b > -1e29f) ? ex2(b - m_ref) : 0.0f;
+                    lsum += pa + pb;
+                    h[k] = pack_half2(pa, pb);
+                }
+                sts128(prow + (uint32_t)((c ^ (row & 7)) << 4), h[0], h[1], h[2], h[3]);
+            }
+            l_run = l_run * alpha + lsum;
+            fence_proxy_async();
+            tc_fence_before();
+            mbar_arrive(bar(kBarPReady));
+            if (tid == 0) {   // a failed wait only raises the flag: the warp leaves the loop together
+                if (mbar_wait(bar(kBarPReady), par) && mbar_wait(bar(kBarFullV), par)) {
+                    tc_fence_after();
+#pragma unroll
+                    for (int ks = 0; ks < 4; ++ks) {
+                        const uint64_t a = tc_smem_desc(p_t + 32u * ks, 16u, 1024u);
+                        const uint64_t b = tc_smem_desc(v_t + 2048u * ks, kTcKeys * 128u, 1024u);
+                        tc_mma_f16(tmem + kTcColO, a, b, kIdescPv, (j > 0 || ks > 0) ? 1u : 0u);
+                    }
+                    tc_commit(bar(kBarPv));
+                    tc_commit(bar(kBarEmptyV));
+                    if (j + 1 < nblocks) issue_qk(j + 1);
+                } else {
+                    *abort_flag = 1u;
+                }
+            }
+            __syncwarp();
+        }
+        // the last output product
+        if (nblocks > 0 && !aborted_any()) {
+            if (!wait_all(bar(kBarPv), (uint32_t)((nblocks - 1) & 1))) *abort_flag = 1u;
+        }
+        tc_fence_after();
+    }
+
+    // ---- epilogue: O / l -> staging -> inverse rotation -> global ---------------------------------
+    // (staging aliases the Q / K / V tiles: every MMA that read them has completed)
+    __syncthreads();
+    const bool aborted = *abort_flag != 0u;
+    float* stage = reinterpret_cast<float*>(gen);
+    if (wid < 4 && nblocks > 0 && !aborted) {
+        const uint32_t t_o = tmem + ((uint32_t)(32 * wid) << 16) + kTcColO;
+        const float inv = (l_run > 0.0f) ? (1.0f / l_run) : 0.0f;
+#pragma unroll 1
+        for (int c = 0; c < 8; ++c) {
+            uint32_t o[32];
+            tc_ld32(o, t_o + 32u * c);
+            tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) stage[tid * kTcStageStride + 32 * c + i] = __uint_as_float(o[i]) * inv;
+        }
+        stage[tid * kTcStageStride + 256] = l_run;
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (wid == 0) {
+        tc_fence_after();
+        tc_dealloc(tmem, kTcTmemCols);
+    }
+    if (aborted) {
+        if (tid == 0 && p.status != nullptr) atomicOr(p.status, 4);
+        return;
+    }
+    if (!active) return;
+    for (int row = wid; row < rows_used; row += 8) {
+        const int q_off = tok0 + row / p.gqa;
+        const int q_head = kv_head * p.gqa + row % p.gqa;
+        if (p.batch.valid_token_mask != nullptr && p.batch.valid_token_mask[g.q_start + q_off] == 0) continue;
+        float tv[8];
+        const bool has = nblocks > 0 && stage[row * kTcStageStride + 256] > 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) tv[j] = has ? stage[row * kTcStageStride + lane + 32 * j] : 0.0f;
+        wht256_lanes(tv, lane);
+        const size_t out_base = ((size_t)(g.q_start + q_off) * p.num_q_heads + q_head) * kHeadDim;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) store_act(p.attn_out, out_base + lane + 32 * j, apply_sign(tv[j], lane + 32 * j), p.io_bf16);
+    }
+}
+
+}  // namespace w34
