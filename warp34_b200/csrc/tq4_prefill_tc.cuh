@@ -4,64 +4,75 @@
 // Replaces paged_attention_prefill_mma_f16_kernel<128> (crates/warp34-kernels/csrc/ops/
 // op_paged_attn.cu:594-1128) for head_dim 256, 16-token pages, canonical TQ4 packing.
 //
-// One CTA = 128 query rows (128 / gqa tokens x gqa heads of one KV head) and 8 warps:
+// One CTA = 128 query rows (128 / gqa tokens x gqa heads of one KV head) and 14 warps:
 //   warps 0-3 (consumers): thread r owns query row r = TMEM lane r.  Per block of 64 keys they
 //     read the scores S from TMEM (tcgen05.ld), run the online softmax with a lazily updated
 //     reference maximum, write P as fp16 into a swizzled shared-memory tile and, rarely,
-//     rescale the output accumulator in TMEM.  Thread 0 issues every tcgen05.mma:
-//       S_h[128 x 64] = Q'_h[128 x 128] K_h^T  8 instructions (K = 16 each) per 128-half h
-//       O[128 x 256] += P[128 x 64] V          4 instructions, A = P from smem, B = V (MN-major)
-//   warps 4-7 (producers): bulk-copy the raw (page, head) runs of four pages (2112 B each for
-//     K and for V) into a staging buffer, then dequantise them once per CTA into fp16 tiles in
-//     the 128-byte-swizzled layout the MMA descriptors expect: lookup of a code byte ->
-//     half2 of table centroids, 16-byte stores; the row scales go to a small fp32 array.
-// Completion of MMAs is tracked with tcgen05.commit on mbarriers; every wait is bounded and a
-// wait that gives up raises a flag that ends all loops (no thread is ever left at a barrier).
+//     rescale the output accumulator in TMEM.
+//   warps 4-11 (producers): take the code words of a block from the staging buffer into
+//     registers (releasing it at once), then dequantise them once per CTA into fp16 tiles in the
+//     128-byte-swizzled layout the MMA descriptors expect: lookup of a code byte -> half2 of
+//     table centroids, times the row scale, 16-byte stores.  K and V tiles are double-buffered.
+//   warp 12: lane 0 issues every tcgen05.mma, the scores of block j + 1 ahead of the output
+//     product of block j so that they are computed during the softmax of block j:
+//       S[128 x 64]   = Q'[128 x 256] K^T   16 instructions (K = 16), A = Q' in TMEM, B = K tile
+//       O[128 x 256] += P[128 x 64] V        4 instructions, A = P tile, B = V tile (MN-major)
+//   warp 13: lane 0 bulk-copies the raw (page, head) runs of the next block's four pages
+//     (2112 B each for K and for V) into the staging buffer.
+// Completion of MMAs is tracked with tcgen05.commit on mbarriers; every wait is bounded and
+// warp-uniform, and a wait that gives up raises a flag that ends all loops (no thread is ever
+// left at a barrier, and the tensor memory is always freed).
 //
-// Shared-memory tiles (all 1024-byte aligned, rows of 128 B = 64 fp16, 16-byte chunk index
-// XOR (row & 7)):
-//   Q' [4 dim blocks][128 rows][64]  K-major A operand      64 KB
-//   K  [4 dim blocks][ 64 keys][64]  K-major B operand      32 KB
-//   V  [4 dim blocks][ 64 keys][64]  MN-major B operand     32 KB  (same physical layout as K)
-//   P  [128 rows][64 keys]           K-major A operand      16 KB
-// TMEM (512 columns allocated): O in columns [0, 256), the two per-half score accumulators in
-// [256, 320) and [320, 384), fp32, lane = query row.
-// Scales: K tiles hold unscaled (table) centroids and the two K scales of a key multiply the
-// per-half partial scores in fp32.  V tiles are scaled while they are dequantised, each element
-// being the product rounded once.  (A scale, or P times a scale, rounded to fp16 per 128-half
-// puts a different relative error on the two halves of a row; through the inverse rotation that
-// difference moves a fraction of channel c ^ 128 into channel c, which is visible next to a
-// x20 outlier channel.  Element-wise rounding has no such coherent part.)
+// Shared-memory tiles (1024-byte aligned, rows of 128 B = 64 fp16, 16-byte chunk index XOR
+// (row & 7)):
+//   K  [2][4 dim blocks][64 keys][64]  K-major B operand      2 x 32 KB
+//   V  [2][4 dim blocks][64 keys][64]  MN-major B operand     2 x 32 KB  (same physical layout)
+//   P  [128 rows][64 keys]             K-major A operand      16 KB
+// TMEM (512 columns): O in [0, 256), two score buffers in [256, 320) and [320, 384) (fp32, lane =
+// query row), Q' in [384, 512) (two fp16 per column).
+// Scales: every K and V element is table centroid x row scale, the product rounded once
+// (scale = hi + lo in fp16, v = fma(e, hi, e * lo)).  (A scale, or P times a scale, rounded to
+// fp16 per 128-half puts a different relative error on the two halves of a row; through the
+// inverse rotation that difference moves a fraction of channel c ^ 128 into channel c, which is
+// visible next to a x20 outlier channel.  Element-wise rounding has no such coherent part.)
 #pragma once
 
 namespace w34 {
 
 constexpr int kTcRows = 128;
 constexpr int kTcKeys = 64;                      // keys per block = 4 pages
-constexpr int kTcThreads = 256;
-constexpr uint32_t kTcQBytes = 4u * kTcRows * 128u;          // 65536
+constexpr int kTcProducerWarps = 8;
+constexpr int kTcProducers = kTcProducerWarps * 32;
+constexpr int kTcWarps = 4 + kTcProducerWarps + 2;   // 4 consumer, 8 producer, 1 MMA-issue, 1 copy-issue warp
+constexpr int kTcThreads = kTcWarps * 32;
 constexpr uint32_t kTcKvBytes = 4u * kTcKeys * 128u;         // 32768
 constexpr uint32_t kTcPBytes = kTcRows * 128u;               // 16384
 constexpr uint32_t kTcRawStage = 2u * 4u * kTq4PageHeadBytes;  // K runs then V runs of four pages: 16896
 constexpr uint32_t kTcLutBytes = 256u * 128u;                // lane-replicated, 128-byte entry stride
-constexpr uint32_t kTcOffQ = 0;
-constexpr uint32_t kTcOffK = kTcOffQ + kTcQBytes;
-constexpr uint32_t kTcOffV = kTcOffK + kTcKvBytes;
-constexpr uint32_t kTcOffP = kTcOffV + kTcKvBytes;
+constexpr uint32_t kTcOffK = 0;                               // K is double-buffered
+constexpr uint32_t kTcOffQStage = 0;                          // Q' staging (before the first block), 64 KB
+constexpr uint32_t kTcOffV = kTcOffK + 2u * kTcKvBytes;
+constexpr uint32_t kTcOffP = kTcOffV + 2u * kTcKvBytes;      // V is double-buffered
 constexpr uint32_t kTcOffRaw = kTcOffP + kTcPBytes;
-constexpr uint32_t kTcOffLut = kTcOffRaw + kTcRawStage;
+constexpr int kTcRawStages = 1;                  // producers take the code words into registers and release it at once
+constexpr uint32_t kTcOffLut = kTcOffRaw + (uint32_t)kTcRawStages * kTcRawStage;
 constexpr uint32_t kTcOffBars = kTcOffLut + kTcLutBytes;
-constexpr uint32_t kTcOffKScale = kTcOffBars + 128u;              // [2 buffers][2 halves][64 keys] floats
-constexpr uint32_t kTcSmemBytes = kTcOffKScale + 1024u + 1024u;   // + alignment slack
+// barriers, then (at +128 / +132) the TMEM address and the abort flag
+constexpr uint32_t kTcOffRed = kTcOffBars + 144u;                 // 16 ints: per-warp key-range reduction
+constexpr uint32_t kTcSmemBytes = kTcOffRed + 64u;
 constexpr int kTcStageStride = 257;              // floats per row of the epilogue staging
 static_assert(kTcRows * kTcStageStride * 4 <= (int)kTcOffRaw, "epilogue staging must not reach the raw ring");
 constexpr uint32_t kTcTmemCols = 512;
-constexpr uint32_t kTcColO = 0, kTcColS = 256;   // S: one 64-column accumulator per 128-half of the head
+constexpr uint32_t kTcColO = 0, kTcColS = 256;   // S: two buffers of 64 columns
+constexpr uint32_t kTcColQ = 384;                // Q' as the A operand: 256 fp16 per row = 128 columns
 constexpr float kTcRescaleThreshold = 8.0f;      // log2 units: P stays below 2^8
 
 // barrier slots (8 bytes each)
-enum { kBarFullK = 0, kBarFullV, kBarEmptyK, kBarEmptyV, kBarS, kBarPv, kBarPReady,
-       kBarRawFull, kBarRawFree, kBarCount };
+enum { kBarFullK0 = 0, kBarFullK1, kBarFullV0, kBarFullV1, kBarEmptyK0, kBarEmptyK1, kBarEmptyV0, kBarEmptyV1,
+       kBarS0, kBarS1, kBarSFree0, kBarSFree1,
+       kBarPv, kBarPReady,
+       kBarRawFull0, kBarRawFree0 = kBarRawFull0 + kTcRawStages, kBarCount = kBarRawFree0 + kTcRawStages };
+static_assert(kBarCount * 8 <= 128, "barrier slots end before the TMEM address slot");
 
 // ---- tcgen05 wrappers -------------------------------------------------------------------------
 __device__ __forceinline__ void tc_alloc(uint32_t smem_dst, uint32_t ncols) {
@@ -85,6 +96,15 @@ __device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uin
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+// Same with the A operand in tensor memory (lane = row, two fp16 per 32-bit column).
+__device__ __forceinline__ void tc_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                              uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
 }
 // The mbarrier receives one arrival when every MMA issued so far by this thread has completed.
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
@@ -139,16 +159,31 @@ struct PrefillTcParams {
 __global__ void __launch_bounds__(kTcThreads, 1) tq4_attention_prefill_tc_kernel(const PrefillTcParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
-    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
-    const uint32_t q_t = base + kTcOffQ, k_t = base + kTcOffK, v_t = base + kTcOffV, p_t = base + kTcOffP;
+    // The swizzled tiles need a 1024-byte-aligned window; the kernel has no static shared memory,
+    // so the dynamic window starts aligned.  If it ever does not, every thread leaves here.
+    const uint32_t base = smem_u32(smem_raw);
+    if ((base & 1023u) != 0u) {
+        if (tid == 0 && p.status != nullptr) atomicOr(p.status, 8);
+        return;
+    }
+    uint8_t* gen = smem_raw;
+    const uint32_t k_t = base + kTcOffK, v_t = base + kTcOffV, p_t = base + kTcOffP;
+    const uint32_t q_stage = base + kTcOffQStage;
     const uint32_t raw = base + kTcOffRaw, lut = base + kTcOffLut, bars = base + kTcOffBars;
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + kTcOffBars + 96);
-    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(gen + kTcOffBars + 100);
-    float* kscale = reinterpret_cast<float*>(gen + kTcOffKScale);
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + kTcOffBars + 128);
+    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(gen + kTcOffBars + 132);
     auto bar = [&](int which) { return bars + 8u * (uint32_t)which; };
     // Waits and abort checks are made warp-uniform, so that no lane leaves a loop alone and the
     // warp-collective instructions below always see all 32 lanes.
+#ifdef W34_TC_PROFILE
+    // Measurement build only: cycles spent in each kind of wait and in the work between, per role,
+    // written behind the status word (needs a scratch buffer of at least 1 MiB).
+    long long prof[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    long long prof_t = clock64();
+#define W34_PROF(slot) { const long long now_ = clock64(); prof[slot] += now_ - prof_t; prof_t = now_; }
+#else
+#define W34_PROF(slot)
+#endif
     auto wait_all = [&](uint32_t b, uint32_t parity) {
         const bool ok = mbar_wait(b, parity);
         return __all_sync(0xffffffffu, ok) != 0;
@@ -164,20 +199,29 @@ __global__ void __launch_bounds__(kTcThreads, 1) tq4_attention_prefill_tc_kernel
               pack_half2(kLutScale * tq4_centroid(byte & 15), kLutScale * tq4_centroid(byte >> 4)));
     }
     if (tid == 0) {
-        mbar_init(bar(kBarFullK), 128u);
-        mbar_init(bar(kBarFullV), 128u);
-        mbar_init(bar(kBarEmptyK), 1u);
-        mbar_init(bar(kBarEmptyV), 1u);
-        mbar_init(bar(kBarS), 1u);
+        mbar_init(bar(kBarFullK0), (uint32_t)kTcProducers);
+        mbar_init(bar(kBarFullK1), (uint32_t)kTcProducers);
+        mbar_init(bar(kBarFullV0), (uint32_t)kTcProducers);
+        mbar_init(bar(kBarFullV1), (uint32_t)kTcProducers);
+        mbar_init(bar(kBarEmptyK0), 1u);
+        mbar_init(bar(kBarEmptyK1), 1u);
+        mbar_init(bar(kBarEmptyV0), 1u);
+        mbar_init(bar(kBarEmptyV1), 1u);
+        mbar_init(bar(kBarS0), 1u);
+        mbar_init(bar(kBarS1), 1u);
+        mbar_init(bar(kBarSFree0), 128u);
+        mbar_init(bar(kBarSFree1), 128u);
         mbar_init(bar(kBarPv), 1u);
         mbar_init(bar(kBarPReady), 128u);
-        mbar_init(bar(kBarRawFull), 1u);
-        mbar_init(bar(kBarRawFree), 128u);
+        for (int st = 0; st < kTcRawStages; ++st) {
+            mbar_init(bar(kBarRawFull0 + st), 1u);
+            mbar_init(bar(kBarRawFree0 + st), (uint32_t)kTcProducers);
+        }
         *abort_flag = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (wid == 0) {
-        tc_alloc(base + kTcOffBars + 96, kTcTmemCols);
+        tc_alloc(base + kTcOffBars + 128, kTcTmemCols);
         tc_relinquish();
     }
     tc_fence_before();
@@ -214,7 +258,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) tq4_attention_prefill_tc_kernel
                         (p.batch.valid_token_mask == nullptr || p.batch.valid_token_mask[g.q_start + my_qoff] != 0);
     const int rmax = row_ok ? row_max_kv(p.batch, g, my_qoff) : -1;
     const int rmin = row_ok ? row_min_kv(p.batch, g, my_qoff) : 0x7fffffff;
-    __shared__ int s_lo[8], s_hi[8];
+    int* s_lo = reinterpret_cast<int*>(gen + kTcOffRed);
+    int* s_hi = s_lo + 8;
     {
         int lo = rmin, hi = rmax;
 #pragma unroll
@@ -222,7 +267,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) tq4_attention_prefill_tc_kernel
             lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, d));
             hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, d));
         }
-        if (lane == 0) { s_lo[wid] = lo; s_hi[wid] = hi; }
+        if (lane == 0 && wid < 4) { s_lo[wid] = lo; s_hi[wid] = hi; }
     }
     __syncthreads();
     int kv_lo = 0x7fffffff, kv_hi = -1;
@@ -234,7 +279,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) tq4_attention_prefill_tc_kernel
     const int pg_hi = any_keys ? (kv_hi >> 4) : -1;
 
     // ---- Q' -> swizzled A tile: one warp per row, natural rotated-column order -------------------
-    for (int row = wid; row < kTcRows; row += 8) {
+    for (int row = wid; row < kTcRows; row += kTcWarps) {
         const int q_off = tok0 + row / p.gqa;
         const int q_head = kv_head * p.gqa + row % p.gqa;
         const bool ok = row < rows_used &&
@@ -252,156 +297,227 @@ __global__ void __launch_bounds__(kTcThreads, 1) tq4_attention_prefill_tc_kernel
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             const int c = lane + 32 * j;                 // rotated column
-            const int db = c >> 6, cc = c & 63;
-            const uint32_t addr = q_t + (uint32_t)db * (kTcRows * 128u) + (uint32_t)row * 128u +
-                                  (uint32_t)((((cc >> 3) ^ (row & 7)) << 4) + ((cc & 7) << 1));
+            // staging row = 512 B; its 16-byte chunks are XOR-swizzled by the row so that the
+            // thread-per-row reads below spread over the banks
+            const uint32_t addr = q_stage + (uint32_t)row * 512u + (uint32_t)((((c >> 3) ^ (row & 31)) << 4) + ((c & 7) << 1));
             sts16(addr, (uint32_t)__half_as_ushort(__float2half_rn(tv[j] * p.q_scale)));
         }
     }
-    fence_proxy_async();
     __syncthreads();
+    // Q' is the A operand of the score product and lives in TMEM: lane = row, 256 fp16 = 128 columns
+    if (wid < 4) {
+        const uint32_t t_q = tmem + ((uint32_t)(32 * wid) << 16) + kTcColQ;
+#pragma unroll 1
+        for (int c4 = 0; c4 < 4; ++c4) {     // 32 columns = 64 fp16 = 8 chunks per step
+            uint32_t r[32];
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                const uint32_t chunk = (uint32_t)(8 * c4 + c);
+                const uint32_t addr = q_stage + (uint32_t)tid * 512u + ((chunk ^ (uint32_t)(tid & 31)) << 4);
+                asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(r[4 * c]), "=r"(r[4 * c + 1]), "=r"(r[4 * c + 2]), "=r"(r[4 * c + 3]) : "r"(addr));
+            }
+            tc_st32(t_q + 32u * c4, r);
+        }
+        tc_wait_st();
+    }
+    tc_fence_before();
+    __syncthreads();      // the staging area becomes the K tiles
 
     const int32_t* blocks = p.batch.block_tables + (size_t)(req >= 0 ? req : 0) * p.batch.max_blocks_per_req;
     float l_run = 0.0f;
 
-    if (wid >= 4) {
-        // ======================= producers: raw copies + dequantisation ============================
-        const int tp = tid - 128;
-        const int key = tp & 63, half = tp >> 6;
+    if (wid == 4 + kTcProducerWarps) {
+        // ======================= MMA issue: lane 0 feeds the tensor core ================================
+        // Order in the tensor pipe: QK(0), QK(1), PV(0), QK(2), PV(1), ...: the scores of block j + 1
+        // are computed while the consumers run the softmax of block j.
+        constexpr uint32_t kIdescQk = tc_idesc(kTcRows, kTcKeys, 0);
+        constexpr uint32_t kIdescPv = tc_idesc(kTcRows, kHeadDim, 1);
+        const uint64_t desc_k = tc_smem_desc(k_t, 16u, 1024u);
+        const uint64_t desc_p = tc_smem_desc(p_t, 16u, 1024u);
+        const uint64_t desc_v = tc_smem_desc(v_t, kTcKeys * 128u, 1024u);
+#pragma unroll 1
+        for (int j = 0; j <= nblocks; ++j) {
+            if (aborted_any()) break;
+            if (j < nblocks) {
+                W34_PROF(0)
+                bool ok = wait_all(bar(kBarFullK0 + (j & 1)), (uint32_t)((j >> 1) & 1));
+                W34_PROF(1)
+                // S buffer j & 1 was last read by the softmax of block j - 2
+                if (ok && j > 1) ok = wait_all(bar(kBarSFree0 + (j & 1)), (uint32_t)(((j - 2) >> 1) & 1));
+                W34_PROF(2)
+                if (!ok) { *abort_flag = 1u; break; }
+                tc_fence_after();
+                if (lane == 0) {
+                    const uint32_t d = tmem + kTcColS + 64u * (uint32_t)(j & 1);
+#pragma unroll
+                    for (int ks = 0; ks < 16; ++ks) {
+                        // start-address field is in 16-byte units: dim block ks >> 2, 32 bytes per k-step
+                        const uint64_t b = desc_k + (uint64_t)((j & 1) * (kTcKvBytes / 16) + (ks >> 2) * (kTcKeys * 128 / 16) + 2 * (ks & 3));
+                        tc_mma_f16_ts(d, tmem + kTcColQ + 8u * (uint32_t)ks, b, kIdescQk, ks ? 1u : 0u);
+                    }
+                    tc_commit(bar(kBarS0 + (j & 1)));
+                    tc_commit(bar(kBarEmptyK0 + (j & 1)));
+                }
+                __syncwarp();
+            }
+            if (j > 0) {
+                const int i = j - 1;
+                W34_PROF(0)
+                bool ok = wait_all(bar(kBarPReady), (uint32_t)(i & 1));
+                W34_PROF(3)
+                ok = ok && wait_all(bar(kBarFullV0 + (i & 1)), (uint32_t)((i >> 1) & 1));
+                W34_PROF(4)
+                if (!ok) { *abort_flag = 1u; break; }
+                tc_fence_after();
+                if (lane == 0) {
+#pragma unroll
+                    for (int ks = 0; ks < 4; ++ks) {
+                        const uint64_t a = desc_p + (uint64_t)(2 * ks);
+                        const uint64_t b = desc_v + (uint64_t)((i & 1) * (kTcKvBytes / 16) + (2048 / 16) * ks);
+                        tc_mma_f16(tmem + kTcColO, a, b, kIdescPv, (i > 0 || ks > 0) ? 1u : 0u);
+                    }
+                    tc_commit(bar(kBarPv));
+                    tc_commit(bar(kBarEmptyV0 + (i & 1)));
+                }
+                __syncwarp();
+            }
+        }
+    } else if (wid == 4 + kTcProducerWarps + 1) {
+        // ======================= copy issue: raw (page, head) runs of four pages per block ==============
         const uint8_t* k_head_base = (const uint8_t*)(uintptr_t)p.layout.k_base + (size_t)kv_head * p.layout.k_head_stride_bytes;
         const uint8_t* v_head_base = (const uint8_t*)(uintptr_t)p.layout.v_base + (size_t)kv_head * p.layout.v_head_stride_bytes;
-        auto issue = [&](int j) {   // producer thread 0: raw runs of block j
-            const uint32_t dst = raw;
-            const uint32_t fb = bar(kBarRawFull);
-            int npg = 0;
-            for (int pp = 0; pp < 4; ++pp) npg += (4 * (kb_lo + j) + pp <= pg_hi) ? 1 : 0;
-            mbar_expect_tx(fb, (uint32_t)npg * 2u * kTq4PageHeadBytes);
-            for (int pp = 0; pp < npg; ++pp) {
-                const int32_t page = blocks[4 * (kb_lo + j) + pp];
-                bulk_g2s(dst + (uint32_t)pp * kTq4PageHeadBytes,
-                         k_head_base + (size_t)page * p.layout.k_page_stride_bytes, kTq4PageHeadBytes, fb);
-                bulk_g2s(dst + (uint32_t)(4 + pp) * kTq4PageHeadBytes,
-                         v_head_base + (size_t)page * p.layout.v_page_stride_bytes, kTq4PageHeadBytes, fb);
+        // page ids of block j, read one block ahead of their use (a global load)
+        auto page_ids = [&](int j, int32_t (&ids)[4]) {
+#pragma unroll
+            for (int pp = 0; pp < 4; ++pp) {
+                const int pg = 4 * (kb_lo + j) + pp;
+                ids[pp] = (j < nblocks && pg <= pg_hi) ? blocks[pg] : -1;
             }
         };
-        // one (key, 128-half) of K or V: 16 code words -> 16 swizzled 16-byte chunks
-        auto dequant = [&](uint32_t rowp, uint32_t tile, bool key_ok, float* scale_out) {
-            uint32_t w[16];
-            uint32_t dbits;
-            if (half == 0) {
-                uint32_t x[17];
+        int32_t ids[4];
+        page_ids(0, ids);
+#pragma unroll 1
+        for (int j = 0; j < nblocks; ++j) {
+            if (aborted_any()) break;
+            // the staging buffer is free once every producer has taken block j - 1 into registers
+            if (j > 0 && !wait_all(bar(kBarRawFree0), (uint32_t)((j - 1) & 1))) { *abort_flag = 1u; break; }
+            if (lane == 0) {
+                const uint32_t fb = bar(kBarRawFull0);
+                int npg = 0;
 #pragma unroll
-                for (int j = 0; j < 17; ++j) x[j] = lds32(rowp + 4u * j);
-                dbits = x[0] & 0xffffu;
+                for (int pp = 0; pp < 4; ++pp) npg += (ids[pp] >= 0) ? 1 : 0;
+                mbar_expect_tx(fb, (uint32_t)npg * 2u * kTq4PageHeadBytes);
+                for (int pp = 0; pp < npg; ++pp) {
+                    const int32_t page = ids[pp];
+                    bulk_g2s(raw + (uint32_t)pp * kTq4PageHeadBytes,
+                             k_head_base + (size_t)page * p.layout.k_page_stride_bytes, kTq4PageHeadBytes, fb);
+                    bulk_g2s(raw + (uint32_t)(4 + pp) * kTq4PageHeadBytes,
+                             v_head_base + (size_t)page * p.layout.v_page_stride_bytes, kTq4PageHeadBytes, fb);
+                }
+            }
+            __syncwarp();
+            page_ids(j + 1, ids);
+        }
+    } else if (wid >= 4) {
+        // ======================= producers: dequantisation ==========================================
+        const int tp = tid - 128;                       // 0 .. kTcProducers - 1
+        const int key = tp & 63, qd = tp >> 6;       // qd: 64-dim block of the row
+        const int half = qd >> 1, sub = qd & 1;
+        // one (key, 64-dim block) of K or V: 8 code words -> 8 swizzled 16-byte chunks
+        auto load_words = [&](uint32_t rowp, uint32_t (&w)[8], uint32_t& dbits) {
+            if (half == 0) {      // codes of half 0 start at byte 2: read 9 words and shift by 16 bits
+                uint32_t x[9];
 #pragma unroll
-                for (int j = 0; j < 16; ++j) w[j] = __funnelshift_r(x[j], x[j + 1], 16);
+                for (int j = 0; j < 9; ++j) x[j] = lds32(rowp + 32u * sub + 4u * j);
+                dbits = lds_u16(rowp);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) w[j] = __funnelshift_r(x[j], x[j + 1], 16);
             } else {
                 dbits = lds_u16(rowp + 66u);
 #pragma unroll
-                for (int j = 0; j < 16; ++j) w[j] = lds32(rowp + 68u + 4u * j);
+                for (int j = 0; j < 8; ++j) w[j] = lds32(rowp + 68u + 32u * sub + 4u * j);
             }
+        };
+        auto convert = [&](const uint32_t (&w)[8], uint32_t dbits, uint32_t tile, bool key_ok) {
             if (!key_ok) dbits = 0u;      // a key no row can see may hold never-written bytes
-            // K tiles hold table values: the row scale (table factor divided out) multiplies the
-            // partial scores in fp32.  V tiles are scaled here: scale = hi + lo in fp16 and
-            // v = fma(e, hi, e * lo) is the product rounded once (to within 2^-22).
+            // scale (table factor divided out) = hi + lo in fp16; v = fma(e, hi, e * lo) is the
+            // product rounded once (to within 2^-22)
             const float dscaled = __half2float(__ushort_as_half((unsigned short)dbits)) * (1.0f / kLutScale);
             const __half d_hi = __float2half_rn(dscaled);
             const __half2 hi2 = __half2half2(d_hi);
             const __half2 lo2 = __float2half2_rn(dscaled - __half2float(d_hi));
-            if (scale_out != nullptr) *scale_out = dscaled;
             const uint32_t lut_lane = lut + 4u * (uint32_t)lane;
+            const uint32_t dst = tile + (uint32_t)qd * (kTcKeys * 128u) + (uint32_t)key * 128u;
 #pragma unroll
-            for (int c = 0; c < 16; ++c) {
+            for (int c = 0; c < 8; ++c) {
                 uint32_t h[4];
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
                     const uint32_t e = lds32(lut_lane + (__byte_perm(w[c], 0, 0x4440 + k) << 7));
-                    if (scale_out != nullptr) {
-                        h[k] = e;
-                    } else {
-                        const __half2 e2 = *reinterpret_cast<const __half2*>(&e);
-                        const __half2 v = __hfma2(e2, hi2, __hmul2(e2, lo2));
-                        h[k] = *reinterpret_cast<const uint32_t*>(&v);
-                    }
+                    const __half2 e2 = *reinterpret_cast<const __half2*>(&e);
+                    const __half2 v = __hfma2(e2, hi2, __hmul2(e2, lo2));
+                    h[k] = *reinterpret_cast<const uint32_t*>(&v);
                 }
-                const int db = 2 * half + (c >> 3), cc = c & 7;
-                sts128(tile + (uint32_t)db * (kTcKeys * 128u) + (uint32_t)key * 128u + (uint32_t)((cc ^ (key & 7)) << 4),
-                       h[0], h[1], h[2], h[3]);
+                sts128(dst + (uint32_t)((c ^ (key & 7)) << 4), h[0], h[1], h[2], h[3]);
             }
         };
 
-        if (tp == 0 && nblocks > 0) issue(0);
 #pragma unroll 1
         for (int j = 0; j < nblocks; ++j) {
             if (aborted_any()) break;
             const uint32_t par = (uint32_t)(j & 1);
-            if (!wait_all(bar(kBarRawFull), par)) { *abort_flag = 1u; break; }
+            W34_PROF(0)
+            if (!wait_all(bar(kBarRawFull0), par)) { *abort_flag = 1u; break; }
+            W34_PROF(1)
             const int pos = ((kb_lo + j) << 6) + key;
             const bool key_ok = pos >= kv_lo && pos <= kv_hi;
             const uint32_t rowp = raw + (uint32_t)key * kTq4RowBytes;
-            float* scales = kscale + (j & 1) * 128 + half * 64 + key;
-            if (j > 0 && !wait_all(bar(kBarEmptyK), par ^ 1u)) { *abort_flag = 1u; break; }
-            dequant(rowp, k_t, key_ok, scales);
+            uint32_t wk[8], wv[8], dk, dv;
+            load_words(rowp, wk, dk);
+            load_words(rowp + 4u * kTq4PageHeadBytes, wv, dv);
+            mbar_arrive(bar(kBarRawFree0));     // the next block's runs can be copied in
+            // K buffer j & 1 was last read by the score product of block j - 2
+            if (j > 1 && !wait_all(bar(kBarEmptyK0 + (j & 1)), (uint32_t)(((j - 2) >> 1) & 1))) { *abort_flag = 1u; break; }
+            W34_PROF(2)
+            convert(wk, dk, k_t + (uint32_t)(j & 1) * kTcKvBytes, key_ok);
             fence_proxy_async();
-            mbar_arrive(bar(kBarFullK));
-            if (j > 0 && !wait_all(bar(kBarEmptyV), par ^ 1u)) { *abort_flag = 1u; break; }
-            dequant(rowp + 4u * kTq4PageHeadBytes, v_t, key_ok, nullptr);
+            mbar_arrive(bar(kBarFullK0 + (j & 1)));
+            W34_PROF(3)
+            // V buffer j & 1 was last read by the output product of block j - 2
+            if (j > 1 && !wait_all(bar(kBarEmptyV0 + (j & 1)), (uint32_t)(((j - 2) >> 1) & 1))) { *abort_flag = 1u; break; }
+            W34_PROF(4)
+            convert(wv, dv, v_t + (uint32_t)(j & 1) * kTcKvBytes, key_ok);
             fence_proxy_async();
-            mbar_arrive(bar(kBarFullV));
-            // The next block's raw runs fly while this thread waits for the tiles to be consumed.
-            mbar_arrive(bar(kBarRawFree));
-            if (tp == 0 && j + 1 < nblocks) {   // the loop's next abort check ends the warp together
-                if (mbar_wait(bar(kBarRawFree), par)) issue(j + 1); else *abort_flag = 1u;
-            }
+            mbar_arrive(bar(kBarFullV0 + (j & 1)));
+            W34_PROF(5)
         }
     } else {
         // ======================= consumers: MMA issue, softmax, P, rescale =========================
         const int row = tid;
         const uint32_t lane_base = (uint32_t)(32 * wid) << 16;
         const uint32_t t_o = tmem + lane_base + kTcColO, t_s = tmem + lane_base + kTcColS;
-        constexpr uint32_t kIdescQk = tc_idesc(kTcRows, kTcKeys, 0);
-        constexpr uint32_t kIdescPv = tc_idesc(kTcRows, kHeadDim, 1);
         float m_ref = -1e30f;
-        auto issue_qk = [&](int j) {   // thread 0
-            if (!mbar_wait(bar(kBarFullK), (uint32_t)(j & 1))) { *abort_flag = 1u; return; }
-            tc_fence_after();
-#pragma unroll
-            for (int ks = 0; ks < 16; ++ks) {
-                const uint32_t off = (uint32_t)(ks >> 2);
-                const uint64_t a = tc_smem_desc(q_t + off * (kTcRows * 128u) + 32u * (ks & 3), 16u, 1024u);
-                const uint64_t b = tc_smem_desc(k_t + off * (kTcKeys * 128u) + 32u * (ks & 3), 16u, 1024u);
-                tc_mma_f16(tmem + kTcColS + 64u * (uint32_t)(ks >> 3), a, b, kIdescQk, (ks & 7) ? 1u : 0u);
-            }
-            tc_commit(bar(kBarS));
-            tc_commit(bar(kBarEmptyK));
-        };
-        if (tid == 0 && nblocks > 0) issue_qk(0);
 #pragma unroll 1
         for (int j = 0; j < nblocks; ++j) {
             if (aborted_any()) break;
             const uint32_t par = (uint32_t)(j & 1);
-            if (!wait_all(bar(kBarS), par)) { *abort_flag = 1u; break; }
+            W34_PROF(0)
+            if (!wait_all(bar(kBarS0 + (j & 1)), (uint32_t)((j >> 1) & 1))) { *abort_flag = 1u; break; }
+            W34_PROF(1)
             tc_fence_after();
+            const uint32_t t_sj = t_s + 64u * (uint32_t)(j & 1);
             float sv[64];
             {
-                const float4* ks0 = reinterpret_cast<const float4*>(kscale + (j & 1) * 128);
-                const float4* ks1 = ks0 + 16;
+                uint32_t r0[32], r1[32];
+                tc_ld32(r0, t_sj);
+                tc_ld32(r1, t_sj + 32u);
+                tc_wait_ld();
 #pragma unroll
-                for (int hh = 0; hh < 2; ++hh) {
-                    uint32_t r0[32], r1[32];
-                    tc_ld32(r0, t_s + 32u * hh);
-                    tc_ld32(r1, t_s + 64u + 32u * hh);
-                    tc_wait_ld();
-#pragma unroll
-                    for (int i4 = 0; i4 < 8; ++i4) {
-                        const float4 a = ks0[8 * hh + i4], b = ks1[8 * hh + i4];
-                        sv[32 * hh + 4 * i4 + 0] = a.x * __uint_as_float(r0[4 * i4 + 0]) + b.x * __uint_as_float(r1[4 * i4 + 0]);
-                        sv[32 * hh + 4 * i4 + 1] = a.y * __uint_as_float(r0[4 * i4 + 1]) + b.y * __uint_as_float(r1[4 * i4 + 1]);
-                        sv[32 * hh + 4 * i4 + 2] = a.z * __uint_as_float(r0[4 * i4 + 2]) + b.z * __uint_as_float(r1[4 * i4 + 2]);
-                        sv[32 * hh + 4 * i4 + 3] = a.w * __uint_as_float(r0[4 * i4 + 3]) + b.w * __uint_as_float(r1[4 * i4 + 3]);
-                    }
-                }
+                for (int i = 0; i < 32; ++i) { sv[i] = __uint_as_float(r0[i]); sv[32 + i] = __uint_as_float(r1[i]); }
             }
+            tc_fence_before();
+            mbar_arrive(bar(kBarSFree0 + (j & 1)));      // the scores are in registers
             const int kbase = (kb_lo + j) << 6;
             if (!(kbase >= rmin && kbase + 63 <= rmax)) {
 #pragma unroll
@@ -410,9 +526,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) tq4_attention_prefill_tc_kernel
                     if (!(pos >= rmin && pos <= rmax)) sv[i] = -1e30f;
                 }
             }
-            float mx = sv[0];
+            float mx4[4] = {sv[0], sv[1], sv[2], sv[3]};     // four independent chains
 #pragma unroll
-            for (int i = 1; i < 64; ++i) mx = fmaxf(mx, sv[i]);
+            for (int i = 4; i < 64; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], sv[i]);
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             // the reference maximum moves only when the true maximum ran ahead by more than the threshold
             const bool need = mx > m_ref + kTcRescaleThreshold;
             float alpha = 1.0f;
@@ -421,7 +538,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) tq4_attention_prefill_tc_kernel
                 m_ref = mx;
             }
             // P(j - 1) and O are in use until the previous output product has completed
+            W34_PROF(2)
             if (j > 0 && !wait_all(bar(kBarPv), par ^ 1u)) { *abort_flag = 1u; break; }
+            W34_PROF(3)
             tc_fence_after();
             if (j > 0 && __any_sync(0xffffffffu, need)) {
 #pragma unroll 1
@@ -435,42 +554,27 @@ __global__ void __launch_bounds__(kTcThreads, 1) tq4_attention_prefill_tc_kernel
                 }
                 tc_wait_st();
             }
-            float lsum = 0.0f;
+            W34_PROF(4)
+            float ls4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            const float m_use = (m_ref < -1e29f) ? 0.0f : m_ref;     // nothing visible yet: every P is 0
             const uint32_t prow = p_t + (uint32_t)row * 128u;
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
                 uint32_t h[4];
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
-                    const float a = sv[8 * c + 2 * k], b = sv[8 * c + 2 * k + 1];
-                    const float pa = (a > -1e29f) ? ex2(a - m_ref) : 0.0f;
-                    const float pb = (b > -1e29f) ? ex2(b - m_ref) : 0.0f;
-                    lsum += pa + pb;
+                    // masked scores are -1e30: ex2 gives exactly 0 against any finite reference
+                    const float pa = ex2(sv[8 * c + 2 * k] - m_use), pb = ex2(sv[8 * c + 2 * k + 1] - m_use);
+                    ls4[k] += pa + pb;
                     h[k] = pack_half2(pa, pb);
                 }
                 sts128(prow + (uint32_t)((c ^ (row & 7)) << 4), h[0], h[1], h[2], h[3]);
             }
-            l_run = l_run * alpha + lsum;
+            l_run = l_run * alpha + ((ls4[0] + ls4[1]) + (ls4[2] + ls4[3]));
             fence_proxy_async();
             tc_fence_before();
             mbar_arrive(bar(kBarPReady));
-            if (tid == 0) {   // a failed wait only raises the flag: the warp leaves the loop together
-                if (mbar_wait(bar(kBarPReady), par) && mbar_wait(bar(kBarFullV), par)) {
-                    tc_fence_after();
-#pragma unroll
-                    for (int ks = 0; ks < 4; ++ks) {
-                        const uint64_t a = tc_smem_desc(p_t + 32u * ks, 16u, 1024u);
-                        const uint64_t b = tc_smem_desc(v_t + 2048u * ks, kTcKeys * 128u, 1024u);
-                        tc_mma_f16(tmem + kTcColO, a, b, kIdescPv, (j > 0 || ks > 0) ? 1u : 0u);
-                    }
-                    tc_commit(bar(kBarPv));
-                    tc_commit(bar(kBarEmptyV));
-                    if (j + 1 < nblocks) issue_qk(j + 1);
-                } else {
-                    *abort_flag = 1u;
-                }
-            }
-            __syncwarp();
+            W34_PROF(5)
         }
         // the last output product
         if (nblocks > 0 && !aborted_any()) {
@@ -479,6 +583,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) tq4_attention_prefill_tc_kernel
         tc_fence_after();
     }
 
+#ifdef W34_TC_PROFILE
+    if (p.status != nullptr && lane == 0 && (wid == 0 || wid == 4 || wid == 4 + kTcProducerWarps)) {
+        long long* out = reinterpret_cast<long long*>(p.status) + 512 +
+                         ((size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 3 + (wid == 0 ? 0 : (wid == 4 ? 1 : 2))) * 8;
+        for (int i = 0; i < 8; ++i) out[i] = prof[i];
+        if (wid == 0) out[7] = nblocks;
+    }
+#endif
     // ---- epilogue: O / l -> staging -> inverse rotation -> global ---------------------------------
     // (staging aliases the Q / K / V tiles: every MMA that read them has completed)
     __syncthreads();
@@ -508,7 +620,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) tq4_attention_prefill_tc_kernel
         return;
     }
     if (!active) return;
-    for (int row = wid; row < rows_used; row += 8) {
+    for (int row = wid; row < rows_used; row += kTcWarps) {
         const int q_off = tok0 + row / p.gqa;
         const int q_head = kv_head * p.gqa + row % p.gqa;
         if (p.batch.valid_token_mask != nullptr && p.batch.valid_token_mask[g.q_start + q_off] == 0) continue;
