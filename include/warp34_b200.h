@@ -56,6 +56,9 @@ enum {
 /* Additive as well: chunked-prefill batches take the 64-row mma.sync kernel even where the
  * 128-row tcgen05 kernel applies (cross-checks, A/B measurements). */
 #define WARP34_B200_EXEC_FLAG_PREFILL_MMA_SYNC (1ull << 41)
+/* Additive: multi-token verify batches (more than 8 query rows per request and KV head) take the
+ * tcgen05 kernel, one 128-row CTA per request and KV head, instead of the split-KV team kernel. */
+#define WARP34_B200_EXEC_FLAG_TCGEN05_VERIFY (1ull << 42)
 
 /* ---- descriptors (reference: warp34_cuda.h:50-101) -------------------------- */
 typedef struct {

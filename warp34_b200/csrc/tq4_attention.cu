@@ -2062,12 +2062,13 @@ static int launch_attention(const warp34_exec* ex, const warp34_kv_layer_layout*
     const int gqa = num_q_heads / layout->local_kv_heads;
     // Prefill chunks (more query rows per request and kv head than one team item holds): 64-row
     // CTAs, no scratch.  Not for the partial-output mode, which is a decode-time feature.
+    const bool want_tc = (ex->flags & WARP34_B200_EXEC_FLAG_TCGEN05_VERIFY) != 0 && (long long)batch->max_q_len * gqa > 8;
     if (triple_out == nullptr && (ex->flags & WARP34_B200_EXEC_FLAG_PRECISE_ATTENTION) == 0 &&
         stream_layout_ok(layout) && batch->max_blocks_per_req > 0 && gqa <= kPfRows &&
-        (long long)batch->max_q_len * gqa > 24) {
+        ((long long)batch->max_q_len * gqa > 24 || want_tc)) {
         // 128-row tiles on tcgen05 once a request fills a tile; the 64-row mma.sync kernel below
         // for shorter chunks and when the caller asks for it.
-        if ((ex->flags & WARP34_B200_EXEC_FLAG_PREFILL_MMA_SYNC) == 0 && (long long)batch->max_q_len * gqa >= kTcRows &&
+        if ((ex->flags & WARP34_B200_EXEC_FLAG_PREFILL_MMA_SYNC) == 0 && ((long long)batch->max_q_len * gqa >= kTcRows || want_tc) &&
             (size_t)dev->smem_optin >= kTcSmemBytes) {
             PrefillTcParams tp;
             tp.layout = *layout;
