@@ -406,8 +406,12 @@ def main():
     ctx = synth.context_lengths(batch, lo, hi, seed + 1000 * rank)
     if sharded:
         ctx = ctx - q_len  # every shard plays "context + the query token" so all its keys are visible
-    wl = synth.PagedWorkload([int(c) for c in ctx], [q_len] * batch, hkv, seed=seed + 1000 * rank, device=dev)
-    step = kv.DecodeStep(wl.layer, wl.seqs, hq, max_q_len=q_len, scratch_bytes=64 << 20, device=dev)
+    speculative = q_len > 1      # MTP verify: the end-to-end loop commits accepted tokens and rolls back the rest
+    grow_pages = 56 if speculative else 0   # 200 steps x at most 4 tokens
+    wl = synth.PagedWorkload([int(c) for c in ctx], [q_len] * batch, hkv, seed=seed + 1000 * rank, device=dev,
+                             slack_pages=64 + batch * grow_pages)
+    step = kv.DecodeStep(wl.layer, wl.seqs, hq, max_q_len=q_len, scratch_bytes=64 << 20, device=dev,
+                         extra_blocks=grow_pages)
     triples = gathered = None
     if sharded:
         import torch.distributed as dist
@@ -492,14 +496,36 @@ def main():
         step.run(q_lens, lib=lib, attend=attend)
     barrier(world)
     e2e_steps = max(3, min(args.steps, 200))
-    e0.record()
-    for _ in range(e2e_steps):
-        step.run(q_lens, lib=lib, sync=True, attend=attend)
-    e1.record()
-    barrier(world)
-    e2e_ms = max_over_ranks(e0.elapsed_time(e1), world) / e2e_steps
+    rollback = None
+    if speculative:
+        # Each step: pages for 1 + 3 draft tokens, append + verify, then a seeded-random suffix of
+        # 0..3 draft tokens is rejected: the accepted ones are committed, pages that only held
+        # rejected tokens go back to the pool.  Sequences grow, so the bytes are summed per step.
+        spec = kv.SpeculativeBatch(wl.seqs)
+        rng = np.random.RandomState(seed + 99 + rank)
+        freed_pages, e2e_bytes, accepted_total = 0, 0.0, 0
+        e0.record()
+        for _ in range(e2e_steps):
+            spec.reserve_ahead(q_len)
+            e2e_bytes += float(sum(s.committed_len + q_len for s in wl.seqs)) * hkv * 264
+            step.run(q_lens, lib=lib, sync=True, attend=attend)
+            accepted = q_len - rng.randint(0, q_len, size=batch)
+            freed_pages += len(spec.commit_and_rollback(accepted))
+            accepted_total += int(accepted.sum())
+        e1.record()
+        barrier(world)
+        e2e_ms = max_over_ranks(e0.elapsed_time(e1), world) / e2e_steps
+        e2e_value = sum_over_ranks(e2e_bytes / e2e_steps, world) / (e2e_ms * 1e-3) / 1e9
+        rollback = {"accepted_tokens_per_step": accepted_total / e2e_steps, "pages_freed_per_step": freed_pages / e2e_steps}
+    else:
+        e0.record()
+        for _ in range(e2e_steps):
+            step.run(q_lens, lib=lib, sync=True, attend=attend)
+        e1.record()
+        barrier(world)
+        e2e_ms = max_over_ranks(e0.elapsed_time(e1), world) / e2e_steps
+        e2e_value = all_bytes / (e2e_ms * 1e-3) / 1e9
     sampler.stop_flag = True
-    e2e_value = all_bytes / (e2e_ms * 1e-3) / 1e9
 
     status = int(step.ex.scratch[:4].cpu().numpy().view(np.int32)[0]) if not reference else 0
 
@@ -541,7 +567,7 @@ def main():
                      "kernel": "tq4_attention_stream_kernel (+ plan and merge launches, timed together)",
                      "launch_ms": attn_ms, "traffic": None},
         "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": step.h2d_bytes,
-                "d2h_bytes_per_step": step.d2h_bytes},
+                "d2h_bytes_per_step": step.d2h_bytes, **({"speculative_rollback": rollback} if rollback else {})},
         "gpu_launches": 4 * args.steps,
         "clocks": clocks,
         "append_tokens_per_s": n_tok / (append_ms * 1e-3), "append_ms": append_ms,

@@ -134,6 +134,16 @@ int32_t w34_seq_set_committed(w34_seq* seq, int32_t committed_len);
  * or W34_ERR_CAPACITY. */
 int32_t w34_seq_rollback(w34_seq* seq, int32_t* freed, int32_t freed_capacity);
 
+/* One speculative step for a batch (mtp/propose.rs + radix.rs:1197-1245 per sequence): before the
+ * step every sequence gets pages for committed + extra_tokens positions (all-or-nothing over the
+ * batch when the sequences share one pool; returns pages added).  After the verify pass
+ * accepted[i] of the extra tokens are committed and the pages that only held rejected tokens are
+ * released; their ids go to `freed` (may be NULL with capacity 0 only if nothing is freed).
+ * Returns the number of pages freed. */
+int32_t w34_seqs_reserve_ahead(w34_seq* const* seqs, int32_t num_seqs, int32_t extra_tokens);
+int32_t w34_seqs_commit_and_rollback(w34_seq* const* seqs, const int32_t* accepted, int32_t num_seqs,
+                                     int32_t* freed, int32_t freed_capacity);
+
 int32_t w34_seq_committed_len(const w34_seq* seq);
 int32_t w34_seq_num_pages(const w34_seq* seq);
 int32_t w34_seq_protected_pages(const w34_seq* seq);

@@ -208,3 +208,29 @@ def test_step_metadata_slots_and_block_tables():
             tok += 1
     with pytest.raises(RuntimeError):
         build_step(seqs, ql, max_blocks_per_req=2, sm_scale=0.0625, device="cpu")
+
+
+def test_speculative_batch_commits_accepted_tokens_and_frees_rejected_pages(native_libs):
+    """1 + 3 draft tokens per step; a rejected suffix gives its pages back (radix.rs:1234-1245)."""
+    from warp34_b200 import kv
+    pool = kv.PagePool(64, 16)
+    seqs = [kv.Sequence(pool) for _ in range(3)]
+    for s, c in zip(seqs, (14, 16, 31)):
+        assert s.reserve(c) >= 0
+        s.commit(c)
+    spec = kv.SpeculativeBatch(seqs)
+    free0 = pool.free_count
+    added = spec.reserve_ahead(4)           # positions 14..17 | 16..19 | 31..34
+    assert added == 1 + 1 + 1
+    assert [s.num_pages for s in seqs] == [2, 2, 3]
+    freed = spec.commit_and_rollback([1, 4, 1])   # 15 | 20 | 32 committed tokens
+    assert [s.committed_len for s in seqs] == [15, 20, 32]
+    assert [s.num_pages for s in seqs] == [1, 2, 2]
+    assert len(freed) == 2 and pool.free_count == free0 - 1
+    # exhaustion is all-or-nothing over the batch
+    hog = kv.Sequence(pool)
+    assert hog.reserve(16 * (pool.free_count - 1)) >= 0
+    before = [s.num_pages for s in seqs]
+    with pytest.raises(RuntimeError):
+        spec.reserve_ahead(40)
+    assert [s.num_pages for s in seqs] == before

@@ -344,6 +344,42 @@ int32_t w34_seq_rollback(w34_seq* s, int32_t* freed, int32_t cap) {
     return n;
 }
 
+int32_t w34_seqs_reserve_ahead(w34_seq* const* seqs, int32_t num_seqs, int32_t extra_tokens) {
+    if (!seqs || num_seqs < 0 || extra_tokens < 0) return W34_ERR_INVALID;
+    // all-or-nothing over the batch: count first, then allocate
+    int64_t need_total = 0;
+    for (int32_t i = 0; i < num_seqs; ++i) {
+        const w34_seq* s = seqs[i];
+        if (!s) return W34_ERR_INVALID;
+        const int32_t B = s->pool->block_size;
+        const int32_t need = (s->committed + extra_tokens + B - 1) / B - (int32_t)s->pages.size();
+        if (need > 0) need_total += need;
+    }
+    if (num_seqs > 0 && need_total > seqs[0]->pool->available()) return W34_ERR_EXHAUSTED;
+    int32_t added = 0;
+    for (int32_t i = 0; i < num_seqs; ++i) {
+        const int32_t rc = w34_seq_reserve(seqs[i], seqs[i]->committed + extra_tokens);
+        if (rc < 0) return rc;      // sequences of different pools: the earlier ones keep their pages
+        added += rc;
+    }
+    return added;
+}
+
+int32_t w34_seqs_commit_and_rollback(w34_seq* const* seqs, const int32_t* accepted, int32_t num_seqs,
+                                     int32_t* freed, int32_t freed_capacity) {
+    if (!seqs || !accepted || num_seqs < 0 || freed_capacity < 0) return W34_ERR_INVALID;
+    int32_t total = 0;
+    for (int32_t i = 0; i < num_seqs; ++i) {
+        if (!seqs[i] || accepted[i] < 0) return W34_ERR_INVALID;
+        const int32_t rc = w34_seq_commit(seqs[i], accepted[i]);
+        if (rc < 0) return rc;
+        const int32_t n = w34_seq_rollback(seqs[i], freed ? freed + total : nullptr, freed_capacity - total);
+        if (n < 0) return n;
+        total += n;
+    }
+    return total;
+}
+
 int32_t w34_seq_committed_len(const w34_seq* s) { return s ? s->committed : 0; }
 int32_t w34_seq_num_pages(const w34_seq* s) { return s ? (int32_t)s->pages.size() : 0; }
 int32_t w34_seq_protected_pages(const w34_seq* s) { return s ? s->protected_pages : 0; }

@@ -122,6 +122,8 @@ _HOST_SIGS = {
     "w34_seq_commit": (C.c_int32, [C.c_void_p, C.c_int32]),
     "w34_seq_set_committed": (C.c_int32, [C.c_void_p, C.c_int32]),
     "w34_seq_rollback": (C.c_int32, [C.c_void_p, _P(C.c_int32), C.c_int32]),
+    "w34_seqs_reserve_ahead": (C.c_int32, [_P(C.c_void_p), C.c_int32, C.c_int32]),
+    "w34_seqs_commit_and_rollback": (C.c_int32, [_P(C.c_void_p), _P(C.c_int32), C.c_int32, _P(C.c_int32), C.c_int32]),
     "w34_seq_committed_len": (C.c_int32, [C.c_void_p]),
     "w34_seq_num_pages": (C.c_int32, [C.c_void_p]),
     "w34_seq_protected_pages": (C.c_int32, [C.c_void_p]),

@@ -184,6 +184,34 @@ class PrefixCache:
         return self._h.w34_radix_sanity_check(self.handle)
 
 
+class SpeculativeBatch:
+    """The page bookkeeping of one speculative (draft + verify) step for a fixed set of sequences:
+    reserve pages for `extra` tokens each, and after the verify pass commit the accepted tokens and
+    hand back the pages that only held rejected ones (mtp/propose.rs, radix.rs:1197-1245)."""
+
+    def __init__(self, seqs):
+        self.seqs = list(seqs)
+        n = len(self.seqs)
+        self._handles = (C.c_void_p * n)(*[s.handle for s in self.seqs])
+        self._accepted = (C.c_int32 * n)()
+        self._freed = (C.c_int32 * max(4 * n, 1))()
+        self._h = ffi.host()
+
+    def reserve_ahead(self, extra_tokens):
+        rc = self._h.w34_seqs_reserve_ahead(self._handles, len(self.seqs), extra_tokens)
+        if rc < 0:
+            raise RuntimeError(f"w34_seqs_reserve_ahead: {rc}")
+        return rc
+
+    def commit_and_rollback(self, accepted):
+        n = len(self.seqs)
+        self._accepted[:] = [int(a) for a in accepted]
+        rc = self._h.w34_seqs_commit_and_rollback(self._handles, self._accepted, n, self._freed, len(self._freed))
+        if rc < 0:
+            raise RuntimeError(f"w34_seqs_commit_and_rollback: {rc}")
+        return list(self._freed[:rc])
+
+
 def resolve_layer(policy, ordinal, num_layers, supports_fp8=False):
     out = (C.c_int32 * 4)()
     rc = ffi.host().w34_kv_policy_resolve_layer(policy, ordinal, num_layers, int(supports_fp8), out)
@@ -433,11 +461,11 @@ class DecodeStep:
     """The call a user of this path makes once per model step and layer: new K/V rows and Q in
     HOST memory in, attention output in HOST memory out (append then attend, forward.rs:1141-1188)."""
 
-    def __init__(self, layer, seqs, num_q_heads, max_q_len=1, scratch_bytes=64 << 20, device="cuda"):
+    def __init__(self, layer, seqs, num_q_heads, max_q_len=1, scratch_bytes=64 << 20, device="cuda", extra_blocks=0):
         self.layer, self.seqs, self.hq = layer, seqs, num_q_heads
         hkv = layer.layout.local_kv_heads
         n_tok = len(seqs) * max_q_len
-        max_blocks = max(s.num_pages for s in seqs)
+        max_blocks = max(s.num_pages for s in seqs) + extra_blocks   # room for sequences that grow
         self.io = StepIo(len(seqs), n_tok, max_blocks, device=device)
         self.ex = Executor(scratch_bytes, device=device)
         pin = lambda *shape: torch.zeros(*shape, dtype=torch.float16).pin_memory()  # noqa: E731
