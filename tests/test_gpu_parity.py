@@ -515,3 +515,102 @@ def test_mixed_prefill_and_decode_batch_with_masks(env):
         want = _oracle_attention(wl, b, q, hq)
         ok, msg = tensor_core_parity(f16(bits[live]), want[live], vs[live])
         assert ok, (window, msg)
+
+
+def _logical_rows(layer, seq, n_tokens, hkv):
+    """K and V rows of a sequence in position order, read through its block table."""
+    lay = layer.layout
+    kp, vp = layer.k.cpu().numpy(), layer.v.cpu().numpy()
+    pages = seq.pages
+    ks, vs = [], []
+    for pos in range(n_tokens):
+        page, off = pages[pos // 16], pos % 16
+        for h in range(hkv):
+            o = page * lay.k_page_stride_bytes + h * lay.k_head_stride_bytes + off * lay.k_token_stride_bytes
+            ks.append(kp[o:o + 132])
+            o = page * lay.v_page_stride_bytes + h * lay.v_head_stride_bytes + off * lay.v_token_stride_bytes
+            vs.append(vp[o:o + 132])
+    return np.stack(ks), np.stack(vs)
+
+
+def test_speculative_steps_with_rollback_leave_the_cache_as_if_only_accepted_tokens_were_appended(env):
+    """Three verify steps of 1 + 3 draft tokens with rejected suffixes (pages truncated and reused):
+    the cache then holds, position by position, the bytes of a plain append of the accepted tokens,
+    and the next verify pass agrees with the CPU oracle."""
+    kv, synth = env["kv"], env["synth"]
+    hq, hkv, ql = 24, 4, 4
+    ctx = [13, 30, 64]
+    wl = synth.PagedWorkload(ctx, [ql] * 3, hkv, seed=41, slack_pages=16)
+    kept = wl.fill_context(env["ex"], 41, keep=True)
+    spec = kv.SpeculativeBatch(wl.seqs)
+    accepted_rows = [[kept[i][0], kept[i][1]] for i in range(3)]       # fp16 K, V of every accepted token
+    plan = [[2, 4, 1], [1, 3, 4], [4, 1, 2]]
+    for step_i, accepted in enumerate(plan):
+        spec.reserve_ahead(ql)
+        k, v = synth.make_kv(3 * ql, hkv, 500 + step_i)
+        b = wl.step(q_lens=[ql] * 3)
+        kv.kv_cache_write(env["ex"], wl.layer, b, k.cuda(), v.cuda())
+        torch.cuda.synchronize()
+        for i, a in enumerate(accepted):
+            accepted_rows[i][0] = torch.cat([accepted_rows[i][0], k[i * ql:i * ql + a]])
+            accepted_rows[i][1] = torch.cat([accepted_rows[i][1], v[i * ql:i * ql + a]])
+        spec.commit_and_rollback(accepted)
+    lens = [c + sum(p[i] for p in plan) for i, c in enumerate(ctx)]
+    assert [s.committed_len for s in wl.seqs] == lens
+    assert [s.num_pages for s in wl.seqs] == [(n + 15) // 16 for n in lens]
+    # reference cache: the accepted tokens appended in one go
+    ref = synth.PagedWorkload([0] * 3, lens, hkv, seed=77)
+    kk = torch.cat([r[0] for r in accepted_rows]).cuda()
+    vv = torch.cat([r[1] for r in accepted_rows]).cuda()
+    kv.kv_cache_write(env["ex"], ref.layer, ref.step(), kk, vv)
+    torch.cuda.synchronize()
+    for i in range(3):
+        a_k, a_v = _logical_rows(wl.layer, wl.seqs[i], lens[i], hkv)
+        b_k, b_v = _logical_rows(ref.layer, ref.seqs[i], lens[i], hkv)
+        assert (a_k == b_k).all() and (a_v == b_v).all()
+    # one more verify pass over the rolled-back cache
+    spec.reserve_ahead(ql)
+    k, v = synth.make_kv(3 * ql, hkv, 900)
+    q = synth.make_q(3 * ql, hq, 900)
+    b = wl.step(q_lens=[ql] * 3)
+    kv.kv_cache_write(env["ex"], wl.layer, b, k.cuda(), v.cuda())
+    out = torch.zeros(3 * ql, hq, 256, dtype=torch.float16, device="cuda")
+    kv.paged_attention(env["ex"], wl.layer, b, q.cuda(), out, hq)
+    torch.cuda.synchronize()
+    want = _oracle_attention(wl, b, q, hq)
+    v_all = torch.cat([torch.cat([accepted_rows[i][1], v[i * ql:(i + 1) * ql]]) for i in range(3)]).numpy()
+    bounds = np.concatenate([[0], np.cumsum([n + ql for n in lens])])
+    vs = channel_scale(v_all, [(int(bounds[i]), int(bounds[i + 1])) for i in range(3)], [ql] * 3, hq, hkv)
+    ok, msg = tensor_core_parity(out.float().cpu().numpy(), want, vs)
+    assert ok, msg
+
+
+@pytest.mark.parametrize("mode", ["default", "mma_sync", "short_chunk", "verify_flag"])
+def test_prefill_dispatch_paths_agree_with_the_oracle(env, mode):
+    """The tcgen05 kernel (default for chunks that fill a 128-row tile), the 64-row mma.sync kernel
+    (by flag, and by itself for 25..127 rows) and the tcgen05 kernel on a verify batch."""
+    kv, synth, ffi = env["kv"], env["synth"], env["ffi"]
+    hkv = 4
+    hq, q_len, ctx_before = {"default": (16, 200, 333), "mma_sync": (16, 200, 333),
+                             "short_chunk": (16, 20, 100), "verify_flag": (24, 4, 1500)}[mode]
+    flags = {"default": 0, "mma_sync": ffi.EXEC_FLAG_PREFILL_MMA_SYNC, "short_chunk": 0,
+             "verify_flag": ffi.EXEC_FLAG_TCGEN05_VERIFY}[mode]
+    total = ctx_before + q_len
+    wl = synth.PagedWorkload([0, 0], [total, total // 2 + q_len], hkv, seed=610, fill=0xFF)
+    lens = [total, total // 2 + q_len]
+    k, v = synth.make_kv(sum(lens), hkv, 610)
+    kv.kv_cache_write(env["ex"], wl.layer, wl.step(), k.cuda(), v.cuda())
+    for s, n in zip(wl.seqs, lens):
+        s.commit(n - q_len)
+    b = wl.step(q_lens=[q_len, q_len])
+    q = synth.make_q(2 * q_len, hq, 611)
+    ex = kv.Executor(8 << 20)
+    ex.ex.flags = flags
+    out = torch.full((2 * q_len, hq, 256), 5.0, dtype=torch.float16, device="cuda")
+    kv.paged_attention(ex, wl.layer, b, q.cuda(), out, hq)
+    torch.cuda.synchronize()
+    assert int(ex.scratch[:4].cpu().numpy().view(np.int32)[0]) == 0
+    want = _oracle_attention(wl, b, q, hq)
+    vs = channel_scale(v.numpy(), [(0, lens[0]), (lens[0], lens[0] + lens[1])], [q_len, q_len], hq, hkv)
+    ok, msg = tensor_core_parity(out.float().cpu().numpy(), want, vs)
+    assert ok, (mode, msg)

@@ -448,6 +448,10 @@ extern "C" int warp34_paged_attention_bf16(const warp34_exec* ex, const warp34_k
     w34::tq4_attention_plan_kernel<<<1, 32, 0, st>>>(p);
     w34::bf16kv_attention_stream_kernel<<<grid, w34::kBfWarps * 32, p.smem_bytes, st>>>(p);
     const long long rows = (long long)batch->total_tokens * num_q_heads;
-    w34::tq4_attention_merge_kernel<false><<<(unsigned)rows, 128, 0, st>>>(p);
+    if (rows * 4 < (long long)grid * w34::kBfWarps / 8) {
+        w34::tq4_attention_merge_kernel<false, 32><<<(unsigned)rows, 1024, 0, st>>>(p);
+    } else {
+        w34::tq4_attention_merge_kernel<false, 4><<<(unsigned)rows, 128, 0, st>>>(p);
+    }
     return (int)cudaGetLastError();
 }

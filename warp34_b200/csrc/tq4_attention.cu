@@ -342,6 +342,14 @@ __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+// First MMA of a chain: the accumulator input is the zero register, no clearing moves.
+__device__ __forceinline__ void mma16816_zero(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                              uint32_t b0, uint32_t b1) {
+    asm(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
+}
 __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -660,6 +668,8 @@ __global__ void __launch_bounds__(W34_WARPS * 32, 1) tq4_attention_stream_kernel
                     const uint32_t ql = qlo[2 * s8 + hk];
                     if (W34_QK_CHAINS == 4 && !W34_SPLIT_Q && hk == 1) {
                         mma16816(sl[half], a0, a1, a2, a3, qb[2 * s8 + hk][0], qb[2 * s8 + hk][1]);
+                    } else if ((s8 & 3) == 0 && hk == 0) {
+                        mma16816_zero(sa[half], a0, a1, a2, a3, qb[2 * s8 + hk][0], qb[2 * s8 + hk][1]);
                     } else {
                         mma16816(sa[half], a0, a1, a2, a3, qb[2 * s8 + hk][0], qb[2 * s8 + hk][1]);
                     }
@@ -1742,15 +1752,15 @@ namespace w34 {
 // pre-scaled scores) and l.
 constexpr int kRowTripleFloats = kHeadDim + 2;
 
-// One block of four warps per (token, q head): warp w combines the partials w, w+4, ... of the
-// row with an online softmax merge, the four results are combined through shared memory, then
+// One block of MW warps per (token, q head): warp w combines the partials w, w + MW, ... of the
+// row with an online softmax merge, the MW results are combined through shared memory, then
 // either normalise + inverse rotation + fp16 store, or (PARTIAL_OUT) store the merged
-// (acc, m, l) triple for a cross-shard merge.  A long single sequence has hundreds of partials
-// per row and only a few rows, hence the split over warps.
-template <bool PARTIAL_OUT>
-__global__ void __launch_bounds__(128) tq4_attention_merge_kernel(const StreamParams p) {
-    __shared__ float s_acc[4][kHeadDim];
-    __shared__ float s_m[4], s_l[4];
+// (acc, m, l) triple for a cross-shard merge.  MW = 4 for batches; a long single sequence has
+// hundreds of partials per row and only a few rows, for which MW = 32.
+template <bool PARTIAL_OUT, int MW>
+__global__ void __launch_bounds__(MW * 32) tq4_attention_merge_kernel(const StreamParams p) {
+    __shared__ float s_acc[MW][kHeadDim];
+    __shared__ float s_m[MW], s_l[MW];
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const long long row_ll = blockIdx.x;
     const int tok = (int)(row_ll / p.num_q_heads), q_head = (int)(row_ll % p.num_q_heads);
@@ -1784,10 +1794,10 @@ __global__ void __launch_bounds__(128) tq4_attention_merge_kernel(const StreamPa
         const int w_first = us / per, w_last = (us + npages - 1) / per;
         const float* base = partials + (size_t)(w_first + item_prefix[r] + item) * part_floats;
         const int nparts = w_last - w_first + 1;
-        // this warp's partials: wid, wid + 4, ...; lanes fetch up to 32 (m, l) pairs at once so
+        // this warp's partials: wid, wid + MW, ...; lanes fetch up to 32 (m, l) pairs at once so
         // that the accumulation runs over independent loads
-        for (int c0 = wid; c0 < nparts; c0 += 128) {
-            const int mine = c0 + 4 * lane;
+        for (int c0 = wid; c0 < nparts; c0 += 32 * MW) {
+            const int mine = c0 + MW * lane;
             float m_s = -1e30f, l_s = 0.0f;
             if (mine < nparts) {
                 const float* ps = base + (size_t)mine * part_floats + rpg * kHeadDim;
@@ -1808,28 +1818,30 @@ __global__ void __launch_bounds__(128) tq4_attention_merge_kernel(const StreamPa
 #pragma unroll
             for (int d = 16; d > 0; d >>= 1) lw += __shfl_xor_sync(0xffffffffu, lw, d);
             l_tot += lw;
-            const int n_here = min(32, (nparts - c0 + 3) / 4);
+            const int n_here = min(32, (nparts - c0 + MW - 1) / MW);
 #pragma unroll 4
             for (int sidx = 0; sidx < n_here; ++sidx) {
                 const float wgt = __shfl_sync(0xffffffffu, w_s, sidx);
-                const float* pa = base + (size_t)(c0 + 4 * sidx) * part_floats + row8 * kHeadDim;
+                const float* pa = base + (size_t)(c0 + MW * sidx) * part_floats + row8 * kHeadDim;
 #pragma unroll
                 for (int j = 0; j < 8; ++j) acc[j] += pa[lane + 32 * j] * wgt;
             }
         }
     }
-    // combine the four warps
+    // combine the warps
 #pragma unroll
     for (int j = 0; j < 8; ++j) s_acc[wid][lane + 32 * j] = acc[j];
     if (lane == 0) { s_m[wid] = m_tot; s_l[wid] = l_tot; }
     __syncthreads();
     if (wid != 0) return;
-    m_tot = fmaxf(fmaxf(s_m[0], s_m[1]), fmaxf(s_m[2], s_m[3]));
+    m_tot = s_m[0];
+#pragma unroll
+    for (int w = 1; w < MW; ++w) m_tot = fmaxf(m_tot, s_m[w]);
     l_tot = 0.0f;
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
-#pragma unroll
-    for (int w = 0; w < 4; ++w) {
+#pragma unroll 4
+    for (int w = 0; w < MW; ++w) {
         const float wgt = (s_l[w] > 0.0f) ? ex2(s_m[w] - m_tot) : 0.0f;
         l_tot += s_l[w] * wgt;
 #pragma unroll
@@ -2167,10 +2179,14 @@ static int launch_attention(const warp34_exec* ex, const warp34_kv_layer_layout*
         tq4_attention_team_kernel<3><<<grid, kTeams * kTeamWarps * 32, smem, st>>>(p);
     }
     const long long rows = (long long)batch->total_tokens * num_q_heads;
+    // Few rows with hundreds of partials each (one long sequence): 32 warps per row instead of 4.
+    const bool wide = rows * 4 < (long long)grid * workers_per_cta / 8;
     if (triple_out != nullptr) {
-        tq4_attention_merge_kernel<true><<<(unsigned)rows, 128, 0, st>>>(p);
+        if (wide) tq4_attention_merge_kernel<true, 32><<<(unsigned)rows, 1024, 0, st>>>(p);
+        else tq4_attention_merge_kernel<true, 4><<<(unsigned)rows, 128, 0, st>>>(p);
     } else {
-        tq4_attention_merge_kernel<false><<<(unsigned)rows, 128, 0, st>>>(p);
+        if (wide) tq4_attention_merge_kernel<false, 32><<<(unsigned)rows, 1024, 0, st>>>(p);
+        else tq4_attention_merge_kernel<false, 4><<<(unsigned)rows, 128, 0, st>>>(p);
     }
     return (int)cudaGetLastError();
 }
