@@ -587,8 +587,8 @@ def test_speculative_steps_with_rollback_leave_the_cache_as_if_only_accepted_tok
 
 @pytest.mark.parametrize("mode", ["default", "mma_sync", "short_chunk", "verify_flag"])
 def test_prefill_dispatch_paths_agree_with_the_oracle(env, mode):
-    """The tcgen05 kernel (default for chunks that fill a 128-row tile), the 64-row mma.sync kernel
-    (by flag, and by itself for 25..127 rows) and the tcgen05 kernel on a verify batch."""
+    """The tcgen05 kernel (default, also with partly filled 128-row tiles), the 64-row mma.sync kernel
+    (by flag) and the tcgen05 kernel on a verify batch."""
     kv, synth, ffi = env["kv"], env["synth"], env["ffi"]
     hkv = 4
     hq, q_len, ctx_before = {"default": (16, 200, 333), "mma_sync": (16, 200, 333),

@@ -2078,9 +2078,9 @@ static int launch_attention(const warp34_exec* ex, const warp34_kv_layer_layout*
     if (triple_out == nullptr && (ex->flags & WARP34_B200_EXEC_FLAG_PRECISE_ATTENTION) == 0 &&
         stream_layout_ok(layout) && batch->max_blocks_per_req > 0 && gqa <= kPfRows &&
         ((long long)batch->max_q_len * gqa > 24 || want_tc)) {
-        // 128-row tiles on tcgen05 once a request fills a tile; the 64-row mma.sync kernel below
-        // for shorter chunks and when the caller asks for it.
-        if ((ex->flags & WARP34_B200_EXEC_FLAG_PREFILL_MMA_SYNC) == 0 && ((long long)batch->max_q_len * gqa >= kTcRows || want_tc) &&
+        // 128-row tiles on tcgen05 (a partly filled tile still beats the 64-row mma.sync kernel
+        // below, which stays for callers that ask for it and for devices without the shared memory).
+        if ((ex->flags & WARP34_B200_EXEC_FLAG_PREFILL_MMA_SYNC) == 0 &&
             (size_t)dev->smem_optin >= kTcSmemBytes) {
             PrefillTcParams tp;
             tp.layout = *layout;
