@@ -34,7 +34,8 @@
 // (scale = hi + lo in fp16, v = fma(e, hi, e * lo)).  (A scale, or P times a scale, rounded to
 // fp16 per 128-half puts a different relative error on the two halves of a row; through the
 // inverse rotation that difference moves a fraction of channel c ^ 128 into channel c, which is
-// visible next to a x20 outlier channel.  Element-wise rounding has no such coherent part.)
+// visible next to a x20 outlier channel.)  The V scale is dithered per coordinate, see
+// kVScaleDither; K needs none (its rounding errors meet a different query value at every coordinate).
 #pragma once
 
 namespace w34 {
@@ -66,6 +67,31 @@ constexpr uint32_t kTcTmemCols = 512;
 constexpr uint32_t kTcColO = 0, kTcColS = 256;   // S: two buffers of 64 columns
 constexpr uint32_t kTcColQ = 384;                // Q' as the A operand: 256 fp16 per row = 128 columns
 constexpr float kTcRescaleThreshold = 8.0f;      // log2 units: P stays below 2^8
+
+// Dither of the V scale, one half2 per pair of rotated coordinates (128 per row): uniform in
+// +-0.5 x 2^-11, fixed.  Rounding centroid x scale to fp16 gives the same error to every
+// coordinate that holds the same code; for a row dominated by a few outlier channels the codes
+// follow the sign patterns of those channels' Hadamard rows, and the inverse rotation then
+// collects that error on the channels whose index is an XOR of outlier channel indices (up to
+// 1e-2 there).  Perturbing the scale per coordinate by less than the rounding step makes the
+// rounding errors independent of the codes; they then add up incoherently (about 1e-3).
+__constant__ uint32_t kVScaleDither[128] = {
+    0x86800500u, 0x878f83ccu, 0x8b0a0b6cu, 0x06c7086eu, 0x0b5c881bu, 0x0b0e8945u, 0x071f89b6u, 0x8a800892u,
+    0x8731012fu, 0x89e80215u, 0x87d388d6u, 0x093806e6u, 0x09300aebu, 0x06268b99u, 0x01020a1du, 0x046a84aeu,
+    0x09988a15u, 0x059c0753u, 0x096f04adu, 0x84978851u, 0x034c04a2u, 0x095f88cbu, 0x00bb80cbu, 0x8473042bu,
+    0x80d20039u, 0x0a6505fbu, 0x0aad8b40u, 0x816b0496u, 0x058701b2u, 0x0b340bbfu, 0x0a6c8a79u, 0x005c0b72u,
+    0x017b89deu, 0x08928a7du, 0x83930734u, 0x06c384beu, 0x060a81feu, 0x0b200ad2u, 0x0b85830cu, 0x8a4d0a8bu,
+    0x83660225u, 0x07660206u, 0x8ba20a9cu, 0x04c583e9u, 0x0af880c0u, 0x05f78642u, 0x887c88d8u, 0x8ad18b86u,
+    0x09120910u, 0x8a758b9fu, 0x822f882bu, 0x86250b71u, 0x898288c8u, 0x02618ae5u, 0x03168192u, 0x05de8487u,
+    0x8b5a880fu, 0x83a80835u, 0x8b708447u, 0x0a3489a3u, 0x00db0090u, 0x88da0134u, 0x86e48a86u, 0x09c608e6u,
+    0x095a8866u, 0x06360ae6u, 0x841081eeu, 0x89868941u, 0x0b148258u, 0x861f0986u, 0x876f0280u, 0x0b6a0506u,
+    0x02b08a38u, 0x8ab900b6u, 0x81ea0a2bu, 0x898882b5u, 0x0b30831du, 0x887982d9u, 0x0ae98851u, 0x884009c4u,
+    0x8b4304cdu, 0x06390147u, 0x09e38298u, 0x8366888cu, 0x078f8488u, 0x8b4c091du, 0x07248965u, 0x089d814bu,
+    0x865c059au, 0x034700d9u, 0x842301aeu, 0x0b27039bu, 0x88fc0a8bu, 0x882901f8u, 0x090f04b7u, 0x03640932u,
+    0x0a870a23u, 0x80558889u, 0x83c08862u, 0x81d38a8cu, 0x89b709efu, 0x023089cdu, 0x05378b6au, 0x82df00a9u,
+    0x88bd80d4u, 0x02af8a46u, 0x856c89f9u, 0x83af08b8u, 0x08718b8fu, 0x082088bbu, 0x87bd88cbu, 0x870a8001u,
+    0x0a478713u, 0x021a817bu, 0x01230300u, 0x84a583beu, 0x87880a9cu, 0x09148713u, 0x073b0786u, 0x82cb0424u,
+    0x8a858588u, 0x07d00867u, 0x0bc80b32u, 0x0aba8410u, 0x89d20991u, 0x060f8608u, 0x805e0a3au, 0x8a9f8b2au};
 
 // barrier slots (8 bytes each)
 enum { kBarFullK0 = 0, kBarFullK1, kBarFullV0, kBarFullV1, kBarEmptyK0, kBarEmptyK1, kBarEmptyV0, kBarEmptyV1,
@@ -439,7 +465,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) tq4_attention_prefill_tc_kernel
                 for (int j = 0; j < 8; ++j) w[j] = lds32(rowp + 68u + 32u * sub + 4u * j);
             }
         };
-        auto convert = [&](const uint32_t (&w)[8], uint32_t dbits, uint32_t tile, bool key_ok) {
+        uint32_t dith[32];          // this thread's 64 coordinates = 32 pairs
+#pragma unroll
+        for (int i = 0; i < 32; ++i) dith[i] = kVScaleDither[32 * qd + i];
+        auto convert = [&](const uint32_t (&w)[8], uint32_t dbits, uint32_t tile, bool key_ok, bool is_v) {
             if (!key_ok) dbits = 0u;      // a key no row can see may hold never-written bytes
             // scale (table factor divided out) = hi + lo in fp16; v = fma(e, hi, e * lo) is the
             // product rounded once (to within 2^-22)
@@ -456,7 +485,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) tq4_attention_prefill_tc_kernel
                 for (int k = 0; k < 4; ++k) {
                     const uint32_t e = lds32(lut_lane + (__byte_perm(w[c], 0, 0x4440 + k) << 7));
                     const __half2 e2 = *reinterpret_cast<const __half2*>(&e);
-                    const __half2 v = __hfma2(e2, hi2, __hmul2(e2, lo2));
+                    // V: the low part of the scale carries the per-coordinate dither
+                    const __half2 lo_j = is_v ? __hfma2(hi2, *reinterpret_cast<const __half2*>(&dith[4 * c + k]), lo2) : lo2;
+                    const __half2 v = __hfma2(e2, hi2, __hmul2(e2, lo_j));
                     h[k] = *reinterpret_cast<const uint32_t*>(&v);
                 }
                 sts128(dst + (uint32_t)((c ^ (key & 7)) << 4), h[0], h[1], h[2], h[3]);
@@ -480,14 +511,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) tq4_attention_prefill_tc_kernel
             // K buffer j & 1 was last read by the score product of block j - 2
             if (j > 1 && !wait_all(bar(kBarEmptyK0 + (j & 1)), (uint32_t)(((j - 2) >> 1) & 1))) { *abort_flag = 1u; break; }
             W34_PROF(2)
-            convert(wk, dk, k_t + (uint32_t)(j & 1) * kTcKvBytes, key_ok);
+            convert(wk, dk, k_t + (uint32_t)(j & 1) * kTcKvBytes, key_ok, false);
             fence_proxy_async();
             mbar_arrive(bar(kBarFullK0 + (j & 1)));
             W34_PROF(3)
             // V buffer j & 1 was last read by the output product of block j - 2
             if (j > 1 && !wait_all(bar(kBarEmptyV0 + (j & 1)), (uint32_t)(((j - 2) >> 1) & 1))) { *abort_flag = 1u; break; }
             W34_PROF(4)
-            convert(wv, dv, v_t + (uint32_t)(j & 1) * kTcKvBytes, key_ok);
+            convert(wv, dv, v_t + (uint32_t)(j & 1) * kTcKvBytes, key_ok, true);
             fence_proxy_async();
             mbar_arrive(bar(kBarFullV0 + (j & 1)));
             W34_PROF(5)
