@@ -173,8 +173,9 @@ def host_step_batch(kv, step, batch, n_tok):
     """The step's metadata as a host-side StepBatch (keeps the arrays alive for the oracle)."""
     io = step.io
     o = io._offs
+    # arena order: query_start_loc | context_lens_before | seq_lens_after | write_slot_mapping | block_tables
     return kv.StepBatch(io._np[o[0]:o[0] + batch + 1], io._np[o[1]:o[1] + batch], io._np[o[2]:o[2] + batch],
-                        io._np[o[3]:o[3] + batch * io.max_blocks].reshape(batch, -1), io._np[o[4]:o[4] + n_tok],
+                        io._np[o[4]:o[4] + batch * io.max_blocks].reshape(batch, -1), io._np[o[3]:o[3] + n_tok],
                         io.max_blocks, 1.0 / 16.0, device="cpu")
 
 
@@ -373,7 +374,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=300)
-    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="cfg1_batched_decode")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -497,6 +498,7 @@ def main():
     barrier(world)
     e2e_steps = max(3, min(args.steps, 200))
     rollback = None
+    h2d_before = step.h2d_bytes_total
     if speculative:
         # Each step: pages for 1 + 3 draft tokens, append + verify, then a seeded-random suffix of
         # 0..3 draft tokens is rejected: the accepted ones are committed, pages that only held
@@ -566,7 +568,7 @@ def main():
                      "peak_kind": f"of {peak_kind}", "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,
                      "kernel": "tq4_attention_stream_kernel (+ plan and merge launches, timed together)",
                      "launch_ms": attn_ms, "traffic": None},
-        "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": step.h2d_bytes,
+        "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": (step.h2d_bytes_total - h2d_before) / e2e_steps,
                 "d2h_bytes_per_step": step.d2h_bytes, **({"speculative_rollback": rollback} if rollback else {})},
         "gpu_launches": 4 * args.steps,
         "clocks": clocks,

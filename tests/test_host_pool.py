@@ -234,3 +234,33 @@ def test_speculative_batch_commits_accepted_tokens_and_frees_rejected_pages(nati
     with pytest.raises(RuntimeError):
         spec.reserve_ahead(40)
     assert [s.num_pages for s in seqs] == before
+
+
+def test_step_io_uploads_only_changed_block_table_suffixes(native_libs):
+    """Lengths and slots travel every step; of the block tables only the row suffixes that changed
+    (graph_io.rs:109-195).  Runs on the CPU: host and "device" arenas are both host tensors."""
+    from warp34_b200 import kv
+    pool = kv.PagePool(256, 16)
+    seqs = [kv.Sequence(pool) for _ in range(4)]
+    for s, c in zip(seqs, (15, 16, 40, 100)):
+        assert s.reserve(c + 1) >= 0
+        s.commit(c)
+    io = kv.StepIo(4, 4, 16, device="cpu")
+    io.pack(seqs, [1, 1, 1, 1], 0.0625)
+    first = io.upload()
+    assert first == io.nbytes                      # nothing uploaded before: everything
+    assert torch_equal(io.dev, io.host)
+    for s in seqs:
+        s.commit(1)
+        assert s.reserve(s.committed_len + 1) >= 0
+    io.pack(seqs, [1, 1, 1, 1], 0.0625)
+    second = io.upload()
+    head_bytes = 4 * int(io._offs[4])
+    # sequence 0 went from 16 to 17 reserved positions (a second page), sequence 1 already had two pages
+    assert second == head_bytes + 4 * 1
+    assert torch_equal(io.dev, io.host)
+
+
+def torch_equal(a, b):
+    import torch
+    return bool(torch.equal(a, b))

@@ -406,28 +406,34 @@ def kv_page_copy(ex, layer, src_page, dst_page, rows, lib=None):
 
 
 class StepIo:
-    """Persistent step-metadata buffers: one pinned host arena, one device arena, one copy per
-    step (the reference packs tokens | slots | block tables | lengths into a single pinned
-    upload, crates/warp34-host/src/model/execution.rs:38-93; graph_io.rs:368-420)."""
+    """Persistent step-metadata buffers: one pinned host arena and one device arena (the reference
+    packs tokens | slots | block tables | lengths into a single pinned upload,
+    crates/warp34-host/src/model/execution.rs:38-93; graph_io.rs:368-420).  Each step uploads the
+    small arrays (lengths, slots) in one copy and, of the block tables, only the row suffixes that
+    changed since the last upload (graph_io.rs:109-195): a decode step adds a page to one sequence
+    in sixteen."""
 
     def __init__(self, max_reqs, max_tokens, max_blocks_per_req, device="cuda"):
         self.max_reqs, self.max_tokens, self.max_blocks = max_reqs, max_tokens, max_blocks_per_req
-        sizes = [max_reqs + 1, max_reqs, max_reqs, max_reqs * max_blocks_per_req, max_tokens]
+        # arena order: query_start_loc | context_lens_before | seq_lens_after | write_slot_mapping | block_tables
+        sizes = [max_reqs + 1, max_reqs, max_reqs, max_tokens, max_reqs * max_blocks_per_req]
         offs = np.concatenate([[0], np.cumsum([(s + 3) // 4 * 4 for s in sizes])])
         self._offs, self._sizes = offs, sizes
         total = int(offs[-1])
         self.host = torch.zeros(total, dtype=torch.int32).pin_memory() if device != "cpu" else torch.zeros(total, dtype=torch.int32)
         self.dev = torch.zeros(total, dtype=torch.int32, device=device)
         self._np = self.host.numpy()
+        self._bt_shadow = None          # block tables as last uploaded
         self.desc = ffi.AttentionBatch()
         base = self.dev.data_ptr()
         self.desc.query_start_loc = base + 4 * int(offs[0])
         self.desc.context_lens_before = base + 4 * int(offs[1])
         self.desc.seq_lens_after = base + 4 * int(offs[2])
-        self.desc.block_tables = base + 4 * int(offs[3])
-        self.desc.write_slot_mapping = base + 4 * int(offs[4])
+        self.desc.write_slot_mapping = base + 4 * int(offs[3])
+        self.desc.block_tables = base + 4 * int(offs[4])
         self.desc.max_blocks_per_req = max_blocks_per_req
-        self.nbytes = total * 4
+        self.nbytes = total * 4          # a full upload
+        self.last_upload_bytes = 0
 
     def _ptr(self, i):
         return C.cast(self._np.ctypes.data + 4 * int(self._offs[i]), C.POINTER(C.c_int32))
@@ -439,7 +445,7 @@ class StepIo:
         ql = (C.c_int32 * n)(*q_lens)
         mq, ms = C.c_int32(), C.c_int32()
         rc = ffi.host().w34_build_step_metadata(handles, ql, n, self.max_blocks, self._ptr(0), self._ptr(1),
-                                                self._ptr(2), self._ptr(3), self._ptr(4), C.byref(mq), C.byref(ms))
+                                                self._ptr(2), self._ptr(4), self._ptr(3), C.byref(mq), C.byref(ms))
         if rc < 0:
             raise RuntimeError(f"w34_build_step_metadata: {rc}")
         d = self.desc
@@ -448,8 +454,32 @@ class StepIo:
         d.mask_mode, d.sliding_window, d.sm_scale = mask_mode, sliding_window, sm_scale
         return rc
 
-    def upload(self):
-        self.dev.copy_(self.host, non_blocking=True)
+    def upload(self, full=False):
+        """Copies what changed since the last upload; returns the bytes copied."""
+        bt0, bt1 = int(self._offs[4]), int(self._offs[5])
+        head = bt0                                   # lengths and slots: always
+        self.dev[:head].copy_(self.host[:head], non_blocking=True)
+        copied = head
+        bt = self._np[bt0:bt0 + self.max_reqs * self.max_blocks].reshape(self.max_reqs, self.max_blocks)
+        if full or self._bt_shadow is None:
+            self.dev[bt0:bt1].copy_(self.host[bt0:bt1], non_blocking=True)
+            copied += bt1 - bt0
+        else:
+            diff = bt != self._bt_shadow
+            rows = np.flatnonzero(diff.any(axis=1))
+            if len(rows) > 32:                       # many rows: one copy is cheaper than many
+                self.dev[bt0:bt1].copy_(self.host[bt0:bt1], non_blocking=True)
+                copied += bt1 - bt0
+            else:
+                for r in rows:
+                    cols = np.flatnonzero(diff[r])
+                    a = bt0 + int(r) * self.max_blocks + int(cols[0])
+                    b = bt0 + int(r) * self.max_blocks + int(cols[-1]) + 1
+                    self.dev[a:b].copy_(self.host[a:b], non_blocking=True)
+                    copied += b - a
+        self._bt_shadow = bt.copy()
+        self.last_upload_bytes = 4 * copied
+        return self.last_upload_bytes
 
 
 class _DescOnly:
@@ -475,12 +505,15 @@ class DecodeStep:
         self.v_dev = torch.zeros_like(self.v_host, device=device)
         self.q_dev = torch.zeros_like(self.q_host, device=device)
         self.out_dev = torch.zeros_like(self.out_host, device=device)
-        self.h2d_bytes = self.io.nbytes + 2 * self.k_host.numel() * 2 + self.q_host.numel() * 2
+        self.payload_bytes = 2 * self.k_host.numel() * 2 + self.q_host.numel() * 2
+        self.h2d_bytes = self.io.nbytes + self.payload_bytes      # upper bound: a full metadata upload
+        self.h2d_bytes_total = 0                                  # bytes actually copied by run() so far
         self.d2h_bytes = self.out_host.numel() * 2
 
     def run(self, q_lens, sm_scale=1.0 / 16.0, lib=None, sync=True, attend=None):
         self.io.pack(self.seqs, q_lens, sm_scale)
-        self.io.upload()
+        self.meta_bytes_last = self.io.upload()
+        self.h2d_bytes_total += self.meta_bytes_last + self.payload_bytes
         self.k_dev.copy_(self.k_host, non_blocking=True)
         self.v_dev.copy_(self.v_host, non_blocking=True)
         self.q_dev.copy_(self.q_host, non_blocking=True)
