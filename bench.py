@@ -195,7 +195,7 @@ def run_chunked_prefill(args):
     rank, local, world = init_dist(args.gpus)
     dev = f"cuda:{local}"
     lib = ffi.bind_kernel_abi(ref_path) if ref_path else ffi.kernels()
-    hq, hkv, n_seq, seq_len, chunk, prefix = 16, 4, 8, 16384, 2048, 4096
+    hq, hkv, n_seq, seq_len, chunk, prefix = 16, 4, 8, 16384, 2048, args.prefix_tokens
     lo, hi = sharding.split_batch(n_seq, world, rank)
     my_seqs = max(hi - lo, 0)
     pages_needed = my_seqs * (seq_len // 16) + 64
@@ -218,11 +218,17 @@ def run_chunked_prefill(args):
         flops, n_tok = 0.0, 0
         evs = []
 
-        def step(seqs, start):
-            nonlocal flops, n_tok
+        cow_copies = 0
+
+        def step(seqs, start, chunk=chunk):
+            nonlocal flops, n_tok, cow_copies
             n = len(seqs)
             for s in seqs:
                 assert s.reserve(start + chunk) >= 0
+                cow = s.prepare_append()     # a shared, partly filled tail page is copied before the first write
+                if cow is not None:
+                    kv.kv_page_copy(ex, layer, *cow)
+                    cow_copies += 1
             b = kv.build_step(seqs, [chunk] * n, max_blocks, 1.0 / 16.0, device=dev)
             if timed:
                 e = tuple(torch.cuda.Event(enable_timing=True) for _ in range(3))
@@ -242,20 +248,24 @@ def run_chunked_prefill(args):
 
         pool_seqs = [kv.Sequence(pool) for _ in range(my_seqs)]
         if my_seqs > 0:
+            # the first sequence prefills the shared prefix (its last piece may be shorter than a chunk)
             for start in range(0, prefix, chunk):
-                step(pool_seqs[:1], start)
-            cache.insert(tokens[:prefix], pool_seqs[0].pages[:prefix // 16])
+                step(pool_seqs[:1], start, min(chunk, prefix - start))
+            whole = prefix // 16 * 16            # the radix cache works in whole pages
+            cache.insert(tokens[:whole], pool_seqs[0].pages[:whole // 16])
             for s in pool_seqs[1:]:
-                pages, matched, node = cache.match_prefix(tokens[:prefix])
-                assert matched == prefix
-                s.attach_prefix(pages, matched)
+                pages, matched, node = cache.match_prefix(tokens[:whole])
+                assert matched == whole
+                if prefix > whole:               # share the partly filled tail page as well: copy-on-write later
+                    pages = pages + [pool_seqs[0].pages[whole // 16]]
+                s.attach_prefix(pages, prefix)
             for start in range(prefix, seq_len, chunk):
-                step(pool_seqs, start)
+                step(pool_seqs, start, min(chunk, seq_len - start))
         torch.cuda.synchronize()
         for s in pool_seqs:
             s.close()
         freed = cache.evict(10 ** 9)
-        return flops, n_tok, evs, len(freed)
+        return flops, n_tok, evs, len(freed), cow_copies
 
     run_job(False)                            # warm-up pass over the whole job
     barrier(world)
@@ -264,7 +274,7 @@ def run_chunked_prefill(args):
     sampler.start()
     t_begin = time.perf_counter()
     e0.record()
-    flops, n_tok, evs, shared_pages = run_job(True)
+    flops, n_tok, evs, shared_pages, cow_copies = run_job(True)
     e1.record()
     barrier(world)
     t_end = time.perf_counter()
@@ -286,7 +296,8 @@ def run_chunked_prefill(args):
                                    "shared refcounted prefix computed once, then one chunk of every sequence per call; "
                                    "16 q heads / 4 kv heads, d256; a step is the whole job",
                        "l2": "each chunk re-reads its sequence's cached KV (up to 17 MB): L2-resident by design of the workload",
-                       "parallelism": f"sequences split over {world} rank(s), no collective", "shared_prefix_pages": shared_pages},
+                       "parallelism": f"sequences split over {world} rank(s), no collective", "shared_prefix_pages": shared_pages,
+                       "shared_prefix_tokens": prefix, "copy_on_write_tail_pages": cow_copies},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                          "peak_kind": f"of {kind} (sustained bf16)", "kernel": "tq4_attention_prefill_tc_kernel (tcgen05, 128-row CTAs)", "traffic": None,
                          "attention_ms_rank0": attn_ms},
@@ -379,6 +390,8 @@ def main():
     ap.add_argument("--config", default="cfg1_batched_decode")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--append-tokens", type=int, default=32768, help="tokens of the bulk-append measurement")
+    ap.add_argument("--prefix-tokens", type=int, default=4096,
+                    help="cfg2: shared prefix length; 4100 leaves a partly filled shared tail page (copy-on-write)")
     ap.add_argument("--kv", default="tq4", choices=["tq4", "bf16"],
                     help="bf16: the uncompressed-storage comparison arm of the same decode step (one GPU)")
     args = ap.parse_args()
