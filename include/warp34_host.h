@@ -211,6 +211,17 @@ int32_t w34_build_step_metadata(w34_seq* const* seqs, const int32_t* q_lens, int
                                 int32_t* block_tables, int32_t* write_slot_mapping,
                                 int32_t* out_max_q_len, int32_t* out_max_seq_len);
 
+/* The same packer for a persistent arena: block_tables must still hold what the previous call
+ * left there.  For every row i it reports the column range [changed_lo[i], changed_hi[i]) whose
+ * entries differ from before (changed_lo >= changed_hi: nothing), so that the caller uploads only
+ * those suffixes (graph_io.rs:109-195). */
+int32_t w34_build_step_metadata_delta(w34_seq* const* seqs, const int32_t* q_lens, int32_t num_seqs,
+                                      int32_t max_blocks_per_req, int32_t* query_start_loc,
+                                      int32_t* context_lens_before, int32_t* seq_lens_after,
+                                      int32_t* block_tables, int32_t* write_slot_mapping,
+                                      int32_t* out_max_q_len, int32_t* out_max_seq_len,
+                                      int32_t* changed_lo, int32_t* changed_hi);
+
 #ifdef __cplusplus
 }
 #endif

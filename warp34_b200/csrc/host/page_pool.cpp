@@ -391,10 +391,11 @@ int32_t w34_seq_set_pages_unchecked(w34_seq* s, const int32_t* pages, int32_t n,
     return W34_OK;
 }
 
-int32_t w34_build_step_metadata(w34_seq* const* seqs, const int32_t* q_lens, int32_t num_seqs,
-                                int32_t max_blocks, int32_t* qsl, int32_t* ctx_before,
-                                int32_t* seq_after, int32_t* block_tables, int32_t* slots,
-                                int32_t* out_max_q, int32_t* out_max_seq) {
+int32_t w34_build_step_metadata_delta(w34_seq* const* seqs, const int32_t* q_lens, int32_t num_seqs,
+                                      int32_t max_blocks, int32_t* qsl, int32_t* ctx_before,
+                                      int32_t* seq_after, int32_t* block_tables, int32_t* slots,
+                                      int32_t* out_max_q, int32_t* out_max_seq,
+                                      int32_t* changed_lo, int32_t* changed_hi) {
     if (!seqs || !q_lens || num_seqs < 0 || max_blocks <= 0 || !qsl || !ctx_before || !seq_after ||
         !block_tables || !slots) return W34_ERR_INVALID;
     int32_t total = 0, max_q = 0, max_seq = 0;
@@ -408,7 +409,17 @@ int32_t w34_build_step_metadata(w34_seq* const* seqs, const int32_t* q_lens, int
         if (need > (int32_t)s->pages.size()) return W34_ERR_INVALID;   // reserve first
         if (need > max_blocks) return W34_ERR_CAPACITY;
         int32_t* row = block_tables + (size_t)i * (size_t)max_blocks;
-        for (int32_t b = 0; b < max_blocks; ++b) row[b] = b < need ? s->pages[(size_t)b] : 0;
+        int32_t lo = max_blocks, hi = 0;          // columns [lo, hi) of this row differ from what was there
+        for (int32_t b = 0; b < max_blocks; ++b) {
+            const int32_t v = b < need ? s->pages[(size_t)b] : 0;
+            if (row[b] != v) {
+                row[b] = v;
+                if (b < lo) lo = b;
+                hi = b + 1;
+            }
+        }
+        if (changed_lo) changed_lo[i] = lo;
+        if (changed_hi) changed_hi[i] = hi;
         for (int32_t t = 0; t < q_lens[i]; ++t) {
             const int32_t pos = s->committed + t;
             slots[total + t] = s->pages[(size_t)(pos / B)] * B + pos % B;
@@ -423,6 +434,14 @@ int32_t w34_build_step_metadata(w34_seq* const* seqs, const int32_t* q_lens, int
     if (out_max_q) *out_max_q = max_q;
     if (out_max_seq) *out_max_seq = max_seq;
     return total;
+}
+
+int32_t w34_build_step_metadata(w34_seq* const* seqs, const int32_t* q_lens, int32_t num_seqs,
+                                int32_t max_blocks, int32_t* qsl, int32_t* ctx_before,
+                                int32_t* seq_after, int32_t* block_tables, int32_t* slots,
+                                int32_t* out_max_q, int32_t* out_max_seq) {
+    return w34_build_step_metadata_delta(seqs, q_lens, num_seqs, max_blocks, qsl, ctx_before, seq_after,
+                                         block_tables, slots, out_max_q, out_max_seq, nullptr, nullptr);
 }
 
 }  // extern "C"

@@ -141,6 +141,8 @@ _HOST_SIGS = {
     "w34_radix_sanity_check": (C.c_int32, [C.c_void_p]),
     "w34_build_step_metadata": (C.c_int32, [_P(C.c_void_p), _P(C.c_int32), C.c_int32, C.c_int32] +
                                 [_P(C.c_int32)] * 7),
+    "w34_build_step_metadata_delta": (C.c_int32, [_P(C.c_void_p), _P(C.c_int32), C.c_int32, C.c_int32] +
+                                      [_P(C.c_int32)] * 9),
 }
 
 

@@ -423,7 +423,12 @@ class StepIo:
         self.host = torch.zeros(total, dtype=torch.int32).pin_memory() if device != "cpu" else torch.zeros(total, dtype=torch.int32)
         self.dev = torch.zeros(total, dtype=torch.int32, device=device)
         self._np = self.host.numpy()
-        self._bt_shadow = None          # block tables as last uploaded
+        # per-row changed column ranges: of the last pack, and pending since the last upload
+        self._lo = np.zeros(max_reqs, np.int32)
+        self._hi = np.zeros(max_reqs, np.int32)
+        self._pend_lo = np.full(max_reqs, max_blocks_per_req, np.int32)
+        self._pend_hi = np.zeros(max_reqs, np.int32)
+        self._uploaded_once = False
         self.desc = ffi.AttentionBatch()
         base = self.dev.data_ptr()
         self.desc.query_start_loc = base + 4 * int(offs[0])
@@ -444,10 +449,15 @@ class StepIo:
         handles = (C.c_void_p * n)(*[s.handle for s in seqs])
         ql = (C.c_int32 * n)(*q_lens)
         mq, ms = C.c_int32(), C.c_int32()
-        rc = ffi.host().w34_build_step_metadata(handles, ql, n, self.max_blocks, self._ptr(0), self._ptr(1),
-                                                self._ptr(2), self._ptr(4), self._ptr(3), C.byref(mq), C.byref(ms))
+        ip = lambda a: a.ctypes.data_as(C.POINTER(C.c_int32))  # noqa: E731
+        rc = ffi.host().w34_build_step_metadata_delta(handles, ql, n, self.max_blocks, self._ptr(0), self._ptr(1),
+                                                      self._ptr(2), self._ptr(4), self._ptr(3), C.byref(mq), C.byref(ms),
+                                                      ip(self._lo), ip(self._hi))
         if rc < 0:
-            raise RuntimeError(f"w34_build_step_metadata: {rc}")
+            raise RuntimeError(f"w34_build_step_metadata_delta: {rc}")
+        # rows changed since the last upload: union over the packs in between
+        np.minimum(self._pend_lo[:n], self._lo[:n], out=self._pend_lo[:n])
+        np.maximum(self._pend_hi[:n], self._hi[:n], out=self._pend_hi[:n])
         d = self.desc
         d.num_reqs, d.total_tokens = n, rc
         d.max_q_len, d.max_seq_len = mq.value, ms.value
@@ -460,24 +470,19 @@ class StepIo:
         head = bt0                                   # lengths and slots: always
         self.dev[:head].copy_(self.host[:head], non_blocking=True)
         copied = head
-        bt = self._np[bt0:bt0 + self.max_reqs * self.max_blocks].reshape(self.max_reqs, self.max_blocks)
-        if full or self._bt_shadow is None:
+        rows = np.flatnonzero(self._pend_hi > self._pend_lo)
+        if full or not self._uploaded_once or len(rows) > 32:    # many rows: one copy is cheaper than many
             self.dev[bt0:bt1].copy_(self.host[bt0:bt1], non_blocking=True)
             copied += bt1 - bt0
         else:
-            diff = bt != self._bt_shadow
-            rows = np.flatnonzero(diff.any(axis=1))
-            if len(rows) > 32:                       # many rows: one copy is cheaper than many
-                self.dev[bt0:bt1].copy_(self.host[bt0:bt1], non_blocking=True)
-                copied += bt1 - bt0
-            else:
-                for r in rows:
-                    cols = np.flatnonzero(diff[r])
-                    a = bt0 + int(r) * self.max_blocks + int(cols[0])
-                    b = bt0 + int(r) * self.max_blocks + int(cols[-1]) + 1
-                    self.dev[a:b].copy_(self.host[a:b], non_blocking=True)
-                    copied += b - a
-        self._bt_shadow = bt.copy()
+            for r in rows:
+                a = bt0 + int(r) * self.max_blocks + int(self._pend_lo[r])
+                b = bt0 + int(r) * self.max_blocks + int(self._pend_hi[r])
+                self.dev[a:b].copy_(self.host[a:b], non_blocking=True)
+                copied += b - a
+        self._uploaded_once = True
+        self._pend_lo[:] = self.max_blocks
+        self._pend_hi[:] = 0
         self.last_upload_bytes = 4 * copied
         return self.last_upload_bytes
 
