@@ -236,9 +236,9 @@ def test_speculative_batch_commits_accepted_tokens_and_frees_rejected_pages(nati
     assert [s.num_pages for s in seqs] == before
 
 
-def test_step_io_uploads_only_changed_block_table_suffixes(native_libs):
-    """Lengths and slots travel every step; of the block tables only the row suffixes that changed
-    (graph_io.rs:109-195).  Runs on the CPU: host and "device" arenas are both host tensors."""
+def test_step_io_upload_stops_at_the_last_changed_block_table_entry(native_libs):
+    """Lengths and slots travel every step; of the block tables only what lies before the last
+    changed entry (graph_io.rs:109-195).  Runs on the CPU: both arenas are host tensors."""
     from warp34_b200 import kv
     pool = kv.PagePool(256, 16)
     seqs = [kv.Sequence(pool) for _ in range(4)]
@@ -256,8 +256,15 @@ def test_step_io_uploads_only_changed_block_table_suffixes(native_libs):
     io.pack(seqs, [1, 1, 1, 1], 0.0625)
     second = io.upload()
     head_bytes = 4 * int(io._offs[4])
-    # sequence 0 went from 16 to 17 reserved positions (a second page), sequence 1 already had two pages
-    assert second == head_bytes + 4 * 1
+    # sequence 0 went from 16 to 17 reserved positions (a second page), sequence 1 already had two pages:
+    # the copy ends right after entry 1 of row 0
+    assert second == head_bytes + 4 * 2
+    assert torch_equal(io.dev, io.host)
+    for s in seqs:
+        s.commit(1)
+        assert s.reserve(s.committed_len + 1) >= 0
+    io.pack(seqs, [1, 1, 1, 1], 0.0625)
+    assert io.upload() == head_bytes             # no table entry changed
     assert torch_equal(io.dev, io.host)
 
 

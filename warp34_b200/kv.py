@@ -465,25 +465,22 @@ class StepIo:
         return rc
 
     def upload(self, full=False):
-        """Copies what changed since the last upload; returns the bytes copied."""
+        """One copy of the arena up to the last block-table entry that changed since the previous
+        upload (the length and slot arrays sit in front of the tables); returns the bytes copied."""
         bt0, bt1 = int(self._offs[4]), int(self._offs[5])
-        head = bt0                                   # lengths and slots: always
-        self.dev[:head].copy_(self.host[:head], non_blocking=True)
-        copied = head
-        rows = np.flatnonzero(self._pend_hi > self._pend_lo)
-        if full or not self._uploaded_once or len(rows) > 32:    # many rows: one copy is cheaper than many
-            self.dev[bt0:bt1].copy_(self.host[bt0:bt1], non_blocking=True)
-            copied += bt1 - bt0
+        end = bt0
+        if full or not self._uploaded_once:
+            end = bt1
         else:
-            for r in rows:
-                a = bt0 + int(r) * self.max_blocks + int(self._pend_lo[r])
-                b = bt0 + int(r) * self.max_blocks + int(self._pend_hi[r])
-                self.dev[a:b].copy_(self.host[a:b], non_blocking=True)
-                copied += b - a
+            rows = np.flatnonzero(self._pend_hi > self._pend_lo)
+            if len(rows):
+                r = int(rows[-1])
+                end = bt0 + r * self.max_blocks + int(self._pend_hi[r])
+        self.dev[:end].copy_(self.host[:end], non_blocking=True)
         self._uploaded_once = True
         self._pend_lo[:] = self.max_blocks
         self._pend_hi[:] = 0
-        self.last_upload_bytes = 4 * copied
+        self.last_upload_bytes = 4 * end
         return self.last_upload_bytes
 
 
