@@ -429,6 +429,10 @@ class StepIo:
         self._pend_lo = np.full(max_reqs, max_blocks_per_req, np.int32)
         self._pend_hi = np.zeros(max_reqs, np.int32)
         self._uploaded_once = False
+        self._packs_pending = 0
+        ip = lambda a: a.ctypes.data_as(C.POINTER(C.c_int32))  # noqa: E731
+        self._lo_p, self._hi_p = ip(self._lo), ip(self._hi)
+        self._pack_fn = ffi.host().w34_build_step_metadata_delta
         self.desc = ffi.AttentionBatch()
         base = self.dev.data_ptr()
         self.desc.query_start_loc = base + 4 * int(offs[0])
@@ -437,6 +441,7 @@ class StepIo:
         self.desc.write_slot_mapping = base + 4 * int(offs[3])
         self.desc.block_tables = base + 4 * int(offs[4])
         self.desc.max_blocks_per_req = max_blocks_per_req
+        self._arena_ptrs = (self._ptr(0), self._ptr(1), self._ptr(2), self._ptr(4), self._ptr(3))
         self.nbytes = total * 4          # a full upload
         self.last_upload_bytes = 0
 
@@ -449,15 +454,16 @@ class StepIo:
         handles = (C.c_void_p * n)(*[s.handle for s in seqs])
         ql = (C.c_int32 * n)(*q_lens)
         mq, ms = C.c_int32(), C.c_int32()
-        ip = lambda a: a.ctypes.data_as(C.POINTER(C.c_int32))  # noqa: E731
-        rc = ffi.host().w34_build_step_metadata_delta(handles, ql, n, self.max_blocks, self._ptr(0), self._ptr(1),
-                                                      self._ptr(2), self._ptr(4), self._ptr(3), C.byref(mq), C.byref(ms),
-                                                      ip(self._lo), ip(self._hi))
+        # the packer writes the changed ranges of this pack; a second pack before an upload folds the
+        # earlier ranges in
+        if self._packs_pending:
+            np.minimum(self._pend_lo, self._lo, out=self._pend_lo)
+            np.maximum(self._pend_hi, self._hi, out=self._pend_hi)
+        rc = self._pack_fn(handles, ql, n, self.max_blocks, *self._arena_ptrs, C.byref(mq), C.byref(ms),
+                           self._lo_p, self._hi_p)
         if rc < 0:
             raise RuntimeError(f"w34_build_step_metadata_delta: {rc}")
-        # rows changed since the last upload: union over the packs in between
-        np.minimum(self._pend_lo[:n], self._lo[:n], out=self._pend_lo[:n])
-        np.maximum(self._pend_hi[:n], self._hi[:n], out=self._pend_hi[:n])
+        self._packs_pending += 1
         d = self.desc
         d.num_reqs, d.total_tokens = n, rc
         d.max_q_len, d.max_seq_len = mq.value, ms.value
@@ -472,14 +478,19 @@ class StepIo:
         if full or not self._uploaded_once:
             end = bt1
         else:
-            rows = np.flatnonzero(self._pend_hi > self._pend_lo)
+            lo, hi = self._lo, self._hi
+            if self._packs_pending > 1:
+                lo, hi = np.minimum(self._pend_lo, lo), np.maximum(self._pend_hi, hi)
+            rows = np.flatnonzero(hi > lo)
             if len(rows):
                 r = int(rows[-1])
-                end = bt0 + r * self.max_blocks + int(self._pend_hi[r])
+                end = bt0 + r * self.max_blocks + int(hi[r])
         self.dev[:end].copy_(self.host[:end], non_blocking=True)
         self._uploaded_once = True
-        self._pend_lo[:] = self.max_blocks
-        self._pend_hi[:] = 0
+        if self._packs_pending > 1:
+            self._pend_lo[:] = self.max_blocks
+            self._pend_hi[:] = 0
+        self._packs_pending = 0
         self.last_upload_bytes = 4 * end
         return self.last_upload_bytes
 
