@@ -390,6 +390,7 @@ def main():
     ap.add_argument("--config", default="cfg1_batched_decode")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--append-tokens", type=int, default=32768, help="tokens of the bulk-append measurement")
+    ap.add_argument("--no-graph", action="store_true", help="time eager launches only (no CUDA graph replay)")
     ap.add_argument("--prefix-tokens", type=int, default=4096,
                     help="cfg2: shared prefix length; 4100 leaves a partly filled shared tail page (copy-on-write)")
     ap.add_argument("--kv", default="tq4", choices=["tq4", "bf16"],
@@ -499,6 +500,38 @@ def main():
     t_end = time.perf_counter()
     total_ms = max_over_ranks(e0.elapsed_time(e1), world)
     ms_per_step = total_ms / args.steps
+    eager_ms_per_step = ms_per_step
+    # The same K steps replayed from one CUDA graph (how the reference's engine runs a decode step,
+    # crates/warp34-host/src/model/graphs.rs:199-259): launch gaps between the four kernels go away.
+    # Not for the page-sharded case (its collective stays outside a graph here) nor the reference arm.
+    graph_used = False
+    if not args.no_graph and not sharded and not reference:
+        try:
+            g = torch.cuda.CUDAGraph()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                step.ex.set_stream()
+                device_step()
+            torch.cuda.current_stream().wait_stream(side)
+            with torch.cuda.graph(g):
+                step.ex.set_stream()
+                device_step()
+            step.ex.set_stream()
+            for _ in range(3):
+                g.replay()
+            barrier(world)
+            e0.record()
+            for _ in range(args.steps):
+                g.replay()
+            e1.record()
+            barrier(world)
+            ms_per_step = max_over_ranks(e0.elapsed_time(e1), world) / args.steps
+            graph_used = True
+        except Exception as exc:  # keep the eager numbers
+            step.ex.set_stream()
+            sys.stderr.write(f"CUDA graph replay unavailable: {exc}\n")
+    t_end = time.perf_counter()
     append_ms = float(np.mean([a.elapsed_time(b) for a, b, c in evs]))
     attn_ms = float(np.mean([b.elapsed_time(c) for a, b, c in evs]))
     clocks = sampler.summary(t_begin, t_end)
@@ -583,7 +616,7 @@ def main():
                      "launch_ms": attn_ms, "traffic": None},
         "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": (step.h2d_bytes_total - h2d_before) / e2e_steps,
                 "d2h_bytes_per_step": step.d2h_bytes, **({"speculative_rollback": rollback} if rollback else {})},
-        "gpu_launches": 4 * args.steps,
+        "gpu_launches": 4 * args.steps, "cuda_graph_replay": graph_used, "eager_ms_per_step": eager_ms_per_step,
         "clocks": clocks,
         "append_tokens_per_s": n_tok / (append_ms * 1e-3), "append_ms": append_ms,
         "append_bulk": {"tokens": bulk_tokens, "ms": bulk_ms, "tokens_per_s": bulk_tok_s,
