@@ -539,8 +539,13 @@ def main():
     value = all_bytes / (ms_per_step * 1e-3) / 1e9
 
     # ---- end to end: host buffers in, host result out, every step ----------------------------
+    use_graph = not args.no_graph and not sharded       # both arms: one graph replay per step
+    if sharded:
+        attend_e2e = attend
+    else:
+        attend_e2e = None                               # the plain attention call: eligible for the graph
     for _ in range(3):
-        step.run(q_lens, lib=lib, attend=attend)
+        step.run(q_lens, lib=lib, attend=attend_e2e, graph=use_graph)
     barrier(world)
     e2e_steps = max(3, min(args.steps, 200))
     rollback = None
@@ -556,7 +561,7 @@ def main():
         for _ in range(e2e_steps):
             spec.reserve_ahead(q_len)
             e2e_bytes += float(sum(s.committed_len + q_len for s in wl.seqs)) * hkv * 264
-            step.run(q_lens, lib=lib, sync=True, attend=attend)
+            step.run(q_lens, lib=lib, sync=True, attend=attend_e2e, graph=use_graph)
             accepted = q_len - rng.randint(0, q_len, size=batch)
             freed_pages += len(spec.commit_and_rollback(accepted))
             accepted_total += int(accepted.sum())
@@ -568,7 +573,7 @@ def main():
     else:
         e0.record()
         for _ in range(e2e_steps):
-            step.run(q_lens, lib=lib, sync=True, attend=attend)
+            step.run(q_lens, lib=lib, sync=True, attend=attend_e2e, graph=use_graph)
         e1.record()
         barrier(world)
         e2e_ms = max_over_ranks(e0.elapsed_time(e1), world) / e2e_steps
@@ -615,7 +620,8 @@ def main():
                      "kernel": "tq4_attention_stream_kernel (+ plan and merge launches, timed together)",
                      "launch_ms": attn_ms, "traffic": None},
         "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": (step.h2d_bytes_total - h2d_before) / e2e_steps,
-                "d2h_bytes_per_step": step.d2h_bytes, **({"speculative_rollback": rollback} if rollback else {})},
+                "d2h_bytes_per_step": step.d2h_bytes, "cuda_graph_replay": use_graph,
+                **({"speculative_rollback": rollback} if rollback else {})},
         "gpu_launches": 4 * args.steps, "cuda_graph_replay": graph_used, "eager_ms_per_step": eager_ms_per_step,
         "clocks": clocks,
         "append_tokens_per_s": n_tok / (append_ms * 1e-3), "append_ms": append_ms,

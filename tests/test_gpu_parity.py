@@ -615,3 +615,35 @@ def test_prefill_dispatch_paths_agree_with_the_oracle(env, mode):
     vs = channel_scale(v.numpy(), [(0, lens[0]), (lens[0], lens[0] + lens[1])], [q_len, q_len], hq, hkv)
     ok, msg = tensor_core_parity(out.float().cpu().numpy(), want, vs)
     assert ok, (mode, msg)
+
+
+def test_graph_replayed_steps_match_eager_steps(env):
+    """DecodeStep.run(graph=True) replays one captured CUDA graph per step (uploads, append,
+    attention, download) with the block-table changes copied in front of it: over steps in which
+    sequences grow across page boundaries its outputs and cache bytes equal the eager path's."""
+    kv, synth = env["kv"], env["synth"]
+    hq, hkv = 16, 4
+    ctx = [14, 15, 16, 31, 100]
+    outs, pools = [], []
+    for use_graph in (False, True):
+        wl = synth.PagedWorkload(ctx, [1] * len(ctx), hkv, seed=71, slack_pages=16)
+        ex0 = kv.Executor(8 << 20)
+        wl.fill_context(ex0, 71)
+        step = kv.DecodeStep(wl.layer, wl.seqs, hq, max_q_len=1, scratch_bytes=8 << 20, extra_blocks=2)
+        res = []
+        for it in range(6):
+            for s in wl.seqs:
+                assert s.reserve(s.committed_len + 1) >= 0
+            k, v = synth.make_kv(len(ctx), hkv, 800 + it)
+            q = synth.make_q(len(ctx), hq, 800 + it)
+            step.k_host.copy_(k); step.v_host.copy_(v); step.q_host.copy_(q)
+            out = step.run([1] * len(ctx), graph=use_graph)
+            res.append(out.clone())
+            for s in wl.seqs:
+                s.commit(1)
+        outs.append(res)
+        pools.append([_logical_rows(wl.layer, s, s.committed_len, hkv) for s in wl.seqs])
+    for a, b in zip(outs[0], outs[1]):
+        assert torch.equal(a, b)
+    for (ak, av), (bk, bv) in zip(pools[0], pools[1]):
+        assert (ak == bk).all() and (av == bv).all()

@@ -470,9 +470,11 @@ class StepIo:
         d.mask_mode, d.sliding_window, d.sm_scale = mask_mode, sliding_window, sm_scale
         return rc
 
-    def upload(self, full=False):
+    def upload(self, full=False, tables_only=False):
         """One copy of the arena up to the last block-table entry that changed since the previous
-        upload (the length and slot arrays sit in front of the tables); returns the bytes copied."""
+        upload (the length and slot arrays sit in front of the tables); returns the bytes copied.
+        tables_only: the copy starts at the block tables (the caller uploads the front part itself,
+        e.g. from a captured graph) and is skipped when no entry changed."""
         bt0, bt1 = int(self._offs[4]), int(self._offs[5])
         end = bt0
         if full or not self._uploaded_once:
@@ -485,14 +487,21 @@ class StepIo:
             if len(rows):
                 r = int(rows[-1])
                 end = bt0 + r * self.max_blocks + int(hi[r])
-        self.dev[:end].copy_(self.host[:end], non_blocking=True)
+        begin = bt0 if tables_only else 0
+        if end > begin:
+            self.dev[begin:end].copy_(self.host[begin:end], non_blocking=True)
         self._uploaded_once = True
         if self._packs_pending > 1:
             self._pend_lo[:] = self.max_blocks
             self._pend_hi[:] = 0
         self._packs_pending = 0
-        self.last_upload_bytes = 4 * end
+        self.last_upload_bytes = 4 * (end - begin)
         return self.last_upload_bytes
+
+    @property
+    def head_words(self):
+        """Words in front of the block tables: lengths and slots."""
+        return int(self._offs[4])
 
 
 class _DescOnly:
@@ -521,10 +530,53 @@ class DecodeStep:
         self.payload_bytes = 2 * self.k_host.numel() * 2 + self.q_host.numel() * 2
         self.h2d_bytes = self.io.nbytes + self.payload_bytes      # upper bound: a full metadata upload
         self.h2d_bytes_total = 0                                  # bytes actually copied by run() so far
+        self._graphs = {}
         self.d2h_bytes = self.out_host.numel() * 2
 
-    def run(self, q_lens, sm_scale=1.0 / 16.0, lib=None, sync=True, attend=None):
+    def _capture(self, lib):
+        """One CUDA graph of the whole step: uploads of lengths, slots, K, V and Q from pinned memory,
+        append, attention, download of the output (the reference replays its decode steps the same
+        way, crates/warp34-host/src/model/graphs.rs:199-259).  Block tables are not in the graph:
+        their changed part is copied before the replay."""
+        head = self.io.head_words
+        b = _DescOnly(self.io.desc)
+
+        def body():
+            self.ex.set_stream()
+            self.io.dev[:head].copy_(self.io.host[:head], non_blocking=True)
+            self.k_dev.copy_(self.k_host, non_blocking=True)
+            self.v_dev.copy_(self.v_host, non_blocking=True)
+            self.q_dev.copy_(self.q_host, non_blocking=True)
+            kv_cache_write(self.ex, self.layer, b, self.k_dev, self.v_dev, lib=lib)
+            paged_attention(self.ex, self.layer, b, self.q_dev, self.out_dev, self.hq, lib=lib)
+            self.out_host.copy_(self.out_dev, non_blocking=True)
+
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            body()                      # warm-up outside the capture (one-time attribute calls)
+        torch.cuda.current_stream().wait_stream(side)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            body()
+        self.ex.set_stream()
+        return g
+
+    def run(self, q_lens, sm_scale=1.0 / 16.0, lib=None, sync=True, attend=None, graph=False):
         self.io.pack(self.seqs, q_lens, sm_scale)
+        if graph and attend is None:
+            # geometry baked into the captured launches: token count and request count must not change
+            key = (id(lib), self.io.desc.num_reqs, self.io.desc.total_tokens, self.io.desc.max_q_len)
+            g = self._graphs.get(key)
+            if g is None:
+                self.io.upload(full=True)
+                g = self._graphs[key] = self._capture(lib)
+            self.meta_bytes_last = self.io.upload(tables_only=True) + 4 * self.io.head_words
+            self.h2d_bytes_total += self.meta_bytes_last + self.payload_bytes
+            g.replay()
+            if sync:
+                torch.cuda.current_stream().synchronize()
+            return self.out_host
         self.meta_bytes_last = self.io.upload()
         self.h2d_bytes_total += self.meta_bytes_last + self.payload_bytes
         self.k_dev.copy_(self.k_host, non_blocking=True)
