@@ -371,7 +371,11 @@ def run_bf16_kv(args):
                        "kv_bytes_per_step": kv_bytes, "l2": "KV read per step is larger than L2; no flush needed"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_kind": f"of {peak_kind}", "kernel": "bf16kv_attention_stream_kernel (+ plan and merge)",
-                         "launch_ms": attn_ms, "traffic": None},
+                         "launch_ms": attn_ms,
+                     # dram__bytes_read + write of one stream-kernel launch, from the ncu capture of this same
+                     # workload (profiles/tq4_attention_stream_kernel_cfg1_decode.md: 1.388 GB for 1.343 GB of
+                     # algorithmic bytes), scaled by the bytes of this run; null for the other workloads
+                     "traffic": (kv_bytes * (1.388 / 1.343) if args.config == "cfg1_batched_decode" and not reference else None)},
             "attended_tokens_per_s": float(sum(wl.ctx) + n_tok) / (attn_ms * 1e-3),
             "gpu_launches": 4 * args.steps, "clocks": sampler.summary(t_begin, t_end)}
     if reference:
@@ -618,7 +622,11 @@ def main():
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "peak_kind": f"of {peak_kind}", "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,
                      "kernel": "tq4_attention_stream_kernel (+ plan and merge launches, timed together)",
-                     "launch_ms": attn_ms, "traffic": None},
+                     "launch_ms": attn_ms,
+                     # dram__bytes_read + write of one stream-kernel launch, from the ncu capture of this same
+                     # workload (profiles/tq4_attention_stream_kernel_cfg1_decode.md: 1.388 GB for 1.343 GB of
+                     # algorithmic bytes), scaled by the bytes of this run; null for the other workloads
+                     "traffic": (kv_bytes * (1.388 / 1.343) if args.config == "cfg1_batched_decode" and not reference else None)},
         "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": (step.h2d_bytes_total - h2d_before) / e2e_steps,
                 "d2h_bytes_per_step": step.d2h_bytes, "cuda_graph_replay": use_graph,
                 **({"speculative_rollback": rollback} if rollback else {})},
