@@ -410,10 +410,23 @@ int32_t w34_build_step_metadata_delta(w34_seq* const* seqs, const int32_t* q_len
         if (need > max_blocks) return W34_ERR_CAPACITY;
         int32_t* row = block_tables + (size_t)i * (size_t)max_blocks;
         int32_t lo = max_blocks, hi = 0;          // columns [lo, hi) of this row differ from what was there
-        for (int32_t b = 0; b < max_blocks; ++b) {
-            const int32_t v = b < need ? s->pages[(size_t)b] : 0;
-            if (row[b] != v) {
-                row[b] = v;
+        const int32_t* pages = s->pages.data();
+        if (std::memcmp(row, pages, (size_t)need * sizeof(int32_t)) != 0) {   // rare: find the range
+            for (int32_t b = 0; b < need; ++b) {
+                if (row[b] != pages[b]) {
+                    row[b] = pages[b];
+                    if (b < lo) lo = b;
+                    hi = b + 1;
+                }
+            }
+        }
+        // Entries past the sequence are never read by the kernels and are kept at 0, the trash page.
+        // Plain call (no change report): the whole tail is cleared.  Persistent arena: the row held a
+        // valid table before, so clearing stops at the first zero (if page 0 was a real entry of a
+        // longer old table, ids behind it stay: harmless, and host and device copies still agree).
+        for (int32_t b = need; b < max_blocks && (changed_lo == nullptr || row[b] != 0); ++b) {
+            if (row[b] != 0) {
+                row[b] = 0;
                 if (b < lo) lo = b;
                 hi = b + 1;
             }

@@ -430,6 +430,7 @@ class StepIo:
         self._pend_hi = np.zeros(max_reqs, np.int32)
         self._uploaded_once = False
         self._packs_pending = 0
+        self._arg_key = None
         ip = lambda a: a.ctypes.data_as(C.POINTER(C.c_int32))  # noqa: E731
         self._lo_p, self._hi_p = ip(self._lo), ip(self._hi)
         self._pack_fn = ffi.host().w34_build_step_metadata_delta
@@ -451,8 +452,12 @@ class StepIo:
     def pack(self, seqs, q_lens, sm_scale, mask_mode=0, sliding_window=0):
         n = len(seqs)
         assert n <= self.max_reqs and sum(q_lens) <= self.max_tokens
-        handles = (C.c_void_p * n)(*[s.handle for s in seqs])
-        ql = (C.c_int32 * n)(*q_lens)
+        key = (tuple(id(s) for s in seqs), tuple(q_lens))
+        if key != self._arg_key:          # the ctypes argument arrays are rebuilt only when the batch changes
+            self._arg_key = key
+            self._handles = (C.c_void_p * n)(*[s.handle for s in seqs])
+            self._ql = (C.c_int32 * n)(*q_lens)
+        handles, ql = self._handles, self._ql
         mq, ms = C.c_int32(), C.c_int32()
         # the packer writes the changed ranges of this pack; a second pack before an upload folds the
         # earlier ranges in
