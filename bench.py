@@ -561,14 +561,16 @@ def main():
         spec = kv.SpeculativeBatch(wl.seqs)
         rng = np.random.RandomState(seed + 99 + rank)
         freed_pages, e2e_bytes, accepted_total = 0, 0.0, 0
+        cached_tokens = sum(s.committed_len for s in wl.seqs)     # kept up to date from the accepted counts
         e0.record()
         for _ in range(e2e_steps):
             spec.reserve_ahead(q_len)
-            e2e_bytes += float(sum(s.committed_len + q_len for s in wl.seqs)) * hkv * 264
+            e2e_bytes += float(cached_tokens + batch * q_len) * hkv * 264
             step.run(q_lens, lib=lib, sync=True, attend=attend_e2e, graph=use_graph)
             accepted = q_len - rng.randint(0, q_len, size=batch)
             freed_pages += len(spec.commit_and_rollback(accepted))
             accepted_total += int(accepted.sum())
+            cached_tokens += int(accepted.sum())
         e1.record()
         barrier(world)
         e2e_ms = max_over_ranks(e0.elapsed_time(e1), world) / e2e_steps
