@@ -7,8 +7,8 @@
 // One CTA = 128 query rows (128 / gqa tokens x gqa heads of one KV head) and 14 warps:
 //   warps 0-3 (consumers): thread r owns query row r = TMEM lane r.  Per block of 64 keys they
 //     read the scores S from TMEM (tcgen05.ld), run the online softmax with a lazily updated
-//     reference maximum, write P as fp16 into a swizzled shared-memory tile and, rarely,
-//     rescale the output accumulator in TMEM.
+//     reference maximum, write P as fp16 pairs over the scores they came from (tcgen05.st) and,
+//     rarely, rescale the output accumulator in TMEM.
 //   warps 4-11 (producers): take the code words of a block from the staging buffer into
 //     registers (releasing it at once), then dequantise them once per CTA into fp16 tiles in the
 //     128-byte-swizzled layout the MMA descriptors expect: lookup of a code byte -> half2 of
@@ -16,7 +16,7 @@
 //   warp 12: lane 0 issues every tcgen05.mma, the scores of block j + 1 ahead of the output
 //     product of block j so that they are computed during the softmax of block j:
 //       S[128 x 64]   = Q'[128 x 256] K^T   16 instructions (K = 16), A = Q' in TMEM, B = K tile
-//       O[128 x 256] += P[128 x 64] V        4 instructions, A = P tile, B = V tile (MN-major)
+//       O[128 x 256] += P[128 x 64] V        4 instructions, A = P in TMEM, B = V tile (MN-major)
 //   warp 13: lane 0 bulk-copies the raw (page, head) runs of the next block's four pages
 //     (2112 B each for K and for V) into the staging buffer.
 // Completion of MMAs is tracked with tcgen05.commit on mbarriers; every wait is bounded and
@@ -27,9 +27,11 @@
 // (row & 7)):
 //   K  [2][4 dim blocks][64 keys][64]  K-major B operand      2 x 32 KB
 //   V  [2][4 dim blocks][64 keys][64]  MN-major B operand     2 x 32 KB  (same physical layout)
-//   P  [128 rows][64 keys]             K-major A operand      16 KB
 // TMEM (512 columns): O in [0, 256), two score buffers in [256, 320) and [320, 384) (fp32, lane =
-// query row), Q' in [384, 512) (two fp16 per column).
+// query row; the first 32 columns of a buffer are reused for the P of the same block), Q' in
+// [384, 512) (two fp16 per column).  Both A operands of the MMAs come from TMEM: with P in shared
+// memory the output product competed with the producers for shared-memory bandwidth and ran at
+// half rate.
 // Scales: every K and V element is table centroid x row scale, the product rounded once
 // (scale = hi + lo in fp16, v = fma(e, hi, e * lo)).  (A scale, or P times a scale, rounded to
 // fp16 per 128-half puts a different relative error on the two halves of a row; through the
@@ -47,14 +49,12 @@ constexpr int kTcProducers = kTcProducerWarps * 32;
 constexpr int kTcWarps = 4 + kTcProducerWarps + 2;   // 4 consumer, 8 producer, 1 MMA-issue, 1 copy-issue warp
 constexpr int kTcThreads = kTcWarps * 32;
 constexpr uint32_t kTcKvBytes = 4u * kTcKeys * 128u;         // 32768
-constexpr uint32_t kTcPBytes = kTcRows * 128u;               // 16384
 constexpr uint32_t kTcRawStage = 2u * 4u * kTq4PageHeadBytes;  // K runs then V runs of four pages: 16896
 constexpr uint32_t kTcLutBytes = 256u * 128u;                // lane-replicated, 128-byte entry stride
 constexpr uint32_t kTcOffK = 0;                               // K is double-buffered
 constexpr uint32_t kTcOffQStage = 0;                          // Q' staging (before the first block), 64 KB
 constexpr uint32_t kTcOffV = kTcOffK + 2u * kTcKvBytes;
-constexpr uint32_t kTcOffP = kTcOffV + 2u * kTcKvBytes;      // V is double-buffered
-constexpr uint32_t kTcOffRaw = kTcOffP + kTcPBytes;
+constexpr uint32_t kTcOffRaw = kTcOffV + 2u * kTcKvBytes;    // V is double-buffered
 constexpr int kTcRawStages = 1;                  // producers take the code words into registers and release it at once
 constexpr uint32_t kTcOffLut = kTcOffRaw + (uint32_t)kTcRawStages * kTcRawStage;
 constexpr uint32_t kTcOffBars = kTcOffLut + kTcLutBytes;
@@ -62,7 +62,7 @@ constexpr uint32_t kTcOffBars = kTcOffLut + kTcLutBytes;
 constexpr uint32_t kTcOffRed = kTcOffBars + 144u;                 // 16 ints: per-warp key-range reduction
 constexpr uint32_t kTcSmemBytes = kTcOffRed + 64u;
 constexpr int kTcStageStride = 257;              // floats per row of the epilogue staging
-static_assert(kTcRows * kTcStageStride * 4 <= (int)kTcOffRaw, "epilogue staging must not reach the raw ring");
+static_assert(kTcRows * kTcStageStride * 4 <= (int)kTcOffLut, "epilogue staging (over the tiles and the idle staging buffer) must not reach the table");
 constexpr uint32_t kTcTmemCols = 512;
 constexpr uint32_t kTcColO = 0, kTcColS = 256;   // S: two buffers of 64 columns
 constexpr uint32_t kTcColQ = 384;                // Q' as the A operand: 256 fp16 per row = 128 columns
@@ -193,7 +193,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) tq4_attention_prefill_tc_kernel
         return;
     }
     uint8_t* gen = smem_raw;
-    const uint32_t k_t = base + kTcOffK, v_t = base + kTcOffV, p_t = base + kTcOffP;
+    const uint32_t k_t = base + kTcOffK, v_t = base + kTcOffV;
     const uint32_t q_stage = base + kTcOffQStage;
     const uint32_t raw = base + kTcOffRaw, lut = base + kTcOffLut, bars = base + kTcOffBars;
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + kTcOffBars + 128);
@@ -360,7 +360,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) tq4_attention_prefill_tc_kernel
         constexpr uint32_t kIdescQk = tc_idesc(kTcRows, kTcKeys, 0);
         constexpr uint32_t kIdescPv = tc_idesc(kTcRows, kHeadDim, 1);
         const uint64_t desc_k = tc_smem_desc(k_t, 16u, 1024u);
-        const uint64_t desc_p = tc_smem_desc(p_t, 16u, 1024u);
         const uint64_t desc_v = tc_smem_desc(v_t, kTcKeys * 128u, 1024u);
 #pragma unroll 1
         for (int j = 0; j <= nblocks; ++j) {
@@ -399,9 +398,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) tq4_attention_prefill_tc_kernel
                 if (lane == 0) {
 #pragma unroll
                     for (int ks = 0; ks < 4; ++ks) {
-                        const uint64_t a = desc_p + (uint64_t)(2 * ks);
+                        // A = P(i): fp16 pairs the consumers wrote over the first 32 columns of score buffer i & 1
                         const uint64_t b = desc_v + (uint64_t)((i & 1) * (kTcKvBytes / 16) + (2048 / 16) * ks);
-                        tc_mma_f16(tmem + kTcColO, a, b, kIdescPv, (i > 0 || ks > 0) ? 1u : 0u);
+                        tc_mma_f16_ts(tmem + kTcColO, tmem + kTcColS + 64u * (uint32_t)(i & 1) + 8u * (uint32_t)ks, b, kIdescPv,
+                                      (i > 0 || ks > 0) ? 1u : 0u);
                     }
                     tc_commit(bar(kBarPv));
                     tc_commit(bar(kBarEmptyV0 + (i & 1)));
@@ -525,7 +525,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) tq4_attention_prefill_tc_kernel
         }
     } else {
         // ======================= consumers: MMA issue, softmax, P, rescale =========================
-        const int row = tid;
         const uint32_t lane_base = (uint32_t)(32 * wid) << 16;
         const uint32_t t_o = tmem + lane_base + kTcColO, t_s = tmem + lane_base + kTcColS;
         float m_ref = -1e30f;
@@ -588,21 +587,19 @@ __global__ void __launch_bounds__(kTcThreads, 1) tq4_attention_prefill_tc_kernel
             W34_PROF(4)
             float ls4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
             const float m_use = (m_ref < -1e29f) ? 0.0f : m_ref;     // nothing visible yet: every P is 0
-            const uint32_t prow = p_t + (uint32_t)row * 128u;
+            // P as fp16 pairs goes where its own scores were: the first 32 columns of this score buffer
+            // (A operand of the output product, lane = row, key 2 i in the low half of column i)
+            uint32_t pk[32];
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                uint32_t h[4];
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    // masked scores are -1e30: ex2 gives exactly 0 against any finite reference
-                    const float pa = ex2(sv[8 * c + 2 * k] - m_use), pb = ex2(sv[8 * c + 2 * k + 1] - m_use);
-                    ls4[k] += pa + pb;
-                    h[k] = pack_half2(pa, pb);
-                }
-                sts128(prow + (uint32_t)((c ^ (row & 7)) << 4), h[0], h[1], h[2], h[3]);
+            for (int i = 0; i < 32; ++i) {
+                // masked scores are -1e30: ex2 gives exactly 0 against any finite reference
+                const float pa = ex2(sv[2 * i] - m_use), pb = ex2(sv[2 * i + 1] - m_use);
+                ls4[i & 3] += pa + pb;
+                pk[i] = pack_half2(pa, pb);
             }
+            tc_st32(t_sj, pk);
+            tc_wait_st();
             l_run = l_run * alpha + ((ls4[0] + ls4[1]) + (ls4[2] + ls4[3]));
-            fence_proxy_async();
             tc_fence_before();
             mbar_arrive(bar(kBarPReady));
             W34_PROF(5)
