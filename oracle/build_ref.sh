@@ -12,9 +12,9 @@
 # The library is the bit-exactness checker for the TQ4 append path and the
 # dequant-then-attend checker for attention.  The product never links or loads it.
 #
-# usage: oracle/build_ref.sh [reference_root]      (default /root/reference)
+# usage: oracle/build_ref.sh [reference_root]      (default: $WARP34_REFERENCE_ROOT, else the checkout next to this repository)
 set -euo pipefail
-REF="${1:-/root/reference}"
+REF="${1:-${WARP34_REFERENCE_ROOT:-$(cd "$(dirname "$0")/../.." && pwd)/reference}}"
 HERE="$(cd "$(dirname "$0")" && pwd)"
 OUT="$HERE/_ref"
 CSRC="$REF/crates/warp34-kernels/csrc"
