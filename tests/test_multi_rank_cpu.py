@@ -26,6 +26,23 @@ def test_sharding_helpers():
     assert [sharding.split_pages(20, 4, r) for r in range(4)] == [(0, 16), (16, 20), (20, 20), (20, 20)]
 
 
+def test_per_rank_seeds_of_eight_ranks_are_accepted():
+    """The bench seeds rank r's workload with seed + 1000 * r and the context fill multiplies that
+    by a large prime: every generator in synth must take the result (numpy's seeds are 32-bit)."""
+    from warp34_b200 import synth
+    seen = set()
+    for cfg in synth.CONFIGS.values():
+        seed = cfg[-1]
+        for rank in range(8):
+            s = (seed + 1000 * rank) * 1000003 + 63 * 1009 + 131072
+            k, v = synth.make_kv(2, 2, s)
+            assert k.shape == (2, 512) and v.shape == (2, 512)
+            ctx = synth.context_lengths(4, 10, 20, s)
+            assert ctx.min() >= 10 and ctx.max() <= 20
+            seen.add(tuple(synth.outlier_channels(2, s).ravel()))
+    assert len(seen) > 8
+
+
 def _worker(rank, world, port, tmp):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
     sys.path.insert(0, ROOT)

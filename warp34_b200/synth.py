@@ -30,7 +30,7 @@ def _grid(x_bf16):
 
 
 def outlier_channels(num_heads, seed):
-    g = np.random.RandomState(seed + 7919)
+    g = np.random.RandomState((seed + 7919) % (1 << 32))  # numpy seeds are 32-bit; per-rank seeds exceed that
     return np.stack([np.sort(g.choice(HEAD_DIM, 4, replace=False)) for _ in range(num_heads)])
 
 
@@ -58,7 +58,7 @@ def make_q(num_tokens, num_q_heads, seed, device="cpu"):
 
 
 def context_lengths(batch, lo, hi, seed):
-    g = np.random.RandomState(seed)
+    g = np.random.RandomState(seed % (1 << 32))
     return g.randint(lo, hi + 1, size=batch).astype(np.int64)
 
 
