@@ -377,7 +377,9 @@ def run_bf16_kv(args):
                      # algorithmic bytes), scaled by the bytes of this run; null for the other workloads
                      "traffic": (kv_bytes * (1.388 / 1.343) if args.config == "cfg1_batched_decode" and not reference else None)},
             "attended_tokens_per_s": float(sum(wl.ctx) + n_tok) / (attn_ms * 1e-3),
-            "gpu_launches": 4 * args.steps, "clocks": sampler.summary(t_begin, t_end)}
+            **({"exchange": "peer", "exchange_equals_allgather_merge": bool(exchange_ok and peer_px.status() == 0)}
+           if peer_px is not None else {}),
+        "gpu_launches": 4 * args.steps, "clocks": sampler.summary(t_begin, t_end)}
     if reference:
         line["impl"] = "reference"
         line["roofline"]["kernel"] = "reference paged_attention_gqa_bf16_kernel"
@@ -391,6 +393,8 @@ def main():
     ap.add_argument("--steps", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--exchange", default="peer", choices=["nccl", "peer"],
+                    help="page-sharded long context: all-gather over NCCL + merge, or one kernel over peer-mapped mailboxes")
     ap.add_argument("--config", default="cfg1_batched_decode")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--append-tokens", type=int, default=32768, help="tokens of the bulk-append measurement")
@@ -431,11 +435,22 @@ def main():
                              slack_pages=64 + batch * grow_pages)
     step = kv.DecodeStep(wl.layer, wl.seqs, hq, max_q_len=q_len, scratch_bytes=64 << 20, device=dev,
                          extra_blocks=grow_pages)
-    triples = gathered = None
+    triples = gathered = peer_px = None
+    exchange_ok = True
     if sharded:
         import torch.distributed as dist
         triples = torch.zeros(batch * q_len * hq, 258, dtype=torch.float32, device=dev)
         gathered = torch.zeros(world * batch * q_len * hq, 258, dtype=torch.float32, device=dev)  # rank-major
+        if args.exchange == "peer":
+            # mailboxes in symmetric memory: the exchange and the merge are one kernel over NVLink
+            try:
+                peer_px = kv.PeerExchange.symmetric(dist.group.WORLD, batch * q_len * hq, dev)
+            except Exception as exc:  # no peer mapping on this box: every rank falls back together
+                sys.stderr.write(f"rank {rank}: peer mailboxes unavailable ({exc}); using the NCCL all-gather\n")
+            have = torch.tensor([1 if peer_px is not None else 0], device=dev)
+            dist.all_reduce(have, op=dist.ReduceOp.MIN)
+            if int(have.item()) == 0:
+                peer_px = None
     wl.fill_context(step.ex, seed + 1000 * rank, chunk_tokens=32768)  # untimed: KV pool resident in HBM
     n_tok = batch * q_len
     k_new, v_new = synth.make_kv(n_tok, hkv, seed + 17)
@@ -473,8 +488,11 @@ def main():
     def attend(desc_):
         if sharded:
             kv.paged_attention_partial(step.ex, wl.layer, desc_, step.q_dev, triples, hq)
-            dist.all_gather_into_tensor(gathered, triples)
-            kv.merge_shards(step.ex, gathered.view(world, -1, 258), step.out_dev)
+            if peer_px is not None:
+                peer_px.exchange_merge(step.ex, triples, step.out_dev)
+            else:
+                dist.all_gather_into_tensor(gathered, triples)
+                kv.merge_shards(step.ex, gathered.view(world, -1, 258), step.out_dev)
         else:
             kv.paged_attention(step.ex, wl.layer, desc_, step.q_dev, step.out_dev, hq, lib=lib)
 
@@ -488,8 +506,21 @@ def main():
         if ev is not None:
             ev[2].record()
 
+    if peer_px is not None:
+        # one step each way: the fused exchange must reproduce the all-gather + merge bit for bit
+        barrier(world)
+        device_step()
+        fused = step.out_dev.clone()
+        saved, peer_px = peer_px, None
+        attend(desc)
+        peer_px = saved
+        torch.cuda.synchronize()
+        if not torch.equal(fused.view(torch.int16), step.out_dev.view(torch.int16)) or peer_px.status() != 0:
+            exchange_ok = False   # reported in the JSON line; the run goes on so that every rank leaves in step
+            sys.stderr.write(f"rank {rank}: fused exchange differs from all-gather + merge (status {peer_px.status()})\n")
     sampler = ClockSampler(local)
     sampler.start()
+    barrier(world)
     for _ in range(args.warmup):
         device_step()
     barrier(world)
@@ -507,9 +538,9 @@ def main():
     eager_ms_per_step = ms_per_step
     # The same K steps replayed from one CUDA graph (how the reference's engine runs a decode step,
     # crates/warp34-host/src/model/graphs.rs:199-259): launch gaps between the four kernels go away.
-    # Not for the page-sharded case (its collective stays outside a graph here) nor the reference arm.
+    # The page-sharded case captures its NCCL all-gather in the same graph.  Not for the reference arm.
     graph_used = False
-    if not args.no_graph and not sharded and not reference:
+    if not args.no_graph and not reference:
         try:
             g = torch.cuda.CUDAGraph()
             side = torch.cuda.Stream()
@@ -619,7 +650,9 @@ def main():
                                f"d256, TQ4 pages of 16, step = append {q_len} token/seq + decode attention",
                    "kv_bytes_per_step_per_gpu": kv_bytes, "tokens_in_cache_per_gpu": int(sum(wl.ctx)),
                    "l2": "KV read per step (>1.3 GB) is larger than L2; no flush needed",
-                   "per_gpu_batch": batch, "parallelism": (f"pages of one sequence sharded x{world}, (m, l, acc) triples all-gathered over NCCL"
+                   "per_gpu_batch": batch, "parallelism": ((f"pages of one sequence sharded x{world}, (m, l, acc) triples exchanged and merged by one kernel over peer-mapped memory"
+                                    if peer_px is not None else
+                                    f"pages of one sequence sharded x{world}, (m, l, acc) triples all-gathered over NCCL")
                                    if sharded else f"batch-sharded x{world}, no collective")},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "peak_kind": f"of {peak_kind}", "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,
@@ -632,6 +665,8 @@ def main():
         "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": (step.h2d_bytes_total - h2d_before) / e2e_steps,
                 "d2h_bytes_per_step": step.d2h_bytes, "cuda_graph_replay": use_graph,
                 **({"speculative_rollback": rollback} if rollback else {})},
+        **({"exchange": "peer", "exchange_equals_allgather_merge": bool(exchange_ok and peer_px.status() == 0)}
+           if peer_px is not None else {}),
         "gpu_launches": 4 * args.steps, "cuda_graph_replay": graph_used, "eager_ms_per_step": eager_ms_per_step,
         "clocks": clocks,
         "append_tokens_per_s": n_tok / (append_ms * 1e-3), "append_ms": append_ms,

@@ -251,6 +251,42 @@ int warp34_paged_attention_merge_shards_f16(const warp34_exec* ex, const float* 
                                             int num_shards, int64_t num_rows, void* attn_out);
 
 /*
+ * Page-sharded attention without a library collective: the exchange of the (acc, m, l) triples and
+ * their merge in ONE kernel over peer-mapped memory (NVLink).  Every rank owns a mailbox that all
+ * ranks have mapped (CUDA IPC / symmetric memory; the caller does the mapping):
+ *
+ *   inbox  float    [2][world][max_rows][258]   parity of the step, source rank, row
+ *   flags  uint32_t [world][max_rows]           step number of the last triple that arrived
+ *
+ * and, private to the rank, steps uint32_t [max_rows] (the number of steps this rank has run).  All
+ * three start as zeros.  A call makes one warp per row: it stores its own triple row into every
+ * peer's inbox[step & 1][rank][row], publishes the step number in the peer's flags[rank][row] with
+ * a system-scope release, waits (acquire, bounded) for every peer's flag of this row to reach the
+ * step, merges the world triples exactly as warp34_paged_attention_merge_shards_f16 does (shards in
+ * rank order, so every rank computes bit-identical output) and writes fp16 [num_rows, 256].
+ * Every rank must make the same sequence of calls with the same num_rows.  The step number lives
+ * in device memory, so a captured CUDA graph can be replayed.  A wait that runs out (wait_limit
+ * polls of about 0.25 us; 0 = about one second) ORs 1 into *status (device memory, may be null),
+ * leaves the row's output untouched and still counts the step, so later steps stay aligned.
+ * No counterpart in the reference, which has no multi-GPU attention.
+ */
+#define WARP34_B200_MAX_PEERS 8
+typedef struct warp34_peer_mailboxes {
+    int32_t world;                             /* 1..8 */
+    int32_t rank;
+    int64_t max_rows;
+    uint64_t inbox[WARP34_B200_MAX_PEERS];     /* rank w's inbox as mapped in THIS process */
+    uint64_t flags[WARP34_B200_MAX_PEERS];     /* rank w's flags as mapped in THIS process */
+    uint64_t steps;                            /* this rank's private step counters */
+    uint64_t status;                           /* int32_t in device memory, or 0 */
+    uint32_t wait_limit;
+    uint32_t reserved;
+} warp34_peer_mailboxes;
+
+int warp34_paged_attention_exchange_merge_f16(const warp34_exec* ex, const warp34_peer_mailboxes* boxes,
+                                              const float* triples, int64_t num_rows, void* attn_out);
+
+/*
  * Copies the first `rows` token rows (all kv heads, K and V) of page src_page to page dst_page
  * of one layer: the device half of copy-on-write for a shared partial tail page
  * (docs/contracts/cache-layout.md:106-110 specifies the copy; the reference never implemented

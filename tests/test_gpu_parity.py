@@ -374,6 +374,82 @@ def test_page_sharded_partials_merge_to_the_unsharded_result(env):
     assert (merged2.cpu().numpy().view(np.uint16) == merged.cpu().numpy().view(np.uint16)).all()
 
 
+def _mailbox_views(kv, buf, world, max_rows):
+    n_in = 2 * world * max_rows * 258 * 4
+    inbox = buf[:n_in].view(torch.float32).view(2, world, max_rows, 258)
+    flags = buf[n_in:n_in + world * max_rows * 4].view(torch.int32).view(world, max_rows)
+    return inbox, flags
+
+
+def test_exchange_merge_over_mailboxes_equals_the_gathered_merge(env):
+    """Three ranks played one after another on one device (kernels that wait on one another never
+    run side by side on one GPU): before rank r runs, the host plays the stores of the ranks that
+    have not run yet; ranks that have run delivered theirs through the kernel.  Rank 2's inbox is
+    filled by kernels only.  Every rank's output must equal the merge of the gathered triples
+    bit for bit, over several steps (both mailbox parities, the device-side step counter)."""
+    kv = env["kv"]
+    world, rows, max_rows = 3, 10, 12
+    g = torch.Generator(device="cuda")
+    g.manual_seed(99)
+    bufs = [torch.zeros(kv.PeerExchange.mailbox_bytes(world, max_rows), dtype=torch.uint8, device="cuda")
+            for _ in range(world)]
+    px = [kv.PeerExchange.over_buffers(r, max_rows, bufs, wait_limit=2000) for r in range(world)]
+    for step in range(1, 5):
+        triples = torch.randn(world, rows, 258, generator=g, device="cuda")
+        triples[:, :, 256] = torch.randn(world, rows, generator=g, device="cuda") * 4.0  # m
+        triples[:, :, 257] = torch.rand(world, rows, generator=g, device="cuda") + 0.1   # l > 0
+        if step == 3:
+            triples[1, :, 257] = 0.0  # a shard without keys
+        want = torch.zeros(rows, 256, dtype=torch.float16, device="cuda")
+        kv.merge_shards(env["ex"], triples, want)
+        for r in range(world):
+            inbox, flags = _mailbox_views(kv, bufs[r], world, max_rows)
+            for w in range(r + 1, world):  # peers that have not run this step yet
+                inbox[step & 1, w, :rows] = triples[w]
+                flags[w, :rows] = step
+            out = torch.full((rows, 256), 7.0, dtype=torch.float16, device="cuda")
+            px[r].exchange_merge(env["ex"], triples[r].contiguous(), out)
+            torch.cuda.synchronize()
+            assert px[r].status() == 0
+            assert torch.equal(out.view(torch.int16), want.view(torch.int16)), (step, r)
+        # what the kernels delivered is what the host would have stored
+        for r in range(world):
+            inbox, flags = _mailbox_views(kv, bufs[r], world, max_rows)
+            for w in range(world):
+                if w != r:
+                    assert torch.equal(inbox[step & 1, w, :rows], triples[w])
+                    assert (flags[w, :rows] == step).all() and (flags[w, rows:] == 0).all()
+        assert (px[0].private[:rows] == step).all()
+
+
+def test_exchange_merge_wait_runs_out_with_a_status(env):
+    """A flag that nothing sets: the bounded wait gives up, reports through the status word, leaves
+    the output alone and still counts the step, so the next step (its peer delivered) is right."""
+    kv = env["kv"]
+    world, rows = 2, 5
+    bufs = [torch.zeros(kv.PeerExchange.mailbox_bytes(world, rows), dtype=torch.uint8, device="cuda")
+            for _ in range(world)]
+    px = kv.PeerExchange.over_buffers(0, rows, bufs, wait_limit=300)
+    triples = torch.rand(world, rows, 258, device="cuda") + 0.5
+    out = torch.full((rows, 256), 7.0, dtype=torch.float16, device="cuda")
+    px.exchange_merge(env["ex"], triples[0].contiguous(), out)
+    torch.cuda.synchronize()
+    assert px.status() == 1
+    assert (out == 7.0).all()
+    inbox, flags = _mailbox_views(kv, bufs[0], world, rows)
+    inbox[0, 1] = triples[1]   # step 2 uses parity 0
+    flags[1] = 2
+    px.exchange_merge(env["ex"], triples[0].contiguous(), out)
+    torch.cuda.synchronize()
+    want = torch.zeros(rows, 256, dtype=torch.float16, device="cuda")
+    kv.merge_shards(env["ex"], triples, want)
+    torch.cuda.synchronize()
+    assert torch.equal(out.view(torch.int16), want.view(torch.int16))
+    assert px.status() == 1  # sticky
+    with pytest.raises(Exception):
+        px.exchange_merge(env["ex"], torch.zeros(rows + 1, 258, device="cuda"), out)  # more rows than the mailbox holds
+
+
 def test_copy_on_write_tail_page_gives_the_unshared_result(env):
     """A request attaches a 68-token prefix whose last page is shared and partial, gets a private
     copy of that page (w34_seq_prepare_append + warp34_kv_page_copy), appends 9 tokens: its

@@ -1900,6 +1900,101 @@ __global__ void __launch_bounds__(128) tq4_attention_merge_shards_kernel(
     for (int j = 0; j < 8; ++j) store_act(attn_out, (size_t)row * kHeadDim + lane + 32 * j, apply_sign(acc[j], lane + 32 * j), io_bf16);
 }
 
+// ---- exchange + merge over peer-mapped mailboxes -------------------------------------------------
+__device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// One warp per row.  Stores the row's triple into every peer's inbox, publishes the step number,
+// waits (bounded) for the peers' triples of the same step and merges all of them in rank order.
+// Mailbox rows alternate between two buffers by step parity: a peer can run at most one step
+// ahead of a rank that has not yet read its inbox (its own next wait needs that rank's next
+// store), so the buffer being read is never the one being written.
+__global__ void __launch_bounds__(128) tq4_attention_exchange_merge_kernel(
+    const warp34_peer_mailboxes mb, const float* __restrict__ mine, long long rows, void* __restrict__ attn_out) {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const long long row = (long long)blockIdx.x * 4 + wid;
+    if (row >= rows) return;
+    uint32_t* steps = reinterpret_cast<uint32_t*>((uintptr_t)mb.steps);
+    const uint32_t step = steps[row] + 1u;  // every lane reads the same word; lane 0 stores it last
+    const size_t per_rank = (size_t)mb.max_rows * kRowTripleFloats;
+    const size_t slot = ((size_t)(step & 1u) * mb.world + mb.rank) * per_rank + (size_t)row * kRowTripleFloats;
+    const float* src = mine + (size_t)row * kRowTripleFloats;
+
+    // own triple: 258 floats, kept in registers for the merge as well
+    float t_own[9];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) t_own[j] = src[lane + 32 * j];
+    t_own[8] = (lane < 2) ? src[kHeadDim + lane] : 0.0f;
+    for (int w = 0; w < mb.world; ++w) {
+        if (w == mb.rank) continue;
+        float* dst = reinterpret_cast<float*>((uintptr_t)mb.inbox[w]) + slot;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) dst[lane + 32 * j] = t_own[j];
+        if (lane < 2) dst[kHeadDim + lane] = t_own[8];
+    }
+    __threadfence_system();  // every lane's stores are ordered before the flag of lane w below
+    __syncwarp();
+    if (lane < mb.world && lane != mb.rank) {
+        uint32_t* f = reinterpret_cast<uint32_t*>((uintptr_t)mb.flags[lane]) + (size_t)mb.rank * mb.max_rows + row;
+        st_release_sys_u32(f, step);
+    }
+
+    // wait for the peers: lane w watches rank w's flag in this rank's own mailbox
+    bool ok = true;
+    if (lane < mb.world && lane != mb.rank) {
+        const uint32_t* f = reinterpret_cast<const uint32_t*>((uintptr_t)mb.flags[mb.rank]) + (size_t)lane * mb.max_rows + row;
+        const uint32_t limit = mb.wait_limit ? mb.wait_limit : (1u << 22);
+        uint32_t n = 0;
+        // steps are compared as a signed distance so that the counter may wrap
+        while ((int32_t)(ld_acquire_sys_u32(f) - step) < 0) {
+            if (++n >= limit) { ok = false; break; }
+            __nanosleep(200);
+        }
+    }
+    ok = __all_sync(0xffffffffu, ok);
+    if (lane == 0) steps[row] = step;
+    if (!ok) {
+        if (lane == 0 && mb.status) atomicOr(reinterpret_cast<int*>((uintptr_t)mb.status), 1);
+        return;
+    }
+
+    const float* inbox = reinterpret_cast<const float*>((uintptr_t)mb.inbox[mb.rank]) +
+                         (size_t)(step & 1u) * mb.world * per_rank + (size_t)row * kRowTripleFloats;
+    const float m_own = __shfl_sync(0xffffffffu, t_own[8], 0), l_own = __shfl_sync(0xffffffffu, t_own[8], 1);
+    float m_tot = -1e30f;
+    for (int w = 0; w < mb.world; ++w) {
+        const float* t = inbox + (size_t)w * per_rank;
+        const float ls = (w == mb.rank) ? l_own : __ldcg(t + kHeadDim + 1);
+        const float ms = (w == mb.rank) ? m_own : __ldcg(t + kHeadDim);
+        if (ls > 0.0f) m_tot = fmaxf(m_tot, ms);
+    }
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    float l_tot = 0.0f;
+    for (int w = 0; w < mb.world; ++w) {
+        const float* t = inbox + (size_t)w * per_rank;
+        const bool own = (w == mb.rank);
+        const float ls = own ? l_own : __ldcg(t + kHeadDim + 1);
+        if (ls > 0.0f) {
+            const float wgt = ex2((own ? m_own : __ldcg(t + kHeadDim)) - m_tot);
+            l_tot += ls * wgt;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] += (own ? t_own[j] : __ldcg(t + lane + 32 * j)) * wgt;
+        }
+    }
+    const float inv_l = (l_tot > 0.0f) ? (1.0f / (l_tot * kLutScale)) : 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] *= inv_l;
+    wht256_lanes(acc, lane);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) store_act(attn_out, (size_t)row * kHeadDim + lane + 32 * j, apply_sign(acc[j], lane + 32 * j), 0);
+}
+
 // Copies the first `rows` token rows of every kv head of one page to another page of the same
 // slabs (copy-on-write of a shared partial tail page).  One block per (kv head, K or V).
 __global__ void __launch_bounds__(128) kv_page_copy_kernel(const warp34_kv_layer_layout layout, int src_page,
@@ -2285,6 +2380,22 @@ extern "C" int warp34_paged_attention_merge_shards_f16(const warp34_exec* ex, co
     if (num_rows == 0) return 0;
     w34::tq4_attention_merge_shards_kernel<<<(unsigned)((num_rows + 3) / 4), 128, 0, (cudaStream_t)ex->stream>>>(
         triples, num_shards, (long long)num_rows, attn_out, 0);
+    return (int)cudaGetLastError();
+}
+
+extern "C" int warp34_paged_attention_exchange_merge_f16(const warp34_exec* ex, const warp34_peer_mailboxes* boxes,
+                                                         const float* triples, int64_t num_rows, void* attn_out) {
+    if (ex == nullptr || boxes == nullptr || triples == nullptr || attn_out == nullptr || num_rows < 0 ||
+        boxes->world < 1 || boxes->world > WARP34_B200_MAX_PEERS || boxes->rank < 0 ||
+        boxes->rank >= boxes->world || num_rows > boxes->max_rows || boxes->steps == 0) {
+        return (int)cudaErrorInvalidValue;
+    }
+    for (int w = 0; w < boxes->world; ++w) {
+        if (boxes->inbox[w] == 0 || boxes->flags[w] == 0) return (int)cudaErrorInvalidValue;
+    }
+    if (num_rows == 0) return 0;
+    w34::tq4_attention_exchange_merge_kernel<<<(unsigned)((num_rows + 3) / 4), 128, 0, (cudaStream_t)ex->stream>>>(
+        *boxes, triples, (long long)num_rows, attn_out);
     return (int)cudaGetLastError();
 }
 

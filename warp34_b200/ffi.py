@@ -62,6 +62,14 @@ class PoolStats(C.Structure):
                 ("shared_pages", C.c_int32), ("active_pages", C.c_int32)]
 
 
+class PeerMailboxes(C.Structure):
+    _fields_ = [("world", C.c_int32), ("rank", C.c_int32), ("max_rows", C.c_int64),
+                ("inbox", C.c_uint64 * 8), ("flags", C.c_uint64 * 8),
+                ("steps", C.c_uint64), ("status", C.c_uint64),
+                ("wait_limit", C.c_uint32), ("reserved", C.c_uint32)]
+
+
+assert C.sizeof(PeerMailboxes) == 168
 assert C.sizeof(Exec) == 32 and C.sizeof(KvLayerLayout) == 104 and C.sizeof(AttentionBatch) == 96
 
 _P = C.POINTER
@@ -80,6 +88,8 @@ _KERNEL_SIGS = {
     "warp34_paged_attention_partial_f16": (C.c_int, [_P(Exec), _P(KvLayerLayout), _P(AttentionBatch),
                                                       C.c_void_p, C.c_void_p, C.c_int]),
     "warp34_paged_attention_merge_shards_f16": (C.c_int, [_P(Exec), C.c_void_p, C.c_int, C.c_int64, C.c_void_p]),
+    "warp34_paged_attention_exchange_merge_f16": (C.c_int, [_P(Exec), _P(PeerMailboxes), C.c_void_p, C.c_int64,
+                                                             C.c_void_p]),
     "warp34_paged_attention_f16_static_scratch": (C.c_int, [C.c_size_t, _P(KvLayerLayout), _P(AttentionBatch),
                                                              C.c_void_p, C.c_void_p, C.c_int, _P(C.c_size_t)]),
     "warp34_kv_page_copy": (C.c_int, [_P(Exec), _P(KvLayerLayout), C.c_int32, C.c_int32, C.c_int32]),

@@ -8,6 +8,7 @@ two kernel calls of run_attention_block (crates/warp34-host/src/model/forward.rs
 torch is used only to own device memory and streams.
 """
 import ctypes as C
+import os
 
 import numpy as np
 import torch
@@ -397,6 +398,68 @@ def merge_shards(ex, triples, out, lib=None):
     shards, rows = triples.shape[0], triples[0].numel() // 258
     rc = lib.warp34_paged_attention_merge_shards_f16(C.byref(ex.ex), triples.data_ptr(), shards, rows, out.data_ptr())
     _check(rc, "warp34_paged_attention_merge_shards_f16")
+
+
+class PeerExchange:
+    """Mailboxes of warp34_paged_attention_exchange_merge_f16: per rank one buffer
+    [inbox fp32 [2][world][max_rows][258] | flags u32 [world][max_rows]] that every rank has mapped,
+    plus this rank's private step counters and status word.
+
+    `symmetric()` allocates the buffers in torch's symmetric memory (peer-mapped over NVLink) for a
+    process group; `over_buffers()` takes addresses the caller mapped itself (tests hand it several
+    buffers of one device to play the peers' parts)."""
+
+    @staticmethod
+    def mailbox_bytes(world, max_rows):
+        return 2 * world * max_rows * 258 * 4 + world * max_rows * 4
+
+    def __init__(self, world, rank, max_rows, base_addrs, device, wait_limit=0, keep=()):
+        self.world, self.rank, self.max_rows = world, rank, max_rows
+        self.private = torch.zeros(max_rows + 1, dtype=torch.int32, device=device)  # steps | status
+        self._keep = keep
+        mb = ffi.PeerMailboxes()
+        mb.world, mb.rank, mb.max_rows, mb.wait_limit = world, rank, max_rows, wait_limit
+        inbox_bytes = 2 * world * max_rows * 258 * 4
+        for w in range(world):
+            mb.inbox[w] = int(base_addrs[w])
+            mb.flags[w] = int(base_addrs[w]) + inbox_bytes
+        mb.steps = self.private.data_ptr()
+        mb.status = self.private.data_ptr() + 4 * max_rows
+        self.mb = mb
+
+    @classmethod
+    def over_buffers(cls, rank, max_rows, buffers, wait_limit=0):
+        world = len(buffers)
+        for b in buffers:
+            assert b.dtype == torch.uint8 and b.numel() >= cls.mailbox_bytes(world, max_rows)
+        return cls(world, rank, max_rows, [b.data_ptr() for b in buffers], buffers[rank].device,
+                   wait_limit=wait_limit, keep=tuple(buffers))
+
+    @classmethod
+    def symmetric(cls, group, max_rows, device, wait_limit=0):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        # plain peer mappings only: the mailboxes are never bound to an NVSwitch multicast object
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        buf = symm.empty(cls.mailbox_bytes(world, max_rows), dtype=torch.uint8, device=device)
+        buf.zero_()
+        handle = symm.rendezvous(buf, group)
+        torch.cuda.synchronize()
+        dist.barrier(group)  # every mailbox is zeroed before anyone stores into it
+        return cls(world, rank, max_rows, list(handle.buffer_ptrs), device, wait_limit=wait_limit,
+                   keep=(buf, handle))
+
+    def status(self):
+        return int(self.private[self.max_rows].item())
+
+    def exchange_merge(self, ex, triples, out, lib=None):
+        """triples fp32 [rows, 258] of this rank -> out fp16 [rows, 256] merged over all ranks."""
+        lib = lib or ffi.kernels()
+        rows = triples.numel() // 258
+        rc = lib.warp34_paged_attention_exchange_merge_f16(C.byref(ex.ex), C.byref(self.mb), triples.data_ptr(),
+                                                           rows, out.data_ptr())
+        _check(rc, "warp34_paged_attention_exchange_merge_f16")
 
 
 def kv_page_copy(ex, layer, src_page, dst_page, rows, lib=None):
