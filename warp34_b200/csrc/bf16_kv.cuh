@@ -443,6 +443,8 @@ extern "C" int warp34_paged_attention_bf16(const warp34_exec* ex, const warp34_k
     p.rows_per_group = w34::kBfRows;
     p.q_scale = batch->sm_scale * 1.4426950408889634f;
     p.natural = 1;
+    p.qfrag = nullptr;
+    p.q_groups_max = 0;
     p.smem_bytes = (uint32_t)(w34::kBfWarps * w34::kBfStages * w34::kBfStageBytes);
     cudaStream_t st = (cudaStream_t)ex->stream;
     w34::tq4_attention_plan_kernel<<<1, 32, 0, st>>>(p);

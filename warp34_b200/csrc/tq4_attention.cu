@@ -168,7 +168,8 @@ constexpr float kLutScale = 0.954016f;
 
 // Scratch header written by the plan kernel.
 struct PlanHeader {
-    int32_t status;        // 0 ok; bit 0: an mbarrier wait gave up
+    int32_t status;        // 0 ok; bit 0: an mbarrier wait gave up; bit 1: shared-memory window too small;
+                           // bit 2: a request's q_len exceeded batch.max_q_len (its extra rows were dropped)
     int32_t total_items;
     int32_t total_units;
     int32_t units_per_warp;
@@ -198,13 +199,34 @@ struct StreamParams {
     int rows_per_group;    // query rows per work item: 8 (one warp per item) or 8 * NT (teams)
     float q_scale;         // sm_scale * log2(e) / kLutScale, folded into Q'
     int natural;           // partials are in natural (unrotated, unscaled) coordinates: uncompressed KV
+    uint32_t* qfrag;       // rotated queries as MMA fragments, written by the plan launch (or null)
+    int q_groups_max;      // row groups per (request, kv head) that qfrag has room for
 };
 
 __device__ __forceinline__ int32_t* plan_array(uint8_t* scratch, int which, int num_reqs) {
     return reinterpret_cast<int32_t*>(scratch + sizeof(PlanHeader)) + (size_t)which * (num_reqs + 1);
 }
 
-__global__ void __launch_bounds__(32) tq4_attention_plan_kernel(const StreamParams p) {
+#ifndef W34_SPLIT_Q
+#define W34_SPLIT_Q 0   // second QK MMA with the fp16 rounding residual of Q'
+#endif
+// Words per lane of one work item's query fragments: 16 k-steps x 2 B-fragment words of fp16(Q'),
+// plus 16 words of residual bytes when the second QK product is compiled in.
+constexpr int kQFragWords = W34_SPLIT_Q ? 48 : 32;
+__host__ __device__ inline size_t qfrag_item_bytes() { return (size_t)kQFragWords * 32 * sizeof(uint32_t); }
+__device__ void qprep_block(const StreamParams& p, int idx);
+constexpr int kPlanThreads = 32 * kRowsPerGroup;  // the query-fragment blocks use one warp per query row
+
+// Block 0 plans the split.  Blocks 1.. (one-warp items only) each rotate and scale the query rows
+// of one (request, kv head, row group) and store them as the B fragments of S^T = K Q'^T, so that
+// the stream kernel's warps (several per item, and again for every further item a warp reaches)
+// only load them.  The fragments are indexed without the plan, so both run side by side.
+__global__ void __launch_bounds__(kPlanThreads) tq4_attention_plan_kernel(const StreamParams p) {
+    if (blockIdx.x > 0) {
+        qprep_block(p, (int)blockIdx.x - 1);
+        return;
+    }
+    if (threadIdx.x >= 32) return;
     const int lane = threadIdx.x;
     const int R = p.batch.num_reqs;
     int32_t* unit_prefix = plan_array(p.scratch, 0, R);
@@ -214,6 +236,7 @@ __global__ void __launch_bounds__(32) tq4_attention_plan_kernel(const StreamPara
     int32_t* ngroups_a = plan_array(p.scratch, 4, R);
     const int hkv = p.layout.local_kv_heads;
     int unit_carry = 0, item_carry = 0;
+    bool clamped = false;
     for (int base = 0; base < R; base += 32) {
         const int r = base + lane;
         int npages = 0, ngroups = 0, plo = 0;
@@ -224,6 +247,8 @@ __global__ void __launch_bounds__(32) tq4_attention_plan_kernel(const StreamPara
                 const int hi = row_max_kv(p.batch, g, g.q_len - 1);
                 if (hi >= lo) { plo = lo >> 4; npages = (hi >> 4) - plo + 1; }
                 ngroups = (g.q_len * p.gqa + p.rows_per_group - 1) / p.rows_per_group;
+                // a request longer than the batch's max_q_len has no room in the fragment store
+                if (p.qfrag != nullptr && ngroups > p.q_groups_max) { ngroups = p.q_groups_max; clamped = true; }
             }
         }
         const int items = hkv * ngroups;
@@ -245,12 +270,13 @@ __global__ void __launch_bounds__(32) tq4_attention_plan_kernel(const StreamPara
         unit_carry += __shfl_sync(0xffffffffu, iu, 31);
         item_carry += __shfl_sync(0xffffffffu, ii, 31);
     }
+    const bool clamped_any = __any_sync(0xffffffffu, clamped);
     if (lane == 0) {
         unit_prefix[R] = unit_carry;
         item_prefix[R] = item_carry;
         page_lo[R] = 0; npages_a[R] = 0; ngroups_a[R] = 0;
         PlanHeader* h = reinterpret_cast<PlanHeader*>(p.scratch);
-        h->status = 0;
+        h->status = clamped_any ? 4 : 0;  // bit 2: a request's q_len exceeded batch.max_q_len, rows dropped
         h->total_items = item_carry;
         h->total_units = unit_carry;
         int per = (unit_carry + p.num_warps - 1) / (p.num_warps > 0 ? p.num_warps : 1);
@@ -399,16 +425,94 @@ __device__ __forceinline__ uint32_t token_offset(int t) {  // byte offset of tok
 #ifndef W34_QK_CHAINS
 #define W34_QK_CHAINS 2   // independent accumulator chains of the QK product per 128-half x 2
 #endif
-#ifndef W34_SPLIT_Q
-#define W34_SPLIT_Q 0   // second QK MMA with the fp16 rounding residual of Q'
-#endif
 #ifndef W34_SPLIT_P
 #define W34_SPLIT_P 0   // second PV MMA with the fp16 rounding residual of P * d_v
+#endif
+
+// Eight warps: the query fragments of item idx = (request * kv heads + kv head) * q_groups_max + group.
+// Warp w rotates and scales query row w of the group into shared memory (fp32 [8 rows][256 rotated
+// columns], times q_scale); after the barrier it builds the fragment words of step w.
+__device__ void qprep_block(const StreamParams& p, int idx) {
+    __shared__ float q_stage[kRowsPerGroup * kHeadDim];
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int gid = lane >> 2, tig = lane & 3;
+    const int hkv = p.layout.local_kv_heads;
+    const int group = idx % p.q_groups_max;
+    const int kv_head = (idx / p.q_groups_max) % hkv;
+    const int r = idx / (p.q_groups_max * hkv);
+    if (r >= p.batch.num_reqs || p.qfrag == nullptr) return;  // block-uniform
+    const ReqGeom g = load_req(p.batch, r);
+    const int rows_in_req = g.q_len * p.gqa;
+    if (!g.valid || group * kRowsPerGroup >= rows_in_req) return;  // block-uniform
+    {
+        const int row8 = wid;
+        const int row = group * kRowsPerGroup + row8;
+        const int q_off = row / p.gqa;
+        const int q_head = kv_head * p.gqa + (row - q_off * p.gqa);
+        const bool ok = row < rows_in_req &&
+                        (p.batch.valid_token_mask == nullptr || p.batch.valid_token_mask[g.q_start + q_off] != 0);
+        float t[8];
+        if (ok) {
+            const size_t q_base = ((size_t)(g.q_start + q_off) * p.num_q_heads + q_head) * kHeadDim;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) t[j] = apply_sign(load_act(p.q_in, q_base + lane + 32 * j, p.io_bf16), lane + 32 * j);
+            wht256_lanes(t, lane);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) t[j] = 0.0f;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) q_stage[row8 * kHeadDim + lane + 32 * j] = t[j] * p.q_scale;
+    }
+    __syncthreads();
+    // B fragments of Q'^T: step s (0..7) covers half s >> 2, virtual word 4 tig + (s & 3);
+    // k-step 2 s uses elements 0..3 of the word, k-step 2 s + 1 elements 4..7.
+    // Q' = hi + lo: hi is fp16, lo (the fp16 rounding residual) is kept as 4 e5m2 bytes per
+    // k-step and widened to fp16 pairs by two PRMTs right before its MMA.
+    const int s = wid;
+    const int half = s >> 2, vw = 4 * tig + (s & 3);
+    uint32_t* dst = p.qfrag + (size_t)idx * (kQFragWords * 32) + lane;
+#pragma unroll
+    for (int hk = 0; hk < 2; ++hk) {
+        uint32_t lo_bytes = 0;
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+            const int e = 4 * hk + 2 * x;
+            const float f0 = q_stage[gid * kHeadDim + vword_col(half, vw, e)];
+            const float f1 = q_stage[gid * kHeadDim + vword_col(half, vw, e + 1)];
+            const __half h0 = __float2half_rn(f0), h1 = __float2half_rn(f1);
+            dst[(2 * (2 * s + hk) + x) * 32] = (uint32_t)__half_as_ushort(h0) | ((uint32_t)__half_as_ushort(h1) << 16);
+            // residuals, rounded to the top byte of their fp16 encoding (e5m2)
+            const uint32_t r0 = __half_as_ushort(__float2half_rn(f0 - __half2float(h0)));
+            const uint32_t r1 = __half_as_ushort(__float2half_rn(f1 - __half2float(h1)));
+            const uint32_t b0 = (r0 + 0x7fu + ((r0 >> 8) & 1u)) >> 8;
+            const uint32_t b1 = (r1 + 0x7fu + ((r1 >> 8) & 1u)) >> 8;
+            lo_bytes |= (b0 & 0xffu) << (16 * x) | (b1 & 0xffu) << (16 * x + 8);
+        }
+        if (W34_SPLIT_Q) dst[(32 + 2 * s + hk) * 32] = lo_bytes;
+    }
+}
+
+#ifdef W34_STREAM_PROFILE
+// Development aid: per-warp time stamps (ns) written at scratch + 48 MiB; needs a 64 MiB scratch.
+__device__ __forceinline__ unsigned long long prof_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+#define W34_STAMP(i) do { if (lane == 0) prof_t[i] = prof_now(); } while (0)
+#else
+#define W34_STAMP(i) do { } while (0)
 #endif
 
 template <int STAGES>
 __global__ void __launch_bounds__(W34_WARPS * 32, 1) tq4_attention_stream_kernel(const StreamParams p) {
     extern __shared__ __align__(1024) uint8_t smem[];
+#ifdef W34_STREAM_PROFILE
+    unsigned long long prof_t[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    const unsigned long long prof_t0 = prof_now();
+    int prof_segments = 0;
+#endif
     // The lookup table sits at the first 64 KB-aligned SHARED address inside the dynamic window,
     // so that (table address | code byte << 8 | lane << 2) is one PRMT.  Warp rings fill the
     // space below and above it; the mbarriers follow the last ring.
@@ -452,6 +556,7 @@ __global__ void __launch_bounds__(W34_WARPS * 32, 1) tq4_attention_stream_kernel
     const int32_t* ngroups_a = plan_array(p.scratch, 4, R);
     float* partials = reinterpret_cast<float*>(p.scratch + plan_bytes(R));
 
+    W34_STAMP(1);
     const int w_global = blockIdx.x * warps_per_cta + wid;
     const int per = hdr->units_per_warp;
     const int total_units = hdr->total_units;
@@ -481,6 +586,7 @@ __global__ void __launch_bounds__(W34_WARPS * 32, 1) tq4_attention_stream_kernel
         r = lo;
     }
 
+    W34_STAMP(2);
     while (u < u_end && !failed) {
         while (unit_prefix[r + 1] <= u) ++r;  // skips requests without units
         const int npages = npages_a[r];
@@ -517,60 +623,19 @@ __global__ void __launch_bounds__(W34_WARPS * 32, 1) tq4_attention_stream_kernel
             safe_lo = max(safe_lo, __shfl_xor_sync(0xffffffffu, safe_lo, d));
         }
 
-        // ---- stage Q' for the group's rows: ring memory is idle here ---------------------
-        // layout: fp32 [8 rows][256 rotated columns], pre-multiplied by q_scale
-        float* q_stage = reinterpret_cast<float*>(ring_gen);
-        for (int row8 = 0; row8 < kRowsPerGroup; ++row8) {
-            const int row = group * kRowsPerGroup + row8;
-            const int q_off = row / p.gqa;
-            const int q_head = kv_head * p.gqa + (row - q_off * p.gqa);
-            const bool ok = row < rows_in_req &&
-                            (p.batch.valid_token_mask == nullptr || p.batch.valid_token_mask[g.q_start + q_off] != 0);
-            float t[8];
-            if (ok) {
-                const size_t q_base = ((size_t)(g.q_start + q_off) * p.num_q_heads + q_head) * kHeadDim;
-#pragma unroll
-                for (int j = 0; j < 8; ++j) t[j] = apply_sign(load_act(p.q_in, q_base + lane + 32 * j, p.io_bf16), lane + 32 * j);
-                wht256_lanes(t, lane);
-            } else {
-#pragma unroll
-                for (int j = 0; j < 8; ++j) t[j] = 0.0f;
-            }
-#pragma unroll
-            for (int j = 0; j < 8; ++j) q_stage[row8 * kHeadDim + lane + 32 * j] = t[j] * p.q_scale;
-        }
-        __syncwarp();
-        // B fragments of Q'^T: step s (0..7) covers half s >> 2, virtual word 4 tig + (s & 3);
-        // k-step 2 s uses elements 0..3 of the word, k-step 2 s + 1 elements 4..7.
-        // Q' = hi + lo: hi is fp16, lo (the fp16 rounding residual) is kept as 4 e5m2 bytes per
-        // k-step and widened to fp16 pairs by two PRMTs right before its MMA.
+        // ---- Q' fragments of this item, prepared by the plan launch ---------------------------
         uint32_t qb[16][2];
         uint32_t qlo[16];
+        {
+            const uint32_t* qf = p.qfrag + ((size_t)(r * p.layout.local_kv_heads + kv_head) * p.q_groups_max + group) *
+                                               (kQFragWords * 32) + lane;
 #pragma unroll
-        for (int s = 0; s < 8; ++s) {
-            const int half = s >> 2, vw = 4 * tig + (s & 3);
-#pragma unroll
-            for (int hk = 0; hk < 2; ++hk) {
-                uint32_t lo_bytes = 0;
-#pragma unroll
-                for (int x = 0; x < 2; ++x) {
-                    const int e = 4 * hk + 2 * x;
-                    const float f0 = q_stage[gid * kHeadDim + vword_col(half, vw, e)];
-                    const float f1 = q_stage[gid * kHeadDim + vword_col(half, vw, e + 1)];
-                    const __half h0 = __float2half_rn(f0), h1 = __float2half_rn(f1);
-                    qb[2 * s + hk][x] = (uint32_t)__half_as_ushort(h0) | ((uint32_t)__half_as_ushort(h1) << 16);
-                    // residuals, rounded to the top byte of their fp16 encoding (e5m2)
-                    const uint32_t r0 = __half_as_ushort(__float2half_rn(f0 - __half2float(h0)));
-                    const uint32_t r1 = __half_as_ushort(__float2half_rn(f1 - __half2float(h1)));
-                    const uint32_t b0 = (r0 + 0x7fu + ((r0 >> 8) & 1u)) >> 8;
-                    const uint32_t b1 = (r1 + 0x7fu + ((r1 >> 8) & 1u)) >> 8;
-                    lo_bytes |= (b0 & 0xffu) << (16 * x) | (b1 & 0xffu) << (16 * x + 8);
-                }
-                qlo[2 * s + hk] = lo_bytes;
+            for (int i = 0; i < 16; ++i) {
+                qb[i][0] = __ldg(qf + (2 * i) * 32);
+                qb[i][1] = __ldg(qf + (2 * i + 1) * 32);
+                qlo[i] = W34_SPLIT_Q ? __ldg(qf + (32 + i) * 32) : 0u;
             }
         }
-        __syncwarp();
-
         // ---- accumulators ----------------------------------------------------------------
         float o[16][4];
 #pragma unroll
@@ -585,6 +650,9 @@ __global__ void __launch_bounds__(W34_WARPS * 32, 1) tq4_attention_stream_kernel
         int32_t my_page = (lane < n_here) ? blocks[pg0 + lane] : 0;  // page ids of units [0, 32)
         int32_t next_page = (32 + lane < n_here) ? blocks[pg0 + 32 + lane] : 0;
 
+#ifdef W34_STREAM_PROFILE
+        if (prof_segments++ == 0) W34_STAMP(3);
+#endif
         fence_proxy_async();  // the staging writes above precede async-proxy writes to the ring
         auto issue = [&](int idx) {  // called by all lanes; lane 0 issues the four copies
             const int32_t page = __shfl_sync(0xffffffffu, (idx & 32) ? next_page : my_page, idx & 31);
@@ -622,6 +690,9 @@ __global__ void __launch_bounds__(W34_WARPS * 32, 1) tq4_attention_stream_kernel
             if (!mbar_wait(bars + 8u * s, (phase_bits >> s) & 1u)) { failed = true; break; }
             phase_bits ^= 1u << s;
             pending &= ~(1u << s);
+#ifdef W34_STREAM_PROFILE
+            if (prof_segments == 1 && i == 0) W34_STAMP(4);
+#endif
 
             const uint32_t kst = ring + (uint32_t)s * kStageStride;
             const uint32_t vst = kst + kRunStride;
@@ -819,6 +890,7 @@ __global__ void __launch_bounds__(W34_WARPS * 32, 1) tq4_attention_stream_kernel
             break;
         }
 
+        W34_STAMP(5);  // last segment's value survives
         // ---- write the partial: natural column order, through the idle ring ------------------
         // l: add the 8 lanes (gid) that share a query row
 #pragma unroll
@@ -856,6 +928,15 @@ __global__ void __launch_bounds__(W34_WARPS * 32, 1) tq4_attention_stream_kernel
         __syncwarp();
         u += n_here;
     }
+#ifdef W34_STREAM_PROFILE
+    if (lane == 0) {
+        unsigned long long* dst = reinterpret_cast<unsigned long long*>(p.scratch + (48u << 20)) + (size_t)w_global * 8;
+        dst[0] = prof_t0;
+        for (int i = 1; i < 6; ++i) dst[i] = prof_t[i];
+        dst[6] = prof_now();
+        dst[7] = (unsigned long long)prof_segments;
+    }
+#endif
 }
 
 // ---------------------------------------------------------------------------------------
@@ -2096,6 +2177,12 @@ static long long items_bound(const warp34_kv_layer_layout* l, const warp34_atten
     return (long long)l->local_kv_heads * ((rows + rows_per_group - 1) / rows_per_group + b->num_reqs);
 }
 
+// Entries of the query-fragment store of the one-warp path: requests x kv heads x row groups.
+static long long qfrag_items(const warp34_kv_layer_layout* l, const warp34_attention_batch* b, int gqa) {
+    const long long groups = ((long long)(b->max_q_len > 0 ? b->max_q_len : 1) * gqa + kRowsPerGroup - 1) / kRowsPerGroup;
+    return (long long)b->num_reqs * l->local_kv_heads * groups;
+}
+
 // Query rows that share one KV pass: 8 with one warp per work item (decode), 16 or 24 with
 // four-warp teams (several draft tokens per request, or prefill chunks).
 static int pick_row_tiles(const warp34_attention_batch* b, int gqa) {
@@ -2144,7 +2231,8 @@ extern "C" size_t warp34_paged_attention_scratch_bytes(const warp34_kv_layer_lay
     const int rpg = 8 * nt;
     const long long slots = (long long)sms * (nt == 1 ? w34::kWarpsPerCta : w34::kTeams) +
                             w34::items_bound(layout, batch, num_q_heads, rpg);
-    return w34::plan_bytes(batch->num_reqs) + (size_t)slots * (size_t)(rpg * w34::kHeadDim + 2 * rpg) * sizeof(float);
+    const size_t qfrag = (nt == 1) ? (size_t)w34::qfrag_items(layout, batch, num_q_heads / layout->local_kv_heads) * w34::qfrag_item_bytes() : 0;
+    return w34::plan_bytes(batch->num_reqs) + (size_t)slots * (size_t)(rpg * w34::kHeadDim + 2 * rpg) * sizeof(float) + qfrag;
 }
 
 namespace w34 {
@@ -2231,8 +2319,13 @@ static int launch_attention(const warp34_exec* ex, const warp34_kv_layer_layout*
                   stream_layout_ok(layout) && ex->scratch_ptr != 0 && (ex->scratch_ptr & 15u) == 0u &&
                   units_bound < 0x7fffffffll && batch->max_blocks_per_req > 0;
     int grid = dev->sm_count;
+    // one-warp items also keep their query fragments in the scratch, after the partial slots
+    const long long q_items = (nt == 1) ? qfrag_items(layout, batch, gqa) : 0;
+    if (q_items > 0x3fffffffll) return (int)cudaErrorInvalidValue;
+    const size_t qfrag_bytes = (size_t)q_items * qfrag_item_bytes();
     if (stream) {
-        const size_t avail = ex->scratch_size > plan ? ex->scratch_size - plan : 0;
+        const size_t fixed = plan + qfrag_bytes;
+        const size_t avail = ex->scratch_size > fixed ? ex->scratch_size - fixed : 0;
         const long long slots_avail = (long long)(avail / slot_bytes);
         long long workers = slots_avail - items;
         if (workers < workers_per_cta) {
@@ -2262,10 +2355,12 @@ static int launch_attention(const warp34_exec* ex, const warp34_kv_layer_layout*
     p.rows_per_group = rpg;
     p.q_scale = batch->sm_scale * 1.4426950408889634f / kLutScale;
     p.natural = 0;
+    p.qfrag = (nt == 1) ? reinterpret_cast<uint32_t*>(p.scratch + plan + (size_t)p.max_slots * slot_bytes) : nullptr;
     cudaStream_t st = (cudaStream_t)ex->stream;
     const size_t smem = (size_t)dev->smem_optin;
     p.smem_bytes = (uint32_t)smem;
-    tq4_attention_plan_kernel<<<1, 32, 0, st>>>(p);
+    p.q_groups_max = (nt == 1) ? (int)(q_items / ((long long)batch->num_reqs * layout->local_kv_heads)) : 0;
+    tq4_attention_plan_kernel<<<1 + (unsigned)q_items, q_items > 0 ? kPlanThreads : 32, 0, st>>>(p);
     if (nt == 1) {
         tq4_attention_stream_kernel<kStages><<<grid, kWarpsPerCta * 32, smem, st>>>(p);
     } else if (nt == 2) {
@@ -2346,7 +2441,8 @@ extern "C" int warp34_paged_attention_f16_static_scratch(uintptr_t stream, const
     const size_t needed = w34::plan_bytes(batch->num_reqs) +
                           (size_t)(w34::items_bound(layout, batch, num_q_heads, rpg) +
                                    (nt == 1 ? w34::kWarpsPerCta : w34::kTeams)) *
-                              (size_t)(rpg * w34::kHeadDim + 2 * rpg) * sizeof(float);
+                              (size_t)(rpg * w34::kHeadDim + 2 * rpg) * sizeof(float) +
+                          (nt == 1 ? (size_t)w34::qfrag_items(layout, batch, num_q_heads / layout->local_kv_heads) * w34::qfrag_item_bytes() : 0);
     if (scratch_needed != nullptr) *scratch_needed = needed;
     if (needed > kStaticScratchBytes) return (int)cudaErrorInvalidValue;  // batch too large for the built-in workspace
     warp34_exec ex;
