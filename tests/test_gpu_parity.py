@@ -339,6 +339,34 @@ def test_split_partitioning_does_not_change_the_result_beyond_tolerance(env):
     assert np.abs(outs[0] - outs[1]).max() <= 2e-3 + 1e-2 * np.abs(want).max()
 
 
+def test_understated_max_q_len_is_reported_and_the_declared_rows_stay_right(env):
+    """batch.max_q_len sizes the store of prepared query fragments.  A request with more query
+    tokens than it declares keeps its first row group (8 rows: 2 tokens x 4 heads here), the rest
+    is dropped and bit 2 of the status word at the head of the scratch says so."""
+    kv = env["kv"]
+    hq, hkv = 8, 2
+    wl, q = _decode_case(env, [300, 200], hq, hkv, seed=83, q_lens=[3, 1])
+    honest = wl.step(q_lens=[3, 1])
+    want = _oracle_attention(wl, honest, q, hq)
+    lied = wl.step(q_lens=[3, 1], max_q_len=1)
+    out = torch.full((4, hq, 256), 7.0, dtype=torch.float16, device="cuda")
+    kv.paged_attention(env["ex"], wl.layer, lied, q.cuda(), out, hq)
+    torch.cuda.synchronize()
+    status = int(env["ex"].scratch[:4].cpu().numpy().view(np.int32)[0])
+    assert status & 4
+    got = out.float().cpu().numpy()
+    for tok in (0, 1, 3):   # the first group of request 0, and request 1
+        ok, msg = tensor_core_parity(got[tok:tok + 1], want[tok:tok + 1], wl.v_scale[tok:tok + 1])
+        assert ok, (tok, msg)
+    assert (got[2] == 7.0).all()
+    # declared honestly the same batch is complete and the status clear
+    kv.paged_attention(env["ex"], wl.layer, honest, q.cuda(), out, hq)
+    torch.cuda.synchronize()
+    assert int(env["ex"].scratch[:4].cpu().numpy().view(np.int32)[0]) == 0
+    ok, msg = tensor_core_parity(out.float().cpu().numpy(), want, wl.v_scale)
+    assert ok, msg
+
+
 def test_page_sharded_partials_merge_to_the_unsharded_result(env):
     """One sequence cut into page ranges (as the GPUs of the 256K configuration hold it): every
     shard emits un-normalised (acc, m, l) triples, the merge reproduces single-pass attention."""

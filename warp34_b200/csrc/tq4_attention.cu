@@ -1863,6 +1863,7 @@ __global__ void __launch_bounds__(MW * 32) tq4_attention_merge_kernel(const Stre
     const int rpg = p.rows_per_group;
     const int part_floats = rpg * kHeadDim + 2 * rpg;
     const int group = row_in_req / rpg, row8 = row_in_req - group * rpg;
+    if (group >= ngroups_a[r]) return;  // rows the plan dropped (q_len above the declared max_q_len)
     const int item = kv_head * ngroups_a[r] + group;
     const int npages = npages_a[r];
     const int per = hdr->units_per_warp;

@@ -320,8 +320,9 @@ def build_step(seqs, q_lens, max_blocks_per_req, sm_scale, device="cuda", **kw):
                                             ip(seq), ip(bt), ip(slots), C.byref(mq), C.byref(ms))
     if rc < 0:
         raise RuntimeError(f"w34_build_step_metadata: {rc}")
+    kw.setdefault("max_q_len", mq.value)  # a caller may declare another bound (tests of the contract)
     return StepBatch(qsl, ctx, seq, bt, slots[:total], max_blocks_per_req, sm_scale, device=device,
-                     max_q_len=mq.value, max_seq_len=ms.value, **kw)
+                     max_seq_len=ms.value, **kw)
 
 
 class Executor:
