@@ -373,13 +373,11 @@ def run_bf16_kv(args):
                          "peak_kind": f"of {peak_kind}", "kernel": "bf16kv_attention_stream_kernel (+ plan and merge)",
                          "launch_ms": attn_ms,
                      # dram__bytes_read + write of one stream-kernel launch, from the ncu capture of this same
-                     # workload (profiles/tq4_attention_stream_kernel_cfg1_decode.md: 1.388 GB for 1.343 GB of
+                     # workload (summarised under profiles/: 1.388 GB for 1.343 GB of
                      # algorithmic bytes), scaled by the bytes of this run; null for the other workloads
                      "traffic": (kv_bytes * (1.388 / 1.343) if args.config == "cfg1_batched_decode" and not reference else None)},
             "attended_tokens_per_s": float(sum(wl.ctx) + n_tok) / (attn_ms * 1e-3),
-            **({"exchange": "peer", "exchange_equals_allgather_merge": bool(exchange_ok and peer_px.status() == 0)}
-           if peer_px is not None else {}),
-        "gpu_launches": 4 * args.steps, "clocks": sampler.summary(t_begin, t_end)}
+            "gpu_launches": 4 * args.steps, "clocks": sampler.summary(t_begin, t_end)}
     if reference:
         line["impl"] = "reference"
         line["roofline"]["kernel"] = "reference paged_attention_gqa_bf16_kernel"
@@ -659,7 +657,7 @@ def main():
                      "kernel": "tq4_attention_stream_kernel (+ plan and merge launches, timed together)",
                      "launch_ms": attn_ms,
                      # dram__bytes_read + write of one stream-kernel launch, from the ncu capture of this same
-                     # workload (profiles/tq4_attention_stream_kernel_cfg1_decode.md: 1.388 GB for 1.343 GB of
+                     # workload (summarised under profiles/: 1.388 GB for 1.343 GB of
                      # algorithmic bytes), scaled by the bytes of this run; null for the other workloads
                      "traffic": (kv_bytes * (1.388 / 1.343) if args.config == "cfg1_batched_decode" and not reference else None)},
         "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": (step.h2d_bytes_total - h2d_before) / e2e_steps,
