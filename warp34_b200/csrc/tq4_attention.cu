@@ -158,7 +158,10 @@ constexpr int kRowsPerGroup = 8;            // N of the MMA: query rows per work
 constexpr int kLutBytes = 256 * 256;         // byte-pair table: 256-byte entry stride, 32 lane copies each
 constexpr int kPartialFloats = kRowsPerGroup * kHeadDim + 2 * kRowsPerGroup;
 constexpr long long kWaitCycleLimit = 1ll << 31;  // about one second of SM clocks
-constexpr int kMinUnitsPerWarp = 4;
+#ifndef W34_MIN_UNITS
+#define W34_MIN_UNITS 4
+#endif
+constexpr int kMinUnitsPerWarp = W34_MIN_UNITS;
 // The lookup table holds fp16(kLutScale * centroid).  fp16 rounding of the 8 centroid
 // magnitudes is a systematic error of up to 3.7e-4 relative; with this common factor every one
 // of them lands within 9.5e-5 of an fp16 grid point (found by exhaustive search over
@@ -557,7 +560,9 @@ __global__ void __launch_bounds__(W34_WARPS * 32, 1) tq4_attention_stream_kernel
     float* partials = reinterpret_cast<float*>(p.scratch + plan_bytes(R));
 
     W34_STAMP(1);
-    const int w_global = blockIdx.x * warps_per_cta + wid;
+    // Worker index: consecutive workers sit on different SMs, so that a step with fewer shares
+    // than warps spreads over the whole GPU instead of filling the first CTAs.
+    const int w_global = wid * (int)gridDim.x + (int)blockIdx.x;
     const int per = hdr->units_per_warp;
     const int total_units = hdr->total_units;
     long long u_ll = (long long)w_global * per;
