@@ -129,6 +129,14 @@ _Static_assert(sizeof(warp34_attention_batch) == 96, "warp34_attention_batch ABI
  * write_slot_mapping[token].  Replaces warp34_kv_cache_write
  * (warp34_cuda.h:354-356, op_kv_cache.cu:852-858); k_in / v_in are
  * [total_tokens, local_kv_heads * head_dim] contiguous.
+ *
+ * Layer formats covered at head_dim 256, 16-token pages: TQ4 rows with the sign-diagonal +
+ * WHT-256 rotation (132 B), and the unrotated 8-bit rows of the boundary layers,
+ * WARP34_KV_FORMAT_Q8_0 (272 B: 4 x { float d; int8 qs[64] }) and WARP34_KV_FORMAT_FP8_E4M3
+ * (264 B: uint8 qs[256], float d0, d1), K and V each in either 8-bit format
+ * (op_kv_cache.cu:32-151; cache.rs:62-108 pairs them with the identity transform only).  Rows of
+ * the 8-bit formats must be 4-byte aligned.  Anything else returns cudaErrorNotSupported (801).
+ * warp34_paged_attention_f16 and warp34_paged_attention_scalar_f16 read the same layers.
  */
 int warp34_kv_cache_write(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
                           const warp34_attention_batch* batch,

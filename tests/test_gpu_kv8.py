@@ -1,0 +1,177 @@
+"""GPU parity of the unrotated 8-bit boundary-layer formats (Q8_0 and FP8 E4M3 rows), through the
+C ABI.  Append: bit-exact against the reference's own kernels when oracle/_ref travelled with the
+repository, and against the CPU restatement (oracle/kv8.py) up to one quantisation step on a few
+codes (the restatement divides exactly, the kernels use the fast reciprocal).  Attention:
+|a-b| <= 2e-3 + 1e-2|b| against float64 dequant-then-attend over the stored bytes (which are the
+reference's bytes).  The reference's attention kernels are not called on these layers: driven
+through the C ABI with the layouts its own policy produces they returned non-finite output and,
+for one geometry, an illegal memory access.  Formats and policies: crates/warp34-host/src/cache.rs:62-108."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+ATOL, RTOL = 2e-3, 1e-2
+
+
+@pytest.fixture(scope="module")
+def env(native_libs):
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    from warp34_b200 import ffi, kv, synth
+    return dict(ffi=ffi, kv=kv, synth=synth, ex=kv.Executor(16 << 20), lib=native_libs[0])
+
+
+@pytest.fixture(scope="module")
+def ref_lib(env):
+    import oracle
+    p = oracle.ref_lib_path()
+    if p is None:
+        pytest.skip("reference kernels not built (oracle/_ref)")
+    return env["ffi"].bind_kernel_abi(p)
+
+
+def _formats(ffi, fmt):
+    return (fmt, fmt, ffi.KV_TRANSFORM_IDENTITY, ffi.KV_TRANSFORM_IDENTITY)
+
+
+def _workload(env, fmt, ctx, hkv, seed, fill=0x11):
+    synth, ffi = env["synth"], env["ffi"]
+    wl = synth.PagedWorkload([0] * len(ctx), [int(c) for c in ctx], hkv, seed=seed, fill=fill,
+                             formats=_formats(ffi, fmt))
+    return wl
+
+
+def _pool_rows(layer, fmt_bytes, hkv):
+    """[pages, hkv, 16, row bytes] views of the K and V slabs."""
+    k = layer.k.cpu().numpy().reshape(layer.num_pages, hkv, 16, fmt_bytes)
+    v = layer.v.cpu().numpy().reshape(layer.num_pages, hkv, 16, fmt_bytes)
+    return k, v
+
+
+@pytest.mark.parametrize("fmt_name", ["q8_0", "fp8_e4m3"])
+def test_append_8bit_rows_bit_exact_with_reference_and_close_to_the_restatement(env, fmt_name, request):
+    from oracle import kv8
+    ffi, kv, synth = env["ffi"], env["kv"], env["synth"]
+    fmt = ffi.KV_FORMAT_Q8_0 if fmt_name == "q8_0" else ffi.KV_FORMAT_FP8_E4M3
+    hkv, ctx = 2, [70, 33, 129, 24]
+    T = sum(ctx)
+    k, v = synth.make_kv(T, hkv, 31)
+    edge = T - 24   # the last request carries edge rows
+    k[edge] = 0
+    v[edge + 1] = 0
+    k[edge + 2] = 6.1e-5
+    v[edge + 3] = 1000.0
+    k[edge + 4] = 0
+    k[edge + 4, 17] = 3.0
+    v[edge + 5, :256] = 0
+    k[edge + 6] = 60000.0
+    v[edge + 7] = -1.0
+    pools = {}
+    for name in ("ours", "ref"):
+        if name == "ref":
+            try:
+                lib = request.getfixturevalue("ref_lib")
+            except pytest.skip.Exception:
+                continue
+        else:
+            lib = None
+        wl = _workload(env, fmt, ctx, hkv, seed=31)
+        kv.kv_cache_write(env["ex"], wl.layer, wl.step(), k.cuda(), v.cuda(), lib=lib)
+        torch.cuda.synchronize()
+        pools[name] = (wl, wl.layer.k.cpu().numpy(), wl.layer.v.cpu().numpy())
+    wl, pk, pv = pools["ours"]
+    if "ref" in pools:
+        assert (pk == pools["ref"][1]).all() and (pv == pools["ref"][2]).all()
+    # against the CPU restatement, row by row through the block tables
+    rb = kv8.ROW_BYTES[fmt]
+    kr, vr = _pool_rows(wl.layer, rb, hkv)
+    start = 0
+    worst, differing, total = 0, 0, 0
+    for s, c in zip(wl.seqs, ctx):
+        pages = s.pages
+        for h in range(hkv):
+            for src, pool in ((k, kr), (v, vr)):
+                x = src[start:start + c, 256 * h:256 * h + 256].float().numpy()
+                want = kv8.encode_rows(x, fmt)
+                got = np.stack([pool[pages[t // 16], h, t % 16] for t in range(c)])
+                if fmt == ffi.KV_FORMAT_Q8_0:
+                    sc_g = np.concatenate([got[:, 68 * b:68 * b + 4] for b in range(4)], axis=1)
+                    sc_w = np.concatenate([want[:, 68 * b:68 * b + 4] for b in range(4)], axis=1)
+                else:
+                    sc_g, sc_w = got[:, 256:], want[:, 256:]
+                # scales: fast division may differ in the last place
+                dg, dw = sc_g.copy().view(np.float32), sc_w.copy().view(np.float32)
+                assert np.all(np.abs(dg - dw) <= 2.0 ** -22 * np.abs(dw))
+                cg, cw = kv8.codes(got, fmt), kv8.codes(want, fmt)
+                worst = max(worst, int(np.abs(cg - cw).max()))
+                differing += int((cg != cw).sum())
+                total += cg.size
+        start += c
+    assert worst <= 1, worst
+    assert differing <= total * 0.01, (differing, total)
+    # bytes of pages nobody wrote keep the fill pattern
+    used = {p for s in wl.seqs for p in s.pages}
+    free = [p for p in range(wl.layer.num_pages) if p not in used]
+    assert free and (kr[free] == 0x11).all() and (vr[free] == 0x11).all()
+
+
+def _dequant_then_attend(env, wl, fmt, ctx, q_lens, q, hq, hkv):
+    from oracle import kv8
+    rb = kv8.ROW_BYTES[fmt]
+    kr, vr = _pool_rows(wl.layer, rb, hkv)
+    g = hq // hkv
+    out = np.zeros((sum(q_lens), hq, 256))
+    t0 = 0
+    for s, c, ql in zip(wl.seqs, ctx, q_lens):
+        pages = s.pages
+        for h in range(hkv):
+            kd = kv8.decode_rows(np.stack([kr[pages[t // 16], h, t % 16] for t in range(c)]), fmt)
+            vd = kv8.decode_rows(np.stack([vr[pages[t // 16], h, t % 16] for t in range(c)]), fmt)
+            for j in range(ql):
+                n_vis = c - ql + j + 1
+                qq = q[t0 + j, h * g:(h + 1) * g].float().numpy()
+                out[t0 + j, h * g:(h + 1) * g] = kv8.attention(kd[:n_vis], vd[:n_vis], qq, 1.0 / 16.0)
+        t0 += ql
+    return out
+
+
+@pytest.mark.parametrize("fmt_name", ["q8_0", "fp8_e4m3"])
+@pytest.mark.parametrize("hq,hkv,q_len", [(24, 4, 1), (16, 4, 3), (8, 8, 1)])
+def test_attention_over_8bit_rows_matches_dequant_then_attend(env, fmt_name, hq, hkv, q_len):
+    ffi, kv, synth = env["ffi"], env["kv"], env["synth"]
+    fmt = ffi.KV_FORMAT_Q8_0 if fmt_name == "q8_0" else ffi.KV_FORMAT_FP8_E4M3
+    ctx = [257, 40, 16, 1000]
+    q_lens = [q_len] * len(ctx)
+    T = sum(ctx)
+    k, v = synth.make_kv(T, hkv, 47)
+    wl = _workload(env, fmt, ctx, hkv, seed=47)
+    kv.kv_cache_write(env["ex"], wl.layer, wl.step(), k.cuda(), v.cuda())
+    for s, c, ql in zip(wl.seqs, ctx, q_lens):
+        s.commit(c - ql)
+    b = wl.step(q_lens=q_lens)
+    q = synth.make_q(sum(q_lens), hq, 47)
+    out = torch.zeros(sum(q_lens), hq, 256, dtype=torch.float16, device="cuda")
+    kv.paged_attention(env["ex"], wl.layer, b, q.cuda(), out, hq)
+    torch.cuda.synchronize()
+    got = out.float().cpu().numpy()
+    want = _dequant_then_attend(env, wl, fmt, ctx, q_lens, q, hq, hkv)
+    assert np.all(np.abs(got - want) <= ATOL + RTOL * np.abs(want)), float(np.abs(got - want).max())
+    # the scalar entry point takes the same path
+    out2 = torch.zeros_like(out)
+    kv.paged_attention(env["ex"], wl.layer, b, q.cuda(), out2, hq, scalar=True)
+    torch.cuda.synchronize()
+    assert torch.equal(out.view(torch.int16), out2.view(torch.int16))
+
+
+def test_8bit_layers_refuse_what_they_do_not_cover(env):
+    ffi, kv, synth = env["ffi"], env["kv"], env["synth"]
+    rotated = (ffi.KV_FORMAT_Q8_0, ffi.KV_FORMAT_Q8_0, ffi.KV_TRANSFORM_RADEMACHER_WHT256,
+               ffi.KV_TRANSFORM_RADEMACHER_WHT256)
+    wl = synth.PagedWorkload([0], [20], 2, seed=3, formats=rotated)
+    k, v = synth.make_kv(20, 2, 3)
+    rc = env["lib"].warp34_kv_cache_write(C.byref(env["ex"].ex), C.byref(wl.layer.layout), C.byref(wl.step().desc),
+                                          k.cuda().data_ptr(), v.cuda().data_ptr())
+    assert rc == ffi.CUDA_ERROR_NOT_SUPPORTED

@@ -344,7 +344,39 @@ __global__ void __launch_bounds__(128, W34_APPEND_BLOCKS_PER_SM) tq4_append_kern
 
 }  // namespace w34
 
+#include "kv8_append.cuh"
+
 namespace w34 {
+// Unrotated 8-bit layers: one warp per row.
+static int launch_append_kv8(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
+                             const warp34_attention_batch* batch, const void* k_in, const void* v_in,
+                             int k_row_stride, int v_row_stride) {
+    const int min_stride = layout->local_kv_heads * layout->head_dim;
+    if (k_row_stride < min_stride || v_row_stride < min_stride) return (int)cudaErrorInvalidValue;
+    if (batch->write_slot_mapping == nullptr || layout->k_base == 0 || layout->v_base == 0) {
+        return (int)cudaErrorInvalidValue;
+    }
+    // Scales are fp32 and the codes are stored as 32-bit words: every row must be 4-byte aligned
+    // (the reference's row structs have the same alignment).
+    if ((layout->k_base | layout->v_base | layout->k_page_stride_bytes | layout->k_head_stride_bytes |
+         layout->k_token_stride_bytes | layout->v_page_stride_bytes | layout->v_head_stride_bytes |
+         layout->v_token_stride_bytes) & 3u) {
+        return (int)cudaErrorInvalidValue;
+    }
+    AppendParams p;
+    p.layout = *layout;
+    p.batch = *batch;
+    p.k_in = static_cast<const uint16_t*>(k_in);
+    p.v_in = static_cast<const uint16_t*>(v_in);
+    p.k_row_stride = k_row_stride;
+    p.v_row_stride = v_row_stride;
+    const long long rows = 2ll * batch->total_tokens * layout->local_kv_heads;
+    if (rows > 0x7fffffffll) return (int)cudaErrorInvalidValue;
+    p.total_rows = (int)rows;
+    kv8_append_kernel<<<(unsigned)((rows + 3) / 4), 128, 0, (cudaStream_t)ex->stream>>>(p);
+    return (int)cudaGetLastError();
+}
+
 static int launch_append(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
                          const warp34_attention_batch* batch, const void* k_in, const void* v_in,
                          int k_row_stride, int v_row_stride, bool in_bf16) {
@@ -352,6 +384,10 @@ static int launch_append(const warp34_exec* ex, const warp34_kv_layer_layout* la
         return (int)cudaErrorInvalidValue;
     }
     if (batch->total_tokens <= 0 || layout->local_kv_heads <= 0) return 0;
+    if (kv8_layout_ok(layout)) {
+        if (in_bf16) return (int)cudaErrorNotSupported;
+        return launch_append_kv8(ex, layout, batch, k_in, v_in, k_row_stride, v_row_stride);
+    }
     if (layout->head_dim != kHeadDim || layout->block_size != kPageTokens ||
         layout->k_format != WARP34_KV_FORMAT_TQ4 || layout->v_format != WARP34_KV_FORMAT_TQ4 ||
         layout->k_transform != WARP34_KV_TRANSFORM_RADEMACHER_WHT256 ||

@@ -151,6 +151,10 @@ __global__ void __launch_bounds__(128) tq4_attention_scalar_kernel(
     for (int j = 0; j < 8; ++j) store_act(attn_out, row_base + lane + 32 * j, apply_sign(t[j], lane + 32 * j), io_bf16);
 }
 
+}  // namespace w34
+#include "kv8_attention.cuh"
+namespace w34 {
+
 // ---------------------------------------------------------------------------------------
 // Split-KV streaming path
 // ---------------------------------------------------------------------------------------
@@ -2218,6 +2222,9 @@ static int w34::launch_scalar(const warp34_exec* ex, const warp34_kv_layer_layou
         return (int)cudaErrorInvalidValue;
     }
     if (batch->total_tokens <= 0 || num_q_heads <= 0) return 0;
+    if (w34::kv8_attention_layout_ok(layout)) {
+        return w34::launch_kv8_attention(ex, layout, batch, q_in, attn_out, num_q_heads, io_bf16);
+    }
     if (!w34::tq4_layout_ok(layout)) return (int)cudaErrorNotSupported;
     if (num_q_heads % layout->local_kv_heads != 0 || batch->num_reqs <= 0) return (int)cudaErrorInvalidValue;
     const long long rows = (long long)batch->total_tokens * num_q_heads;
@@ -2253,6 +2260,10 @@ static int launch_attention(const warp34_exec* ex, const warp34_kv_layer_layout*
         return (int)cudaErrorInvalidValue;
     }
     if (batch->total_tokens <= 0 || num_q_heads <= 0) return 0;
+    if (kv8_attention_layout_ok(layout)) {   // unrotated 8-bit boundary layers
+        if (triple_out != nullptr) return (int)cudaErrorNotSupported;
+        return launch_kv8_attention(ex, layout, batch, q_in, attn_out, num_q_heads, io_bf16);
+    }
     if (!tq4_layout_ok(layout)) return (int)cudaErrorNotSupported;
     if (num_q_heads % layout->local_kv_heads != 0 || batch->num_reqs <= 0) return (int)cudaErrorInvalidValue;
 
