@@ -136,21 +136,33 @@ __global__ void __launch_bounds__(kKv8Warps * 32) kv8_attention_kernel(
                         for (int h = 0; h < G; ++h) dot[i][h] += __shfl_xor_sync(0xffffffffu, dot[i][h], o);
                     }
                 }
+                // one rescale per head for the four keys; keys past the end get weight 0
+                float vx[4][8];
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    if (p0 + i <= hi) {   // warp-uniform
-                        float vx[8];
-                        kv8_decode(vr[i], layout.v_format, vx);
+                for (int i = 0; i < 4; ++i) kv8_decode(vr[i], layout.v_format, vx[i]);
 #pragma unroll
-                        for (int h = 0; h < G; ++h) {
-                            const float m_new = fmaxf(m_i[h], dot[i][h]);
-                            const float alpha = __expf(m_i[h] - m_new);
-                            const float pr = __expf(dot[i][h] - m_new);
-                            l_i[h] = l_i[h] * alpha + pr;
-                            m_i[h] = m_new;
+                for (int h = 0; h < G; ++h) {
+                    float m_new = m_i[h];
 #pragma unroll
-                            for (int e = 0; e < 8; ++e) acc[h][e] = acc[h][e] * alpha + pr * vx[e];
-                        }
+                    for (int i = 0; i < 4; ++i) {
+                        if (p0 + i > hi) dot[i][h] = -1e30f;
+                        m_new = fmaxf(m_new, dot[i][h]);
+                    }
+                    const float alpha = __expf(m_i[h] - m_new);
+                    float pr[4], psum = 0.0f;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        pr[i] = (p0 + i <= hi) ? __expf(dot[i][h] - m_new) : 0.0f;
+                        psum += pr[i];
+                    }
+                    l_i[h] = l_i[h] * alpha + psum;
+                    m_i[h] = m_new;
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        float t = acc[h][e] * alpha;
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) t += pr[i] * vx[i][e];
+                        acc[h][e] = t;
                     }
                 }
             }
