@@ -603,19 +603,22 @@ class DecodeStep:
         self.d2h_bytes = self.out_host.numel() * 2
 
     def _capture(self, lib):
-        """One CUDA graph of the whole step: uploads of lengths, slots, K, V and Q from pinned memory,
-        append, attention, download of the output (the reference replays its decode steps the same
-        way, crates/warp34-host/src/model/graphs.rs:199-259).  Block tables are not in the graph:
-        their changed part is copied before the replay."""
+        """Two CUDA graphs for the whole step (the reference replays its decode steps the same way,
+        crates/warp34-host/src/model/graphs.rs:199-259): the first uploads K, V and Q from pinned
+        memory and is launched before the host packs the step's metadata, so that the copies run
+        while the CPU works; the second uploads lengths and slots, appends, attends and downloads
+        the output.  Block tables are in neither: their changed part is copied between the two."""
         head = self.io.head_words
         b = _DescOnly(self.io.desc)
+
+        def payload():
+            self.k_dev.copy_(self.k_host, non_blocking=True)
+            self.v_dev.copy_(self.v_host, non_blocking=True)
+            self.q_dev.copy_(self.q_host, non_blocking=True)
 
         def body():
             self.ex.set_stream()
             self.io.dev[:head].copy_(self.io.host[:head], non_blocking=True)
-            self.k_dev.copy_(self.k_host, non_blocking=True)
-            self.v_dev.copy_(self.v_host, non_blocking=True)
-            self.q_dev.copy_(self.q_host, non_blocking=True)
             kv_cache_write(self.ex, self.layer, b, self.k_dev, self.v_dev, lib=lib)
             paged_attention(self.ex, self.layer, b, self.q_dev, self.out_dev, self.hq, lib=lib)
             self.out_host.copy_(self.out_dev, non_blocking=True)
@@ -623,29 +626,37 @@ class DecodeStep:
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
+            payload()
             body()                      # warm-up outside the capture (one-time attribute calls)
         torch.cuda.current_stream().wait_stream(side)
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
-            body()
+        graphs = []
+        for fn in (payload, body):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                fn()
+            graphs.append(g)
         self.ex.set_stream()
-        return g
+        return tuple(graphs)
 
     def run(self, q_lens, sm_scale=1.0 / 16.0, lib=None, sync=True, attend=None, graph=False):
-        self.io.pack(self.seqs, q_lens, sm_scale)
         if graph and attend is None:
             # geometry baked into the captured launches: token count and request count must not change
-            key = (id(lib), self.io.desc.num_reqs, self.io.desc.total_tokens, self.io.desc.max_q_len)
+            key = (id(lib), len(self.seqs), int(sum(q_lens)), int(max(q_lens)))
             g = self._graphs.get(key)
+            if g is not None:
+                g[0].replay()           # K, V, Q on their way while the metadata is packed
+            self.io.pack(self.seqs, q_lens, sm_scale)
             if g is None:
                 self.io.upload(full=True)
                 g = self._graphs[key] = self._capture(lib)
+                g[0].replay()
             self.meta_bytes_last = self.io.upload(tables_only=True) + 4 * self.io.head_words
             self.h2d_bytes_total += self.meta_bytes_last + self.payload_bytes
-            g.replay()
+            g[1].replay()
             if sync:
                 torch.cuda.current_stream().synchronize()
             return self.out_host
+        self.io.pack(self.seqs, q_lens, sm_scale)
         self.meta_bytes_last = self.io.upload()
         self.h2d_bytes_total += self.meta_bytes_last + self.payload_bytes
         self.k_dev.copy_(self.k_host, non_blocking=True)
