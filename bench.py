@@ -310,13 +310,20 @@ def run_chunked_prefill(args):
     print(json.dumps(line))
 
 
-def run_bf16_kv(args):
-    """Comparison arm: the same decode step over uncompressed BF16 pages (1024 B per token and KV
-    head instead of 264), device-resident, one GPU.  `--impl reference` runs the reference's
-    own bf16 kernels when they were built."""
+def run_other_kv(args):
+    """The same decode step over another storage format of the reference, device-resident, one GPU:
+    `--kv bf16` uncompressed BF16 pages (1024 B per token and KV head instead of 264; the comparison
+    arm), `--kv fp8` / `--kv q8` the unrotated 8-bit rows of the boundary layers (528 / 544 B).
+    `--impl reference` runs the reference's own bf16 kernels when they were built; its attention
+    kernels are not run on the 8-bit layers (they faulted on them here)."""
     import oracle
     from warp34_b200 import ffi, kv, synth
     reference = args.impl == "reference"
+    bf16 = args.kv == "bf16"
+    if reference and not bf16:
+        print(json.dumps({"impl": "reference", "unavailable": "the reference's attention kernels returned non-finite "
+                          "output and raised an illegal memory access on Q8_0 / FP8 layers here; not run again"}))
+        return
     ref_path = oracle.ref_lib_path() if reference else None
     if reference and ref_path is None:
         print(json.dumps({"impl": "reference", "unavailable": "reference kernels not built (oracle/_ref missing)"}))
@@ -324,21 +331,31 @@ def run_bf16_kv(args):
     lib = ffi.bind_kernel_abi(ref_path) if ref_path else ffi.kernels()
     hq, hkv, batch, lo, hi, q_len, seed = synth.CONFIGS[args.config]
     ctx = synth.context_lengths(batch, lo, hi, seed)
-    wl = synth.PagedWorkload([int(c) for c in ctx], [q_len] * batch, hkv, seed=seed, formats=kv.BF16_KV_FORMATS)
+    if bf16:
+        formats, act = kv.BF16_KV_FORMATS, torch.bfloat16
+        append, attend = kv.kv_cache_write_bf16, kv.paged_attention_bf16kv
+        kernel, label = "bf16kv_attention_stream_kernel (+ plan and merge)", "uncompressed BF16 pages"
+    else:
+        fmt = ffi.KV_FORMAT_FP8_E4M3 if args.kv == "fp8" else ffi.KV_FORMAT_Q8_0
+        formats, act = (fmt, fmt, ffi.KV_TRANSFORM_IDENTITY, ffi.KV_TRANSFORM_IDENTITY), torch.float16
+        append, attend = kv.kv_cache_write, kv.paged_attention
+        kernel = "kv8_attention_kernel"
+        label = "unrotated FP8 E4M3 rows" if args.kv == "fp8" else "unrotated Q8_0 rows"
+    wl = synth.PagedWorkload([int(c) for c in ctx], [q_len] * batch, hkv, seed=seed, formats=formats)
     ex = kv.Executor(64 << 20)
     wl.fill_context(ex, seed, chunk_tokens=32768)
     n_tok = batch * q_len
-    k_new, v_new = (x.to(torch.bfloat16).cuda() for x in synth.make_kv(n_tok, hkv, seed + 17))
-    q = synth.make_q(n_tok, hq, seed + 17).to(torch.bfloat16).cuda()
+    k_new, v_new = (x.to(act).cuda() for x in synth.make_kv(n_tok, hkv, seed + 17))
+    q = synth.make_q(n_tok, hq, seed + 17).to(act).cuda()
     out = torch.zeros_like(q)
     b = wl.step()
     ex.set_stream()
 
     def one(ev=None):
-        kv.kv_cache_write_bf16(ex, wl.layer, b, k_new, v_new, lib=lib)
+        append(ex, wl.layer, b, k_new, v_new, lib=lib)
         if ev is not None:
             ev[0].record()
-        kv.paged_attention_bf16kv(ex, wl.layer, b, q, out, hq, lib=lib)
+        attend(ex, wl.layer, b, q, out, hq, lib=lib)
         if ev is not None:
             ev[1].record()
 
@@ -363,21 +380,16 @@ def run_bf16_kv(args):
     peaks, peak_kind = measured_peaks()
     peak = float(peaks.get("hbm_gbs", FALLBACK_HBM_GBS))
     achieved = kv_bytes / (attn_ms * 1e-3) / 1e9
-    line = {"metric": "bf16_kv_decode_GBps", "value": kv_bytes / (ms * 1e-3) / 1e9, "unit": "GB/s", "n_gpus": 1,
+    line = {"metric": f"{args.kv}_kv_decode_GBps", "value": kv_bytes / (ms * 1e-3) / 1e9, "unit": "GB/s", "n_gpus": 1,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"{args.config} over uncompressed BF16 pages: {batch} seqs x ctx U[{lo},{hi}], "
+            "vs_baseline": None, "dtype": "bf16" if bf16 else "f32", "data": "synthetic",
+            "config": {"workload": f"{args.config} over {label}: {batch} seqs x ctx U[{lo},{hi}], "
                                    f"{hq} q heads / {hkv} kv heads, d256, step = append {q_len} token/seq + decode attention",
                        "kv_bytes_per_step": kv_bytes, "l2": "KV read per step is larger than L2; no flush needed"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "peak_kind": f"of {peak_kind}", "kernel": "bf16kv_attention_stream_kernel (+ plan and merge)",
-                         "launch_ms": attn_ms,
-                     # dram__bytes_read + write of one stream-kernel launch, from the ncu capture of this same
-                     # workload (summarised under profiles/: 1.388 GB for 1.343 GB of
-                     # algorithmic bytes), scaled by the bytes of this run; null for the other workloads
-                     "traffic": (kv_bytes * (1.388 / 1.343) if args.config == "cfg1_batched_decode" and not reference else None)},
+                         "peak_kind": f"of {peak_kind}", "kernel": kernel, "launch_ms": attn_ms, "traffic": None},
             "attended_tokens_per_s": float(sum(wl.ctx) + n_tok) / (attn_ms * 1e-3),
-            "gpu_launches": 4 * args.steps, "clocks": sampler.summary(t_begin, t_end)}
+            "gpu_launches": (4 if bf16 else 2) * args.steps, "clocks": sampler.summary(t_begin, t_end)}
     if reference:
         line["impl"] = "reference"
         line["roofline"]["kernel"] = "reference paged_attention_gqa_bf16_kernel"
@@ -399,12 +411,13 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="time eager launches only (no CUDA graph replay)")
     ap.add_argument("--prefix-tokens", type=int, default=4096,
                     help="cfg2: shared prefix length; 4100 leaves a partly filled shared tail page (copy-on-write)")
-    ap.add_argument("--kv", default="tq4", choices=["tq4", "bf16"],
-                    help="bf16: the uncompressed-storage comparison arm of the same decode step (one GPU)")
+    ap.add_argument("--kv", default="tq4", choices=["tq4", "bf16", "fp8", "q8"],
+                    help="bf16: the uncompressed-storage comparison arm of the same decode step; fp8 / q8: the "
+                         "unrotated 8-bit rows of the boundary layers (one GPU each)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
-    if args.kv == "bf16":
-        return run_bf16_kv(args)
+    if args.kv != "tq4":
+        return run_other_kv(args)
     if args.config == "cfg2_chunked_prefill":
         return run_chunked_prefill(args)
 

@@ -68,7 +68,8 @@ constexpr int kKv8Warps = 8;
 template <int G>
 __global__ void __launch_bounds__(kKv8Warps * 32) kv8_attention_kernel(
     const warp34_kv_layer_layout layout, const warp34_attention_batch batch,
-    const void* __restrict__ q_in, void* __restrict__ attn_out, int num_q_heads, int io_bf16) {
+    const void* __restrict__ q_in, void* __restrict__ attn_out, int num_q_heads, int io_bf16,
+    int splits, float* __restrict__ partials) {
     __shared__ float s_acc[4][G][kHeadDim];
     __shared__ float s_ml[4][G][2];
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
@@ -98,7 +99,12 @@ __global__ void __launch_bounds__(kKv8Warps * 32) kv8_attention_kernel(
     }
     const int32_t* blocks = batch.block_tables + (size_t)req * batch.max_blocks_per_req;
     if (max_kv >= min_kv) {
-        for (int pg = (min_kv >> 4) + wid; pg <= (max_kv >> 4); pg += kKv8Warps) {
+        // blockIdx.y takes the y-th of `splits` equal page ranges of the row's keys
+        const int p_lo = min_kv >> 4, p_hi = max_kv >> 4;
+        const int chunk = (p_hi - p_lo + splits) / splits;
+        const int my_lo = p_lo + (int)blockIdx.y * chunk;
+        const int my_hi = min(p_hi, my_lo + chunk - 1);
+        for (int pg = my_lo + wid; pg <= my_hi; pg += kKv8Warps) {
             const int page = blocks[pg];
             const int lo = max(min_kv, pg << 4), hi = min(max_kv, (pg << 4) + 15);
             const uint8_t* kpage = (const uint8_t*)(uintptr_t)layout.k_base + (size_t)page * layout.k_page_stride_bytes +
@@ -201,6 +207,20 @@ __global__ void __launch_bounds__(kKv8Warps * 32) kv8_attention_kernel(
         __syncthreads();
     }
     if (wid != 0) return;
+    if (splits > 1) {
+        // un-normalised state of this page range: [item][split][head][256 acc | m | l]
+        float* dst = partials + (((size_t)blockIdx.x * splits + blockIdx.y) * G) * kRowTripleFloats;
+#pragma unroll
+        for (int h = 0; h < G; ++h) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) dst[h * kRowTripleFloats + 8 * lane + e] = acc[h][e];
+            if (lane == 0) {
+                dst[h * kRowTripleFloats + kHeadDim] = m_i[h];
+                dst[h * kRowTripleFloats + kHeadDim + 1] = l_i[h];
+            }
+        }
+        return;
+    }
 #pragma unroll
     for (int h = 0; h < G; ++h) {
         const float inv_l = (l_i[h] > 0.0f) ? (1.0f / l_i[h]) : 0.0f;
@@ -208,6 +228,47 @@ __global__ void __launch_bounds__(kKv8Warps * 32) kv8_attention_kernel(
 #pragma unroll
         for (int e = 0; e < 8; ++e) store_act(attn_out, base + e, acc[h][e] * inv_l, io_bf16);
     }
+}
+
+// Combines the `splits` states of every (token, q head): one warp per output row.
+__global__ void __launch_bounds__(128) kv8_merge_kernel(
+    const warp34_kv_layer_layout layout, const warp34_attention_batch batch, void* __restrict__ attn_out,
+    int num_q_heads, int io_bf16, int splits, const float* __restrict__ partials) {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const long long row = (long long)blockIdx.x * 4 + wid;
+    if (row >= (long long)batch.total_tokens * num_q_heads) return;
+    const int tok = (int)(row / num_q_heads), q_head = (int)(row % num_q_heads);
+    // the same exits as the attention blocks: rows they skipped have no states
+    if (batch.valid_token_mask != nullptr && batch.valid_token_mask[tok] == 0) return;
+    const int req = find_request(batch.query_start_loc, batch.num_reqs, tok);
+    if (req < 0) return;
+    const ReqGeom g = load_req(batch, req);
+    if (!g.valid) return;
+    const int gqa = num_q_heads / layout.local_kv_heads;
+    const int kv_head = q_head / gqa, h = q_head - kv_head * gqa;
+    const float* base = partials + ((((size_t)tok * layout.local_kv_heads + kv_head) * splits) * gqa + h) * kRowTripleFloats;
+    const size_t stride = (size_t)gqa * kRowTripleFloats;
+    float m_tot = -1e30f;
+    for (int sidx = 0; sidx < splits; ++sidx) {
+        const float* t = base + sidx * stride;
+        if (t[kHeadDim + 1] > 0.0f) m_tot = fmaxf(m_tot, t[kHeadDim]);
+    }
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    float l_tot = 0.0f;
+    for (int sidx = 0; sidx < splits; ++sidx) {
+        const float* t = base + sidx * stride;
+        const float ls = t[kHeadDim + 1];
+        if (ls > 0.0f) {
+            const float w = __expf(t[kHeadDim] - m_tot);
+            l_tot += ls * w;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[e] += t[8 * lane + e] * w;
+        }
+    }
+    const float inv_l = (l_tot > 0.0f) ? (1.0f / l_tot) : 0.0f;
+    const size_t out_base = ((size_t)tok * num_q_heads + q_head) * kHeadDim + 8 * lane;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) store_act(attn_out, out_base + e, acc[e] * inv_l, io_bf16);
 }
 
 static bool kv8_attention_layout_ok(const warp34_kv_layer_layout* l) {
@@ -236,13 +297,39 @@ static int launch_kv8_attention(const warp34_exec* ex, const warp34_kv_layer_lay
     if (items > 0x7fffffffll) return (int)cudaErrorInvalidValue;
     const unsigned blocks = (unsigned)items;
     cudaStream_t st = (cudaStream_t)ex->stream;
-#define W34_KV8_CASE(Gv) case Gv: kv8_attention_kernel<Gv><<<blocks, kKv8Warps * 32, 0, st>>>(*layout, *batch, q_in, attn_out, num_q_heads, io_bf16); break
+    // One block fills an SM (registers): few (token, kv head) items leave SMs idle and long rows
+    // finish last.  With a scratch buffer every row's pages are cut into `splits` ranges, about
+    // four blocks per SM in all, and a second launch combines the states.
+    int splits = 1;
+    float* partials = nullptr;
+    {
+        int rc = 0;
+        DeviceInfo* dev = device_info(&rc);
+        const long long want = dev != nullptr ? (4ll * dev->sm_count + items - 1) / items : 1;
+        const size_t per_split = (size_t)items * gqa * kRowTripleFloats * sizeof(float);
+        if (want > 1 && ex->scratch_ptr != 0 && (ex->scratch_ptr & 15u) == 0 && per_split > 0) {
+            long long fit = (long long)(ex->scratch_size / per_split);
+            long long sp = want < 16 ? want : 16;
+            if (sp > fit) sp = fit;
+            if (sp > 1) {
+                splits = (int)sp;
+                partials = reinterpret_cast<float*>((uintptr_t)ex->scratch_ptr);
+            }
+        }
+    }
+    const dim3 grid(blocks, (unsigned)splits);
+#define W34_KV8_CASE(Gv) case Gv: kv8_attention_kernel<Gv><<<grid, kKv8Warps * 32, 0, st>>>(*layout, *batch, q_in, attn_out, num_q_heads, io_bf16, splits, partials); break
     switch (gqa) {
         W34_KV8_CASE(1); W34_KV8_CASE(2); W34_KV8_CASE(3); W34_KV8_CASE(4);
         W34_KV8_CASE(5); W34_KV8_CASE(6); W34_KV8_CASE(7); W34_KV8_CASE(8);
         default: return (int)cudaErrorNotSupported;
     }
 #undef W34_KV8_CASE
+    if (splits > 1) {
+        const long long rows = (long long)batch->total_tokens * num_q_heads;
+        kv8_merge_kernel<<<(unsigned)((rows + 3) / 4), 128, 0, st>>>(*layout, *batch, attn_out, num_q_heads, io_bf16,
+                                                                     splits, partials);
+    }
     return (int)cudaGetLastError();
 }
 

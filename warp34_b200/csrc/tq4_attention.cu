@@ -151,10 +151,6 @@ __global__ void __launch_bounds__(128) tq4_attention_scalar_kernel(
     for (int j = 0; j < 8; ++j) store_act(attn_out, row_base + lane + 32 * j, apply_sign(t[j], lane + 32 * j), io_bf16);
 }
 
-}  // namespace w34
-#include "kv8_attention.cuh"
-namespace w34 {
-
 // ---------------------------------------------------------------------------------------
 // Split-KV streaming path
 // ---------------------------------------------------------------------------------------
@@ -2202,6 +2198,8 @@ static int pick_row_tiles(const warp34_attention_batch* b, int gqa) {
 }
 
 }  // namespace w34
+
+#include "kv8_attention.cuh"
 
 namespace w34 {
 static int launch_scalar(const warp34_exec* ex, const warp34_kv_layer_layout* layout,

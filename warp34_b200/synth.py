@@ -9,6 +9,7 @@ seeded shuffled free list with page 0 kept as the trash sink.
 import numpy as np
 import torch
 
+from . import ffi
 from . import kv as kvmod
 
 HEAD_DIM = 256
@@ -132,6 +133,8 @@ class PagedWorkload:
 
     def algorithmic_kv_bytes(self):
         """KV bytes one decode / verify pass must read: sum(ctx+q) * Hkv * (K row + V row bytes):
-        264 for TQ4 storage, 1024 for uncompressed BF16."""
-        row_pair = 1024 if self.bf16_storage else 264
+        264 for TQ4 storage, 1024 for uncompressed BF16, 528 for FP8 E4M3 rows, 544 for Q8_0 rows."""
+        lay = self.layer.layout
+        row_pair = (ffi.host().w34_kv_format_row_bytes(lay.k_format, HEAD_DIM) +
+                    ffi.host().w34_kv_format_row_bytes(lay.v_format, HEAD_DIM))
         return sum(c + q for c, q in zip(self.ctx, self.q_lens)) * self.num_kv_heads * row_pair
