@@ -12,7 +12,9 @@ crates/warp34-kernels/csrc/ops/op_paged_attn.cu:59-105 (decode), identity transf
 The reference is built with fast math (approximate reciprocal), this file divides exactly: a code may
 differ by one step where x / d sits on a rounding boundary.  Parity of the bytes is therefore pinned
 against the reference's own kernels (oracle/_ref) in the GPU tests, and this restatement is held to
-"almost all bytes equal, none off by more than one step".
+"almost all bytes equal, none off by more than one step".  The attention function below is plain
+float64 dequant-then-attend over stored bytes: parity unpinned against the reference's attention
+output for these layers (its kernels did not return finite output on them where this was tried).
 """
 import numpy as np
 import torch
