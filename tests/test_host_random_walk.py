@@ -139,3 +139,61 @@ def test_random_walk_keeps_page_accounting_exact(seed):
     assert hits >= 10   # the walk did share prefixes
     cache.close()
     assert pool.free_count == pool.num_pages
+
+
+@pytest.mark.parametrize("seed", [11, 12, 13])
+def test_persistent_step_arena_always_equals_a_fresh_pack(seed):
+    """StepIo packs into a persistent arena and uploads only what changed (lengths and slots every
+    step, block tables up to the last changed entry).  Over a random walk of growing, rolled-back
+    and replaced sequences the device-side copy must always equal what a from-scratch pack of the
+    same step produces (graph_io.rs:109-195, :368-420)."""
+    import numpy as np
+    import torch
+
+    from warp34_b200 import kv
+    rng = random.Random(seed)
+    pool = PagePool(512)
+    n, max_q, max_blocks = 6, 4, 24
+    seqs = [Sequence(pool) for _ in range(n)]
+    for s in seqs:
+        c = rng.randrange(1, 200)
+        assert s.reserve(c + max_q) >= 0
+        s.commit(c)
+    io = kv.StepIo(n, n * max_q, max_blocks, device="cpu")
+    full_bytes = 0
+    for step in range(120):
+        q_lens = [rng.randrange(1, max_q + 1) for _ in range(n)]
+        for s, q in zip(seqs, q_lens):
+            if s.reserve(s.committed_len + q) < 0 or s.num_pages > max_blocks:
+                # start over as a fresh short request in the same row
+                s.rollback()
+                s.set_committed(0)
+                s.rollback()
+                assert s.reserve(rng.randrange(1, 40) + q) >= 0
+                s.commit(s.num_pages * PAGE - PAGE if s.num_pages > 1 else 0)
+                assert s.reserve(s.committed_len + q) >= 0
+        io.pack(seqs, q_lens, 0.0625)
+        full_bytes -= io.upload()
+        fresh = kv.build_step(seqs, q_lens, max_blocks, 0.0625, device="cpu")
+        total = sum(q_lens)
+        d = io.desc
+        assert (d.num_reqs, d.total_tokens, d.max_q_len) == (n, total, max(q_lens))
+        assert d.max_seq_len == fresh.desc.max_seq_len
+        arena, offs = io.dev.numpy(), io._offs   # the device-side copy after the partial upload
+        got = {"query_start_loc": arena[offs[0]:offs[0] + n + 1], "context_lens_before": arena[offs[1]:offs[1] + n],
+               "seq_lens_after": arena[offs[2]:offs[2] + n], "write_slot_mapping": arena[offs[3]:offs[3] + total],
+               "block_tables": arena[offs[4]:offs[4] + n * max_blocks].reshape(n, max_blocks)}
+        for key in ("query_start_loc", "context_lens_before", "seq_lens_after", "write_slot_mapping"):
+            assert (got[key] == fresh.host[key]).all(), key
+        # live part of every block-table row; entries past a row's pages are never read
+        for r, s in enumerate(seqs):
+            assert (got["block_tables"][r, :s.num_pages] == fresh.host["block_tables"][r, :s.num_pages]).all()
+        full_bytes += io.nbytes
+        # accept a random part of the step's tokens, hand the rest back
+        for s, q in zip(seqs, q_lens):
+            s.commit(rng.randrange(0, q + 1))
+            s.rollback()
+    assert full_bytes > 0   # the partial uploads moved fewer bytes than full ones would have
+    for s in seqs:
+        s.close()
+    assert pool.free_count == pool.num_pages
