@@ -8,7 +8,9 @@
 //   paged_attention_kernel<__half> (scalar path)  (op_kv_cache.cu:373-461, :619-792)
 //
 // Three launches per call:
-//   plan   : per request page range, item count and prefix sums -> scratch header.
+//   plan   : block 0: per request page range, item count and prefix sums -> scratch header;
+//            blocks 1..: the rotated, scaled query rows of every (request, kv head) as the
+//            stream kernel's MMA fragments (decode-sized batches).
 //   stream : persistent grid, one CTA per SM.  The work list is the flattened sequence of
 //            (request, kv head, row group, page) units, cut into equal contiguous shares, one
 //            per warp.  A warp streams its pages through a private ring of shared-memory
