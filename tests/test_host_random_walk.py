@@ -147,9 +147,6 @@ def test_persistent_step_arena_always_equals_a_fresh_pack(seed):
     step, block tables up to the last changed entry).  Over a random walk of growing, rolled-back
     and replaced sequences the device-side copy must always equal what a from-scratch pack of the
     same step produces (graph_io.rs:109-195, :368-420)."""
-    import numpy as np
-    import torch
-
     from warp34_b200 import kv
     rng = random.Random(seed)
     pool = PagePool(512)
