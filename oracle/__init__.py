@@ -41,6 +41,10 @@ def lib():
         L.w34o_tq4_decode_row.argtypes = [vp, vp]
         L.w34o_wht256.restype = None
         L.w34o_wht256.argtypes = [vp]
+        L.w34o_kv8_encode_row.restype = None
+        L.w34o_kv8_encode_row.argtypes = [vp, i, vp]
+        L.w34o_kv8_decode_row.restype = None
+        L.w34o_kv8_decode_row.argtypes = [vp, i, vp]
         for name in ("w34o_centroid", "w34o_boundary", "w34o_sign"):
             getattr(L, name).restype = C.c_float
             getattr(L, name).argtypes = [i]

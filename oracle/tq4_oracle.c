@@ -14,6 +14,11 @@
  *                              paged_attention_kernel<__half>
  *                              (op_kv_cache.cu:373-461, :619-792)
  *   - tables                   tq4_codebook.cuh:46-101 (via ../warp34_b200/csrc/tq4_tables.h)
+ *   - w34o_kv8_encode_row / _decode_row and the 8-bit branches of the two entry points follow the
+ *                              Q8_0 / FP8 E4M3 rows of the unrotated boundary layers
+ *                              (op_kv_cache.cu:32-151, op_paged_attn.cu:59-105); pinned on the GPU against the
+ *                              bytes the reference's kernels write, and here against a second, independent
+ *                              restatement (oracle/kv8.py)
  *
  * Parity status: the reference has no byte-level golden vectors for TQ4 and no
  * CPU implementation; this restatement is pinned against outputs of the
@@ -193,6 +198,90 @@ void w34o_tq4_decode_row(const uint8_t* row, float* out) {
 }
 
 /* ---- request lookup shared by both entry points ------------------------------ */
+/* ---- unrotated 8-bit rows (Q8_0, FP8 E4M3) ----------------------------------------
+ * Row definitions: crates/warp34-kernels/csrc/tq/tq4_kv_common.cuh:29-46; encode:
+ * ops/op_kv_cache.cu:32-151 (identity transform); decode to fp16: ops/op_paged_attn.cu:59-105. */
+static float e4m3_to_float(uint8_t v) {
+    const int e = (v >> 3) & 15, m = v & 7;
+    float a;
+    if (e == 0) a = ldexpf((float)m, -9);
+    else if (e == 15 && m == 7) a = NAN;
+    else a = ldexpf(1.0f + (float)m / 8.0f, e - 7);
+    return (v & 0x80) ? -a : a;
+}
+
+/* round to nearest even, saturating at +-448, NaN -> 0x7F (the satfinite conversion) */
+static uint8_t float_to_e4m3(float x) {
+    if (x != x) return 0x7F;
+    const uint8_t sign = signbit(x) ? 0x80 : 0;
+    float a = fabsf(x);
+    if (a > 448.0f) a = 448.0f;
+    if (a == 0.0f) return sign;
+    int e;
+    (void)frexpf(a, &e);      /* a = f * 2^e, f in [0.5, 1) */
+    e -= 1;                   /* floor(log2 a) */
+    if (e < -6) e = -6;       /* subnormal range shares the smallest normal's step */
+    float q = nearbyintf(ldexpf(a, 3 - e));   /* in units of 2^(e-3): 8..16 normal, 0..8 subnormal */
+    if (q >= 16.0f) { q = 8.0f; e += 1; }
+    const int r = (int)q;
+    if (r < 8) return (uint8_t)(sign | r);                       /* exponent field 0 */
+    return (uint8_t)(sign | ((e + 7) << 3) | (r - 8));
+}
+
+void w34o_kv8_encode_row(const uint16_t* x, int format, uint8_t* out) {
+    float v[256];
+    for (int i = 0; i < 256; ++i) v[i] = w34o_half_to_float(x[i]);
+    if (format == WARP34_KV_FORMAT_Q8_0) {
+        for (int sb = 0; sb < 4; ++sb) {
+            float amax = 0.0f;
+            for (int i = 0; i < 64; ++i) amax = fmaxf(amax, fabsf(v[64 * sb + i]));
+            const float d = amax / 127.0f;
+            const float inv = (d > 1e-12f) ? (1.0f / d) : 0.0f;
+            memcpy(out + 68 * sb, &d, 4);
+            for (int i = 0; i < 64; ++i) {
+                float q = roundf(v[64 * sb + i] * inv);
+                q = fminf(127.0f, fmaxf(-127.0f, q));
+                out[68 * sb + 4 + i] = (uint8_t)(int8_t)q;
+            }
+        }
+        return;
+    }
+    for (int h = 0; h < 2; ++h) {
+        float amax = 0.0f;
+        for (int i = 0; i < 128; ++i) amax = fmaxf(amax, fabsf(v[128 * h + i]));
+        const float d = amax * (1.0f / 448.0f);
+        const float inv = (d > 1e-30f) ? (1.0f / d) : 0.0f;
+        memcpy(out + 256 + 4 * h, &d, 4);
+        for (int i = 0; i < 128; ++i) out[128 * h + i] = float_to_e4m3(v[128 * h + i] * inv);
+    }
+}
+
+/* Values as the reference's readers hand them to the tensor cores: d * code, rounded to fp16. */
+void w34o_kv8_decode_row(const uint8_t* row, int format, float* out) {
+    if (format == WARP34_KV_FORMAT_Q8_0) {
+        for (int sb = 0; sb < 4; ++sb) {
+            float d;
+            memcpy(&d, row + 68 * sb, 4);
+            for (int i = 0; i < 64; ++i) {
+                out[64 * sb + i] = w34o_half_to_float(w34o_float_to_half(d * (float)(int8_t)row[68 * sb + 4 + i]));
+            }
+        }
+        return;
+    }
+    float d[2];
+    memcpy(d, row + 256, 8);
+    for (int i = 0; i < 256; ++i) {
+        out[i] = w34o_half_to_float(w34o_float_to_half(e4m3_to_float(row[i]) * d[i >> 7]));
+    }
+}
+
+static int is_kv8(const warp34_kv_layer_layout* l) {
+    const int k8 = l->k_format == WARP34_KV_FORMAT_Q8_0 || l->k_format == WARP34_KV_FORMAT_FP8_E4M3;
+    const int v8 = l->v_format == WARP34_KV_FORMAT_Q8_0 || l->v_format == WARP34_KV_FORMAT_FP8_E4M3;
+    return k8 && v8 && l->head_dim == 256 && l->k_transform == WARP34_KV_TRANSFORM_IDENTITY &&
+           l->v_transform == WARP34_KV_TRANSFORM_IDENTITY;
+}
+
 static int find_req(const warp34_attention_batch* b, int tok, int* q_start, int* q_end) {
     for (int r = 0; r < b->num_reqs; ++r) {
         const int lo = b->query_start_loc[r], hi = b->query_start_loc[r + 1];
@@ -259,6 +348,11 @@ static void write_one(void* p, long idx) {
                   (size_t)head * l->k_head_stride_bytes + (size_t)off * l->k_token_stride_bytes;
     uint8_t* vd = (uint8_t*)(uintptr_t)l->v_base + (size_t)page * l->v_page_stride_bytes +
                   (size_t)head * l->v_head_stride_bytes + (size_t)off * l->v_token_stride_bytes;
+    if (is_kv8(l)) {
+        w34o_kv8_encode_row(c->k + (size_t)tok * c->ks + (size_t)head * 256, l->k_format, kd);
+        w34o_kv8_encode_row(c->v + (size_t)tok * c->vs + (size_t)head * 256, l->v_format, vd);
+        return;
+    }
     w34o_tq4_encode_row(c->k + (size_t)tok * c->ks + (size_t)head * 256, kd, NULL, NULL);
     w34o_tq4_encode_row(c->v + (size_t)tok * c->vs + (size_t)head * 256, vd, NULL, NULL);
 }
@@ -269,9 +363,10 @@ int w34o_kv_cache_write_strided(const warp34_kv_layer_layout* l, const warp34_at
                                 int k_row_stride, int v_row_stride, int nthreads) {
     if (!l || !b || !k_in || !v_in) return 1;
     if (b->total_tokens <= 0 || l->local_kv_heads <= 0) return 0;
-    if (l->head_dim != 256 || l->k_format != WARP34_KV_FORMAT_TQ4 || l->v_format != WARP34_KV_FORMAT_TQ4 ||
-        l->k_transform != WARP34_KV_TRANSFORM_RADEMACHER_WHT256 ||
-        l->v_transform != WARP34_KV_TRANSFORM_RADEMACHER_WHT256) return 801;
+    if (!is_kv8(l) &&
+        (l->head_dim != 256 || l->k_format != WARP34_KV_FORMAT_TQ4 || l->v_format != WARP34_KV_FORMAT_TQ4 ||
+         l->k_transform != WARP34_KV_TRANSFORM_RADEMACHER_WHT256 ||
+         l->v_transform != WARP34_KV_TRANSFORM_RADEMACHER_WHT256)) return 801;
     const int min_stride = l->local_kv_heads * l->head_dim;
     if (k_row_stride < min_stride || v_row_stride < min_stride) return 1;
     write_ctx c = {l, b, k_in, v_in, k_row_stride, v_row_stride};
@@ -315,6 +410,34 @@ static void attn_one(void* p, long idx) {
     const uint16_t* q_row = c->q + ((size_t)tok * hq + q_head) * 256;
     uint16_t* out_row = c->out + ((size_t)tok * hq + q_head) * 256;
 
+    if (is_kv8(l)) {
+        /* unrotated rows: plain dequant-then-attend, one stream, fp32 with an online softmax */
+        if (c->triples) return;
+        float q[256], kx[256], vx[256], o[256];
+        for (int i = 0; i < 256; ++i) { q[i] = w34o_half_to_float(q_row[i]); o[i] = 0.0f; }
+        const int32_t* bl = b->block_tables + (size_t)req * b->max_blocks_per_req;
+        float m_i = -3.402823466e+38f, l_i = 0.0f;
+        for (int pos = min_kv; pos <= max_kv; ++pos) {
+            const int page = bl[pos / l->block_size], off = pos % l->block_size;
+            const uint8_t* kp = (const uint8_t*)(uintptr_t)l->k_base + (size_t)page * l->k_page_stride_bytes +
+                                (size_t)kv_head * l->k_head_stride_bytes + (size_t)off * l->k_token_stride_bytes;
+            const uint8_t* vp = (const uint8_t*)(uintptr_t)l->v_base + (size_t)page * l->v_page_stride_bytes +
+                                (size_t)kv_head * l->v_head_stride_bytes + (size_t)off * l->v_token_stride_bytes;
+            w34o_kv8_decode_row(kp, l->k_format, kx);
+            w34o_kv8_decode_row(vp, l->v_format, vx);
+            double dot = 0.0;
+            for (int i = 0; i < 256; ++i) dot += (double)q[i] * kx[i];
+            const float score = (float)dot * b->sm_scale;
+            const float m_new = fmaxf(m_i, score);
+            const float alpha = expf(m_i - m_new), pr = expf(score - m_new);
+            l_i = l_i * alpha + pr;
+            m_i = m_new;
+            for (int i = 0; i < 256; ++i) o[i] = o[i] * alpha + pr * vx[i];
+        }
+        const float inv = (l_i > 0.0f) ? (1.0f / l_i) : 0.0f;
+        for (int i = 0; i < 256; ++i) out_row[i] = w34o_float_to_half(o[i] * inv);
+        return;
+    }
     float qr[256];
     for (int i = 0; i < 256; ++i) qr[i] = w34o_half_to_float(q_row[i]) * sign_of(i);
     w34o_wht256(qr);
@@ -401,9 +524,10 @@ int w34o_paged_attention_f16(const warp34_kv_layer_layout* l, const warp34_atten
                              const uint16_t* q_in, uint16_t* attn_out, int num_q_heads, int nthreads) {
     if (!l || !b || !q_in || !attn_out) return 1;
     if (b->total_tokens <= 0 || num_q_heads <= 0) return 0;
-    if (l->head_dim != 256 || l->k_format != WARP34_KV_FORMAT_TQ4 || l->v_format != WARP34_KV_FORMAT_TQ4 ||
-        l->k_transform != WARP34_KV_TRANSFORM_RADEMACHER_WHT256 ||
-        l->v_transform != WARP34_KV_TRANSFORM_RADEMACHER_WHT256) return 801;
+    if (!is_kv8(l) &&
+        (l->head_dim != 256 || l->k_format != WARP34_KV_FORMAT_TQ4 || l->v_format != WARP34_KV_FORMAT_TQ4 ||
+         l->k_transform != WARP34_KV_TRANSFORM_RADEMACHER_WHT256 ||
+         l->v_transform != WARP34_KV_TRANSFORM_RADEMACHER_WHT256)) return 801;
     if (l->local_kv_heads <= 0 || num_q_heads % l->local_kv_heads) return 1;
     attn_ctx c = {l, b, q_in, attn_out, num_q_heads, NULL};
     parallel_for((long)b->total_tokens * num_q_heads, nthreads, attn_one, &c);
@@ -417,6 +541,7 @@ int w34o_paged_attention_partial(const warp34_kv_layer_layout* l, const warp34_a
     if (!l || !b || !q_in || !triples) return 1;
     if (b->total_tokens <= 0 || num_q_heads <= 0) return 0;
     if (l->local_kv_heads <= 0 || num_q_heads % l->local_kv_heads) return 1;
+    if (is_kv8(l)) return 801;   /* page-sharded partials exist for TQ4 layers only */
     attn_ctx c = {l, b, q_in, NULL, num_q_heads, triples};
     parallel_for((long)b->total_tokens * num_q_heads, nthreads, attn_one, &c);
     return 0;
