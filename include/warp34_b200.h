@@ -59,6 +59,12 @@ enum {
 /* Additive: multi-token verify batches (more than 8 query rows per request and KV head) take the
  * tcgen05 kernel, one 128-row CTA per request and KV head, instead of the split-KV team kernel. */
 #define WARP34_B200_EXEC_FLAG_TCGEN05_VERIFY (1ull << 42)
+/* Additive: the tensor-core kernels feed every operand as one fp16 value, as the reference's own
+ * tensor-core kernel does (op_paged_attn.cu:357, :47-50, :470).  Faster; a softmax weight is then
+ * off by a few 1e-4 relative, so an output channel in which large values of V cancel can miss
+ * 2e-3 + 1e-2 |b| against dequant-then-attend.  Without the flag the kernels carry the rounding
+ * residuals of Q', of the K centroids and of P through extra products and meet that bound. */
+#define WARP34_B200_EXEC_FLAG_FAST_ATTENTION (1ull << 43)
 
 /* ---- descriptors (reference: warp34_cuda.h:50-101) -------------------------- */
 typedef struct {

@@ -160,10 +160,7 @@ constexpr int kRowsPerGroup = 8;            // N of the MMA: query rows per work
 constexpr int kLutBytes = 256 * 256;         // byte-pair table: 256-byte entry stride, 32 lane copies each
 constexpr int kPartialFloats = kRowsPerGroup * kHeadDim + 2 * kRowsPerGroup;
 constexpr long long kWaitCycleLimit = 1ll << 31;  // about one second of SM clocks
-#ifndef W34_MIN_UNITS
-#define W34_MIN_UNITS 4
-#endif
-constexpr int kMinUnitsPerWarp = W34_MIN_UNITS;
+constexpr int kMinUnitsPerWarp = 4;   // 8, 16 and 32 measured equal or slower on small batches
 // The lookup table holds fp16(kLutScale * centroid).  fp16 rounding of the 8 centroid
 // magnitudes is a systematic error of up to 3.7e-4 relative; with this common factor every one
 // of them lands within 9.5e-5 of an fp16 grid point (found by exhaustive search over
@@ -212,12 +209,9 @@ __device__ __forceinline__ int32_t* plan_array(uint8_t* scratch, int which, int 
     return reinterpret_cast<int32_t*>(scratch + sizeof(PlanHeader)) + (size_t)which * (num_reqs + 1);
 }
 
-#ifndef W34_SPLIT_Q
-#define W34_SPLIT_Q 0   // second QK MMA with the fp16 rounding residual of Q'
-#endif
 // Words per lane of one work item's query fragments: 16 k-steps x 2 B-fragment words of fp16(Q'),
-// plus 16 words of residual bytes when the second QK product is compiled in.
-constexpr int kQFragWords = W34_SPLIT_Q ? 48 : 32;
+// then 16 words holding the fp16 rounding residual of Q' as e5m2 bytes (four per k-step).
+constexpr int kQFragWords = 48;
 __host__ __device__ inline size_t qfrag_item_bytes() { return (size_t)kQFragWords * 32 * sizeof(uint32_t); }
 __device__ void qprep_block(const StreamParams& p, int idx);
 constexpr int kPlanThreads = 32 * kRowsPerGroup;  // the query-fragment blocks use one warp per query row
@@ -351,6 +345,12 @@ __device__ __forceinline__ uint32_t lds32_lut(uint32_t addr) {
     asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
     return v;
 }
+template <bool B> struct BoolTag { static constexpr bool value = B; };
+__device__ __forceinline__ uint2 lds64_lut(uint32_t addr) {
+    uint2 v;
+    asm("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
 __device__ __forceinline__ uint32_t lds32_dep(uint32_t addr, uint32_t token) {
     uint32_t v;
     asm("ld.shared.u32 %0, [%1+0];  // dep %2" : "=r"(v) : "r"(addr), "r"(token));
@@ -416,23 +416,27 @@ __device__ __forceinline__ uint32_t token_offset(int t) {  // byte offset of tok
     return (uint32_t)((t >> 3) * kHalfStride + (t & 7) * kTq4RowBytes);
 }
 
-#ifndef W34_WARPS
-#define W34_WARPS 12
-#endif
-#ifndef W34_STAGES
-#define W34_STAGES 3
-#endif
-// Optional extra-precision MMAs (compile-time).  Measured on the 64-sequence decode benchmark:
-// SPLIT_Q adds 22% to the kernel time and cuts score errors about 4x (Q' is then accurate to
-// 2^-14 instead of 2^-11); SPLIT_P adds 8% and only matters for softmaxes over a handful of keys.
-// Both are off by default: the fp16 lookup-table values of K bound the score accuracy either
-// way, and callers that need fp32 scores can set WARP34_B200_EXEC_FLAG_PRECISE_ATTENTION.
-#ifndef W34_QK_CHAINS
-#define W34_QK_CHAINS 2   // independent accumulator chains of the QK product per 128-half x 2
-#endif
-#ifndef W34_SPLIT_P
-#define W34_SPLIT_P 0   // second PV MMA with the fp16 rounding residual of P * d_v
-#endif
+// The streaming kernel comes in two builds.
+//  * exact (default): every fp16 tensor-core operand that carries a rounding error of its own is
+//    fed as value + residual: Q' (residual kept as e5m2 bytes, widened in registers), the K
+//    centroids (the lookup returns value pair and residual pair at once) and, on pages where some
+//    weight is large enough to matter, P x d_v.  Three score MMAs per k-step instead of one.  With
+//    fp16 operands alone a softmax weight is off by a few 1e-4 relative, which a x20 outlier channel
+//    of V turns into several 1e-3 absolute where its large terms cancel.
+//  * fast (WARP34_B200_EXEC_FLAG_FAST_ATTENTION): single fp16 operands, as the reference's own
+//    tensor-core kernel computes (op_paged_attn.cu:357, :47-50, :470).
+constexpr int kFastWarps = 12, kFastStages = 3;
+constexpr int kExactWarps = 8, kExactStages = 4;
+// A page is "peaked" when one of its softmax weights exceeds this fraction of the running maximum.
+// Only there does the rounding residual of the V centroids (1e-4 relative, but the same for every
+// coordinate that holds the same code, so the inverse rotation can collect it on one channel) go
+// through an extra product: a weight below a quarter of the maximum moves the output by less than
+// a quarter of that.
+constexpr float kPeakedWeight = 0.25f;
+// Rounding residuals are 2^-12 of their values, which for Q' (about 0.1) and for the table's
+// centroids (0.008 .. 0.16) lies in fp16's subnormal range; as e5m2 bytes they would keep no
+// significant bits at all.  They are stored times 2^11 and the products scaled back in fp32.
+constexpr float kResidualScale = 2048.0f;
 
 // Eight warps: the query fragments of item idx = (request * kv heads + kv head) * q_groups_max + group.
 // Warp w rotates and scales query row w of the group into shared memory (fp32 [8 rows][256 rotated
@@ -472,8 +476,8 @@ __device__ void qprep_block(const StreamParams& p, int idx) {
     __syncthreads();
     // B fragments of Q'^T: step s (0..7) covers half s >> 2, virtual word 4 tig + (s & 3);
     // k-step 2 s uses elements 0..3 of the word, k-step 2 s + 1 elements 4..7.
-    // Q' = hi + lo: hi is fp16, lo (the fp16 rounding residual) is kept as 4 e5m2 bytes per
-    // k-step and widened to fp16 pairs by two PRMTs right before its MMA.
+    // Q' = hi + lo: hi is fp16, lo (the fp16 rounding residual, times kResidualScale) is kept as
+    // 4 e5m2 bytes per k-step and widened to fp16 pairs by two PRMTs right before its MMA.
     const int s = wid;
     const int half = s >> 2, vw = 4 * tig + (s & 3);
     uint32_t* dst = p.qfrag + (size_t)idx * (kQFragWords * 32) + lane;
@@ -488,36 +492,19 @@ __device__ void qprep_block(const StreamParams& p, int idx) {
             const __half h0 = __float2half_rn(f0), h1 = __float2half_rn(f1);
             dst[(2 * (2 * s + hk) + x) * 32] = (uint32_t)__half_as_ushort(h0) | ((uint32_t)__half_as_ushort(h1) << 16);
             // residuals, rounded to the top byte of their fp16 encoding (e5m2)
-            const uint32_t r0 = __half_as_ushort(__float2half_rn(f0 - __half2float(h0)));
-            const uint32_t r1 = __half_as_ushort(__float2half_rn(f1 - __half2float(h1)));
+            const uint32_t r0 = __half_as_ushort(__float2half_rn((f0 - __half2float(h0)) * kResidualScale));
+            const uint32_t r1 = __half_as_ushort(__float2half_rn((f1 - __half2float(h1)) * kResidualScale));
             const uint32_t b0 = (r0 + 0x7fu + ((r0 >> 8) & 1u)) >> 8;
             const uint32_t b1 = (r1 + 0x7fu + ((r1 >> 8) & 1u)) >> 8;
             lo_bytes |= (b0 & 0xffu) << (16 * x) | (b1 & 0xffu) << (16 * x + 8);
         }
-        if (W34_SPLIT_Q) dst[(32 + 2 * s + hk) * 32] = lo_bytes;
+        dst[(32 + 2 * s + hk) * 32] = lo_bytes;
     }
 }
 
-#ifdef W34_STREAM_PROFILE
-// Development aid: per-warp time stamps (ns) written at scratch + 48 MiB; needs a 64 MiB scratch.
-__device__ __forceinline__ unsigned long long prof_now() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-#define W34_STAMP(i) do { if (lane == 0) prof_t[i] = prof_now(); } while (0)
-#else
-#define W34_STAMP(i) do { } while (0)
-#endif
-
-template <int STAGES>
-__global__ void __launch_bounds__(W34_WARPS * 32, 1) tq4_attention_stream_kernel(const StreamParams p) {
+template <int STAGES, int WARPS, bool EXACT>
+__global__ void __launch_bounds__(WARPS * 32, 1) tq4_attention_stream_kernel(const StreamParams p) {
     extern __shared__ __align__(1024) uint8_t smem[];
-#ifdef W34_STREAM_PROFILE
-    unsigned long long prof_t[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    const unsigned long long prof_t0 = prof_now();
-    int prof_segments = 0;
-#endif
     // The lookup table sits at the first 64 KB-aligned SHARED address inside the dynamic window,
     // so that (table address | code byte << 8 | lane << 2) is one PRMT.  Warp rings fill the
     // space below and above it; the mbarriers follow the last ring.
@@ -544,8 +531,21 @@ __global__ void __launch_bounds__(W34_WARPS * 32, 1) tq4_attention_stream_kernel
     // half2(s * centroid[byte & 15], s * centroid[byte >> 4]); bank = lane for any data.
     for (int i = threadIdx.x; i < 256 * 32; i += blockDim.x) {
         const int byte = i >> 5, ln = i & 31;
-        sts32(lut_addr + (uint32_t)(byte * 256 + ln * 4),
-              pack_half2(kLutScale * tq4_centroid(byte & 15), kLutScale * tq4_centroid(byte >> 4)));
+        const float c0 = kLutScale * tq4_centroid(byte & 15), c1 = kLutScale * tq4_centroid(byte >> 4);
+        if (EXACT) {
+            // K table: (value pair, residual pair) in 16 copies of 8 bytes; V table: value pair in
+            // 32 copies of 4 bytes, in the upper half of the same 256-byte entry
+            const uint32_t hi = pack_half2(c0, c1);
+            const float2 hf = __half22float2(*reinterpret_cast<const __half2*>(&hi));
+            if (ln < 16) {
+                sts32(lut_addr + (uint32_t)(byte * 256 + ln * 8), hi);
+                sts32(lut_addr + (uint32_t)(byte * 256 + ln * 8 + 4),
+                      pack_half2((c0 - hf.x) * kResidualScale, (c1 - hf.y) * kResidualScale));
+            }
+            sts32(lut_addr + (uint32_t)(byte * 256 + 128 + ln * 4), hi);
+        } else {
+            sts32(lut_addr + (uint32_t)(byte * 256 + ln * 4), pack_half2(c0, c1));
+        }
     }
     if (lane == 0) {
         for (int s = 0; s < STAGES; ++s) mbar_init(bars + 8u * s, 1u);
@@ -561,7 +561,6 @@ __global__ void __launch_bounds__(W34_WARPS * 32, 1) tq4_attention_stream_kernel
     const int32_t* ngroups_a = plan_array(p.scratch, 4, R);
     float* partials = reinterpret_cast<float*>(p.scratch + plan_bytes(R));
 
-    W34_STAMP(1);
     // Worker index: consecutive workers sit on different SMs, so that a step with fewer shares
     // than warps spreads over the whole GPU instead of filling the first CTAs.
     const int w_global = wid * (int)gridDim.x + (int)blockIdx.x;
@@ -577,7 +576,9 @@ __global__ void __launch_bounds__(W34_WARPS * 32, 1) tq4_attention_stream_kernel
     const int key_a = (gid & 3) + 8 * (gid >> 2);      // row gid; row gid + 8 is token key_a + 4
     // In the PV product thread tig owns tokens kv0 + {0, 1, 4, 5} (k positions 2tig, 2tig+1, +8, +9).
     const int kv0 = 2 * (tig & 1) + 8 * (tig >> 1);
-    const uint32_t lut_lane = lut_addr + 4u * lane;  // byte 1 is zero: the code byte goes there
+    // byte 1 of these is zero: the code byte goes there
+    const uint32_t lut_lane = EXACT ? lut_addr + 128u + 4u * lane : lut_addr + 4u * lane;   // V (and K) values
+    const uint32_t lutk_lane = lut_addr + 8u * (lane & 15);                                      // K value + residual
     uint32_t phase_bits = 0;   // bit s = parity to wait for on stage s
     uint32_t pending = 0;      // bit s = a copy into stage s has been issued and not yet awaited
     bool failed = false;
@@ -593,7 +594,6 @@ __global__ void __launch_bounds__(W34_WARPS * 32, 1) tq4_attention_stream_kernel
         r = lo;
     }
 
-    W34_STAMP(2);
     while (u < u_end && !failed) {
         while (unit_prefix[r + 1] <= u) ++r;  // skips requests without units
         const int npages = npages_a[r];
@@ -640,7 +640,7 @@ __global__ void __launch_bounds__(W34_WARPS * 32, 1) tq4_attention_stream_kernel
             for (int i = 0; i < 16; ++i) {
                 qb[i][0] = __ldg(qf + (2 * i) * 32);
                 qb[i][1] = __ldg(qf + (2 * i + 1) * 32);
-                qlo[i] = W34_SPLIT_Q ? __ldg(qf + (32 + i) * 32) : 0u;
+                qlo[i] = EXACT ? __ldg(qf + (32 + i) * 32) : 0u;
             }
         }
         // ---- accumulators ----------------------------------------------------------------
@@ -657,9 +657,6 @@ __global__ void __launch_bounds__(W34_WARPS * 32, 1) tq4_attention_stream_kernel
         int32_t my_page = (lane < n_here) ? blocks[pg0 + lane] : 0;  // page ids of units [0, 32)
         int32_t next_page = (32 + lane < n_here) ? blocks[pg0 + 32 + lane] : 0;
 
-#ifdef W34_STREAM_PROFILE
-        if (prof_segments++ == 0) W34_STAMP(3);
-#endif
         fence_proxy_async();  // the staging writes above precede async-proxy writes to the ring
         auto issue = [&](int idx) {  // called by all lanes; lane 0 issues the four copies
             const int32_t page = __shfl_sync(0xffffffffu, (idx & 32) ? next_page : my_page, idx & 31);
@@ -697,9 +694,6 @@ __global__ void __launch_bounds__(W34_WARPS * 32, 1) tq4_attention_stream_kernel
             if (!mbar_wait(bars + 8u * s, (phase_bits >> s) & 1u)) { failed = true; break; }
             phase_bits ^= 1u << s;
             pending &= ~(1u << s);
-#ifdef W34_STREAM_PROFILE
-            if (prof_segments == 1 && i == 0) W34_STAMP(4);
-#endif
 
             const uint32_t kst = ring + (uint32_t)s * kStageStride;
             const uint32_t vst = kst + kRunStride;
@@ -708,13 +702,15 @@ __global__ void __launch_bounds__(W34_WARPS * 32, 1) tq4_attention_stream_kernel
             const uint32_t ptok = page_token(i);
 #define W34_LDS(addr) lds32_dep(addr, ptok)
 #define W34_LUT(word, k) lds32_lut(__byte_perm((word), lut_lane, 0x7604 + ((k) << 4)))
+#define W34_LUTK(word, k) lds64_lut(__byte_perm((word), lutk_lane, 0x7604 + ((k) << 4)))
 
             // ---- S^T = K Q'^T, one accumulator per 128-half ------------------------------
-            float sa[2][4], sl[2][4];  // hi and lo chains are independent
+            float sa[2][4], sl[2][4], sk[2][4];  // value, query-residual and key-residual chains are independent
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 sa[h][0] = sa[h][1] = sa[h][2] = sa[h][3] = 0.0f;
                 sl[h][0] = sl[h][1] = sl[h][2] = sl[h][3] = 0.0f;
+                sk[h][0] = sk[h][1] = sk[h][2] = sk[h][3] = 0.0f;
             }
             const uint32_t krow_a = kst + token_offset(key_a);
             const uint32_t krow_b = krow_a + 4u * kTq4RowBytes;
@@ -739,19 +735,25 @@ __global__ void __launch_bounds__(W34_WARPS * 32, 1) tq4_attention_stream_kernel
                 }
 #pragma unroll
                 for (int hk = 0; hk < 2; ++hk) {
-                    const uint32_t a0 = W34_LUT(wa, 2 * hk);
-                    const uint32_t a1 = W34_LUT(wb, 2 * hk);
-                    const uint32_t a2 = W34_LUT(wa, 2 * hk + 1);
-                    const uint32_t a3 = W34_LUT(wb, 2 * hk + 1);
+                    uint32_t a0, a1, a2, a3;
+                    if (EXACT) {
+                        const uint2 e0 = W34_LUTK(wa, 2 * hk), e1 = W34_LUTK(wb, 2 * hk);
+                        const uint2 e2 = W34_LUTK(wa, 2 * hk + 1), e3 = W34_LUTK(wb, 2 * hk + 1);
+                        a0 = e0.x; a1 = e1.x; a2 = e2.x; a3 = e3.x;
+                        mma16816(sk[half], e0.y, e1.y, e2.y, e3.y, qb[2 * s8 + hk][0], qb[2 * s8 + hk][1]);
+                    } else {
+                        a0 = W34_LUT(wa, 2 * hk);
+                        a1 = W34_LUT(wb, 2 * hk);
+                        a2 = W34_LUT(wa, 2 * hk + 1);
+                        a3 = W34_LUT(wb, 2 * hk + 1);
+                    }
                     const uint32_t ql = qlo[2 * s8 + hk];
-                    if (W34_QK_CHAINS == 4 && !W34_SPLIT_Q && hk == 1) {
-                        mma16816(sl[half], a0, a1, a2, a3, qb[2 * s8 + hk][0], qb[2 * s8 + hk][1]);
-                    } else if ((s8 & 3) == 0 && hk == 0) {
+                    if ((s8 & 3) == 0 && hk == 0) {
                         mma16816_zero(sa[half], a0, a1, a2, a3, qb[2 * s8 + hk][0], qb[2 * s8 + hk][1]);
                     } else {
                         mma16816(sa[half], a0, a1, a2, a3, qb[2 * s8 + hk][0], qb[2 * s8 + hk][1]);
                     }
-                    if (W34_SPLIT_Q) {
+                    if (EXACT) {   // residual bytes -> fp16 pairs: byte b becomes the half b << 8
                         mma16816(sl[half], a0, a1, a2, a3, __byte_perm(ql, 0, 0x1404), __byte_perm(ql, 0, 0x3424));
                     }
                 }
@@ -762,11 +764,11 @@ __global__ void __launch_bounds__(W34_WARPS * 32, 1) tq4_attention_stream_kernel
             const float dkb0 = __half2float(__ushort_as_half((unsigned short)(kb0 & 0xffffu)));
             const float dkb1 = __half2float(__ushort_as_half((unsigned short)(kb16 >> 16)));
             // sc[0],sc[1]: token key_a, rows 2tig, 2tig+1;  sc[2],sc[3]: token key_a + 4
-            if (W34_SPLIT_Q || W34_QK_CHAINS == 4) {
+            if (EXACT) {
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
 #pragma unroll
-                    for (int x = 0; x < 4; ++x) sa[h][x] += sl[h][x];
+                    for (int x = 0; x < 4; ++x) sa[h][x] += (sl[h][x] + sk[h][x]) * (1.0f / kResidualScale);
                 }
             }
             float sc[4];
@@ -827,20 +829,23 @@ __global__ void __launch_bounds__(W34_WARPS * 32, 1) tq4_attention_stream_kernel
             }
             l_run[0] += pr[0] + pr[2];
             l_run[1] += pr[1] + pr[3];
-            // P * d_v per half as B fragments (k = key, n = query row), split into an fp16 value
-            // and the fp16 of its rounding residual so that few-key softmaxes keep fp32-like weights
-            uint32_t pb[2][2], pl[2][2];
-            {
-                const float pd[2][4] = {{pr[0] * dva0, pr[1] * dva0, pr[2] * dvb0, pr[3] * dvb0},
-                                        {pr[0] * dva1, pr[1] * dva1, pr[2] * dvb1, pr[3] * dvb1}};
+            // P * d_v per half as B fragments (k = key, n = query row); the exact build adds the fp16
+            // rounding residual of P * d_v as a second fragment.
+            // (rows that do not exist score 0 against their zero query; they must not count as peaks)
+            uint32_t pb[2][2], pl[2][2] = {{0u, 0u}, {0u, 0u}};
+            const float pk0 = rvalid[0] ? fmaxf(pr[0], pr[2]) : 0.0f, pk1 = rvalid[1] ? fmaxf(pr[1], pr[3]) : 0.0f;
+            const bool peaked = EXACT && __any_sync(0xffffffffu, fmaxf(pk0, pk1) > kPeakedWeight);
+            const float pd[2][4] = {{pr[0] * dva0, pr[1] * dva0, pr[2] * dvb0, pr[3] * dvb0},
+                                    {pr[0] * dva1, pr[1] * dva1, pr[2] * dvb1, pr[3] * dvb1}};
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
+            for (int h = 0; h < 2; ++h) {
 #pragma unroll
-                    for (int x = 0; x < 2; ++x) {
-                        const __half2 hi = __floats2half2_rn(pd[h][2 * x], pd[h][2 * x + 1]);
+                for (int x = 0; x < 2; ++x) {
+                    const __half2 hi = __floats2half2_rn(pd[h][2 * x], pd[h][2 * x + 1]);
+                    pb[h][x] = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&hi));
+                    if (EXACT) {
                         const float2 hf = __half22float2(hi);
                         const __half2 lo = __floats2half2_rn(pd[h][2 * x] - hf.x, pd[h][2 * x + 1] - hf.y);
-                        pb[h][x] = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&hi));
                         pl[h][x] = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&lo));
                     }
                 }
@@ -851,6 +856,10 @@ __global__ void __launch_bounds__(W34_WARPS * 32, 1) tq4_attention_stream_kernel
             // tokens kv0 + {0, 1, 4, 5}
             const uint32_t vr = vst + token_offset(kv0);
             const uint32_t vwb = 4u * (uint32_t)(gid >> 1) + (uint32_t)(gid & 1);
+            // Every page: V P (+ V P_residual).  A peaked page then adds V_residual P in a second pass
+            // over its V codes (the K table holds the residuals).
+            // The second pass is a branch of its own so that the common pass stays one basic block
+            // with the softmax above it, whose latencies its loads and look-ups fill.
 #pragma unroll
             for (int i4 = 0; i4 < 4; ++i4) {
                 const int half = i4 >> 1;
@@ -878,10 +887,53 @@ __global__ void __launch_bounds__(W34_WARPS * 32, 1) tq4_attention_stream_kernel
                     const uint32_t a2 = W34_LUT(lo_cd, t);
                     const uint32_t a3 = W34_LUT(hi_cd, t);
                     mma16816(o[4 * i4 + t], a0, a1, a2, a3, pb[half][0], pb[half][1]);
-                    if (W34_SPLIT_P) mma16816(o[4 * i4 + t], a0, a1, a2, a3, pl[half][0], pl[half][1]);
+                    if (EXACT) mma16816(o[4 * i4 + t], a0, a1, a2, a3, pl[half][0], pl[half][1]);
                 }
             }
+            if (peaked) {
+                // P * d_v / kResidualScale, the partner of the scaled centroid residuals
+                uint32_t ps[2][2];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+#pragma unroll
+                    for (int x = 0; x < 2; ++x) {
+                        const __half2 sc2 = __floats2half2_rn(pd[h][2 * x] * (1.0f / kResidualScale),
+                                                              pd[h][2 * x + 1] * (1.0f / kResidualScale));
+                        ps[h][x] = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&sc2));
+                    }
+                }
+                auto pv_fix = [&]() {
+#pragma unroll
+                    for (int i4 = 0; i4 < 4; ++i4) {
+                        const int half = i4 >> 1;
+                        uint32_t w[4];
+                        const uint32_t off = 4u * ((half ? 17u : 0u) + vwb + 2u * (i4 & 1));
+                        w[0] = W34_LDS(vr + off);
+                        w[1] = W34_LDS(vr + kTq4RowBytes + off);
+                        w[2] = W34_LDS(vr + 4u * kTq4RowBytes + off);
+                        w[3] = W34_LDS(vr + 5u * kTq4RowBytes + off);
+                        if (i4 == 0 && gid == 0) {
+                            w[0] = (w[0] >> 16) | (W34_LDS(vr + 64) << 16);
+                            w[1] = (w[1] >> 16) | (W34_LDS(vr + kTq4RowBytes + 64) << 16);
+                            w[2] = (w[2] >> 16) | (W34_LDS(vr + 4u * kTq4RowBytes + 64) << 16);
+                            w[3] = (w[3] >> 16) | (W34_LDS(vr + 5u * kTq4RowBytes + 64) << 16);
+                        }
+                        const uint32_t lo_ab = (w[0] & 0x0f0f0f0fu) | ((w[1] << 4) & 0xf0f0f0f0u);
+                        const uint32_t hi_ab = ((w[0] >> 4) & 0x0f0f0f0fu) | (w[1] & 0xf0f0f0f0u);
+                        const uint32_t lo_cd = (w[2] & 0x0f0f0f0fu) | ((w[3] << 4) & 0xf0f0f0f0u);
+                        const uint32_t hi_cd = ((w[2] >> 4) & 0x0f0f0f0fu) | (w[3] & 0xf0f0f0f0u);
+#pragma unroll
+                        for (int t = 0; t < 4; ++t) {
+                            const uint2 e0 = W34_LUTK(lo_ab, t), e1 = W34_LUTK(hi_ab, t);
+                            const uint2 e2 = W34_LUTK(lo_cd, t), e3 = W34_LUTK(hi_cd, t);
+                            mma16816(o[4 * i4 + t], e0.y, e1.y, e2.y, e3.y, ps[half][0], ps[half][1]);
+                        }
+                    }
+                };
+                pv_fix();
+            }
 #undef W34_LUT
+#undef W34_LUTK
 #undef W34_LDS
             __syncwarp();  // every lane is done with stage s before it is refilled
         }
@@ -897,7 +949,6 @@ __global__ void __launch_bounds__(W34_WARPS * 32, 1) tq4_attention_stream_kernel
             break;
         }
 
-        W34_STAMP(5);  // last segment's value survives
         // ---- write the partial: natural column order, through the idle ring ------------------
         // l: add the 8 lanes (gid) that share a query row
 #pragma unroll
@@ -935,15 +986,6 @@ __global__ void __launch_bounds__(W34_WARPS * 32, 1) tq4_attention_stream_kernel
         __syncwarp();
         u += n_here;
     }
-#ifdef W34_STREAM_PROFILE
-    if (lane == 0) {
-        unsigned long long* dst = reinterpret_cast<unsigned long long*>(p.scratch + (48u << 20)) + (size_t)w_global * 8;
-        dst[0] = prof_t0;
-        for (int i = 1; i < 6; ++i) dst[i] = prof_t[i];
-        dst[6] = prof_now();
-        dst[7] = (unsigned long long)prof_segments;
-    }
-#endif
 }
 
 // ---------------------------------------------------------------------------------------
@@ -2105,13 +2147,14 @@ __global__ void __launch_bounds__(128) kv_page_copy_kernel(const warp34_kv_layer
 }
 
 // ---- host side ---------------------------------------------------------------------------
-constexpr int kStages = W34_STAGES;
-constexpr int kWarpsPerCta = W34_WARPS;
+constexpr int kWarpsPerCta = kFastWarps > kExactWarps ? kFastWarps : kExactWarps;   // scratch is sized for the larger build
 
 // LUT + rings + mbarriers, plus up to 64 KB - 1 of alignment slack in front of the table; the
 // kernel is given the whole opt-in maximum and checks the carve-up itself.
 static size_t stream_smem_min_bytes() {
-    return kLutBytes + (size_t)kWarpsPerCta * kStages * (kStageStride + 8);
+    const size_t fast = (size_t)kFastWarps * kFastStages * (kStageStride + 8);
+    const size_t exact = (size_t)kExactWarps * kExactStages * (kStageStride + 8);
+    return kLutBytes + (fast > exact ? fast : exact);
 }
 
 static size_t prefill_smem_bytes() {
@@ -2139,7 +2182,10 @@ static DeviceInfo* device_info(int* rc) {
         *rc = (int)cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
         if (*rc != 0) return nullptr;
         if ((size_t)optin < stream_smem_min_bytes()) { *rc = (int)cudaErrorNotSupported; return nullptr; }
-        *rc = (int)cudaFuncSetAttribute(tq4_attention_stream_kernel<kStages>,
+        *rc = (int)cudaFuncSetAttribute(tq4_attention_stream_kernel<kExactStages, kExactWarps, true>,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, optin);
+        if (*rc != 0) return nullptr;
+        *rc = (int)cudaFuncSetAttribute(tq4_attention_stream_kernel<kFastStages, kFastWarps, false>,
                                         cudaFuncAttributeMaxDynamicSharedMemorySize, optin);
         if (*rc != 0) return nullptr;
         *rc = (int)cudaFuncSetAttribute(tq4_attention_team_kernel<2>,
@@ -2327,7 +2373,8 @@ static int launch_attention(const warp34_exec* ex, const warp34_kv_layer_layout*
     // item) or four-warp teams (16 / 24 rows per item).
     const int nt = pick_row_tiles(batch, gqa);
     const int rpg = 8 * nt;
-    const int workers_per_cta = (nt == 1) ? kWarpsPerCta : kTeams;
+    const bool fast = (ex->flags & WARP34_B200_EXEC_FLAG_FAST_ATTENTION) != 0;
+    const int workers_per_cta = (nt == 1) ? (fast ? kFastWarps : kExactWarps) : kTeams;
     const long long items = items_bound(layout, batch, num_q_heads, rpg);
     const long long units_bound = items * (long long)(batch->max_blocks_per_req > 0 ? batch->max_blocks_per_req : 1);
     const size_t plan = plan_bytes(batch->num_reqs);
@@ -2379,7 +2426,8 @@ static int launch_attention(const warp34_exec* ex, const warp34_kv_layer_layout*
     p.q_groups_max = (nt == 1) ? (int)(q_items / ((long long)batch->num_reqs * layout->local_kv_heads)) : 0;
     tq4_attention_plan_kernel<<<1 + (unsigned)q_items, q_items > 0 ? kPlanThreads : 32, 0, st>>>(p);
     if (nt == 1) {
-        tq4_attention_stream_kernel<kStages><<<grid, kWarpsPerCta * 32, smem, st>>>(p);
+        if (fast) tq4_attention_stream_kernel<kFastStages, kFastWarps, false><<<grid, kFastWarps * 32, smem, st>>>(p);
+        else tq4_attention_stream_kernel<kExactStages, kExactWarps, true><<<grid, kExactWarps * 32, smem, st>>>(p);
     } else if (nt == 2) {
         tq4_attention_team_kernel<2><<<grid, kTeams * kTeamWarps * 32, smem, st>>>(p);
     } else {

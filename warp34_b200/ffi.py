@@ -20,6 +20,7 @@ POLICY_FP16, POLICY_BF16, POLICY_Q8_0, POLICY_FP8, POLICY_TQ4, POLICY_TQ4_ALL = 
 EXEC_FLAG_PRECISE_ATTENTION = 1 << 40
 EXEC_FLAG_PREFILL_MMA_SYNC = 1 << 41
 EXEC_FLAG_TCGEN05_VERIFY = 1 << 42
+EXEC_FLAG_FAST_ATTENTION = 1 << 43
 CUDA_ERROR_INVALID_VALUE = 1
 CUDA_ERROR_NOT_SUPPORTED = 801
 W34_ERR_INVALID, W34_ERR_EXHAUSTED, W34_ERR_PROTECTED, W34_ERR_CAPACITY = -1, -2, -3, -4
