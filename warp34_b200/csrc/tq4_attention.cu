@@ -2237,12 +2237,26 @@ static long long qfrag_items(const warp34_kv_layer_layout* l, const warp34_atten
     return (long long)b->num_reqs * l->local_kv_heads * groups;
 }
 
-// Query rows that share one KV pass: 8 with one warp per work item (decode), 16 or 24 with
-// four-warp teams (several draft tokens per request, or prefill chunks).
-static int pick_row_tiles(const warp34_attention_batch* b, int gqa) {
+// Query rows that share one KV pass.  Exact build: 8, one warp per work item; a request with more
+// rows per kv head (several draft tokens) becomes several items that read the same pages, close
+// enough in time for the second and third read to come from L2.  Fast build: 8 with one warp per
+// item, 16 or 24 with four-warp teams.
+static int pick_row_tiles(const warp34_attention_batch* b, int gqa, bool fast) {
     const long long rows = (long long)(b->max_q_len > 0 ? b->max_q_len : 1) * gqa;
-    if (rows <= 8) return 1;
+    if (!fast || rows <= 8) return 1;
     return rows <= 16 ? 2 : 3;
+}
+
+// Workspace of the streaming path with `workers` worker warps (or teams): plan, one partial slot
+// per worker and per work item, and the query fragments of one-warp items.
+static size_t stream_scratch_bytes(const warp34_kv_layer_layout* l, const warp34_attention_batch* b, int hq,
+                                   bool fast, long long workers) {
+    const int gqa = hq / l->local_kv_heads;
+    const int nt = pick_row_tiles(b, gqa, fast);
+    const int rpg = 8 * nt;
+    const long long slots = workers + items_bound(l, b, hq, rpg);
+    const size_t qfrag = (nt == 1) ? (size_t)qfrag_items(l, b, gqa) * qfrag_item_bytes() : 0;
+    return plan_bytes(b->num_reqs) + (size_t)slots * (size_t)(rpg * kHeadDim + 2 * rpg) * sizeof(float) + qfrag;
 }
 
 }  // namespace w34
@@ -2286,15 +2300,25 @@ extern "C" size_t warp34_paged_attention_scratch_bytes(const warp34_kv_layer_lay
     int rc = 0;
     w34::DeviceInfo* d = w34::device_info(&rc);
     const int sms = d ? d->sm_count : 148;
-    const int nt = w34::pick_row_tiles(batch, num_q_heads / layout->local_kv_heads);
-    const int rpg = 8 * nt;
-    const long long slots = (long long)sms * (nt == 1 ? w34::kWarpsPerCta : w34::kTeams) +
-                            w34::items_bound(layout, batch, num_q_heads, rpg);
-    const size_t qfrag = (nt == 1) ? (size_t)w34::qfrag_items(layout, batch, num_q_heads / layout->local_kv_heads) * w34::qfrag_item_bytes() : 0;
-    return w34::plan_bytes(batch->num_reqs) + (size_t)slots * (size_t)(rpg * w34::kHeadDim + 2 * rpg) * sizeof(float) + qfrag;
+    // enough for a full grid in either build
+    const int gqa = num_q_heads / layout->local_kv_heads;
+    const int nt_fast = w34::pick_row_tiles(batch, gqa, true);
+    const size_t fast = w34::stream_scratch_bytes(layout, batch, num_q_heads, true,
+                                                  (long long)sms * (nt_fast == 1 ? w34::kFastWarps : w34::kTeams));
+    const size_t exact = w34::stream_scratch_bytes(layout, batch, num_q_heads, false, (long long)sms * w34::kExactWarps);
+    return fast > exact ? fast : exact;
 }
 
 namespace w34 {
+
+// Prefill chunks (more query rows per request and kv head than three row groups hold) go to the
+// 128-row tcgen05 kernel, which needs no scratch beyond the status word.
+static bool takes_prefill_path(uint64_t flags, const warp34_kv_layer_layout* l,
+                               const warp34_attention_batch* b, int gqa) {
+    const bool want_tc = (flags & WARP34_B200_EXEC_FLAG_TCGEN05_VERIFY) != 0 && (long long)b->max_q_len * gqa > 8;
+    return (flags & WARP34_B200_EXEC_FLAG_PRECISE_ATTENTION) == 0 && stream_layout_ok(l) &&
+           b->max_blocks_per_req > 0 && gqa <= kPfRows && ((long long)b->max_q_len * gqa > 24 || want_tc);
+}
 
 // Shared body of the attention entry points.  triple_out != nullptr: stop after the split-KV
 // merge and write per-row (acc, m, l) instead of attn_out (streaming path only).
@@ -2320,10 +2344,7 @@ static int launch_attention(const warp34_exec* ex, const warp34_kv_layer_layout*
     const int gqa = num_q_heads / layout->local_kv_heads;
     // Prefill chunks (more query rows per request and kv head than one team item holds): 64-row
     // CTAs, no scratch.  Not for the partial-output mode, which is a decode-time feature.
-    const bool want_tc = (ex->flags & WARP34_B200_EXEC_FLAG_TCGEN05_VERIFY) != 0 && (long long)batch->max_q_len * gqa > 8;
-    if (triple_out == nullptr && (ex->flags & WARP34_B200_EXEC_FLAG_PRECISE_ATTENTION) == 0 &&
-        stream_layout_ok(layout) && batch->max_blocks_per_req > 0 && gqa <= kPfRows &&
-        ((long long)batch->max_q_len * gqa > 24 || want_tc)) {
+    if (triple_out == nullptr && takes_prefill_path(ex->flags, layout, batch, gqa)) {
         // 128-row tiles on tcgen05 (a partly filled tile still beats the 64-row mma.sync kernel
         // below, which stays for callers that ask for it and for devices without the shared memory).
         if ((ex->flags & WARP34_B200_EXEC_FLAG_PREFILL_MMA_SYNC) == 0 &&
@@ -2371,9 +2392,9 @@ static int launch_attention(const warp34_exec* ex, const warp34_kv_layer_layout*
     // Streaming path: canonical layout, scratch that holds the plan plus at least one partial
     // per item and per worker, unit count within int32.  Workers are warps (8 query rows per
     // item) or four-warp teams (16 / 24 rows per item).
-    const int nt = pick_row_tiles(batch, gqa);
-    const int rpg = 8 * nt;
     const bool fast = (ex->flags & WARP34_B200_EXEC_FLAG_FAST_ATTENTION) != 0;
+    const int nt = pick_row_tiles(batch, gqa, fast);
+    const int rpg = 8 * nt;
     const int workers_per_cta = (nt == 1) ? (fast ? kFastWarps : kExactWarps) : kTeams;
     const long long items = items_bound(layout, batch, num_q_heads, rpg);
     const long long units_bound = items * (long long)(batch->max_blocks_per_req > 0 ? batch->max_blocks_per_req : 1);
@@ -2497,17 +2518,17 @@ extern "C" int warp34_paged_attention_f16_static_scratch(uintptr_t stream, const
     }
     if (batch->total_tokens <= 0 || num_q_heads <= 0) return 0;
     if (!w34::tq4_layout_ok(layout)) return (int)cudaErrorNotSupported;
-    if (!w34::stream_layout_ok(layout)) return (int)cudaErrorNotSupported;  // this entry point has no scratch-free fallback
+    // Layouts the streaming and prefill kernels cannot take would fall to the fp32 kernel, which
+    // uses no workspace at all; callers with such layouts have no use for this entry point.
+    if (!w34::stream_layout_ok(layout) || batch->max_blocks_per_req <= 0) return (int)cudaErrorNotSupported;
     if (num_q_heads % layout->local_kv_heads != 0 || batch->num_reqs <= 0) return (int)cudaErrorInvalidValue;
-    // Smallest workspace the streaming path accepts: the plan plus one partial per work item
-    // and per warp of a single CTA.
-    const int nt = w34::pick_row_tiles(batch, num_q_heads / layout->local_kv_heads);
-    const int rpg = 8 * nt;
-    const size_t needed = w34::plan_bytes(batch->num_reqs) +
-                          (size_t)(w34::items_bound(layout, batch, num_q_heads, rpg) +
-                                   (nt == 1 ? w34::kWarpsPerCta : w34::kTeams)) *
-                              (size_t)(rpg * w34::kHeadDim + 2 * rpg) * sizeof(float) +
-                          (nt == 1 ? (size_t)w34::qfrag_items(layout, batch, num_q_heads / layout->local_kv_heads) * w34::qfrag_item_bytes() : 0);
+    // What warp34_paged_attention_f16 needs at the least for the same batch with flags 0: a prefill
+    // chunk only the status word, everything else the plan plus one partial per work item and per
+    // warp of a single CTA plus the query fragments.
+    const int gqa = num_q_heads / layout->local_kv_heads;
+    const size_t needed = w34::takes_prefill_path(0, layout, batch, gqa)
+                              ? sizeof(w34::PlanHeader)
+                              : w34::stream_scratch_bytes(layout, batch, num_q_heads, false, w34::kExactWarps);
     if (scratch_needed != nullptr) *scratch_needed = needed;
     if (needed > kStaticScratchBytes) return (int)cudaErrorInvalidValue;  // batch too large for the built-in workspace
     warp34_exec ex;
