@@ -53,9 +53,6 @@ enum {
  * operands, no scratch) for callers that want scores at fp32 accuracy. */
 #define WARP34_EXEC_FLAG_ALLOW_W4A8_PREFILL (1ull << 0)
 #define WARP34_B200_EXEC_FLAG_PRECISE_ATTENTION (1ull << 40)
-/* Additive as well: chunked-prefill batches take the 64-row mma.sync kernel even where the
- * 128-row tcgen05 kernel applies (cross-checks, A/B measurements). */
-#define WARP34_B200_EXEC_FLAG_PREFILL_MMA_SYNC (1ull << 41)
 /* Additive: multi-token verify batches (more than 8 query rows per request and KV head) take the
  * tcgen05 kernel, one 128-row CTA per request and KV head, instead of the split-KV team kernel. */
 #define WARP34_B200_EXEC_FLAG_TCGEN05_VERIFY (1ull << 42)
@@ -170,6 +167,12 @@ int warp34_kv_cache_write_strided(const warp34_exec* ex, const warp34_kv_layer_l
  * much a batch geometry can use, and any 16-byte-aligned scratch of at least
  * 1 MiB is accepted (less scratch means fewer, longer KV partitions).
  * Masked rows of attn_out are left untouched.
+ *
+ * Accuracy: every output is within 2e-3 + 1e-2 |b| of fp32 dequant-then-attend (b).  The
+ * tensor-core kernels get there by feeding each fp16 operand as value + rounding residual;
+ * WARP34_B200_EXEC_FLAG_FAST_ATTENTION trades that for speed.  Kernels: decode and verify batches
+ * (up to 24 query rows per request and kv head) stream split-KV work items of 8 rows; larger
+ * chunks take a 128-row prefill kernel (register MMAs; tcgen05 + TMEM with the fast flag).
  */
 int warp34_paged_attention_f16(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
                                const warp34_attention_batch* batch,
@@ -186,6 +189,22 @@ int warp34_paged_attention_scalar_f16(const warp34_exec* ex, const warp34_kv_lay
                                       const warp34_attention_batch* batch,
                                       const void* q_in, void* attn_out,
                                       int num_q_heads);
+
+/*
+ * Test-only kernel selector.  Replaces warp34_paged_attention_f16_force_kernel_for_test
+ * (op_paged_attn.cu:1451-1458), against which the reference's variant-equality tests link
+ * (crates/warp34-host/src/cuda/tests.rs:111-576).  use_64q: 0 = the reference's 16-row kernel,
+ * here the 8-row split-KV items; 1 = its 64-row prefill kernel, here the 128-row register-MMA
+ * prefill kernel; 2 = its 128-row prefill kernel, here the 128-row tcgen05 kernel.  The
+ * reference's three variants share their arithmetic and are compared at 0 ULP; these do not:
+ * selectors 0 and 1 meet 2e-3 + 1e-2 |b| against dequant-then-attend on every element,
+ * selector 2 computes with single fp16 operands (see WARP34_B200_EXEC_FLAG_FAST_ATTENTION).
+ * TQ4 layers in the canonical packing only (cudaErrorNotSupported otherwise).
+ */
+int warp34_paged_attention_f16_force_kernel_for_test(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
+                                                     const warp34_attention_batch* batch,
+                                                     const void* q_in, void* attn_out,
+                                                     int num_q_heads, int use_64q);
 
 /*
  * Uncompressed BF16 KV storage with identity transforms (the comparison arm of the TQ4 path).

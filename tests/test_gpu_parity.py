@@ -13,7 +13,7 @@ import os
 import numpy as np
 import pytest
 
-from util import GOLDEN, channel_scale, f16, host_layout, parity_stats, tensor_core_parity, tq4_rows_equal_up_to_scale_ulp, within_tol
+from util import GOLDEN, f16, fast_parity, host_layout, parity_stats, plain_parity, tq4_rows_equal_up_to_scale_ulp, within_tol
 
 torch = pytest.importorskip("torch")
 pytestmark = pytest.mark.gpu
@@ -171,16 +171,17 @@ def test_attention_matches_reference_dequant_then_attend(env, tag, scalar):
         ok = within_tol(got, want)
         assert ok.all(), f"{(~ok).sum()} of {ok.size} outside tolerance, max abs {np.abs(got - want).max()}"
     else:
-        ctx = [int(c) for c in fx["ctx"]]
-        starts = np.concatenate([[0], np.cumsum(ctx)])
-        ql = np.diff(fx[f"{tag}_query_start_loc"]).tolist()
-        vs = channel_scale(fx["v_in"].view(np.float16), [(int(starts[i]), int(starts[i + 1])) for i in range(3)],
-                           ql, int(fx["hq"]), int(fx["hkv"]))
-        ok, msg = tensor_core_parity(got, want, vs)
+        ok, msg = plain_parity(got, want)
         assert ok, msg
-        # and it is at least as close to dequant-then-attend as the reference's production kernel
+        # the fast build stays at least as close to dequant-then-attend as the reference's own
+        # tensor-core kernel, whose output on the same inputs is in the fixture
+        fast = kv.Executor(64 << 20)
+        fast.ex.flags = env["ffi"].EXEC_FLAG_FAST_ATTENTION
+        out_f = torch.zeros_like(q)
+        kv.paged_attention(fast, layer, b, q, out_f, int(fx["hq"]))
+        torch.cuda.synchronize()
         ref_viol, ref_worst = parity_stats(f16(fx[f"out_{tag}_prod"]), want)
-        my_viol, my_worst = parity_stats(got, want)
+        my_viol, my_worst = parity_stats(out_f.float().cpu().numpy(), want)
         assert my_viol <= ref_viol + 2 and my_worst <= max(1.0, 1.25 * ref_worst), (my_viol, my_worst, ref_viol, ref_worst)
 
 
@@ -193,9 +194,6 @@ def _decode_case(env, ctx, hq, hkv, seed, q_lens=None, shuffle=True, fill=None):
     for s, c, ql in zip(wl.seqs, ctx, q_lens):
         s.commit(int(c) - ql)
     q = synth.make_q(sum(q_lens), hq, seed)
-    starts = np.concatenate([[0], np.cumsum([int(c) for c in ctx])])
-    wl.v_scale = channel_scale(v.numpy(), [(int(starts[i]), int(starts[i + 1])) for i in range(len(ctx))],
-                               q_lens, hq, hkv)
     return wl, q
 
 
@@ -220,7 +218,7 @@ def test_attention_matches_cpu_oracle_on_ragged_batches(env, hq, hkv, q_len):
     torch.cuda.synchronize()
     want = _oracle_attention(wl, b, q, hq)
     got = out.float().cpu().numpy()
-    ok, msg = tensor_core_parity(got, want, wl.v_scale)
+    ok, msg = plain_parity(got, want)
     assert ok, msg
     status = int(env["ex"].scratch[:4].cpu().numpy().view(np.int32)[0])
     assert status == 0
@@ -270,7 +268,7 @@ def test_masks_windows_and_untouched_rows(env):
         assert (got_bits[4] == sentinel).all() and (got_bits[6:] == sentinel).all()
         want = _oracle_attention(wl, b, q, hq)
         live = [0, 1, 2, 3, 5]
-        ok, msg = tensor_core_parity(f16(got_bits[live]), want[live], wl.v_scale[live])
+        ok, msg = plain_parity(f16(got_bits[live]), want[live])
         assert ok, (mode, window, msg)
 
 
@@ -296,7 +294,7 @@ def test_block_table_entries_past_the_sequence_are_never_used(env):
     torch.cuda.synchronize()
     got = out.float().cpu().numpy()
     assert np.isfinite(got).all()
-    ok, msg = tensor_core_parity(got, _oracle_attention(wl, b, q, hq), wl.v_scale)
+    ok, msg = plain_parity(got, _oracle_attention(wl, b, q, hq))
     assert ok, msg
 
 
@@ -334,7 +332,7 @@ def test_split_partitioning_does_not_change_the_result_beyond_tolerance(env):
         outs.append(out.float().cpu().numpy())
     want = _oracle_attention(wl, b, q, hq)
     for o in outs:
-        ok, msg = tensor_core_parity(o, want, wl.v_scale)
+        ok, msg = plain_parity(o, want)
         assert ok, msg
     assert np.abs(outs[0] - outs[1]).max() <= 2e-3 + 1e-2 * np.abs(want).max()
 
@@ -356,14 +354,14 @@ def test_understated_max_q_len_is_reported_and_the_declared_rows_stay_right(env)
     assert status & 4
     got = out.float().cpu().numpy()
     for tok in (0, 1, 3):   # the first group of request 0, and request 1
-        ok, msg = tensor_core_parity(got[tok:tok + 1], want[tok:tok + 1], wl.v_scale[tok:tok + 1])
+        ok, msg = plain_parity(got[tok:tok + 1], want[tok:tok + 1])
         assert ok, (tok, msg)
     assert (got[2] == 7.0).all()
     # declared honestly the same batch is complete and the status clear
     kv.paged_attention(env["ex"], wl.layer, honest, q.cuda(), out, hq)
     torch.cuda.synchronize()
     assert int(env["ex"].scratch[:4].cpu().numpy().view(np.int32)[0]) == 0
-    ok, msg = tensor_core_parity(out.float().cpu().numpy(), want, wl.v_scale)
+    ok, msg = plain_parity(out.float().cpu().numpy(), want)
     assert ok, msg
 
 
@@ -390,7 +388,7 @@ def test_page_sharded_partials_merge_to_the_unsharded_result(env):
     kv.merge_shards(env["ex"], triples, merged)
     torch.cuda.synchronize()
     want = _oracle_attention(wl, b, q, hq)
-    ok, msg = tensor_core_parity(merged.float().cpu().numpy(), want, wl.v_scale)
+    ok, msg = plain_parity(merged.float().cpu().numpy(), want)
     assert ok, msg
     diff = np.abs(merged.float().cpu().numpy() - whole.float().cpu().numpy())
     assert diff.max() <= 2e-3 + 1e-2 * np.abs(want).max()
@@ -569,7 +567,7 @@ def test_bf16_activations_match_the_fp16_entry_points(env):
 @pytest.mark.parametrize("hq", [16, 24])
 @pytest.mark.parametrize("q_len,ctx_before", [(64, 0), (65, 19), (137, 128), (256, 200)])
 def test_chunked_prefill_matches_cpu_oracle(env, hq, q_len, ctx_before):
-    """Prefill chunks through the 64-row kernel, on the shapes the reference uses to compare its
+    """Prefill chunks through the default prefill kernel, on the shapes the reference uses to compare its
     16- / 64- / 128-row kernels (crates/warp34-host/src/cuda/tests.rs:111-576): a chunk of q_len
     tokens after ctx_before cached tokens, causal inside the chunk."""
     kv, synth = env["kv"], env["synth"]
@@ -585,8 +583,7 @@ def test_chunked_prefill_matches_cpu_oracle(env, hq, q_len, ctx_before):
     kv.paged_attention(env["ex"], wl.layer, b, q.cuda(), out, hq)
     torch.cuda.synchronize()
     want = _oracle_attention(wl, b, q, hq)
-    vs = channel_scale(v.numpy(), [(0, total)], [q_len], hq, hkv)
-    ok, msg = tensor_core_parity(out.float().cpu().numpy(), want, vs)
+    ok, msg = plain_parity(out.float().cpu().numpy(), want)
     assert ok, msg
 
 
@@ -603,8 +600,6 @@ def test_mixed_prefill_and_decode_batch_with_masks(env):
     for s, c in zip(wl.seqs, ctx_before):
         s.commit(c)
     q = synth.make_q(sum(q_lens), hq, 300)
-    starts = np.concatenate([[0], np.cumsum(totals)])
-    vs = channel_scale(v.numpy(), [(int(starts[i]), int(starts[i + 1])) for i in range(3)], q_lens, hq, hkv)
     sentinel = np.uint16(0x5500)
     for window in (0, 33):
         vtm = np.ones(sum(q_lens), np.uint8)
@@ -617,7 +612,7 @@ def test_mixed_prefill_and_decode_batch_with_masks(env):
         assert (bits[60] == sentinel).all()
         live = np.array([i for i in range(sum(q_lens)) if i != 60])
         want = _oracle_attention(wl, b, q, hq)
-        ok, msg = tensor_core_parity(f16(bits[live]), want[live], vs[live])
+        ok, msg = plain_parity(f16(bits[live]), want[live])
         assert ok, (window, msg)
 
 
@@ -682,23 +677,73 @@ def test_speculative_steps_with_rollback_leave_the_cache_as_if_only_accepted_tok
     kv.paged_attention(env["ex"], wl.layer, b, q.cuda(), out, hq)
     torch.cuda.synchronize()
     want = _oracle_attention(wl, b, q, hq)
-    v_all = torch.cat([torch.cat([accepted_rows[i][1], v[i * ql:(i + 1) * ql]]) for i in range(3)]).numpy()
-    bounds = np.concatenate([[0], np.cumsum([n + ql for n in lens])])
-    vs = channel_scale(v_all, [(int(bounds[i]), int(bounds[i + 1])) for i in range(3)], [ql] * 3, hq, hkv)
-    ok, msg = tensor_core_parity(out.float().cpu().numpy(), want, vs)
+    ok, msg = plain_parity(out.float().cpu().numpy(), want)
     assert ok, msg
 
 
-@pytest.mark.parametrize("mode", ["default", "mma_sync", "short_chunk", "verify_flag"])
-def test_prefill_dispatch_paths_agree_with_the_oracle(env, mode):
-    """The tcgen05 kernel (default, also with partly filled 128-row tiles), the 64-row mma.sync kernel
-    (by flag) and the tcgen05 kernel on a verify batch."""
+@pytest.mark.parametrize("selector", [0, 1, 2])
+@pytest.mark.parametrize("hq", [16, 24])
+def test_forced_kernel_variants_on_the_reference_shapes(env, hq, selector):
+    """warp34_paged_attention_f16_force_kernel_for_test on the shapes of the reference's
+    variant-equality test (crates/warp34-host/src/cuda/tests.rs:111-576): four requests with
+    (q_len, cached) = (64, 0), (65, 19), (137, 128), (256, 200) in one call, one masked token whose
+    output row must keep its sentinel 0x5500.  The reference compares its variants at 0 ULP because
+    they share their arithmetic; these do not, so each is compared with the oracle: selectors 0 and 1
+    inside the plain bound on every element, selector 2 (tcgen05, single fp16 operands) inside the
+    bound of the fast build."""
     kv, synth, ffi = env["kv"], env["synth"], env["ffi"]
     hkv = 4
-    hq, q_len, ctx_before = {"default": (16, 200, 333), "mma_sync": (16, 200, 333),
-                             "short_chunk": (16, 20, 100), "verify_flag": (24, 4, 1500)}[mode]
-    flags = {"default": 0, "mma_sync": ffi.EXEC_FLAG_PREFILL_MMA_SYNC, "short_chunk": 0,
-             "verify_flag": ffi.EXEC_FLAG_TCGEN05_VERIFY}[mode]
+    shapes = [(64, 0), (65, 19), (137, 128), (256, 200)]
+    q_lens = [s[0] for s in shapes]
+    totals = [s[0] + s[1] for s in shapes]
+    wl = synth.PagedWorkload([0] * 4, totals, hkv, seed=700 + hq)
+    k, v = synth.make_kv(sum(totals), hkv, 700 + hq)
+    kv.kv_cache_write(env["ex"], wl.layer, wl.step(), k.cuda(), v.cuda())
+    for s, (ql, c) in zip(wl.seqs, shapes):
+        s.commit(c)
+    n = sum(q_lens)
+    vtm = np.ones(n, np.uint8)
+    vtm[70] = 0                                   # a token of the second request
+    b = wl.step(q_lens=q_lens, valid_token_mask=vtm)
+    q = synth.make_q(n, hq, 701)
+    out = torch.full((n, hq, 256), 0, dtype=torch.int16, device="cuda")
+    out.fill_(0x5500)
+    rc = env["lib"].warp34_paged_attention_f16_force_kernel_for_test(
+        C.byref(env["ex"].ex), C.byref(wl.layer.layout), C.byref(b.desc), q.cuda().data_ptr(), out.data_ptr(), hq, selector)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert int(env["ex"].scratch[:4].cpu().numpy().view(np.int32)[0]) == 0
+    bits = out.cpu().numpy().view(np.uint16)
+    assert (bits[70] == 0x5500).all(), "masked row was written"
+    live = vtm.astype(bool)
+    want = _oracle_attention(wl, b, q, hq)
+    ok, msg = (fast_parity if selector == 2 else plain_parity)(f16(bits[live]), want[live])
+    assert ok, (selector, msg)
+
+
+def test_forced_kernel_selector_validates_like_the_reference(env):
+    ffi = env["ffi"]
+    lay, b = ffi.KvLayerLayout(), ffi.AttentionBatch()
+    fn = env["lib"].warp34_paged_attention_f16_force_kernel_for_test
+    assert fn(None, C.byref(lay), C.byref(b), 1, 1, 16, 0) == ffi.CUDA_ERROR_INVALID_VALUE
+    assert fn(C.byref(env["ex"].ex), C.byref(lay), C.byref(b), 1, 1, 16, 1) == 0      # empty batch: no launch
+    b.total_tokens, b.num_reqs = 1, 1
+    lay.head_dim, lay.block_size, lay.local_kv_heads = 128, 16, 4                      # head_dim other than 256
+    assert fn(C.byref(env["ex"].ex), C.byref(lay), C.byref(b), 1, 1, 16, 2) == ffi.CUDA_ERROR_INVALID_VALUE
+
+
+@pytest.mark.parametrize("mode", ["default", "short_chunk", "verify", "fast", "fast_short_chunk", "fast_verify", "verify_flag"])
+def test_prefill_dispatch_paths_agree_with_the_oracle(env, mode):
+    """Default: the register-MMA prefill kernel with value + residual operands (also with partly
+    filled 128-row tiles) and 8-row items for a verify batch, held to the plain bound.  With the
+    fast flag: the tcgen05 kernel and the four-warp team kernel, held to the bound of the fast build."""
+    kv, synth, ffi = env["kv"], env["synth"], env["ffi"]
+    hkv = 4
+    shape = {"default": (16, 200, 333), "short_chunk": (16, 20, 100), "verify": (24, 4, 1500)}
+    hq, q_len, ctx_before = shape[mode.replace("fast_", "").replace("_flag", "").replace("fast", "default")]
+    flags = ffi.EXEC_FLAG_FAST_ATTENTION if mode.startswith("fast") else 0
+    if mode == "verify_flag":
+        flags = ffi.EXEC_FLAG_TCGEN05_VERIFY
     total = ctx_before + q_len
     wl = synth.PagedWorkload([0, 0], [total, total // 2 + q_len], hkv, seed=610, fill=0xFF)
     lens = [total, total // 2 + q_len]
@@ -716,8 +761,7 @@ def test_prefill_dispatch_paths_agree_with_the_oracle(env, mode):
     torch.cuda.synchronize()
     assert int(ex.scratch[:4].cpu().numpy().view(np.int32)[0]) == 0
     want = _oracle_attention(wl, b, q, hq)
-    vs = channel_scale(v.numpy(), [(0, lens[0]), (lens[0], lens[0] + lens[1])], [q_len, q_len], hq, hkv)
-    ok, msg = tensor_core_parity(out.float().cpu().numpy(), want, vs)
+    ok, msg = (plain_parity if flags == 0 else fast_parity)(out.float().cpu().numpy(), want)
     assert ok, (mode, msg)
 
 

@@ -18,35 +18,6 @@ def within_tol(a, b):
     return np.abs(a - b) <= ATOL + RTOL * np.abs(b)
 
 
-# The tensor-core kernel feeds fp16 operands (rotated Q, codebook values, softmax weights) to
-# the MMAs, like the reference's production kernel (op_paged_attn.cu:357, :470, :47-50).  Rounding
-# the rotated query to fp16 perturbs a score by about 2^-12 |q||k| sm_scale, i.e. a softmax weight
-# by up to 1e-3 relative when K has x20 outlier channels, and that moves an output channel by
-# eps * |V value|, not by eps * |average|: where an outlier channel of two dominant keys
-# cancels, the output is near zero while the error scales with the V values that were averaged.
-# No fp16-operand kernel, the reference's included, meets 2e-3 + 1e-2|b| on those few elements
-# (the fixture test compares against the reference's production kernel).
-# So for this kernel: the plain bound must hold for at least 99.95 % of the elements, and every
-# element must be inside the bound widened by CHANNEL_TERM * (largest |V| of that request, kv
-# head and channel).  The fp32 kernel (WARP34_B200_EXEC_FLAG_PRECISE_ATTENTION,
-# warp34_paged_attention_scalar_f16) meets the plain bound everywhere.
-CHANNEL_TERM = 2e-3
-MIN_FRACTION_WITHIN = 0.9995
-
-
-def channel_scale(v_rows, req_token_ranges, q_lens, hq, hkv):
-    """max |V| per (query token, q head, channel): v_rows is fp16/fp32 [T_kv, hkv*256] holding the
-    requests' keys back to back, req_token_ranges[i] = (first, last+1) row range of request i."""
-    v = np.abs(np.asarray(v_rows, np.float32)).reshape(len(v_rows), hkv, 256)
-    out = []
-    g = hq // hkv
-    for (lo, hi), ql in zip(req_token_ranges, q_lens):
-        m = v[lo:hi].max(axis=0) if hi > lo else np.zeros((hkv, 256), np.float32)  # [hkv, 256]
-        per_head = np.repeat(m, g, axis=0)                                          # [hq, 256]
-        out.extend([per_head] * ql)
-    return np.stack(out)
-
-
 def parity_stats(a, b):
     """(violations of the plain bound, max error / plain bound) of a against b."""
     a = np.asarray(a, np.float32)
@@ -56,20 +27,39 @@ def parity_stats(a, b):
     return int((d > tol).sum()), float((d / tol).max())
 
 
-def tensor_core_parity(a, b, v_scale):
-    """Returns (ok, message) for the fp16-operand kernel against dequant-then-attend."""
+def plain_parity(a, b):
+    """(ok, message): every element of a inside 2e-3 + 1e-2|b| of b.  This is the bar for every
+    default code path: the fp32 kernel and the tensor-core kernels with value + residual operands."""
+    a = np.asarray(a, np.float32)
+    b = np.asarray(b, np.float32)
+    d = np.abs(a - b)
+    tol = ATOL + RTOL * np.abs(b)
+    bad = d > tol
+    msg = f"{bad.sum()} of {bad.size} outside 2e-3 + 1e-2|b|, worst {float((d / tol).max()):.2f} x the bound, max abs {d.max():.3e}"
+    for idx in np.argwhere(bad)[:4]:
+        i = tuple(idx)
+        msg += f"; at {tuple(int(x) for x in i)}: got {a[i]:.5f} want {b[i]:.5f}"
+    return bool(not bad.any()), msg
+
+
+# Opt-in kernels behind WARP34_B200_EXEC_FLAG_FAST_ATTENTION (single fp16 operands, like the
+# reference's own tensor-core kernel: op_paged_attn.cu:357, :470, :47-50).  A softmax weight is off
+# by a few 1e-4 relative there, and a x20 outlier channel of V turns that into a few 1e-3 .. 1e-2
+# absolute where its large terms cancel.  They are held to: at least 99.9 % of the elements inside
+# the plain bound, and no element further away than FAST_ABS + FAST_REL x (largest |b| of its row).
+FAST_MIN_FRACTION, FAST_ABS, FAST_REL = 0.999, 0.15, 5e-3
+
+
+def fast_parity(a, b):
     a = np.asarray(a, np.float32)
     b = np.asarray(b, np.float32)
     d = np.abs(a - b)
     plain = d <= ATOL + RTOL * np.abs(b)
-    capped = d <= ATOL + RTOL * np.abs(b) + CHANNEL_TERM * np.asarray(v_scale, np.float32)
+    cap = FAST_ABS + FAST_REL * np.abs(b).max(axis=-1, keepdims=True)
     frac = plain.mean()
-    msg = (f"{(~plain).sum()} of {plain.size} outside 2e-3 + 1e-2|b| (fraction inside {frac:.6f}), "
-           f"{(~capped).sum()} outside the channel-scaled bound, max abs {d.max():.3e}")
-    for idx in np.argwhere(~capped)[:4]:
-        i = tuple(idx)
-        msg += f"; at {tuple(int(x) for x in i)}: got {a[i]:.5f} want {b[i]:.5f} channel max {v_scale[i]:.3f}"
-    return bool(capped.all() and frac >= MIN_FRACTION_WITHIN), msg
+    msg = (f"{(~plain).sum()} of {plain.size} outside the plain bound (fraction inside {frac:.6f}), "
+           f"{(d > cap).sum()} outside the cap, max abs {d.max():.3e}")
+    return bool(frac >= FAST_MIN_FRACTION and (d <= cap).all()), msg
 
 
 def f16(bits):

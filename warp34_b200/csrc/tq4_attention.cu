@@ -1485,23 +1485,8 @@ __global__ void __launch_bounds__(kTeams * kTeamWarps * 32, 1) tq4_attention_tea
 }
 
 // ---------------------------------------------------------------------------------------
-// Chunked-prefill kernel: 64 query rows (64 / G tokens x G heads of one kv head) per CTA, four
-// warps of 16 rows.  Replaces paged_attention_prefill_mma_f16_kernel<64>
-// (op_paged_attn.cu:594-1128).  Per page the CTA dequantises K and V once into fp16 tiles in
-// shared memory (natural rotated-column order, unscaled centroids) while the previous page's
-// tiles feed the MMAs: S = Q' K^T with ldmatrix B fragments and one accumulator per 128-half
-// (scores = d0 S0 + d1 S1), online softmax in registers, O += (P d_v) V with ldmatrix.trans.
-// The 4-bit look-ups are paid once per 64 rows.  No scratch, no split: a CTA walks all pages
-// its rows can see; causal / window masks are applied per row on the pages that need them.
-// (A tcgen05 version with TMEM accumulators is the intended successor of this kernel.)
+// Helpers shared by the tile-based kernels (tcgen05 prefill, uncompressed bf16 KV).
 // ---------------------------------------------------------------------------------------
-constexpr int kPfRows = 64;
-constexpr int kPfWarps = 4;
-constexpr int kPfStages = 3;                 // raw pages in flight
-constexpr int kTileStride = 264;             // halves per dequantised row: 528 B, conflict-free ldmatrix
-constexpr int kTileBytes = 16 * kTileStride * 2;
-constexpr int kPfLutBytes = 256 * 32 * 4;    // 128-byte entry stride (PRMT + LEA addressing)
-
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
@@ -1514,367 +1499,9 @@ __device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, ui
     asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
-struct PrefillParams {
-    warp34_kv_layer_layout layout;
-    warp34_attention_batch batch;
-    const void* q_in;
-    void* attn_out;
-    int io_bf16;
-    int num_q_heads;
-    int gqa;
-    int tok_per_tile;      // 64 / gqa
-    float q_scale;         // sm_scale * log2(e) / kLutScale
-    int32_t* status;       // may be null
-};
-
-__global__ void __launch_bounds__(kPfWarps * 32, 2) tq4_attention_prefill_kernel(const PrefillParams p) {
-    extern __shared__ __align__(1024) uint8_t smem[];
-    // [lut 32 KB][K tile x2][V tile x2][raw ring][scales 2 x 64 floats][mbarriers]
-    const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
-    const int gid = lane >> 2, tig = lane & 3;
-    const uint32_t lut = smem_u32(smem);
-    const uint32_t ktile = lut + kPfLutBytes;
-    const uint32_t vtile = ktile + 2 * kTileBytes;
-    const uint32_t raw = vtile + 2 * kTileBytes;
-    const uint32_t scl = raw + kPfStages * kStageStride;     // [buf][K0 K1 V0 V1][16 keys] floats
-    const uint32_t bars = scl + 2 * 64 * 4;
-    float* scl_gen = reinterpret_cast<float*>(smem + (scl - lut));
-
-    for (int i = tid; i < 256 * 32; i += blockDim.x) {
-        const int byte = i >> 5, ln = i & 31;
-        sts32(lut + (uint32_t)(byte * 128 + ln * 4),
-              pack_half2(kLutScale * tq4_centroid(byte & 15), kLutScale * tq4_centroid(byte >> 4)));
-    }
-    if (tid == 0) {
-        for (int s = 0; s < kPfStages; ++s) mbar_init(bars + 8u * s, 1u);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    __syncthreads();
-
-    // ---- which (request, token tile) is this CTA? ---------------------------------------------
-    const int tpt = p.tok_per_tile;
-    const int kv_head = blockIdx.y;
-    int req = -1, tile_in_req = 0;
-    {
-        int t = blockIdx.x;
-        for (int r = 0; r < p.batch.num_reqs; ++r) {
-            const int ql = p.batch.query_start_loc[r + 1] - p.batch.query_start_loc[r];
-            const int nt = (ql + tpt - 1) / tpt;
-            if (t < nt) { req = r; tile_in_req = t; break; }
-            t -= nt;
-        }
-    }
-    if (req < 0) return;
-    const ReqGeom g = load_req(p.batch, req);
-    if (!g.valid) return;
-    const int tok0 = tile_in_req * tpt;                         // first query token of the tile (in request)
-    const int ntok = min(tpt, g.q_len - tok0);
-    const int rows_used = ntok * p.gqa;
-
-    // this lane's two rows: 16 wid + gid and + 8
-    int rmax[2], rmin[2];
-    bool rvalid[2];
-#pragma unroll
-    for (int x = 0; x < 2; ++x) {
-        const int row = 16 * wid + gid + 8 * x;
-        const int q_off = tok0 + row / p.gqa;
-        rvalid[x] = row < rows_used &&
-                    (p.batch.valid_token_mask == nullptr || p.batch.valid_token_mask[g.q_start + q_off] != 0);
-        rmax[x] = rvalid[x] ? row_max_kv(p.batch, g, q_off) : -1;
-        rmin[x] = rvalid[x] ? row_min_kv(p.batch, g, q_off) : 0x7fffffff;
-    }
-    // page range of the whole tile, and the range of keys every valid row sees
-    __shared__ int s_lo[kPfWarps], s_hi[kPfWarps], s_slo[kPfWarps], s_shi[kPfWarps];
-    {
-        int lo = min(rmin[0], rmin[1]), hi = max(rmax[0], rmax[1]);
-        int slo = max(rvalid[0] ? rmin[0] : 0, rvalid[1] ? rmin[1] : 0);
-        int shi = min(rvalid[0] ? rmax[0] : 0x7fffffff, rvalid[1] ? rmax[1] : 0x7fffffff);
-#pragma unroll
-        for (int d = 16; d > 0; d >>= 1) {
-            lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, d));
-            hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, d));
-            slo = max(slo, __shfl_xor_sync(0xffffffffu, slo, d));
-            shi = min(shi, __shfl_xor_sync(0xffffffffu, shi, d));
-        }
-        if (lane == 0) { s_lo[wid] = lo; s_hi[wid] = hi; s_slo[wid] = slo; s_shi[wid] = shi; }
-    }
-    __syncthreads();
-    int kv_lo = 0x7fffffff, kv_hi = -1, safe_lo = 0, safe_hi = 0x7fffffff;
-#pragma unroll
-    for (int w = 0; w < kPfWarps; ++w) {
-        kv_lo = min(kv_lo, s_lo[w]); kv_hi = max(kv_hi, s_hi[w]);
-        safe_lo = max(safe_lo, s_slo[w]); safe_hi = min(safe_hi, s_shi[w]);
-    }
-    const int pg_lo = (kv_hi >= kv_lo) ? (kv_lo >> 4) : 0;
-    const int npages = (kv_hi >= kv_lo) ? ((kv_hi >> 4) - pg_lo + 1) : 0;
-
-    // ---- Q' rows of this warp -> A fragments (natural rotated-column order) -----------------------
-    // staging through this warp's slice of the K tiles (idle before the first page)
-    uint32_t qa[16][4];
-    {
-        __half* stage = reinterpret_cast<__half*>(smem + (ktile - lut)) + wid * 16 * kTileStride;  // [16][264]
-        for (int rr = 0; rr < 16; ++rr) {
-            const int row = 16 * wid + rr;
-            const int q_off = tok0 + row / p.gqa;
-            const int q_head = kv_head * p.gqa + row % p.gqa;
-            const bool ok = row < rows_used &&
-                            (p.batch.valid_token_mask == nullptr || p.batch.valid_token_mask[g.q_start + q_off] != 0);
-            float tv[8];
-            if (ok) {
-                const size_t q_base = ((size_t)(g.q_start + q_off) * p.num_q_heads + q_head) * kHeadDim;
-#pragma unroll
-                for (int j = 0; j < 8; ++j) tv[j] = apply_sign(load_act(p.q_in, q_base + lane + 32 * j, p.io_bf16), lane + 32 * j);
-                wht256_lanes(tv, lane);
-            } else {
-#pragma unroll
-                for (int j = 0; j < 8; ++j) tv[j] = 0.0f;
-            }
-#pragma unroll
-            for (int j = 0; j < 8; ++j) stage[rr * kTileStride + lane + 32 * j] = __float2half_rn(tv[j] * p.q_scale);
-        }
-        __syncwarp();
-        const uint32_t* st32 = reinterpret_cast<const uint32_t*>(stage);
-#pragma unroll
-        for (int ks = 0; ks < 16; ++ks) {
-            qa[ks][0] = st32[(gid * kTileStride + 16 * ks + 2 * tig) >> 1];
-            qa[ks][1] = st32[((gid + 8) * kTileStride + 16 * ks + 2 * tig) >> 1];
-            qa[ks][2] = st32[(gid * kTileStride + 16 * ks + 8 + 2 * tig) >> 1];
-            qa[ks][3] = st32[((gid + 8) * kTileStride + 16 * ks + 8 + 2 * tig) >> 1];
-        }
-    }
-    __syncthreads();   // staging area becomes the K tile buffers
-
-    float o[32][4];
-#pragma unroll
-    for (int n = 0; n < 32; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f; }
-    float m_run[2] = {-1e30f, -1e30f}, l_run[2] = {0.0f, 0.0f};
-
-    const int32_t* blocks = p.batch.block_tables + (size_t)req * p.batch.max_blocks_per_req;
-    const uint8_t* k_head_base = (const uint8_t*)(uintptr_t)p.layout.k_base + (size_t)kv_head * p.layout.k_head_stride_bytes;
-    const uint8_t* v_head_base = (const uint8_t*)(uintptr_t)p.layout.v_base + (size_t)kv_head * p.layout.v_head_stride_bytes;
-    uint32_t phase_bits = 0;
-    bool failed = false;
-
-    auto issue = [&](int idx) {   // thread 0 only
-        const int s = idx % kPfStages;
-        const int32_t page = blocks[pg_lo + idx];
-        const uint32_t bar = bars + 8u * s;
-        const uint32_t dst = raw + (uint32_t)s * kStageStride;
-        const uint8_t* ksrc = k_head_base + (size_t)page * p.layout.k_page_stride_bytes;
-        const uint8_t* vsrc = v_head_base + (size_t)page * p.layout.v_page_stride_bytes;
-        mbar_expect_tx(bar, 4 * kHalfBytes);
-        bulk_g2s(dst, ksrc, kHalfBytes, bar);
-        bulk_g2s(dst + kHalfStride, ksrc + kHalfBytes, kHalfBytes, bar);
-        bulk_g2s(dst + kRunStride, vsrc, kHalfBytes, bar);
-        bulk_g2s(dst + kRunStride + kHalfStride, vsrc + kHalfBytes, kHalfBytes, bar);
-    };
-    // Dequantises raw page `idx` into tile buffer idx & 1: thread -> (token row, 32-column chunk).
-    auto dequant = [&](int idx) {
-        const int s = idx % kPfStages;
-        if (!failed && !mbar_wait(bars + 8u * s, (phase_bits >> s) & 1u)) {
-            failed = true;
-            if (p.status != nullptr && lane == 0) atomicOr(p.status, 1);
-        }
-        phase_bits ^= 1u << s;
-        const int buf = idx & 1;
-        const int r = tid >> 3, c = tid & 7;            // token row, chunk of 32 rotated columns
-        const int half = c >> 2;
-#pragma unroll
-        for (int kvsel = 0; kvsel < 2; ++kvsel) {
-            const uint32_t rowp = raw + (uint32_t)s * kStageStride + (kvsel ? kRunStride : 0) + token_offset(r);
-            uint32_t w[4];
-            if (half == 0) {   // codes of half 0 start at byte 2: read 5 words and shift by 16 bits
-                const uint32_t b = rowp + 16u * (c & 3);
-                uint32_t x[5];
-#pragma unroll
-                for (int j = 0; j < 5; ++j) x[j] = lds32(b + 4u * j);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) w[j] = __funnelshift_r(x[j], x[j + 1], 16);
-            } else {
-                const uint32_t b = rowp + 68u + 16u * (c & 3);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) w[j] = lds32(b + 4u * j);
-            }
-            const uint32_t dst = (kvsel ? vtile : ktile) + (uint32_t)buf * kTileBytes +
-                                 (uint32_t)(r * kTileStride + 32 * c) * 2u;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                uint32_t h[4];
-#pragma unroll
-                for (int k = 0; k < 4; ++k) h[k] = lds32(lut + 4u * lane + (__byte_perm(w[j], 0, 0x4440 + k) << 7));
-                sts128(dst + 16u * j, h[0], h[1], h[2], h[3]);
-            }
-            if ((c & 3) == 0) {   // one thread per (row, half) publishes the scale
-                const uint32_t sw = lds32(rowp + (half ? 64u : 0u));
-                const float d = __half2float(__ushort_as_half((unsigned short)(half ? (sw >> 16) : (sw & 0xffffu))));
-                scl_gen[buf * 64 + (kvsel * 2 + half) * 16 + r] = d;
-            }
-        }
-    };
-
-    if (tid == 0) {
-        for (int i = 0; i < kPfStages && i < npages; ++i) issue(i);
-    }
-    if (npages > 0) dequant(0);
-    __syncthreads();
-
-#pragma unroll 1
-    for (int i = 0; i < npages; ++i) {
-        const int buf = i & 1;
-        // raw stage of page i is free (dequantised before the last barrier): refill it
-        if (tid == 0 && i + kPfStages < npages) issue(i + kPfStages);
-        if (i + 1 < npages) dequant(i + 1);   // overlaps the MMAs below
-
-        const int kv_base = (pg_lo + i) << 4;
-        const bool full = (kv_base >= safe_lo) && (kv_base + 15 <= safe_hi);
-        const uint32_t kt = ktile + (uint32_t)buf * kTileBytes, vt = vtile + (uint32_t)buf * kTileBytes;
-        const float* sc_ = scl_gen + buf * 64;
-
-        // ---- S = Q' K^T: [16 rows x 16 keys], per 128-half ------------------------------------
-        float sacc[2][2][4];   // [half][key n-tile][c]
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-#pragma unroll
-            for (int n = 0; n < 2; ++n) { sacc[h][n][0] = sacc[h][n][1] = sacc[h][n][2] = sacc[h][n][3] = 0.0f; }
-        }
-        // ldmatrix.x4: matrices (keys 0-7, cols k0..+7), (keys 0-7, cols k0+8..), (keys 8-15, k0..), (keys 8-15, k0+8..)
-        const uint32_t kaddr = kt + (uint32_t)(((lane & 7) + 8 * (lane >> 4)) * kTileStride + 8 * ((lane >> 3) & 1)) * 2u;
-#pragma unroll
-        for (int ks = 0; ks < 16; ++ks) {
-            uint32_t b[4];
-            ldmatrix_x4(b, kaddr + 32u * ks);
-            mma16816(sacc[ks >> 3][0], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b[0], b[1]);
-            mma16816(sacc[ks >> 3][1], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b[2], b[3]);
-        }
-        // this lane's keys: n-tile n -> keys 8 n + 2 tig, + 1
-        float sc[2][4];
-        float dv0[2][2], dv1[2][2];
-#pragma unroll
-        for (int n = 0; n < 2; ++n) {
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const int key = 8 * n + 2 * tig + e;
-                const float dk0 = sc_[0 * 16 + key], dk1 = sc_[1 * 16 + key];
-                dv0[n][e] = sc_[2 * 16 + key];
-                dv1[n][e] = sc_[3 * 16 + key];
-                sc[n][e] = dk0 * sacc[0][n][e] + dk1 * sacc[1][n][e];               // row gid
-                sc[n][2 + e] = dk0 * sacc[0][n][2 + e] + dk1 * sacc[1][n][2 + e];   // row gid + 8
-            }
-        }
-        bool msk[2][4];
-#pragma unroll
-        for (int n = 0; n < 2; ++n) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) msk[n][e] = false;
-        }
-        if (!full) {
-#pragma unroll
-            for (int n = 0; n < 2; ++n) {
-#pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    const int pos = kv_base + 8 * n + 2 * tig + e;
-                    msk[n][e] = !(pos >= rmin[0] && pos <= rmax[0]);
-                    msk[n][2 + e] = !(pos >= rmin[1] && pos <= rmax[1]);
-                    if (msk[n][e]) sc[n][e] = -1e30f;
-                    if (msk[n][2 + e]) sc[n][2 + e] = -1e30f;
-                    // a key beyond the sequence may hold never-written bytes: keep its V scale finite
-                    if (pos > kv_hi || pos < kv_lo) { dv0[n][e] = 0.0f; dv1[n][e] = 0.0f; }
-                }
-            }
-        }
-        // ---- online softmax: rows gid (x = 0) and gid + 8 (x = 1), 4 lanes share a row -----------
-        float mx[2];
-        mx[0] = fmaxf(fmaxf(sc[0][0], sc[0][1]), fmaxf(sc[1][0], sc[1][1]));
-        mx[1] = fmaxf(fmaxf(sc[0][2], sc[0][3]), fmaxf(sc[1][2], sc[1][3]));
-#pragma unroll
-        for (int d = 1; d < 4; d <<= 1) {
-            mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xffffffffu, mx[0], d));
-            mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xffffffffu, mx[1], d));
-        }
-        const float mn0 = fmaxf(m_run[0], mx[0]), mn1 = fmaxf(m_run[1], mx[1]);
-        if (__any_sync(0xffffffffu, mn0 > m_run[0] || mn1 > m_run[1])) {
-            const float al0 = ex2(m_run[0] - mn0), al1 = ex2(m_run[1] - mn1);
-            l_run[0] *= al0; l_run[1] *= al1;
-#pragma unroll
-            for (int n = 0; n < 32; ++n) { o[n][0] *= al0; o[n][1] *= al0; o[n][2] *= al1; o[n][3] *= al1; }
-            m_run[0] = mn0; m_run[1] = mn1;
-        }
-        float pr[2][4];
-#pragma unroll
-        for (int n = 0; n < 2; ++n) {
-            pr[n][0] = msk[n][0] ? 0.0f : ex2(sc[n][0] - mn0);
-            pr[n][1] = msk[n][1] ? 0.0f : ex2(sc[n][1] - mn0);
-            pr[n][2] = msk[n][2] ? 0.0f : ex2(sc[n][2] - mn1);
-            pr[n][3] = msk[n][3] ? 0.0f : ex2(sc[n][3] - mn1);
-            l_run[0] += pr[n][0] + pr[n][1];
-            l_run[1] += pr[n][2] + pr[n][3];
-        }
-        // P d_v as A fragments (k = 16 keys of the page), one set per 128-half of V
-        uint32_t pa0[4], pa1[4];
-        pa0[0] = pack_half2(pr[0][0] * dv0[0][0], pr[0][1] * dv0[0][1]);
-        pa0[1] = pack_half2(pr[0][2] * dv0[0][0], pr[0][3] * dv0[0][1]);
-        pa0[2] = pack_half2(pr[1][0] * dv0[1][0], pr[1][1] * dv0[1][1]);
-        pa0[3] = pack_half2(pr[1][2] * dv0[1][0], pr[1][3] * dv0[1][1]);
-        pa1[0] = pack_half2(pr[0][0] * dv1[0][0], pr[0][1] * dv1[0][1]);
-        pa1[1] = pack_half2(pr[0][2] * dv1[0][0], pr[0][3] * dv1[0][1]);
-        pa1[2] = pack_half2(pr[1][0] * dv1[1][0], pr[1][1] * dv1[1][1]);
-        pa1[3] = pack_half2(pr[1][2] * dv1[1][0], pr[1][3] * dv1[1][1]);
-        // ---- O += P V: ldmatrix.trans gives (keys 0-7 | 8-15) x (cols n0..+7 | n0+8..+15) -----------
-        const uint32_t vaddr = vt + (uint32_t)(((lane & 7) + 8 * ((lane >> 3) & 1)) * kTileStride + 8 * (lane >> 4)) * 2u;
-#pragma unroll
-        for (int np = 0; np < 16; ++np) {
-            uint32_t b[4];
-            ldmatrix_x4_trans(b, vaddr + 32u * np);
-            if (np < 8) {
-                mma16816(o[2 * np], pa0[0], pa0[1], pa0[2], pa0[3], b[0], b[1]);
-                mma16816(o[2 * np + 1], pa0[0], pa0[1], pa0[2], pa0[3], b[2], b[3]);
-            } else {
-                mma16816(o[2 * np], pa1[0], pa1[1], pa1[2], pa1[3], b[0], b[1]);
-                mma16816(o[2 * np + 1], pa1[0], pa1[1], pa1[2], pa1[3], b[2], b[3]);
-            }
-        }
-        __syncthreads();   // tiles of page i + 1 are complete; tiles of page i may be overwritten
-    }
-
-    // ---- epilogue: normalise, inverse rotation, store -------------------------------------------------
-#pragma unroll
-    for (int d = 1; d < 4; d <<= 1) {
-        l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], d);
-        l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], d);
-    }
-    const float inv0 = (l_run[0] > 0.0f) ? (1.0f / (l_run[0] * kLutScale)) : 0.0f;
-    const float inv1 = (l_run[1] > 0.0f) ? (1.0f / (l_run[1] * kLutScale)) : 0.0f;
-    // each warp stages 8 rows at a time in its 8 KB slice of the (now idle) tile buffers
-    float* ostage = reinterpret_cast<float*>(smem + (ktile - lut)) + wid * 8 * kHeadDim;
-#pragma unroll
-    for (int x = 0; x < 2; ++x) {
-        __syncwarp();
-#pragma unroll
-        for (int n = 0; n < 32; ++n) {
-            ostage[gid * kHeadDim + 8 * n + 2 * tig] = o[n][2 * x] * (x ? inv1 : inv0);
-            ostage[gid * kHeadDim + 8 * n + 2 * tig + 1] = o[n][2 * x + 1] * (x ? inv1 : inv0);
-        }
-        __syncwarp();
-        for (int rr = 0; rr < 8; ++rr) {
-            const int row = 16 * wid + rr + 8 * x;
-            const int q_off = tok0 + row / p.gqa;
-            const int q_head = kv_head * p.gqa + row % p.gqa;
-            const bool ok = row < rows_used &&
-                            (p.batch.valid_token_mask == nullptr || p.batch.valid_token_mask[g.q_start + q_off] != 0);
-            if (!ok) continue;
-            float tv[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) tv[j] = ostage[rr * kHeadDim + lane + 32 * j];
-            wht256_lanes(tv, lane);
-            const size_t out_base = ((size_t)(g.q_start + q_off) * p.num_q_heads + q_head) * kHeadDim;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) store_act(p.attn_out, out_base + lane + 32 * j, apply_sign(tv[j], lane + 32 * j), p.io_bf16);
-        }
-    }
-}
-
 }  // namespace w34
 #include "tq4_prefill_tc.cuh"
+#include "tq4_prefill_exact.cuh"
 namespace w34 {
 
 // Row triple written when the caller merges across page shards itself: 256 un-normalised
@@ -2157,8 +1784,10 @@ static size_t stream_smem_min_bytes() {
     return kLutBytes + (fast > exact ? fast : exact);
 }
 
-static size_t prefill_smem_bytes() {
-    return (size_t)kPfLutBytes + 4 * (size_t)kTileBytes + (size_t)kPfStages * kStageStride + 2 * 64 * 4 + kPfStages * 8 + 64;
+// Exact prefill kernel: table, eight fragment areas, the page ring and its barriers.
+static size_t prefill_exact_smem_min_bytes() {
+    return kLutBytes + (size_t)kPxWarps * (kPxQHiBytes + kPxQLoBytes) + (size_t)kPxStages * kStageStride + 128 +
+           2 * kPxStages * 8 + 16 * kPxWarps;
 }
 
 struct DeviceInfo {
@@ -2194,8 +1823,9 @@ static DeviceInfo* device_info(int* rc) {
         *rc = (int)cudaFuncSetAttribute(tq4_attention_team_kernel<3>,
                                         cudaFuncAttributeMaxDynamicSharedMemorySize, optin);
         if (*rc != 0) return nullptr;
-        *rc = (int)cudaFuncSetAttribute(tq4_attention_prefill_kernel,
-                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)prefill_smem_bytes());
+        if ((size_t)optin < prefill_exact_smem_min_bytes()) { *rc = (int)cudaErrorNotSupported; return nullptr; }
+        *rc = (int)cudaFuncSetAttribute(tq4_attention_prefill_exact_kernel,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, optin);
         if (*rc != 0) return nullptr;
         *rc = (int)cudaFuncSetAttribute(tq4_attention_prefill_tc_kernel,
                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBytes);
@@ -2311,20 +1941,23 @@ extern "C" size_t warp34_paged_attention_scratch_bytes(const warp34_kv_layer_lay
 
 namespace w34 {
 
-// Prefill chunks (more query rows per request and kv head than three row groups hold) go to the
-// 128-row tcgen05 kernel, which needs no scratch beyond the status word.
+// Prefill chunks (more query rows per request and kv head than three row groups hold) go to a
+// 128-row kernel, which needs no scratch beyond the status word.
 static bool takes_prefill_path(uint64_t flags, const warp34_kv_layer_layout* l,
                                const warp34_attention_batch* b, int gqa) {
     const bool want_tc = (flags & WARP34_B200_EXEC_FLAG_TCGEN05_VERIFY) != 0 && (long long)b->max_q_len * gqa > 8;
     return (flags & WARP34_B200_EXEC_FLAG_PRECISE_ATTENTION) == 0 && stream_layout_ok(l) &&
-           b->max_blocks_per_req > 0 && gqa <= kPfRows && ((long long)b->max_q_len * gqa > 24 || want_tc);
+           b->max_blocks_per_req > 0 && gqa <= kPxRows && ((long long)b->max_q_len * gqa > 24 || want_tc);
 }
 
 // Shared body of the attention entry points.  triple_out != nullptr: stop after the split-KV
 // merge and write per-row (acc, m, l) instead of attn_out (streaming path only).
+// force: -1 = dispatch by batch geometry and flags; otherwise the kernel family the reference's
+// test selector names: 0 = the row-group kernels (8 query rows per item), 1 = the register-MMA
+// prefill kernel, 2 = the tcgen05 prefill kernel.
 static int launch_attention(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
                             const warp34_attention_batch* batch, const void* q_in, void* attn_out,
-                            float* triple_out, int num_q_heads, int io_bf16 = 0) {
+                            float* triple_out, int num_q_heads, int io_bf16 = 0, int force = -1) {
     if (ex == nullptr || layout == nullptr || batch == nullptr || q_in == nullptr ||
         (attn_out == nullptr && triple_out == nullptr)) {
         return (int)cudaErrorInvalidValue;
@@ -2342,13 +1975,23 @@ static int launch_attention(const warp34_exec* ex, const warp34_kv_layer_layout*
     if (dev == nullptr) return rc;
 
     const int gqa = num_q_heads / layout->local_kv_heads;
-    // Prefill chunks (more query rows per request and kv head than one team item holds): 64-row
-    // CTAs, no scratch.  Not for the partial-output mode, which is a decode-time feature.
-    if (triple_out == nullptr && takes_prefill_path(ex->flags, layout, batch, gqa)) {
-        // 128-row tiles on tcgen05 (a partly filled tile still beats the 64-row mma.sync kernel
-        // below, which stays for callers that ask for it and for devices without the shared memory).
-        if ((ex->flags & WARP34_B200_EXEC_FLAG_PREFILL_MMA_SYNC) == 0 &&
-            (size_t)dev->smem_optin >= kTcSmemBytes) {
+    // Prefill chunks: 128-row CTAs, no scratch.  Not for the partial-output mode, which is a
+    // decode-time feature.  Default: register MMAs with value + residual operands; with the fast
+    // flag (or the tcgen05-verify flag) tcgen05 + TMEM with single fp16 operands.
+    const bool chunk_geometry_ok = stream_layout_ok(layout) && batch->max_blocks_per_req > 0 && gqa <= kPxRows;
+    if (force >= 1 && (!chunk_geometry_ok || triple_out != nullptr)) return (int)cudaErrorNotSupported;
+    if (force >= 1 || (force < 0 && triple_out == nullptr && takes_prefill_path(ex->flags, layout, batch, gqa))) {
+        int32_t* status = nullptr;
+        if (ex->scratch_ptr != 0 && (ex->scratch_ptr & 3u) == 0 && ex->scratch_size >= sizeof(PlanHeader)) {
+            status = reinterpret_cast<int32_t*>((uintptr_t)ex->scratch_ptr);   // PlanHeader::status
+            rc = (int)cudaMemsetAsync(status, 0, sizeof(int32_t), (cudaStream_t)ex->stream);
+            if (rc != 0) return rc;
+        }
+        const bool tc = force == 2 || (force < 0 && (ex->flags & (WARP34_B200_EXEC_FLAG_FAST_ATTENTION |
+                                                                  WARP34_B200_EXEC_FLAG_TCGEN05_VERIFY)) != 0);
+        if (layout->local_kv_heads > 65535) return (int)cudaErrorInvalidValue;
+        if (tc) {
+            if ((size_t)dev->smem_optin < kTcSmemBytes) return (int)cudaErrorNotSupported;
             PrefillTcParams tp;
             tp.layout = *layout;
             tp.batch = *batch;
@@ -2359,19 +2002,14 @@ static int launch_attention(const warp34_exec* ex, const warp34_kv_layer_layout*
             tp.gqa = gqa;
             tp.tok_per_tile = kTcRows / gqa;
             tp.q_scale = batch->sm_scale * 1.4426950408889634f;
-            tp.status = nullptr;
-            if (ex->scratch_ptr != 0 && (ex->scratch_ptr & 3u) == 0 && ex->scratch_size >= sizeof(PlanHeader)) {
-                tp.status = reinterpret_cast<int32_t*>((uintptr_t)ex->scratch_ptr);   // PlanHeader::status
-                rc = (int)cudaMemsetAsync(tp.status, 0, sizeof(int32_t), (cudaStream_t)ex->stream);
-                if (rc != 0) return rc;
-            }
+            tp.status = status;
             const long long tiles = (long long)batch->total_tokens / tp.tok_per_tile + batch->num_reqs;
-            if (tiles > 0x7fffffffll || layout->local_kv_heads > 65535) return (int)cudaErrorInvalidValue;
+            if (tiles > 0x7fffffffll) return (int)cudaErrorInvalidValue;
             const dim3 grid((unsigned)tiles, (unsigned)layout->local_kv_heads);
             tq4_attention_prefill_tc_kernel<<<grid, kTcThreads, kTcSmemBytes, (cudaStream_t)ex->stream>>>(tp);
             return (int)cudaGetLastError();
         }
-        PrefillParams pp;
+        PrefillExactParams pp;
         pp.layout = *layout;
         pp.batch = *batch;
         pp.q_in = q_in;
@@ -2379,13 +2017,14 @@ static int launch_attention(const warp34_exec* ex, const warp34_kv_layer_layout*
         pp.io_bf16 = io_bf16;
         pp.num_q_heads = num_q_heads;
         pp.gqa = gqa;
-        pp.tok_per_tile = kPfRows / gqa;
+        pp.tok_per_tile = kPxRows / gqa;
         pp.q_scale = batch->sm_scale * 1.4426950408889634f / kLutScale;
-        pp.status = nullptr;
+        pp.status = status;
+        pp.smem_bytes = (uint32_t)dev->smem_optin;
         const long long tiles = (long long)batch->total_tokens / pp.tok_per_tile + batch->num_reqs;
-        if (tiles > 0x7fffffffll || layout->local_kv_heads > 65535) return (int)cudaErrorInvalidValue;
+        if (tiles > 0x7fffffffll) return (int)cudaErrorInvalidValue;
         const dim3 grid((unsigned)tiles, (unsigned)layout->local_kv_heads);
-        tq4_attention_prefill_kernel<<<grid, kPfWarps * 32, prefill_smem_bytes(), (cudaStream_t)ex->stream>>>(pp);
+        tq4_attention_prefill_exact_kernel<<<grid, kPxWarps * 32, (size_t)dev->smem_optin, (cudaStream_t)ex->stream>>>(pp);
         return (int)cudaGetLastError();
     }
 
@@ -2474,6 +2113,24 @@ extern "C" int warp34_paged_attention_f16(const warp34_exec* ex, const warp34_kv
                                           void* attn_out, int num_q_heads) {
     if (attn_out == nullptr) return (int)cudaErrorInvalidValue;
     return w34::launch_attention(ex, layout, batch, q_in, attn_out, nullptr, num_q_heads);
+}
+
+// Test-only selector of the reference (op_paged_attn.cu:1451-1458): 0 = its 16-row kernel, 1 = its
+// 64-row, 2 = its 128-row prefill kernel.  Here: 0 = the row-group kernels, 1 = the register-MMA
+// prefill kernel (value + residual operands), 2 = the tcgen05 prefill kernel.
+extern "C" int warp34_paged_attention_f16_force_kernel_for_test(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
+                                                                const warp34_attention_batch* batch, const void* q_in,
+                                                                void* attn_out, int num_q_heads, int use_64q) {
+    if (ex == nullptr || layout == nullptr || batch == nullptr || q_in == nullptr || attn_out == nullptr) {
+        return (int)cudaErrorInvalidValue;
+    }
+    if (batch->total_tokens <= 0 || num_q_heads <= 0) return 0;
+    if (layout->head_dim != 256 || layout->block_size != 16 || layout->local_kv_heads <= 0 ||
+        (num_q_heads % layout->local_kv_heads) != 0 || batch->num_reqs < 1) {
+        return (int)cudaErrorInvalidValue;
+    }
+    return w34::launch_attention(ex, layout, batch, q_in, attn_out, nullptr, num_q_heads, 0,
+                                 use_64q == 2 ? 2 : (use_64q != 0 ? 1 : 0));
 }
 
 // ---- attention without any caller-provided or allocated workspace ---------------------------

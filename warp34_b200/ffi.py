@@ -18,7 +18,6 @@ KV_NAMESPACE_TARGET_FULL_ATTN, KV_NAMESPACE_MTP_FULL_ATTN, KV_NAMESPACE_DFLASH_D
 POLICY_FP16, POLICY_BF16, POLICY_Q8_0, POLICY_FP8, POLICY_TQ4, POLICY_TQ4_ALL = range(6)
 
 EXEC_FLAG_PRECISE_ATTENTION = 1 << 40
-EXEC_FLAG_PREFILL_MMA_SYNC = 1 << 41
 EXEC_FLAG_TCGEN05_VERIFY = 1 << 42
 EXEC_FLAG_FAST_ATTENTION = 1 << 43
 CUDA_ERROR_INVALID_VALUE = 1
@@ -82,6 +81,8 @@ _KERNEL_SIGS = {
                                               C.c_void_p, C.c_void_p, C.c_int]),
     "warp34_paged_attention_scalar_f16": (C.c_int, [_P(Exec), _P(KvLayerLayout), _P(AttentionBatch),
                                                      C.c_void_p, C.c_void_p, C.c_int]),
+    "warp34_paged_attention_f16_force_kernel_for_test": (C.c_int, [_P(Exec), _P(KvLayerLayout), _P(AttentionBatch),
+                                                                    C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
     "warp34_tq4_kv_cache_write_strided_bf16": (C.c_int, [_P(Exec), _P(KvLayerLayout), _P(AttentionBatch),
                                                           C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
     "warp34_tq4_paged_attention_bf16": (C.c_int, [_P(Exec), _P(KvLayerLayout), _P(AttentionBatch),
