@@ -12,7 +12,11 @@ seeded; the KV read per step (about 1.34 GB) is far larger than L2.
 
 Metric: compressed-KV GB/s = sum(ctx_len) * Hkv * 264 B per step / step time.  With N > 1
 every rank runs its own 64-sequence batch (weak scaling, no data-path collective); the value
-is all ranks' bytes over the slowest rank's time.
+is all ranks' bytes over the slowest rank's time.  The K-step loop is timed five times; the
+median is reported.  The line also carries the count of the step's outputs outside
+2e-3 + 1e-2 |b| of dequant-then-attend (`parity`), the numbers of the opt-in single-operand
+build (`fast_build`) and, in `sharded`, the strong-scaling cases: the same 64 sequences split by
+KV head (and batch halves at 8 GPUs), and one 262 144-token sequence split by pages.
 
 `--impl reference` runs the same steps through the reference's own kernels compiled for
 sm_100a (oracle/_ref), or, when that library is absent, through the CPU oracle.
@@ -37,6 +41,18 @@ NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
 
 
+def measured_traffic_ratio(kernel):
+    """DRAM bytes per algorithmic byte of `kernel`, from the small JSON that sits beside its ncu
+    summary (written when the capture is taken; carries the capture's date and workload).  None when
+    there is no capture of the kernel as it is built now."""
+    p = os.path.join(ROOT, "profiles", "dram_traffic.json")
+    try:
+        rec = json.load(open(p)).get(kernel)
+        return float(rec["dram_bytes"]) / float(rec["algorithmic_bytes"]), rec
+    except Exception:
+        return None, None
+
+
 def measured_peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -50,7 +66,7 @@ def measured_peaks():
 class ClockSampler(threading.Thread):
     """Polls NVML (read-only) for SM clock and clock-event reasons while the benchmark runs."""
 
-    def __init__(self, index, period_s=0.02):
+    def __init__(self, index, period_s=0.004):
         super().__init__(daemon=True)
         self.index, self.period = index, period_s
         self.samples = []  # (t, sm_mhz, reasons_bitmask)
@@ -179,6 +195,139 @@ def host_step_batch(kv, step, batch, n_tok):
                         io.max_blocks, 1.0 / 16.0, device="cpu")
 
 
+def strong_scaling_cases(args, world, rank, dev, headline):
+    """The sharded configurations with the TOTAL work fixed (strong scaling), device-resident, one CUDA
+    graph replay per step, timed like the headline (K steps, five times, median, max over ranks):
+
+      cfg1_by_kv_head  the same 64 sequences of config 1 on every N: kv heads split over 1 / 2 / 4 GPUs
+                       (4 / 2 / 1 local kv heads with their 6 q heads each, the reference's TP split,
+                       forward.rs:1085-1086); at 8 GPUs one kv head and one half of the batch per GPU.
+                       No collective.
+      cfg4_by_pages    one sequence of 262 144 tokens, pages split in contiguous ranges; every GPU runs
+                       partial attention over its range, the (m, l, acc) triples are exchanged and
+                       merged by one kernel over peer-mapped mailboxes (NCCL all-gather + merge kernel
+                       when no peer mapping is available).
+    """
+    from warp34_b200 import kv, sharding, synth
+    import torch.distributed as dist
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    REPS = 5
+
+    def timed_graph(body, ex):
+        g = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            ex.set_stream()
+            body()
+        torch.cuda.current_stream().wait_stream(side)
+        with torch.cuda.graph(g):
+            ex.set_stream()
+            body()
+        ex.set_stream()
+        for _ in range(3):
+            g.replay()
+        out = []
+        for _ in range(REPS):
+            barrier(world)
+            e0.record()
+            for _ in range(args.steps):
+                g.replay()
+            e1.record()
+            barrier(world)
+            out.append(max_over_ranks(e0.elapsed_time(e1), world) / args.steps)
+        return float(np.median(out)), [float(min(out)), float(max(out))]
+
+    res = {}
+    # ---- config 1, strong: kv heads (and batch halves at 8 GPUs) --------------------------------
+    hq, hkv, batch, lo, hi, q_len, seed = synth.CONFIGS["cfg1_batched_decode"]
+    ctx_all = [int(c) for c in synth.context_lengths(batch, lo, hi, seed)]
+    if world == 1:
+        res["cfg1_by_kv_head"] = {"partition": "4 kv heads x 64 sequences on 1 GPU (the headline's workload)",
+                                  "ms_per_step": headline["ms_per_step"], "value": headline["value"], "unit": UNIT,
+                                  "kv_bytes_total": headline["kv_bytes"]}
+    elif world in (2, 4, 8):
+        (h0, h1), _, batch_split = sharding.split_kv_heads(hkv, hq, world, rank)
+        b0, b1 = sharding.split_batch(batch, batch_split, rank % batch_split)
+        ctx = ctx_all[b0:b1]
+        lh = h1 - h0
+        lq = lh * (hq // hkv)
+        wl = synth.PagedWorkload(ctx, [q_len] * len(ctx), lh, seed=seed + 1000 * rank, device=dev)
+        ex = kv.Executor(64 << 20, device=dev)
+        wl.fill_context(ex, seed + 1000 * rank, chunk_tokens=32768)
+        b = wl.step()
+        k_new, v_new = synth.make_kv(len(ctx) * q_len, lh, seed + 17, device=dev)
+        q = synth.make_q(len(ctx) * q_len, lq, seed + 17).to(dev)
+        out = torch.zeros_like(q)
+
+        def body():
+            kv.kv_cache_write(ex, wl.layer, b, k_new, v_new)
+            kv.paged_attention(ex, wl.layer, b, q, out, lq)
+
+        ms, span = timed_graph(body, ex)
+        total = sum_over_ranks(float(wl.algorithmic_kv_bytes()), world)
+        status = int(max_over_ranks(float(int(ex.scratch[:4].cpu().numpy().view(np.int32)[0])), world))
+        res["cfg1_by_kv_head"] = {"partition": f"{lh} kv head(s) x {len(ctx)} sequences per GPU, no collective",
+                                  "ms_per_step": ms, "ms_per_step_min_max": span, "value": total / (ms * 1e-3) / 1e9,
+                                  "unit": UNIT, "kv_bytes_total": total, "kernel_status": status}
+        del wl, ex
+    # ---- config 4, strong: pages of one sequence --------------------------------------------------
+    hq, hkv, batch, lo, hi, q_len, seed = synth.CONFIGS["cfg4_long_context"]
+    n_local = (hi // world) // 16 * 16
+    wl = synth.PagedWorkload([n_local - q_len], [q_len], hkv, seed=seed + 1000 * rank, device=dev)
+    ex = kv.Executor(64 << 20, device=dev)
+    wl.fill_context(ex, seed + 1000 * rank, chunk_tokens=32768)
+    b = wl.step()
+    k_new, v_new = synth.make_kv(q_len, hkv, seed + 17, device=dev)
+    q = synth.make_q(q_len, hq, seed + 17).to(dev)
+    out = torch.zeros_like(q)
+    rows = q_len * hq
+    mode, px, equal = "single GPU", None, None
+    if world > 1:
+        triples = torch.zeros(rows, 258, dtype=torch.float32, device=dev)
+        gathered = torch.zeros(world * rows, 258, dtype=torch.float32, device=dev)
+        try:
+            px = kv.PeerExchange.symmetric(dist.group.WORLD, rows, dev)
+        except Exception as exc:
+            sys.stderr.write(f"rank {rank}: peer mailboxes unavailable ({exc}); using the NCCL all-gather\n")
+        have = torch.tensor([1 if px is not None else 0], device=dev)
+        dist.all_reduce(have, op=dist.ReduceOp.MIN)
+        if int(have.item()) == 0:
+            px = None
+        mode = ("peer-mapped mailboxes: exchange + merge in one kernel" if px is not None
+                else "NCCL all-gather + merge kernel")
+
+    def gather_merge():
+        dist.all_gather_into_tensor(gathered, triples)
+        kv.merge_shards(ex, gathered.view(world, -1, 258), out)
+
+    def body4():
+        kv.kv_cache_write(ex, wl.layer, b, k_new, v_new)
+        if world == 1:
+            kv.paged_attention(ex, wl.layer, b, q, out, hq)
+            return
+        kv.paged_attention_partial(ex, wl.layer, b, q, triples, hq)
+        if px is not None:
+            px.exchange_merge(ex, triples, out)
+        else:
+            gather_merge()
+
+    if px is not None:     # once: the fused exchange must reproduce all-gather + merge bit for bit
+        barrier(world)
+        body4()
+        fused = out.clone()
+        gather_merge()
+        torch.cuda.synchronize()
+        equal = bool(torch.equal(fused.view(torch.int16), out.view(torch.int16)) and px.status() == 0)
+    ms, span = timed_graph(body4, ex)
+    total = sum_over_ranks(float(wl.algorithmic_kv_bytes()), world)
+    res["cfg4_by_pages"] = {"partition": f"{n_local} tokens of one {n_local * world}-token sequence per GPU; {mode}",
+                            "ms_per_step": ms, "ms_per_step_min_max": span, "value": total / (ms * 1e-3) / 1e9, "unit": UNIT,
+                            "kv_bytes_total": total,
+                            **({"exchange_equals_allgather_merge": equal, "exchange_status": px.status()} if px is not None else {})}
+    return res
+
+
 def run_chunked_prefill(args):
     """Config 2: 8 sequences x 16384 tokens prefilled in 2048-token chunks (quantize-and-append,
     then causal chunk attention over everything cached so far); the first 4096 tokens are one
@@ -284,6 +433,22 @@ def run_chunked_prefill(args):
     app_ms = sum(a.elapsed_time(b) for a, b, c in evs)
     tot_flops = sum_over_ranks(flops, world)
     tot_tok = sum_over_ranks(float(n_tok), world)
+    fast_build = None
+    if not reference:
+        # the same job with the opt-in single-operand build: chunks take the tcgen05 + TMEM kernel
+        ex.ex.flags = ffi.EXEC_FLAG_FAST_ATTENTION
+        run_job(False)
+        barrier(world)
+        e0.record()
+        f_flops, _, f_evs, _, _ = run_job(True)
+        e1.record()
+        barrier(world)
+        ex.ex.flags = 0
+        f_ms = max_over_ranks(e0.elapsed_time(e1), world)
+        f_attn_ms = sum(b.elapsed_time(c) for a, b, c in f_evs)
+        fast_build = {"flag": "WARP34_B200_EXEC_FLAG_FAST_ATTENTION", "kernel": "tq4_attention_prefill_tc_kernel (tcgen05, 128-row CTAs)",
+                      "ms_per_step": f_ms, "value": tot_flops / (f_ms * 1e-3) / 1e12,
+                      "attention_tflops_rank0": f_flops / (f_attn_ms * 1e-3) / 1e12 if f_attn_ms > 0 else None}
     if rank != 0:
         return
     peaks, kind = measured_peaks()
@@ -299,11 +464,15 @@ def run_chunked_prefill(args):
                        "parallelism": f"sequences split over {world} rank(s), no collective", "shared_prefix_pages": shared_pages,
                        "shared_prefix_tokens": prefix, "copy_on_write_tail_pages": cow_copies},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                         "peak_kind": f"of {kind} (sustained bf16)", "kernel": "tq4_attention_prefill_tc_kernel (tcgen05, 128-row CTAs)", "traffic": None,
+                         "peak_kind": f"of {kind} (sustained bf16)",
+                         "kernel": "tq4_attention_prefill_exact_kernel (register MMAs, value + residual operands, 128-row CTAs)", "traffic": None,
                          "attention_ms_rank0": attn_ms},
             "append_tokens_per_s": n_tok / (app_ms * 1e-3) if app_ms > 0 else None,
             "prefill_tokens_per_s": tot_tok / (ms * 1e-3), "gpu_launches": 2 * len(evs),
             "clocks": sampler.summary(t_begin, t_end)}
+    if fast_build is not None:
+        fast_build["roofline_frac"] = (fast_build["attention_tflops_rank0"] or 0.0) / peak
+        line["fast_build"] = fast_build
     if reference:
         line["impl"] = "reference"
         line["roofline"]["kernel"] = "reference paged_attention_prefill_mma_f16_kernel<64>"
@@ -407,6 +576,7 @@ def main():
                     help="page-sharded long context: all-gather over NCCL + merge, or one kernel over peer-mapped mailboxes")
     ap.add_argument("--config", default="cfg1_batched_decode")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-sharded", action="store_true", help="skip the strong-scaling cases of the `sharded` object")
     ap.add_argument("--append-tokens", type=int, default=32768, help="tokens of the bulk-append measurement")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches only (no CUDA graph replay)")
     ap.add_argument("--prefix-tokens", type=int, default=4096,
@@ -462,7 +632,7 @@ def main():
             dist.all_reduce(have, op=dist.ReduceOp.MIN)
             if int(have.item()) == 0:
                 peer_px = None
-    wl.fill_context(step.ex, seed + 1000 * rank, chunk_tokens=32768)  # untimed: KV pool resident in HBM
+    wl.fill_context(step.ex, seed + 1000 * rank, chunk_tokens=32768, lib=lib)  # untimed: KV pool resident in HBM
     n_tok = batch * q_len
     k_new, v_new = synth.make_kv(n_tok, hkv, seed + 17)
     q_new = synth.make_q(n_tok, hq, seed + 17)
@@ -529,6 +699,36 @@ def main():
         if not torch.equal(fused.view(torch.int16), step.out_dev.view(torch.int16)) or peer_px.status() != 0:
             exchange_ok = False   # reported in the JSON line; the run goes on so that every rank leaves in step
             sys.stderr.write(f"rank {rank}: fused exchange differs from all-gather + merge (status {peer_px.status()})\n")
+    REPS = 5     # the K-step loop is timed this many times; the median is reported, the extremes kept beside it
+
+    def timed_reps(fn):
+        out = []
+        for _ in range(REPS):
+            barrier(world)
+            e0.record()
+            for i in range(args.steps):
+                fn(i)
+            e1.record()
+            barrier(world)
+            out.append(max_over_ranks(e0.elapsed_time(e1), world) / args.steps)
+        return out
+
+    def capture(body):
+        g = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            step.ex.set_stream()
+            body()
+        torch.cuda.current_stream().wait_stream(side)
+        with torch.cuda.graph(g):
+            step.ex.set_stream()
+            body()
+        step.ex.set_stream()
+        for _ in range(3):
+            g.replay()
+        return g
+
     sampler = ClockSampler(local)
     sampler.start()
     barrier(world)
@@ -538,45 +738,22 @@ def main():
     evs = [tuple(torch.cuda.Event(enable_timing=True) for _ in range(3)) for _ in range(args.steps)]
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t_begin = time.perf_counter()
-    e0.record()
-    for i in range(args.steps):
-        device_step(evs[i])
-    e1.record()
-    barrier(world)
-    t_end = time.perf_counter()
-    total_ms = max_over_ranks(e0.elapsed_time(e1), world)
-    ms_per_step = total_ms / args.steps
-    eager_ms_per_step = ms_per_step
+    eager_reps = timed_reps(lambda i: device_step(evs[i]))     # the events keep the last repetition's stamps
+    rep_ms = eager_reps
+    eager_ms_per_step = float(np.median(eager_reps))
     # The same K steps replayed from one CUDA graph (how the reference's engine runs a decode step,
     # crates/warp34-host/src/model/graphs.rs:199-259): launch gaps between the four kernels go away.
-    # The page-sharded case captures its NCCL all-gather in the same graph.  Not for the reference arm.
+    # The page-sharded case captures its exchange in the same graph.  Not for the reference arm.
     graph_used = False
     if not args.no_graph and not reference:
         try:
-            g = torch.cuda.CUDAGraph()
-            side = torch.cuda.Stream()
-            side.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(side):
-                step.ex.set_stream()
-                device_step()
-            torch.cuda.current_stream().wait_stream(side)
-            with torch.cuda.graph(g):
-                step.ex.set_stream()
-                device_step()
-            step.ex.set_stream()
-            for _ in range(3):
-                g.replay()
-            barrier(world)
-            e0.record()
-            for _ in range(args.steps):
-                g.replay()
-            e1.record()
-            barrier(world)
-            ms_per_step = max_over_ranks(e0.elapsed_time(e1), world) / args.steps
+            g = capture(device_step)
+            rep_ms = timed_reps(lambda i: g.replay())
             graph_used = True
         except Exception as exc:  # keep the eager numbers
             step.ex.set_stream()
             sys.stderr.write(f"CUDA graph replay unavailable: {exc}\n")
+    ms_per_step = float(np.median(rep_ms))
     t_end = time.perf_counter()
     append_ms = float(np.mean([a.elapsed_time(b) for a, b, c in evs]))
     attn_ms = float(np.mean([b.elapsed_time(c) for a, b, c in evs]))
@@ -630,6 +807,50 @@ def main():
 
     status = int(step.ex.scratch[:4].cpu().numpy().view(np.int32)[0]) if not reference else 0
 
+    # ---- the step's own outputs against dequant-then-attend, and the opt-in fast build ------------
+    parity = fast_build = None
+    if not reference and not sharded:
+        check_path = oracle.ref_lib_path()
+        check_lib = ffi.bind_kernel_abi(check_path) if check_path else None
+        want = torch.zeros_like(step.out_dev)
+        kv.paged_attention(step.ex, wl.layer, desc, step.q_dev, want, hq, lib=check_lib, scalar=True)
+        torch.cuda.synchronize()
+        w = want.float()
+
+        def outside(flags):
+            step.ex.ex.flags = flags
+            kv.paged_attention(step.ex, wl.layer, desc, step.q_dev, step.out_dev, hq)
+            torch.cuda.synchronize()
+            step.ex.ex.flags = 0
+            d = (step.out_dev.float() - w).abs()
+            tol = 2e-3 + 1e-2 * w.abs()
+            return int((d > tol).sum().item()), float((d / tol).max().item())
+
+        n_out, worst = outside(0)
+        parity = {"against": ("the reference's scalar dequant-then-attend kernel (oracle/_ref) on the same pool" if check_path
+                              else "this library's fp32 dequant-then-attend kernel on the same pool"),
+                  "outputs": int(w.numel()), "outside_2e-3_plus_1e-2_rel": n_out, "worst_error_over_bound": worst}
+        if not args.no_graph:
+            n_fast, worst_fast = outside(ffi.EXEC_FLAG_FAST_ATTENTION)
+            step.ex.ex.flags = ffi.EXEC_FLAG_FAST_ATTENTION
+            try:
+                gf = capture(device_step)
+                fast_ms = float(np.median(timed_reps(lambda i: gf.replay())))
+                ev_f = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+                ev_f[0].record()
+                for _ in range(20):
+                    attend(desc)
+                ev_f[1].record()
+                torch.cuda.synchronize()
+                fast_attn_ms = ev_f[0].elapsed_time(ev_f[1]) / 20
+                fast_build = {"flag": "WARP34_B200_EXEC_FLAG_FAST_ATTENTION", "ms_per_step": fast_ms,
+                              "value": all_bytes / (fast_ms * 1e-3) / 1e9, "attention_ms": fast_attn_ms,
+                              "roofline_frac": kv_bytes / (fast_attn_ms * 1e-3) / 1e9 / float(measured_peaks()[0].get("hbm_gbs", FALLBACK_HBM_GBS)),
+                              "outside_2e-3_plus_1e-2_rel": n_fast, "worst_error_over_bound": worst_fast}
+            finally:
+                step.ex.ex.flags = 0
+                step.ex.set_stream()
+
     # ---- bulk append (prefill-sized): the "appended tokens/s" half of the metric ----------------
     bulk_tokens = args.append_tokens
     wl2 = synth.PagedWorkload([0], [bulk_tokens], hkv, seed=seed + 5 + 1000 * rank, device=dev)
@@ -647,11 +868,19 @@ def main():
     bulk_ms = max_over_ranks(e0.elapsed_time(e1), world) / n_bulk
     bulk_tok_s = world * bulk_tokens / (bulk_ms * 1e-3)
 
+    sharded_cases = None
+    if args.config == "cfg1_batched_decode" and not reference and not args.no_sharded:
+        try:
+            sharded_cases = strong_scaling_cases(args, world, rank, dev,
+                                                 {"ms_per_step": ms_per_step, "value": value, "kv_bytes": all_bytes})
+        except Exception as exc:     # every rank raises or none: the collectives inside are entered by all
+            sharded_cases = {"error": repr(exc)}
     if rank != 0:
         return
     peaks, peak_kind = measured_peaks()
     peak = float(peaks.get("hbm_gbs", FALLBACK_HBM_GBS))
     achieved = kv_bytes / (attn_ms * 1e-3) / 1e9
+    traffic_ratio, traffic_rec = (None, None) if reference else measured_traffic_ratio("tq4_attention_stream_kernel<exact>")
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
@@ -667,18 +896,22 @@ def main():
                                    if sharded else f"batch-sharded x{world}, no collective")},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "peak_kind": f"of {peak_kind}", "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,
-                     "kernel": "tq4_attention_stream_kernel (+ plan and merge launches, timed together)",
+                     "kernel": "tq4_attention_stream_kernel, exact build (+ plan and merge launches, timed together)",
                      "launch_ms": attn_ms,
-                     # dram__bytes_read + write of one stream-kernel launch, from the ncu capture of this same
-                     # workload (summarised under profiles/: 1.388 GB for 1.343 GB of
-                     # algorithmic bytes), scaled by the bytes of this run; null for the other workloads
-                     "traffic": (kv_bytes * (1.388 / 1.343) if args.config == "cfg1_batched_decode" and not reference else None)},
+                     # DRAM bytes of one stream-kernel launch: the ratio measured by ncu on a smaller case of
+                     # the same kernel (recorded with its date and workload) times this run's bytes
+                     "traffic": (kv_bytes * traffic_ratio if traffic_ratio is not None and not sharded else None),
+                     **({"traffic_source": traffic_rec} if traffic_rec is not None and not sharded else {})},
         "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": (step.h2d_bytes_total - h2d_before) / e2e_steps,
                 "d2h_bytes_per_step": step.d2h_bytes, "cuda_graph_replay": use_graph,
                 **({"speculative_rollback": rollback} if rollback else {})},
         **({"exchange": "peer", "exchange_equals_allgather_merge": bool(exchange_ok and peer_px.status() == 0)}
            if peer_px is not None else {}),
         "gpu_launches": 4 * args.steps, "cuda_graph_replay": graph_used, "eager_ms_per_step": eager_ms_per_step,
+        "repeats": REPS, "ms_per_step_min_max": [float(min(rep_ms)), float(max(rep_ms))],
+        **({"parity": parity} if parity is not None else {}),
+        **({"sharded": sharded_cases} if sharded_cases is not None else {}),
+        **({"fast_build": fast_build} if fast_build is not None else {}),
         "clocks": clocks,
         "append_tokens_per_s": n_tok / (append_ms * 1e-3), "append_ms": append_ms,
         "append_bulk": {"tokens": bulk_tokens, "ms": bulk_ms, "tokens_per_s": bulk_tok_s,

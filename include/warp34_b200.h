@@ -341,13 +341,19 @@ int warp34_kv_page_copy(const warp34_exec* ex, const warp34_kv_layer_layout* lay
  *
  *  - Same inputs, outputs, masks and result as warp34_paged_attention_f16; `stream` replaces
  *    the warp34_exec.
- *  - Limit: the batch must fit the built-in workspace (plan + one 8256-byte partial per work
- *    item, i.e. per (request, kv head, group of 8 query rows), + 12): 64 decode requests x 24
- *    heads use the whole grid, about 1900 work items is the ceiling.  Larger batches, and
- *    layouts that are not the canonical 132-byte-row packing, are refused with
- *    cudaErrorInvalidValue / cudaErrorNotSupported and nothing is launched; when
- *    `scratch_needed` is not NULL it receives the bytes the batch would have needed, so the
- *    caller can tell "too large" from a malformed argument.
+ *  - Limit: the batch must fit the built-in workspace: the plan, 8256-byte partials (one per
+ *    group of 8 query rows and one more per request, for every kv head, plus 8) and 6 KiB of
+ *    query fragments per group; about 740 (request, kv head) pairs of a decode batch, e.g. 185
+ *    requests at 4 kv heads, is the ceiling.  A
+ *    prefill chunk (more than 24 query rows per request and kv head) uses only the status word,
+ *    whatever its size.  Larger batches are refused with cudaErrorInvalidValue and nothing is
+ *    launched; when `scratch_needed` is not NULL it receives the bytes the batch would have
+ *    needed, so the caller can tell "too large" from a malformed argument.
+ *  - TQ4 layers in the canonical 132-byte-row packing only: other packings and the 8-bit
+ *    boundary layers (Q8_0, FP8 E4M3), which warp34_paged_attention_f16 serves, are refused
+ *    here with cudaErrorNotSupported (801).
+ *  - The status word that warp34_paged_attention_f16 leaves at the start of the caller's
+ *    scratch sits in the built-in array; warp34_static_scratch_status() reads it.
  *  - The first call on each device looks up the array's device address
  *    (cudaGetSymbolAddress, with that device current) and configures the kernel's shared
  *    memory; make that first call outside any stream capture.
@@ -360,6 +366,17 @@ int warp34_paged_attention_f16_static_scratch(uintptr_t stream, const warp34_kv_
                                               const warp34_attention_batch* batch,
                                               const void* q_in, void* attn_out, int num_q_heads,
                                               size_t* scratch_needed);
+
+/*
+ * Status word of the last warp34_paged_attention_f16_static_scratch call on the current device
+ * (no counterpart in the reference): 0 = ok; bit 0 = a bounded wait inside a kernel gave up (the
+ * output is void); bit 1 = the shared-memory window could not hold the kernel's layout; bit 2 =
+ * a request had more query tokens than batch->max_q_len declared and its extra rows were
+ * dropped.  A blocking 4-byte copy from the built-in array: it waits for the work queued before
+ * it, so call it where a synchronisation is acceptable, never inside a stream capture.
+ * Allocates nothing.
+ */
+int warp34_static_scratch_status(int32_t* status_out);
 
 /* Library identification: returns a static string "warp34_b200 <version> sm_100a". */
 const char* warp34_b200_version(void);

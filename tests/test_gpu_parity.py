@@ -400,6 +400,31 @@ def test_page_sharded_partials_merge_to_the_unsharded_result(env):
     assert (merged2.cpu().numpy().view(np.uint16) == merged.cpu().numpy().view(np.uint16)).all()
 
 
+def test_masked_rows_stay_untouched_through_the_sharded_path(env):
+    """A masked request's rows carry "no keys" triples out of every shard, and the cross-shard
+    merge leaves its output rows as they were."""
+    kv = env["kv"]
+    ctx, hq, hkv = [700, 400], 16, 4
+    wl, q = _decode_case(env, ctx, hq, hkv, seed=62)
+    vrm = np.array([1, 0], np.uint8)
+    b = wl.step(q_lens=[1, 1], valid_req_mask=vrm)
+    triples = torch.full((2, 2 * hq, 258), 7.0, dtype=torch.float32, device="cuda")   # stale contents
+    for g in range(2):
+        kv.paged_attention_partial(env["ex"], wl.layer, b, q.cuda(), triples[g], hq)
+    merged = torch.full((2, hq, 256), 0, dtype=torch.int16, device="cuda")
+    merged.fill_(0x5500)
+    kv.merge_shards(env["ex"], triples, merged.view(torch.float16))
+    torch.cuda.synchronize()
+    t = triples.cpu().numpy().reshape(2, 2, hq, 258)
+    assert (t[:, 1, :, 257] == 0).all() and (t[:, 1, :, :256] == 0).all()
+    bits = merged.cpu().numpy().view(np.uint16)
+    assert (bits[1] == 0x5500).all(), "masked request's rows were written"
+    # two identical shards merge to the single-pass result of the live request
+    want = _oracle_attention(wl, b, q, hq)
+    ok, msg = plain_parity(f16(bits[0:1]), want[0:1])
+    assert ok, msg
+
+
 def _mailbox_views(kv, buf, world, max_rows):
     n_in = 2 * world * max_rows * 258 * 4
     inbox = buf[:n_in].view(torch.float32).view(2, world, max_rows, 258)

@@ -37,22 +37,28 @@ def test_static_scratch_entry_point_matches_the_ordinary_one_twice(native_libs):
         kv.paged_attention(ex, wl.layer, b, q, want, hq)
         return wl, b, q, want
 
-    # two different batches back to back: the second runs over the first one's leftovers
-    for ctx, q_len, seed in (([900, 17, 2500, 64], 1, 5), ([300, 33], 4, 6)):
+    # different batches back to back, each over the previous one's leftovers: decode, verify, and a
+    # prefill chunk (which takes the 128-row kernel and needs the status word only)
+    for ctx, q_len, seed in (([900, 17, 2500, 64], 1, 5), ([300, 33], 4, 6), ([500, 140], 70, 7)):
         wl, b, q, want = case(ctx, q_len, seed)
         got = torch.full_like(q, 3.0)
         needed = C.c_size_t(0)
         rc = lib.warp34_paged_attention_f16_static_scratch(stream, C.byref(wl.layer.layout), C.byref(b.desc),
                                                            q.data_ptr(), got.data_ptr(), hq, C.byref(needed))
         assert rc == 0 and 0 < needed.value <= (16 << 20)
+        assert (needed.value == 16) == (q_len == 70)
         torch.cuda.synchronize()
         a, w = got.float().cpu().numpy(), want.float().cpu().numpy()
         assert (np.abs(a - w) <= ATOL + RTOL * np.abs(w)).all()
+        status = C.c_int32(-1)
+        assert lib.warp34_static_scratch_status(C.byref(status)) == 0 and status.value == 0
 
-    # a batch beyond the built-in workspace is refused before anything is launched
+    # A decode batch beyond the built-in workspace is refused before anything is launched.  (Only the
+    # sizes are inflated: had the call gone through, the kernels would have read past the two requests'
+    # metadata, so the descriptor is a decode one, whose size the entry point checks.)
     big = ffi.AttentionBatch()
     C.memmove(C.byref(big), C.byref(b.desc), C.sizeof(big))
-    big.total_tokens, big.num_reqs = 4096, 2048
+    big.total_tokens, big.num_reqs, big.max_q_len = 4096, 4096, 1
     sentinel = got.clone()
     needed = C.c_size_t(0)
     rc = lib.warp34_paged_attention_f16_static_scratch(stream, C.byref(wl.layer.layout), C.byref(big), q.data_ptr(),

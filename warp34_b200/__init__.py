@@ -6,8 +6,7 @@ Layout of the package:
   ffi.py     ctypes bindings of both ABIs
   kv.py      host-side mirror of the reference's KvPool / request page state / step metadata
   synth.py   seeded synthetic workloads of the benchmark configurations
-  sharding.py        how batches, KV heads and pages are cut across GPUs
-  stream_profile.py  development aid: per-warp time stamps of the decode kernel
+  sharding.py  how batches, KV heads and pages are cut across GPUs
 """
 from . import ffi  # noqa: F401
 

@@ -31,21 +31,10 @@
 namespace w34 {
 
 // The reference computes warp_reduce_sum(a * b): the product is rounded, then summed by the
-// butterfly.  Had the compiler contracted the first butterfly add with the product into an
-// fma, lanes with column bit 4 clear ("lo class") would hold fma(a_lo, b_lo, rn(a_hi*b_hi))
-// and the others fma(a_hi, b_hi, rn(a_lo*b_lo)): two different sums.  Comparing all eight
-// on/off combinations against the reference kernels built for sm_100a showed that it does
-// not (all three off is bit-identical; turning either least-squares sum on is not), so the
-// switches default to 0; the emulation stays for re-checking against another toolchain.
-#ifndef W34_CONTRACT_SQ
-#define W34_CONTRACT_SQ 0
-#endif
-#ifndef W34_CONTRACT_VC
-#define W34_CONTRACT_VC 0
-#endif
-#ifndef W34_CONTRACT_CC
-#define W34_CONTRACT_CC 0
-#endif
+// butterfly, and nvcc does not contract the butterfly's first add with the product into an fma
+// (all eight contracted / uncontracted combinations of the three sums were compared with the
+// reference kernels built for sm_100a: only "none contracted" is bit-identical).  Products and adds
+// below are therefore explicit __fmul_rn / __fadd_rn.
 
 // code = #{i : rv > boundary_i} for the 15 ascending, symmetric boundaries (b[7] = 0), by a
 // three-level binary search on |rv| in the integer domain.  bpos[k] = bits(boundary[8 + k]) > 0.
@@ -99,22 +88,12 @@ __device__ __forceinline__ float seq4(float t, int lane_base, int g0) {
 
 // Register-only levels (column bits 4 then 3) of the butterfly over products a*b for one
 // group; r indexes column bits 3,4 as (bit3 = r & 1, bit4 = r >> 1).
-template <bool CONTRACT>
 __device__ __forceinline__ void reg_levels(const float (&a)[4], const float (&b)[4], float& lo, float& hi) {
     float p[4];
 #pragma unroll
     for (int r = 0; r < 4; ++r) p[r] = __fmul_rn(a[r], b[r]);
-    if (CONTRACT) {
-        const float l0 = __fmaf_rn(a[0], b[0], p[2]);
-        const float l1 = __fmaf_rn(a[1], b[1], p[3]);
-        const float h0 = __fmaf_rn(a[2], b[2], p[0]);
-        const float h1 = __fmaf_rn(a[3], b[3], p[1]);
-        lo = __fadd_rn(l0, l1);
-        hi = __fadd_rn(h0, h1);
-    } else {
-        lo = __fadd_rn(__fadd_rn(p[0], p[2]), __fadd_rn(p[1], p[3]));
-        hi = lo;
-    }
+    lo = __fadd_rn(__fadd_rn(p[0], p[2]), __fadd_rn(p[1], p[3]));
+    hi = lo;
 }
 
 struct AppendParams {
@@ -127,14 +106,12 @@ struct AppendParams {
     int total_rows;  // total_tokens * local_kv_heads * 2
 };
 
-#ifndef W34_APPEND_BLOCKS_PER_SM
-#define W34_APPEND_BLOCKS_PER_SM 5
-#endif
+constexpr int kAppendBlocksPerSm = 5;   // 4, 6 and 8 measured within 3 % of it on a 32 768-token append
 
 // IN_BF16: activations are bf16 instead of fp16.  Values that both types can hold encode to the
 // same bytes; bf16 values beyond the fp16 range are simply larger fp32 inputs.
 template <bool IN_BF16>
-__global__ void __launch_bounds__(128, W34_APPEND_BLOCKS_PER_SM) tq4_append_kernel(const AppendParams p) {
+__global__ void __launch_bounds__(128, kAppendBlocksPerSm) tq4_append_kernel(const AppendParams p) {
     __shared__ float s_centroid[16];
     if (threadIdx.x < 16) s_centroid[threadIdx.x] = tq4_centroid(threadIdx.x);
     __syncthreads();
@@ -236,21 +213,14 @@ __global__ void __launch_bounds__(128, W34_APPEND_BLOCKS_PER_SM) tq4_append_kern
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             const float a[4] = {v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]};
-            reg_levels<W34_CONTRACT_SQ != 0>(a, a, xl[j], xh[j]);
+            reg_levels(a, a, xl[j], xh[j]);
         }
         const float tl = group_totals(xl, sub);
         const float s0l = seq4(tl, lane_base, 0), s1l = seq4(tl, lane_base, 4);
         inv_lo[0] = (s0l > 1e-20f) ? (0.7071067811865475f * rsqrtf(s0l)) : 0.0f;
         inv_lo[1] = (s1l > 1e-20f) ? (0.7071067811865475f * rsqrtf(s1l)) : 0.0f;
-        if (W34_CONTRACT_SQ != 0) {
-            const float thh = group_totals(xh, sub);
-            const float s0h = seq4(thh, lane_base, 0), s1h = seq4(thh, lane_base, 4);
-            inv_hi[0] = (s0h > 1e-20f) ? (0.7071067811865475f * rsqrtf(s0h)) : 0.0f;
-            inv_hi[1] = (s1h > 1e-20f) ? (0.7071067811865475f * rsqrtf(s1h)) : 0.0f;
-        } else {
-            inv_hi[0] = inv_lo[0];
-            inv_hi[1] = inv_lo[1];
-        }
+        inv_hi[0] = inv_lo[0];
+        inv_hi[1] = inv_lo[1];
     }
 
     // ---- codes, centroids, least-squares sums ------------------------------------------
@@ -269,8 +239,8 @@ __global__ void __launch_bounds__(128, W34_APPEND_BLOCKS_PER_SM) tq4_append_kern
             c[q4] = s_centroid[q];
         }
         float hi_unused;
-        reg_levels<W34_CONTRACT_VC != 0>(a, c, vcl[j], hi_unused);
-        reg_levels<W34_CONTRACT_CC != 0>(c, c, ccl[j], hi_unused);
+        reg_levels(a, c, vcl[j], hi_unused);
+        reg_levels(c, c, ccl[j], hi_unused);
     }
     // Only lane 0 of the reference warp (a lo-class lane) uses these sums.
     const float vct = group_totals(vcl, sub);
@@ -429,7 +399,7 @@ static int launch_append(const warp34_exec* ex, const warp34_kv_layer_layout* la
         }
         if (sm_count_cache[dev] > 0) sms = sm_count_cache[dev];
     }
-    const long long resident = (long long)sms * W34_APPEND_BLOCKS_PER_SM;
+    const long long resident = (long long)sms * kAppendBlocksPerSm;
     const unsigned blocks = (unsigned)(blocks_needed < resident ? blocks_needed : resident);
     if (in_bf16) {
         tq4_append_kernel<true><<<blocks, 128, 0, (cudaStream_t)ex->stream>>>(p);

@@ -31,6 +31,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <mutex>
+
 namespace w34 {
 
 // ---------------------------------------------------------------------------------------
@@ -999,15 +1001,9 @@ __global__ void __launch_bounds__(WARPS * 32, 1) tq4_attention_stream_kernel(con
 // the output product of a page runs after the next meeting, so one page's softmax overlaps the
 // next page's score product.  Three teams per CTA, one CTA per SM, each team with its own ring.
 // ---------------------------------------------------------------------------------------
-#ifndef W34_TEAMS
-#define W34_TEAMS 3
-#endif
-#ifndef W34_TEAM_STAGES
-#define W34_TEAM_STAGES 8
-#endif
-constexpr int kTeams = W34_TEAMS;
+constexpr int kTeams = 3;
 constexpr int kTeamWarps = 4;
-constexpr int kTeamStages = W34_TEAM_STAGES;
+constexpr int kTeamStages = 8;
 
 __device__ __forceinline__ void team_barrier(int team) {
     asm volatile("bar.sync %0, %1;" ::"r"(team + 1), "r"(kTeamWarps * 32) : "memory");
@@ -1521,11 +1517,21 @@ __global__ void __launch_bounds__(MW * 32) tq4_attention_merge_kernel(const Stre
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const long long row_ll = blockIdx.x;
     const int tok = (int)(row_ll / p.num_q_heads), q_head = (int)(row_ll % p.num_q_heads);
-    if (p.batch.valid_token_mask != nullptr && p.batch.valid_token_mask[tok] == 0) return;
+    // A row that takes no part (masked token or request, rows the plan dropped) leaves attn_out
+    // untouched; as a triple it is written as "no keys" (l = 0), which the cross-shard merges skip.
+    auto skip_row = [&]() {
+        if (PARTIAL_OUT && wid == 0) {
+            float* dst = p.triple_out + ((size_t)tok * p.num_q_heads + q_head) * (kHeadDim + 2);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) dst[lane + 32 * j] = 0.0f;
+            if (lane == 0) { dst[kHeadDim] = -1e30f; dst[kHeadDim + 1] = 0.0f; }
+        }
+    };
+    if (p.batch.valid_token_mask != nullptr && p.batch.valid_token_mask[tok] == 0) { skip_row(); return; }
     const int R = p.batch.num_reqs;
     const int r = find_request(p.batch.query_start_loc, R, tok);
-    if (r < 0) return;
-    if (p.batch.valid_req_mask != nullptr && p.batch.valid_req_mask[r] == 0) return;
+    if (r < 0) { skip_row(); return; }
+    if (p.batch.valid_req_mask != nullptr && p.batch.valid_req_mask[r] == 0) { skip_row(); return; }
 
     const PlanHeader* hdr = reinterpret_cast<const PlanHeader*>(p.scratch);
     const int32_t* unit_prefix = plan_array(p.scratch, 0, R);
@@ -1539,7 +1545,7 @@ __global__ void __launch_bounds__(MW * 32) tq4_attention_merge_kernel(const Stre
     const int rpg = p.rows_per_group;
     const int part_floats = rpg * kHeadDim + 2 * rpg;
     const int group = row_in_req / rpg, row8 = row_in_req - group * rpg;
-    if (group >= ngroups_a[r]) return;  // rows the plan dropped (q_len above the declared max_q_len)
+    if (group >= ngroups_a[r]) { skip_row(); return; }  // rows the plan dropped (q_len above the declared max_q_len)
     const int item = kv_head * ngroups_a[r] + group;
     const int npages = npages_a[r];
     const int per = hdr->units_per_warp;
@@ -1650,7 +1656,8 @@ __global__ void __launch_bounds__(128) tq4_attention_merge_shards_kernel(
             for (int j = 0; j < 8; ++j) acc[j] += t[lane + 32 * j] * wgt;
         }
     }
-    const float inv_l = (l_tot > 0.0f) ? (1.0f / (l_tot * kLutScale)) : 0.0f;
+    if (!(l_tot > 0.0f)) return;   // no shard had a key for this row (a masked row): attn_out stays as it is
+    const float inv_l = 1.0f / (l_tot * kLutScale);
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] *= inv_l;
     wht256_lanes(acc, lane);
@@ -1745,7 +1752,8 @@ __global__ void __launch_bounds__(128) tq4_attention_exchange_merge_kernel(
             for (int j = 0; j < 8; ++j) acc[j] += (own ? t_own[j] : __ldcg(t + lane + 32 * j)) * wgt;
         }
     }
-    const float inv_l = (l_tot > 0.0f) ? (1.0f / (l_tot * kLutScale)) : 0.0f;
+    if (!(l_tot > 0.0f)) return;   // a row without keys on any rank (a masked row): attn_out stays as it is
+    const float inv_l = 1.0f / (l_tot * kLutScale);
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] *= inv_l;
     wht256_lanes(acc, lane);
@@ -1798,6 +1806,8 @@ struct DeviceInfo {
 
 static DeviceInfo* device_info(int* rc) {
     static DeviceInfo info[64];
+    static std::mutex guard;   // the one-time set-up of a device may be reached from several host threads
+    std::lock_guard<std::mutex> lock(guard);
     int dev = 0;
     *rc = (int)cudaGetDevice(&dev);
     if (*rc != 0) return nullptr;
@@ -2149,10 +2159,12 @@ namespace w34 {
 static int static_scratch_address(uint64_t* out) {
     static uint64_t addr[64];
     static bool known[64];
+    static std::mutex guard;   // rank threads may make their first calls at the same time
     int dev = 0;
     int rc = (int)cudaGetDevice(&dev);
     if (rc != 0) return rc;
     if (dev < 0 || dev >= 64) return (int)cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> lock(guard);
     if (!known[dev]) {
         void* ptr = nullptr;
         rc = (int)cudaGetSymbolAddress(&ptr, g_static_scratch);
@@ -2195,6 +2207,11 @@ extern "C" int warp34_paged_attention_f16_static_scratch(uintptr_t stream, const
     const int rc = w34::static_scratch_address(&ex.scratch_ptr);
     if (rc != 0) return rc;
     return w34::launch_attention(&ex, layout, batch, q_in, attn_out, nullptr, num_q_heads);
+}
+
+extern "C" int warp34_static_scratch_status(int32_t* status_out) {
+    if (status_out == nullptr) return (int)cudaErrorInvalidValue;
+    return (int)cudaMemcpyFromSymbol(status_out, g_static_scratch, sizeof(int32_t), 0, cudaMemcpyDeviceToHost);
 }
 
 extern "C" int warp34_tq4_paged_attention_bf16(const warp34_exec* ex, const warp34_kv_layer_layout* layout,

@@ -201,15 +201,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) tq4_attention_prefill_tc_kernel
     auto bar = [&](int which) { return bars + 8u * (uint32_t)which; };
     // Waits and abort checks are made warp-uniform, so that no lane leaves a loop alone and the
     // warp-collective instructions below always see all 32 lanes.
-#ifdef W34_TC_PROFILE
-    // Measurement build only: cycles spent in each kind of wait and in the work between, per role,
-    // written behind the status word (needs a scratch buffer of at least 1 MiB).
-    long long prof[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    long long prof_t = clock64();
-#define W34_PROF(slot) { const long long now_ = clock64(); prof[slot] += now_ - prof_t; prof_t = now_; }
-#else
-#define W34_PROF(slot)
-#endif
     auto wait_all = [&](uint32_t b, uint32_t parity) {
         const bool ok = mbar_wait(b, parity);
         return __all_sync(0xffffffffu, ok) != 0;
@@ -365,12 +356,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) tq4_attention_prefill_tc_kernel
         for (int j = 0; j <= nblocks; ++j) {
             if (aborted_any()) break;
             if (j < nblocks) {
-                W34_PROF(0)
                 bool ok = wait_all(bar(kBarFullK0 + (j & 1)), (uint32_t)((j >> 1) & 1));
-                W34_PROF(1)
                 // S buffer j & 1 was last read by the softmax of block j - 2
                 if (ok && j > 1) ok = wait_all(bar(kBarSFree0 + (j & 1)), (uint32_t)(((j - 2) >> 1) & 1));
-                W34_PROF(2)
                 if (!ok) { *abort_flag = 1u; break; }
                 tc_fence_after();
                 if (lane == 0) {
@@ -388,11 +376,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) tq4_attention_prefill_tc_kernel
             }
             if (j > 0) {
                 const int i = j - 1;
-                W34_PROF(0)
                 bool ok = wait_all(bar(kBarPReady), (uint32_t)(i & 1));
-                W34_PROF(3)
                 ok = ok && wait_all(bar(kBarFullV0 + (i & 1)), (uint32_t)((i >> 1) & 1));
-                W34_PROF(4)
                 if (!ok) { *abort_flag = 1u; break; }
                 tc_fence_after();
                 if (lane == 0) {
@@ -498,9 +483,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) tq4_attention_prefill_tc_kernel
         for (int j = 0; j < nblocks; ++j) {
             if (aborted_any()) break;
             const uint32_t par = (uint32_t)(j & 1);
-            W34_PROF(0)
             if (!wait_all(bar(kBarRawFull0), par)) { *abort_flag = 1u; break; }
-            W34_PROF(1)
             const int pos = ((kb_lo + j) << 6) + key;
             const bool key_ok = pos >= kv_lo && pos <= kv_hi;
             const uint32_t rowp = raw + (uint32_t)key * kTq4RowBytes;
@@ -510,18 +493,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) tq4_attention_prefill_tc_kernel
             mbar_arrive(bar(kBarRawFree0));     // the next block's runs can be copied in
             // K buffer j & 1 was last read by the score product of block j - 2
             if (j > 1 && !wait_all(bar(kBarEmptyK0 + (j & 1)), (uint32_t)(((j - 2) >> 1) & 1))) { *abort_flag = 1u; break; }
-            W34_PROF(2)
             convert(wk, dk, k_t + (uint32_t)(j & 1) * kTcKvBytes, key_ok, false);
             fence_proxy_async();
             mbar_arrive(bar(kBarFullK0 + (j & 1)));
-            W34_PROF(3)
             // V buffer j & 1 was last read by the output product of block j - 2
             if (j > 1 && !wait_all(bar(kBarEmptyV0 + (j & 1)), (uint32_t)(((j - 2) >> 1) & 1))) { *abort_flag = 1u; break; }
-            W34_PROF(4)
             convert(wv, dv, v_t + (uint32_t)(j & 1) * kTcKvBytes, key_ok, true);
             fence_proxy_async();
             mbar_arrive(bar(kBarFullV0 + (j & 1)));
-            W34_PROF(5)
         }
     } else {
         // ======================= consumers: MMA issue, softmax, P, rescale =========================
@@ -532,9 +511,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) tq4_attention_prefill_tc_kernel
         for (int j = 0; j < nblocks; ++j) {
             if (aborted_any()) break;
             const uint32_t par = (uint32_t)(j & 1);
-            W34_PROF(0)
             if (!wait_all(bar(kBarS0 + (j & 1)), (uint32_t)((j >> 1) & 1))) { *abort_flag = 1u; break; }
-            W34_PROF(1)
             tc_fence_after();
             const uint32_t t_sj = t_s + 64u * (uint32_t)(j & 1);
             float sv[64];
@@ -568,9 +545,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) tq4_attention_prefill_tc_kernel
                 m_ref = mx;
             }
             // P(j - 1) and O are in use until the previous output product has completed
-            W34_PROF(2)
             if (j > 0 && !wait_all(bar(kBarPv), par ^ 1u)) { *abort_flag = 1u; break; }
-            W34_PROF(3)
             tc_fence_after();
             if (j > 0 && __any_sync(0xffffffffu, need)) {
 #pragma unroll 1
@@ -584,7 +559,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) tq4_attention_prefill_tc_kernel
                 }
                 tc_wait_st();
             }
-            W34_PROF(4)
             float ls4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
             const float m_use = (m_ref < -1e29f) ? 0.0f : m_ref;     // nothing visible yet: every P is 0
             // P as fp16 pairs goes where its own scores were: the first 32 columns of this score buffer
@@ -602,7 +576,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) tq4_attention_prefill_tc_kernel
             l_run = l_run * alpha + ((ls4[0] + ls4[1]) + (ls4[2] + ls4[3]));
             tc_fence_before();
             mbar_arrive(bar(kBarPReady));
-            W34_PROF(5)
         }
         // the last output product
         if (nblocks > 0 && !aborted_any()) {
@@ -611,14 +584,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) tq4_attention_prefill_tc_kernel
         tc_fence_after();
     }
 
-#ifdef W34_TC_PROFILE
-    if (p.status != nullptr && lane == 0 && (wid == 0 || wid == 4 || wid == 4 + kTcProducerWarps)) {
-        long long* out = reinterpret_cast<long long*>(p.status) + 512 +
-                         ((size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 3 + (wid == 0 ? 0 : (wid == 4 ? 1 : 2))) * 8;
-        for (int i = 0; i < 8; ++i) out[i] = prof[i];
-        if (wid == 0) out[7] = nblocks;
-    }
-#endif
     // ---- epilogue: O / l -> staging -> inverse rotation -> global ---------------------------------
     // (staging aliases the Q / K / V tiles: every MMA that read them has completed)
     __syncthreads();

@@ -601,6 +601,7 @@ class DecodeStep:
         self.h2d_bytes_total = 0                                  # bytes actually copied by run() so far
         self._graphs = {}
         self.d2h_bytes = self.out_host.numel() * 2
+        self._fence = None      # recorded after a step's last use of the pinned buffers when sync=False
 
     def _capture(self, lib):
         """Two CUDA graphs for the whole step (the reference replays its decode steps the same way,
@@ -638,14 +639,23 @@ class DecodeStep:
         self.ex.set_stream()
         return tuple(graphs)
 
-    def run(self, q_lens, sm_scale=1.0 / 16.0, lib=None, sync=True, attend=None, graph=False):
+    def run(self, q_lens, sm_scale=1.0 / 16.0, lib=None, sync=True, attend=None, graph=False,
+            mask_mode=0, sliding_window=0):
+        """sync=False returns while the step is still running: the pinned K / V / Q / metadata
+        buffers and out_host belong to the device until the NEXT run() (which waits for this step
+        first) or until the caller synchronises the stream."""
+        if self._fence is not None:     # the previous step may still be reading the pinned arena
+            self._fence.synchronize()
+            self._fence = None
         if graph and attend is None:
-            # geometry baked into the captured launches: token count and request count must not change
-            key = (id(lib), len(self.seqs), int(sum(q_lens)), int(max(q_lens)))
+            # baked into the captured launches (the descriptors are passed by value): the geometry,
+            # the softmax scale, the mask mode and the window, and the executor's flags
+            key = (id(lib), len(self.seqs), int(sum(q_lens)), int(max(q_lens)), float(sm_scale),
+                   int(mask_mode), int(sliding_window), int(self.ex.ex.flags))
             g = self._graphs.get(key)
             if g is not None:
                 g[0].replay()           # K, V, Q on their way while the metadata is packed
-            self.io.pack(self.seqs, q_lens, sm_scale)
+            self.io.pack(self.seqs, q_lens, sm_scale, mask_mode, sliding_window)
             if g is None:
                 self.io.upload(full=True)
                 g = self._graphs[key] = self._capture(lib)
@@ -653,10 +663,9 @@ class DecodeStep:
             self.meta_bytes_last = self.io.upload(tables_only=True) + 4 * self.io.head_words
             self.h2d_bytes_total += self.meta_bytes_last + self.payload_bytes
             g[1].replay()
-            if sync:
-                torch.cuda.current_stream().synchronize()
+            self._finish(sync)
             return self.out_host
-        self.io.pack(self.seqs, q_lens, sm_scale)
+        self.io.pack(self.seqs, q_lens, sm_scale, mask_mode, sliding_window)
         self.meta_bytes_last = self.io.upload()
         self.h2d_bytes_total += self.meta_bytes_last + self.payload_bytes
         self.k_dev.copy_(self.k_host, non_blocking=True)
@@ -670,6 +679,12 @@ class DecodeStep:
         else:
             paged_attention(self.ex, self.layer, b, self.q_dev, self.out_dev, self.hq, lib=lib)
         self.out_host.copy_(self.out_dev, non_blocking=True)
+        self._finish(sync)
+        return self.out_host
+
+    def _finish(self, sync):
         if sync:
             torch.cuda.current_stream().synchronize()
-        return self.out_host
+        else:
+            self._fence = torch.cuda.Event()
+            self._fence.record()
