@@ -577,6 +577,9 @@ def main():
     ap.add_argument("--config", default="cfg1_batched_decode")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sharded", action="store_true", help="skip the strong-scaling cases of the `sharded` object")
+    ap.add_argument("--batch", type=int, default=0,
+                    help="override the number of sequences of the configuration (a smaller case of the same "
+                         "kernels for profiler captures; not a benchmark value)")
     ap.add_argument("--append-tokens", type=int, default=32768, help="tokens of the bulk-append measurement")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches only (no CUDA graph replay)")
     ap.add_argument("--prefix-tokens", type=int, default=4096,
@@ -603,6 +606,8 @@ def main():
     lib = ffi.bind_kernel_abi(ref_path) if ref_path else ffi.kernels()
 
     hq, hkv, batch, lo, hi, q_len, seed = synth.CONFIGS[args.config]
+    if args.batch > 0:
+        batch = args.batch
     sharded = args.config == "cfg4_long_context" and world > 1 and not reference
     if sharded:
         # one sequence, pages split across ranks: rank r holds tokens [r L / N, (r + 1) L / N)
@@ -869,7 +874,7 @@ def main():
     bulk_tok_s = world * bulk_tokens / (bulk_ms * 1e-3)
 
     sharded_cases = None
-    if args.config == "cfg1_batched_decode" and not reference and not args.no_sharded:
+    if args.config == "cfg1_batched_decode" and not reference and not args.no_sharded and args.batch == 0:
         try:
             sharded_cases = strong_scaling_cases(args, world, rank, dev,
                                                  {"ms_per_step": ms_per_step, "value": value, "kv_bytes": all_bytes})

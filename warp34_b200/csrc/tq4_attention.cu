@@ -429,11 +429,12 @@ __device__ __forceinline__ uint32_t token_offset(int t) {  // byte offset of tok
 //    tensor-core kernel computes (op_paged_attn.cu:357, :47-50, :470).
 constexpr int kFastWarps = 12, kFastStages = 3;
 constexpr int kExactWarps = 8, kExactStages = 4;
-// A page is "peaked" when one of its softmax weights exceeds this fraction of the running maximum.
-// Only there does the rounding residual of the V centroids (1e-4 relative, but the same for every
-// coordinate that holds the same code, so the inverse rotation can collect it on one channel) go
-// through an extra product: a weight below a quarter of the maximum moves the output by less than
-// a quarter of that.
+// A page is "peaked" when one of its keys holds more than this fraction of a row's softmax mass so
+// far (an upper bound of the key's final weight: the mass only grows).  Only there does the rounding
+// residual of the V centroids (1e-4 relative, but the same for every coordinate that holds the same
+// code, so the inverse rotation can collect it on one channel) go through an extra product: a key
+// below a quarter of the mass moves the output by less than a quarter of that.  (Gating the residual
+// of P x d_v the same way, at 1/16 of the mass, measured no faster than carrying it on every page.)
 constexpr float kPeakedWeight = 0.25f;
 // Rounding residuals are 2^-12 of their values, which for Q' (about 0.1) and for the table's
 // centroids (0.008 .. 0.16) lies in fp16's subnormal range; as e5m2 bytes they would keep no
@@ -829,14 +830,28 @@ __global__ void __launch_bounds__(WARPS * 32, 1) tq4_attention_stream_kernel(con
                 if (msk[0] && msk[1]) { dva0 = 0.0f; dva1 = 0.0f; }
                 if (msk[2] && msk[3]) { dvb0 = 0.0f; dvb1 = 0.0f; }
             }
-            l_run[0] += pr[0] + pr[2];
-            l_run[1] += pr[1] + pr[3];
+            bool peaked = false;
+            if (EXACT) {
+                // the exact build keeps the row totals (every lane of a row holds the same l) for the test
+                float ps0 = pr[0] + pr[2], ps1 = pr[1] + pr[3];
+#pragma unroll
+                for (int d = 4; d < 32; d <<= 1) {
+                    ps0 += __shfl_xor_sync(0xffffffffu, ps0, d);
+                    ps1 += __shfl_xor_sync(0xffffffffu, ps1, d);
+                }
+                l_run[0] += ps0;
+                l_run[1] += ps1;
+                // (rows that do not exist score 0 against their zero query; they must not count as peaks)
+                const bool pk0 = rvalid[0] && fmaxf(pr[0], pr[2]) > kPeakedWeight * l_run[0];
+                const bool pk1 = rvalid[1] && fmaxf(pr[1], pr[3]) > kPeakedWeight * l_run[1];
+                peaked = __any_sync(0xffffffffu, pk0 || pk1);
+            } else {
+                l_run[0] += pr[0] + pr[2];
+                l_run[1] += pr[1] + pr[3];
+            }
             // P * d_v per half as B fragments (k = key, n = query row); the exact build adds the fp16
             // rounding residual of P * d_v as a second fragment.
-            // (rows that do not exist score 0 against their zero query; they must not count as peaks)
             uint32_t pb[2][2], pl[2][2] = {{0u, 0u}, {0u, 0u}};
-            const float pk0 = rvalid[0] ? fmaxf(pr[0], pr[2]) : 0.0f, pk1 = rvalid[1] ? fmaxf(pr[1], pr[3]) : 0.0f;
-            const bool peaked = EXACT && __any_sync(0xffffffffu, fmaxf(pk0, pk1) > kPeakedWeight);
             const float pd[2][4] = {{pr[0] * dva0, pr[1] * dva0, pr[2] * dvb0, pr[3] * dvb0},
                                     {pr[0] * dva1, pr[1] * dva1, pr[2] * dvb1, pr[3] * dvb1}};
 #pragma unroll
@@ -858,8 +873,8 @@ __global__ void __launch_bounds__(WARPS * 32, 1) tq4_attention_stream_kernel(con
             // tokens kv0 + {0, 1, 4, 5}
             const uint32_t vr = vst + token_offset(kv0);
             const uint32_t vwb = 4u * (uint32_t)(gid >> 1) + (uint32_t)(gid & 1);
-            // Every page: V P (+ V P_residual).  A peaked page then adds V_residual P in a second pass
-            // over its V codes (the K table holds the residuals).
+            // Every page: V P + V P_residual.  A peaked page then adds V_residual P in a second pass over
+            // its V codes (the K table holds the residuals).
             // The second pass is a branch of its own so that the common pass stays one basic block
             // with the softmax above it, whose latencies its loads and look-ups fill.
 #pragma unroll
@@ -952,11 +967,13 @@ __global__ void __launch_bounds__(WARPS * 32, 1) tq4_attention_stream_kernel(con
         }
 
         // ---- write the partial: natural column order, through the idle ring ------------------
-        // l: add the 8 lanes (gid) that share a query row
+        // l: add the 8 lanes (gid) that share a query row (the exact build already holds row totals)
+        if (!EXACT) {
 #pragma unroll
-        for (int d = 4; d < 32; d <<= 1) {
-            l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], d);
-            l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], d);
+            for (int d = 4; d < 32; d <<= 1) {
+                l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], d);
+                l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], d);
+            }
         }
         float* stage_o = reinterpret_cast<float*>(ring_gen);  // [8 rows][256]
 #pragma unroll

@@ -389,20 +389,30 @@ __global__ void __launch_bounds__(kPxWarps * 32, 1) tq4_attention_prefill_exact_
             m_run[1] = mn1;
         }
         float pr[2][4];
-        float pk0 = 0.0f, pk1 = 0.0f;
+        float pk0 = 0.0f, pk1 = 0.0f, ps0 = 0.0f, ps1 = 0.0f;
 #pragma unroll
         for (int n = 0; n < 2; ++n) {
             pr[n][0] = msk[n][0] ? 0.0f : ex2(sc[n][0] - mn0);
             pr[n][1] = msk[n][1] ? 0.0f : ex2(sc[n][1] - mn0);
             pr[n][2] = msk[n][2] ? 0.0f : ex2(sc[n][2] - mn1);
             pr[n][3] = msk[n][3] ? 0.0f : ex2(sc[n][3] - mn1);
-            l_run[0] += pr[n][0] + pr[n][1];
-            l_run[1] += pr[n][2] + pr[n][3];
+            ps0 += pr[n][0] + pr[n][1];
+            ps1 += pr[n][2] + pr[n][3];
             pk0 = fmaxf(pk0, fmaxf(pr[n][0], pr[n][1]));
             pk1 = fmaxf(pk1, fmaxf(pr[n][2], pr[n][3]));
         }
+        // row totals (every lane of a quad holds the same l): a page is peaked when one key holds more
+        // than kPeakedWeight of a row's softmax mass so far
+#pragma unroll
+        for (int d = 1; d < 4; d <<= 1) {
+            ps0 += __shfl_xor_sync(0xffffffffu, ps0, d);
+            ps1 += __shfl_xor_sync(0xffffffffu, ps1, d);
+        }
+        l_run[0] += ps0;
+        l_run[1] += ps1;
         // rows that do not exist score 0 against their zero query; they must not count as peaks
-        const bool peaked = __any_sync(0xffffffffu, fmaxf(rvalid[0] ? pk0 : 0.0f, rvalid[1] ? pk1 : 0.0f) > kPeakedWeight);
+        const bool peaked = __any_sync(0xffffffffu, (rvalid[0] && pk0 > kPeakedWeight * l_run[0]) ||
+                                                    (rvalid[1] && pk1 > kPeakedWeight * l_run[1]));
         // P d_v as A fragments (k = the page's 16 tokens), value and residual, one set per 128-half of V
         float pd[2][2][4];   // [half][n][c]
 #pragma unroll
@@ -528,11 +538,6 @@ __global__ void __launch_bounds__(kPxWarps * 32, 1) tq4_attention_prefill_exact_
 
     // ---- epilogue: normalise, inverse rotation, store; 8 rows at a time through this warp's
     //      fragment area (8 KB of fp32) -------------------------------------------------------------
-#pragma unroll
-    for (int d = 1; d < 4; d <<= 1) {
-        l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], d);
-        l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], d);
-    }
     const float inv0 = (l_run[0] > 0.0f) ? (1.0f / (l_run[0] * kLutScale)) : 0.0f;
     const float inv1 = (l_run[1] > 0.0f) ? (1.0f / (l_run[1] * kLutScale)) : 0.0f;
     float* ostage = reinterpret_cast<float*>(qhi_gen);   // [8 rows][256]
