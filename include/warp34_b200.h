@@ -207,6 +207,36 @@ int warp34_paged_attention_f16_force_kernel_for_test(const warp34_exec* ex, cons
                                                      int num_q_heads, int use_64q);
 
 /*
+ * Paged attention with the layer's output epilogue folded into the kernels' final store: the
+ * sigmoid output gate and, with hadamard64 != 0, the 64-point Hadamard (x 1/8) over every 64
+ * columns that pre-rotates the input of an offline-rotated o_proj.  Additive: replaces the pair
+ * warp34_paged_attention_f16 + warp34_apply_attn_output_gate(_hadamard)_f16 of the reference's
+ * layer (crates/warp34-host/src/model/forward.rs:1181-1211) and saves the round trip of the
+ * attention output through HBM.  gate and out are fp16 [total_tokens, num_q_heads, 256]; out may
+ * not alias q_in.  Rounding follows the two-kernel sequence (attention output to fp16, gated value
+ * to fp16 before the Hadamard); masked rows of out are left untouched.  TQ4 layers apply the
+ * epilogue inside the merge / prefill kernels, 8-bit layers in a second launch in place.
+ */
+int warp34_paged_attention_gated_f16(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
+                                     const warp34_attention_batch* batch,
+                                     const void* q_in, const void* gate, void* out,
+                                     int num_q_heads, int hadamard64);
+
+/*
+ * The epilogue's two steps on their own.  Replace warp34_apply_attn_output_gate_f16
+ * (warp34_cuda.h:297-300, op_norms_rope_act.cu:742-764, :1329-1345) and
+ * warp34_apply_attn_output_gate_hadamard_f16 (warp34_cuda.h:945-947,
+ * op_norms_rope_act.cu:805-851, :2032-2056): out = fp16(attn_out * sigmoid(gate)), the second
+ * followed by the Hadamard-64; rows with valid_token_mask == 0 are skipped; out may alias
+ * attn_out.  total_dim must be a multiple of 64 for the Hadamard variant.
+ */
+int warp34_apply_attn_output_gate_f16(const warp34_exec* ex, const void* attn_out, const void* gate, void* out,
+                                      const uint8_t* valid_token_mask, int num_tokens, int total_dim);
+int warp34_apply_attn_output_gate_hadamard_f16(const warp34_exec* ex, const void* attn_out, const void* gate,
+                                               void* out, const uint8_t* valid_token_mask, int num_tokens,
+                                               int total_dim);
+
+/*
  * Uncompressed BF16 KV storage with identity transforms (the comparison arm of the TQ4 path).
  * Replace warp34_kv_cache_write_bf16 / warp34_kv_cache_write_strided_bf16 /
  * warp34_paged_attention_bf16 (warp34_cuda.h:363-368; op_kv_cache.cu:1170-1241) for

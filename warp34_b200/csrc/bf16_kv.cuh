@@ -429,6 +429,8 @@ extern "C" int warp34_paged_attention_bf16(const warp34_exec* ex, const warp34_k
     if (workers / w34::kBfWarps < grid) grid = (int)(workers / w34::kBfWarps);
 
     w34::StreamParams p;
+    p.og.gate = nullptr;
+    p.og.mode = 0;
     p.layout = *layout;
     p.batch = *batch;
     p.q_in = q_in;

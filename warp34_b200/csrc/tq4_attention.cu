@@ -80,11 +80,116 @@ __device__ __forceinline__ void store_act(void* base, size_t idx, float x, int b
 }
 
 // ---------------------------------------------------------------------------------------
+// Output epilogue.  The reference's layer multiplies the attention output by a sigmoid gate and,
+// when its o_proj weights were rotated offline, applies a 64-point Hadamard to every 64 columns
+// (warp34_apply_attn_output_gate_f16 / _hadamard_f16, op_norms_rope_act.cu:742-764, :805-851; call
+// site crates/warp34-host/src/model/forward.rs:1192-1211).  Both steps round like the two-kernel
+// sequence does: the attention output to the activation type first, the gated value again
+// before the Hadamard.
+// ---------------------------------------------------------------------------------------
+struct OutputGate {
+    const void* gate;   // [total_tokens, num_q_heads, 256] in the activation type, or null
+    int mode;           // 0 none, 1 sigmoid gate, 2 sigmoid gate then Hadamard-64 (x 1/8) per 64 columns
+};
+
+__device__ __forceinline__ float round_act(float x, int bf16) {
+    return bf16 ? __bfloat162float(__float2bfloat16_rn(x)) : __half2float(__float2half_rn(x));
+}
+
+// v[j] = column lane + 32 j of one 256-wide row (8 registers per lane of one warp).
+__device__ __forceinline__ void apply_output_gate(float (&v)[8], const OutputGate& og, size_t row_base, int lane, int io_bf16) {
+    if (og.mode == 0) return;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const float g = load_act(og.gate, row_base + lane + 32 * j, io_bf16);
+        v[j] = round_act(v[j], io_bf16) * (1.0f / (1.0f + __expf(-g)));
+    }
+    if (og.mode != 2) return;
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {   // block b = columns [64 b, 64 b + 64): index bits 0-4 = lane, bit 5 = register
+        const float x0 = round_act(v[2 * b], io_bf16), x1 = round_act(v[2 * b + 1], io_bf16);
+        float a0 = x0 + x1, a1 = x0 - x1;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const float o0 = __shfl_xor_sync(0xffffffffu, a0, d), o1 = __shfl_xor_sync(0xffffffffu, a1, d);
+            const bool up = (lane & d) != 0;
+            a0 = up ? (o0 - a0) : (a0 + o0);
+            a1 = up ? (o1 - a1) : (a1 + o1);
+        }
+        v[2 * b] = a0 * 0.125f;
+        v[2 * b + 1] = a1 * 0.125f;
+    }
+}
+
+// Stores one output row of a TQ4 layer: t[j] is column lane + 32 j after the inverse rotation,
+// before the sign diagonal.
+__device__ __forceinline__ void store_output_row(void* out, size_t row_base, float (&t)[8], int lane, int io_bf16,
+                                                 const OutputGate& og) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) t[j] = apply_sign(t[j], lane + 32 * j);
+    apply_output_gate(t, og, row_base, lane, io_bf16);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) store_act(out, row_base + lane + 32 * j, t[j], io_bf16);
+}
+
+// The two steps on their own (for layers whose attention kernel has no fused epilogue): one warp per
+// 256 columns, in place or out of place.
+__global__ void __launch_bounds__(128) attn_output_gate_kernel(const void* __restrict__ attn, const void* gate,
+                                                               void* out, const uint8_t* __restrict__ valid_token_mask,
+                                                               int num_tokens, int total_dim, int mode, int io_bf16) {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int chunks = (total_dim + 255) / 256;
+    const long long w = (long long)blockIdx.x * 4 + wid;
+    if (w >= (long long)num_tokens * chunks) return;
+    const int tok = (int)(w / chunks), c = (int)(w % chunks);
+    if (valid_token_mask != nullptr && valid_token_mask[tok] == 0) return;
+    const size_t base = (size_t)tok * total_dim + (size_t)c * 256;
+    const int cols = min(256, total_dim - c * 256);    // a multiple of 64 when mode == 2 (checked by the caller)
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = (lane + 32 * j < cols) ? load_act(attn, base + lane + 32 * j, io_bf16) : 0.0f;
+    OutputGate og;
+    og.gate = gate;
+    og.mode = mode;
+    if (cols == 256) {
+        apply_output_gate(v, og, base, lane, io_bf16);
+    } else {   // ragged tail: the gate column by column; whole 64-blocks only reach the Hadamard
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            if (lane + 32 * j < cols) {
+                const float g = load_act(gate, base + lane + 32 * j, io_bf16);
+                v[j] = round_act(v[j], io_bf16) * (1.0f / (1.0f + __expf(-g)));
+            }
+        }
+        if (mode == 2) {
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                const float x0 = round_act(v[2 * b], io_bf16), x1 = round_act(v[2 * b + 1], io_bf16);
+                float a0 = x0 + x1, a1 = x0 - x1;
+#pragma unroll
+                for (int d = 1; d < 32; d <<= 1) {
+                    const float o0 = __shfl_xor_sync(0xffffffffu, a0, d), o1 = __shfl_xor_sync(0xffffffffu, a1, d);
+                    const bool up = (lane & d) != 0;
+                    a0 = up ? (o0 - a0) : (a0 + o0);
+                    a1 = up ? (o1 - a1) : (a1 + o1);
+                }
+                v[2 * b] = a0 * 0.125f;
+                v[2 * b + 1] = a1 * 0.125f;
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        if (lane + 32 * j < cols) store_act(out, base + lane + 32 * j, v[j], io_bf16);
+    }
+}
+
+// ---------------------------------------------------------------------------------------
 // Scalar dequant-then-attend: one warp per (token, q head), fp32, any strides.
 // ---------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(128) tq4_attention_scalar_kernel(
     const warp34_kv_layer_layout layout, const warp34_attention_batch batch,
-    const void* __restrict__ q_in, void* __restrict__ attn_out, int num_q_heads, int io_bf16) {
+    const void* __restrict__ q_in, void* __restrict__ attn_out, int num_q_heads, int io_bf16, const OutputGate og) {
     __shared__ float s_x[4][kHeadDim];
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const long long row = (long long)blockIdx.x * 4 + wid;
@@ -151,8 +256,7 @@ __global__ void __launch_bounds__(128) tq4_attention_scalar_kernel(
 #pragma unroll
     for (int j = 0; j < 8; ++j) t[j] = s_x[wid][lane + 32 * j];
     wht256_lanes(t, lane);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) store_act(attn_out, row_base + lane + 32 * j, apply_sign(t[j], lane + 32 * j), io_bf16);
+    store_output_row(attn_out, row_base, t, lane, io_bf16, og);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -205,6 +309,7 @@ struct StreamParams {
     int natural;           // partials are in natural (unrotated, unscaled) coordinates: uncompressed KV
     uint32_t* qfrag;       // rotated queries as MMA fragments, written by the plan launch (or null)
     int q_groups_max;      // row groups per (request, kv head) that qfrag has room for
+    OutputGate og;         // applied by the merge kernel when it stores attn_out
 };
 
 __device__ __forceinline__ int32_t* plan_array(uint8_t* scratch, int which, int num_reqs) {
@@ -1646,8 +1751,7 @@ __global__ void __launch_bounds__(MW * 32) tq4_attention_merge_kernel(const Stre
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] *= inv_l;
     wht256_lanes(acc, lane);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) store_act(p.attn_out, out_base + lane + 32 * j, apply_sign(acc[j], lane + 32 * j), p.io_bf16);
+    store_output_row(p.attn_out, out_base, acc, lane, p.io_bf16, p.og);
 }
 
 // Cross-shard merge: parts is [num_parts][rows][258]; one warp per row.
@@ -1923,7 +2027,9 @@ static size_t stream_scratch_bytes(const warp34_kv_layer_layout* l, const warp34
 namespace w34 {
 static int launch_scalar(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
                          const warp34_attention_batch* batch, const void* q_in, void* attn_out,
-                         int num_q_heads, int io_bf16);
+                         int num_q_heads, int io_bf16, const OutputGate* og = nullptr);
+static int launch_output_gate(const warp34_exec* ex, const void* attn, const void* gate, void* out,
+                              const uint8_t* valid_token_mask, int num_tokens, int total_dim, int mode, int io_bf16);
 }
 
 extern "C" int warp34_paged_attention_scalar_f16(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
@@ -1932,14 +2038,32 @@ extern "C" int warp34_paged_attention_scalar_f16(const warp34_exec* ex, const wa
     return w34::launch_scalar(ex, layout, batch, q_in, attn_out, num_q_heads, 0);
 }
 
+static int w34::launch_output_gate(const warp34_exec* ex, const void* attn, const void* gate, void* out,
+                                   const uint8_t* valid_token_mask, int num_tokens, int total_dim, int mode,
+                                   int io_bf16) {
+    if (ex == nullptr || attn == nullptr || gate == nullptr || out == nullptr) return (int)cudaErrorInvalidValue;
+    if (mode == 2 && (total_dim & 63) != 0) return (int)cudaErrorInvalidValue;
+    if ((((uintptr_t)attn | (uintptr_t)gate | (uintptr_t)out) & 1u) != 0u) return (int)cudaErrorInvalidValue;
+    if (num_tokens <= 0 || total_dim <= 0) return 0;
+    const long long warps = (long long)num_tokens * ((total_dim + 255) / 256);
+    if ((warps + 3) / 4 > 0x7fffffffll) return (int)cudaErrorInvalidValue;
+    w34::attn_output_gate_kernel<<<(unsigned)((warps + 3) / 4), 128, 0, (cudaStream_t)ex->stream>>>(
+        attn, gate, out, valid_token_mask, num_tokens, total_dim, mode, io_bf16);
+    return (int)cudaGetLastError();
+}
+
 static int w34::launch_scalar(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
                               const warp34_attention_batch* batch, const void* q_in, void* attn_out,
-                              int num_q_heads, int io_bf16) {
+                              int num_q_heads, int io_bf16, const OutputGate* og) {
     if (ex == nullptr || layout == nullptr || batch == nullptr || q_in == nullptr || attn_out == nullptr) {
         return (int)cudaErrorInvalidValue;
     }
     if (batch->total_tokens <= 0 || num_q_heads <= 0) return 0;
+    w34::OutputGate none;
+    none.gate = nullptr;
+    none.mode = 0;
     if (w34::kv8_attention_layout_ok(layout)) {
+        if (og != nullptr && og->mode != 0) return (int)cudaErrorNotSupported;   // callers gate these layers in a second step
         return w34::launch_kv8_attention(ex, layout, batch, q_in, attn_out, num_q_heads, io_bf16);
     }
     if (!w34::tq4_layout_ok(layout)) return (int)cudaErrorNotSupported;
@@ -1947,7 +2071,7 @@ static int w34::launch_scalar(const warp34_exec* ex, const warp34_kv_layer_layou
     const long long rows = (long long)batch->total_tokens * num_q_heads;
     const unsigned blocks = (unsigned)((rows + 3) / 4);
     w34::tq4_attention_scalar_kernel<<<blocks, 128, 0, (cudaStream_t)ex->stream>>>(
-        *layout, *batch, q_in, attn_out, num_q_heads, io_bf16);
+        *layout, *batch, q_in, attn_out, num_q_heads, io_bf16, og != nullptr ? *og : none);
     return (int)cudaGetLastError();
 }
 
@@ -1984,15 +2108,23 @@ static bool takes_prefill_path(uint64_t flags, const warp34_kv_layer_layout* l,
 // prefill kernel, 2 = the tcgen05 prefill kernel.
 static int launch_attention(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
                             const warp34_attention_batch* batch, const void* q_in, void* attn_out,
-                            float* triple_out, int num_q_heads, int io_bf16 = 0, int force = -1) {
+                            float* triple_out, int num_q_heads, int io_bf16 = 0, int force = -1,
+                            const OutputGate* gate = nullptr) {
+    OutputGate og;
+    og.gate = gate != nullptr ? gate->gate : nullptr;
+    og.mode = gate != nullptr ? gate->mode : 0;
+    if (og.mode != 0 && (triple_out != nullptr || og.gate == nullptr)) return (int)cudaErrorInvalidValue;
     if (ex == nullptr || layout == nullptr || batch == nullptr || q_in == nullptr ||
         (attn_out == nullptr && triple_out == nullptr)) {
         return (int)cudaErrorInvalidValue;
     }
     if (batch->total_tokens <= 0 || num_q_heads <= 0) return 0;
-    if (kv8_attention_layout_ok(layout)) {   // unrotated 8-bit boundary layers
+    if (kv8_attention_layout_ok(layout)) {   // unrotated 8-bit boundary layers: the epilogue is a second launch, in place
         if (triple_out != nullptr) return (int)cudaErrorNotSupported;
-        return launch_kv8_attention(ex, layout, batch, q_in, attn_out, num_q_heads, io_bf16);
+        const int rc8 = launch_kv8_attention(ex, layout, batch, q_in, attn_out, num_q_heads, io_bf16);
+        if (rc8 != 0 || og.mode == 0) return rc8;
+        return launch_output_gate(ex, attn_out, og.gate, attn_out, batch->valid_token_mask, batch->total_tokens,
+                                  num_q_heads * kHeadDim, og.mode, io_bf16);
     }
     if (!tq4_layout_ok(layout)) return (int)cudaErrorNotSupported;
     if (num_q_heads % layout->local_kv_heads != 0 || batch->num_reqs <= 0) return (int)cudaErrorInvalidValue;
@@ -2030,6 +2162,7 @@ static int launch_attention(const warp34_exec* ex, const warp34_kv_layer_layout*
             tp.tok_per_tile = kTcRows / gqa;
             tp.q_scale = batch->sm_scale * 1.4426950408889634f;
             tp.status = status;
+            tp.og = og;
             const long long tiles = (long long)batch->total_tokens / tp.tok_per_tile + batch->num_reqs;
             if (tiles > 0x7fffffffll) return (int)cudaErrorInvalidValue;
             const dim3 grid((unsigned)tiles, (unsigned)layout->local_kv_heads);
@@ -2048,6 +2181,7 @@ static int launch_attention(const warp34_exec* ex, const warp34_kv_layer_layout*
         pp.q_scale = batch->sm_scale * 1.4426950408889634f / kLutScale;
         pp.status = status;
         pp.smem_bytes = (uint32_t)dev->smem_optin;
+        pp.og = og;
         const long long tiles = (long long)batch->total_tokens / pp.tok_per_tile + batch->num_reqs;
         if (tiles > 0x7fffffffll) return (int)cudaErrorInvalidValue;
         const dim3 grid((unsigned)tiles, (unsigned)layout->local_kv_heads);
@@ -2088,7 +2222,7 @@ static int launch_attention(const warp34_exec* ex, const warp34_kv_layer_layout*
     }
     if (!stream) {
         if (triple_out != nullptr) return (int)cudaErrorNotSupported;
-        return launch_scalar(ex, layout, batch, q_in, attn_out, num_q_heads, io_bf16);
+        return launch_scalar(ex, layout, batch, q_in, attn_out, num_q_heads, io_bf16, &og);
     }
 
     StreamParams p;
@@ -2106,6 +2240,7 @@ static int launch_attention(const warp34_exec* ex, const warp34_kv_layer_layout*
     p.rows_per_group = rpg;
     p.q_scale = batch->sm_scale * 1.4426950408889634f / kLutScale;
     p.natural = 0;
+    p.og = og;
     p.qfrag = (nt == 1) ? reinterpret_cast<uint32_t*>(p.scratch + plan + (size_t)p.max_slots * slot_bytes) : nullptr;
     cudaStream_t st = (cudaStream_t)ex->stream;
     const size_t smem = (size_t)dev->smem_optin;
@@ -2224,6 +2359,30 @@ extern "C" int warp34_paged_attention_f16_static_scratch(uintptr_t stream, const
     const int rc = w34::static_scratch_address(&ex.scratch_ptr);
     if (rc != 0) return rc;
     return w34::launch_attention(&ex, layout, batch, q_in, attn_out, nullptr, num_q_heads);
+}
+
+// ---- attention with the layer's output epilogue folded in ---------------------------------------
+extern "C" int warp34_paged_attention_gated_f16(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
+                                                const warp34_attention_batch* batch, const void* q_in,
+                                                const void* gate, void* out, int num_q_heads, int hadamard64) {
+    if (out == nullptr || gate == nullptr) return (int)cudaErrorInvalidValue;
+    w34::OutputGate og;
+    og.gate = gate;
+    og.mode = hadamard64 ? 2 : 1;
+    return w34::launch_attention(ex, layout, batch, q_in, out, nullptr, num_q_heads, 0, -1, &og);
+}
+
+// The two steps on their own, with the reference's names and signatures (warp34_cuda.h:297-300, :945-947).
+extern "C" int warp34_apply_attn_output_gate_f16(const warp34_exec* ex, const void* attn_out, const void* gate,
+                                                 void* out, const uint8_t* valid_token_mask, int num_tokens,
+                                                 int total_dim) {
+    return w34::launch_output_gate(ex, attn_out, gate, out, valid_token_mask, num_tokens, total_dim, 1, 0);
+}
+
+extern "C" int warp34_apply_attn_output_gate_hadamard_f16(const warp34_exec* ex, const void* attn_out, const void* gate,
+                                                          void* out, const uint8_t* valid_token_mask, int num_tokens,
+                                                          int total_dim) {
+    return w34::launch_output_gate(ex, attn_out, gate, out, valid_token_mask, num_tokens, total_dim, 2, 0);
 }
 
 extern "C" int warp34_static_scratch_status(int32_t* status_out) {

@@ -43,6 +43,7 @@ struct PrefillExactParams {
     float q_scale;         // sm_scale * log2(e) / kLutScale
     int32_t* status;       // may be null; bit 0: a wait gave up, bit 1: shared-memory window too small
     uint32_t smem_bytes;
+    OutputGate og;
 };
 
 __device__ __forceinline__ uint4 lds128_v(uint32_t addr) {
@@ -573,8 +574,7 @@ __global__ void __launch_bounds__(kPxWarps * 32, 1) tq4_attention_prefill_exact_
             for (int j = 0; j < 8; ++j) tv[j] = ostage[rr * kHeadDim + lane + 32 * j];
             wht256_lanes(tv, lane);
             const size_t out_base = ((size_t)(g.q_start + q_off) * p.num_q_heads + q_head) * kHeadDim;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) store_act(p.attn_out, out_base + lane + 32 * j, apply_sign(tv[j], lane + 32 * j), p.io_bf16);
+            store_output_row(p.attn_out, out_base, tv, lane, p.io_bf16, p.og);
         }
     }
 }

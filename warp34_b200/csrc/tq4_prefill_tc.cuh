@@ -180,6 +180,7 @@ struct PrefillTcParams {
     int tok_per_tile;      // 128 / gqa
     float q_scale;         // sm_scale * log2(e)
     int32_t* status;       // may be null; bit 2 is set when a wait gave up
+    OutputGate og;
 };
 
 __global__ void __launch_bounds__(kTcThreads, 1) tq4_attention_prefill_tc_kernel(const PrefillTcParams p) {
@@ -623,8 +624,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) tq4_attention_prefill_tc_kernel
         for (int j = 0; j < 8; ++j) tv[j] = has ? stage[row * kTcStageStride + lane + 32 * j] : 0.0f;
         wht256_lanes(tv, lane);
         const size_t out_base = ((size_t)(g.q_start + q_off) * p.num_q_heads + q_head) * kHeadDim;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) store_act(p.attn_out, out_base + lane + 32 * j, apply_sign(tv[j], lane + 32 * j), p.io_bf16);
+        store_output_row(p.attn_out, out_base, tv, lane, p.io_bf16, p.og);
     }
 }
 

@@ -365,6 +365,15 @@ def paged_attention(ex, layer, batch, q, out, num_q_heads, lib=None, scalar=Fals
     _check(rc, "warp34_paged_attention_f16")
 
 
+def paged_attention_gated(ex, layer, batch, q, gate, out, num_q_heads, hadamard64=False, lib=None):
+    """warp34_paged_attention_gated_f16: attention, sigmoid output gate and (optionally) the
+    Hadamard-64 pre-rotation of o_proj's input in one call."""
+    lib = lib or ffi.kernels()
+    rc = lib.warp34_paged_attention_gated_f16(C.byref(ex.ex), C.byref(layer.layout), C.byref(batch.desc), q.data_ptr(),
+                                              gate.data_ptr(), out.data_ptr(), num_q_heads, 1 if hadamard64 else 0)
+    _check(rc, "warp34_paged_attention_gated_f16")
+
+
 BF16_KV_FORMATS = (ffi.KV_FORMAT_BF16, ffi.KV_FORMAT_BF16, ffi.KV_TRANSFORM_IDENTITY, ffi.KV_TRANSFORM_IDENTITY)
 
 
