@@ -2,10 +2,14 @@
 C ABI.  Append: bit-exact against the reference's own kernels when oracle/_ref travelled with the
 repository, and against the CPU restatement (oracle/kv8.py) up to one quantisation step on a few
 codes (the restatement divides exactly, the kernels use the fast reciprocal).  Attention:
-|a-b| <= 2e-3 + 1e-2|b| against float64 dequant-then-attend over the stored bytes (which are the
-reference's bytes).  The reference's attention kernels are not called on these layers: driven
-through the C ABI with the layouts its own policy produces they returned non-finite output and,
-for one geometry, an illegal memory access.  Formats and policies: crates/warp34-host/src/cache.rs:62-108."""
+|a-b| <= 2e-3 + 1e-2|b| against the reference's own scalar dequant-then-attend kernel
+(warp34_paged_attention_scalar_f16 -> paged_attention_kernel<__half> with read_kv_elem,
+op_kv_cache.cu:288-322, :373-792, :1244) run on the same pool, which also pins the float64
+restatement of the decode (oracle/kv8.py).  The reference's tensor-core dispatcher
+(warp34_paged_attention_f16, op_paged_attn.cu:1266) is NOT called on these layers: in an earlier run
+it returned non-finite output and, for one geometry, an illegal memory access, and reading its
+dispatcher, row decoder and 16-row kernel against the descriptors passed here did not show why.
+Formats and policies: crates/warp34-host/src/cache.rs:62-108."""
 import ctypes as C
 
 import numpy as np
@@ -140,7 +144,7 @@ def _dequant_then_attend(env, wl, fmt, ctx, q_lens, q, hq, hkv):
 
 @pytest.mark.parametrize("fmt_name", ["q8_0", "fp8_e4m3"])
 @pytest.mark.parametrize("hq,hkv,q_len", [(24, 4, 1), (16, 4, 3), (8, 8, 1)])
-def test_attention_over_8bit_rows_matches_dequant_then_attend(env, fmt_name, hq, hkv, q_len):
+def test_attention_over_8bit_rows_matches_dequant_then_attend(env, fmt_name, hq, hkv, q_len, request):
     ffi, kv, synth = env["ffi"], env["kv"], env["synth"]
     fmt = ffi.KV_FORMAT_Q8_0 if fmt_name == "q8_0" else ffi.KV_FORMAT_FP8_E4M3
     ctx = [257, 40, 16, 1000]
@@ -164,6 +168,21 @@ def test_attention_over_8bit_rows_matches_dequant_then_attend(env, fmt_name, hq,
     kv.paged_attention(env["ex"], wl.layer, b, q.cuda(), out2, hq, scalar=True)
     torch.cuda.synchronize()
     assert torch.equal(out.view(torch.int16), out2.view(torch.int16))
+    # The pin: the reference's scalar kernel (fp32, read_kv_elem) over the same bytes.  This library's
+    # output must sit inside the plain bound of it, and so must the float64 restatement, which the
+    # tests of the 8-bit path lean on when the reference library is absent.
+    try:
+        ref = request.getfixturevalue("ref_lib")
+    except pytest.skip.Exception:
+        return
+    out3 = torch.zeros_like(out)
+    kv.paged_attention(env["ex"], wl.layer, b, q.cuda(), out3, hq, lib=ref, scalar=True)
+    torch.cuda.synchronize()
+    r = out3.float().cpu().numpy()
+    assert np.isfinite(r).all()
+    assert np.all(np.abs(got - r) <= ATOL + RTOL * np.abs(r)), float(np.abs(got - r).max())
+    # the restatement against the reference, fp16 output rounding aside
+    assert np.all(np.abs(want - r) <= 2.0 ** -10 * np.abs(r) + 2e-4), float(np.abs(want - r).max())
 
 
 def test_8bit_layers_refuse_what_they_do_not_cover(env):
