@@ -160,6 +160,28 @@ int warp34_kv_cache_write_strided(const warp34_exec* ex, const warp34_kv_layer_l
                                   int k_row_stride, int v_row_stride);
 
 /*
+ * The layer's K producer fused in front of the append (additive): per-head Gemma RMS norm
+ * (weight 1 + w) and partial interleaved 3-D mRoPE of the K rows, then the TQ4 rotate /
+ * quantise / pack / scale-write, in one kernel; V rows are appended as they are.  Replaces,
+ * for the K and V half of the layer, the pair
+ *   warp34_fused_qk_rmsnorm_rope_gate_strided_f16   (warp34_cuda.h:264-287, op_norms_rope_act.cu:524-680)
+ *   warp34_kv_cache_write_strided                   (warp34_cuda.h:357-360)
+ * at the reference's call site crates/warp34-host/src/model/forward.rs:1109-1149, and saves the
+ * round trip of the fp16 K rows through HBM (the reference has such a fused kernel for another
+ * KV family only: warp34_dflash_qk_norm_rope_kv_write_bf16_f32_table, warp34_cuda.h:625-628).
+ * The Q half of the producer stays the caller's (the reference kernel with num_kv_heads = 0).
+ * k_in / v_in are row slices of the packed QKV activation (strides in elements), k_norm_w is
+ * fp16 [256], positions is int32 [3 planes][pos_plane_stride]; the remaining arguments are
+ * those of the reference's producer.  The packed bytes equal those of the two-kernel sequence.
+ * TQ4 layers, fp16 activations, rotary_dim a multiple of 16 (cudaErrorNotSupported otherwise).
+ */
+int warp34_fused_k_rmsnorm_rope_kv_cache_write_f16(
+    const warp34_exec* ex, const warp34_kv_layer_layout* layout, const warp34_attention_batch* batch,
+    const void* k_in, const void* v_in, const void* k_norm_w, const int32_t* positions, int pos_plane_stride,
+    int rotary_dim, int mrope_s0, int mrope_s1, int mrope_s2, int k_row_stride, int v_row_stride,
+    float rope_theta, float rms_eps);
+
+/*
  * Paged attention over the pool: q_in and attn_out are fp16
  * [total_tokens, num_q_heads, head_dim].  Replaces warp34_paged_attention_f16
  * (warp34_cuda.h:370-373, op_paged_attn.cu:1266-1448).  Split-KV partials

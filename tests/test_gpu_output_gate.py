@@ -5,8 +5,7 @@ crates/warp34-kernels/csrc/ops/op_norms_rope_act.cu:742-764, :805-851).
 
 Oracle: attention by the CPU oracle, then the gate (and the Hadamard-64 per 64 columns) in numpy with
 the two-kernel sequence's roundings.  The stand-alone steps are also compared with the reference's
-own kernels when oracle/_ref was built with them (it is not: those kernels live in a unit outside the
-path, so numpy stands alone)."""
+own kernels when oracle/_ref holds them (oracle/build_ref.sh compiles op_norms_rope_act.cu as well)."""
 import ctypes as C
 
 import numpy as np
@@ -122,3 +121,24 @@ def test_stand_alone_gate_steps(env, hadamard, total_dim):
     assert (d2 <= 2e-3 + 2.0 ** -10 * np.abs(want[live])).all()
     if hadamard:
         assert fn(C.byref(env["ex"].ex), a_dev.data_ptr(), g_dev.data_ptr(), out.data_ptr(), None, t, 100) == 1
+    # the reference's own kernels on the same inputs (when its unit was built into oracle/_ref): equal
+    # up to the last place of fp16 (it divides and exponentiates with the fast-math variants)
+    import oracle
+    path = oracle.ref_lib_path()
+    ref = C.CDLL(path) if path else None
+    name = "warp34_apply_attn_output_gate_hadamard_f16" if hadamard else "warp34_apply_attn_output_gate_f16"
+    if ref is None or not hasattr(ref, name):
+        return
+    rfn = getattr(ref, name)
+    rfn.restype = C.c_int
+    rfn.argtypes = [C.c_void_p] * 5 + [C.c_int, C.c_int]
+    out_r = torch.full((t, total_dim), 0, dtype=torch.int16, device="cuda")
+    out_r.fill_(0x5500)
+    a2 = attn.cuda()
+    assert rfn(C.addressof(env["ex"].ex), a2.data_ptr(), g_dev.data_ptr(), out_r.data_ptr(), mask.data_ptr(), t, total_dim) == 0
+    torch.cuda.synchronize()
+    rb = out_r.cpu().numpy().view(np.uint16)
+    assert (rb[5] == 0x5500).all()
+    mine, theirs = f16(bits)[live], f16(rb)[live]
+    assert np.abs(mine - theirs).max() <= 2.0 ** -10 * np.abs(theirs).max() + 1e-6
+    assert (bits[live] == rb[live]).mean() > 0.98

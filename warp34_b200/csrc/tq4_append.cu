@@ -104,16 +104,108 @@ struct AppendParams {
     int k_row_stride;
     int v_row_stride;
     int total_rows;  // total_tokens * local_kv_heads * 2
+    // producer fused in front of the K rows (PRODUCER builds only)
+    const uint16_t* k_norm_w;   // fp16 [256]
+    const int32_t* positions;   // [planes][pos_plane_stride]
+    int pos_plane_stride;
+    int rotary_dim;
+    int mrope_s1, mrope_s2;
+    float rope_theta;
+    float rms_eps;
 };
+
+// Accurate libdevice routines, by name, as the reference's producer calls them
+// (op_norms_rope_act.cu:14-16): -use_fast_math must not swap them for the approximate ones.
+extern "C" __device__ float __nv_sinf(float);
+extern "C" __device__ float __nv_cosf(float);
+extern "C" __device__ float __nv_powf(float, float);
+
+// The producer of the reference's layer, K half: per-head Gemma RMS norm (weight 1 + w) and partial
+// interleaved 3-D mRoPE (fused_qk_rmsnorm_rope_gate_f16_kernel, op_norms_rope_act.cu:524-680), on a row
+// held as x[r] = column sub + 8 r by the 8 lanes of a row group, returning the fp16 values that
+// kernel would have written to k_out, so that the packed bytes are the same as those of the
+// two-kernel sequence.  Arithmetic order is the reference's:
+//  * sum of squares: its thread t adds the squares of columns 8 t .. 8 t + 7 in order, as a chain of
+//    fused multiply-adds from 0 (here: register t passed down the 8 lanes), then a 32-wide xor
+//    butterfly (here: in the registers of the last lane);
+//  * x * inv_rms, then * (1 + w), each rounded, then to fp16;
+//  * angle = position * (1 / powf(theta, 2 i / rotary_dim)), sine and cosine rounded to fp16.
+// Every lane of the warp takes part (the chain uses shuffles); the caller keeps the result for K
+// rows only.  rotary_dim / 2 must be a multiple of 8 so that both elements of a rotated pair sit in
+// one lane.
+__device__ __forceinline__ void k_producer(float (&x)[32], int sub, int lane_base, int tok, const AppendParams& p,
+                                           const float* s_w1, const float* s_inv_freq) {
+    float part[32];
+#pragma unroll
+    for (int r = 0; r < 32; ++r) part[r] = __fmaf_rn(x[r], x[r], 0.0f);
+#pragma unroll
+    for (int step = 1; step < 8; ++step) {
+#pragma unroll
+        for (int r = 0; r < 32; ++r) {
+            const float in = __shfl_up_sync(0xffffffffu, part[r], 1, 8);
+            part[r] = __fmaf_rn(x[r], x[r], in);
+        }
+    }
+    // lane 7 of the group now holds the reference's 32 per-thread sums; its butterfly 16, 8, 4, 2, 1
+#pragma unroll
+    for (int h = 16; h > 0; h >>= 1) {
+#pragma unroll
+        for (int r = 0; r < 16; ++r) {
+            if (r < h) part[r] = __fadd_rn(part[r], part[r + h]);
+        }
+    }
+    const float sum_sq = __shfl_sync(0xffffffffu, part[0], lane_base + 7);
+    const float inv_rms = rsqrtf(sum_sq / (float)kHeadDim + p.rms_eps);
+#pragma unroll
+    for (int r = 0; r < 32; ++r) {
+        const float v = __fmul_rn(x[r], inv_rms);
+        x[r] = __half2float(__float2half(__fmul_rn(v, s_w1[sub + 8 * r])));
+    }
+    const int half_rot = p.rotary_dim >> 1;
+    const int regs = half_rot >> 3;
+#pragma unroll
+    for (int r = 0; r < 16; ++r) {
+        if (r < regs) {
+            const int i = sub + 8 * r;
+            int plane = 0;
+            if ((i % 3) == 1 && i < p.mrope_s1 * 3) {
+                plane = 1;
+            } else if ((i % 3) == 2 && i < p.mrope_s2 * 3) {
+                plane = 2;
+            }
+            const float pos = (float)p.positions[(size_t)plane * p.pos_plane_stride + tok];
+            const float angle = pos * s_inv_freq[i];
+            float sin_a = __nv_sinf(angle);
+            float cos_a = __nv_cosf(angle);
+            sin_a = __half2float(__float2half_rn(sin_a));
+            cos_a = __half2float(__float2half_rn(cos_a));
+            const float x1 = x[r];
+            const float x2 = x[r + regs];
+            x[r] = __half2float(__float2half(x1 * cos_a - x2 * sin_a));
+            x[r + regs] = __half2float(__float2half(x2 * cos_a + x1 * sin_a));
+        }
+    }
+}
 
 constexpr int kAppendBlocksPerSm = 5;   // 4, 6 and 8 measured within 3 % of it on a 32 768-token append
 
 // IN_BF16: activations are bf16 instead of fp16.  Values that both types can hold encode to the
 // same bytes; bf16 values beyond the fp16 range are simply larger fp32 inputs.
-template <bool IN_BF16>
-__global__ void __launch_bounds__(128, kAppendBlocksPerSm) tq4_append_kernel(const AppendParams p) {
+// PRODUCER: K rows go through k_producer() first (fp16 activations only).
+template <bool IN_BF16, bool PRODUCER>
+__global__ void __launch_bounds__(128, PRODUCER ? 3 : kAppendBlocksPerSm) tq4_append_kernel(const AppendParams p) {
     __shared__ float s_centroid[16];
+    __shared__ float s_w1[PRODUCER ? kHeadDim : 1];
+    __shared__ float s_inv_freq[PRODUCER ? kHeadDim / 2 : 1];
     if (threadIdx.x < 16) s_centroid[threadIdx.x] = tq4_centroid(threadIdx.x);
+    if (PRODUCER) {
+        for (int i = threadIdx.x; i < kHeadDim; i += blockDim.x) {
+            s_w1[i] = 1.0f + __half2float(__ushort_as_half(p.k_norm_w[i]));
+        }
+        for (int i = threadIdx.x; i < (p.rotary_dim >> 1); i += blockDim.x) {
+            s_inv_freq[i] = __fdiv_rn(1.0f, __nv_powf(p.rope_theta, (float)(2 * i) / (float)p.rotary_dim));
+        }
+    }
     __syncthreads();
 
     const int lane = threadIdx.x & 31;
@@ -181,7 +273,18 @@ __global__ void __launch_bounds__(128, kAppendBlocksPerSm) tq4_append_kernel(con
     for (int r = 0; r < 32; ++r) {
         const uint16_t raw = active ? src[sub + 8 * r] : (uint16_t)0;
         const float x = IN_BF16 ? __uint_as_float((uint32_t)raw << 16) : __half2float(__ushort_as_half(raw));
-        v[r] = __uint_as_float(__float_as_uint(x) ^ ((sign_word << (31 - r)) & 0x80000000u));
+        v[r] = PRODUCER ? x : __uint_as_float(__float_as_uint(x) ^ ((sign_word << (31 - r)) & 0x80000000u));
+    }
+    if (PRODUCER) {
+        float kx[32];
+#pragma unroll
+        for (int r = 0; r < 32; ++r) kx[r] = v[r];
+        k_producer(kx, sub, lane_base, tok, p, s_w1, s_inv_freq);
+#pragma unroll
+        for (int r = 0; r < 32; ++r) {
+            const float x = (which == 0) ? kx[r] : v[r];
+            v[r] = __uint_as_float(__float_as_uint(x) ^ ((sign_word << (31 - r)) & 0x80000000u));
+        }
     }
 
     // ---- WHT-256: stages 1,2,4 across lanes, 8..128 in registers ----------------------
@@ -347,15 +450,29 @@ static int launch_append_kv8(const warp34_exec* ex, const warp34_kv_layer_layout
     return (int)cudaGetLastError();
 }
 
+struct KProducer {
+    const void* k_norm_w;
+    const int32_t* positions;
+    int pos_plane_stride, rotary_dim, mrope_s1, mrope_s2;
+    float rope_theta, rms_eps;
+};
+
 static int launch_append(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
                          const warp34_attention_batch* batch, const void* k_in, const void* v_in,
-                         int k_row_stride, int v_row_stride, bool in_bf16) {
+                         int k_row_stride, int v_row_stride, bool in_bf16, const KProducer* producer = nullptr) {
     if (ex == nullptr || layout == nullptr || batch == nullptr || k_in == nullptr || v_in == nullptr) {
         return (int)cudaErrorInvalidValue;
     }
+    if (producer != nullptr) {
+        if (producer->k_norm_w == nullptr || producer->positions == nullptr) return (int)cudaErrorInvalidValue;
+        // both elements of a rotated pair must sit in one lane: rotary_dim / 2 a multiple of 8
+        if (producer->rotary_dim < 0 || producer->rotary_dim > kHeadDim || (producer->rotary_dim & 15) != 0) {
+            return (int)cudaErrorNotSupported;
+        }
+    }
     if (batch->total_tokens <= 0 || layout->local_kv_heads <= 0) return 0;
     if (kv8_layout_ok(layout)) {
-        if (in_bf16) return (int)cudaErrorNotSupported;
+        if (in_bf16 || producer != nullptr) return (int)cudaErrorNotSupported;
         return launch_append_kv8(ex, layout, batch, k_in, v_in, k_row_stride, v_row_stride);
     }
     if (layout->head_dim != kHeadDim || layout->block_size != kPageTokens ||
@@ -399,12 +516,27 @@ static int launch_append(const warp34_exec* ex, const warp34_kv_layer_layout* la
         }
         if (sm_count_cache[dev] > 0) sms = sm_count_cache[dev];
     }
-    const long long resident = (long long)sms * kAppendBlocksPerSm;
+    const long long resident = (long long)sms * (producer != nullptr ? 3 : kAppendBlocksPerSm);
     const unsigned blocks = (unsigned)(blocks_needed < resident ? blocks_needed : resident);
-    if (in_bf16) {
-        tq4_append_kernel<true><<<blocks, 128, 0, (cudaStream_t)ex->stream>>>(p);
+    p.k_norm_w = nullptr;
+    p.positions = nullptr;
+    p.pos_plane_stride = p.rotary_dim = p.mrope_s1 = p.mrope_s2 = 0;
+    p.rope_theta = p.rms_eps = 0.0f;
+    if (producer != nullptr) {
+        if (in_bf16) return (int)cudaErrorNotSupported;
+        p.k_norm_w = static_cast<const uint16_t*>(producer->k_norm_w);
+        p.positions = producer->positions;
+        p.pos_plane_stride = producer->pos_plane_stride;
+        p.rotary_dim = producer->rotary_dim;
+        p.mrope_s1 = producer->mrope_s1;
+        p.mrope_s2 = producer->mrope_s2;
+        p.rope_theta = producer->rope_theta;
+        p.rms_eps = producer->rms_eps;
+        tq4_append_kernel<false, true><<<blocks, 128, 0, (cudaStream_t)ex->stream>>>(p);
+    } else if (in_bf16) {
+        tq4_append_kernel<true, false><<<blocks, 128, 0, (cudaStream_t)ex->stream>>>(p);
     } else {
-        tq4_append_kernel<false><<<blocks, 128, 0, (cudaStream_t)ex->stream>>>(p);
+        tq4_append_kernel<false, false><<<blocks, 128, 0, (cudaStream_t)ex->stream>>>(p);
     }
     return (int)cudaGetLastError();
 }
@@ -414,6 +546,27 @@ extern "C" int warp34_kv_cache_write_strided(const warp34_exec* ex, const warp34
                                              const warp34_attention_batch* batch, const void* k_in,
                                              const void* v_in, int k_row_stride, int v_row_stride) {
     return w34::launch_append(ex, layout, batch, k_in, v_in, k_row_stride, v_row_stride, false);
+}
+
+// K-norm + RoPE + rotate / quantise / pack in one kernel: the K half of the reference's
+// warp34_fused_qk_rmsnorm_rope_gate_strided_f16 followed by its warp34_kv_cache_write_strided
+// (crates/warp34-host/src/model/forward.rs:1109-1149), without the fp16 K rows going through HBM.
+extern "C" int warp34_fused_k_rmsnorm_rope_kv_cache_write_f16(
+    const warp34_exec* ex, const warp34_kv_layer_layout* layout, const warp34_attention_batch* batch,
+    const void* k_in, const void* v_in, const void* k_norm_w, const int32_t* positions, int pos_plane_stride,
+    int rotary_dim, int mrope_s0, int mrope_s1, int mrope_s2, int k_row_stride, int v_row_stride, float rope_theta,
+    float rms_eps) {
+    (void)mrope_s0;   // the first section needs no bound: plane 0 is the default (op_norms_rope_act.cu:640-646)
+    w34::KProducer pr;
+    pr.k_norm_w = k_norm_w;
+    pr.positions = positions;
+    pr.pos_plane_stride = pos_plane_stride;
+    pr.rotary_dim = rotary_dim;
+    pr.mrope_s1 = mrope_s1;
+    pr.mrope_s2 = mrope_s2;
+    pr.rope_theta = rope_theta;
+    pr.rms_eps = rms_eps;
+    return w34::launch_append(ex, layout, batch, k_in, v_in, k_row_stride, v_row_stride, false, &pr);
 }
 
 extern "C" int warp34_kv_cache_write(const warp34_exec* ex, const warp34_kv_layer_layout* layout,

@@ -95,6 +95,10 @@ _KERNEL_SIGS = {
     "warp34_paged_attention_f16_static_scratch": (C.c_int, [C.c_size_t, _P(KvLayerLayout), _P(AttentionBatch),
                                                              C.c_void_p, C.c_void_p, C.c_int, _P(C.c_size_t)]),
     "warp34_static_scratch_status": (C.c_int, [_P(C.c_int32)]),
+    "warp34_fused_k_rmsnorm_rope_kv_cache_write_f16": (C.c_int, [_P(Exec), _P(KvLayerLayout), _P(AttentionBatch),
+                                                                  C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int,
+                                                                  C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                                                                  C.c_float, C.c_float]),
     "warp34_paged_attention_gated_f16": (C.c_int, [_P(Exec), _P(KvLayerLayout), _P(AttentionBatch),
                                                     C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
     "warp34_apply_attn_output_gate_f16": (C.c_int, [_P(Exec), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
