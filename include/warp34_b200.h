@@ -430,6 +430,26 @@ int warp34_paged_attention_f16_static_scratch(uintptr_t stream, const warp34_kv_
  */
 int warp34_static_scratch_status(int32_t* status_out);
 
+/*
+ * Bounds-checked build (stand-in for the reference's sanitizer runs of this path,
+ * tools/check_cuda_sanitizer.py:77-102).  A library compiled with -DW34_BOUNDS
+ * (`python -m warp34_b200.build --bounds` -> libwarp34_b200_bounds.so) range-checks, in every kernel,
+ * each index into a block table against batch->max_blocks_per_req, each page id read from one and each
+ * write slot against the pool's page count, before an address is formed.  The layer descriptor does
+ * not carry that count, so the host states it once per device with warp34_bounds_set_pool_pages()
+ * (0 = unknown: only block-table indices are checked).  A violating access goes to entry 0 / page 0
+ * (reads) or is skipped (writes); nothing traps.  warp34_bounds_report() fills
+ *   out4[0] = what | where << 8   what: 1 block-table index, 2 page id, 3 write slot; 0 = no violation
+ *                                 where: 1 append, 2 fp32 attention, 3 decode stream, 4 verify team,
+ *                                        5 / 6 prefill kernels, 7 bf16 KV, 8 8-bit KV
+ *   out4[1] = the offending value, out4[2] = its limit     (of the first violation seen)
+ *   out4[3] = number of violations since the last reset
+ * and clears the record when `reset` is non-zero.  Both calls are blocking copies.  In the regular
+ * build both return cudaErrorNotSupported (801) and the checks cost nothing.
+ */
+int warp34_bounds_set_pool_pages(int32_t num_pages);
+int warp34_bounds_report(int32_t* out4, int32_t reset);
+
 /* Library identification: returns a static string "warp34_b200 <version> sm_100a". */
 const char* warp34_b200_version(void);
 

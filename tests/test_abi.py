@@ -48,6 +48,19 @@ def test_kernel_library_exports_every_declared_symbol(native_libs):
     assert kernels.warp34_b200_version().decode().endswith("sm_100a")
 
 
+def test_bounds_checked_build_exports_the_same_abi(native_libs):
+    """The -DW34_BOUNDS build is the same library with range checks compiled in: same symbols; the
+    regular build answers the two bounds calls with 801 (host-only returns, no GPU needed)."""
+    import ctypes as C
+    from warp34_b200 import build, ffi
+    blib = ffi.bind_kernel_abi(build.build_bounds())
+    for name in _declared_functions("warp34_b200.h"):
+        assert hasattr(blib, name), f"{name} missing from the bounds-checked build"
+    out = (C.c_int32 * 4)()
+    assert native_libs[0].warp34_bounds_set_pool_pages(4) == 801
+    assert native_libs[0].warp34_bounds_report(out, 0) == 801
+
+
 def test_host_library_exports_every_declared_symbol(native_libs):
     _, host = native_libs
     declared = [n for n in _declared_functions("warp34_host.h") if n.startswith("w34_")]

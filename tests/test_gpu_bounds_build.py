@@ -1,0 +1,168 @@
+"""The bounds-checked build of the kernel library (-DW34_BOUNDS, libwarp34_b200_bounds.so): the stand-in
+for the reference's sanitizer runs of this path (tools/check_cuda_sanitizer.py:77-102).
+
+ * every kernel family runs its small cases under it with the pool's page count stated: no violation
+   is recorded and the results equal the regular build's bit for bit;
+ * descriptors that point outside what the host declared are caught: the record names what, where,
+   the value and its limit, the access is redirected (reads) or skipped (writes).  The violating
+   values are only outside the DECLARED extent (a pool declared smaller than the one allocated, a
+   block table declared narrower than the array behind it), so nothing can reach unowned memory in
+   either build."""
+import ctypes as C
+import os
+
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def env(native_libs):
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    from warp34_b200 import build, ffi, kv, synth
+    path = build.build_bounds()
+    assert os.path.exists(path)
+    return dict(ffi=ffi, kv=kv, synth=synth, ex=kv.Executor(64 << 20), lib=native_libs[0],
+                blib=ffi.bind_kernel_abi(path))
+
+
+def _report(blib, reset=True):
+    out = (C.c_int32 * 4)()
+    assert blib.warp34_bounds_report(out, 1 if reset else 0) == 0
+    return dict(what=out[0] & 255, where=out[0] >> 8, value=out[1], limit=out[2], count=out[3])
+
+
+def test_regular_build_has_no_checks(env):
+    out = (C.c_int32 * 4)()
+    assert env["lib"].warp34_bounds_set_pool_pages(16) == 801
+    assert env["lib"].warp34_bounds_report(out, 0) == 801
+
+
+CASES = {
+    # name: (contexts, q_len, flags name, formats)
+    "decode": ([700, 31, 2000, 16], 1, None, None),
+    "verify": ([300, 1000], 4, None, None),
+    "verify_team": ([300, 1000], 4, "EXEC_FLAG_FAST_ATTENTION", None),
+    "chunk": ([90, 260], 70, None, None),
+    "chunk_tcgen05": ([90, 260], 70, "EXEC_FLAG_FAST_ATTENTION", None),
+    "fp32": ([500, 40], 1, "EXEC_FLAG_PRECISE_ATTENTION", None),
+    "bf16": ([400, 33], 1, None, "bf16"),
+    "fp8": ([400, 33], 1, None, "fp8"),
+    "q8": ([400, 33], 1, None, "q8"),
+}
+
+
+@pytest.mark.parametrize("name", list(CASES))
+def test_small_cases_run_clean_and_equal_the_regular_build(env, name):
+    kv, synth, ffi, blib = env["kv"], env["synth"], env["ffi"], env["blib"]
+    ctx, q_len, flag, fmt = CASES[name]
+    code = {None: None, "bf16": ffi.KV_FORMAT_BF16, "fp8": ffi.KV_FORMAT_FP8_E4M3, "q8": ffi.KV_FORMAT_Q8_0}[fmt]
+    formats = None if code is None else (code, code, ffi.KV_TRANSFORM_IDENTITY, ffi.KV_TRANSFORM_IDENTITY)
+    hq, hkv, n = 24, 4, len(ctx)
+    outs, pools = [], []
+    for lib in (env["lib"], blib):
+        wl = synth.PagedWorkload([c - q_len for c in ctx], [q_len] * n, hkv, seed=77, formats=formats)
+        if lib is blib:
+            assert blib.warp34_bounds_set_pool_pages(wl.num_pages) == 0
+            _report(blib)
+        ex = kv.Executor(64 << 20)
+        wl.fill_context(ex, 77, lib=lib)
+        b = wl.step()
+        k, v = synth.make_kv(n * q_len, hkv, 78, device="cuda")
+        q = synth.make_q(n * q_len, hq, 79).cuda()
+        ex.ex.flags = getattr(ffi, flag) if flag else 0
+        if fmt == "bf16":
+            k, v, q = k.to(torch.bfloat16), v.to(torch.bfloat16), q.to(torch.bfloat16)
+            out = torch.zeros(n * q_len, hq, 256, dtype=torch.bfloat16, device="cuda")
+            kv.kv_cache_write_bf16(ex, wl.layer, b, k, v, lib=lib)
+            kv.paged_attention_bf16kv(ex, wl.layer, b, q, out, hq, lib=lib)
+        else:
+            out = torch.zeros(n * q_len, hq, 256, dtype=torch.float16, device="cuda")
+            kv.kv_cache_write(ex, wl.layer, b, k, v, lib=lib)
+            kv.paged_attention(ex, wl.layer, b, q, out, hq, lib=lib)
+        torch.cuda.synchronize()
+        outs.append(out.view(torch.int16).cpu())
+        pools.append((wl.layer.k.cpu(), wl.layer.v.cpu()))
+    r = _report(blib)
+    assert r["count"] == 0 and r["what"] == 0, r
+    assert torch.equal(outs[0], outs[1])
+    assert torch.equal(pools[0][0], pools[1][0]) and torch.equal(pools[0][1], pools[1][1])
+    assert outs[0].numpy().any()
+
+
+def _decode_case(env, lib, seed=5):
+    kv, synth = env["kv"], env["synth"]
+    wl = synth.PagedWorkload([200, 90], [1, 1], 4, seed=seed, slack_pages=64)
+    ex = kv.Executor(64 << 20)
+    wl.fill_context(ex, seed, lib=lib)
+    return wl, ex
+
+
+def test_page_id_outside_the_declared_pool_is_recorded_and_redirected(env):
+    kv, synth, ffi, blib = env["kv"], env["synth"], env["ffi"], env["blib"]
+    assert blib.warp34_bounds_set_pool_pages(0) == 0
+    wl, ex = _decode_case(env, blib)
+    b = wl.step()
+    k, v = synth.make_kv(2, 4, 6, device="cuda")
+    kv.kv_cache_write(ex, wl.layer, b, k, v, lib=blib)
+    q = synth.make_q(2, 24, 7).cuda()
+    used = sorted({int(p) for s in wl.seqs for p in s.pages})
+    declared = used[len(used) // 2]          # every page id >= declared is now "outside the pool"
+    outside = [p for p in used if p >= declared]
+    _report(blib)
+    assert blib.warp34_bounds_set_pool_pages(declared) == 0
+    for flags, where in ((0, 3), (ffi.EXEC_FLAG_PRECISE_ATTENTION, 2)):
+        ex.ex.flags = flags
+        out = torch.zeros(2, 24, 256, dtype=torch.float16, device="cuda")
+        assert kv.paged_attention(ex, wl.layer, b, q, out, 24, lib=blib) in (0, None)
+        torch.cuda.synchronize()
+        r = _report(blib)
+        assert r["what"] == 2 and r["where"] == where and r["limit"] == declared and r["value"] in outside, r
+        assert r["count"] >= len(outside)
+        assert torch.isfinite(out.float()).all()
+    assert blib.warp34_bounds_set_pool_pages(0) == 0
+
+
+def test_write_slot_outside_the_declared_pool_is_recorded_and_skipped(env):
+    kv, synth, blib = env["kv"], env["synth"], env["blib"]
+    wl, ex = _decode_case(env, blib, seed=9)
+    b = wl.step()
+    slots = b.host["write_slot_mapping"]
+    declared = int(slots.max()) // 16            # the page of the larger slot is outside, the other inside
+    assert int(slots.min()) // 16 < declared
+    assert blib.warp34_bounds_set_pool_pages(declared) == 0
+    _report(blib)
+    before = (wl.layer.k.clone(), wl.layer.v.clone())
+    k, v = synth.make_kv(2, 4, 10, device="cuda")
+    kv.kv_cache_write(ex, wl.layer, b, k, v, lib=blib)
+    torch.cuda.synchronize()
+    r = _report(blib)
+    assert r["what"] == 3 and r["where"] == 1 and r["value"] == int(slots.max()) and r["limit"] == declared * 16, r
+    page_bytes = wl.layer.k.numel() // wl.num_pages
+    kb, ka = before[0].view(torch.uint8).view(wl.num_pages, page_bytes), wl.layer.k.view(torch.uint8).view(wl.num_pages, page_bytes)
+    changed = (kb != ka).any(dim=1).nonzero().flatten().tolist()
+    assert changed == [int(slots.min()) // 16], changed
+    assert blib.warp34_bounds_set_pool_pages(0) == 0
+
+
+def test_block_table_index_beyond_the_declared_width_is_recorded(env):
+    kv, synth, ffi, blib = env["kv"], env["synth"], env["ffi"], env["blib"]
+    wl, ex = _decode_case(env, blib, seed=11)
+    s = wl.seqs[0]
+    n_tok = 200                                   # all of them appended by the fill
+    pages = list(s.pages)                         # 13 pages behind the row
+    bt = np.asarray([pages], np.int32)
+    # the descriptor declares a 4-entry row while the sequence is 200 tokens long: entries 4..12 are
+    # outside the declared width (and inside the array that is really there)
+    b = kv.StepBatch([0, 1], [n_tok - 1], [n_tok], bt, [-1], 4, 0.0625, max_seq_len=64)
+    _report(blib)
+    ex.ex.flags = ffi.EXEC_FLAG_PRECISE_ATTENTION
+    q = synth.make_q(1, 24, 12).cuda()
+    out = torch.zeros(1, 24, 256, dtype=torch.float16, device="cuda")
+    kv.paged_attention(ex, wl.layer, b, q, out, 24, lib=blib)
+    torch.cuda.synchronize()
+    r = _report(blib)
+    assert r["what"] == 1 and r["where"] == 2 and r["limit"] == 4 and 4 <= r["value"] <= 12, r
+    assert torch.isfinite(out.float()).all()

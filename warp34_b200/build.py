@@ -81,10 +81,19 @@ def build_host(force=False):
     return target
 
 
+def build_bounds(force=False):
+    """The bounds-checked build of the kernel library (-DW34_BOUNDS): same sources, every block-table
+    index, page id and write slot range-checked, violations recorded instead of trapping."""
+    return build_cuda(force, extra_defines=("-DW34_BOUNDS",), out_name="libwarp34_b200_bounds.so")
+
+
 def build_all(force=False):
-    return build_cuda(force), build_host(force)
+    return build_cuda(force), build_host(force), build_bounds(force)
 
 
 if __name__ == "__main__":
-    for t in build_all(force="--force" in sys.argv):
-        print("built", t)
+    if "--bounds" in sys.argv:
+        print("built", build_bounds(force="--force" in sys.argv))
+    else:
+        for t in build_all(force="--force" in sys.argv):
+            print("built", t)

@@ -59,7 +59,7 @@ __global__ void __launch_bounds__(128) kv_cache_write_bf16_kernel(const warp34_k
     const int req = find_request(batch.query_start_loc, batch.num_reqs, tok);
     if (req < 0 || (batch.valid_req_mask != nullptr && batch.valid_req_mask[req] == 0)) return;
     const int slot = batch.write_slot_mapping[tok];
-    if (slot < 0) return;
+    if (slot < 0 || !write_slot_ok(slot, kInBf16)) return;
     const int page = slot >> 4, off = slot & 15;
     const uint64_t kd = layout.k_base + (uint64_t)page * layout.k_page_stride_bytes +
                         (uint64_t)head * layout.k_head_stride_bytes + (uint64_t)off * layout.k_token_stride_bytes;
@@ -188,7 +188,7 @@ __global__ void __launch_bounds__(kBfWarps * 32, 1) bf16kv_attention_stream_kern
         const uint8_t* k_head_base = (const uint8_t*)(uintptr_t)p.layout.k_base + (size_t)kv_head * p.layout.k_head_stride_bytes;
         const uint8_t* v_head_base = (const uint8_t*)(uintptr_t)p.layout.v_base + (size_t)kv_head * p.layout.v_head_stride_bytes;
         auto issue = [&](int idx) {
-            const int32_t page = blocks[pg0 + idx];
+            const int32_t page = block_table_page(blocks, pg0 + idx, p.batch.max_blocks_per_req, kInBf16);
             const uint8_t* ks = k_head_base + (size_t)page * p.layout.k_page_stride_bytes + lane * 16;
             const uint8_t* vs = v_head_base + (size_t)page * p.layout.v_page_stride_bytes + lane * 16;
             const uint32_t dst = ring + (uint32_t)(idx % kBfStages) * kBfStageBytes + lane * 16;

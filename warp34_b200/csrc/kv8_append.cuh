@@ -43,7 +43,7 @@ __global__ void __launch_bounds__(128) kv8_append_kernel(const AppendParams p) {
         if (req < 0 || p.batch.valid_req_mask[req] == 0) return;
     }
     const int slot = p.batch.write_slot_mapping[tok];
-    if (slot < 0) return;
+    if (slot < 0 || !write_slot_ok(slot, kInKv8)) return;
     const int page = slot >> 4, off = slot & 15;
     const uint16_t* src;
     uint8_t* dst;

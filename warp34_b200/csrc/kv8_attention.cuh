@@ -105,7 +105,7 @@ __global__ void __launch_bounds__(kKv8Warps * 32) kv8_attention_kernel(
         const int my_lo = p_lo + (int)blockIdx.y * chunk;
         const int my_hi = min(p_hi, my_lo + chunk - 1);
         for (int pg = my_lo + wid; pg <= my_hi; pg += kKv8Warps) {
-            const int page = blocks[pg];
+            const int page = block_table_page(blocks, pg, batch.max_blocks_per_req, kInKv8);
             const int lo = max(min_kv, pg << 4), hi = min(max_kv, (pg << 4) + 15);
             const uint8_t* kpage = (const uint8_t*)(uintptr_t)layout.k_base + (size_t)page * layout.k_page_stride_bytes +
                                    (size_t)kv_head * layout.k_head_stride_bytes;

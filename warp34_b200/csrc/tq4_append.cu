@@ -248,7 +248,7 @@ __global__ void __launch_bounds__(128, PRODUCER ? 3 : kAppendBlocksPerSm) tq4_ap
     }
     if (active) {
         slot = p.batch.write_slot_mapping[tok];
-        if (slot < 0) active = false;
+        if (slot < 0 || !write_slot_ok(slot, kInAppend)) active = false;
     }
     // All 8 lanes of a row agree on `active`; rows of a warp may differ, and every lane
     // still takes part in the shuffles below.
@@ -414,6 +414,8 @@ __global__ void __launch_bounds__(128, PRODUCER ? 3 : kAppendBlocksPerSm) tq4_ap
     }
     }  // row-quad loop
 }
+
+W34_BOUNDS_HOST_HOOKS(append)
 
 }  // namespace w34
 

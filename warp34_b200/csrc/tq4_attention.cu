@@ -226,7 +226,7 @@ __global__ void __launch_bounds__(128) tq4_attention_scalar_kernel(
     const int32_t* blocks = batch.block_tables + (size_t)req * batch.max_blocks_per_req;
     float m_i = -1e30f, l_i = 0.0f;
     for (int pos = min_kv; pos <= max_kv; ++pos) {
-        const int page = blocks[pos >> 4], off = pos & 15;
+        const int page = block_table_page(blocks, pos >> 4, batch.max_blocks_per_req, kInScalar), off = pos & 15;
         const uint8_t* kp = (const uint8_t*)(uintptr_t)layout.k_base + (size_t)page * layout.k_page_stride_bytes +
                             (size_t)kv_head * layout.k_head_stride_bytes + (size_t)off * layout.k_token_stride_bytes;
         const uint8_t* vp = (const uint8_t*)(uintptr_t)layout.v_base + (size_t)page * layout.v_page_stride_bytes +
@@ -762,8 +762,8 @@ __global__ void __launch_bounds__(WARPS * 32, 1) tq4_attention_stream_kernel(con
         const int32_t* blocks = p.batch.block_tables + (size_t)r * p.batch.max_blocks_per_req;
         const uint8_t* k_head_base = (const uint8_t*)(uintptr_t)p.layout.k_base + (size_t)kv_head * p.layout.k_head_stride_bytes;
         const uint8_t* v_head_base = (const uint8_t*)(uintptr_t)p.layout.v_base + (size_t)kv_head * p.layout.v_head_stride_bytes;
-        int32_t my_page = (lane < n_here) ? blocks[pg0 + lane] : 0;  // page ids of units [0, 32)
-        int32_t next_page = (32 + lane < n_here) ? blocks[pg0 + 32 + lane] : 0;
+        int32_t my_page = (lane < n_here) ? block_table_page(blocks, pg0 + lane, p.batch.max_blocks_per_req, kInStream) : 0;  // page ids of units [0, 32)
+        int32_t next_page = (32 + lane < n_here) ? block_table_page(blocks, pg0 + 32 + lane, p.batch.max_blocks_per_req, kInStream) : 0;
 
         fence_proxy_async();  // the staging writes above precede async-proxy writes to the ring
         auto issue = [&](int idx) {  // called by all lanes; lane 0 issues the four copies
@@ -791,7 +791,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) tq4_attention_stream_kernel(con
             // refill page-id registers every 32 units, one window ahead
             if ((i & 31) == 0 && i > 0) {
                 const int base = i + 32;  // ids for [i+32, i+64) replace the window just consumed
-                const int32_t fresh = (base + lane < n_here) ? blocks[pg0 + base + lane] : 0;
+                const int32_t fresh = (base + lane < n_here) ? block_table_page(blocks, pg0 + base + lane, p.batch.max_blocks_per_req, kInStream) : 0;
                 if (i & 32) my_page = fresh; else next_page = fresh;
             }
             {
@@ -1344,8 +1344,8 @@ __global__ void __launch_bounds__(kTeams * kTeamWarps * 32, 1) tq4_attention_tea
         const uint8_t* k_head_base = (const uint8_t*)(uintptr_t)p.layout.k_base + (size_t)kv_head * p.layout.k_head_stride_bytes;
         const uint8_t* v_head_base = (const uint8_t*)(uintptr_t)p.layout.v_base + (size_t)kv_head * p.layout.v_head_stride_bytes;
         // page ids are only needed by the issuing warp (t == 0)
-        int32_t my_page = (t == 0 && lane < n_here) ? blocks[pg0 + lane] : 0;
-        int32_t next_page = (t == 0 && 32 + lane < n_here) ? blocks[pg0 + 32 + lane] : 0;
+        int32_t my_page = (t == 0 && lane < n_here) ? block_table_page(blocks, pg0 + lane, p.batch.max_blocks_per_req, kInTeam) : 0;
+        int32_t next_page = (t == 0 && 32 + lane < n_here) ? block_table_page(blocks, pg0 + 32 + lane, p.batch.max_blocks_per_req, kInTeam) : 0;
 
         fence_proxy_async();
         auto issue = [&](int idx) {
@@ -1457,7 +1457,7 @@ __global__ void __launch_bounds__(kTeams * kTeamWarps * 32, 1) tq4_attention_tea
                 if (t == 0 && ((i - 1 + kTeamStages) & 31) == 0) {
                     // entering a new id window: the window being replaced was fully issued long ago
                     const int base = i - 1 + kTeamStages + 32;
-                    const int32_t fresh = (base + lane < n_here) ? blocks[pg0 + base + lane] : 0;
+                    const int32_t fresh = (base + lane < n_here) ? block_table_page(blocks, pg0 + base + lane, p.batch.max_blocks_per_req, kInTeam) : 0;
                     if ((i - 1 + kTeamStages) & 32) my_page = fresh; else next_page = fresh;
                 }
                 issue(i - 1 + kTeamStages);
@@ -1616,6 +1616,8 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t add
 __device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
     asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
+
+W34_BOUNDS_HOST_HOOKS(attention)
 
 }  // namespace w34
 #include "tq4_prefill_tc.cuh"

@@ -79,4 +79,57 @@ __device__ __forceinline__ int find_request(const int32_t* __restrict__ qsl, int
     return lo;
 }
 
+// ---- bounds-checked build (-DW34_BOUNDS) ----------------------------------------------------------
+// Every index into a block table, every page id read from one and every write slot is range-checked
+// before an address is formed from it.  The first violation is recorded in a device word (what, the
+// value, its limit; a count of all violations beside it) that warp34_bounds_report() reads, and the
+// access goes to entry 0 / page 0 / is skipped instead: nothing traps, the context stays usable.  The
+// layer descriptor does not carry the pool's page count, so the host states it once with
+// warp34_bounds_set_pool_pages().  Without the define these helpers cost nothing.
+enum { kBoundsBlockIndex = 1, kBoundsPageId = 2, kBoundsWriteSlot = 3 };
+enum { kInAppend = 1, kInScalar = 2, kInStream = 3, kInTeam = 4, kInPrefillExact = 5, kInPrefillTc = 6,
+       kInBf16 = 7, kInKv8 = 8 };
+#ifdef W34_BOUNDS
+struct BoundsWord { int what, value, limit, count; };
+static __device__ BoundsWord g_bounds;       // one per translation unit; the report merges them
+static __device__ int g_bounds_pool_pages;   // 0: not stated, page ids and slots are not checked
+__device__ __forceinline__ bool bounds_ok(int v, int limit, int what, int where) {
+    if ((unsigned)v < (unsigned)limit) return true;
+    if (atomicAdd(&g_bounds.count, 1) == 0) {
+        g_bounds.value = v;
+        g_bounds.limit = limit;
+        __threadfence();
+        g_bounds.what = what | (where << 8);
+    }
+    return false;
+}
+__device__ __forceinline__ int block_table_page(const int32_t* __restrict__ blocks, int idx, int max_blocks, int where) {
+    if (!bounds_ok(idx, max_blocks, kBoundsBlockIndex, where)) idx = 0;
+    int page = blocks[idx];
+    const int pages = g_bounds_pool_pages;
+    if (pages > 0 && !bounds_ok(page, pages, kBoundsPageId, where)) page = 0;
+    return page;
+}
+// false: the slot points outside the pool and the row must not be written
+__device__ __forceinline__ bool write_slot_ok(int slot, int where) {
+    const int pages = g_bounds_pool_pages;
+    return pages <= 0 || bounds_ok(slot, pages * kPageTokens, kBoundsWriteSlot, where);
+}
+#define W34_BOUNDS_HOST_HOOKS(tag)                                                                  \
+    int bounds_fetch_##tag(int32_t* out, int reset) {                                               \
+        BoundsWord w;                                                                               \
+        if (cudaMemcpyFromSymbol(&w, g_bounds, sizeof(w)) != cudaSuccess) return 1;                 \
+        out[0] = w.what; out[1] = w.value; out[2] = w.limit; out[3] = w.count;                      \
+        if (reset) { w = BoundsWord{0, 0, 0, 0}; cudaMemcpyToSymbol(g_bounds, &w, sizeof(w)); }     \
+        return 0;                                                                                   \
+    }                                                                                               \
+    int bounds_set_pages_##tag(int pages) {                                                         \
+        return cudaMemcpyToSymbol(g_bounds_pool_pages, &pages, sizeof(int)) == cudaSuccess ? 0 : 1; \
+    }
+#else
+__device__ __forceinline__ int block_table_page(const int32_t* __restrict__ blocks, int idx, int, int) { return blocks[idx]; }
+__device__ __forceinline__ bool write_slot_ok(int, int) { return true; }
+#define W34_BOUNDS_HOST_HOOKS(tag)
+#endif
+
 }  // namespace w34

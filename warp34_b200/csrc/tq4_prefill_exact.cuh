@@ -234,7 +234,7 @@ __global__ void __launch_bounds__(kPxWarps * 32, 1) tq4_attention_prefill_exact_
 
     auto issue = [&](int idx) {   // thread 0 only
         const int s = idx % kPxStages;
-        const int32_t page = blocks[pg_lo + idx];
+        const int32_t page = block_table_page(blocks, pg_lo + idx, p.batch.max_blocks_per_req, kInPrefillExact);
         const uint32_t bar = bars + 8u * s;
         const uint32_t dst = ring + (uint32_t)s * kStageStride;
         const uint8_t* ksrc = k_head_base + (size_t)page * p.layout.k_page_stride_bytes;

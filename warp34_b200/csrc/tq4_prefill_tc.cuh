@@ -404,7 +404,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) tq4_attention_prefill_tc_kernel
 #pragma unroll
             for (int pp = 0; pp < 4; ++pp) {
                 const int pg = 4 * (kb_lo + j) + pp;
-                ids[pp] = (j < nblocks && pg <= pg_hi) ? blocks[pg] : -1;
+                ids[pp] = (j < nblocks && pg <= pg_hi) ? block_table_page(blocks, pg, p.batch.max_blocks_per_req, kInPrefillTc) : -1;
             }
         };
         int32_t ids[4];
