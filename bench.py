@@ -508,7 +508,8 @@ def run_other_kv(args):
         fmt = ffi.KV_FORMAT_FP8_E4M3 if args.kv == "fp8" else ffi.KV_FORMAT_Q8_0
         formats, act = (fmt, fmt, ffi.KV_TRANSFORM_IDENTITY, ffi.KV_TRANSFORM_IDENTITY), torch.float16
         append, attend = kv.kv_cache_write, kv.paged_attention
-        kernel = "kv8_attention_kernel"
+        kernel = ("fp8kv_attention_stream_kernel (+ plan and merge)" if args.kv == "fp8" and not reference
+                  else "kv8_attention_kernel" if not reference else "reference kernels")
         label = "unrotated FP8 E4M3 rows" if args.kv == "fp8" else "unrotated Q8_0 rows"
     wl = synth.PagedWorkload([int(c) for c in ctx], [q_len] * batch, hkv, seed=seed, formats=formats)
     ex = kv.Executor(64 << 20)

@@ -160,14 +160,21 @@ def test_attention_over_8bit_rows_matches_dequant_then_attend(env, fmt_name, hq,
     out = torch.zeros(sum(q_lens), hq, 256, dtype=torch.float16, device="cuda")
     kv.paged_attention(env["ex"], wl.layer, b, q.cuda(), out, hq)
     torch.cuda.synchronize()
+    if fmt == ffi.KV_FORMAT_FP8_E4M3:   # the stream kernel's status word (no bounded wait gave up)
+        assert int(env["ex"].scratch[:4].cpu().numpy().view(np.int32)[0]) == 0
     got = out.float().cpu().numpy()
     want = _dequant_then_attend(env, wl, fmt, ctx, q_lens, q, hq, hkv)
     assert np.all(np.abs(got - want) <= ATOL + RTOL * np.abs(want)), float(np.abs(got - want).max())
-    # the scalar entry point takes the same path
+    # the scalar entry point is the fp32 dequant-then-attend kernel; Q8_0 layers take it by default too,
+    # FP8 layers take the tensor-core stream kernel (exact operands, P as value + residual)
     out2 = torch.zeros_like(out)
     kv.paged_attention(env["ex"], wl.layer, b, q.cuda(), out2, hq, scalar=True)
     torch.cuda.synchronize()
-    assert torch.equal(out.view(torch.int16), out2.view(torch.int16))
+    if fmt == ffi.KV_FORMAT_Q8_0:
+        assert torch.equal(out.view(torch.int16), out2.view(torch.int16))
+    else:
+        g2 = out2.float().cpu().numpy()
+        assert np.all(np.abs(g2 - want) <= ATOL + RTOL * np.abs(want)), float(np.abs(g2 - want).max())
     # The pin: the reference's scalar kernel (fp32, read_kv_elem) over the same bytes.  This library's
     # output must sit inside the plain bound of it, and so must the float64 restatement, which the
     # tests of the 8-bit path lean on when the reference library is absent.
@@ -194,3 +201,83 @@ def test_8bit_layers_refuse_what_they_do_not_cover(env):
     rc = env["lib"].warp34_kv_cache_write(C.byref(env["ex"].ex), C.byref(wl.layer.layout), C.byref(wl.step().desc),
                                           k.cuda().data_ptr(), v.cuda().data_ptr())
     assert rc == ffi.CUDA_ERROR_NOT_SUPPORTED
+
+
+@pytest.mark.parametrize("case", ["verify_gqa6", "chunk", "window", "masked_rows", "long_few_rows", "bf16_io"])
+def test_fp8_stream_kernel_geometries_against_the_fp32_kernel(env, case, request):
+    """The tensor-core path of FP8 layers against this library's fp32 dequant-then-attend kernel (itself
+    pinned above) and, when it travelled, the reference's scalar kernel: draft tokens with 24 query
+    rows per kv head, a prefill chunk, a sliding window, masked tokens and requests, one long sequence
+    cut into many shares, bf16 activations.  The pool is pre-filled with 0xFF bytes (NaN as e4m3 codes
+    and as scales), so a key past a row's last visible position that leaked into a product would show."""
+    ffi, kv, synth = env["ffi"], env["kv"], env["synth"]
+    fmt = ffi.KV_FORMAT_FP8_E4M3
+    hq, hkv = 24, 4
+    ctx, q_len, kw = {
+        "verify_gqa6": ([300, 1000, 17, 64], 4, {}),
+        "chunk": ([90, 260], 70, {}),
+        "window": ([700, 130, 2000], 2, dict(sliding_window=128)),
+        "masked_rows": ([500, 40, 260], 3, {}),
+        "long_few_rows": ([40000], 1, {}),
+        "bf16_io": ([700, 31], 1, {}),
+    }[case]
+    n = len(ctx)
+    wl = _workload(env, fmt, ctx, hkv, seed=61, fill=0xFF)
+    k, v = synth.make_kv(sum(ctx), hkv, 61)
+    ex = env["kv"].Executor(64 << 20)
+    kv.kv_cache_write(ex, wl.layer, wl.step(), k.cuda(), v.cuda())
+    for s, c in zip(wl.seqs, ctx):
+        s.commit(c - q_len)
+    if case == "masked_rows":
+        vtm = np.ones(n * q_len, np.uint8)
+        vtm[1] = 0
+        vtm[-1] = 0
+        kw = dict(valid_token_mask=vtm, valid_req_mask=np.asarray([1, 0, 1], np.uint8))
+    b = wl.step(q_lens=[q_len] * n, **kw)
+    q = synth.make_q(n * q_len, hq, 62).cuda()
+    if case == "bf16_io":
+        # bf16 activations (warp34_tq4_paged_attention_bf16): stream kernel against the fp32 kernel
+        fn = env["lib"].warp34_tq4_paged_attention_bf16
+        qb = q.to(torch.bfloat16)
+        res = []
+        for flags in (0, ffi.EXEC_FLAG_PRECISE_ATTENTION):
+            ex.ex.flags = flags
+            o = torch.zeros(n * q_len, hq, 256, dtype=torch.bfloat16, device="cuda")
+            assert fn(C.byref(ex.ex), C.byref(wl.layer.layout), C.byref(b.desc), qb.data_ptr(), o.data_ptr(), hq) == 0
+            torch.cuda.synchronize()
+            res.append(o.float().cpu().numpy())
+        ex.ex.flags = 0
+        assert np.isfinite(res[0]).all() and np.abs(res[1]).max() > 0.1
+        assert np.all(np.abs(res[0] - res[1]) <= ATOL + RTOL * np.abs(res[1])), float(np.abs(res[0] - res[1]).max())
+        return
+    out = torch.full((n * q_len, hq, 256), 0, dtype=torch.int16, device="cuda")
+    out.fill_(0x5500)
+    kv.paged_attention(ex, wl.layer, b, q, out.view(torch.float16), hq)
+    torch.cuda.synchronize()
+    assert int(ex.scratch[:4].cpu().numpy().view(np.int32)[0]) == 0
+    want = torch.full_like(out, 0)
+    want.fill_(0x5500)
+    ex.ex.flags = ffi.EXEC_FLAG_PRECISE_ATTENTION
+    kv.paged_attention(ex, wl.layer, b, q, want.view(torch.float16), hq)
+    ex.ex.flags = 0
+    torch.cuda.synchronize()
+    gb, wb = out.cpu().numpy().view(np.uint16), want.cpu().numpy().view(np.uint16)
+    untouched = (wb == 0x5500).all(axis=(1, 2))
+    if case == "masked_rows":
+        assert untouched.sum() == 5                # token 1, the last token, request 1's three tokens
+    assert ((gb == 0x5500).all(axis=(1, 2)) == untouched).all(), "masked rows differ"
+    g, w = gb.view(np.float16).astype(np.float32)[~untouched], wb.view(np.float16).astype(np.float32)[~untouched]
+    assert np.isfinite(g).all() and np.isfinite(w).all()
+    assert np.all(np.abs(g - w) <= ATOL + RTOL * np.abs(w)), float(np.abs(g - w).max())
+    try:
+        ref = request.getfixturevalue("ref_lib")
+    except pytest.skip.Exception:
+        return
+    if case in ("window",):
+        return   # the reference's scalar kernel has no window argument of its own to compare here
+    r = torch.zeros(n * q_len, hq, 256, dtype=torch.float16, device="cuda")
+    kv.paged_attention(ex, wl.layer, b, q, r, hq, lib=ref, scalar=True)
+    torch.cuda.synchronize()
+    rr = r.float().cpu().numpy()[~untouched]
+    assert np.isfinite(rr).all()
+    assert np.all(np.abs(g - rr) <= ATOL + RTOL * np.abs(rr)), float(np.abs(g - rr).max())

@@ -271,6 +271,397 @@ __global__ void __launch_bounds__(128) kv8_merge_kernel(
     for (int e = 0; e < 8; ++e) store_act(attn_out, out_base + e, acc[e] * inv_l, io_bf16);
 }
 
+// ---------------------------------------------------------------------------------------------------
+// Tensor-core path for FP8 E4M3 layers in the canonical packing (264-byte rows, one (page, kv head)
+// run of 4224 bytes for K and one for V).  Same persistent split-KV structure as the TQ4 stream kernel
+// (plan launch, one share of (request, kv head, 8-row group, page) units per worker warp, per-warp
+// mbarrier ring filled by bulk copies, partials merged by tq4_attention_merge_kernel in natural
+// coordinates), but there is no table and nothing to round:
+//   * e4m3 codes convert EXACTLY to fp16 (cvt.rn.f16x2.e4m3x2, two codes per instruction) straight into
+//     MMA A fragments; the unrotated query is the fp16 B operand as it arrives; scales and sm_scale stay
+//     outside the operands in fp32: S^T = K Q^T has no operand rounding at all;
+//   * P x d_v (d_v: the V scale of the key and 128-half) is fed as fp16 value + fp16 residual, so
+//     O^T += V^T (P d_v)^T carries P to about 2^-22.
+// Shared-memory reads are 64-bit and conflict-free with the rows as they lie in global memory (a
+// row is 66 words, so consecutive tokens are two banks apart):
+//   K: lane (gid, tig) reads its key's words 32 h + 8 tig + 2 j + {0, 1}  (h: 128-half, j = 0..3);
+//      the 4 codes of a word are the k positions {2 tig, 2 tig + 1, 2 tig + 8, 2 tig + 9} of one MMA
+//      step, and the query fragments are loaded in the same order;
+//   V: lane reads, for its four tokens, words base(gid) + 16 jj + {0, 1} with
+//      base = 2 (gid & 1) + 8 ((gid >> 1) & 1) + 4 (gid >> 2); two PRMTs pair the bytes of two tokens
+//      per channel (the k positions of an A register), each word giving two m-tiles.
+// ---------------------------------------------------------------------------------------------------
+constexpr int kFp8RowBytesA = kHeadDim + 8;                  // 264
+constexpr int kFp8RunBytes = kPageTokens * kFp8RowBytesA;    // 4224, a multiple of 16
+constexpr int kFp8StageBytes = 2 * kFp8RunBytes;             // K run, then V run
+constexpr int kFp8Warps = 8;
+constexpr int kFp8Stages = 3;
+
+__device__ __forceinline__ uint2 lds64_dep(uint32_t addr, uint32_t token) {
+    uint2 v;
+    asm("ld.shared.v2.u32 {%0,%1}, [%2+0];  // dep %3" : "=r"(v.x), "=r"(v.y) : "r"(addr), "r"(token));
+    return v;
+}
+// Four e4m3 codes -> two fp16 pairs (bytes 0,1 and bytes 2,3).
+__device__ __forceinline__ void e4m3x4_to_f16x4(uint32_t w, uint32_t& lo, uint32_t& hi) {
+    asm("{\n\t.reg .b16 l, h;\n\tmov.b32 {l, h}, %2;\n\tcvt.rn.f16x2.e4m3x2 %0, l;\n\tcvt.rn.f16x2.e4m3x2 %1, h;\n\t}"
+        : "=r"(lo), "=r"(hi) : "r"(w));
+}
+
+template <int STAGES>
+__global__ void __launch_bounds__(kFp8Warps * 32, 1) fp8kv_attention_stream_kernel(const StreamParams p) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    constexpr uint32_t kRingBytes = STAGES * kFp8StageBytes;
+    const uint32_t win_lo = smem_u32(smem);
+    const uint32_t ring = win_lo + (uint32_t)wid * kRingBytes;
+    const uint32_t bars = win_lo + (uint32_t)kFp8Warps * kRingBytes + (uint32_t)wid * STAGES * 8u;
+    uint8_t* ring_gen = smem + (size_t)wid * kRingBytes;
+    PlanHeader* hdr = reinterpret_cast<PlanHeader*>(p.scratch);
+    if (lane == 0) {
+        for (int s = 0; s < STAGES; ++s) mbar_init(bars + 8u * s, 1u);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    const int R = p.batch.num_reqs;
+    const int32_t* unit_prefix = plan_array(p.scratch, 0, R);
+    const int32_t* item_prefix = plan_array(p.scratch, 1, R);
+    const int32_t* page_lo_a = plan_array(p.scratch, 2, R);
+    const int32_t* npages_a = plan_array(p.scratch, 3, R);
+    const int32_t* ngroups_a = plan_array(p.scratch, 4, R);
+    float* partials = reinterpret_cast<float*>(p.scratch + plan_bytes(R));
+
+    const int w_global = wid * (int)gridDim.x + (int)blockIdx.x;   // consecutive workers on different SMs
+    const int per = hdr->units_per_warp;
+    const int total_units = hdr->total_units;
+    long long u_ll = (long long)w_global * per;
+    if (per <= 0 || u_ll >= total_units) return;
+    int u = (int)u_ll;
+    const int u_end = min(u + per, total_units);
+
+    const int gid = lane >> 2, tig = lane & 3;
+    // MMA row m of S^T <-> token (m & 3) + 8 ((m >> 2) & 1) + 4 (m >> 3) of the page, which makes the
+    // score accumulators of a lane, transposed by movmatrix, the P fragments of the tokens it owns in
+    // the output product: kv0 + {0, 1, 4, 5} at k positions 2 tig, 2 tig + 1, 2 tig + 8, 2 tig + 9.
+    const int key_a = (gid & 3) + 8 * (gid >> 2);
+    const int kv0 = 2 * (tig & 1) + 8 * (tig >> 1);
+    const uint32_t k_lane = (uint32_t)(key_a * kFp8RowBytesA + 32 * tig);
+    const uint32_t v_lane = (uint32_t)(kFp8RunBytes + kv0 * kFp8RowBytesA +
+                                       4 * (2 * (gid & 1) + 8 * ((gid >> 1) & 1) + 4 * (gid >> 2)));
+    uint32_t phase_bits = 0, pending = 0;
+    bool failed = false;
+
+    int r;
+    {
+        int lo = 0, hi = R;
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (unit_prefix[mid] <= u) lo = mid; else hi = mid;
+        }
+        r = lo;
+    }
+
+    while (u < u_end && !failed) {
+        while (unit_prefix[r + 1] <= u) ++r;
+        const int npages = npages_a[r];
+        const int ngroups = ngroups_a[r];
+        const int in_req = u - unit_prefix[r];
+        const int item = in_req / npages;
+        const int page_in_item = in_req - item * npages;
+        const int n_here = min(u_end - u, npages - page_in_item);
+        const int kv_head = item / ngroups;
+        const int group = item - kv_head * ngroups;
+        const int pg0 = page_lo_a[r] + page_in_item;
+        const int slot = w_global + item_prefix[r] + item;
+        const ReqGeom g = load_req(p.batch, r);
+        const int rows_in_req = g.q_len * p.gqa;
+
+        int rmax[2], rmin[2];
+        bool rvalid[2];
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+            const int row = group * kRowsPerGroup + 2 * tig + x;
+            const int q_off = row / p.gqa;
+            rvalid[x] = row < rows_in_req &&
+                        (p.batch.valid_token_mask == nullptr || p.batch.valid_token_mask[g.q_start + q_off] != 0);
+            rmax[x] = rvalid[x] ? row_max_kv(p.batch, g, q_off) : -1;
+            rmin[x] = rvalid[x] ? row_min_kv(p.batch, g, q_off) : 0x7fffffff;
+        }
+        int safe_hi = min(rvalid[0] ? rmax[0] : 0x7fffffff, rvalid[1] ? rmax[1] : 0x7fffffff);
+        int safe_lo = max(rvalid[0] ? rmin[0] : 0, rvalid[1] ? rmin[1] : 0);
+        int kv_hi = max(rmax[0], rmax[1]);   // last key any row of the group can see
+#pragma unroll
+        for (int d = 1; d < 4; d <<= 1) {
+            safe_hi = min(safe_hi, __shfl_xor_sync(0xffffffffu, safe_hi, d));
+            safe_lo = max(safe_lo, __shfl_xor_sync(0xffffffffu, safe_lo, d));
+            kv_hi = max(kv_hi, __shfl_xor_sync(0xffffffffu, kv_hi, d));
+        }
+
+        // ---- query row gid of the group as B fragments, in the K loads' column order ----------------
+        uint32_t qb[16][2];
+        {
+            const int row = group * kRowsPerGroup + gid;
+            const int q_off = row / p.gqa;
+            const int q_head = kv_head * p.gqa + (row - q_off * p.gqa);
+            const bool ok = row < rows_in_req &&
+                            (p.batch.valid_token_mask == nullptr || p.batch.valid_token_mask[g.q_start + q_off] != 0);
+            const size_t q_base = ((size_t)(g.q_start + q_off) * p.num_q_heads + q_head) * kHeadDim;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int col = 4 * (32 * h + 8 * tig + 2 * j);     // 8 columns, 16 bytes
+                    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                    if (ok) {
+                        if (p.io_bf16) {
+                            uint32_t t[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                t[e] = pack_half2(load_act(p.q_in, q_base + col + 2 * e, 1),
+                                                  load_act(p.q_in, q_base + col + 2 * e + 1, 1));
+                            }
+                            v = make_uint4(t[0], t[1], t[2], t[3]);
+                        } else {
+                            v = __ldg(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.q_in) + q_base + col));
+                        }
+                    }
+                    const int ks = 2 * (4 * h + j);
+                    qb[ks][0] = v.x; qb[ks][1] = v.y;
+                    qb[ks + 1][0] = v.z; qb[ks + 1][1] = v.w;
+                }
+            }
+        }
+        float o[16][4];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
+        float m_run[2] = {-1e30f, -1e30f};
+        float l_run[2] = {0.0f, 0.0f};
+
+        const int32_t* blocks = p.batch.block_tables + (size_t)r * p.batch.max_blocks_per_req;
+        const uint8_t* k_head_base = (const uint8_t*)(uintptr_t)p.layout.k_base + (size_t)kv_head * p.layout.k_head_stride_bytes;
+        const uint8_t* v_head_base = (const uint8_t*)(uintptr_t)p.layout.v_base + (size_t)kv_head * p.layout.v_head_stride_bytes;
+        int32_t my_page = (lane < n_here) ? block_table_page(blocks, pg0 + lane, p.batch.max_blocks_per_req, kInKv8) : 0;
+        int32_t next_page = (32 + lane < n_here) ? block_table_page(blocks, pg0 + 32 + lane, p.batch.max_blocks_per_req, kInKv8) : 0;
+
+        fence_proxy_async();   // generic-proxy writes to the ring (partials, cleared rows) precede the copies
+        auto issue = [&](int idx) {
+            const int32_t page = __shfl_sync(0xffffffffu, (idx & 32) ? next_page : my_page, idx & 31);
+            pending |= 1u << (idx % STAGES);
+            if (lane == 0) {
+                const int s = idx % STAGES;
+                const uint32_t bar = bars + 8u * s;
+                const uint32_t dst = ring + (uint32_t)s * kFp8StageBytes;
+                mbar_expect_tx(bar, 2 * kFp8RunBytes);
+                bulk_g2s(dst, k_head_base + (size_t)page * p.layout.k_page_stride_bytes, kFp8RunBytes, bar);
+                bulk_g2s(dst + kFp8RunBytes, v_head_base + (size_t)page * p.layout.v_page_stride_bytes, kFp8RunBytes, bar);
+            }
+        };
+#pragma unroll 1
+        for (int i = 0; i < STAGES - 1 && i < n_here; ++i) issue(i);
+
+#pragma unroll 1
+        for (int i = 0; i < n_here; ++i) {
+            if ((i & 31) == 0 && i > 0) {
+                const int base = i + 32;
+                const int32_t fresh = (base + lane < n_here) ? block_table_page(blocks, pg0 + base + lane, p.batch.max_blocks_per_req, kInKv8) : 0;
+                if (i & 32) my_page = fresh; else next_page = fresh;
+            }
+            {
+                const int ahead = i + STAGES - 1;
+                if (ahead < n_here) issue(ahead);
+            }
+            const int s = i % STAGES;
+            if (!mbar_wait(bars + 8u * s, (phase_bits >> s) & 1u)) { failed = true; break; }
+            phase_bits ^= 1u << s;
+            pending &= ~(1u << s);
+
+            const uint32_t st = ring + (uint32_t)s * kFp8StageBytes;
+            const int kv_base = (pg0 + i) << 4;
+            const bool full = (kv_base >= safe_lo) && (kv_base + 15 <= safe_hi);
+            // Tokens past the last visible key may never have been written: their code bytes can be
+            // NaN patterns, and 0 x NaN is NaN inside the MMA.  Their V rows are cleared in the stage.
+            if (kv_base + 15 > kv_hi) {
+                const int first = max(kv_hi + 1 - kv_base, 0);
+                for (int w = first * (kFp8RowBytesA / 4) + lane; w < kPageTokens * (kFp8RowBytesA / 4); w += 32) {
+                    sts32(st + kFp8RunBytes + 4u * (uint32_t)w, 0u);
+                }
+                __syncwarp();
+            }
+            const uint32_t ptok = page_token(i);
+
+            // ---- S^T = K Q^T: one accumulator per 128-half, exact operands ---------------------------
+            float sa[2][4];
+            const uint32_t krow_a = st + k_lane, krow_b = krow_a + 4u * kFp8RowBytesA;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint2 wa = lds64_dep(krow_a + 4u * (32u * h + 2u * j), ptok);
+                    const uint2 wb = lds64_dep(krow_b + 4u * (32u * h + 2u * j), ptok);
+                    uint32_t a0, a1, a2, a3;
+                    const int ks = 2 * (4 * h + j);
+                    e4m3x4_to_f16x4(wa.x, a0, a2);
+                    e4m3x4_to_f16x4(wb.x, a1, a3);
+                    if (j == 0) mma16816_zero(sa[h], a0, a1, a2, a3, qb[ks][0], qb[ks][1]);
+                    else mma16816(sa[h], a0, a1, a2, a3, qb[ks][0], qb[ks][1]);
+                    e4m3x4_to_f16x4(wa.y, a0, a2);
+                    e4m3x4_to_f16x4(wb.y, a1, a3);
+                    mma16816(sa[h], a0, a1, a2, a3, qb[ks + 1][0], qb[ks + 1][1]);
+                }
+            }
+            // scales of this lane's two keys (two floats behind the 256 codes), K and V
+            const uint2 dka = lds64_dep(st + (uint32_t)(key_a * kFp8RowBytesA + kHeadDim), ptok);
+            const uint2 dkb = lds64_dep(st + (uint32_t)((key_a + 4) * kFp8RowBytesA + kHeadDim), ptok);
+            const uint2 dva_w = lds64_dep(st + (uint32_t)(kFp8RunBytes + key_a * kFp8RowBytesA + kHeadDim), ptok);
+            const uint2 dvb_w = lds64_dep(st + (uint32_t)(kFp8RunBytes + (key_a + 4) * kFp8RowBytesA + kHeadDim), ptok);
+            float dva0 = __uint_as_float(dva_w.x), dva1 = __uint_as_float(dva_w.y);
+            float dvb0 = __uint_as_float(dvb_w.x), dvb1 = __uint_as_float(dvb_w.y);
+            float sc[4];
+            sc[0] = (__uint_as_float(dka.x) * sa[0][0] + __uint_as_float(dka.y) * sa[1][0]) * p.q_scale;
+            sc[1] = (__uint_as_float(dka.x) * sa[0][1] + __uint_as_float(dka.y) * sa[1][1]) * p.q_scale;
+            sc[2] = (__uint_as_float(dkb.x) * sa[0][2] + __uint_as_float(dkb.y) * sa[1][2]) * p.q_scale;
+            sc[3] = (__uint_as_float(dkb.x) * sa[0][3] + __uint_as_float(dkb.y) * sa[1][3]) * p.q_scale;
+
+            bool msk[4] = {false, false, false, false};
+            if (!full) {
+                const int pos_a = kv_base + key_a, pos_b = pos_a + 4;
+                msk[0] = !(pos_a >= rmin[0] && pos_a <= rmax[0]);
+                msk[1] = !(pos_a >= rmin[1] && pos_a <= rmax[1]);
+                msk[2] = !(pos_b >= rmin[0] && pos_b <= rmax[0]);
+                msk[3] = !(pos_b >= rmin[1] && pos_b <= rmax[1]);
+#pragma unroll
+                for (int x = 0; x < 4; ++x) if (msk[x]) sc[x] = -1e30f;
+            }
+            float mx0 = fmaxf(sc[0], sc[2]), mx1 = fmaxf(sc[1], sc[3]);
+#pragma unroll
+            for (int d = 4; d < 32; d <<= 1) {
+                mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, d));
+                mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, d));
+            }
+            const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
+            const bool grew = (mn0 > m_run[0]) || (mn1 > m_run[1]);
+            if (__any_sync(0xffffffffu, grew)) {
+                const float al0 = ex2(m_run[0] - mn0), al1 = ex2(m_run[1] - mn1);
+                l_run[0] *= al0;
+                l_run[1] *= al1;
+#pragma unroll
+                for (int t = 0; t < 16; ++t) {
+                    o[t][0] *= al0; o[t][1] *= al1; o[t][2] *= al0; o[t][3] *= al1;
+                }
+                m_run[0] = mn0;
+                m_run[1] = mn1;
+            }
+            float pr[4];
+            pr[0] = ex2(sc[0] - mn0);
+            pr[1] = ex2(sc[1] - mn1);
+            pr[2] = ex2(sc[2] - mn0);
+            pr[3] = ex2(sc[3] - mn1);
+            if (!full) {
+#pragma unroll
+                for (int x = 0; x < 4; ++x) if (msk[x]) pr[x] = 0.0f;
+                // a key no row can see may hold never-written bytes: keep its scale finite
+                if (msk[0] && msk[1]) { dva0 = 0.0f; dva1 = 0.0f; }
+                if (msk[2] && msk[3]) { dvb0 = 0.0f; dvb1 = 0.0f; }
+            }
+            l_run[0] += pr[0] + pr[2];
+            l_run[1] += pr[1] + pr[3];
+            // P x d_v per 128-half as B fragments (k = key, n = query row): fp16 value + fp16 residual
+            uint32_t pb[2][2], pl[2][2];
+            const float pd[2][4] = {{pr[0] * dva0, pr[1] * dva0, pr[2] * dvb0, pr[3] * dvb0},
+                                    {pr[0] * dva1, pr[1] * dva1, pr[2] * dvb1, pr[3] * dvb1}};
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+#pragma unroll
+                for (int x = 0; x < 2; ++x) {
+                    const __half2 hi = __floats2half2_rn(pd[h][2 * x], pd[h][2 * x + 1]);
+                    const float2 hf = __half22float2(hi);
+                    const __half2 lo = __floats2half2_rn(pd[h][2 * x] - hf.x, pd[h][2 * x + 1] - hf.y);
+                    pb[h][x] = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&hi));
+                    pl[h][x] = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&lo));
+                }
+            }
+
+            // ---- O^T += V^T (P d_v)^T ---------------------------------------------------------------
+            const uint32_t vr = st + v_lane;
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) {
+                const int half = jj >> 1;
+                const uint2 w0 = lds64_dep(vr + 64u * jj, ptok);
+                const uint2 w1 = lds64_dep(vr + kFp8RowBytesA + 64u * jj, ptok);
+                const uint2 w2 = lds64_dep(vr + 4u * kFp8RowBytesA + 64u * jj, ptok);
+                const uint2 w3 = lds64_dep(vr + 5u * kFp8RowBytesA + 64u * jj, ptok);
+#pragma unroll
+                for (int x = 0; x < 2; ++x) {
+                    const uint32_t t0 = x ? w0.y : w0.x, t1 = x ? w1.y : w1.x;
+                    const uint32_t t2 = x ? w2.y : w2.x, t3 = x ? w3.y : w3.x;
+                    // bytes (token a, token b) of channels 0, 1 | 2, 3 of the word
+                    const uint32_t ab01 = __byte_perm(t0, t1, 0x5140), ab23 = __byte_perm(t0, t1, 0x7362);
+                    const uint32_t cd01 = __byte_perm(t2, t3, 0x5140), cd23 = __byte_perm(t2, t3, 0x7362);
+                    uint32_t a0, a1, a2, a3;
+                    e4m3x4_to_f16x4(ab01, a0, a1);
+                    e4m3x4_to_f16x4(cd01, a2, a3);
+                    mma16816(o[4 * jj + 2 * x], a0, a1, a2, a3, pb[half][0], pb[half][1]);
+                    mma16816(o[4 * jj + 2 * x], a0, a1, a2, a3, pl[half][0], pl[half][1]);
+                    e4m3x4_to_f16x4(ab23, a0, a1);
+                    e4m3x4_to_f16x4(cd23, a2, a3);
+                    mma16816(o[4 * jj + 2 * x + 1], a0, a1, a2, a3, pb[half][0], pb[half][1]);
+                    mma16816(o[4 * jj + 2 * x + 1], a0, a1, a2, a3, pl[half][0], pl[half][1]);
+                }
+            }
+            __syncwarp();   // every lane is done with stage s before it is refilled
+            if (kv_base + 15 > kv_hi) fence_proxy_async();   // the cleared rows precede the next copy into s
+        }
+
+        if (failed) {
+            for (int s = 0; s < STAGES; ++s) {
+                if (pending & (1u << s)) (void)mbar_wait(bars + 8u * s, (phase_bits >> s) & 1u);
+            }
+            if (lane == 0) atomicOr(&hdr->status, 1);
+            break;
+        }
+
+        // ---- partial: natural column order, through the idle ring -----------------------------------
+#pragma unroll
+        for (int d = 4; d < 32; d <<= 1) {
+            l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], d);
+            l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], d);
+        }
+        float* stage_o = reinterpret_cast<float*>(ring_gen);   // [8 rows][256]
+        const int wbase = 2 * (gid & 1) + 8 * ((gid >> 1) & 1) + 4 * (gid >> 2);
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+#pragma unroll
+            for (int x = 0; x < 2; ++x) {
+#pragma unroll
+                for (int ps = 0; ps < 2; ++ps) {
+                    // m-tile 4 jj + 2 x + ps: row gid = channel c, row gid + 8 = channel c + 1
+                    const int c = 4 * (wbase + 16 * jj + x) + 2 * ps;
+                    const float* acc = o[4 * jj + 2 * x + ps];
+                    *reinterpret_cast<float2*>(stage_o + (2 * tig) * kHeadDim + c) = make_float2(acc[0], acc[2]);
+                    *reinterpret_cast<float2*>(stage_o + (2 * tig + 1) * kHeadDim + c) = make_float2(acc[1], acc[3]);
+                }
+            }
+        }
+        __syncwarp();
+        if (slot < p.max_slots) {
+            float* dst = partials + (size_t)slot * kPartialFloats;
+            const float4* src4 = reinterpret_cast<const float4*>(stage_o);
+            float4* dst4 = reinterpret_cast<float4*>(dst);
+#pragma unroll
+            for (int k = 0; k < (kRowsPerGroup * kHeadDim / 4) / 32; ++k) dst4[k * 32 + lane] = src4[k * 32 + lane];
+            if (gid == 0) {
+                dst[kRowsPerGroup * kHeadDim + 2 * tig] = m_run[0];
+                dst[kRowsPerGroup * kHeadDim + 2 * tig + 1] = m_run[1];
+                dst[kRowsPerGroup * kHeadDim + kRowsPerGroup + 2 * tig] = l_run[0];
+                dst[kRowsPerGroup * kHeadDim + kRowsPerGroup + 2 * tig + 1] = l_run[1];
+            }
+        }
+        __syncwarp();
+        u += n_here;
+    }
+}
+
 static bool kv8_attention_layout_ok(const warp34_kv_layer_layout* l) {
     const bool k8 = l->k_format == WARP34_KV_FORMAT_Q8_0 || l->k_format == WARP34_KV_FORMAT_FP8_E4M3;
     const bool v8 = l->v_format == WARP34_KV_FORMAT_Q8_0 || l->v_format == WARP34_KV_FORMAT_FP8_E4M3;
@@ -278,14 +669,101 @@ static bool kv8_attention_layout_ok(const warp34_kv_layer_layout* l) {
            l->k_transform == WARP34_KV_TRANSFORM_IDENTITY && l->v_transform == WARP34_KV_TRANSFORM_IDENTITY;
 }
 
+// The tensor-core path serves FP8 E4M3 K and V in the canonical packing with 16-byte-aligned runs, a
+// 16-byte-aligned query and a workspace that holds the plan and at least one CTA's partial slots.
+static bool fp8_stream_ok(const warp34_exec* ex, const warp34_kv_layer_layout* l, const warp34_attention_batch* b,
+                          const void* q_in, int io_bf16) {
+    if (l->k_format != WARP34_KV_FORMAT_FP8_E4M3 || l->v_format != WARP34_KV_FORMAT_FP8_E4M3) return false;
+    if (l->k_token_stride_bytes != (uint64_t)kFp8RowBytesA || l->v_token_stride_bytes != (uint64_t)kFp8RowBytesA) return false;
+    if ((l->k_base | l->v_base | l->k_page_stride_bytes | l->v_page_stride_bytes | l->k_head_stride_bytes |
+         l->v_head_stride_bytes) & 15u) {
+        return false;
+    }
+    if (!io_bf16 && ((uintptr_t)q_in & 15u) != 0) return false;
+    if (b->block_tables == nullptr || b->max_blocks_per_req <= 0) return false;
+    return ex->scratch_ptr != 0 && (ex->scratch_ptr & 15u) == 0;
+}
+
+static int launch_fp8_stream(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
+                             const warp34_attention_batch* batch, const void* q_in, void* attn_out,
+                             int num_q_heads, int io_bf16, bool* taken) {
+    *taken = false;
+    int rc = 0;
+    DeviceInfo* dev = device_info(&rc);
+    if (dev == nullptr) return rc;
+    const long long items = items_bound(layout, batch, num_q_heads, kRowsPerGroup);
+    if (items * (long long)batch->max_blocks_per_req >= 0x7fffffffll) return 0;
+    const size_t plan = plan_bytes(batch->num_reqs);
+    const size_t slot_bytes = (size_t)kPartialFloats * sizeof(float);
+    const size_t avail = ex->scratch_size > plan ? ex->scratch_size - plan : 0;
+    const long long workers = (long long)(avail / slot_bytes) - items;
+    if (workers < kFp8Warps) return 0;            // the caller falls back to the fp32 kernel
+    int grid = dev->sm_count;
+    if (workers / kFp8Warps < grid) grid = (int)(workers / kFp8Warps);
+    const uint32_t smem = (uint32_t)(kFp8Warps * kFp8Stages * kFp8StageBytes + kFp8Warps * kFp8Stages * 8);
+    {
+        static std::mutex mu;
+        static bool done[64];
+        int d = 0;
+        rc = (int)cudaGetDevice(&d);
+        if (rc != 0) return rc;
+        if (d < 0 || d >= 64) return (int)cudaErrorInvalidDevice;
+        std::lock_guard<std::mutex> lock(mu);
+        if (!done[d]) {
+            rc = (int)cudaFuncSetAttribute(fp8kv_attention_stream_kernel<kFp8Stages>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (rc != 0) return rc;
+            done[d] = true;
+        }
+    }
+    StreamParams p;
+    p.og.gate = nullptr;
+    p.og.mode = 0;
+    p.layout = *layout;
+    p.batch = *batch;
+    p.q_in = q_in;
+    p.attn_out = attn_out;
+    p.io_bf16 = io_bf16;
+    p.triple_out = nullptr;
+    p.scratch = reinterpret_cast<uint8_t*>((uintptr_t)ex->scratch_ptr);
+    p.num_q_heads = num_q_heads;
+    p.gqa = num_q_heads / layout->local_kv_heads;
+    p.num_warps = grid * kFp8Warps;
+    p.max_slots = (int)(p.num_warps + items);
+    p.smem_bytes = smem;
+    p.rows_per_group = kRowsPerGroup;
+    p.q_scale = batch->sm_scale * 1.4426950408889634f;
+    p.natural = 1;
+    p.qfrag = nullptr;
+    p.q_groups_max = 0;
+    cudaStream_t st = (cudaStream_t)ex->stream;
+    tq4_attention_plan_kernel<<<1, 32, 0, st>>>(p);
+    fp8kv_attention_stream_kernel<kFp8Stages><<<grid, kFp8Warps * 32, smem, st>>>(p);
+    const long long rows = (long long)batch->total_tokens * num_q_heads;
+    if (rows * 4 < (long long)grid * kFp8Warps / 8) {
+        tq4_attention_merge_kernel<false, 32><<<(unsigned)rows, 1024, 0, st>>>(p);
+    } else {
+        tq4_attention_merge_kernel<false, 4><<<(unsigned)rows, 128, 0, st>>>(p);
+    }
+    *taken = true;
+    return (int)cudaGetLastError();
+}
+
+// allow_stream = false: the fp32 dequant-then-attend kernel whatever the layout (the scalar entry
+// point and WARP34_B200_EXEC_FLAG_PRECISE_ATTENTION).
 static int launch_kv8_attention(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
                                 const warp34_attention_batch* batch, const void* q_in, void* attn_out,
-                                int num_q_heads, int io_bf16) {
+                                int num_q_heads, int io_bf16, bool allow_stream = false) {
     if (batch->total_tokens <= 0 || num_q_heads <= 0) return 0;
     if (layout->local_kv_heads <= 0 || num_q_heads % layout->local_kv_heads != 0 || batch->num_reqs <= 0) {
         return (int)cudaErrorInvalidValue;
     }
     if (layout->k_base == 0 || layout->v_base == 0) return (int)cudaErrorInvalidValue;
+    if (allow_stream && fp8_stream_ok(ex, layout, batch, q_in, io_bf16)) {
+        bool taken = false;
+        const int rc = launch_fp8_stream(ex, layout, batch, q_in, attn_out, num_q_heads, io_bf16, &taken);
+        if (rc != 0 || taken) return rc;
+    }
     if ((layout->k_base | layout->v_base | layout->k_page_stride_bytes | layout->k_head_stride_bytes |
          layout->k_token_stride_bytes | layout->v_page_stride_bytes | layout->v_head_stride_bytes |
          layout->v_token_stride_bytes) & 3u) {

@@ -2123,7 +2123,8 @@ static int launch_attention(const warp34_exec* ex, const warp34_kv_layer_layout*
     if (batch->total_tokens <= 0 || num_q_heads <= 0) return 0;
     if (kv8_attention_layout_ok(layout)) {   // unrotated 8-bit boundary layers: the epilogue is a second launch, in place
         if (triple_out != nullptr) return (int)cudaErrorNotSupported;
-        const int rc8 = launch_kv8_attention(ex, layout, batch, q_in, attn_out, num_q_heads, io_bf16);
+        const int rc8 = launch_kv8_attention(ex, layout, batch, q_in, attn_out, num_q_heads, io_bf16,
+                                             (ex->flags & WARP34_B200_EXEC_FLAG_PRECISE_ATTENTION) == 0 && force <= 0);
         if (rc8 != 0 || og.mode == 0) return rc8;
         return launch_output_gate(ex, attn_out, og.gate, attn_out, batch->valid_token_mask, batch->total_tokens,
                                   num_q_heads * kHeadDim, og.mode, io_bf16);
