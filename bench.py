@@ -499,6 +499,8 @@ def run_other_kv(args):
         return
     lib = ffi.bind_kernel_abi(ref_path) if ref_path else ffi.kernels()
     hq, hkv, batch, lo, hi, q_len, seed = synth.CONFIGS[args.config]
+    if args.batch > 0:
+        batch = args.batch
     ctx = synth.context_lengths(batch, lo, hi, seed)
     if bf16:
         formats, act = kv.BF16_KV_FORMATS, torch.bfloat16
@@ -559,7 +561,7 @@ def run_other_kv(args):
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_kind": f"of {peak_kind}", "kernel": kernel, "launch_ms": attn_ms, "traffic": None},
             "attended_tokens_per_s": float(sum(wl.ctx) + n_tok) / (attn_ms * 1e-3),
-            "gpu_launches": (4 if bf16 else 2) * args.steps, "clocks": sampler.summary(t_begin, t_end)}
+            "gpu_launches": (4 if bf16 or args.kv == "fp8" else 2) * args.steps, "clocks": sampler.summary(t_begin, t_end)}
     if reference:
         line["impl"] = "reference"
         line["roofline"]["kernel"] = "reference paged_attention_gqa_bf16_kernel"
