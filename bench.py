@@ -510,8 +510,7 @@ def run_other_kv(args):
         fmt = ffi.KV_FORMAT_FP8_E4M3 if args.kv == "fp8" else ffi.KV_FORMAT_Q8_0
         formats, act = (fmt, fmt, ffi.KV_TRANSFORM_IDENTITY, ffi.KV_TRANSFORM_IDENTITY), torch.float16
         append, attend = kv.kv_cache_write, kv.paged_attention
-        kernel = ("fp8kv_attention_stream_kernel (+ plan and merge)" if args.kv == "fp8" and not reference
-                  else "kv8_attention_kernel" if not reference else "reference kernels")
+        kernel = "kv8_attention_stream_kernel (+ plan and merge)" if not reference else "reference kernels"
         label = "unrotated FP8 E4M3 rows" if args.kv == "fp8" else "unrotated Q8_0 rows"
     wl = synth.PagedWorkload([int(c) for c in ctx], [q_len] * batch, hkv, seed=seed, formats=formats)
     ex = kv.Executor(64 << 20)
@@ -561,7 +560,7 @@ def run_other_kv(args):
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_kind": f"of {peak_kind}", "kernel": kernel, "launch_ms": attn_ms, "traffic": None},
             "attended_tokens_per_s": float(sum(wl.ctx) + n_tok) / (attn_ms * 1e-3),
-            "gpu_launches": (4 if bf16 or args.kv == "fp8" else 2) * args.steps, "clocks": sampler.summary(t_begin, t_end)}
+            "gpu_launches": 4 * args.steps, "clocks": sampler.summary(t_begin, t_end)}
     if reference:
         line["impl"] = "reference"
         line["roofline"]["kernel"] = "reference paged_attention_gqa_bf16_kernel"

@@ -160,21 +160,19 @@ def test_attention_over_8bit_rows_matches_dequant_then_attend(env, fmt_name, hq,
     out = torch.zeros(sum(q_lens), hq, 256, dtype=torch.float16, device="cuda")
     kv.paged_attention(env["ex"], wl.layer, b, q.cuda(), out, hq)
     torch.cuda.synchronize()
-    if fmt == ffi.KV_FORMAT_FP8_E4M3:   # the stream kernel's status word (no bounded wait gave up)
-        assert int(env["ex"].scratch[:4].cpu().numpy().view(np.int32)[0]) == 0
+    # the stream kernel's status word (no bounded wait gave up)
+    assert int(env["ex"].scratch[:4].cpu().numpy().view(np.int32)[0]) == 0
     got = out.float().cpu().numpy()
     want = _dequant_then_attend(env, wl, fmt, ctx, q_lens, q, hq, hkv)
     assert np.all(np.abs(got - want) <= ATOL + RTOL * np.abs(want)), float(np.abs(got - want).max())
-    # the scalar entry point is the fp32 dequant-then-attend kernel; Q8_0 layers take it by default too,
-    # FP8 layers take the tensor-core stream kernel (exact operands, P as value + residual)
+    # the scalar entry point is the fp32 dequant-then-attend kernel; the default path is the tensor-core
+    # stream kernel (exact operands, P as value + residual)
     out2 = torch.zeros_like(out)
     kv.paged_attention(env["ex"], wl.layer, b, q.cuda(), out2, hq, scalar=True)
     torch.cuda.synchronize()
-    if fmt == ffi.KV_FORMAT_Q8_0:
-        assert torch.equal(out.view(torch.int16), out2.view(torch.int16))
-    else:
-        g2 = out2.float().cpu().numpy()
-        assert np.all(np.abs(g2 - want) <= ATOL + RTOL * np.abs(want)), float(np.abs(g2 - want).max())
+    g2 = out2.float().cpu().numpy()
+    assert np.all(np.abs(g2 - want) <= ATOL + RTOL * np.abs(want)), float(np.abs(g2 - want).max())
+    assert not torch.equal(out.view(torch.int16), out2.view(torch.int16)), "the default path did not take the stream kernel"
     # The pin: the reference's scalar kernel (fp32, read_kv_elem) over the same bytes.  This library's
     # output must sit inside the plain bound of it, and so must the float64 restatement, which the
     # tests of the 8-bit path lean on when the reference library is absent.
@@ -203,15 +201,16 @@ def test_8bit_layers_refuse_what_they_do_not_cover(env):
     assert rc == ffi.CUDA_ERROR_NOT_SUPPORTED
 
 
+@pytest.mark.parametrize("fmt_name", ["fp8_e4m3", "q8_0"])
 @pytest.mark.parametrize("case", ["verify_gqa6", "chunk", "window", "masked_rows", "long_few_rows", "bf16_io"])
-def test_fp8_stream_kernel_geometries_against_the_fp32_kernel(env, case, request):
-    """The tensor-core path of FP8 layers against this library's fp32 dequant-then-attend kernel (itself
+def test_8bit_stream_kernel_geometries_against_the_fp32_kernel(env, case, fmt_name, request):
+    """The tensor-core path of the 8-bit layers against this library's fp32 dequant-then-attend kernel (itself
     pinned above) and, when it travelled, the reference's scalar kernel: draft tokens with 24 query
     rows per kv head, a prefill chunk, a sliding window, masked tokens and requests, one long sequence
     cut into many shares, bf16 activations.  The pool is pre-filled with 0xFF bytes (NaN as e4m3 codes
     and as scales), so a key past a row's last visible position that leaked into a product would show."""
     ffi, kv, synth = env["ffi"], env["kv"], env["synth"]
-    fmt = ffi.KV_FORMAT_FP8_E4M3
+    fmt = ffi.KV_FORMAT_Q8_0 if fmt_name == "q8_0" else ffi.KV_FORMAT_FP8_E4M3
     hq, hkv = 24, 4
     ctx, q_len, kw = {
         "verify_gqa6": ([300, 1000, 17, 64], 4, {}),

@@ -272,50 +272,86 @@ __global__ void __launch_bounds__(128) kv8_merge_kernel(
 }
 
 // ---------------------------------------------------------------------------------------------------
-// Tensor-core path for FP8 E4M3 layers in the canonical packing (264-byte rows, one (page, kv head)
-// run of 4224 bytes for K and one for V).  Same persistent split-KV structure as the TQ4 stream kernel
-// (plan launch, one share of (request, kv head, 8-row group, page) units per worker warp, per-warp
-// mbarrier ring filled by bulk copies, partials merged by tq4_attention_merge_kernel in natural
-// coordinates), but there is no table and nothing to round:
-//   * e4m3 codes convert EXACTLY to fp16 (cvt.rn.f16x2.e4m3x2, two codes per instruction) straight into
-//     MMA A fragments; the unrotated query is the fp16 B operand as it arrives; scales and sm_scale stay
-//     outside the operands in fp32: S^T = K Q^T has no operand rounding at all;
-//   * P x d_v (d_v: the V scale of the key and 128-half) is fed as fp16 value + fp16 residual, so
+// Tensor-core path for 8-bit layers in the canonical packing (one (page, kv head) run of 16 rows for K
+// and one for V).  Same persistent split-KV structure as the TQ4 stream kernel (plan launch, one share of
+// (request, kv head, 8-row group, page) units per worker warp, per-warp mbarrier ring filled by bulk
+// copies, partials merged by tq4_attention_merge_kernel in natural coordinates), but there is no table
+// and nothing to round:
+//   * the codes convert EXACTLY to fp16 straight into MMA A fragments: e4m3 with cvt.rn.f16x2.e4m3x2
+//     (two codes per instruction); int8 through the byte trick 0x6400 | (q ^ 0x80) = 1152 + q, minus
+//     1152.  The unrotated query is the fp16 B operand as it arrives; block scales and sm_scale stay
+//     outside the operands in fp32, one score accumulator per scale block: S^T = K Q^T has no operand
+//     rounding at all;
+//   * P x d_v (d_v: the V scale of the key and block) is fed as fp16 value + fp16 residual, so
 //     O^T += V^T (P d_v)^T carries P to about 2^-22.
-// Shared-memory reads are 64-bit and conflict-free with the rows as they lie in global memory (a
-// row is 66 words, so consecutive tokens are two banks apart):
-//   K: lane (gid, tig) reads its key's words 32 h + 8 tig + 2 j + {0, 1}  (h: 128-half, j = 0..3);
-//      the 4 codes of a word are the k positions {2 tig, 2 tig + 1, 2 tig + 8, 2 tig + 9} of one MMA
-//      step, and the query fragments are loaded in the same order;
-//   V: lane reads, for its four tokens, words base(gid) + 16 jj + {0, 1} with
-//      base = 2 (gid & 1) + 8 ((gid >> 1) & 1) + 4 (gid >> 2); two PRMTs pair the bytes of two tokens
-//      per channel (the k positions of an A register), each word giving two m-tiles.
+// Shared-memory reads are conflict-free:
+//   FP8 (264-byte rows = 66 words, consecutive tokens two banks apart, staged as they lie in memory),
+//   64-bit loads.  K: lane (gid, tig) reads its key's words 32 h + 8 tig + 2 j + {0, 1} (h: 128-half,
+//   j = 0..3); the 4 codes of a word are the k positions {2 tig, 2 tig + 1, 2 tig + 8, 2 tig + 9} of one
+//   MMA step and the query fragments are loaded in the same order.  V: lane reads, for its four tokens,
+//   words base(gid) + 16 jj + {0, 1}, base = 2 (gid & 1) + 8 ((gid >> 1) & 1) + 4 (gid >> 2); two PRMTs
+//   pair the bytes of two tokens per channel (the k positions of an A register), a word gives two m-tiles.
+//   Q8_0 (272-byte rows = 68 words: four blocks of {fp32 d; 64 int8}), staged as two 8-row halves 64
+//   bytes apart so that tokens 8-15 sit 16 banks from tokens 0-7; 32-bit loads.  K: code word tig + 4 s
+//   of block b (s = 0..3); V: code word gid + 8 x of block b (x = 0, 1).
 // ---------------------------------------------------------------------------------------------------
-constexpr int kFp8RowBytesA = kHeadDim + 8;                  // 264
-constexpr int kFp8RunBytes = kPageTokens * kFp8RowBytesA;    // 4224, a multiple of 16
-constexpr int kFp8StageBytes = 2 * kFp8RunBytes;             // K run, then V run
-constexpr int kFp8Warps = 8;
-constexpr int kFp8Stages = 3;
+template <int FMT> struct Kv8Stage;
+template <> struct Kv8Stage<WARP34_KV_FORMAT_FP8_E4M3> {
+    static constexpr int kRow = kHeadDim + 8;               // 264
+    static constexpr int kHalf = 8 * kRow;                  // 2112
+    static constexpr int kHalfStride = kHalf;               // the run is staged as it lies in memory
+    static constexpr int kRunStride = 2 * kHalf;            // 4224
+    static constexpr int kBlocks = 2;                       // scale blocks per row
+};
+template <> struct Kv8Stage<WARP34_KV_FORMAT_Q8_0> {
+    static constexpr int kRow = 4 * 68;                     // 272
+    static constexpr int kHalf = 8 * kRow;                  // 2176, a multiple of 16
+    static constexpr int kHalfStride = kHalf + 64;          // tokens 8-15 sixteen banks from tokens 0-7
+    static constexpr int kRunStride = 2 * kHalfStride;      // 4480
+    static constexpr int kBlocks = 4;
+};
+constexpr int kKv8StreamWarps = 8;
+constexpr int kKv8StreamStages = 3;
 
+template <int FMT>
+__host__ __device__ constexpr uint32_t kv8_token_offset(int t) {
+    return (uint32_t)((t >> 3) * Kv8Stage<FMT>::kHalfStride + (t & 7) * Kv8Stage<FMT>::kRow);
+}
 __device__ __forceinline__ uint2 lds64_dep(uint32_t addr, uint32_t token) {
     uint2 v;
     asm("ld.shared.v2.u32 {%0,%1}, [%2+0];  // dep %3" : "=r"(v.x), "=r"(v.y) : "r"(addr), "r"(token));
     return v;
 }
-// Four e4m3 codes -> two fp16 pairs (bytes 0,1 and bytes 2,3).
-__device__ __forceinline__ void e4m3x4_to_f16x4(uint32_t w, uint32_t& lo, uint32_t& hi) {
-    asm("{\n\t.reg .b16 l, h;\n\tmov.b32 {l, h}, %2;\n\tcvt.rn.f16x2.e4m3x2 %0, l;\n\tcvt.rn.f16x2.e4m3x2 %1, h;\n\t}"
-        : "=r"(lo), "=r"(hi) : "r"(w));
+// Four 8-bit codes -> two fp16 pairs (bytes 0,1 and bytes 2,3), exactly.
+template <int FMT>
+__device__ __forceinline__ void kv8x4_to_f16x4(uint32_t w, uint32_t& lo, uint32_t& hi) {
+    if (FMT == WARP34_KV_FORMAT_FP8_E4M3) {
+        asm("{\n\t.reg .b16 l, h;\n\tmov.b32 {l, h}, %2;\n\tcvt.rn.f16x2.e4m3x2 %0, l;\n\tcvt.rn.f16x2.e4m3x2 %1, h;\n\t}"
+            : "=r"(lo), "=r"(hi) : "r"(w));
+    } else {
+        const uint32_t x = w ^ 0x80808080u;                               // q + 128 as an unsigned byte
+        const uint32_t l = __byte_perm(x, 0x64646464u, 0x4140);           // halves 1024 + (q + 128)
+        const uint32_t h = __byte_perm(x, 0x64646464u, 0x4342);
+        const __half2 bias = __half2half2(__ushort_as_half((unsigned short)0x6480));   // 1152
+        const __half2 lh = __hsub2(*reinterpret_cast<const __half2*>(&l), bias);
+        const __half2 hh = __hsub2(*reinterpret_cast<const __half2*>(&h), bias);
+        lo = *reinterpret_cast<const uint32_t*>(&lh);
+        hi = *reinterpret_cast<const uint32_t*>(&hh);
+    }
 }
 
-template <int STAGES>
-__global__ void __launch_bounds__(kFp8Warps * 32, 1) fp8kv_attention_stream_kernel(const StreamParams p) {
+template <int FMT, int STAGES>
+__global__ void __launch_bounds__(kKv8StreamWarps * 32, 1) kv8_attention_stream_kernel(const StreamParams p) {
+    using G = Kv8Stage<FMT>;
+    constexpr bool FP8 = FMT == WARP34_KV_FORMAT_FP8_E4M3;
+    constexpr int NB = G::kBlocks;
+    constexpr uint32_t kStage = 2u * G::kRunStride;
     extern __shared__ __align__(1024) uint8_t smem[];
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-    constexpr uint32_t kRingBytes = STAGES * kFp8StageBytes;
+    constexpr uint32_t kRingBytes = STAGES * kStage;
     const uint32_t win_lo = smem_u32(smem);
     const uint32_t ring = win_lo + (uint32_t)wid * kRingBytes;
-    const uint32_t bars = win_lo + (uint32_t)kFp8Warps * kRingBytes + (uint32_t)wid * STAGES * 8u;
+    const uint32_t bars = win_lo + (uint32_t)kKv8StreamWarps * kRingBytes + (uint32_t)wid * STAGES * 8u;
     uint8_t* ring_gen = smem + (size_t)wid * kRingBytes;
     PlanHeader* hdr = reinterpret_cast<PlanHeader*>(p.scratch);
     if (lane == 0) {
@@ -346,9 +382,11 @@ __global__ void __launch_bounds__(kFp8Warps * 32, 1) fp8kv_attention_stream_kern
     // the output product: kv0 + {0, 1, 4, 5} at k positions 2 tig, 2 tig + 1, 2 tig + 8, 2 tig + 9.
     const int key_a = (gid & 3) + 8 * (gid >> 2);
     const int kv0 = 2 * (tig & 1) + 8 * (tig >> 1);
-    const uint32_t k_lane = (uint32_t)(key_a * kFp8RowBytesA + 32 * tig);
-    const uint32_t v_lane = (uint32_t)(kFp8RunBytes + kv0 * kFp8RowBytesA +
-                                       4 * (2 * (gid & 1) + 8 * ((gid >> 1) & 1) + 4 * (gid >> 2)));
+    const uint32_t krow_off = kv8_token_offset<FMT>(key_a);          // token key_a + 4 is 4 rows further
+    const uint32_t vrow_off = (uint32_t)G::kRunStride + kv8_token_offset<FMT>(kv0);
+    // first code word (of 64, in column order) of this lane in the K and in the V loads
+    const int kword0 = FP8 ? 8 * tig : tig;
+    const int vword0 = FP8 ? 2 * (gid & 1) + 8 * ((gid >> 1) & 1) + 4 * (gid >> 2) : gid;
     uint32_t phase_bits = 0, pending = 0;
     bool failed = false;
 
@@ -399,6 +437,8 @@ __global__ void __launch_bounds__(kFp8Warps * 32, 1) fp8kv_attention_stream_kern
         }
 
         // ---- query row gid of the group as B fragments, in the K loads' column order ----------------
+        // k-step ks reads code word kw(ks) of the row: columns 4 kw .. 4 kw + 3.
+        //   FP8: kw = 32 h + 8 tig + 2 j + x, ks = 2 (4 h + j) + x;  Q8_0: kw = 16 b + tig + 4 s, ks = 4 b + s
         uint32_t qb[16][2];
         {
             const int row = group * kRowsPerGroup + gid;
@@ -408,28 +448,20 @@ __global__ void __launch_bounds__(kFp8Warps * 32, 1) fp8kv_attention_stream_kern
                             (p.batch.valid_token_mask == nullptr || p.batch.valid_token_mask[g.q_start + q_off] != 0);
             const size_t q_base = ((size_t)(g.q_start + q_off) * p.num_q_heads + q_head) * kHeadDim;
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int col = 4 * (32 * h + 8 * tig + 2 * j);     // 8 columns, 16 bytes
-                    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-                    if (ok) {
-                        if (p.io_bf16) {
-                            uint32_t t[4];
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                t[e] = pack_half2(load_act(p.q_in, q_base + col + 2 * e, 1),
-                                                  load_act(p.q_in, q_base + col + 2 * e + 1, 1));
-                            }
-                            v = make_uint4(t[0], t[1], t[2], t[3]);
-                        } else {
-                            v = __ldg(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.q_in) + q_base + col));
-                        }
+            for (int ks = 0; ks < 16; ++ks) {
+                const int kw = FP8 ? 32 * (ks >> 3) + 2 * ((ks >> 1) & 3) + (ks & 1) + kword0
+                                   : 16 * (ks >> 2) + 4 * (ks & 3) + kword0;
+                uint2 v = make_uint2(0u, 0u);
+                if (ok) {
+                    if (p.io_bf16) {
+                        v.x = pack_half2(load_act(p.q_in, q_base + 4 * kw, 1), load_act(p.q_in, q_base + 4 * kw + 1, 1));
+                        v.y = pack_half2(load_act(p.q_in, q_base + 4 * kw + 2, 1), load_act(p.q_in, q_base + 4 * kw + 3, 1));
+                    } else {
+                        v = __ldg(reinterpret_cast<const uint2*>(static_cast<const uint16_t*>(p.q_in) + q_base + 4 * kw));
                     }
-                    const int ks = 2 * (4 * h + j);
-                    qb[ks][0] = v.x; qb[ks][1] = v.y;
-                    qb[ks + 1][0] = v.z; qb[ks + 1][1] = v.w;
                 }
+                qb[ks][0] = v.x;
+                qb[ks][1] = v.y;
             }
         }
         float o[16][4];
@@ -451,10 +483,19 @@ __global__ void __launch_bounds__(kFp8Warps * 32, 1) fp8kv_attention_stream_kern
             if (lane == 0) {
                 const int s = idx % STAGES;
                 const uint32_t bar = bars + 8u * s;
-                const uint32_t dst = ring + (uint32_t)s * kFp8StageBytes;
-                mbar_expect_tx(bar, 2 * kFp8RunBytes);
-                bulk_g2s(dst, k_head_base + (size_t)page * p.layout.k_page_stride_bytes, kFp8RunBytes, bar);
-                bulk_g2s(dst + kFp8RunBytes, v_head_base + (size_t)page * p.layout.v_page_stride_bytes, kFp8RunBytes, bar);
+                const uint32_t dst = ring + (uint32_t)s * kStage;
+                const uint8_t* ksrc = k_head_base + (size_t)page * p.layout.k_page_stride_bytes;
+                const uint8_t* vsrc = v_head_base + (size_t)page * p.layout.v_page_stride_bytes;
+                mbar_expect_tx(bar, 4 * G::kHalf);
+                if (G::kHalfStride == G::kHalf) {
+                    bulk_g2s(dst, ksrc, 2 * G::kHalf, bar);
+                    bulk_g2s(dst + G::kRunStride, vsrc, 2 * G::kHalf, bar);
+                } else {
+                    bulk_g2s(dst, ksrc, G::kHalf, bar);
+                    bulk_g2s(dst + G::kHalfStride, ksrc + G::kHalf, G::kHalf, bar);
+                    bulk_g2s(dst + G::kRunStride, vsrc, G::kHalf, bar);
+                    bulk_g2s(dst + G::kRunStride + G::kHalfStride, vsrc + G::kHalf, G::kHalf, bar);
+                }
             }
         };
 #pragma unroll 1
@@ -476,52 +517,91 @@ __global__ void __launch_bounds__(kFp8Warps * 32, 1) fp8kv_attention_stream_kern
             phase_bits ^= 1u << s;
             pending &= ~(1u << s);
 
-            const uint32_t st = ring + (uint32_t)s * kFp8StageBytes;
+            const uint32_t st = ring + (uint32_t)s * kStage;
             const int kv_base = (pg0 + i) << 4;
             const bool full = (kv_base >= safe_lo) && (kv_base + 15 <= safe_hi);
-            // Tokens past the last visible key may never have been written: their code bytes can be
-            // NaN patterns, and 0 x NaN is NaN inside the MMA.  Their V rows are cleared in the stage.
-            if (kv_base + 15 > kv_hi) {
-                const int first = max(kv_hi + 1 - kv_base, 0);
-                for (int w = first * (kFp8RowBytesA / 4) + lane; w < kPageTokens * (kFp8RowBytesA / 4); w += 32) {
-                    sts32(st + kFp8RunBytes + 4u * (uint32_t)w, 0u);
+            // Tokens past the last visible key may never have been written: as e4m3 codes their bytes can
+            // be NaN patterns, and 0 x NaN is NaN inside the MMA.  Their V rows are cleared in the stage.
+            const bool clear_tail = FP8 && (kv_base + 15 > kv_hi);
+            if (clear_tail) {
+                for (int t = max(kv_hi + 1 - kv_base, 0); t < kPageTokens; ++t) {
+                    for (int w = lane; w < G::kRow / 4; w += 32) {
+                        sts32(st + (uint32_t)G::kRunStride + kv8_token_offset<FMT>(t) + 4u * (uint32_t)w, 0u);
+                    }
                 }
                 __syncwarp();
             }
             const uint32_t ptok = page_token(i);
 
-            // ---- S^T = K Q^T: one accumulator per 128-half, exact operands ---------------------------
-            float sa[2][4];
-            const uint32_t krow_a = st + k_lane, krow_b = krow_a + 4u * kFp8RowBytesA;
+            // ---- S^T = K Q^T: one accumulator per scale block, exact operands -------------------------
+            float sa[NB][4];
+            const uint32_t krow_a = st + krow_off, krow_b = krow_a + 4u * G::kRow;
+            if (FP8) {
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
+                for (int h = 0; h < 2; ++h) {
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const uint2 wa = lds64_dep(krow_a + 4u * (32u * h + 2u * j), ptok);
-                    const uint2 wb = lds64_dep(krow_b + 4u * (32u * h + 2u * j), ptok);
-                    uint32_t a0, a1, a2, a3;
-                    const int ks = 2 * (4 * h + j);
-                    e4m3x4_to_f16x4(wa.x, a0, a2);
-                    e4m3x4_to_f16x4(wb.x, a1, a3);
-                    if (j == 0) mma16816_zero(sa[h], a0, a1, a2, a3, qb[ks][0], qb[ks][1]);
-                    else mma16816(sa[h], a0, a1, a2, a3, qb[ks][0], qb[ks][1]);
-                    e4m3x4_to_f16x4(wa.y, a0, a2);
-                    e4m3x4_to_f16x4(wb.y, a1, a3);
-                    mma16816(sa[h], a0, a1, a2, a3, qb[ks + 1][0], qb[ks + 1][1]);
+                    for (int j = 0; j < 4; ++j) {
+                        const uint32_t off = 4u * (uint32_t)(32 * h + 2 * j + kword0);
+                        const uint2 wa = lds64_dep(krow_a + off, ptok);
+                        const uint2 wb = lds64_dep(krow_b + off, ptok);
+                        uint32_t a0, a1, a2, a3;
+                        const int ks = 2 * (4 * h + j);
+                        kv8x4_to_f16x4<FMT>(wa.x, a0, a2);
+                        kv8x4_to_f16x4<FMT>(wb.x, a1, a3);
+                        if (j == 0) mma16816_zero(sa[h], a0, a1, a2, a3, qb[ks][0], qb[ks][1]);
+                        else mma16816(sa[h], a0, a1, a2, a3, qb[ks][0], qb[ks][1]);
+                        kv8x4_to_f16x4<FMT>(wa.y, a0, a2);
+                        kv8x4_to_f16x4<FMT>(wb.y, a1, a3);
+                        mma16816(sa[h], a0, a1, a2, a3, qb[ks + 1][0], qb[ks + 1][1]);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+#pragma unroll
+                    for (int s4 = 0; s4 < 4; ++s4) {
+                        const uint32_t off = (uint32_t)(68 * b + 4 + 4 * (4 * s4 + kword0));
+                        const uint32_t wa = lds32_dep(krow_a + off, ptok);
+                        const uint32_t wb = lds32_dep(krow_b + off, ptok);
+                        uint32_t a0, a1, a2, a3;
+                        kv8x4_to_f16x4<FMT>(wa, a0, a2);
+                        kv8x4_to_f16x4<FMT>(wb, a1, a3);
+                        if (s4 == 0) mma16816_zero(sa[b], a0, a1, a2, a3, qb[4 * b][0], qb[4 * b][1]);
+                        else mma16816(sa[b], a0, a1, a2, a3, qb[4 * b + s4][0], qb[4 * b + s4][1]);
+                    }
                 }
             }
-            // scales of this lane's two keys (two floats behind the 256 codes), K and V
-            const uint2 dka = lds64_dep(st + (uint32_t)(key_a * kFp8RowBytesA + kHeadDim), ptok);
-            const uint2 dkb = lds64_dep(st + (uint32_t)((key_a + 4) * kFp8RowBytesA + kHeadDim), ptok);
-            const uint2 dva_w = lds64_dep(st + (uint32_t)(kFp8RunBytes + key_a * kFp8RowBytesA + kHeadDim), ptok);
-            const uint2 dvb_w = lds64_dep(st + (uint32_t)(kFp8RunBytes + (key_a + 4) * kFp8RowBytesA + kHeadDim), ptok);
-            float dva0 = __uint_as_float(dva_w.x), dva1 = __uint_as_float(dva_w.y);
-            float dvb0 = __uint_as_float(dvb_w.x), dvb1 = __uint_as_float(dvb_w.y);
-            float sc[4];
-            sc[0] = (__uint_as_float(dka.x) * sa[0][0] + __uint_as_float(dka.y) * sa[1][0]) * p.q_scale;
-            sc[1] = (__uint_as_float(dka.x) * sa[0][1] + __uint_as_float(dka.y) * sa[1][1]) * p.q_scale;
-            sc[2] = (__uint_as_float(dkb.x) * sa[0][2] + __uint_as_float(dkb.y) * sa[1][2]) * p.q_scale;
-            sc[3] = (__uint_as_float(dkb.x) * sa[0][3] + __uint_as_float(dkb.y) * sa[1][3]) * p.q_scale;
+            // block scales of this lane's two keys, K then V (fp32 words)
+            float dka[NB], dkb[NB], dva[NB], dvb[NB];
+            {
+                const uint32_t vrow_a = st + (uint32_t)G::kRunStride + krow_off, vrow_b = vrow_a + 4u * G::kRow;
+                if (FP8) {
+                    const uint2 a = lds64_dep(krow_a + kHeadDim, ptok), b2 = lds64_dep(krow_b + kHeadDim, ptok);
+                    const uint2 c = lds64_dep(vrow_a + kHeadDim, ptok), d = lds64_dep(vrow_b + kHeadDim, ptok);
+                    dka[0] = __uint_as_float(a.x); dka[1] = __uint_as_float(a.y);
+                    dkb[0] = __uint_as_float(b2.x); dkb[1] = __uint_as_float(b2.y);
+                    dva[0] = __uint_as_float(c.x); dva[1] = __uint_as_float(c.y);
+                    dvb[0] = __uint_as_float(d.x); dvb[1] = __uint_as_float(d.y);
+                } else {
+#pragma unroll
+                    for (int b = 0; b < NB; ++b) {
+                        dka[b] = __uint_as_float(lds32_dep(krow_a + 68u * b, ptok));
+                        dkb[b] = __uint_as_float(lds32_dep(krow_b + 68u * b, ptok));
+                        dva[b] = __uint_as_float(lds32_dep(vrow_a + 68u * b, ptok));
+                        dvb[b] = __uint_as_float(lds32_dep(vrow_b + 68u * b, ptok));
+                    }
+                }
+            }
+            float sc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+            for (int b = 0; b < NB; ++b) {
+                sc[0] += dka[b] * sa[b][0];
+                sc[1] += dka[b] * sa[b][1];
+                sc[2] += dkb[b] * sa[b][2];
+                sc[3] += dkb[b] * sa[b][3];
+            }
+#pragma unroll
+            for (int x = 0; x < 4; ++x) sc[x] *= p.q_scale;
 
             bool msk[4] = {false, false, false, false};
             if (!full) {
@@ -560,57 +640,77 @@ __global__ void __launch_bounds__(kFp8Warps * 32, 1) fp8kv_attention_stream_kern
             if (!full) {
 #pragma unroll
                 for (int x = 0; x < 4; ++x) if (msk[x]) pr[x] = 0.0f;
-                // a key no row can see may hold never-written bytes: keep its scale finite
-                if (msk[0] && msk[1]) { dva0 = 0.0f; dva1 = 0.0f; }
-                if (msk[2] && msk[3]) { dvb0 = 0.0f; dvb1 = 0.0f; }
+                // a key no row can see may hold never-written bytes: keep its scales finite
+                if (msk[0] && msk[1]) {
+#pragma unroll
+                    for (int b = 0; b < NB; ++b) dva[b] = 0.0f;
+                }
+                if (msk[2] && msk[3]) {
+#pragma unroll
+                    for (int b = 0; b < NB; ++b) dvb[b] = 0.0f;
+                }
             }
             l_run[0] += pr[0] + pr[2];
             l_run[1] += pr[1] + pr[3];
-            // P x d_v per 128-half as B fragments (k = key, n = query row): fp16 value + fp16 residual
-            uint32_t pb[2][2], pl[2][2];
-            const float pd[2][4] = {{pr[0] * dva0, pr[1] * dva0, pr[2] * dvb0, pr[3] * dvb0},
-                                    {pr[0] * dva1, pr[1] * dva1, pr[2] * dvb1, pr[3] * dvb1}};
+            // P x d_v per scale block as B fragments (k = key, n = query row): fp16 value + fp16 residual
+            uint32_t pb[NB][2], pl[NB][2];
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
+            for (int b = 0; b < NB; ++b) {
+                const float pd[4] = {pr[0] * dva[b], pr[1] * dva[b], pr[2] * dvb[b], pr[3] * dvb[b]};
 #pragma unroll
                 for (int x = 0; x < 2; ++x) {
-                    const __half2 hi = __floats2half2_rn(pd[h][2 * x], pd[h][2 * x + 1]);
+                    const __half2 hi = __floats2half2_rn(pd[2 * x], pd[2 * x + 1]);
                     const float2 hf = __half22float2(hi);
-                    const __half2 lo = __floats2half2_rn(pd[h][2 * x] - hf.x, pd[h][2 * x + 1] - hf.y);
-                    pb[h][x] = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&hi));
-                    pl[h][x] = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&lo));
+                    const __half2 lo = __floats2half2_rn(pd[2 * x] - hf.x, pd[2 * x + 1] - hf.y);
+                    pb[b][x] = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&hi));
+                    pl[b][x] = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&lo));
                 }
             }
 
-            // ---- O^T += V^T (P d_v)^T ---------------------------------------------------------------
-            const uint32_t vr = st + v_lane;
+            // ---- O^T += V^T (P d_v)^T: m-tile mt covers the channels of code word vw(mt >> 1) -----------
+            //   FP8: vw = vword0 + 16 jj + x, mt = 4 jj + 2 x + ps;  Q8_0: vw = 16 b + vword0 + 8 x, mt = 4 b + 2 x + ps
+            const uint32_t vr = st + vrow_off;
+            auto pv_word = [&](uint32_t t0, uint32_t t1, uint32_t t2, uint32_t t3, int mt, int blk) {
+                // bytes (token a, token b) of channels 0, 1 | 2, 3 of the word
+                const uint32_t ab01 = __byte_perm(t0, t1, 0x5140), ab23 = __byte_perm(t0, t1, 0x7362);
+                const uint32_t cd01 = __byte_perm(t2, t3, 0x5140), cd23 = __byte_perm(t2, t3, 0x7362);
+                uint32_t a0, a1, a2, a3;
+                kv8x4_to_f16x4<FMT>(ab01, a0, a1);
+                kv8x4_to_f16x4<FMT>(cd01, a2, a3);
+                mma16816(o[mt], a0, a1, a2, a3, pb[blk][0], pb[blk][1]);
+                mma16816(o[mt], a0, a1, a2, a3, pl[blk][0], pl[blk][1]);
+                kv8x4_to_f16x4<FMT>(ab23, a0, a1);
+                kv8x4_to_f16x4<FMT>(cd23, a2, a3);
+                mma16816(o[mt + 1], a0, a1, a2, a3, pb[blk][0], pb[blk][1]);
+                mma16816(o[mt + 1], a0, a1, a2, a3, pl[blk][0], pl[blk][1]);
+            };
+            if (FP8) {
 #pragma unroll
-            for (int jj = 0; jj < 4; ++jj) {
-                const int half = jj >> 1;
-                const uint2 w0 = lds64_dep(vr + 64u * jj, ptok);
-                const uint2 w1 = lds64_dep(vr + kFp8RowBytesA + 64u * jj, ptok);
-                const uint2 w2 = lds64_dep(vr + 4u * kFp8RowBytesA + 64u * jj, ptok);
-                const uint2 w3 = lds64_dep(vr + 5u * kFp8RowBytesA + 64u * jj, ptok);
+                for (int jj = 0; jj < 4; ++jj) {
+                    const uint32_t off = 4u * (uint32_t)(vword0 + 16 * jj);
+                    const uint2 w0 = lds64_dep(vr + off, ptok);
+                    const uint2 w1 = lds64_dep(vr + G::kRow + off, ptok);
+                    const uint2 w2 = lds64_dep(vr + 4u * G::kRow + off, ptok);
+                    const uint2 w3 = lds64_dep(vr + 5u * G::kRow + off, ptok);
+                    pv_word(w0.x, w1.x, w2.x, w3.x, 4 * jj, jj >> 1);
+                    pv_word(w0.y, w1.y, w2.y, w3.y, 4 * jj + 2, jj >> 1);
+                }
+            } else {
 #pragma unroll
-                for (int x = 0; x < 2; ++x) {
-                    const uint32_t t0 = x ? w0.y : w0.x, t1 = x ? w1.y : w1.x;
-                    const uint32_t t2 = x ? w2.y : w2.x, t3 = x ? w3.y : w3.x;
-                    // bytes (token a, token b) of channels 0, 1 | 2, 3 of the word
-                    const uint32_t ab01 = __byte_perm(t0, t1, 0x5140), ab23 = __byte_perm(t0, t1, 0x7362);
-                    const uint32_t cd01 = __byte_perm(t2, t3, 0x5140), cd23 = __byte_perm(t2, t3, 0x7362);
-                    uint32_t a0, a1, a2, a3;
-                    e4m3x4_to_f16x4(ab01, a0, a1);
-                    e4m3x4_to_f16x4(cd01, a2, a3);
-                    mma16816(o[4 * jj + 2 * x], a0, a1, a2, a3, pb[half][0], pb[half][1]);
-                    mma16816(o[4 * jj + 2 * x], a0, a1, a2, a3, pl[half][0], pl[half][1]);
-                    e4m3x4_to_f16x4(ab23, a0, a1);
-                    e4m3x4_to_f16x4(cd23, a2, a3);
-                    mma16816(o[4 * jj + 2 * x + 1], a0, a1, a2, a3, pb[half][0], pb[half][1]);
-                    mma16816(o[4 * jj + 2 * x + 1], a0, a1, a2, a3, pl[half][0], pl[half][1]);
+                for (int b = 0; b < 4; ++b) {
+#pragma unroll
+                    for (int x = 0; x < 2; ++x) {
+                        const uint32_t off = (uint32_t)(68 * b + 4 + 4 * (vword0 + 8 * x));
+                        const uint32_t t0 = lds32_dep(vr + off, ptok);
+                        const uint32_t t1 = lds32_dep(vr + G::kRow + off, ptok);
+                        const uint32_t t2 = lds32_dep(vr + 4u * G::kRow + off, ptok);
+                        const uint32_t t3 = lds32_dep(vr + 5u * G::kRow + off, ptok);
+                        pv_word(t0, t1, t2, t3, 4 * b + 2 * x, b);
+                    }
                 }
             }
             __syncwarp();   // every lane is done with stage s before it is refilled
-            if (kv_base + 15 > kv_hi) fence_proxy_async();   // the cleared rows precede the next copy into s
+            if (clear_tail) fence_proxy_async();   // the cleared rows precede the next copy into s
         }
 
         if (failed) {
@@ -628,20 +728,13 @@ __global__ void __launch_bounds__(kFp8Warps * 32, 1) fp8kv_attention_stream_kern
             l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], d);
         }
         float* stage_o = reinterpret_cast<float*>(ring_gen);   // [8 rows][256]
-        const int wbase = 2 * (gid & 1) + 8 * ((gid >> 1) & 1) + 4 * (gid >> 2);
 #pragma unroll
-        for (int jj = 0; jj < 4; ++jj) {
-#pragma unroll
-            for (int x = 0; x < 2; ++x) {
-#pragma unroll
-                for (int ps = 0; ps < 2; ++ps) {
-                    // m-tile 4 jj + 2 x + ps: row gid = channel c, row gid + 8 = channel c + 1
-                    const int c = 4 * (wbase + 16 * jj + x) + 2 * ps;
-                    const float* acc = o[4 * jj + 2 * x + ps];
-                    *reinterpret_cast<float2*>(stage_o + (2 * tig) * kHeadDim + c) = make_float2(acc[0], acc[2]);
-                    *reinterpret_cast<float2*>(stage_o + (2 * tig + 1) * kHeadDim + c) = make_float2(acc[1], acc[3]);
-                }
-            }
+        for (int mt = 0; mt < 16; ++mt) {
+            // m-tile mt: row gid = channel c, row gid + 8 = channel c + 1
+            const int vw = FP8 ? vword0 + 16 * (mt >> 2) + ((mt >> 1) & 1) : 16 * (mt >> 2) + vword0 + 8 * ((mt >> 1) & 1);
+            const int c = 4 * vw + 2 * (mt & 1);
+            *reinterpret_cast<float2*>(stage_o + (2 * tig) * kHeadDim + c) = make_float2(o[mt][0], o[mt][2]);
+            *reinterpret_cast<float2*>(stage_o + (2 * tig + 1) * kHeadDim + c) = make_float2(o[mt][1], o[mt][3]);
         }
         __syncwarp();
         if (slot < p.max_slots) {
@@ -669,22 +762,24 @@ static bool kv8_attention_layout_ok(const warp34_kv_layer_layout* l) {
            l->k_transform == WARP34_KV_TRANSFORM_IDENTITY && l->v_transform == WARP34_KV_TRANSFORM_IDENTITY;
 }
 
-// The tensor-core path serves FP8 E4M3 K and V in the canonical packing with 16-byte-aligned runs, a
-// 16-byte-aligned query and a workspace that holds the plan and at least one CTA's partial slots.
-static bool fp8_stream_ok(const warp34_exec* ex, const warp34_kv_layer_layout* l, const warp34_attention_batch* b,
+// The tensor-core path serves K and V of one 8-bit format in the canonical packing with 16-byte-aligned
+// runs, an 8-byte-aligned query and a workspace that holds the plan and at least one CTA's partial slots.
+static bool kv8_stream_ok(const warp34_exec* ex, const warp34_kv_layer_layout* l, const warp34_attention_batch* b,
                           const void* q_in, int io_bf16) {
-    if (l->k_format != WARP34_KV_FORMAT_FP8_E4M3 || l->v_format != WARP34_KV_FORMAT_FP8_E4M3) return false;
-    if (l->k_token_stride_bytes != (uint64_t)kFp8RowBytesA || l->v_token_stride_bytes != (uint64_t)kFp8RowBytesA) return false;
+    if (l->k_format != l->v_format) return false;
+    const uint64_t row = l->k_format == WARP34_KV_FORMAT_FP8_E4M3 ? (uint64_t)Kv8Stage<WARP34_KV_FORMAT_FP8_E4M3>::kRow
+                                                                  : (uint64_t)Kv8Stage<WARP34_KV_FORMAT_Q8_0>::kRow;
+    if (l->k_token_stride_bytes != row || l->v_token_stride_bytes != row) return false;
     if ((l->k_base | l->v_base | l->k_page_stride_bytes | l->v_page_stride_bytes | l->k_head_stride_bytes |
          l->v_head_stride_bytes) & 15u) {
         return false;
     }
-    if (!io_bf16 && ((uintptr_t)q_in & 15u) != 0) return false;
+    if (!io_bf16 && ((uintptr_t)q_in & 7u) != 0) return false;
     if (b->block_tables == nullptr || b->max_blocks_per_req <= 0) return false;
     return ex->scratch_ptr != 0 && (ex->scratch_ptr & 15u) == 0;
 }
 
-static int launch_fp8_stream(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
+static int launch_kv8_stream(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
                              const warp34_attention_batch* batch, const void* q_in, void* attn_out,
                              int num_q_heads, int io_bf16, bool* taken) {
     *taken = false;
@@ -697,10 +792,13 @@ static int launch_fp8_stream(const warp34_exec* ex, const warp34_kv_layer_layout
     const size_t slot_bytes = (size_t)kPartialFloats * sizeof(float);
     const size_t avail = ex->scratch_size > plan ? ex->scratch_size - plan : 0;
     const long long workers = (long long)(avail / slot_bytes) - items;
-    if (workers < kFp8Warps) return 0;            // the caller falls back to the fp32 kernel
+    if (workers < kKv8StreamWarps) return 0;      // the caller falls back to the fp32 kernel
     int grid = dev->sm_count;
-    if (workers / kFp8Warps < grid) grid = (int)(workers / kFp8Warps);
-    const uint32_t smem = (uint32_t)(kFp8Warps * kFp8Stages * kFp8StageBytes + kFp8Warps * kFp8Stages * 8);
+    if (workers / kKv8StreamWarps < grid) grid = (int)(workers / kKv8StreamWarps);
+    const bool fp8 = layout->k_format == WARP34_KV_FORMAT_FP8_E4M3;
+    const uint32_t stage = 2u * (uint32_t)(fp8 ? Kv8Stage<WARP34_KV_FORMAT_FP8_E4M3>::kRunStride
+                                               : Kv8Stage<WARP34_KV_FORMAT_Q8_0>::kRunStride);
+    const uint32_t smem = (uint32_t)(kKv8StreamWarps * kKv8StreamStages) * (stage + 8u);
     {
         static std::mutex mu;
         static bool done[64];
@@ -710,8 +808,15 @@ static int launch_fp8_stream(const warp34_exec* ex, const warp34_kv_layer_layout
         if (d < 0 || d >= 64) return (int)cudaErrorInvalidDevice;
         std::lock_guard<std::mutex> lock(mu);
         if (!done[d]) {
-            rc = (int)cudaFuncSetAttribute(fp8kv_attention_stream_kernel<kFp8Stages>,
-                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            rc = (int)cudaFuncSetAttribute(kv8_attention_stream_kernel<WARP34_KV_FORMAT_FP8_E4M3, kKv8StreamStages>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (int)((uint32_t)(kKv8StreamWarps * kKv8StreamStages) *
+                                                 (2u * Kv8Stage<WARP34_KV_FORMAT_FP8_E4M3>::kRunStride + 8u)));
+            if (rc != 0) return rc;
+            rc = (int)cudaFuncSetAttribute(kv8_attention_stream_kernel<WARP34_KV_FORMAT_Q8_0, kKv8StreamStages>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (int)((uint32_t)(kKv8StreamWarps * kKv8StreamStages) *
+                                                 (2u * Kv8Stage<WARP34_KV_FORMAT_Q8_0>::kRunStride + 8u)));
             if (rc != 0) return rc;
             done[d] = true;
         }
@@ -728,7 +833,7 @@ static int launch_fp8_stream(const warp34_exec* ex, const warp34_kv_layer_layout
     p.scratch = reinterpret_cast<uint8_t*>((uintptr_t)ex->scratch_ptr);
     p.num_q_heads = num_q_heads;
     p.gqa = num_q_heads / layout->local_kv_heads;
-    p.num_warps = grid * kFp8Warps;
+    p.num_warps = grid * kKv8StreamWarps;
     p.max_slots = (int)(p.num_warps + items);
     p.smem_bytes = smem;
     p.rows_per_group = kRowsPerGroup;
@@ -738,9 +843,13 @@ static int launch_fp8_stream(const warp34_exec* ex, const warp34_kv_layer_layout
     p.q_groups_max = 0;
     cudaStream_t st = (cudaStream_t)ex->stream;
     tq4_attention_plan_kernel<<<1, 32, 0, st>>>(p);
-    fp8kv_attention_stream_kernel<kFp8Stages><<<grid, kFp8Warps * 32, smem, st>>>(p);
+    if (fp8) {
+        kv8_attention_stream_kernel<WARP34_KV_FORMAT_FP8_E4M3, kKv8StreamStages><<<grid, kKv8StreamWarps * 32, smem, st>>>(p);
+    } else {
+        kv8_attention_stream_kernel<WARP34_KV_FORMAT_Q8_0, kKv8StreamStages><<<grid, kKv8StreamWarps * 32, smem, st>>>(p);
+    }
     const long long rows = (long long)batch->total_tokens * num_q_heads;
-    if (rows * 4 < (long long)grid * kFp8Warps / 8) {
+    if (rows * 4 < (long long)grid * kKv8StreamWarps / 8) {
         tq4_attention_merge_kernel<false, 32><<<(unsigned)rows, 1024, 0, st>>>(p);
     } else {
         tq4_attention_merge_kernel<false, 4><<<(unsigned)rows, 128, 0, st>>>(p);
@@ -759,9 +868,9 @@ static int launch_kv8_attention(const warp34_exec* ex, const warp34_kv_layer_lay
         return (int)cudaErrorInvalidValue;
     }
     if (layout->k_base == 0 || layout->v_base == 0) return (int)cudaErrorInvalidValue;
-    if (allow_stream && fp8_stream_ok(ex, layout, batch, q_in, io_bf16)) {
+    if (allow_stream && kv8_stream_ok(ex, layout, batch, q_in, io_bf16)) {
         bool taken = false;
-        const int rc = launch_fp8_stream(ex, layout, batch, q_in, attn_out, num_q_heads, io_bf16, &taken);
+        const int rc = launch_kv8_stream(ex, layout, batch, q_in, attn_out, num_q_heads, io_bf16, &taken);
         if (rc != 0 || taken) return rc;
     }
     if ((layout->k_base | layout->v_base | layout->k_page_stride_bytes | layout->k_head_stride_bytes |
