@@ -479,6 +479,89 @@ def run_chunked_prefill(args):
     print(json.dumps(line))
 
 
+def run_qsa_sparse(args):
+    """`--config qsa_sparse_decode`: query-sparse paged attention over TQ4 pages, one decode step of
+    config 1's geometry: every token attends to 256 selected 4-token groups (1024 keys) of its sequence.
+    `--impl reference` times the reference's own kernel (oracle/_ref) on the same lists."""
+    import ctypes as C
+    import oracle
+    from warp34_b200 import ffi, kv, synth
+    reference = args.impl == "reference"
+    ref_path = oracle.ref_lib_path() if reference else None
+    if reference and ref_path is None:
+        print(json.dumps({"impl": "reference", "unavailable": "reference kernels not built (oracle/_ref missing)"}))
+        return
+    lib = C.CDLL(ref_path) if reference else ffi.kernels()
+    hq, hkv, batch, lo, hi, _, seed = synth.CONFIGS["cfg1_batched_decode"]
+    if args.batch > 0:
+        batch = args.batch
+    select_k = 256
+    ctx = [int(c) for c in synth.context_lengths(batch, lo, hi, seed)]
+    wl = synth.PagedWorkload(ctx, [0] * batch, hkv, seed=seed)
+    ex = kv.Executor(64 << 20)
+    wl.fill_context(ex, seed, chunk_tokens=32768)
+    rng = np.random.default_rng(seed)
+    phys = np.full((batch, select_k), -1, np.int32)
+    logical = np.zeros((batch, select_k), np.int32)
+    for t, c in enumerate(ctx):
+        pages = wl.seqs[t].pages
+        own = (c - 1) // 4
+        pick = np.concatenate([[own], rng.choice(own, select_k - 1, replace=False)])
+        logical[t] = pick
+        phys[t] = np.asarray(pages, np.int64)[pick // 4] * 4 + pick % 4
+    dev = [torch.from_numpy(a).cuda() for a in (phys, logical, np.full(batch, select_k, np.int32),
+                                                np.asarray(ctx, np.int32) - 1)]
+    q = synth.make_q(batch, hq, seed + 17).cuda()
+    gate = synth.make_q(batch, hq, seed + 18).cuda()
+    out = torch.zeros_like(q)
+    fn = lib.warp34_qsa_sparse_paged_attn_f16
+    fn.restype = C.c_int
+    fn.argtypes = [C.c_void_p] * 10 + [C.c_int, C.c_int, C.c_int, C.c_float]
+    ex.set_stream()
+
+    def one():
+        rc = fn(C.addressof(ex.ex), q.data_ptr(), gate.data_ptr(), C.addressof(wl.layer.layout), dev[0].data_ptr(),
+                dev[1].data_ptr(), dev[2].data_ptr(), dev[3].data_ptr(), None, out.data_ptr(), batch, hq, select_k, 0.0625)
+        assert rc == 0, rc
+
+    sampler = ClockSampler(0)
+    sampler.start()
+    for _ in range(args.warmup):
+        one()
+    torch.cuda.synchronize()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    t_begin = time.perf_counter()
+    for a, b in evs:
+        flush.zero_()              # the selected rows of a step fit in L2: evict them between steps
+        a.record()
+        one()
+        b.record()
+    torch.cuda.synchronize()
+    t_end = time.perf_counter()
+    sampler.stop_flag = True
+    ms = float(np.median([a.elapsed_time(b) for a, b in evs]))
+    kv_bytes = batch * hkv * select_k * 4 * 264
+    peaks, peak_kind = measured_peaks()
+    peak = float(peaks.get("hbm_gbs", FALLBACK_HBM_GBS))
+    achieved = kv_bytes / (ms * 1e-3) / 1e9
+    line = {"metric": "qsa_sparse_attention_kv_gbps", "value": achieved, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"qsa_sparse_decode: {batch} tokens x {select_k} selected 4-token groups of contexts "
+                                   f"U[{lo},{hi}], {hq} q heads / {hkv} kv heads, d256, TQ4 pages, sigmoid gate",
+                       "kv_bytes_per_step": kv_bytes, "l2": "a 256 MB buffer is written between timed steps"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_kind": f"of {peak_kind}", "kernel": "qsa_sparse_attention_kernel (+ merge)", "launch_ms": ms,
+                         "traffic": None},
+            "gpu_launches": 2 * args.steps, "clocks": sampler.summary(t_begin, t_end)}
+    if reference:
+        line["impl"] = "reference"
+        line["roofline"]["kernel"] = "reference qsa_sparse_paged_attn_gqa_f16_kernel (+ merge)"
+        line["gpu_launches"] = None
+    print(json.dumps(line))
+
+
 def run_other_kv(args):
     """The same decode step over another storage format of the reference, device-resident, one GPU:
     `--kv bf16` uncompressed BF16 pages (1024 B per token and KV head instead of 264; the comparison
@@ -591,6 +674,8 @@ def main():
                          "unrotated 8-bit rows of the boundary layers (one GPU each)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.config == "qsa_sparse_decode":
+        return run_qsa_sparse(args)
     if args.kv != "tq4":
         return run_other_kv(args)
     if args.config == "cfg2_chunked_prefill":

@@ -431,6 +431,37 @@ int warp34_paged_attention_f16_static_scratch(uintptr_t stream, const warp34_kv_
 int warp34_static_scratch_status(int32_t* status_out);
 
 /*
+ * Query-sparse paged attention: every token attends only to its list of selected 4-token groups.
+ * Replaces warp34_qsa_sparse_paged_attn_f16 / _hadamard_f16 (warp34_cuda.h, QSA section;
+ * crates/warp34-kernels/csrc/ops/op_qsa.cu:716-1572, entry points :1711-1752) with the same
+ * signatures and semantics:
+ *   q, gate, out            fp16 [num_tokens, local_q_heads, 256]; gate may be NULL
+ *   selected_phys_blocks    [num_tokens, select_k_blocks] physical group ids (page * 4 + group in page;
+ *                           negative = skip), selected_logical_blocks their logical group indices: key
+ *                           (entry, off) sits at position 4 * logical + off and takes part iff that is
+ *                           <= token_seq_pos[token]; only the first num_selected_blocks[token] entries are read
+ *   valid_token_mask        may be NULL; a masked token's output rows are written as zeros
+ * The sigmoid gate multiplies the fp32 result; the _hadamard variant then rounds to fp16 and applies the
+ * normalised 64-point Hadamard to every 64 columns.  Layers: head_dim 256, 16-token pages, K and V each
+ * TQ4 with the Rademacher + WHT-256 rotation or Q8_0 / FP8 E4M3 unrotated, any strides; FP16 rows, which
+ * the reference's kernel also reads, are refused with cudaErrorNotSupported like everywhere else here.
+ * An fp32 dequant-then-attend kernel; ex->scratch_ptr, when set, lets it split a token's list over several
+ * blocks (num_tokens * local_q_heads * 1032 bytes per split).
+ */
+int warp34_qsa_sparse_paged_attn_f16(const warp34_exec* ex, const void* q, const void* gate,
+                                     const warp34_kv_layer_layout* kv_layout, const int32_t* selected_phys_blocks,
+                                     const int32_t* selected_logical_blocks, const int32_t* num_selected_blocks,
+                                     const int32_t* token_seq_pos, const uint8_t* valid_token_mask, void* out,
+                                     int num_tokens, int local_q_heads, int select_k_blocks, float sm_scale);
+int warp34_qsa_sparse_paged_attn_hadamard_f16(const warp34_exec* ex, const void* q, const void* gate,
+                                              const warp34_kv_layer_layout* kv_layout,
+                                              const int32_t* selected_phys_blocks,
+                                              const int32_t* selected_logical_blocks,
+                                              const int32_t* num_selected_blocks, const int32_t* token_seq_pos,
+                                              const uint8_t* valid_token_mask, void* out, int num_tokens,
+                                              int local_q_heads, int select_k_blocks, float sm_scale);
+
+/*
  * Bounds-checked build (stand-in for the reference's sanitizer runs of this path,
  * tools/check_cuda_sanitizer.py:77-102).  A library compiled with -DW34_BOUNDS
  * (`python -m warp34_b200.build --bounds` -> libwarp34_b200_bounds.so) range-checks, in every kernel,

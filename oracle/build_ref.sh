@@ -12,7 +12,8 @@
 # The library is the bit-exactness checker for the TQ4 append path and the
 # dequant-then-attend checker for attention.  op_norms_rope_act.cu (the layer's QK-norm / RoPE
 # producer and its output-gate kernels) is built in as the checker of the fused producer and of
-# the output epilogue.  The product never links or loads it.
+# the output epilogue, op_qsa.cu (query-sparse attention over selected 4-token groups) as the checker of
+# the sparse attention entry points.  The product never links or loads it.
 #
 # usage: oracle/build_ref.sh [reference_root]      (default: $WARP34_REFERENCE_ROOT, else the checkout next to this repository)
 set -euo pipefail
@@ -30,7 +31,7 @@ mkdir -p "$OUT/obj"
 FLAGS="-gencode arch=compute_100a,code=sm_100a -O3 -lineinfo -std=c++17 --expt-relaxed-constexpr -use_fast_math -extended-lambda -Xcompiler -fPIC -I $CSRC"
 FA2_FLAGS="-I $VENDOR/flash-attn/src -I $VENDOR/flash-attn/stubs -I $VENDOR/cutlass/include -include $VENDOR/flash-attn/fa2_compat_prelude.h -DFLASHATTENTION_DISABLE_DROPOUT -DFLASHATTENTION_DISABLE_ALIBI -DFLASHATTENTION_DISABLE_SOFTCAP -DFLASHATTENTION_DISABLE_LOCAL"
 pids=()
-for stem in op_kv_cache op_paged_attn op_init op_norms_rope_act; do
+for stem in op_kv_cache op_paged_attn op_init op_norms_rope_act op_qsa; do
   if [ "$OUT/obj/$stem.o" -nt "$CSRC/ops/$stem.cu" ]; then continue; fi
   $NVCC $FLAGS -c "$CSRC/ops/$stem.cu" -o "$OUT/obj/$stem.o" &
   pids+=($!)
@@ -42,5 +43,5 @@ fi
 for p in "${pids[@]}"; do wait "$p"; done
 ${CC:-gcc} -O2 -fPIC -c "$HERE/ref_link_stubs.c" -o "$OUT/obj/ref_link_stubs.o"
 $NVCC -shared -o "$OUT/libwarp34_ref.so" "$OUT"/obj/ref_link_stubs.o "$OUT"/obj/op_kv_cache.o "$OUT"/obj/op_paged_attn.o \
-  "$OUT"/obj/op_init.o "$OUT"/obj/op_paged_fa2.o "$OUT"/obj/op_norms_rope_act.o -lcublas -lcublasLt -lcudart
+  "$OUT"/obj/op_init.o "$OUT"/obj/op_paged_fa2.o "$OUT"/obj/op_norms_rope_act.o "$OUT"/obj/op_qsa.o -lcublas -lcublasLt -lcudart
 echo "built $OUT/libwarp34_ref.so"

@@ -96,15 +96,9 @@ __device__ __forceinline__ float round_act(float x, int bf16) {
     return bf16 ? __bfloat162float(__float2bfloat16_rn(x)) : __half2float(__float2half_rn(x));
 }
 
-// v[j] = column lane + 32 j of one 256-wide row (8 registers per lane of one warp).
-__device__ __forceinline__ void apply_output_gate(float (&v)[8], const OutputGate& og, size_t row_base, int lane, int io_bf16) {
-    if (og.mode == 0) return;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        const float g = load_act(og.gate, row_base + lane + 32 * j, io_bf16);
-        v[j] = round_act(v[j], io_bf16) * (1.0f / (1.0f + __expf(-g)));
-    }
-    if (og.mode != 2) return;
+// Normalised 64-point Hadamard (x 1/8) over every 64 columns of a row held as v[j] = column
+// lane + 32 j, on the values rounded to the activation type.
+__device__ __forceinline__ void hadamard64_row(float (&v)[8], int lane, int io_bf16) {
 #pragma unroll
     for (int b = 0; b < 4; ++b) {   // block b = columns [64 b, 64 b + 64): index bits 0-4 = lane, bit 5 = register
         const float x0 = round_act(v[2 * b], io_bf16), x1 = round_act(v[2 * b + 1], io_bf16);
@@ -119,6 +113,18 @@ __device__ __forceinline__ void apply_output_gate(float (&v)[8], const OutputGat
         v[2 * b] = a0 * 0.125f;
         v[2 * b + 1] = a1 * 0.125f;
     }
+}
+
+// v[j] = column lane + 32 j of one 256-wide row (8 registers per lane of one warp).
+__device__ __forceinline__ void apply_output_gate(float (&v)[8], const OutputGate& og, size_t row_base, int lane, int io_bf16) {
+    if (og.mode == 0) return;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const float g = load_act(og.gate, row_base + lane + 32 * j, io_bf16);
+        v[j] = round_act(v[j], io_bf16) * (1.0f / (1.0f + __expf(-g)));
+    }
+    if (og.mode != 2) return;
+    hadamard64_row(v, lane, io_bf16);
 }
 
 // Stores one output row of a TQ4 layer: t[j] is column lane + 32 j after the inverse rotation,
@@ -2025,6 +2031,7 @@ static size_t stream_scratch_bytes(const warp34_kv_layer_layout* l, const warp34
 }  // namespace w34
 
 #include "kv8_attention.cuh"
+#include "qsa_sparse.cuh"
 
 namespace w34 {
 static int launch_scalar(const warp34_exec* ex, const warp34_kv_layer_layout* layout,

@@ -88,7 +88,7 @@ __device__ __forceinline__ int find_request(const int32_t* __restrict__ qsl, int
 // warp34_bounds_set_pool_pages().  Without the define these helpers cost nothing.
 enum { kBoundsBlockIndex = 1, kBoundsPageId = 2, kBoundsWriteSlot = 3 };
 enum { kInAppend = 1, kInScalar = 2, kInStream = 3, kInTeam = 4, kInPrefillExact = 5, kInPrefillTc = 6,
-       kInBf16 = 7, kInKv8 = 8 };
+       kInBf16 = 7, kInKv8 = 8, kInSparse = 9 };
 #ifdef W34_BOUNDS
 struct BoundsWord { int what, value, limit, count; };
 static __device__ BoundsWord g_bounds;       // one per translation unit; the report merges them
@@ -115,6 +115,11 @@ __device__ __forceinline__ bool write_slot_ok(int slot, int where) {
     const int pages = g_bounds_pool_pages;
     return pages <= 0 || bounds_ok(slot, pages * kPageTokens, kBoundsWriteSlot, where);
 }
+// a page id that did not come from a block table (a selected-block list)
+__device__ __forceinline__ int pool_page(int page, int where) {
+    const int pages = g_bounds_pool_pages;
+    return (pages > 0 && !bounds_ok(page, pages, kBoundsPageId, where)) ? 0 : page;
+}
 #define W34_BOUNDS_HOST_HOOKS(tag)                                                                  \
     int bounds_fetch_##tag(int32_t* out, int reset) {                                               \
         BoundsWord w;                                                                               \
@@ -129,6 +134,7 @@ __device__ __forceinline__ bool write_slot_ok(int slot, int where) {
 #else
 __device__ __forceinline__ int block_table_page(const int32_t* __restrict__ blocks, int idx, int, int) { return blocks[idx]; }
 __device__ __forceinline__ bool write_slot_ok(int, int) { return true; }
+__device__ __forceinline__ int pool_page(int page, int) { return page; }
 #define W34_BOUNDS_HOST_HOOKS(tag)
 #endif
 

@@ -95,6 +95,8 @@ _KERNEL_SIGS = {
     "warp34_paged_attention_f16_static_scratch": (C.c_int, [C.c_size_t, _P(KvLayerLayout), _P(AttentionBatch),
                                                              C.c_void_p, C.c_void_p, C.c_int, _P(C.c_size_t)]),
     "warp34_static_scratch_status": (C.c_int, [_P(C.c_int32)]),
+    "warp34_qsa_sparse_paged_attn_f16": (C.c_int, [C.c_void_p] * 10 + [C.c_int, C.c_int, C.c_int, C.c_float]),
+    "warp34_qsa_sparse_paged_attn_hadamard_f16": (C.c_int, [C.c_void_p] * 10 + [C.c_int, C.c_int, C.c_int, C.c_float]),
     "warp34_bounds_set_pool_pages": (C.c_int, [C.c_int32]),
     "warp34_bounds_report": (C.c_int, [_P(C.c_int32), C.c_int32]),
     "warp34_fused_k_rmsnorm_rope_kv_cache_write_f16": (C.c_int, [_P(Exec), _P(KvLayerLayout), _P(AttentionBatch),
