@@ -547,14 +547,14 @@ def run_qsa_sparse(args):
     achieved = kv_bytes / (ms * 1e-3) / 1e9
     line = {"metric": "qsa_sparse_attention_kv_gbps", "value": achieved, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "f32", "data": "synthetic",
+            "dtype": "f32" if reference else "f16", "data": "synthetic",
             "config": {"workload": f"qsa_sparse_decode: {batch} tokens x {select_k} selected 4-token groups of contexts "
                                    f"U[{lo},{hi}], {hq} q heads / {hkv} kv heads, d256, TQ4 pages, sigmoid gate",
                        "kv_bytes_per_step": kv_bytes, "l2": "a 256 MB buffer is written between timed steps"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "peak_kind": f"of {peak_kind}", "kernel": "qsa_sparse_attention_kernel (+ merge)", "launch_ms": ms,
+                         "peak_kind": f"of {peak_kind}", "kernel": "tq4_attention_stream_kernel, query-sparse instantiation (+ plan and merge launches, timed together)", "launch_ms": ms,
                          "traffic": None},
-            "gpu_launches": 2 * args.steps, "clocks": sampler.summary(t_begin, t_end)}
+            "gpu_launches": 3 * args.steps, "clocks": sampler.summary(t_begin, t_end)}
     if reference:
         line["impl"] = "reference"
         line["roofline"]["kernel"] = "reference qsa_sparse_paged_attn_gqa_f16_kernel (+ merge)"

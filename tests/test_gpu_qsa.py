@@ -87,16 +87,22 @@ def test_sparse_attention_matches_the_reference_kernel(env, fmt_name, hq, hkv, v
     name = "warp34_qsa_sparse_paged_attn_hadamard_f16" if variant == "hadamard" else "warp34_qsa_sparse_paged_attn_f16"
     gt = None if variant == "plain" else gate
     outs = {}
-    for who, lib, scratch in (("ours", env["lib"], True), ("unsplit", env["lib"], False), ("ref", env["ref"], True)):
-        e = ex if scratch else kv.Executor(0)
+    precise = kv.Executor(32 << 20)
+    precise.ex.flags = env["ffi"].EXEC_FLAG_PRECISE_ATTENTION
+    for who, lib, scratch in (("ours", env["lib"], True), ("unsplit", env["lib"], False), ("fp32", env["lib"], None),
+                              ("ref", env["ref"], True)):
+        e = precise if scratch is None else ex if scratch else kv.Executor(0)
         out = torch.full((T, hq, 256), 0, dtype=torch.int16, device="cuda")
         out.fill_(0x5500)
         assert _call(lib, name, e, q, gt, wl.layer, *dev, out, hq, select_k) == 0
         torch.cuda.synchronize()
+        if who == "ours" and fmt_name == "tq4":
+            # TQ4 lists with a workspace run on the tensor-core stream kernel: its status word stays clear
+            assert int(e.scratch[:4].cpu().numpy().view(np.int32)[0]) == 0
         outs[who] = out.cpu().numpy().view(np.uint16)
     want = outs["ref"].view(np.float16).astype(np.float32)
     assert np.isfinite(want).all() and np.abs(want).max() > 0.05
-    for who in ("ours", "unsplit"):
+    for who in ("ours", "unsplit", "fp32"):
         got = outs[who].view(np.float16).astype(np.float32)
         # the masked token is written as zero bits; the token without entries comes out as (signed) zeros
         assert (outs[who][6] == 0).all() and (got[5] == 0).all(), "masked / empty token is not zero"

@@ -315,6 +315,8 @@ __global__ void __launch_bounds__(128) qsa_sparse_merge_kernel(const QsaParams p
     qsa_finish_row(p, s_row[wid], acc, row_base, lane);
 }
 
+static int launch_qsa_stream(const warp34_exec* ex, const QsaParams& q, bool* taken);   // tq4_attention.cu
+
 static bool qsa_layout_ok(const warp34_kv_layer_layout* l) {
     if (l->head_dim != kHeadDim || l->block_size != kPageTokens || l->local_kv_heads <= 0 || l->k_base == 0 || l->v_base == 0) {
         return false;
@@ -387,6 +389,12 @@ static int launch_qsa_sparse(const warp34_exec* ex, const void* q, const void* g
     p.splits = splits;
     p.hadamard = hadamard;
     p.sm_scale = sm_scale;
+    {
+        // TQ4 layers in the canonical packing with enough workspace: the tensor-core stream kernel
+        bool taken = false;
+        const int rcs = launch_qsa_stream(ex, p, &taken);
+        if (rcs != 0 || taken) return rcs;
+    }
     cudaStream_t st = (cudaStream_t)ex->stream;
     if (qgroups > 65535) return (int)cudaErrorInvalidValue;
     const dim3 grid((unsigned)num_tokens, (unsigned)qgroups, (unsigned)splits);

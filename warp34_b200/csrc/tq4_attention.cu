@@ -89,7 +89,9 @@ __device__ __forceinline__ void store_act(void* base, size_t idx, float x, int b
 // ---------------------------------------------------------------------------------------
 struct OutputGate {
     const void* gate;   // [total_tokens, num_q_heads, 256] in the activation type, or null
-    int mode;           // 0 none, 1 sigmoid gate, 2 sigmoid gate then Hadamard-64 (x 1/8) per 64 columns
+    int mode;           // 0 none, 1 sigmoid gate, 2 sigmoid gate then Hadamard-64 (x 1/8) per 64 columns;
+                        // + 4: the gate multiplies the un-rounded fp32 value (the query-sparse kernels'
+                        // epilogue, op_qsa.cu:1040-1067) and may be absent (gate == nullptr)
 };
 
 __device__ __forceinline__ float round_act(float x, int bf16) {
@@ -118,12 +120,15 @@ __device__ __forceinline__ void hadamard64_row(float (&v)[8], int lane, int io_b
 // v[j] = column lane + 32 j of one 256-wide row (8 registers per lane of one warp).
 __device__ __forceinline__ void apply_output_gate(float (&v)[8], const OutputGate& og, size_t row_base, int lane, int io_bf16) {
     if (og.mode == 0) return;
+    if (og.gate != nullptr) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        const float g = load_act(og.gate, row_base + lane + 32 * j, io_bf16);
-        v[j] = round_act(v[j], io_bf16) * (1.0f / (1.0f + __expf(-g)));
+        for (int j = 0; j < 8; ++j) {
+            const float g = load_act(og.gate, row_base + lane + 32 * j, io_bf16);
+            const float a = (og.mode & 4) ? v[j] : round_act(v[j], io_bf16);
+            v[j] = a * (1.0f / (1.0f + __expf(-g)));
+        }
     }
-    if (og.mode != 2) return;
+    if ((og.mode & 3) != 2) return;
     hadamard64_row(v, lane, io_bf16);
 }
 
@@ -316,7 +321,28 @@ struct StreamParams {
     uint32_t* qfrag;       // rotated queries as MMA fragments, written by the plan launch (or null)
     int q_groups_max;      // row groups per (request, kv head) that qfrag has room for
     OutputGate og;         // applied by the merge kernel when it stores attn_out
+    // Query-sparse mode (sel_phys != nullptr): request r is token r, its "pages" are units of four
+    // selected 4-token groups (physical group id = page * 4 + group in page, logical group index for the
+    // causal test against seq_pos[r]); rows of masked tokens are written as zeros.
+    const int32_t* sel_phys = nullptr;
+    const int32_t* sel_logical = nullptr;
+    const int32_t* num_selected = nullptr;
+    const int32_t* seq_pos = nullptr;
+    int select_k = 0;
 };
+
+// Geometry of request r: from the batch descriptor, or in query-sparse mode one query token at
+// position seq_pos[r].
+__device__ __forceinline__ ReqGeom stream_req(const StreamParams& p, int r) {
+    if (p.sel_phys == nullptr) return load_req(p.batch, r);
+    ReqGeom g;
+    g.q_start = r;
+    g.q_len = 1;
+    g.ctx_before = p.seq_pos[r];
+    g.seq_after = g.ctx_before + 1;
+    g.valid = true;
+    return g;
+}
 
 __device__ __forceinline__ int32_t* plan_array(uint8_t* scratch, int which, int num_reqs) {
     return reinterpret_cast<int32_t*>(scratch + sizeof(PlanHeader)) + (size_t)which * (num_reqs + 1);
@@ -352,7 +378,16 @@ __global__ void __launch_bounds__(kPlanThreads) tq4_attention_plan_kernel(const 
     for (int base = 0; base < R; base += 32) {
         const int r = base + lane;
         int npages = 0, ngroups = 0, plo = 0;
-        if (r < R) {
+        if (r < R && p.sel_phys != nullptr) {
+            // query-sparse: a unit is four entries of the token's selected list; masked tokens have no items
+            if (p.batch.valid_token_mask == nullptr || p.batch.valid_token_mask[r] != 0) {
+                int n_sel = p.num_selected[r];
+                if (n_sel > p.select_k) n_sel = p.select_k;
+                npages = n_sel > 0 ? (n_sel + 3) >> 2 : 0;
+                ngroups = (p.gqa + p.rows_per_group - 1) / p.rows_per_group;
+                if (p.qfrag != nullptr && ngroups > p.q_groups_max) { ngroups = p.q_groups_max; clamped = true; }
+            }
+        } else if (r < R) {
             const ReqGeom g = load_req(p.batch, r);
             if (g.valid) {
                 const int lo = row_min_kv(p.batch, g, 0);
@@ -564,7 +599,7 @@ __device__ void qprep_block(const StreamParams& p, int idx) {
     const int kv_head = (idx / p.q_groups_max) % hkv;
     const int r = idx / (p.q_groups_max * hkv);
     if (r >= p.batch.num_reqs || p.qfrag == nullptr) return;  // block-uniform
-    const ReqGeom g = load_req(p.batch, r);
+    const ReqGeom g = stream_req(p, r);
     const int rows_in_req = g.q_len * p.gqa;
     if (!g.valid || group * kRowsPerGroup >= rows_in_req) return;  // block-uniform
     {
@@ -616,7 +651,7 @@ __device__ void qprep_block(const StreamParams& p, int idx) {
     }
 }
 
-template <int STAGES, int WARPS, bool EXACT>
+template <int STAGES, int WARPS, bool EXACT, bool SPARSE = false>
 __global__ void __launch_bounds__(WARPS * 32, 1) tq4_attention_stream_kernel(const StreamParams p) {
     extern __shared__ __align__(1024) uint8_t smem[];
     // The lookup table sits at the first 64 KB-aligned SHARED address inside the dynamic window,
@@ -720,7 +755,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) tq4_attention_stream_kernel(con
         const int group = item - kv_head * ngroups;
         const int pg0 = page_lo_a[r] + page_in_item;  // first logical page of this segment
         const int slot = w_global + item_prefix[r] + item;
-        const ReqGeom g = load_req(p.batch, r);
+        const ReqGeom g = stream_req(p, r);
         const int rows_in_req = g.q_len * p.gqa;
 
         // ---- per-row limits for this lane's two query rows (2 tig, 2 tig + 1) ----------
@@ -768,11 +803,50 @@ __global__ void __launch_bounds__(WARPS * 32, 1) tq4_attention_stream_kernel(con
         const int32_t* blocks = p.batch.block_tables + (size_t)r * p.batch.max_blocks_per_req;
         const uint8_t* k_head_base = (const uint8_t*)(uintptr_t)p.layout.k_base + (size_t)kv_head * p.layout.k_head_stride_bytes;
         const uint8_t* v_head_base = (const uint8_t*)(uintptr_t)p.layout.v_base + (size_t)kv_head * p.layout.v_head_stride_bytes;
-        int32_t my_page = (lane < n_here) ? block_table_page(blocks, pg0 + lane, p.batch.max_blocks_per_req, kInStream) : 0;  // page ids of units [0, 32)
-        int32_t next_page = (32 + lane < n_here) ? block_table_page(blocks, pg0 + 32 + lane, p.batch.max_blocks_per_req, kInStream) : 0;
+        int32_t my_page = 0, next_page = 0;
+        if (!SPARSE) {
+            my_page = (lane < n_here) ? block_table_page(blocks, pg0 + lane, p.batch.max_blocks_per_req, kInStream) : 0;  // page ids of units [0, 32)
+            next_page = (32 + lane < n_here) ? block_table_page(blocks, pg0 + 32 + lane, p.batch.max_blocks_per_req, kInStream) : 0;
+        }
+        // query-sparse: the token's selected list, its length and its position
+        const int32_t* sel_phys = SPARSE ? p.sel_phys + (size_t)r * p.select_k : nullptr;
+        const int32_t* sel_logical = SPARSE ? p.sel_logical + (size_t)r * p.select_k : nullptr;
+        const int n_sel = SPARSE ? min(p.num_selected[r], p.select_k) : 0;
 
         fence_proxy_async();  // the staging writes above precede async-proxy writes to the ring
         auto issue = [&](int idx) {  // called by all lanes; lane 0 issues the four copies
+            if (SPARSE) {
+                // Unit idx = entries 4 (pg0 + idx) .. + 3 of the list.  Lane j < 4 takes entry j: a group of
+                // four rows (528 bytes of K, 528 of V) lands at rows 4 j .. 4 j + 3 of the stage; a skipped
+                // entry (negative id, past the list's end, or wholly after the token's position) copies
+                // nothing and is masked below through the position word kept in the stage's padding.
+                const int s = idx % STAGES;
+                const uint32_t bar = bars + 8u * s;
+                const uint32_t dst = ring + (uint32_t)s * kStageStride;
+                const int gi = 4 * (pg0 + idx) + lane;
+                int ph = -1, first_pos = 0x3fffffff;
+                if (lane < 4 && gi < n_sel) {
+                    ph = sel_phys[gi];
+                    const int lg = sel_logical[gi];
+                    if (ph >= 0 && 4 * lg <= g.ctx_before) first_pos = 4 * lg; else ph = -1;
+                }
+                const int n_valid = __popc(__ballot_sync(0xffffffffu, ph >= 0));
+                pending |= 1u << s;
+                if (lane == 0) mbar_expect_tx(bar, (uint32_t)n_valid * 8u * kTq4RowBytes);
+                __syncwarp();
+                if (lane < 4) {
+                    sts32(dst + kHalfBytes + 4u * lane, (uint32_t)first_pos);
+                    if (ph >= 0) {
+                        const int page = pool_page(ph >> 2, kInStream);
+                        const uint32_t row_off = (uint32_t)(ph & 3) * 4u * kTq4RowBytes;
+                        bulk_g2s(dst + token_offset(4 * lane), k_head_base + (size_t)page * p.layout.k_page_stride_bytes + row_off,
+                                 4u * kTq4RowBytes, bar);
+                        bulk_g2s(dst + kRunStride + token_offset(4 * lane),
+                                 v_head_base + (size_t)page * p.layout.v_page_stride_bytes + row_off, 4u * kTq4RowBytes, bar);
+                    }
+                }
+                return;
+            }
             const int32_t page = __shfl_sync(0xffffffffu, (idx & 32) ? next_page : my_page, idx & 31);
             pending |= 1u << (idx % STAGES);
             if (lane == 0) {
@@ -791,11 +865,12 @@ __global__ void __launch_bounds__(WARPS * 32, 1) tq4_attention_stream_kernel(con
         // `my_page` holds ids for units [64 c, 64 c + 32), `next_page` for [64 c + 32, 64 c + 64).
 #pragma unroll 1
         for (int i = 0; i < STAGES - 1 && i < n_here; ++i) issue(i);
+        if (SPARSE) __syncwarp();   // the position words written by lanes 0-3 are read by all lanes
 
 #pragma unroll 1
         for (int i = 0; i < n_here; ++i) {
             // refill page-id registers every 32 units, one window ahead
-            if ((i & 31) == 0 && i > 0) {
+            if (!SPARSE && (i & 31) == 0 && i > 0) {
                 const int base = i + 32;  // ids for [i+32, i+64) replace the window just consumed
                 const int32_t fresh = (base + lane < n_here) ? block_table_page(blocks, pg0 + base + lane, p.batch.max_blocks_per_req, kInStream) : 0;
                 if (i & 32) my_page = fresh; else next_page = fresh;
@@ -812,8 +887,18 @@ __global__ void __launch_bounds__(WARPS * 32, 1) tq4_attention_stream_kernel(con
             const uint32_t kst = ring + (uint32_t)s * kStageStride;
             const uint32_t vst = kst + kRunStride;
             const int kv_base = (pg0 + i) << 4;
-            const bool full = (kv_base >= safe_lo) && (kv_base + 15 <= safe_hi);
+            bool full = (kv_base >= safe_lo) && (kv_base + 15 <= safe_hi);
             const uint32_t ptok = page_token(i);
+            // query-sparse: position of the first row of the two groups this lane's keys sit in
+            int pos_a_sparse = 0, pos_b_sparse = 0;
+            if (SPARSE) {
+                const uint32_t pw = kst + kHalfBytes;
+                const int f0 = (int)lds32_dep(pw, ptok), f1 = (int)lds32_dep(pw + 4, ptok);
+                const int f2 = (int)lds32_dep(pw + 8, ptok), f3 = (int)lds32_dep(pw + 12, ptok);
+                full = max(max(f0, f1), max(f2, f3)) + 3 <= safe_hi;
+                pos_a_sparse = ((key_a >> 3) ? f2 : f0) + (key_a & 3);
+                pos_b_sparse = ((key_a >> 3) ? f3 : f1) + (key_a & 3);
+            }
 #define W34_LDS(addr) lds32_dep(addr, ptok)
 #define W34_LUT(word, k) lds32_lut(__byte_perm((word), lut_lane, 0x7604 + ((k) << 4)))
 #define W34_LUTK(word, k) lds64_lut(__byte_perm((word), lutk_lane, 0x7604 + ((k) << 4)))
@@ -901,7 +986,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) tq4_attention_stream_kernel(con
 
             bool msk[4] = {false, false, false, false};
             if (!full) {
-                const int pos_a = kv_base + key_a, pos_b = pos_a + 4;
+                const int pos_a = SPARSE ? pos_a_sparse : kv_base + key_a, pos_b = SPARSE ? pos_b_sparse : pos_a + 4;
                 msk[0] = !(pos_a >= rmin[0] && pos_a <= rmax[0]);
                 msk[1] = !(pos_a >= rmin[1] && pos_a <= rmax[1]);
                 msk[2] = !(pos_b >= rmin[0] && pos_b <= rmax[0]);
@@ -1656,10 +1741,14 @@ __global__ void __launch_bounds__(MW * 32) tq4_attention_merge_kernel(const Stre
             for (int j = 0; j < 8; ++j) dst[lane + 32 * j] = 0.0f;
             if (lane == 0) { dst[kHeadDim] = -1e30f; dst[kHeadDim + 1] = 0.0f; }
         }
+        if (!PARTIAL_OUT && wid == 0 && p.sel_phys != nullptr) {   // query-sparse: masked rows are zeros
+#pragma unroll
+            for (int j = 0; j < 8; ++j) store_act(p.attn_out, ((size_t)tok * p.num_q_heads + q_head) * kHeadDim + lane + 32 * j, 0.0f, p.io_bf16);
+        }
     };
     if (p.batch.valid_token_mask != nullptr && p.batch.valid_token_mask[tok] == 0) { skip_row(); return; }
     const int R = p.batch.num_reqs;
-    const int r = find_request(p.batch.query_start_loc, R, tok);
+    const int r = p.sel_phys != nullptr ? tok : find_request(p.batch.query_start_loc, R, tok);
     if (r < 0) { skip_row(); return; }
     if (p.batch.valid_req_mask != nullptr && p.batch.valid_req_mask[r] == 0) { skip_row(); return; }
 
@@ -1671,7 +1760,7 @@ __global__ void __launch_bounds__(MW * 32) tq4_attention_merge_kernel(const Stre
     const float* partials = reinterpret_cast<const float*>(p.scratch + plan_bytes(R));
 
     const int kv_head = q_head / p.gqa;
-    const int row_in_req = (tok - p.batch.query_start_loc[r]) * p.gqa + (q_head - kv_head * p.gqa);
+    const int row_in_req = (tok - (p.sel_phys != nullptr ? r : p.batch.query_start_loc[r])) * p.gqa + (q_head - kv_head * p.gqa);
     const int rpg = p.rows_per_group;
     const int part_floats = rpg * kHeadDim + 2 * rpg;
     const int group = row_in_req / rpg, row8 = row_in_req - group * rpg;
@@ -1954,6 +2043,9 @@ static DeviceInfo* device_info(int* rc) {
                                         cudaFuncAttributeMaxDynamicSharedMemorySize, optin);
         if (*rc != 0) return nullptr;
         *rc = (int)cudaFuncSetAttribute(tq4_attention_stream_kernel<kFastStages, kFastWarps, false>,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, optin);
+        if (*rc != 0) return nullptr;
+        *rc = (int)cudaFuncSetAttribute(tq4_attention_stream_kernel<kExactStages, kExactWarps, true, true>,
                                         cudaFuncAttributeMaxDynamicSharedMemorySize, optin);
         if (*rc != 0) return nullptr;
         *rc = (int)cudaFuncSetAttribute(tq4_attention_team_kernel<2>,
@@ -2275,6 +2367,79 @@ static int launch_attention(const warp34_exec* ex, const warp34_kv_layer_layout*
         if (wide) tq4_attention_merge_kernel<false, 32><<<(unsigned)rows, 1024, 0, st>>>(p);
         else tq4_attention_merge_kernel<false, 4><<<(unsigned)rows, 128, 0, st>>>(p);
     }
+    return (int)cudaGetLastError();
+}
+
+// Query-sparse lists on the exact stream kernel (TQ4 layers in the canonical packing, a workspace that
+// holds the plan, the query fragments and at least one CTA's partial slots).  *taken = false: the caller
+// runs its fp32 kernel instead.
+static int launch_qsa_stream(const warp34_exec* ex, const QsaParams& q, bool* taken) {
+    *taken = false;
+    const warp34_kv_layer_layout* layout = &q.layout;
+    if ((ex->flags & WARP34_B200_EXEC_FLAG_PRECISE_ATTENTION) != 0 || !tq4_layout_ok(layout) || !stream_layout_ok(layout) ||
+        ex->scratch_ptr == 0 || (ex->scratch_ptr & 15u) != 0u || q.select_k <= 0) {
+        return 0;
+    }
+    int rc = 0;
+    DeviceInfo* dev = device_info(&rc);
+    if (dev == nullptr) return rc;
+    const int gqa = q.num_q_heads / layout->local_kv_heads;
+    const long long groups = (gqa + kRowsPerGroup - 1) / kRowsPerGroup;
+    const long long items = (long long)q.num_tokens * layout->local_kv_heads * groups;
+    const long long units_bound = items * (((long long)q.select_k + 3) / 4);
+    if (units_bound >= 0x7fffffffll || items > 0x3fffffffll) return 0;
+    const size_t plan = plan_bytes(q.num_tokens);
+    const size_t slot_bytes = (size_t)kPartialFloats * sizeof(float);
+    const size_t qfrag_bytes = (size_t)items * qfrag_item_bytes();
+    const size_t fixed = plan + qfrag_bytes;
+    const size_t avail = ex->scratch_size > fixed ? ex->scratch_size - fixed : 0;
+    const long long workers = (long long)(avail / slot_bytes) - items;
+    if (workers < kExactWarps) return 0;
+    int grid = dev->sm_count;
+    if (workers / kExactWarps < grid) grid = (int)(workers / kExactWarps);
+
+    StreamParams p;
+    p.layout = *layout;
+    p.batch = warp34_attention_batch{};
+    p.batch.valid_token_mask = q.valid_token_mask;
+    p.batch.num_reqs = q.num_tokens;
+    p.batch.total_tokens = q.num_tokens;
+    p.batch.max_q_len = 1;
+    p.batch.mask_mode = WARP34_ATTN_MASK_CAUSAL;
+    p.batch.sliding_window = 0;
+    p.batch.sm_scale = q.sm_scale;
+    p.q_in = q.q;
+    p.attn_out = q.out;
+    p.io_bf16 = 0;
+    p.triple_out = nullptr;
+    p.scratch = reinterpret_cast<uint8_t*>((uintptr_t)ex->scratch_ptr);
+    p.num_q_heads = q.num_q_heads;
+    p.gqa = gqa;
+    p.num_warps = grid * kExactWarps;
+    p.max_slots = (int)(p.num_warps + items);
+    p.rows_per_group = kRowsPerGroup;
+    p.q_scale = q.sm_scale * 1.4426950408889634f / kLutScale;
+    p.natural = 0;
+    p.og.gate = q.gate;
+    p.og.mode = (q.gate != nullptr || q.hadamard) ? ((q.hadamard ? 2 : 1) | 4) : 0;
+    p.qfrag = reinterpret_cast<uint32_t*>(p.scratch + plan + (size_t)p.max_slots * slot_bytes);
+    p.q_groups_max = (int)groups;
+    p.smem_bytes = (uint32_t)dev->smem_optin;
+    p.sel_phys = q.sel_phys;
+    p.sel_logical = q.sel_logical;
+    p.num_selected = q.num_selected;
+    p.seq_pos = q.seq_pos;
+    p.select_k = q.select_k;
+    cudaStream_t st = (cudaStream_t)ex->stream;
+    tq4_attention_plan_kernel<<<1 + (unsigned)items, kPlanThreads, 0, st>>>(p);
+    tq4_attention_stream_kernel<kExactStages, kExactWarps, true, true><<<grid, kExactWarps * 32, p.smem_bytes, st>>>(p);
+    const long long rows = (long long)q.num_tokens * q.num_q_heads;
+    if (rows * 4 < (long long)grid * kExactWarps / 8) {
+        tq4_attention_merge_kernel<false, 32><<<(unsigned)rows, 1024, 0, st>>>(p);
+    } else {
+        tq4_attention_merge_kernel<false, 4><<<(unsigned)rows, 128, 0, st>>>(p);
+    }
+    *taken = true;
     return (int)cudaGetLastError();
 }
 
