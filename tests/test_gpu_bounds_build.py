@@ -166,3 +166,44 @@ def test_block_table_index_beyond_the_declared_width_is_recorded(env):
     r = _report(blib)
     assert r["what"] == 1 and r["where"] == 2 and r["limit"] == 4 and 4 <= r["value"] <= 12, r
     assert torch.isfinite(out.float()).all()
+
+
+@pytest.mark.parametrize("scratch", [True, False])
+def test_query_sparse_lists_run_clean_under_the_checks(env, scratch):
+    """The selected-group lists of the query-sparse entry point carry page ids of their own: both of its
+    kernels (stream kernel with a workspace, fp32 kernel without) check them against the declared pool."""
+    kv, synth, blib = env["kv"], env["synth"], env["blib"]
+    ctx = [300, 90]
+    wl = synth.PagedWorkload([0, 0], ctx, 4, seed=21)
+    assert blib.warp34_bounds_set_pool_pages(wl.num_pages) == 0
+    _report(blib)
+    ex = kv.Executor(32 << 20 if scratch else 0)
+    fill = kv.Executor(8 << 20)
+    k, v = synth.make_kv(sum(ctx), 4, 21)
+    kv.kv_cache_write(fill, wl.layer, wl.step(), k.cuda(), v.cuda(), lib=blib)
+    select_k, T = 16, 2
+    phys = np.full((T, select_k), -1, np.int32)
+    logical = np.zeros((T, select_k), np.int32)
+    for t in range(T):
+        groups = np.arange(min(select_k, (ctx[t] + 3) // 4))
+        logical[t, :len(groups)] = groups
+        phys[t, :len(groups)] = np.asarray(wl.seqs[t].pages)[groups // 4] * 4 + groups % 4
+    dev = [torch.from_numpy(a).cuda() for a in (phys, logical, np.full(T, select_k, np.int32), np.asarray(ctx, np.int32) - 1)]
+    q = synth.make_q(T, 24, 22).cuda()
+    out = torch.zeros_like(q)
+    fn = blib.warp34_qsa_sparse_paged_attn_f16
+    assert fn(C.addressof(ex.ex), q.data_ptr(), None, C.addressof(wl.layer.layout), dev[0].data_ptr(), dev[1].data_ptr(),
+              dev[2].data_ptr(), dev[3].data_ptr(), None, out.data_ptr(), T, 24, select_k, 0.0625) == 0
+    torch.cuda.synchronize()
+    r = _report(blib)
+    assert r["count"] == 0, r
+    assert torch.isfinite(out.float()).all() and out.float().abs().max() > 0.01
+    # declare a pool that ends below the highest page the lists use: recorded, redirected, no fault
+    top = int(phys.max()) // 4
+    assert blib.warp34_bounds_set_pool_pages(top) == 0
+    assert fn(C.addressof(ex.ex), q.data_ptr(), None, C.addressof(wl.layer.layout), dev[0].data_ptr(), dev[1].data_ptr(),
+              dev[2].data_ptr(), dev[3].data_ptr(), None, out.data_ptr(), T, 24, select_k, 0.0625) == 0
+    torch.cuda.synchronize()
+    r = _report(blib)
+    assert r["what"] == 2 and r["where"] in (3, 9) and r["value"] == top and r["limit"] == top, r
+    assert blib.warp34_bounds_set_pool_pages(0) == 0
