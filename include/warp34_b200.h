@@ -195,6 +195,9 @@ int warp34_fused_k_rmsnorm_rope_kv_cache_write_f16(
  * WARP34_B200_EXEC_FLAG_FAST_ATTENTION trades that for speed.  Kernels: decode and verify batches
  * (up to 24 query rows per request and kv head) stream split-KV work items of 8 rows; larger
  * chunks take a 128-row prefill kernel (register MMAs; tcgen05 + TMEM with the fast flag).
+ * 8-bit boundary layers (Q8_0, FP8 E4M3) in the canonical packing stream the same way on a
+ * tensor-core kernel whose operands are exact (codes convert exactly to fp16); other packings of
+ * them, callers without scratch and WARP34_B200_EXEC_FLAG_PRECISE_ATTENTION take an fp32 kernel.
  */
 int warp34_paged_attention_f16(const warp34_exec* ex, const warp34_kv_layer_layout* layout,
                                const warp34_attention_batch* batch,
