@@ -91,3 +91,16 @@ def test_argument_validation_needs_no_gpu(native_libs):
     lay.k_format = lay.v_format = ffi.KV_FORMAT_TQ4
     lay.k_transform = lay.v_transform = ffi.KV_TRANSFORM_RADEMACHER_WHT256
     assert kernels.warp34_kv_cache_write_strided(C.byref(ex), C.byref(lay), C.byref(b), p, p, 512, 1024) == 1
+    # the query-sparse entry points check their arguments like the reference's launcher (op_qsa.cu:1464-1470)
+    qsa = kernels.warp34_qsa_sparse_paged_attn_f16
+    assert qsa(None, p, None, C.addressof(lay), p, p, p, p, None, p, 1, 8, 4, 0.0625) == 1          # no exec
+    assert qsa(C.addressof(ex), p, None, C.addressof(lay), p, p, p, p, None, p, 1, 6, 4, 0.0625) == 1   # 6 q heads / 4 kv heads
+    assert qsa(C.addressof(ex), p, None, C.addressof(lay), p, p, p, p, None, p, -1, 8, 4, 0.0625) == 1  # negative token count
+    lay.k_format = ffi.KV_FORMAT_FP16
+    lay.k_base = lay.v_base = 4096
+    assert qsa(C.addressof(ex), p, None, C.addressof(lay), p, p, p, p, None, p, 1, 8, 4, 0.0625) == 801  # FP16 rows
+    lay.k_format = ffi.KV_FORMAT_TQ4
+    lay.k_token_stride_bytes = lay.v_token_stride_bytes = 132
+    lay.k_head_stride_bytes = lay.v_head_stride_bytes = 2112
+    lay.k_page_stride_bytes = lay.v_page_stride_bytes = 8448
+    assert qsa(C.addressof(ex), p, None, C.addressof(lay), p, p, p, p, None, p, 0, 8, 4, 0.0625) == 0    # no tokens: no launch

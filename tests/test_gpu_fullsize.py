@@ -76,6 +76,7 @@ def test_full_size_step_is_inside_the_plain_bound_on_every_output(env, name):
     assert np.isfinite(want).all() and np.abs(want).max() > 0.1
     got = _run(env, wl, b, q, hq).float().cpu().numpy()
     ok, msg = plain_parity(got, want)
+    print(f"[margin] {name} default kernels: {msg}")
     assert ok, (name, msg)
     # the opt-in single-operand build stays within its own, wider bound on the same step
     fast = _run(env, wl, b, q, hq, flags=env["ffi"].EXEC_FLAG_FAST_ATTENTION).float().cpu().numpy()
@@ -101,6 +102,7 @@ def test_long_context_single_pass_and_eight_page_shards(env):
     want = _dequant_then_attend(env, wl, b, q, hq)
     whole = _run(env, wl, b, q, hq).float().cpu().numpy()
     ok, msg = plain_parity(whole, want)
+    print(f"[margin] cfg4 single pass: {msg}")
     assert ok, ("single pass", msg)
     pages = wl.seqs[0].pages
     world = 8
@@ -116,6 +118,7 @@ def test_long_context_single_pass_and_eight_page_shards(env):
     kv.merge_shards(env["ex"], triples, merged)
     torch.cuda.synchronize()
     ok, msg = plain_parity(merged.float().cpu().numpy(), want)
+    print(f"[margin] cfg4 eight page shards: {msg}")
     assert ok, ("8 shards", msg)
 
 
@@ -131,6 +134,7 @@ def test_prefill_chunk_after_14k_cached_tokens(env):
     want = _dequant_then_attend(env, wl, b, q, hq)
     got = _run(env, wl, b, q, hq).float().cpu().numpy()
     ok, msg = plain_parity(got, want)
+    print(f"[margin] 2048-token chunk after 14336 tokens: {msg}")
     assert ok, msg
     fast = _run(env, wl, b, q, hq, flags=env["ffi"].EXEC_FLAG_FAST_ATTENTION).float().cpu().numpy()
     ok, msg = fast_parity(fast, want)
