@@ -566,16 +566,13 @@ def run_other_kv(args):
     """The same decode step over another storage format of the reference, device-resident, one GPU:
     `--kv bf16` uncompressed BF16 pages (1024 B per token and KV head instead of 264; the comparison
     arm), `--kv fp8` / `--kv q8` the unrotated 8-bit rows of the boundary layers (528 / 544 B).
-    `--impl reference` runs the reference's own bf16 kernels when they were built; its attention
-    kernels are not run on the 8-bit layers (they faulted on them here)."""
+    `--impl reference` runs the reference's own kernels when they were built: its bf16 kernels, and on
+    the 8-bit layers its scalar dequant-then-attend entry point (its tensor-core dispatcher faulted on
+    these layers here and is not run again)."""
     import oracle
     from warp34_b200 import ffi, kv, synth
     reference = args.impl == "reference"
     bf16 = args.kv == "bf16"
-    if reference and not bf16:
-        print(json.dumps({"impl": "reference", "unavailable": "the reference's attention kernels returned non-finite "
-                          "output and raised an illegal memory access on Q8_0 / FP8 layers here; not run again"}))
-        return
     ref_path = oracle.ref_lib_path() if reference else None
     if reference and ref_path is None:
         print(json.dumps({"impl": "reference", "unavailable": "reference kernels not built (oracle/_ref missing)"}))
@@ -592,8 +589,9 @@ def run_other_kv(args):
     else:
         fmt = ffi.KV_FORMAT_FP8_E4M3 if args.kv == "fp8" else ffi.KV_FORMAT_Q8_0
         formats, act = (fmt, fmt, ffi.KV_TRANSFORM_IDENTITY, ffi.KV_TRANSFORM_IDENTITY), torch.float16
-        append, attend = kv.kv_cache_write, kv.paged_attention
-        kernel = "kv8_attention_stream_kernel (+ plan and merge)" if not reference else "reference kernels"
+        append = kv.kv_cache_write
+        attend = ((lambda *a, **k: kv.paged_attention(*a, scalar=True, **k)) if reference else kv.paged_attention)
+        kernel = "kv8_attention_stream_kernel (+ plan and merge)"
         label = "unrotated FP8 E4M3 rows" if args.kv == "fp8" else "unrotated Q8_0 rows"
     wl = synth.PagedWorkload([int(c) for c in ctx], [q_len] * batch, hkv, seed=seed, formats=formats)
     ex = kv.Executor(64 << 20)
@@ -646,7 +644,8 @@ def run_other_kv(args):
             "gpu_launches": 4 * args.steps, "clocks": sampler.summary(t_begin, t_end)}
     if reference:
         line["impl"] = "reference"
-        line["roofline"]["kernel"] = "reference paged_attention_gqa_bf16_kernel"
+        line["roofline"]["kernel"] = ("reference paged_attention_gqa_bf16_kernel" if bf16 else
+                                      "reference warp34_paged_attention_scalar_f16 (fp32 dequant-then-attend)")
         line["gpu_launches"] = None
     print(json.dumps(line))
 
