@@ -1,0 +1,137 @@
+"""Seeded random geometries through the C ABI: the default (tensor-core) path of every storage format
+against this library's fp32 dequant-then-attend kernels (WARP34_B200_EXEC_FLAG_PRECISE_ATTENTION), which
+the other GPU tests pin against the reference's scalar kernel.  Head counts with GQA groups from 1 to 12,
+ragged contexts from one token to a few hundred, decode / draft / chunk query lengths, sliding windows,
+masked tokens and requests, pools pre-filled with 0xFF bytes; for the query-sparse entry point random
+selected lists with skipped, invisible and partly visible groups.  Bound: 2e-3 + 1e-2 |b| on every output,
+masked rows bit-identical (untouched, or zeros for the query-sparse entry point)."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+ATOL, RTOL = 2e-3, 1e-2
+FORMATS = {"tq4": (2, 1), "fp8": (4, 0), "q8": (3, 0)}
+HEADS = [(4, 4), (8, 4), (16, 4), (24, 4), (8, 1), (24, 2), (6, 3)]
+
+
+@pytest.fixture(scope="module")
+def env(native_libs):
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    from warp34_b200 import ffi, kv, synth
+    return dict(ffi=ffi, kv=kv, synth=synth, lib=native_libs[0])
+
+
+def _close(got_bits, want_bits, sentinel):
+    untouched = (want_bits == sentinel).all(axis=(1, 2))
+    assert ((got_bits == sentinel).all(axis=(1, 2)) == untouched).all(), "masked rows differ"
+    g = got_bits.view(np.float16).astype(np.float32)[~untouched]
+    w = want_bits.view(np.float16).astype(np.float32)[~untouched]
+    assert np.isfinite(g).all() and np.isfinite(w).all()
+    d = np.abs(g - w)
+    assert np.all(d <= ATOL + RTOL * np.abs(w)), float((d / (ATOL + RTOL * np.abs(w))).max())
+    return g.size
+
+
+@pytest.mark.parametrize("fmt_name", ["tq4", "fp8", "q8"])
+@pytest.mark.parametrize("seed", range(8))
+def test_random_batches_default_path_against_the_fp32_kernel(env, fmt_name, seed):
+    ffi, kv, synth = env["ffi"], env["kv"], env["synth"]
+    rng = np.random.default_rng(1000 * seed + len(fmt_name))
+    fmt, tr = FORMATS[fmt_name]
+    hq, hkv = HEADS[int(rng.integers(len(HEADS)))]
+    if fmt_name != "tq4" and hq // hkv > 8:     # the fp32 kernel of the 8-bit layers serves groups of up to 8 heads
+        hq, hkv = 16, 2
+    n = int(rng.integers(1, 6))
+    mode = ["decode", "draft", "chunk"][int(rng.integers(3))]
+    q_lens = {"decode": [1] * n, "draft": [int(rng.integers(1, 6)) for _ in range(n)],
+              "chunk": [int(rng.integers(20, 90)) for _ in range(n)]}[mode]
+    ctx = [int(q + rng.integers(0, 500)) for q in q_lens]            # tokens after the step
+    window = int(rng.integers(8, 200)) if rng.random() < 0.3 else 0
+    wl = synth.PagedWorkload([0] * n, ctx, hkv, seed=seed, fill=0xFF, formats=(fmt, fmt, tr, tr))
+    ex = kv.Executor(64 << 20)
+    k, v = synth.make_kv(sum(ctx), hkv, seed)
+    kv.kv_cache_write(ex, wl.layer, wl.step(), k.cuda(), v.cuda())
+    for s, c, ql in zip(wl.seqs, ctx, q_lens):
+        s.commit(c - ql)
+    T = sum(q_lens)
+    kw = {}
+    if rng.random() < 0.5:
+        vtm = (rng.random(T) > 0.2).astype(np.uint8)
+        kw["valid_token_mask"] = vtm
+    if n > 1 and rng.random() < 0.3:
+        vrm = np.ones(n, np.uint8)
+        vrm[int(rng.integers(n))] = 0
+        kw["valid_req_mask"] = vrm
+    if window:
+        kw["sliding_window"] = window
+    b = wl.step(q_lens=q_lens, **kw)
+    q = synth.make_q(T, hq, seed + 1).cuda()
+    outs = []
+    for flags in (0, ffi.EXEC_FLAG_PRECISE_ATTENTION):
+        ex.ex.flags = flags
+        out = torch.full((T, hq, 256), 0, dtype=torch.int16, device="cuda")
+        out.fill_(0x5500)
+        kv.paged_attention(ex, wl.layer, b, q, out.view(torch.float16), hq)
+        torch.cuda.synchronize()
+        outs.append(out.cpu().numpy().view(np.uint16))
+    ex.ex.flags = 0
+    _close(outs[0], outs[1], 0x5500)
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_random_selected_lists_stream_kernel_against_the_fp32_kernel(env, seed):
+    ffi, kv, synth = env["ffi"], env["kv"], env["synth"]
+    rng = np.random.default_rng(77 + seed)
+    hq, hkv = HEADS[int(rng.integers(len(HEADS)))]
+    n = int(rng.integers(1, 4))
+    ctx = [int(rng.integers(1, 700)) for _ in range(n)]
+    wl = synth.PagedWorkload([0] * n, ctx, hkv, seed=seed, fill=0xFF)
+    ex = kv.Executor(64 << 20)
+    k, v = synth.make_kv(sum(ctx), hkv, seed)
+    kv.kv_cache_write(ex, wl.layer, wl.step(), k.cuda(), v.cuda())
+    T = int(rng.integers(1, 9))
+    select_k = int(rng.integers(1, 70))
+    phys = np.full((T, select_k), -1, np.int32)
+    logical = np.zeros((T, select_k), np.int32)
+    n_sel = np.zeros(T, np.int32)
+    pos = np.zeros(T, np.int32)
+    for t in range(T):
+        s = int(rng.integers(n))
+        pos[t] = int(rng.integers(ctx[s]))
+        groups = (ctx[s] + 3) // 4
+        pick = rng.permutation(groups)[:select_k]              # any group of the sequence: some lie beyond pos
+        pages = np.asarray(wl.seqs[s].pages)
+        logical[t, :len(pick)] = pick
+        phys[t, :len(pick)] = pages[pick // 4] * 4 + pick % 4
+        phys[t, :len(pick)][rng.random(len(pick)) < 0.15] = -1
+        n_sel[t] = int(rng.integers(0, len(pick) + 1))
+    vtm = (rng.random(T) > 0.2).astype(np.uint8)
+    dev = [torch.from_numpy(a).cuda() for a in (phys, logical, n_sel, pos, vtm)]
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(T, hq, 256, generator=g).to(torch.float16).cuda()
+    gate = (torch.randn(T, hq, 256, generator=g) * 2).to(torch.float16).cuda()
+    hadamard = bool(rng.integers(2))
+    fn = getattr(env["lib"], "warp34_qsa_sparse_paged_attn_hadamard_f16" if hadamard else "warp34_qsa_sparse_paged_attn_f16")
+    outs = []
+    for flags in (0, ffi.EXEC_FLAG_PRECISE_ATTENTION):
+        ex.ex.flags = flags
+        out = torch.full((T, hq, 256), 0, dtype=torch.int16, device="cuda")
+        out.fill_(0x5500)
+        assert fn(C.addressof(ex.ex), q.data_ptr(), gate.data_ptr(), C.addressof(wl.layer.layout), dev[0].data_ptr(),
+                  dev[1].data_ptr(), dev[2].data_ptr(), dev[3].data_ptr(), dev[4].data_ptr(), out.data_ptr(), T, hq,
+                  select_k, 0.0625) == 0
+        torch.cuda.synchronize()
+        if flags == 0:
+            assert int(ex.scratch[:4].cpu().numpy().view(np.int32)[0]) & 3 == 0
+        outs.append(out.cpu().numpy().view(np.uint16))
+    ex.ex.flags = 0
+    assert not (outs[1] == 0x5500).any(), "the query-sparse entry point writes every row"
+    assert (outs[0][vtm == 0] == 0).all() and (outs[1][vtm == 0] == 0).all()
+    g0 = outs[0].view(np.float16).astype(np.float32)
+    g1 = outs[1].view(np.float16).astype(np.float32)
+    assert np.isfinite(g0).all() and np.isfinite(g1).all()
+    assert np.all(np.abs(g0 - g1) <= ATOL + RTOL * np.abs(g1)), float(np.abs(g0 - g1).max())
