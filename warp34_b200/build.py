@@ -88,7 +88,11 @@ def build_bounds(force=False):
 
 
 def build_all(force=False):
-    return build_cuda(force), build_host(force), build_bounds(force)
+    """Everything, the regular and the bounds-checked kernel library side by side (nvcc is the long pole)."""
+    from concurrent.futures import ThreadPoolExecutor
+    with ThreadPoolExecutor(max_workers=3) as pool:
+        jobs = [pool.submit(build_cuda, force), pool.submit(build_host, force), pool.submit(build_bounds, force)]
+        return tuple(j.result() for j in jobs)
 
 
 if __name__ == "__main__":
