@@ -582,6 +582,8 @@ constexpr int kExactWarps = 8, kExactStages = 4;
 // below a quarter of the mass moves the output by less than a quarter of that.  (Gating the residual
 // of P x d_v the same way, at 1/16 of the mass, measured no faster than carrying it on every page.)
 constexpr float kPeakedWeight = 0.25f;
+// The prefill kernel (tensor-bound) also gates the residual of P x d_v, at this fraction of the mass.
+constexpr float kPResidualWeight = 1.0f / 64.0f;
 // Rounding residuals are 2^-12 of their values, which for Q' (about 0.1) and for the table's
 // centroids (0.008 .. 0.16) lies in fp16's subnormal range; as e5m2 bytes they would keep no
 // significant bits at all.  They are stored times 2^11 and the products scaled back in fp32.

@@ -414,6 +414,11 @@ __global__ void __launch_bounds__(kPxWarps * 32, 1) tq4_attention_prefill_exact_
         // rows that do not exist score 0 against their zero query; they must not count as peaks
         const bool peaked = __any_sync(0xffffffffu, (rvalid[0] && pk0 > kPeakedWeight * l_run[0]) ||
                                                     (rvalid[1] && pk1 > kPeakedWeight * l_run[1]));
+        // The fp16 rounding residual of P d_v (2^-12 relative, independent from key to key) goes through
+        // its own product only on pages where some key holds more than kPResidualWeight of a row's mass
+        // so far: keys below it move an output by less than 1.4e-4 sqrt(kPResidualWeight) max|v| in all.
+        const bool p_residual = __any_sync(0xffffffffu, (rvalid[0] && pk0 > kPResidualWeight * l_run[0]) ||
+                                                        (rvalid[1] && pk1 > kPResidualWeight * l_run[1]));
         // P d_v as A fragments (k = the page's 16 tokens), value and residual, one set per 128-half of V
         float pd[2][2][4];   // [half][n][c]
 #pragma unroll
@@ -469,9 +474,39 @@ __global__ void __launch_bounds__(kPxWarps * 32, 1) tq4_attention_prefill_exact_
                 const uint32_t a3 = W34_LUT(hi_cd, t);
                 const int n = 2 * (4 * i4 + t);
                 mma16816_a4(o[n], pa[half], a0, a2);
-                mma16816_a4(o[n], pl[half], a0, a2);
                 mma16816_a4(o[n + 1], pa[half], a1, a3);
-                mma16816_a4(o[n + 1], pl[half], a1, a3);
+            }
+        }
+        if (p_residual) {   // (P d_v)_residual V, a second pass over the page's V codes
+#pragma unroll
+            for (int i4 = 0; i4 < 4; ++i4) {
+                const int half = i4 >> 1;
+                uint32_t w[4];
+                const uint32_t off = 4u * ((half ? 17u : 0u) + vwb + 2u * (i4 & 1));
+                w[0] = W34_LDS(vr + off);
+                w[1] = W34_LDS(vr + kTq4RowBytes + off);
+                w[2] = W34_LDS(vr + 4u * kTq4RowBytes + off);
+                w[3] = W34_LDS(vr + 5u * kTq4RowBytes + off);
+                if (i4 == 0 && gid == 0) {
+                    w[0] = (w[0] >> 16) | (W34_LDS(vr + 64) << 16);
+                    w[1] = (w[1] >> 16) | (W34_LDS(vr + kTq4RowBytes + 64) << 16);
+                    w[2] = (w[2] >> 16) | (W34_LDS(vr + 4u * kTq4RowBytes + 64) << 16);
+                    w[3] = (w[3] >> 16) | (W34_LDS(vr + 5u * kTq4RowBytes + 64) << 16);
+                }
+                const uint32_t lo_ab = (w[0] & 0x0f0f0f0fu) | ((w[1] << 4) & 0xf0f0f0f0u);
+                const uint32_t hi_ab = ((w[0] >> 4) & 0x0f0f0f0fu) | (w[1] & 0xf0f0f0f0u);
+                const uint32_t lo_cd = (w[2] & 0x0f0f0f0fu) | ((w[3] << 4) & 0xf0f0f0f0u);
+                const uint32_t hi_cd = ((w[2] >> 4) & 0x0f0f0f0fu) | (w[3] & 0xf0f0f0f0u);
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    const uint32_t a0 = W34_LUT(lo_ab, t);
+                    const uint32_t a1 = W34_LUT(hi_ab, t);
+                    const uint32_t a2 = W34_LUT(lo_cd, t);
+                    const uint32_t a3 = W34_LUT(hi_cd, t);
+                    const int n = 2 * (4 * i4 + t);
+                    mma16816_a4(o[n], pl[half], a0, a2);
+                    mma16816_a4(o[n + 1], pl[half], a1, a3);
+                }
             }
         }
         if (peaked) {   // (P d_v / kResidualScale) V_residual, a second pass over the page's V codes
