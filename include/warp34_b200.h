@@ -397,8 +397,8 @@ int warp34_kv_page_copy(const warp34_exec* ex, const warp34_kv_layer_layout* lay
  *  - Same inputs, outputs, masks and result as warp34_paged_attention_f16; `stream` replaces
  *    the warp34_exec.
  *  - Limit: the batch must fit the built-in workspace: the plan, 8256-byte partials (one per
- *    group of 8 query rows and one more per request, for every kv head, plus 8) and 6 KiB of
- *    query fragments per group; about 740 (request, kv head) pairs of a decode batch, e.g. 185
+ *    group of 8 query rows and one more per request, for every kv head, plus 8) and 6.25 KiB of
+ *    query fragments per group; about 730 (request, kv head) pairs of a decode batch, e.g. 182
  *    requests at 4 kv heads, is the ceiling.  A
  *    prefill chunk (more than 24 query rows per request and kv head) uses only the status word,
  *    whatever its size.  Larger batches are refused with cudaErrorInvalidValue and nothing is

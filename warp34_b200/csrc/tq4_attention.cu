@@ -324,6 +324,7 @@ struct StreamParams {
     // Query-sparse mode (sel_phys != nullptr): request r is token r, its "pages" are units of four
     // selected 4-token groups (physical group id = page * 4 + group in page, logical group index for the
     // causal test against seq_pos[r]); rows of masked tokens are written as zeros.
+    int q_floor = 0;       // query fragments for the exact build: hi rounded down, residual bytes 0..255
     const int32_t* sel_phys = nullptr;
     const int32_t* sel_logical = nullptr;
     const int32_t* num_selected = nullptr;
@@ -349,8 +350,12 @@ __device__ __forceinline__ int32_t* plan_array(uint8_t* scratch, int which, int 
 }
 
 // Words per lane of one work item's query fragments: 16 k-steps x 2 B-fragment words of fp16(Q'),
-// then 16 words holding the fp16 rounding residual of Q' as e5m2 bytes (four per k-step).
-constexpr int kQFragWords = 48;
+// then 16 words holding the residual of Q' as bytes (four per k-step): Q' = hi + lo with hi the fp16
+// value just below Q' (rounded towards minus infinity), so that 0 <= lo < 1 ulp; lo divided by the
+// row's own step (largest lo of the row / 255) and rounded is an integer 0..255, which as the low
+// byte of an fp16 word is the subnormal number integer x 2^-24: exact, and no arithmetic to widen it;
+// then the steps of the lane's two rows (2 tig, 2 tig + 1), times 2^24, as floats.
+constexpr int kQFragWords = 50;
 __host__ __device__ inline size_t qfrag_item_bytes() { return (size_t)kQFragWords * 32 * sizeof(uint32_t); }
 __device__ void qprep_block(const StreamParams& p, int idx);
 constexpr int kPlanThreads = 32 * kRowsPerGroup;  // the query-fragment blocks use one warp per query row
@@ -566,7 +571,7 @@ __device__ __forceinline__ uint32_t token_offset(int t) {  // byte offset of tok
 
 // The streaming kernel comes in two builds.
 //  * exact (default): every fp16 tensor-core operand that carries a rounding error of its own is
-//    fed as value + residual: Q' (residual kept as e5m2 bytes, widened in registers), the K
+//    fed as value + residual: Q' (residual kept as one byte per element, widened in registers), the K
 //    centroids (the lookup returns value pair and residual pair at once) and, on pages where some
 //    weight is large enough to matter, P x d_v.  Three score MMAs per k-step instead of one.  With
 //    fp16 operands alone a softmax weight is off by a few 1e-4 relative, which a x20 outlier channel
@@ -584,9 +589,13 @@ constexpr int kExactWarps = 8, kExactStages = 4;
 constexpr float kPeakedWeight = 0.25f;
 // The prefill kernel (tensor-bound) also gates the residual of P x d_v, at this fraction of the mass.
 constexpr float kPResidualWeight = 1.0f / 64.0f;
-// Rounding residuals are 2^-12 of their values, which for Q' (about 0.1) and for the table's
-// centroids (0.008 .. 0.16) lies in fp16's subnormal range; as e5m2 bytes they would keep no
-// significant bits at all.  They are stored times 2^11 and the products scaled back in fp32.
+// Rounding residuals are 2^-12 of their values.  Those of the table's centroids (values 0.12 .. 2.6
+// after the common factor; residuals at most 1e-3, at least a few hundred fp16 subnormal steps) are
+// stored in this kernel's table times 2^11, as normal fp16 numbers, and their products scaled back in
+// fp32: the MMA takes subnormal operands as they are (the prefill kernel's table holds the residuals
+// unscaled and adds their product straight to the scores), but this kernel measured 1.4 % faster with
+// the scaled table.  The residual of Q' is kept as one byte per element in units of a step of its own
+// row (see the query-fragment block).
 constexpr float kResidualScale = 2048.0f;
 
 // Eight warps: the query fragments of item idx = (request * kv heads + kv head) * q_groups_max + group.
@@ -594,6 +603,7 @@ constexpr float kResidualScale = 2048.0f;
 // columns], times q_scale); after the barrier it builds the fragment words of step w.
 __device__ void qprep_block(const StreamParams& p, int idx) {
     __shared__ float q_stage[kRowsPerGroup * kHeadDim];
+    __shared__ float q_step[kRowsPerGroup];
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int gid = lane >> 2, tig = lane & 3;
     const int hkv = p.layout.local_kv_heads;
@@ -621,17 +631,31 @@ __device__ void qprep_block(const StreamParams& p, int idx) {
 #pragma unroll
             for (int j = 0; j < 8; ++j) t[j] = 0.0f;
         }
+        float rmax = 0.0f;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) q_stage[row8 * kHeadDim + lane + 32 * j] = t[j] * p.q_scale;
+        for (int j = 0; j < 8; ++j) {
+            const float f = t[j] * p.q_scale;
+            q_stage[row8 * kHeadDim + lane + 32 * j] = f;
+            if (p.q_floor) rmax = fmaxf(rmax, f - __half2float(__float2half_rd(f)));
+        }
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, d));
+        if (lane == 0) q_step[row8] = rmax * (1.0f / 255.0f);
     }
     __syncthreads();
     // B fragments of Q'^T: step s (0..7) covers half s >> 2, virtual word 4 tig + (s & 3);
     // k-step 2 s uses elements 0..3 of the word, k-step 2 s + 1 elements 4..7.
-    // Q' = hi + lo: hi is fp16, lo (the fp16 rounding residual, times kResidualScale) is kept as
-    // 4 e5m2 bytes per k-step and widened to fp16 pairs by two PRMTs right before its MMA.
+    // Q' = hi + lo: hi is fp16 (rounded down), lo >= 0 is kept as 4 bytes per k-step, integers in units
+    // of the row's step, and widened to fp16 pairs (subnormals) by two PRMTs right before its MMA.
     const int s = wid;
     const int half = s >> 2, vw = 4 * tig + (s & 3);
     uint32_t* dst = p.qfrag + (size_t)idx * (kQFragWords * 32) + lane;
+    const float step = q_step[gid];
+    const float inv_step = step > 0.0f ? 1.0f / step : 0.0f;
+    if (s == 0) {   // the steps of the rows whose scores this lane holds in the stream kernel
+        dst[48 * 32] = __float_as_uint(q_step[2 * tig] * 16777216.0f);
+        dst[49 * 32] = __float_as_uint(q_step[2 * tig + 1] * 16777216.0f);
+    }
 #pragma unroll
     for (int hk = 0; hk < 2; ++hk) {
         uint32_t lo_bytes = 0;
@@ -640,13 +664,12 @@ __device__ void qprep_block(const StreamParams& p, int idx) {
             const int e = 4 * hk + 2 * x;
             const float f0 = q_stage[gid * kHeadDim + vword_col(half, vw, e)];
             const float f1 = q_stage[gid * kHeadDim + vword_col(half, vw, e + 1)];
-            const __half h0 = __float2half_rn(f0), h1 = __float2half_rn(f1);
+            const __half h0 = p.q_floor ? __float2half_rd(f0) : __float2half_rn(f0);
+            const __half h1 = p.q_floor ? __float2half_rd(f1) : __float2half_rn(f1);
             dst[(2 * (2 * s + hk) + x) * 32] = (uint32_t)__half_as_ushort(h0) | ((uint32_t)__half_as_ushort(h1) << 16);
-            // residuals, rounded to the top byte of their fp16 encoding (e5m2)
-            const uint32_t r0 = __half_as_ushort(__float2half_rn((f0 - __half2float(h0)) * kResidualScale));
-            const uint32_t r1 = __half_as_ushort(__float2half_rn((f1 - __half2float(h1)) * kResidualScale));
-            const uint32_t b0 = (r0 + 0x7fu + ((r0 >> 8) & 1u)) >> 8;
-            const uint32_t b1 = (r1 + 0x7fu + ((r1 >> 8) & 1u)) >> 8;
+            // residuals in units of the row's step: integers 0..255
+            const uint32_t b0 = (uint32_t)max(min(__float2int_rn((f0 - __half2float(h0)) * inv_step), 255), 0);
+            const uint32_t b1 = (uint32_t)max(min(__float2int_rn((f1 - __half2float(h1)) * inv_step), 255), 0);
             lo_bytes |= (b0 & 0xffu) << (16 * x) | (b1 & 0xffu) << (16 * x + 8);
         }
         dst[(32 + 2 * s + hk) * 32] = lo_bytes;
@@ -784,6 +807,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) tq4_attention_stream_kernel(con
         // ---- Q' fragments of this item, prepared by the plan launch ---------------------------
         uint32_t qb[16][2];
         uint32_t qlo[16];
+        float q_step[2] = {0.0f, 0.0f};
         {
             const uint32_t* qf = p.qfrag + ((size_t)(r * p.layout.local_kv_heads + kv_head) * p.q_groups_max + group) *
                                                (kQFragWords * 32) + lane;
@@ -792,6 +816,10 @@ __global__ void __launch_bounds__(WARPS * 32, 1) tq4_attention_stream_kernel(con
                 qb[i][0] = __ldg(qf + (2 * i) * 32);
                 qb[i][1] = __ldg(qf + (2 * i + 1) * 32);
                 qlo[i] = EXACT ? __ldg(qf + (32 + i) * 32) : 0u;
+            }
+            if (EXACT) {
+                q_step[0] = __uint_as_float(__ldg(qf + 48 * 32));
+                q_step[1] = __uint_as_float(__ldg(qf + 49 * 32));
             }
         }
         // ---- accumulators ----------------------------------------------------------------
@@ -954,8 +982,8 @@ __global__ void __launch_bounds__(WARPS * 32, 1) tq4_attention_stream_kernel(con
                     } else {
                         mma16816(sa[half], a0, a1, a2, a3, qb[2 * s8 + hk][0], qb[2 * s8 + hk][1]);
                     }
-                    if (EXACT) {   // residual bytes -> fp16 pairs: byte b becomes the half b << 8
-                        mma16816(sl[half], a0, a1, a2, a3, __byte_perm(ql, 0, 0x1404), __byte_perm(ql, 0, 0x3424));
+                    if (EXACT) {   // residual bytes -> fp16 pairs: byte b becomes the half 0x00bb = b x 2^-24
+                        mma16816(sl[half], a0, a1, a2, a3, __byte_perm(ql, 0, 0x4140), __byte_perm(ql, 0, 0x4342));
                     }
                 }
             }
@@ -969,7 +997,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) tq4_attention_stream_kernel(con
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
 #pragma unroll
-                    for (int x = 0; x < 4; ++x) sa[h][x] += (sl[h][x] + sk[h][x]) * (1.0f / kResidualScale);
+                    for (int x = 0; x < 4; ++x) sa[h][x] += sl[h][x] * q_step[x & 1] + sk[h][x] * (1.0f / kResidualScale);
                 }
             }
             float sc[4];
@@ -2344,6 +2372,7 @@ static int launch_attention(const warp34_exec* ex, const warp34_kv_layer_layout*
     p.rows_per_group = rpg;
     p.q_scale = batch->sm_scale * 1.4426950408889634f / kLutScale;
     p.natural = 0;
+    p.q_floor = fast ? 0 : 1;
     p.og = og;
     p.qfrag = (nt == 1) ? reinterpret_cast<uint32_t*>(p.scratch + plan + (size_t)p.max_slots * slot_bytes) : nullptr;
     cudaStream_t st = (cudaStream_t)ex->stream;
@@ -2422,6 +2451,7 @@ static int launch_qsa_stream(const warp34_exec* ex, const QsaParams& q, bool* ta
     p.rows_per_group = kRowsPerGroup;
     p.q_scale = q.sm_scale * 1.4426950408889634f / kLutScale;
     p.natural = 0;
+    p.q_floor = 1;
     p.og.gate = q.gate;
     p.og.mode = (q.gate != nullptr || q.hadamard) ? ((q.hadamard ? 2 : 1) | 4) : 0;
     p.qfrag = reinterpret_cast<uint32_t*>(p.scratch + plan + (size_t)p.max_slots * slot_bytes);

@@ -29,7 +29,7 @@ constexpr int kPxWarps = 8;
 constexpr int kPxRows = 16 * kPxWarps;
 constexpr int kPxStages = 4;
 constexpr uint32_t kPxQHiBytes = 16u * 32u * 16u;   // per warp [k-step][lane][a0 a1 a2 a3]
-constexpr uint32_t kPxQLoBytes = 16u * 32u * 8u;    // per warp [k-step][lane][two e5m2 bytes per register]
+constexpr uint32_t kPxQLoBytes = 16u * 32u * 8u;    // per warp [k-step][lane][two residual bytes per register]
 
 struct PrefillExactParams {
     warp34_kv_layer_layout layout;
@@ -82,7 +82,7 @@ __global__ void __launch_bounds__(kPxWarps * 32, 1) tq4_attention_prefill_exact_
     }
     ring = carve.take(kPxStages * kStageStride, 128);
     bars = carve.take(2 * kPxStages * 8, 8);        // full[stage], then empty[stage]
-    const uint32_t red = carve.take((4 * kPxWarps + 1) * 4, 4);   // per-warp key ranges, abort flag
+    const uint32_t red = carve.take((4 * kPxWarps + 1) * 4 + kPxRows * 4, 4);   // per-warp key ranges, abort flag, row steps
     if (!carve.ok) {
         if (tid == 0 && p.status != nullptr) atomicOr(p.status, 2);
         return;
@@ -94,8 +94,9 @@ __global__ void __launch_bounds__(kPxWarps * 32, 1) tq4_attention_prefill_exact_
     int* s_slo = s_hi + kPxWarps;
     int* s_shi = s_slo + kPxWarps;
     int* s_failed = s_shi + kPxWarps;
+    float* s_qstep = reinterpret_cast<float*>(s_failed + 1);   // [128 rows]: step of the row's Q' residual bytes
 
-    // Tables as in the exact streaming kernel: (value pair, residual pair x kResidualScale) in 16
+    // Tables as in the exact streaming kernel: (value pair, residual pair) in 16
     // copies of 8 bytes for K, value pair in 32 copies of 4 bytes in the upper half of the entry for V.
     for (int i = tid; i < 256 * 32; i += blockDim.x) {
         const int byte = i >> 5, ln = i & 31;
@@ -105,7 +106,7 @@ __global__ void __launch_bounds__(kPxWarps * 32, 1) tq4_attention_prefill_exact_
         if (ln < 16) {
             sts32(lut_addr + (uint32_t)(byte * 256 + ln * 8), hi);
             sts32(lut_addr + (uint32_t)(byte * 256 + ln * 8 + 4),
-                  pack_half2((c0 - hf.x) * kResidualScale, (c1 - hf.y) * kResidualScale));
+                  pack_half2(c0 - hf.x, c1 - hf.y));
         }
         sts32(lut_addr + (uint32_t)(byte * 256 + 128 + ln * 4), hi);
     }
@@ -184,6 +185,20 @@ __global__ void __launch_bounds__(kPxWarps * 32, 1) tq4_attention_prefill_exact_
 #pragma unroll
             for (int j = 0; j < 8; ++j) tv[j] = 0.0f;
         }
+        // Q' = hi + lo, hi the fp16 value just below Q': 0 <= lo < 1 ulp, stored as a byte in units of the
+        // row's step (largest lo / 255); as the low byte of an fp16 word that byte is the subnormal
+        // number byte x 2^-24, exact and free to widen.
+        float lo_max = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float f = tv[j] * p.q_scale;
+            lo_max = fmaxf(lo_max, f - __half2float(__float2half_rd(f)));
+        }
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) lo_max = fmaxf(lo_max, __shfl_xor_sync(0xffffffffu, lo_max, d));
+        const float step = lo_max * (1.0f / 255.0f);
+        const float inv_step = step > 0.0f ? 1.0f / step : 0.0f;
+        if (lane == 0) s_qstep[16 * wid + rr] = step * 16777216.0f;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             const int c = lane + 32 * j;
@@ -196,9 +211,8 @@ __global__ void __launch_bounds__(kPxWarps * 32, 1) tq4_attention_prefill_exact_
             const int dst_lane = (rr & 7) * 4 + (vw >> 2);
             const int reg = 2 * ((e >> 1) & 1) + (rr >> 3);
             const float f = tv[j] * p.q_scale;
-            const __half h = __float2half_rn(f);
-            const uint32_t r16 = __half_as_ushort(__float2half_rn((f - __half2float(h)) * kResidualScale));
-            const uint32_t r8 = (r16 + 0x7fu + ((r16 >> 8) & 1u)) >> 8;   // fp16 -> e5m2, round to nearest even
+            const __half h = __float2half_rd(f);
+            const uint32_t r8 = (uint32_t)max(min(__float2int_rn((f - __half2float(h)) * inv_step), 255), 0);
             sts16(qhi + (uint32_t)(ks * 512 + dst_lane * 16 + reg * 4 + (e & 1) * 2), __half_as_ushort(h));
             sts8(qlo + (uint32_t)(ks * 256 + dst_lane * 8 + reg * 2 + (e & 1)), r8 & 0xffu);
         }
@@ -213,6 +227,8 @@ __global__ void __launch_bounds__(kPxWarps * 32, 1) tq4_attention_prefill_exact_
     }
     const int pg_lo = (kv_hi >= kv_lo) ? (kv_lo >> 4) : 0;
     const int npages = (kv_hi >= kv_lo) ? ((kv_hi >> 4) - pg_lo + 1) : 0;
+    // steps (x 2^24) of the Q' residual bytes of the two rows whose scores this lane holds
+    const float qstep_a = s_qstep[16 * wid + gid], qstep_b = s_qstep[16 * wid + gid + 8];
 
     float o[32][4];
 #pragma unroll
@@ -279,7 +295,8 @@ __global__ void __launch_bounds__(kPxWarps * 32, 1) tq4_attention_prefill_exact_
 #define W34_LUTK(word, k) lds64_lut(__byte_perm((word), lutk_lane, 0x7604 + ((k) << 4)))
 
         // ---- S = Q' K^T: n-tile 0 = tokens key(0..7), n-tile 1 = tokens key(8..15); per 128-half;
-        //      sr collects both residual products, which carry the factor kResidualScale ------------
+        //      sa also takes the product with the K residuals; sr the one with the Q' residual bytes,
+        //      which carries the steps of the rows (gid for c = 0, 1; gid + 8 for c = 2, 3) ----------
         float sa[2][2][4], sr[2][2][4];
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -314,16 +331,16 @@ __global__ void __launch_bounds__(kPxWarps * 32, 1) tq4_attention_prefill_exact_
                 const uint4 qh4 = lds128_v(qhi + (uint32_t)(ks * 512 + lane * 16));
                 const uint2 ql2 = lds64_v(qlo + (uint32_t)(ks * 256 + lane * 8));
                 const uint32_t qh[4] = {qh4.x, qh4.y, qh4.z, qh4.w};
-                const uint32_t qr[4] = {__byte_perm(ql2.x, 0, 0x1404), __byte_perm(ql2.x, 0, 0x3424),
-                                        __byte_perm(ql2.y, 0, 0x1404), __byte_perm(ql2.y, 0, 0x3424)};
+                const uint32_t qr[4] = {__byte_perm(ql2.x, 0, 0x4140), __byte_perm(ql2.x, 0, 0x4342),
+                                        __byte_perm(ql2.y, 0, 0x4140), __byte_perm(ql2.y, 0, 0x4342)};
                 const uint2 e0 = W34_LUTK(wa, 2 * hk), e1 = W34_LUTK(wb, 2 * hk);
                 const uint2 e2 = W34_LUTK(wa, 2 * hk + 1), e3 = W34_LUTK(wb, 2 * hk + 1);
                 mma16816_a4(sa[half][0], qh, e0.x, e2.x);
                 mma16816_a4(sa[half][1], qh, e1.x, e3.x);
                 mma16816_a4(sr[half][0], qr, e0.x, e2.x);
                 mma16816_a4(sr[half][1], qr, e1.x, e3.x);
-                mma16816_a4(sr[half][0], qh, e0.y, e2.y);
-                mma16816_a4(sr[half][1], qh, e1.y, e3.y);
+                mma16816_a4(sa[half][0], qh, e0.y, e2.y);
+                mma16816_a4(sa[half][1], qh, e1.y, e3.y);
             }
         }
         // ---- scales of this lane's four tokens kv0 + {0, 1, 4, 5} (index 2 n + e) -------------------
@@ -346,8 +363,8 @@ __global__ void __launch_bounds__(kPxWarps * 32, 1) tq4_attention_prefill_exact_
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 const int j = 2 * n + (c & 1);
-                sc[n][c] = dk0[j] * (sa[0][n][c] + sr[0][n][c] * (1.0f / kResidualScale)) +
-                           dk1[j] * (sa[1][n][c] + sr[1][n][c] * (1.0f / kResidualScale));
+                const float qs = (c < 2) ? qstep_a : qstep_b;
+                sc[n][c] = dk0[j] * (sa[0][n][c] + sr[0][n][c] * qs) + dk1[j] * (sa[1][n][c] + sr[1][n][c] * qs);
             }
         }
         bool msk[2][4];
@@ -509,18 +526,7 @@ __global__ void __launch_bounds__(kPxWarps * 32, 1) tq4_attention_prefill_exact_
                 }
             }
         }
-        if (peaked) {   // (P d_v / kResidualScale) V_residual, a second pass over the page's V codes
-            uint32_t ps[2][4];
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-#pragma unroll
-                for (int r4 = 0; r4 < 4; ++r4) {
-                    const int n = r4 >> 1, c = 2 * (r4 & 1);
-                    const __half2 sc2 = __floats2half2_rn(pd[h][n][c] * (1.0f / kResidualScale),
-                                                          pd[h][n][c + 1] * (1.0f / kResidualScale));
-                    ps[h][r4] = *reinterpret_cast<const uint32_t*>(&sc2);
-                }
-            }
+        if (peaked) {   // (P d_v) V_residual, a second pass over the page's V codes
 #pragma unroll
             for (int i4 = 0; i4 < 4; ++i4) {
                 const int half = i4 >> 1;
@@ -545,8 +551,8 @@ __global__ void __launch_bounds__(kPxWarps * 32, 1) tq4_attention_prefill_exact_
                     const uint2 e0 = W34_LUTK(lo_ab, t), e1 = W34_LUTK(hi_ab, t);
                     const uint2 e2 = W34_LUTK(lo_cd, t), e3 = W34_LUTK(hi_cd, t);
                     const int n = 2 * (4 * i4 + t);
-                    mma16816_a4(o[n], ps[half], e0.y, e2.y);
-                    mma16816_a4(o[n + 1], ps[half], e1.y, e3.y);
+                    mma16816_a4(o[n], pa[half], e0.y, e2.y);
+                    mma16816_a4(o[n + 1], pa[half], e1.y, e3.y);
                 }
             }
         }
