@@ -192,7 +192,12 @@ int warp34_fused_k_rmsnorm_rope_kv_cache_write_f16(
  *
  * Accuracy: every output is within 2e-3 + 1e-2 |b| of fp32 dequant-then-attend (b).  The
  * tensor-core kernels get there by feeding each fp16 operand as value + rounding residual;
- * WARP34_B200_EXEC_FLAG_FAST_ATTENTION trades that for speed.  Kernels: decode and verify batches
+ * measured against float64 this holds with margin from K, V ~ N(0, 1) with x20 outlier channels
+ * and Q ~ N(0, 1) up to twice as many outlier channels, x30 (K) and x60 (V) outliers and a query
+ * scale of 2.  For activations far beyond that (x60 outliers in 32 channels and a query scale of
+ * 3: a few outputs per million miss the bound by up to 3.6x) WARP34_B200_EXEC_FLAG_PRECISE_ATTENTION
+ * selects the fp32 kernel, which stays below a seventh of the bound on all of these.
+ * WARP34_B200_EXEC_FLAG_FAST_ATTENTION trades the residual operands for speed.  Kernels: decode and verify batches
  * (up to 24 query rows per request and kv head) stream split-KV work items of 8 rows; larger
  * chunks take a 128-row prefill kernel (register MMAs; tcgen05 + TMEM with the fast flag).
  * 8-bit boundary layers (Q8_0, FP8 E4M3) in the canonical packing stream the same way on a
