@@ -194,7 +194,8 @@ int warp34_fused_k_rmsnorm_rope_kv_cache_write_f16(
  * tensor-core kernels get there by feeding each fp16 operand as value + rounding residual;
  * measured against float64 this holds with margin from K, V ~ N(0, 1) with x20 outlier channels
  * and Q ~ N(0, 1) up to twice as many outlier channels, x30 (K) and x60 (V) outliers and a query
- * scale of 2.  For activations far beyond that (x60 outliers in 32 channels and a query scale of
+ * scale of 2 (V outlier channels that alternate in sign from key to key: up to magnitude 60).  For
+ * activations far beyond that (x60 outliers in 32 channels and a query scale of
  * 3: a few outputs per million miss the bound by up to 3.6x) WARP34_B200_EXEC_FLAG_PRECISE_ATTENTION
  * selects the fp32 kernel, which stays below a seventh of the bound on all of these.
  * WARP34_B200_EXEC_FLAG_FAST_ATTENTION trades the residual operands for speed.  Kernels: decode and verify batches

@@ -589,6 +589,9 @@ constexpr int kExactWarps = 8, kExactStages = 4;
 constexpr float kPeakedWeight = 0.25f;
 // The prefill kernel (tensor-bound) also gates the residual of P x d_v, at this fraction of the mass.
 constexpr float kPResidualWeight = 1.0f / 64.0f;
+// The prefill kernel takes the V-centroid residual pass from an eighth of the mass (its pages serve 16 rows
+// per warp, and the pass costs it little).
+constexpr float kPxPeakedWeight = 0.125f;
 // Rounding residuals are 2^-12 of their values.  Those of the table's centroids (values 0.12 .. 2.6
 // after the common factor; residuals at most 1e-3, at least a few hundred fp16 subnormal steps) are
 // stored in this kernel's table times 2^11, as normal fp16 numbers, and their products scaled back in

@@ -429,8 +429,8 @@ __global__ void __launch_bounds__(kPxWarps * 32, 1) tq4_attention_prefill_exact_
         l_run[0] += ps0;
         l_run[1] += ps1;
         // rows that do not exist score 0 against their zero query; they must not count as peaks
-        const bool peaked = __any_sync(0xffffffffu, (rvalid[0] && pk0 > kPeakedWeight * l_run[0]) ||
-                                                    (rvalid[1] && pk1 > kPeakedWeight * l_run[1]));
+        const bool peaked = __any_sync(0xffffffffu, (rvalid[0] && pk0 > kPxPeakedWeight * l_run[0]) ||
+                                                    (rvalid[1] && pk1 > kPxPeakedWeight * l_run[1]));
         // The fp16 rounding residual of P d_v (2^-12 relative, independent from key to key) goes through
         // its own product only on pages where some key holds more than kPResidualWeight of a row's mass
         // so far: keys below it move an output by less than 1.4e-4 sqrt(kPResidualWeight) max|v| in all.
