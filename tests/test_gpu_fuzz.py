@@ -82,14 +82,16 @@ def test_random_batches_default_path_against_the_fp32_kernel(env, fmt_name, seed
     _close(outs[0], outs[1], 0x5500)
 
 
+@pytest.mark.parametrize("fmt_name", ["tq4", "fp8", "q8"])
 @pytest.mark.parametrize("seed", range(8))
-def test_random_selected_lists_stream_kernel_against_the_fp32_kernel(env, seed):
+def test_random_selected_lists_stream_kernel_against_the_fp32_kernel(env, seed, fmt_name):
     ffi, kv, synth = env["ffi"], env["kv"], env["synth"]
     rng = np.random.default_rng(77 + seed)
+    fmt, tr = FORMATS[fmt_name]
     hq, hkv = HEADS[int(rng.integers(len(HEADS)))]
     n = int(rng.integers(1, 4))
     ctx = [int(rng.integers(1, 700)) for _ in range(n)]
-    wl = synth.PagedWorkload([0] * n, ctx, hkv, seed=seed, fill=0xFF)
+    wl = synth.PagedWorkload([0] * n, ctx, hkv, seed=seed, fill=0xFF, formats=(fmt, fmt, tr, tr))
     ex = kv.Executor(64 << 20)
     k, v = synth.make_kv(sum(ctx), hkv, seed)
     kv.kv_cache_write(ex, wl.layer, wl.step(), k.cuda(), v.cuda())

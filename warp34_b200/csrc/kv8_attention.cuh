@@ -340,12 +340,15 @@ __device__ __forceinline__ void kv8x4_to_f16x4(uint32_t w, uint32_t& lo, uint32_
     }
 }
 
-template <int FMT, int STAGES>
+// SPARSE: the query-sparse lists of warp34_qsa_sparse_paged_attn_f16 (see the TQ4 stream kernel): request r
+// is token r, a unit is four entries of its selected list, lanes 0-3 copy their entry's four rows and leave
+// its first position in 16 bytes behind the stage.
+template <int FMT, int STAGES, bool SPARSE = false>
 __global__ void __launch_bounds__(kKv8StreamWarps * 32, 1) kv8_attention_stream_kernel(const StreamParams p) {
     using G = Kv8Stage<FMT>;
     constexpr bool FP8 = FMT == WARP34_KV_FORMAT_FP8_E4M3;
     constexpr int NB = G::kBlocks;
-    constexpr uint32_t kStage = 2u * G::kRunStride;
+    constexpr uint32_t kStage = 2u * G::kRunStride + (SPARSE ? 16u : 0u);
     extern __shared__ __align__(1024) uint8_t smem[];
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     constexpr uint32_t kRingBytes = STAGES * kStage;
@@ -412,7 +415,7 @@ __global__ void __launch_bounds__(kKv8StreamWarps * 32, 1) kv8_attention_stream_
         const int group = item - kv_head * ngroups;
         const int pg0 = page_lo_a[r] + page_in_item;
         const int slot = w_global + item_prefix[r] + item;
-        const ReqGeom g = load_req(p.batch, r);
+        const ReqGeom g = stream_req(p, r);
         const int rows_in_req = g.q_len * p.gqa;
 
         int rmax[2], rmin[2];
@@ -473,11 +476,45 @@ __global__ void __launch_bounds__(kKv8StreamWarps * 32, 1) kv8_attention_stream_
         const int32_t* blocks = p.batch.block_tables + (size_t)r * p.batch.max_blocks_per_req;
         const uint8_t* k_head_base = (const uint8_t*)(uintptr_t)p.layout.k_base + (size_t)kv_head * p.layout.k_head_stride_bytes;
         const uint8_t* v_head_base = (const uint8_t*)(uintptr_t)p.layout.v_base + (size_t)kv_head * p.layout.v_head_stride_bytes;
-        int32_t my_page = (lane < n_here) ? block_table_page(blocks, pg0 + lane, p.batch.max_blocks_per_req, kInKv8) : 0;
-        int32_t next_page = (32 + lane < n_here) ? block_table_page(blocks, pg0 + 32 + lane, p.batch.max_blocks_per_req, kInKv8) : 0;
+        int32_t my_page = 0, next_page = 0;
+        if (!SPARSE) {
+            my_page = (lane < n_here) ? block_table_page(blocks, pg0 + lane, p.batch.max_blocks_per_req, kInKv8) : 0;
+            next_page = (32 + lane < n_here) ? block_table_page(blocks, pg0 + 32 + lane, p.batch.max_blocks_per_req, kInKv8) : 0;
+        }
+        const int32_t* sel_phys = SPARSE ? p.sel_phys + (size_t)r * p.select_k : nullptr;
+        const int32_t* sel_logical = SPARSE ? p.sel_logical + (size_t)r * p.select_k : nullptr;
+        const int n_sel = SPARSE ? min(p.num_selected[r], p.select_k) : 0;
 
         fence_proxy_async();   // generic-proxy writes to the ring (partials, cleared rows) precede the copies
         auto issue = [&](int idx) {
+            if (SPARSE) {
+                const int s = idx % STAGES;
+                const uint32_t bar = bars + 8u * s;
+                const uint32_t dst = ring + (uint32_t)s * kStage;
+                const int gi = 4 * (pg0 + idx) + lane;
+                int ph = -1, first_pos = 0x3fffffff;
+                if (lane < 4 && gi < n_sel) {
+                    ph = sel_phys[gi];
+                    const int lg = sel_logical[gi];
+                    if (ph >= 0 && 4 * lg <= g.ctx_before) first_pos = 4 * lg; else ph = -1;
+                }
+                const int n_valid = __popc(__ballot_sync(0xffffffffu, ph >= 0));
+                pending |= 1u << s;
+                if (lane == 0) mbar_expect_tx(bar, (uint32_t)n_valid * 8u * G::kRow);
+                __syncwarp();
+                if (lane < 4) {
+                    sts32(dst + 2u * G::kRunStride + 4u * lane, (uint32_t)first_pos);
+                    if (ph >= 0) {
+                        const int page = pool_page(ph >> 2, kInKv8);
+                        const uint32_t row_off = (uint32_t)(ph & 3) * 4u * G::kRow;
+                        bulk_g2s(dst + kv8_token_offset<FMT>(4 * lane),
+                                 k_head_base + (size_t)page * p.layout.k_page_stride_bytes + row_off, 4u * G::kRow, bar);
+                        bulk_g2s(dst + G::kRunStride + kv8_token_offset<FMT>(4 * lane),
+                                 v_head_base + (size_t)page * p.layout.v_page_stride_bytes + row_off, 4u * G::kRow, bar);
+                    }
+                }
+                return;
+            }
             const int32_t page = __shfl_sync(0xffffffffu, (idx & 32) ? next_page : my_page, idx & 31);
             pending |= 1u << (idx % STAGES);
             if (lane == 0) {
@@ -500,10 +537,11 @@ __global__ void __launch_bounds__(kKv8StreamWarps * 32, 1) kv8_attention_stream_
         };
 #pragma unroll 1
         for (int i = 0; i < STAGES - 1 && i < n_here; ++i) issue(i);
+        if (SPARSE) __syncwarp();   // the position words written by lanes 0-3 are read by all lanes
 
 #pragma unroll 1
         for (int i = 0; i < n_here; ++i) {
-            if ((i & 31) == 0 && i > 0) {
+            if (!SPARSE && (i & 31) == 0 && i > 0) {
                 const int base = i + 32;
                 const int32_t fresh = (base + lane < n_here) ? block_table_page(blocks, pg0 + base + lane, p.batch.max_blocks_per_req, kInKv8) : 0;
                 if (i & 32) my_page = fresh; else next_page = fresh;
@@ -519,14 +557,35 @@ __global__ void __launch_bounds__(kKv8StreamWarps * 32, 1) kv8_attention_stream_
 
             const uint32_t st = ring + (uint32_t)s * kStage;
             const int kv_base = (pg0 + i) << 4;
-            const bool full = (kv_base >= safe_lo) && (kv_base + 15 <= safe_hi);
-            // Tokens past the last visible key may never have been written: as e4m3 codes their bytes can
-            // be NaN patterns, and 0 x NaN is NaN inside the MMA.  Their V rows are cleared in the stage.
-            const bool clear_tail = FP8 && (kv_base + 15 > kv_hi);
+            bool full = (kv_base >= safe_lo) && (kv_base + 15 <= safe_hi);
+            // query-sparse: first position of the unit's four groups (0x3fffffff: nothing was copied)
+            int fpos[4] = {0, 0, 0, 0};
+            if (SPARSE) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) fpos[j] = (int)lds32(st + 2u * G::kRunStride + 4u * j);
+                full = max(max(fpos[0], fpos[1]), max(fpos[2], fpos[3])) + 3 <= safe_hi;
+            }
+            // Tokens past the last visible key may never have been written (and the rows of a skipped
+            // entry hold whatever the stage held before): as e4m3 codes their bytes can be NaN patterns,
+            // and 0 x NaN is NaN inside the MMA.  Their V rows are cleared in the stage.
+            const bool clear_tail = FP8 && (SPARSE ? !full : (kv_base + 15 > kv_hi));
             if (clear_tail) {
-                for (int t = max(kv_hi + 1 - kv_base, 0); t < kPageTokens; ++t) {
-                    for (int w = lane; w < G::kRow / 4; w += 32) {
-                        sts32(st + (uint32_t)G::kRunStride + kv8_token_offset<FMT>(t) + 4u * (uint32_t)w, 0u);
+                if (SPARSE) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+#pragma unroll
+                        for (int o4 = 0; o4 < 4; ++o4) {
+                            if (fpos[j] + o4 <= kv_hi) continue;
+                            for (int w = lane; w < G::kRow / 4; w += 32) {
+                                sts32(st + (uint32_t)G::kRunStride + kv8_token_offset<FMT>(4 * j + o4) + 4u * (uint32_t)w, 0u);
+                            }
+                        }
+                    }
+                } else {
+                    for (int t = max(kv_hi + 1 - kv_base, 0); t < kPageTokens; ++t) {
+                        for (int w = lane; w < G::kRow / 4; w += 32) {
+                            sts32(st + (uint32_t)G::kRunStride + kv8_token_offset<FMT>(t) + 4u * (uint32_t)w, 0u);
+                        }
                     }
                 }
                 __syncwarp();
@@ -605,7 +664,8 @@ __global__ void __launch_bounds__(kKv8StreamWarps * 32, 1) kv8_attention_stream_
 
             bool msk[4] = {false, false, false, false};
             if (!full) {
-                const int pos_a = kv_base + key_a, pos_b = pos_a + 4;
+                const int pos_a = SPARSE ? ((key_a >> 3) ? fpos[2] : fpos[0]) + (key_a & 3) : kv_base + key_a;
+                const int pos_b = SPARSE ? ((key_a >> 3) ? fpos[3] : fpos[1]) + (key_a & 3) : pos_a + 4;
                 msk[0] = !(pos_a >= rmin[0] && pos_a <= rmax[0]);
                 msk[1] = !(pos_a >= rmin[1] && pos_a <= rmax[1]);
                 msk[2] = !(pos_b >= rmin[0] && pos_b <= rmax[0]);

@@ -13,14 +13,15 @@
 //   * a token masked out by valid_token_mask gets ZERO output rows (not untouched ones);
 //   * the sigmoid gate multiplies the fp32 result (no rounding before it); the Hadamard-64 variant then
 //     rounds to fp16 and rotates every 64 columns.
-// An fp32 dequant-then-attend kernel: a step of the selected lists reads a few tens of MB in pieces
-// of 528 bytes, so the step is bound by launch latency and parallelism, not by the tensor pipe.  One
-// block of four warps per (token, group of G query heads that share a kv head, split); a warp takes
-// every fourth selected group and handles its four rows in one step: one read and one
-// dequantisation of each K and V row serve all G heads, the loads of the four rows are issued
-// before the first is used and their score reductions interleave.  The selected range is cut into
-// `splits` parts so that about four blocks per SM exist whatever the batch size; their states go
-// through the caller's scratch to a merge kernel.  Without scratch the kernel runs unsplit.
+// Two paths.  With a workspace (ex->scratch_ptr) and the canonical packing the lists run on the
+// tensor-core stream kernels (tq4_attention_stream_kernel<.., sparse> for TQ4 rows,
+// kv8_attention_stream_kernel<.., sparse> for 8-bit rows: launch_qsa_stream in tq4_attention.cu).
+// Otherwise (no workspace, other strides, WARP34_B200_EXEC_FLAG_PRECISE_ATTENTION) the fp32
+// dequant-then-attend kernel of this file: one block of four warps per (token, group of G query heads
+// that share a kv head, split); a warp takes every fourth selected group and handles its four rows in
+// one step: one read and one dequantisation of each K and V row serve all G heads, the loads of the
+// four rows are issued before the first is used and their score reductions interleave.  The selected
+// range is cut into `splits` parts when a workspace is there; without one the kernel runs unsplit.
 #pragma once
 
 namespace w34 {
@@ -390,7 +391,7 @@ static int launch_qsa_sparse(const warp34_exec* ex, const void* q, const void* g
     p.hadamard = hadamard;
     p.sm_scale = sm_scale;
     {
-        // TQ4 layers in the canonical packing with enough workspace: the tensor-core stream kernel
+        // canonical packing with enough workspace: the tensor-core stream kernels (TQ4 or 8-bit rows)
         bool taken = false;
         const int rcs = launch_qsa_stream(ex, p, &taken);
         if (rcs != 0 || taken) return rcs;

@@ -1874,7 +1874,10 @@ __global__ void __launch_bounds__(MW * 32) tq4_attention_merge_kernel(const Stre
     if (p.natural) {
         const float inv = (l_tot > 0.0f) ? (1.0f / l_tot) : 0.0f;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) store_act(p.attn_out, out_base + lane + 32 * j, acc[j] * inv, p.io_bf16);
+        for (int j = 0; j < 8; ++j) acc[j] *= inv;
+        apply_output_gate(acc, p.og, out_base, lane, p.io_bf16);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) store_act(p.attn_out, out_base + lane + 32 * j, acc[j], p.io_bf16);
         return;
     }
     const float inv_l = (l_tot > 0.0f) ? (1.0f / (l_tot * kLutScale)) : 0.0f;
@@ -2407,13 +2410,110 @@ static int launch_attention(const warp34_exec* ex, const warp34_kv_layer_layout*
 // Query-sparse lists on the exact stream kernel (TQ4 layers in the canonical packing, a workspace that
 // holds the plan, the query fragments and at least one CTA's partial slots).  *taken = false: the caller
 // runs its fp32 kernel instead.
+// The same lists over 8-bit layers, on kv8_attention_stream_kernel<format, stages, sparse>.
+static int launch_qsa_stream_kv8(const warp34_exec* ex, const QsaParams& q, bool* taken) {
+    const warp34_kv_layer_layout* layout = &q.layout;
+    warp34_attention_batch b = warp34_attention_batch{};
+    b.block_tables = reinterpret_cast<const int32_t*>(q.sel_phys);   // only tested for presence by kv8_stream_ok
+    b.max_blocks_per_req = 1;
+    if (!kv8_stream_ok(ex, layout, &b, q.q, 0) || q.select_k <= 0) return 0;
+    int rc = 0;
+    DeviceInfo* dev = device_info(&rc);
+    if (dev == nullptr) return rc;
+    const int gqa = q.num_q_heads / layout->local_kv_heads;
+    const long long groups = (gqa + kRowsPerGroup - 1) / kRowsPerGroup;
+    const long long items = (long long)q.num_tokens * layout->local_kv_heads * groups;
+    if (items * (((long long)q.select_k + 3) / 4) >= 0x7fffffffll) return 0;
+    const size_t plan = plan_bytes(q.num_tokens);
+    const size_t slot_bytes = (size_t)kPartialFloats * sizeof(float);
+    const size_t avail = ex->scratch_size > plan ? ex->scratch_size - plan : 0;
+    const long long workers = (long long)(avail / slot_bytes) - items;
+    if (workers < kKv8StreamWarps) return 0;
+    int grid = dev->sm_count;
+    if (workers / kKv8StreamWarps < grid) grid = (int)(workers / kKv8StreamWarps);
+    const bool fp8 = layout->k_format == WARP34_KV_FORMAT_FP8_E4M3;
+    const uint32_t stage = 2u * (uint32_t)(fp8 ? Kv8Stage<WARP34_KV_FORMAT_FP8_E4M3>::kRunStride
+                                               : Kv8Stage<WARP34_KV_FORMAT_Q8_0>::kRunStride) + 16u;
+    const uint32_t smem = (uint32_t)(kKv8StreamWarps * kKv8StreamStages) * (stage + 8u);
+    {
+        static std::mutex mu;
+        static bool done[64];
+        int d = 0;
+        rc = (int)cudaGetDevice(&d);
+        if (rc != 0) return rc;
+        if (d < 0 || d >= 64) return (int)cudaErrorInvalidDevice;
+        std::lock_guard<std::mutex> lock(mu);
+        if (!done[d]) {
+            rc = (int)cudaFuncSetAttribute(kv8_attention_stream_kernel<WARP34_KV_FORMAT_FP8_E4M3, kKv8StreamStages, true>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (int)((uint32_t)(kKv8StreamWarps * kKv8StreamStages) *
+                                                 (2u * Kv8Stage<WARP34_KV_FORMAT_FP8_E4M3>::kRunStride + 24u)));
+            if (rc != 0) return rc;
+            rc = (int)cudaFuncSetAttribute(kv8_attention_stream_kernel<WARP34_KV_FORMAT_Q8_0, kKv8StreamStages, true>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (int)((uint32_t)(kKv8StreamWarps * kKv8StreamStages) *
+                                                 (2u * Kv8Stage<WARP34_KV_FORMAT_Q8_0>::kRunStride + 24u)));
+            if (rc != 0) return rc;
+            done[d] = true;
+        }
+    }
+    StreamParams p;
+    p.layout = *layout;
+    p.batch = warp34_attention_batch{};
+    p.batch.valid_token_mask = q.valid_token_mask;
+    p.batch.num_reqs = q.num_tokens;
+    p.batch.total_tokens = q.num_tokens;
+    p.batch.max_q_len = 1;
+    p.batch.mask_mode = WARP34_ATTN_MASK_CAUSAL;
+    p.batch.sliding_window = 0;
+    p.batch.sm_scale = q.sm_scale;
+    p.q_in = q.q;
+    p.attn_out = q.out;
+    p.io_bf16 = 0;
+    p.triple_out = nullptr;
+    p.scratch = reinterpret_cast<uint8_t*>((uintptr_t)ex->scratch_ptr);
+    p.num_q_heads = q.num_q_heads;
+    p.gqa = gqa;
+    p.num_warps = grid * kKv8StreamWarps;
+    p.max_slots = (int)(p.num_warps + items);
+    p.smem_bytes = smem;
+    p.rows_per_group = kRowsPerGroup;
+    p.q_scale = q.sm_scale * 1.4426950408889634f;
+    p.natural = 1;
+    p.og.gate = q.gate;
+    p.og.mode = (q.gate != nullptr || q.hadamard) ? ((q.hadamard ? 2 : 1) | 4) : 0;
+    p.qfrag = nullptr;
+    p.q_groups_max = 0;
+    p.sel_phys = q.sel_phys;
+    p.sel_logical = q.sel_logical;
+    p.num_selected = q.num_selected;
+    p.seq_pos = q.seq_pos;
+    p.select_k = q.select_k;
+    cudaStream_t st = (cudaStream_t)ex->stream;
+    tq4_attention_plan_kernel<<<1, 32, 0, st>>>(p);
+    if (fp8) {
+        kv8_attention_stream_kernel<WARP34_KV_FORMAT_FP8_E4M3, kKv8StreamStages, true><<<grid, kKv8StreamWarps * 32, smem, st>>>(p);
+    } else {
+        kv8_attention_stream_kernel<WARP34_KV_FORMAT_Q8_0, kKv8StreamStages, true><<<grid, kKv8StreamWarps * 32, smem, st>>>(p);
+    }
+    const long long rows = (long long)q.num_tokens * q.num_q_heads;
+    if (rows * 4 < (long long)grid * kKv8StreamWarps / 8) {
+        tq4_attention_merge_kernel<false, 32><<<(unsigned)rows, 1024, 0, st>>>(p);
+    } else {
+        tq4_attention_merge_kernel<false, 4><<<(unsigned)rows, 128, 0, st>>>(p);
+    }
+    *taken = true;
+    return (int)cudaGetLastError();
+}
+
 static int launch_qsa_stream(const warp34_exec* ex, const QsaParams& q, bool* taken) {
     *taken = false;
     const warp34_kv_layer_layout* layout = &q.layout;
-    if ((ex->flags & WARP34_B200_EXEC_FLAG_PRECISE_ATTENTION) != 0 || !tq4_layout_ok(layout) || !stream_layout_ok(layout) ||
-        ex->scratch_ptr == 0 || (ex->scratch_ptr & 15u) != 0u || q.select_k <= 0) {
+    if ((ex->flags & WARP34_B200_EXEC_FLAG_PRECISE_ATTENTION) != 0 || ex->scratch_ptr == 0 || (ex->scratch_ptr & 15u) != 0u) {
         return 0;
     }
+    if (kv8_attention_layout_ok(layout)) return launch_qsa_stream_kv8(ex, q, taken);
+    if (!tq4_layout_ok(layout) || !stream_layout_ok(layout) || q.select_k <= 0) return 0;
     int rc = 0;
     DeviceInfo* dev = device_info(&rc);
     if (dev == nullptr) return rc;
