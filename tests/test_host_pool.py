@@ -4,7 +4,6 @@ step-metadata builder.  The numeric expectations are the reference's own unit te
 crates/warp34-host/tests/tq4_vision_and_moe.rs:35-80)."""
 import ctypes as C
 
-import numpy as np
 import pytest
 
 from warp34_b200 import ffi

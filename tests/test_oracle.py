@@ -1,6 +1,5 @@
 """The CPU oracle (oracle/tq4_oracle.c) against (a) its own algebraic properties and (b) the
 golden fixture produced by the reference's kernels (tests/golden/make_golden.py)."""
-import ctypes as C
 import os
 
 import numpy as np
