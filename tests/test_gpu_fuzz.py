@@ -137,3 +137,47 @@ def test_random_selected_lists_stream_kernel_against_the_fp32_kernel(env, seed, 
     g1 = outs[1].view(np.float16).astype(np.float32)
     assert np.isfinite(g0).all() and np.isfinite(g1).all()
     assert np.all(np.abs(g0 - g1) <= ATOL + RTOL * np.abs(g1)), float(np.abs(g0 - g1).max())
+
+
+@pytest.mark.parametrize("fmt_name,q_hi,flag", [("tq4", 1, None), ("tq4", 1, "EXEC_FLAG_FAST_ATTENTION"), ("tq4", 4, None),
+                                                ("tq4", 4, "EXEC_FLAG_FAST_ATTENTION"), ("fp8", 1, None), ("q8", 3, None)])
+def test_thousands_of_short_requests_with_idle_ones_between(env, fmt_name, q_hi, flag):
+    """3000 requests in one batch, contexts of 1 to 90 tokens, every seventh request with no new token
+    in this step (equal neighbours in query_start_loc): plan, work split and merge at a request count far
+    above the benchmark's, against the fp32 kernels."""
+    ffi, kv, synth = env["ffi"], env["kv"], env["synth"]
+    rng = np.random.default_rng(9000 + q_hi)
+    fmt, tr = FORMATS[fmt_name]
+    hq, hkv = (24, 4) if fmt_name == "tq4" else (16, 4)
+    n = 3000
+    q_lens = [0 if i % 7 == 3 else int(rng.integers(1, q_hi + 1)) for i in range(n)]
+    ctx = [int(max(q, 1) + rng.integers(0, 90)) for q in q_lens]          # tokens after the step
+    wl = synth.PagedWorkload([0] * n, ctx, hkv, seed=5, fill=0xFF, formats=(fmt, fmt, tr, tr))
+    ex = kv.Executor(128 << 20)
+    k, v = synth.make_kv(sum(ctx), hkv, 5)
+    kv.kv_cache_write(ex, wl.layer, wl.step(), k.cuda(), v.cuda())
+    for s, c, ql in zip(wl.seqs, ctx, q_lens):
+        s.commit(c - ql)
+    T = sum(q_lens)
+    b = wl.step(q_lens=q_lens)
+    assert (np.diff(b.host["query_start_loc"]) == 0).sum() >= n // 7
+    q = synth.make_q(T, hq, 6).cuda()
+    outs = []
+    for flags in (getattr(ffi, flag) if flag else 0, ffi.EXEC_FLAG_PRECISE_ATTENTION):
+        ex.ex.flags = flags
+        out = torch.full((T, hq, 256), 0, dtype=torch.int16, device="cuda")
+        out.fill_(0x5500)
+        kv.paged_attention(ex, wl.layer, b, q, out.view(torch.float16), hq)
+        torch.cuda.synchronize()
+        if flags != ffi.EXEC_FLAG_PRECISE_ATTENTION:
+            assert int(ex.scratch[:4].cpu().numpy().view(np.int32)[0]) == 0
+        outs.append(out.cpu().numpy().view(np.uint16))
+    ex.ex.flags = 0
+    if flag is None:
+        assert _close(outs[0], outs[1], 0x5500) == T * hq * 256
+    else:   # single fp16 operands: the documented bound of that build, 4x the plain one at most on these inputs
+        g = outs[0].view(np.float16).astype(np.float32)
+        w = outs[1].view(np.float16).astype(np.float32)
+        assert np.isfinite(g).all()
+        d = np.abs(g - w) / (ATOL + RTOL * np.abs(w))
+        assert d.max() < 4.0 and (d > 1.0).mean() < 1e-4, (float(d.max()), float((d > 1.0).mean()))
