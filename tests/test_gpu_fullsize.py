@@ -9,6 +9,7 @@ to the same bound against the fixture and the CPU oracle in test_gpu_parity.py).
   config 3   128 sequences x 4 query tokens (causal among the drafts), contexts U[2048, 16384]
   config 4   one sequence of 262 144 tokens: single pass, and 8 page shards merged on one GPU
   config 2   one 2048-token chunk after 14 336 cached tokens, 16 / 4 heads
+  beyond     one sequence of 1 048 576 tokens (four times config 4)
 plus page-permutation invariance at config 1's size (0 ULP, the reference's own relational test,
 crates/warp34-host/tests/backbone_and_collectives.rs:453-572)."""
 import numpy as np
@@ -120,6 +121,22 @@ def test_long_context_single_pass_and_eight_page_shards(env):
     ok, msg = plain_parity(merged.float().cpu().numpy(), want)
     print(f"[margin] cfg4 eight page shards: {msg}")
     assert ok, ("8 shards", msg)
+
+
+def test_one_million_token_sequence(env):
+    """Four times config 4: one sequence of 1 048 576 tokens (a 65 536-entry block table row, 262 144
+    (page, kv head) units, 296 partials per row through the wide merge)."""
+    wl, b, q, hq = _workload(env, "cfg4_long_context", ctx=[(1 << 20) - 1])
+    assert wl.seqs[0].num_pages == 65536
+    want = _dequant_then_attend(env, wl, b, q, hq)
+    assert np.isfinite(want).all() and np.abs(want).max() > 0
+    got = _run(env, wl, b, q, hq).float().cpu().numpy()
+    ok, msg = plain_parity(got, want)
+    print(f"[margin] one sequence of 1 048 576 tokens: {msg}")
+    assert ok, msg
+    fast = _run(env, wl, b, q, hq, flags=env["ffi"].EXEC_FLAG_FAST_ATTENTION).float().cpu().numpy()
+    ok, msg = fast_parity(fast, want)
+    assert ok, ("fast build", msg)
 
 
 def test_prefill_chunk_after_14k_cached_tokens(env):
