@@ -135,3 +135,56 @@ def test_query_sparse_lists_are_repeatable(env, fmt):
             assert np.isfinite(bits.view(np.float16).astype(np.float32)).all()
         else:
             assert np.array_equal(first, bits), f"launch {it} differs"
+
+
+def test_two_host_threads_on_two_streams_with_their_own_workspaces(env):
+    """The library keeps no mutable device state between calls besides the caller's workspace: two host
+    threads, each with a stream, a workspace and a pool of its own, run append + attention steps at the
+    same time (ctypes releases the interpreter lock inside the calls) and get the bits a lone thread gets."""
+    import threading
+    ffi, kv, synth = env["ffi"], env["kv"], env["synth"]
+    hq, hkv = 24, 4
+    jobs = [([3000, 17, 811, 4096], 1), ([900, 2100, 64], 4)]
+
+    def run(job, stream, rounds, sink):
+        ctx, q_len = job
+        n = len(ctx)
+        with torch.cuda.stream(stream):
+            wl = synth.PagedWorkload([c - q_len for c in ctx], [q_len] * n, hkv, seed=81)
+            ex = kv.Executor(96 << 20, stream=stream)
+            wl.fill_context(ex, 81)
+            b = wl.step()
+            k, v = synth.make_kv(n * q_len, hkv, 82, device="cuda")
+            q = synth.make_q(n * q_len, hq, 83).cuda()
+            outs = []
+            for _ in range(rounds):
+                out = torch.zeros(n * q_len, hq, 256, dtype=torch.float16, device="cuda")
+                kv.kv_cache_write(ex, wl.layer, b, k, v)
+                kv.paged_attention(ex, wl.layer, b, q, out, hq)
+                outs.append(out)
+            stream.synchronize()
+            assert int(ex.scratch[:4].cpu().numpy().view(np.int32)[0]) == 0
+            sink.append([o.view(torch.int16).cpu() for o in outs])
+
+    alone = []
+    for job in jobs:
+        run(job, torch.cuda.Stream(), 1, alone)
+    together = [[], []]
+    errors = []
+
+    def guarded(i):
+        try:
+            run(jobs[i], torch.cuda.Stream(), 25, together[i])
+        except Exception as e:  # surfaced in the main thread below
+            errors.append(e)
+
+    threads = [threading.Thread(target=guarded, args=(i,)) for i in range(2)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    for i in range(2):
+        assert len(together[i][0]) == 25
+        for o in together[i][0]:
+            assert torch.equal(o, alone[i][0])
