@@ -186,8 +186,12 @@ int warp34_fused_k_rmsnorm_rope_kv_cache_write_f16(
  * [total_tokens, num_q_heads, head_dim].  Replaces warp34_paged_attention_f16
  * (warp34_cuda.h:370-373, op_paged_attn.cu:1266-1448).  Split-KV partials
  * live in ex->scratch_ptr; warp34_paged_attention_scratch_bytes() says how
- * much a batch geometry can use, and any 16-byte-aligned scratch of at least
- * 1 MiB is accepted (less scratch means fewer, longer KV partitions).
+ * much a batch geometry can use.  Any 16-byte-aligned scratch is accepted: less
+ * than that bound means fewer, longer KV partitions, down to a floor of the plan,
+ * one partial slot (8.1 KiB) and one set of query fragments (6.25 KiB) per
+ * (request, kv head, 8-row group) plus the slots of one thread block; below the
+ * floor (about 4 MiB for a decode batch of 64 sequences and 4 kv heads, 170 MiB for 3000)
+ * the call computes the same result with the fp32 kernel that needs no scratch.
  * Masked rows of attn_out are left untouched.
  *
  * Accuracy: every output is within 2e-3 + 1e-2 |b| of fp32 dequant-then-attend (b).  The

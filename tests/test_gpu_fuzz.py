@@ -161,23 +161,27 @@ def test_thousands_of_short_requests_with_idle_ones_between(env, fmt_name, q_hi,
     T = sum(q_lens)
     b = wl.step(q_lens=q_lens)
     assert (np.diff(b.host["query_start_loc"]) == 0).sum() >= n // 7
+    # a slot and a set of query fragments per (request, kv head, row group): far more workspace than a
+    # benchmark batch needs; with less the call would run the kernel without a workspace instead
+    need = env["lib"].warp34_paged_attention_scratch_bytes(C.byref(wl.layer.layout), C.byref(b.desc), hq)
+    assert (64 << 20) < need < (1 << 30), need
+    ex = kv.Executor(int(need))
     q = synth.make_q(T, hq, 6).cuda()
     outs = []
     for flags in (getattr(ffi, flag) if flag else 0, ffi.EXEC_FLAG_PRECISE_ATTENTION):
         ex.ex.flags = flags
         out = torch.full((T, hq, 256), 0, dtype=torch.int16, device="cuda")
         out.fill_(0x5500)
+        ex.scratch[:4].fill_(0x7f)                 # the plan of the split-KV path rewrites the status word
         kv.paged_attention(ex, wl.layer, b, q, out.view(torch.float16), hq)
         torch.cuda.synchronize()
-        if flags != ffi.EXEC_FLAG_PRECISE_ATTENTION:
-            assert int(ex.scratch[:4].cpu().numpy().view(np.int32)[0]) == 0
+        status = int(ex.scratch[:4].cpu().numpy().view(np.int32)[0])
+        assert status == (0x7f7f7f7f if flags == ffi.EXEC_FLAG_PRECISE_ATTENTION else 0), hex(status)
         outs.append(out.cpu().numpy().view(np.uint16))
     ex.ex.flags = 0
     if flag is None:
         assert _close(outs[0], outs[1], 0x5500) == T * hq * 256
-    else:   # single fp16 operands: the documented bound of that build, 4x the plain one at most on these inputs
-        g = outs[0].view(np.float16).astype(np.float32)
-        w = outs[1].view(np.float16).astype(np.float32)
-        assert np.isfinite(g).all()
-        d = np.abs(g - w) / (ATOL + RTOL * np.abs(w))
-        assert d.max() < 4.0 and (d > 1.0).mean() < 1e-4, (float(d.max()), float((d > 1.0).mean()))
+    else:   # single fp16 operands: that build's own, wider bound (99.9 % inside the plain one, capped outliers)
+        from util import f16, fast_parity
+        ok, msg = fast_parity(f16(outs[0]), f16(outs[1]))
+        assert ok, msg
