@@ -7,9 +7,9 @@ goes to K outliers x30, V outliers x60, 8 outlier channels, a query scale of 2 a
 outlier channels alternate in sign from key to key at three times the outlier scale (so that large terms
 cancel in the output), over contexts of 1 to 300 tokens, where a softmax has few keys and every rounding
 shows.  Asserted: inside the bound everywhere except the corner "x60 V outliers AND the alternating
-pattern" (|v| = 180, nine times the benchmark's outliers), where what is left of the V-centroid rounding
-below the peaked-page threshold reaches the bound on a few outputs per million of a prefill chunk
-(measured 1.06x; held to 1.5x).  The fp32 kernel is held to the bound on all cases (it sits below a
+pattern" (|v| = 180, nine times the benchmark's outliers), where outputs of about 0.05 are what +-180
+terms leave over and a few per million of a prefill chunk reach the bound (measured 1.06x; held to 1.5x;
+the same with the V-centroid pass or the residual of P x d_v taken on every page).  The fp32 kernel is held to the bound on all cases (it sits below a
 tenth of it)."""
 import itertools
 
