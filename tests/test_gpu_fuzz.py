@@ -1,8 +1,9 @@
 """Seeded random geometries through the C ABI: the default (tensor-core) path of every storage format
 against this library's fp32 dequant-then-attend kernels (WARP34_B200_EXEC_FLAG_PRECISE_ATTENTION), which
 the other GPU tests pin against the reference's scalar kernel.  Head counts with GQA groups from 1 to 12,
-ragged contexts from one token to a few hundred, decode / draft / chunk query lengths, sliding windows,
-masked tokens and requests, pools pre-filled with 0xFF bytes; for the query-sparse entry point random
+ragged contexts from one token to a few hundred, decode / draft / chunk query lengths, causal and symmetric
+sliding windows, masked tokens and requests, the fused output epilogue (gate, gate + Hadamard-64), pools
+pre-filled with 0xFF bytes; for the query-sparse entry point random
 selected lists with skipped, invisible and partly visible groups.  Bound: 2e-3 + 1e-2 |b| on every output,
 masked rows bit-identical (untouched, or zeros for the query-sparse entry point)."""
 import ctypes as C
@@ -68,14 +69,22 @@ def test_random_batches_default_path_against_the_fp32_kernel(env, fmt_name, seed
         kw["valid_req_mask"] = vrm
     if window:
         kw["sliding_window"] = window
+        if rng.random() < 0.5:
+            kw["mask_mode"] = ffi.ATTN_MASK_SYMMETRIC_WINDOW
     b = wl.step(q_lens=q_lens, **kw)
     q = synth.make_q(T, hq, seed + 1).cuda()
+    # a third of the cases go through the entry point with the fused output epilogue (gate, gate + Hadamard-64)
+    epilogue = int(rng.integers(3)) if rng.random() < 0.33 else 0
+    gate = (torch.randn(T, hq, 256, generator=torch.Generator().manual_seed(seed)) * 2).to(torch.float16).cuda()
     outs = []
     for flags in (0, ffi.EXEC_FLAG_PRECISE_ATTENTION):
         ex.ex.flags = flags
         out = torch.full((T, hq, 256), 0, dtype=torch.int16, device="cuda")
         out.fill_(0x5500)
-        kv.paged_attention(ex, wl.layer, b, q, out.view(torch.float16), hq)
+        if epilogue:
+            kv.paged_attention_gated(ex, wl.layer, b, q, gate, out.view(torch.float16), hq, hadamard64=(epilogue == 2))
+        else:
+            kv.paged_attention(ex, wl.layer, b, q, out.view(torch.float16), hq)
         torch.cuda.synchronize()
         outs.append(out.cpu().numpy().view(np.uint16))
     ex.ex.flags = 0
