@@ -194,3 +194,74 @@ def test_thousands_of_short_requests_with_idle_ones_between(env, fmt_name, q_hi,
         from util import f16, fast_parity
         ok, msg = fast_parity(f16(outs[0]), f16(outs[1]))
         assert ok, msg
+
+
+@pytest.fixture(scope="module")
+def ref_lib(env):
+    import oracle
+    p = oracle.ref_lib_path()
+    if p is None:
+        pytest.skip("reference kernels not built (oracle/_ref)")
+    return env["ffi"].bind_kernel_abi(p)
+
+
+def _append_case(env, ref_lib, fmt_name, seed):
+    """Random tokens, heads, slots, masks, row strides and value ranges through the append entry point of this
+    library and of the reference's own kernels: the two pools must hold the same bytes."""
+    ffi, kv = env["ffi"], env["kv"]
+    rng = np.random.default_rng(31000 + seed)
+    fmt, tr = FORMATS[fmt_name]
+    hkv = int(rng.choice([1, 2, 3, 4, 8]))
+    T = int(rng.integers(1, 200))
+    num_pages = 40
+    g = torch.Generator().manual_seed(seed)
+    pad = int(rng.choice([0, 8, 64]))
+    width = hkv * 256 + pad
+    kbuf = torch.randn(T, width, generator=g)
+    vbuf = torch.randn(T, width, generator=g)
+    # value ranges per token: ordinary, outlier channels, huge, tiny (fp16 subnormals), exact zeros, one hot
+    kind = rng.integers(0, 6, size=T)
+    for t in range(T):
+        for buf in (kbuf, vbuf):
+            if kind[t] == 1:
+                buf[t, rng.integers(0, hkv * 256, size=6)] *= 25.0
+            elif kind[t] == 2:
+                buf[t] *= 9000.0
+            elif kind[t] == 3:
+                buf[t] *= 3e-6
+            elif kind[t] == 4:
+                buf[t] = 0.0
+            elif kind[t] == 5:
+                buf[t] = 0.0
+                buf[t, int(rng.integers(0, hkv * 256))] = float(rng.choice([1.0, -300.0, 6e-5]))
+    kbuf, vbuf = kbuf.clamp(-65000, 65000).to(torch.float16).cuda(), vbuf.clamp(-65000, 65000).to(torch.float16).cuda()
+    # requests of random lengths; distinct random slots, some skipped
+    cuts = np.sort(rng.choice(np.arange(1, T), size=min(int(rng.integers(0, 5)), T - 1), replace=False)) if T > 1 else np.array([], int)
+    qsl = np.concatenate([[0], cuts, [T]]).astype(np.int32)
+    n = len(qsl) - 1
+    slots = rng.permutation(np.arange(16, num_pages * 16))[:T].astype(np.int32)
+    slots[rng.random(T) < 0.1] = -1
+    kw = {}
+    if rng.random() < 0.5:
+        kw["valid_token_mask"] = (rng.random(T) > 0.15).astype(np.uint8)
+    if rng.random() < 0.3:
+        kw["valid_req_mask"] = (rng.random(n) > 0.3).astype(np.uint8)
+    bt = np.zeros((n, 4), np.int32)
+    lens = np.diff(qsl)
+    pools = []
+    for lib in (env["lib"], ref_lib):
+        layer = kv.KvLayer(num_pages, hkv, formats=(fmt, fmt, tr, tr), fill=0x3C)
+        b = kv.StepBatch(qsl, [0] * n, lens.tolist(), bt, slots, 4, 0.0625, **kw)
+        ex = kv.Executor(1 << 20)
+        kv.kv_cache_write(ex, layer, b, kbuf, vbuf, k_row_stride=width, v_row_stride=width, lib=lib)
+        torch.cuda.synchronize()
+        pools.append((layer.k.cpu().numpy(), layer.v.cpu().numpy()))
+    assert np.array_equal(pools[0][0], pools[1][0]), ("K pool", fmt_name, seed, int((pools[0][0] != pools[1][0]).sum()))
+    assert np.array_equal(pools[0][1], pools[1][1]), ("V pool", fmt_name, seed, int((pools[0][1] != pools[1][1]).sum()))
+    assert (pools[0][0] != 0x3C).any() or (slots < 0).all() or "valid_token_mask" in kw or "valid_req_mask" in kw
+
+
+@pytest.mark.parametrize("fmt_name", ["tq4", "fp8", "q8"])
+@pytest.mark.parametrize("seed", range(6))
+def test_random_appends_give_the_reference_kernels_bytes(env, ref_lib, fmt_name, seed):
+    _append_case(env, ref_lib, fmt_name, seed)
