@@ -186,12 +186,16 @@ int warp34_fused_k_rmsnorm_rope_kv_cache_write_f16(
  * [total_tokens, num_q_heads, head_dim].  Replaces warp34_paged_attention_f16
  * (warp34_cuda.h:370-373, op_paged_attn.cu:1266-1448).  Split-KV partials
  * live in ex->scratch_ptr; warp34_paged_attention_scratch_bytes() says how
- * much a batch geometry can use.  Any 16-byte-aligned scratch is accepted: less
- * than that bound means fewer, longer KV partitions, down to a floor of the plan,
- * one partial slot (8.1 KiB) and one set of query fragments (6.25 KiB) per
- * (request, kv head, 8-row group) plus the slots of one thread block; below the
- * floor (about 4 MiB for a decode batch of 64 sequences and 4 kv heads, 170 MiB for 3000)
- * the call computes the same result with the fp32 kernel that needs no scratch.
+ * much a batch geometry can use.  Any 16-byte-aligned scratch is accepted.  Less
+ * than that bound means fewer, longer KV partitions.  A batch needs the plan, one
+ * partial slot (8.1 KiB) and one set of query fragments (6.25 KiB) per (request,
+ * kv head, 8-row group) and one slot per worker warp; when the scratch leaves
+ * fewer worker slots than half a grid, the requests are served in several passes
+ * over the same scratch (8 MiB, the reference engine's minimum: two passes for a
+ * decode batch of 64 sequences x 4 kv heads, 0.88 ms instead of 0.51 ms with
+ * 17.5 MB; eight passes for 256 sequences).  Only a scratch too small for one
+ * request and one thread block's workers (about 100 KiB) leaves the fp32 kernel,
+ * which needs none.
  * Masked rows of attn_out are left untouched.
  *
  * Accuracy: every output is within 2e-3 + 1e-2 |b| of fp32 dequant-then-attend (b).  The

@@ -337,6 +337,54 @@ def test_split_partitioning_does_not_change_the_result_beyond_tolerance(env):
     assert np.abs(outs[0] - outs[1]).max() <= 2e-3 + 1e-2 * np.abs(want).max()
 
 
+@pytest.mark.parametrize("case", ["many_short_requests_2mib", "decode_batch_8mib", "draft_tokens_masks_4mib", "fast_flag_4mib"])
+def test_a_workspace_too_small_for_the_batch_serves_it_in_several_passes(env, case):
+    """A workspace that cannot hold a partial slot and the query fragments of every (request, kv head) next to
+    a useful number of worker slots (the reference's engine guarantees 8 MiB, op_paged_attn.cu:1301-1315) is
+    used for some of the requests at a time: plan, stream and merge per part.  Same bound as one pass; the
+    status word shows that the split-KV kernels ran and the plan header that the last pass held fewer items
+    than the batch."""
+    kv, ffi = env["kv"], env["ffi"]
+    rng = np.random.default_rng(77)
+    hq, hkv = 24, 4
+    if case == "many_short_requests_2mib":
+        ctx, q_lens, scratch, flags, kw = [int(x) for x in rng.integers(1, 200, size=400)], None, 2 << 20, 0, {}
+    elif case == "decode_batch_8mib":
+        ctx, q_lens, scratch, flags, kw = [int(x) for x in rng.integers(500, 3000, size=64)], None, 8 << 20, 0, {}
+    elif case == "draft_tokens_masks_4mib":
+        q_lens = [int(x) for x in rng.integers(1, 4, size=90)]           # 1 to 3 tokens: up to 18 rows per kv head
+        ctx = [int(q + rng.integers(0, 700)) for q in q_lens]
+        vtm = (rng.random(sum(q_lens)) > 0.2).astype(np.uint8)
+        vrm = (rng.random(90) > 0.1).astype(np.uint8)
+        scratch, flags, kw = 4 << 20, 0, dict(valid_token_mask=vtm, valid_req_mask=vrm, sliding_window=300)
+    else:
+        q_lens = [4] * 40                                                 # fast flag: four-warp teams, 24 rows per item
+        ctx = [int(4 + rng.integers(0, 900)) for _ in q_lens]
+        scratch, flags, kw = 4 << 20, ffi.EXEC_FLAG_FAST_ATTENTION, {}
+    wl, q = _decode_case(env, ctx, hq, hkv, seed=61, q_lens=q_lens)
+    b = wl.step(q_lens=q_lens or [1] * len(ctx), **kw)
+    T = q.shape[0]
+    outs = {}
+    for name, ex, fl in (("small", kv.Executor(scratch), flags), ("fp32", kv.Executor(1 << 20), ffi.EXEC_FLAG_PRECISE_ATTENTION)):
+        ex.ex.flags = fl
+        ex.scratch[:16].fill_(0x7f)
+        out = torch.full((T, hq, 256), 0, dtype=torch.int16, device="cuda")
+        out.fill_(0x5500)
+        kv.paged_attention(ex, wl.layer, b, q.cuda(), out.view(torch.float16), hq)
+        torch.cuda.synchronize()
+        outs[name] = out.cpu().numpy().view(np.uint16)
+        if name == "small":
+            hdr = ex.scratch[:16].cpu().numpy().view(np.int32)
+            assert hdr[0] == 0, "status: the split-KV kernels did not run or reported a failure"
+            whole = hkv * sum(-(-(ql * (hq // hkv)) // (24 if flags else 8)) for ql in (q_lens or [1] * len(ctx)))
+            assert 0 < hdr[1] < whole, (int(hdr[1]), whole)      # items of the last pass < items of the batch
+    untouched = (outs["fp32"] == 0x5500).all(axis=(1, 2))
+    assert ((outs["small"] == 0x5500).all(axis=(1, 2)) == untouched).all(), "masked rows differ"
+    got, want = f16(outs["small"][~untouched]), f16(outs["fp32"][~untouched])
+    ok, msg = (fast_parity if flags else plain_parity)(got, want)
+    assert ok, (case, msg)
+
+
 def test_understated_max_q_len_is_reported_and_the_declared_rows_stay_right(env):
     """batch.max_q_len sizes the store of prepared query fragments.  A request with more query
     tokens than it declares keeps its first row group (8 rows: 2 tokens x 4 heads here), the rest

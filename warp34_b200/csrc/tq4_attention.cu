@@ -325,6 +325,8 @@ struct StreamParams {
     // selected 4-token groups (physical group id = page * 4 + group in page, logical group index for the
     // causal test against seq_pos[r]); rows of masked tokens are written as zeros.
     int q_floor = 0;       // query fragments for the exact build: hi rounded down, residual bytes 0..255
+    int rows_from_first_token = 0;   // merge: block x is row x of the batch (0) or row x counted from the batch's first token (1)
+    int keep_status = 0;             // plan: OR into the status word instead of clearing it (second and later passes)
     const int32_t* sel_phys = nullptr;
     const int32_t* sel_logical = nullptr;
     const int32_t* num_selected = nullptr;
@@ -428,7 +430,9 @@ __global__ void __launch_bounds__(kPlanThreads) tq4_attention_plan_kernel(const 
         item_prefix[R] = item_carry;
         page_lo[R] = 0; npages_a[R] = 0; ngroups_a[R] = 0;
         PlanHeader* h = reinterpret_cast<PlanHeader*>(p.scratch);
-        h->status = clamped_any ? 4 : 0;  // bit 2: a request's q_len exceeded batch.max_q_len, rows dropped
+        // bit 2: a request's q_len exceeded batch.max_q_len, rows dropped.  A later part of a batch that runs in
+        // several passes keeps what the earlier passes reported.
+        h->status = (clamped_any ? 4 : 0) | (p.keep_status ? h->status : 0);
         h->total_items = item_carry;
         h->total_units = unit_carry;
         int per = (unit_carry + p.num_warps - 1) / (p.num_warps > 0 ? p.num_warps : 1);
@@ -1764,7 +1768,12 @@ __global__ void __launch_bounds__(MW * 32) tq4_attention_merge_kernel(const Stre
     __shared__ float s_m[MW], s_l[MW];
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const long long row_ll = blockIdx.x;
-    const int tok = (int)(row_ll / p.num_q_heads), q_head = (int)(row_ll % p.num_q_heads);
+    int tok = (int)(row_ll / p.num_q_heads);
+    const int q_head = (int)(row_ll % p.num_q_heads);
+    if (p.rows_from_first_token) {   // a part of a larger batch: its tokens start at query_start_loc[0]
+        tok += p.batch.query_start_loc[0];
+        if (tok >= p.batch.query_start_loc[p.batch.num_reqs]) return;   // the grid is sized by max_q_len
+    }
     // A row that takes no part (masked token or request, rows the plan dropped) leaves attn_out
     // untouched; as a triple it is written as "no keys" (l = 0), which the cross-shard merges skip.
     auto skip_row = [&]() {
@@ -2334,77 +2343,126 @@ static int launch_attention(const warp34_exec* ex, const warp34_kv_layer_layout*
     const int nt = pick_row_tiles(batch, gqa, fast);
     const int rpg = 8 * nt;
     const int workers_per_cta = (nt == 1) ? (fast ? kFastWarps : kExactWarps) : kTeams;
-    const long long items = items_bound(layout, batch, num_q_heads, rpg);
-    const long long units_bound = items * (long long)(batch->max_blocks_per_req > 0 ? batch->max_blocks_per_req : 1);
-    const size_t plan = plan_bytes(batch->num_reqs);
     const size_t slot_bytes = (size_t)(rpg * kHeadDim + 2 * rpg) * sizeof(float);
-    bool stream = (ex->flags & WARP34_B200_EXEC_FLAG_PRECISE_ATTENTION) == 0 &&
-                  stream_layout_ok(layout) && ex->scratch_ptr != 0 && (ex->scratch_ptr & 15u) == 0u &&
-                  units_bound < 0x7fffffffll && batch->max_blocks_per_req > 0;
-    int grid = dev->sm_count;
-    // one-warp items also keep their query fragments in the scratch, after the partial slots
-    const long long q_items = (nt == 1) ? qfrag_items(layout, batch, gqa) : 0;
-    if (q_items > 0x3fffffffll) return (int)cudaErrorInvalidValue;
-    const size_t qfrag_bytes = (size_t)q_items * qfrag_item_bytes();
-    if (stream) {
-        const size_t fixed = plan + qfrag_bytes;
+    const long long full_workers = (long long)dev->sm_count * workers_per_cta;
+    const bool stream_ok = (ex->flags & WARP34_B200_EXEC_FLAG_PRECISE_ATTENTION) == 0 &&
+                           stream_layout_ok(layout) && ex->scratch_ptr != 0 && (ex->scratch_ptr & 15u) == 0u &&
+                           batch->max_blocks_per_req > 0;
+    if (nt == 1 && qfrag_items(layout, batch, gqa) > 0x3fffffffll) return (int)cudaErrorInvalidValue;
+
+    // Worker slots the workspace leaves for a batch of `reqs` requests with at most `tokens` query tokens
+    // (-1: its unit count does not fit 32 bits).  Each of its items needs a slot and, one-warp items, a set
+    // of query fragments.
+    auto workers_for = [&](int reqs, long long tokens) -> long long {
+        warp34_attention_batch b = *batch;
+        b.num_reqs = reqs;
+        b.total_tokens = (int)tokens;
+        const long long items = items_bound(layout, &b, num_q_heads, rpg);
+        if (items * (long long)batch->max_blocks_per_req >= 0x7fffffffll) return -1;
+        const size_t fixed = plan_bytes(reqs) + ((nt == 1) ? (size_t)qfrag_items(layout, &b, gqa) * qfrag_item_bytes() : 0);
         const size_t avail = ex->scratch_size > fixed ? ex->scratch_size - fixed : 0;
-        const long long slots_avail = (long long)(avail / slot_bytes);
-        long long workers = slots_avail - items;
-        if (workers < workers_per_cta) {
-            stream = false;
-        } else {
-            const long long max_ctas = workers / workers_per_cta;
-            if (max_ctas < grid) grid = (int)max_ctas;
+        const long long w = (long long)(avail / slot_bytes) - items;
+        return w < 0 ? 0 : w;
+    };
+    auto tokens_of = [&](int reqs) -> long long {
+        const long long t = (long long)reqs * (batch->max_q_len > 0 ? batch->max_q_len : 1);
+        return t < batch->total_tokens ? t : (long long)batch->total_tokens;
+    };
+
+    // Requests per pass.  A workspace that leaves fewer worker slots than half a grid for the whole batch
+    // is used for part of the requests at a time (plan, stream, merge per part, one after the other on the
+    // stream, each part reusing the workspace) when that at least doubles the workers.  The cross-GPU
+    // partial mode keeps one pass: its rows are addressed by the caller.
+    int reqs_per_pass = batch->num_reqs;
+    long long workers = stream_ok ? workers_for(reqs_per_pass, batch->total_tokens) : -1;
+    if (stream_ok && triple_out == nullptr && workers < full_workers / 2 && batch->num_reqs > 1) {
+        int best_r = batch->num_reqs, r_try = batch->num_reqs;
+        long long best_w = workers;
+        while (r_try > 1 && best_w < full_workers / 2) {   // halve the part until half a grid fits
+            r_try = (r_try + 1) / 2;
+            const long long w_try = workers_for(r_try, tokens_of(r_try));
+            if (best_w >= workers_per_cta && w_try < best_w + best_w / 4) break;   // twice the passes for little
+            best_r = r_try;
+            best_w = w_try;
+        }
+        if (best_w >= workers_per_cta && (workers < workers_per_cta || 2 * best_w >= 3 * workers)) {
+            reqs_per_pass = best_r;
+            workers = best_w;
         }
     }
-    if (!stream) {
+    if (!stream_ok || workers < workers_per_cta) {
         if (triple_out != nullptr) return (int)cudaErrorNotSupported;
         return launch_scalar(ex, layout, batch, q_in, attn_out, num_q_heads, io_bf16, &og);
     }
 
-    StreamParams p;
-    p.layout = *layout;
-    p.batch = *batch;
-    p.q_in = q_in;
-    p.attn_out = attn_out;
-    p.io_bf16 = io_bf16;
-    p.triple_out = triple_out;
-    p.scratch = reinterpret_cast<uint8_t*>((uintptr_t)ex->scratch_ptr);
-    p.num_q_heads = num_q_heads;
-    p.gqa = gqa;
-    p.num_warps = grid * workers_per_cta;
-    p.max_slots = (int)(p.num_warps + items);
-    p.rows_per_group = rpg;
-    p.q_scale = batch->sm_scale * 1.4426950408889634f / kLutScale;
-    p.natural = 0;
-    p.q_floor = fast ? 0 : 1;
-    p.og = og;
-    p.qfrag = (nt == 1) ? reinterpret_cast<uint32_t*>(p.scratch + plan + (size_t)p.max_slots * slot_bytes) : nullptr;
+    const bool in_parts = reqs_per_pass < batch->num_reqs;
     cudaStream_t st = (cudaStream_t)ex->stream;
     const size_t smem = (size_t)dev->smem_optin;
-    p.smem_bytes = (uint32_t)smem;
-    p.q_groups_max = (nt == 1) ? (int)(q_items / ((long long)batch->num_reqs * layout->local_kv_heads)) : 0;
-    tq4_attention_plan_kernel<<<1 + (unsigned)q_items, q_items > 0 ? kPlanThreads : 32, 0, st>>>(p);
-    if (nt == 1) {
-        if (fast) tq4_attention_stream_kernel<kFastStages, kFastWarps, false><<<grid, kFastWarps * 32, smem, st>>>(p);
-        else tq4_attention_stream_kernel<kExactStages, kExactWarps, true><<<grid, kExactWarps * 32, smem, st>>>(p);
-    } else if (nt == 2) {
-        tq4_attention_team_kernel<2><<<grid, kTeams * kTeamWarps * 32, smem, st>>>(p);
-    } else {
-        tq4_attention_team_kernel<3><<<grid, kTeams * kTeamWarps * 32, smem, st>>>(p);
+    for (int r0 = 0; r0 < batch->num_reqs; r0 += reqs_per_pass) {
+        const int reqs = (batch->num_reqs - r0 < reqs_per_pass) ? batch->num_reqs - r0 : reqs_per_pass;
+        StreamParams p;
+        p.layout = *layout;
+        p.batch = *batch;
+        if (in_parts) {   // the part's requests: arrays by request start at r0, arrays by token stay
+            p.batch.query_start_loc += r0;
+            if (p.batch.context_lens_before != nullptr) p.batch.context_lens_before += r0;
+            p.batch.seq_lens_after += r0;
+            p.batch.block_tables += (size_t)r0 * batch->max_blocks_per_req;
+            if (p.batch.valid_req_mask != nullptr) p.batch.valid_req_mask += r0;
+            p.batch.num_reqs = reqs;
+            p.batch.total_tokens = (int)tokens_of(reqs);
+        }
+        const long long items = items_bound(layout, &p.batch, num_q_heads, rpg);
+        const long long q_items = (nt == 1) ? qfrag_items(layout, &p.batch, gqa) : 0;
+        long long part_workers = in_parts ? workers_for(reqs, p.batch.total_tokens) : workers;   // the last part is smaller
+        if (part_workers > full_workers) part_workers = full_workers;
+        const int grid = (int)(part_workers / workers_per_cta);
+        if (grid < 1) return (int)cudaErrorInvalidValue;
+        const size_t plan = plan_bytes(reqs);
+        p.q_in = q_in;
+        p.attn_out = attn_out;
+        p.io_bf16 = io_bf16;
+        p.triple_out = triple_out;
+        p.scratch = reinterpret_cast<uint8_t*>((uintptr_t)ex->scratch_ptr);
+        p.num_q_heads = num_q_heads;
+        p.gqa = gqa;
+        p.num_warps = grid * workers_per_cta;
+        p.max_slots = (int)(p.num_warps + items);
+        p.rows_per_group = rpg;
+        p.q_scale = batch->sm_scale * 1.4426950408889634f / kLutScale;
+        p.natural = 0;
+        p.q_floor = fast ? 0 : 1;
+        p.og = og;
+        p.rows_from_first_token = in_parts ? 1 : 0;
+        p.keep_status = r0 > 0 ? 1 : 0;
+        p.qfrag = (nt == 1) ? reinterpret_cast<uint32_t*>(p.scratch + plan + (size_t)p.max_slots * slot_bytes) : nullptr;
+        p.smem_bytes = (uint32_t)smem;
+        p.q_groups_max = (nt == 1) ? (int)(q_items / ((long long)reqs * layout->local_kv_heads)) : 0;
+        tq4_attention_plan_kernel<<<1 + (unsigned)q_items, q_items > 0 ? kPlanThreads : 32, 0, st>>>(p);
+        if (nt == 1) {
+            if (fast) tq4_attention_stream_kernel<kFastStages, kFastWarps, false><<<grid, kFastWarps * 32, smem, st>>>(p);
+            else tq4_attention_stream_kernel<kExactStages, kExactWarps, true><<<grid, kExactWarps * 32, smem, st>>>(p);
+        } else if (nt == 2) {
+            tq4_attention_team_kernel<2><<<grid, kTeams * kTeamWarps * 32, smem, st>>>(p);
+        } else {
+            tq4_attention_team_kernel<3><<<grid, kTeams * kTeamWarps * 32, smem, st>>>(p);
+        }
+        // rows of the merge: every token of the batch, or (a part) as many as the part can hold, counted
+        // from its first token
+        const long long rows = (long long)p.batch.total_tokens * num_q_heads;
+        // Few rows with hundreds of partials each (one long sequence): 32 warps per row instead of 4.
+        const bool wide = rows * 4 < (long long)grid * workers_per_cta / 8;
+        if (triple_out != nullptr) {
+            if (wide) tq4_attention_merge_kernel<true, 32><<<(unsigned)rows, 1024, 0, st>>>(p);
+            else tq4_attention_merge_kernel<true, 4><<<(unsigned)rows, 128, 0, st>>>(p);
+        } else {
+            if (wide) tq4_attention_merge_kernel<false, 32><<<(unsigned)rows, 1024, 0, st>>>(p);
+            else tq4_attention_merge_kernel<false, 4><<<(unsigned)rows, 128, 0, st>>>(p);
+        }
+        rc = (int)cudaGetLastError();
+        if (rc != 0) return rc;
     }
-    const long long rows = (long long)batch->total_tokens * num_q_heads;
-    // Few rows with hundreds of partials each (one long sequence): 32 warps per row instead of 4.
-    const bool wide = rows * 4 < (long long)grid * workers_per_cta / 8;
-    if (triple_out != nullptr) {
-        if (wide) tq4_attention_merge_kernel<true, 32><<<(unsigned)rows, 1024, 0, st>>>(p);
-        else tq4_attention_merge_kernel<true, 4><<<(unsigned)rows, 128, 0, st>>>(p);
-    } else {
-        if (wide) tq4_attention_merge_kernel<false, 32><<<(unsigned)rows, 1024, 0, st>>>(p);
-        else tq4_attention_merge_kernel<false, 4><<<(unsigned)rows, 128, 0, st>>>(p);
-    }
-    return (int)cudaGetLastError();
+    return 0;
 }
 
 // Query-sparse lists on the exact stream kernel (TQ4 layers in the canonical packing, a workspace that
