@@ -280,3 +280,45 @@ def test_8bit_stream_kernel_geometries_against_the_fp32_kernel(env, case, fmt_na
     rr = r.float().cpu().numpy()[~untouched]
     assert np.isfinite(rr).all()
     assert np.all(np.abs(g - rr) <= ATOL + RTOL * np.abs(rr)), float(np.abs(g - rr).max())
+
+
+@pytest.mark.parametrize("fmt_name", ["fp8_e4m3", "q8_0"])
+def test_8bit_layers_serve_a_batch_in_several_passes_when_the_workspace_is_small(env, fmt_name):
+    """300 decode requests on an 8-bit layer with 2 MiB of workspace (a slot per (request, kv head) alone
+    is 9.9 MB): the tensor-core stream kernel runs over part of the requests at a time instead of
+    leaving the batch to the fp32 kernel.  The status word shows which kernels ran, the plan header that
+    the last pass held fewer items than the batch."""
+    ffi, kv, synth = env["ffi"], env["kv"], env["synth"]
+    fmt = {"q8_0": ffi.KV_FORMAT_Q8_0, "fp8_e4m3": ffi.KV_FORMAT_FP8_E4M3}[fmt_name]
+    rng = np.random.default_rng(5)
+    hq, hkv, n = 24, 4, 300
+    ctx = [int(x) for x in rng.integers(1, 400, size=n)]
+    wl = _workload(env, fmt, ctx, hkv, seed=9)
+    fill = kv.Executor(16 << 20)
+    k, v = synth.make_kv(sum(ctx), hkv, 9)
+    kv.kv_cache_write(fill, wl.layer, wl.step(), k.cuda(), v.cuda())
+    for s, c in zip(wl.seqs, ctx):
+        s.commit(c - 1)
+    vtm = (rng.random(n) > 0.1).astype(np.uint8)
+    b = wl.step(q_lens=[1] * n, valid_token_mask=vtm)
+    q = synth.make_q(n, hq, 10).cuda()
+    outs = {}
+    for name, ex, flags in (("small", kv.Executor(2 << 20), 0), ("fp32", kv.Executor(1 << 20), ffi.EXEC_FLAG_PRECISE_ATTENTION)):
+        ex.ex.flags = flags
+        ex.scratch[:16].fill_(0x7f)
+        out = torch.full((n, hq, 256), 0, dtype=torch.int16, device="cuda")
+        out.fill_(0x5500)
+        kv.paged_attention(ex, wl.layer, b, q, out.view(torch.float16), hq)
+        torch.cuda.synchronize()
+        outs[name] = out.cpu().numpy().view(np.uint16)
+        if name == "small":
+            hdr = ex.scratch[:16].cpu().numpy().view(np.int32)
+            assert hdr[0] == 0, "status: the stream kernel did not run or reported a failure"
+            assert 0 < hdr[1] < n * hkv, int(hdr[1])
+    untouched = (outs["fp32"] == 0x5500).all(axis=(1, 2))
+    assert (untouched == (vtm == 0)).all()
+    assert ((outs["small"] == 0x5500).all(axis=(1, 2)) == untouched).all(), "masked rows differ"
+    got = outs["small"][~untouched].view(np.float16).astype(np.float32)
+    want = outs["fp32"][~untouched].view(np.float16).astype(np.float32)
+    d = np.abs(got - want)
+    assert np.all(d <= ATOL + RTOL * np.abs(want)), float((d / (ATOL + RTOL * np.abs(want))).max())

@@ -846,15 +846,23 @@ static int launch_kv8_stream(const warp34_exec* ex, const warp34_kv_layer_layout
     int rc = 0;
     DeviceInfo* dev = device_info(&rc);
     if (dev == nullptr) return rc;
-    const long long items = items_bound(layout, batch, num_q_heads, kRowsPerGroup);
-    if (items * (long long)batch->max_blocks_per_req >= 0x7fffffffll) return 0;
-    const size_t plan = plan_bytes(batch->num_reqs);
     const size_t slot_bytes = (size_t)kPartialFloats * sizeof(float);
-    const size_t avail = ex->scratch_size > plan ? ex->scratch_size - plan : 0;
-    const long long workers = (long long)(avail / slot_bytes) - items;
+    const long long full_workers = (long long)dev->sm_count * kKv8StreamWarps;
+    auto workers_for = [&](int reqs, long long tokens) -> long long {
+        warp34_attention_batch b = *batch;
+        b.num_reqs = reqs;
+        b.total_tokens = (int)tokens;
+        const long long items = items_bound(layout, &b, num_q_heads, kRowsPerGroup);
+        if (items * (long long)batch->max_blocks_per_req >= 0x7fffffffll) return -1;
+        const size_t plan = plan_bytes(reqs);
+        const size_t avail = ex->scratch_size > plan ? ex->scratch_size - plan : 0;
+        const long long w = (long long)(avail / slot_bytes) - items;
+        return w < 0 ? 0 : w;
+    };
+    long long workers = 0;
+    const int reqs_per_pass = pick_reqs_per_pass(batch, full_workers, kKv8StreamWarps, true, workers_for, &workers);
     if (workers < kKv8StreamWarps) return 0;      // the caller falls back to the fp32 kernel
-    int grid = dev->sm_count;
-    if (workers / kKv8StreamWarps < grid) grid = (int)(workers / kKv8StreamWarps);
+    const bool in_parts = reqs_per_pass < batch->num_reqs;
     const bool fp8 = layout->k_format == WARP34_KV_FORMAT_FP8_E4M3;
     const uint32_t stage = 2u * (uint32_t)(fp8 ? Kv8Stage<WARP34_KV_FORMAT_FP8_E4M3>::kRunStride
                                                : Kv8Stage<WARP34_KV_FORMAT_Q8_0>::kRunStride);
@@ -881,41 +889,53 @@ static int launch_kv8_stream(const warp34_exec* ex, const warp34_kv_layer_layout
             done[d] = true;
         }
     }
-    StreamParams p;
-    p.og.gate = nullptr;
-    p.og.mode = 0;
-    p.layout = *layout;
-    p.batch = *batch;
-    p.q_in = q_in;
-    p.attn_out = attn_out;
-    p.io_bf16 = io_bf16;
-    p.triple_out = nullptr;
-    p.scratch = reinterpret_cast<uint8_t*>((uintptr_t)ex->scratch_ptr);
-    p.num_q_heads = num_q_heads;
-    p.gqa = num_q_heads / layout->local_kv_heads;
-    p.num_warps = grid * kKv8StreamWarps;
-    p.max_slots = (int)(p.num_warps + items);
-    p.smem_bytes = smem;
-    p.rows_per_group = kRowsPerGroup;
-    p.q_scale = batch->sm_scale * 1.4426950408889634f;
-    p.natural = 1;
-    p.qfrag = nullptr;
-    p.q_groups_max = 0;
     cudaStream_t st = (cudaStream_t)ex->stream;
-    tq4_attention_plan_kernel<<<1, 32, 0, st>>>(p);
-    if (fp8) {
-        kv8_attention_stream_kernel<WARP34_KV_FORMAT_FP8_E4M3, kKv8StreamStages><<<grid, kKv8StreamWarps * 32, smem, st>>>(p);
-    } else {
-        kv8_attention_stream_kernel<WARP34_KV_FORMAT_Q8_0, kKv8StreamStages><<<grid, kKv8StreamWarps * 32, smem, st>>>(p);
-    }
-    const long long rows = (long long)batch->total_tokens * num_q_heads;
-    if (rows * 4 < (long long)grid * kKv8StreamWarps / 8) {
-        tq4_attention_merge_kernel<false, 32><<<(unsigned)rows, 1024, 0, st>>>(p);
-    } else {
-        tq4_attention_merge_kernel<false, 4><<<(unsigned)rows, 128, 0, st>>>(p);
+    for (int r0 = 0; r0 < batch->num_reqs; r0 += reqs_per_pass) {
+        const int reqs = (batch->num_reqs - r0 < reqs_per_pass) ? batch->num_reqs - r0 : reqs_per_pass;
+        StreamParams p;
+        p.og.gate = nullptr;
+        p.og.mode = 0;
+        p.layout = *layout;
+        p.batch = in_parts ? batch_part(batch, r0, reqs) : *batch;
+        const long long items = items_bound(layout, &p.batch, num_q_heads, kRowsPerGroup);
+        long long part_workers = in_parts ? workers_for(reqs, p.batch.total_tokens) : workers;   // the last part is smaller
+        if (part_workers > full_workers) part_workers = full_workers;
+        const int grid = (int)(part_workers / kKv8StreamWarps);
+        if (grid < 1) return (int)cudaErrorInvalidValue;
+        p.q_in = q_in;
+        p.attn_out = attn_out;
+        p.io_bf16 = io_bf16;
+        p.triple_out = nullptr;
+        p.scratch = reinterpret_cast<uint8_t*>((uintptr_t)ex->scratch_ptr);
+        p.num_q_heads = num_q_heads;
+        p.gqa = num_q_heads / layout->local_kv_heads;
+        p.num_warps = grid * kKv8StreamWarps;
+        p.max_slots = (int)(p.num_warps + items);
+        p.smem_bytes = smem;
+        p.rows_per_group = kRowsPerGroup;
+        p.q_scale = batch->sm_scale * 1.4426950408889634f;
+        p.natural = 1;
+        p.qfrag = nullptr;
+        p.q_groups_max = 0;
+        p.rows_from_first_token = in_parts ? 1 : 0;
+        p.keep_status = r0 > 0 ? 1 : 0;
+        tq4_attention_plan_kernel<<<1, 32, 0, st>>>(p);
+        if (fp8) {
+            kv8_attention_stream_kernel<WARP34_KV_FORMAT_FP8_E4M3, kKv8StreamStages><<<grid, kKv8StreamWarps * 32, smem, st>>>(p);
+        } else {
+            kv8_attention_stream_kernel<WARP34_KV_FORMAT_Q8_0, kKv8StreamStages><<<grid, kKv8StreamWarps * 32, smem, st>>>(p);
+        }
+        const long long rows = (long long)p.batch.total_tokens * num_q_heads;
+        if (rows * 4 < (long long)grid * kKv8StreamWarps / 8) {
+            tq4_attention_merge_kernel<false, 32><<<(unsigned)rows, 1024, 0, st>>>(p);
+        } else {
+            tq4_attention_merge_kernel<false, 4><<<(unsigned)rows, 128, 0, st>>>(p);
+        }
+        rc = (int)cudaGetLastError();
+        if (rc != 0) return rc;
     }
     *taken = true;
-    return (int)cudaGetLastError();
+    return 0;
 }
 
 // allow_stream = false: the fp32 dequant-then-attend kernel whatever the layout (the scalar entry

@@ -2165,6 +2165,54 @@ static size_t stream_scratch_bytes(const warp34_kv_layer_layout* l, const warp34
     return plan_bytes(b->num_reqs) + (size_t)slots * (size_t)(rpg * kHeadDim + 2 * rpg) * sizeof(float) + qfrag;
 }
 
+// ---- a batch in several passes ------------------------------------------------------------------
+// A workspace that leaves fewer worker slots than half a grid for the whole batch is used for part of
+// the requests at a time: plan, stream and merge per part, one after the other on the stream, every part
+// reusing the workspace.  `workers_for(reqs, tokens)` says how many worker slots the workspace leaves for a
+// batch of `reqs` requests with at most `tokens` query tokens (negative: its unit count does not fit 32
+// bits).  Returns the requests per pass (num_reqs: one pass) and the worker slots of a full part.
+static long long part_tokens(const warp34_attention_batch* b, int reqs) {
+    const long long t = (long long)reqs * (b->max_q_len > 0 ? b->max_q_len : 1);
+    return t < b->total_tokens ? t : (long long)b->total_tokens;
+}
+
+template <class F>
+static int pick_reqs_per_pass(const warp34_attention_batch* batch, long long full_workers, int workers_per_cta,
+                              bool parts_allowed, F workers_for, long long* workers_out) {
+    int reqs_per_pass = batch->num_reqs;
+    long long workers = workers_for(reqs_per_pass, (long long)batch->total_tokens);
+    if (parts_allowed && workers < full_workers / 2 && batch->num_reqs > 1) {
+        int best_r = batch->num_reqs, r_try = batch->num_reqs;
+        long long best_w = workers;
+        while (r_try > 1 && best_w < full_workers / 2) {   // halve the part until half a grid fits
+            r_try = (r_try + 1) / 2;
+            const long long w_try = workers_for(r_try, part_tokens(batch, r_try));
+            if (best_w >= workers_per_cta && w_try < best_w + best_w / 4) break;   // twice the passes for little
+            best_r = r_try;
+            best_w = w_try;
+        }
+        if (best_w >= workers_per_cta && (workers < workers_per_cta || 2 * best_w >= 3 * workers)) {
+            reqs_per_pass = best_r;
+            workers = best_w;
+        }
+    }
+    *workers_out = workers;
+    return reqs_per_pass;
+}
+
+// The descriptor of requests [r0, r0 + reqs) of a batch: arrays by request start at r0, arrays by token stay.
+static warp34_attention_batch batch_part(const warp34_attention_batch* batch, int r0, int reqs) {
+    warp34_attention_batch b = *batch;
+    b.query_start_loc += r0;
+    if (b.context_lens_before != nullptr) b.context_lens_before += r0;
+    b.seq_lens_after += r0;
+    b.block_tables += (size_t)r0 * batch->max_blocks_per_req;
+    if (b.valid_req_mask != nullptr) b.valid_req_mask += r0;
+    b.num_reqs = reqs;
+    b.total_tokens = (int)part_tokens(batch, reqs);
+    return b;
+}
+
 }  // namespace w34
 
 #include "kv8_attention.cuh"
@@ -2364,31 +2412,12 @@ static int launch_attention(const warp34_exec* ex, const warp34_kv_layer_layout*
         const long long w = (long long)(avail / slot_bytes) - items;
         return w < 0 ? 0 : w;
     };
-    auto tokens_of = [&](int reqs) -> long long {
-        const long long t = (long long)reqs * (batch->max_q_len > 0 ? batch->max_q_len : 1);
-        return t < batch->total_tokens ? t : (long long)batch->total_tokens;
-    };
-
-    // Requests per pass.  A workspace that leaves fewer worker slots than half a grid for the whole batch
-    // is used for part of the requests at a time (plan, stream, merge per part, one after the other on the
-    // stream, each part reusing the workspace) when that at least doubles the workers.  The cross-GPU
-    // partial mode keeps one pass: its rows are addressed by the caller.
+    // Requests per pass: one pass unless the workspace is short (the cross-GPU partial mode keeps one pass:
+    // its rows are addressed by the caller).
+    long long workers = -1;
     int reqs_per_pass = batch->num_reqs;
-    long long workers = stream_ok ? workers_for(reqs_per_pass, batch->total_tokens) : -1;
-    if (stream_ok && triple_out == nullptr && workers < full_workers / 2 && batch->num_reqs > 1) {
-        int best_r = batch->num_reqs, r_try = batch->num_reqs;
-        long long best_w = workers;
-        while (r_try > 1 && best_w < full_workers / 2) {   // halve the part until half a grid fits
-            r_try = (r_try + 1) / 2;
-            const long long w_try = workers_for(r_try, tokens_of(r_try));
-            if (best_w >= workers_per_cta && w_try < best_w + best_w / 4) break;   // twice the passes for little
-            best_r = r_try;
-            best_w = w_try;
-        }
-        if (best_w >= workers_per_cta && (workers < workers_per_cta || 2 * best_w >= 3 * workers)) {
-            reqs_per_pass = best_r;
-            workers = best_w;
-        }
+    if (stream_ok) {
+        reqs_per_pass = pick_reqs_per_pass(batch, full_workers, workers_per_cta, triple_out == nullptr, workers_for, &workers);
     }
     if (!stream_ok || workers < workers_per_cta) {
         if (triple_out != nullptr) return (int)cudaErrorNotSupported;
@@ -2403,15 +2432,7 @@ static int launch_attention(const warp34_exec* ex, const warp34_kv_layer_layout*
         StreamParams p;
         p.layout = *layout;
         p.batch = *batch;
-        if (in_parts) {   // the part's requests: arrays by request start at r0, arrays by token stay
-            p.batch.query_start_loc += r0;
-            if (p.batch.context_lens_before != nullptr) p.batch.context_lens_before += r0;
-            p.batch.seq_lens_after += r0;
-            p.batch.block_tables += (size_t)r0 * batch->max_blocks_per_req;
-            if (p.batch.valid_req_mask != nullptr) p.batch.valid_req_mask += r0;
-            p.batch.num_reqs = reqs;
-            p.batch.total_tokens = (int)tokens_of(reqs);
-        }
+        if (in_parts) p.batch = batch_part(batch, r0, reqs);
         const long long items = items_bound(layout, &p.batch, num_q_heads, rpg);
         const long long q_items = (nt == 1) ? qfrag_items(layout, &p.batch, gqa) : 0;
         long long part_workers = in_parts ? workers_for(reqs, p.batch.total_tokens) : workers;   // the last part is smaller
