@@ -385,6 +385,29 @@ def test_a_workspace_too_small_for_the_batch_serves_it_in_several_passes(env, ca
     assert ok, (case, msg)
 
 
+@pytest.mark.parametrize("q_len,flag", [(1, None), (4, None), (4, "EXEC_FLAG_FAST_ATTENTION"), (60, None),
+                                        (60, "EXEC_FLAG_FAST_ATTENTION"), (1, "EXEC_FLAG_PRECISE_ATTENTION")])
+def test_context_lens_before_may_be_null(env, q_len, flag):
+    """The descriptor's context_lens_before is optional (the context is then seq_lens_after minus the query
+    length, op_paged_attn.cu:266-280): every kernel family gives the same bits with and without it."""
+    kv, ffi = env["kv"], env["ffi"]
+    ctx, hq, hkv = [300, 77, 1200], 24, 4
+    wl, q = _decode_case(env, ctx, hq, hkv, seed=71, q_lens=[q_len] * 3)
+    b = wl.step(q_lens=[q_len] * 3)
+    ex = kv.Executor(64 << 20)
+    ex.ex.flags = getattr(ffi, flag) if flag else 0
+    outs = []
+    for null in (False, True):
+        if null:
+            b.desc.context_lens_before = None
+        out = torch.zeros(3 * q_len, hq, 256, dtype=torch.float16, device="cuda")
+        kv.paged_attention(ex, wl.layer, b, q.cuda(), out, hq)
+        torch.cuda.synchronize()
+        outs.append(out.view(torch.int16).cpu())
+    assert outs[0].numpy().any()
+    assert torch.equal(outs[0], outs[1])
+
+
 def test_understated_max_q_len_is_reported_and_the_declared_rows_stay_right(env):
     """batch.max_q_len sizes the store of prepared query fragments.  A request with more query
     tokens than it declares keeps its first row group (8 rows: 2 tokens x 4 heads here), the rest
