@@ -82,8 +82,13 @@ def test_random_batches_default_path_against_the_fp32_kernel(env, fmt_name, seed
     # a third of the cases go through the entry point with the fused output epilogue (gate, gate + Hadamard-64)
     epilogue = int(rng.integers(3)) if rng.random() < 0.33 else 0
     gate = (torch.randn(T, hq, 256, generator=torch.Generator().manual_seed(seed)) * 2).to(torch.float16).cuda()
+    # the default path also runs with workspaces too small for the batch in one pass (several passes, or the
+    # kernel without a workspace when not even one request fits)
+    small = kv.Executor(int(rng.choice([64 << 20, 1 << 20, 300 << 10])))
     outs = []
+    fill_ex = ex
     for flags in (0, ffi.EXEC_FLAG_PRECISE_ATTENTION):
+        ex = small if flags == 0 else fill_ex
         ex.ex.flags = flags
         out = torch.full((T, hq, 256), 0, dtype=torch.int16, device="cuda")
         out.fill_(0x5500)
