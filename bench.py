@@ -479,6 +479,123 @@ def run_chunked_prefill(args):
     print(json.dumps(line))
 
 
+def run_fused_steps(args):
+    """`--config fused_steps`: what the two fusions around the path save, on one GPU.
+    (1) K producer in front of the append: per-head RMS norm + interleaved 3-D mRoPE + TQ4 append of
+    `--append-tokens` tokens in one kernel, against the append alone on already normalised K (the difference
+    is the whole cost of the fused producer; a separate producer kernel writes and re-reads 2 x 2048 B per
+    token on top) and, when the reference's kernels were built, against its norm/RoPE kernel + its append.
+    (2) Output gate (+ Hadamard-64) behind the attention: config 1's decode step through the gated entry
+    point, against the plain entry point followed by the stand-alone gate kernel."""
+    import ctypes as C
+    import oracle
+    from warp34_b200 import ffi, kv, synth
+    lib = ffi.kernels()
+    ref_path = oracle.ref_lib_path()
+    ex = kv.Executor(64 << 20)
+    ex.set_stream()
+    hq, hkv = 24, 4
+    n_tok = int(args.append_tokens)
+    reps = max(5, min(args.steps, 50))
+
+    def timed(fn, flush=None):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps)]
+        for a, b in evs:
+            if flush is not None:
+                flush.zero_()
+            a.record()
+            fn()
+            b.record()
+        torch.cuda.synchronize()
+        return float(np.median([a.elapsed_time(b) for a, b in evs]))
+
+    # ---- (1) producer + append ------------------------------------------------------------------------
+    g = torch.Generator().manual_seed(5)
+    qgd, kd = hq * 256 * 2, hkv * 256
+    stride = qgd + 2 * kd
+    qkv = (torch.randn(n_tok, stride, generator=g) * 1.5).to(torch.float16).cuda()
+    k_norm_w = (torch.randn(256, generator=g) * 0.2).to(torch.float16).cuda()
+    q_norm_w = (torch.randn(256, generator=g) * 0.2).to(torch.float16).cuda()
+    pos = torch.arange(n_tok, dtype=torch.int32)
+    planes = torch.stack([pos, pos, pos]).contiguous().cuda()
+    wl = synth.PagedWorkload([0], [n_tok], hkv, seed=5)
+    b = wl.step()
+    k_in = qkv.data_ptr() + 2 * qgd
+    v_in = qkv.data_ptr() + 2 * (qgd + kd)
+    rot, sec = 64, (11, 11, 10)
+
+    def fused():
+        rc = lib.warp34_fused_k_rmsnorm_rope_kv_cache_write_f16(
+            C.byref(ex.ex), C.byref(wl.layer.layout), C.byref(b.desc), k_in, v_in, k_norm_w.data_ptr(), planes.data_ptr(),
+            n_tok, rot, sec[0], sec[1], sec[2], stride, stride, 1.0e6, 1e-6)
+        assert rc == 0, rc
+
+    def plain():
+        rc = lib.warp34_kv_cache_write_strided(C.byref(ex.ex), C.byref(wl.layer.layout), C.byref(b.desc), k_in, v_in, stride, stride)
+        assert rc == 0, rc
+
+    producer = {"tokens": n_tok, "fused_norm_rope_append_ms": timed(fused), "append_alone_ms": timed(plain)}
+    if ref_path is not None:
+        ref = C.CDLL(ref_path)
+        ref_abi = ffi.bind_kernel_abi(ref_path)
+        if hasattr(ref, "warp34_fused_qk_rmsnorm_rope_gate_strided_f16"):
+            f = ref.warp34_fused_qk_rmsnorm_rope_gate_strided_f16
+            f.restype = C.c_int
+            f.argtypes = [C.c_void_p] * 10 + [C.c_int] * 11 + [C.c_float, C.c_float]
+            q_out = torch.zeros(n_tok, hq, 256, dtype=torch.float16, device="cuda")
+            gate_out = torch.zeros_like(q_out)
+            k_out = torch.zeros(n_tok, hkv, 256, dtype=torch.float16, device="cuda")
+
+            def ref_norm():
+                rc = f(C.addressof(ex.ex), qkv.data_ptr(), k_in, q_norm_w.data_ptr(), k_norm_w.data_ptr(), planes.data_ptr(), None,
+                       q_out.data_ptr(), k_out.data_ptr(), gate_out.data_ptr(), n_tok, n_tok, hq, hkv, 256, rot, sec[0], sec[1],
+                       sec[2], stride, stride, 1.0e6, 1e-6)
+                assert rc == 0, rc
+
+            def ref_append():
+                rc = ref_abi.warp34_kv_cache_write_strided(C.byref(ex.ex), C.byref(wl.layer.layout), C.byref(b.desc),
+                                                           k_out.data_ptr(), v_in, kd, stride)
+                assert rc == 0, rc
+
+            producer["reference_qk_norm_rope_gate_ms"] = timed(ref_norm)
+            producer["reference_append_ms"] = timed(ref_append)
+            producer["note"] = "the reference's norm kernel also produces Q and the gate (24 heads); its K half cannot be timed alone"
+    del qkv, wl
+
+    # ---- (2) attention + output gate ------------------------------------------------------------------
+    _, _, batch, lo, hi, _, seed = synth.CONFIGS["cfg1_batched_decode"]
+    if args.batch > 0:
+        batch = args.batch
+    ctx = [int(c) for c in synth.context_lengths(batch, lo, hi, seed)]
+    wl = synth.PagedWorkload(ctx, [1] * batch, hkv, seed=seed)
+    wl.fill_context(ex, seed, chunk_tokens=32768)
+    b = wl.step()
+    k1, v1 = synth.make_kv(batch, hkv, 99, device="cuda")
+    kv.kv_cache_write(ex, wl.layer, b, k1, v1)
+    q = synth.make_q(batch, hq, seed + 17).cuda()
+    gate = (synth.make_q(batch, hq, seed + 18) * 2).cuda()
+    out = torch.zeros_like(q)
+    epilogue = {"workload": f"config 1 decode step, {batch} sequences", "tokens_in_cache": int(sum(ctx)) + batch}
+    for name, had in (("gate", False), ("gate_hadamard64", True)):
+        standalone = lib.warp34_apply_attn_output_gate_hadamard_f16 if had else lib.warp34_apply_attn_output_gate_f16
+
+        def fused_call():
+            kv.paged_attention_gated(ex, wl.layer, b, q, gate, out, hq, hadamard64=had)
+
+        def two_calls():
+            kv.paged_attention(ex, wl.layer, b, q, out, hq)
+            rc = standalone(C.byref(ex.ex), out.data_ptr(), gate.data_ptr(), out.data_ptr(), None, batch, hq * 256)
+            assert rc == 0, rc
+
+        epilogue[name] = {"fused_ms": timed(fused_call), "attention_then_gate_kernel_ms": timed(two_calls)}
+    epilogue["attention_alone_ms"] = timed(lambda: kv.paged_attention(ex, wl.layer, b, q, out, hq))
+    print(json.dumps({"metric": "fused_steps_ms", "unit": "ms", "n_gpus": 1, "steps": reps, "warmup": 3, "higher_is_better": False,
+                      "data": "synthetic", "dtype": "f16", "producer_append": producer, "attention_output_gate": epilogue}))
+
+
 def run_qsa_sparse(args):
     """`--config qsa_sparse_decode`: query-sparse paged attention over TQ4 pages, one decode step of
     config 1's geometry: every token attends to 256 selected 4-token groups (1024 keys) of its sequence.
@@ -675,6 +792,8 @@ def main():
     args.warmup = max(args.warmup, 3)
     if args.config == "qsa_sparse_decode":
         return run_qsa_sparse(args)
+    if args.config == "fused_steps":
+        return run_fused_steps(args)
     if args.kv != "tq4":
         return run_other_kv(args)
     if args.config == "cfg2_chunked_prefill":

@@ -126,35 +126,36 @@ extern "C" __device__ float __nv_powf(float, float);
 // kernel would have written to k_out, so that the packed bytes are the same as those of the
 // two-kernel sequence.  Arithmetic order is the reference's:
 //  * sum of squares: its thread t adds the squares of columns 8 t .. 8 t + 7 in order, as a chain of
-//    fused multiply-adds from 0 (here: register t passed down the 8 lanes), then a 32-wide xor
-//    butterfly (here: in the registers of the last lane);
+//    fused multiply-adds from 0, then a 32-wide xor butterfly (here: the row is transposed through
+//    shared memory so that each lane runs four of the chains, and the butterfly's first two levels
+//    stay in the lane);
 //  * x * inv_rms, then * (1 + w), each rounded, then to fp16;
 //  * angle = position * (1 / powf(theta, 2 i / rotary_dim)), sine and cosine rounded to fp16.
-// Every lane of the warp takes part (the chain uses shuffles); the caller keeps the result for K
-// rows only.  rotary_dim / 2 must be a multiple of 8 so that both elements of a rotated pair sit in
-// one lane.
+// Every lane of the warp takes part (the chain uses shuffles): the caller calls it for groups of four K
+// rows.  rotary_dim / 2 must be a multiple of 8 so that both elements of a rotated pair sit in one lane.
 __device__ __forceinline__ void k_producer(float (&x)[32], int sub, int lane_base, int tok, const AppendParams& p,
-                                           const float* s_w1, const float* s_inv_freq) {
-    float part[32];
+                                           const float* s_w1, const float* s_inv_freq, float* s_rows) {
+    // The reference's thread t = sub + 8 j of this row sums columns 8 t .. 8 t + 7; this lane holds column
+    // sub + 8 r in register r.  The row goes through shared memory (one 257-float line per row of the warp)
+    // and comes back as the four 8-column runs of threads sub, sub + 8, sub + 16, sub + 24.
+    float* line = s_rows + (lane_base >> 3) * 257;
 #pragma unroll
-    for (int r = 0; r < 32; ++r) part[r] = __fmaf_rn(x[r], x[r], 0.0f);
+    for (int r = 0; r < 32; ++r) line[sub + 8 * r] = x[r];
+    __syncwarp();
+    float part[4];
 #pragma unroll
-    for (int step = 1; step < 8; ++step) {
+    for (int j = 0; j < 4; ++j) {
+        const float* run = line + 8 * (sub + 8 * j);
+        float acc = 0.0f;
 #pragma unroll
-        for (int r = 0; r < 32; ++r) {
-            const float in = __shfl_up_sync(0xffffffffu, part[r], 1, 8);
-            part[r] = __fmaf_rn(x[r], x[r], in);
-        }
+        for (int c = 0; c < 8; ++c) acc = __fmaf_rn(run[c], run[c], acc);
+        part[j] = acc;
     }
-    // lane 7 of the group now holds the reference's 32 per-thread sums; its butterfly 16, 8, 4, 2, 1
+    __syncwarp();   // the line is rewritten by the next group of rows
+    // its 32-wide xor butterfly 16, 8, 4, 2, 1: thread bits 4 and 3 are j, bits 2..0 are sub
+    float sum_sq = __fadd_rn(__fadd_rn(part[0], part[2]), __fadd_rn(part[1], part[3]));
 #pragma unroll
-    for (int h = 16; h > 0; h >>= 1) {
-#pragma unroll
-        for (int r = 0; r < 16; ++r) {
-            if (r < h) part[r] = __fadd_rn(part[r], part[r + h]);
-        }
-    }
-    const float sum_sq = __shfl_sync(0xffffffffu, part[0], lane_base + 7);
+    for (int h = 4; h > 0; h >>= 1) sum_sq = __fadd_rn(sum_sq, __shfl_xor_sync(0xffffffffu, sum_sq, h));
     const float inv_rms = rsqrtf(sum_sq / (float)kHeadDim + p.rms_eps);
 #pragma unroll
     for (int r = 0; r < 32; ++r) {
@@ -163,22 +164,40 @@ __device__ __forceinline__ void k_producer(float (&x)[32], int sub, int lane_bas
     }
     const int half_rot = p.rotary_dim >> 1;
     const int regs = half_rot >> 3;
+    // sine and cosine of pair i = sub + 8 r at this row's token, rounded to fp16
+    auto sincos_of = [&](int i, float& sin_a, float& cos_a) {
+        int plane = 0;
+        if ((i % 3) == 1 && i < p.mrope_s1 * 3) {
+            plane = 1;
+        } else if ((i % 3) == 2 && i < p.mrope_s2 * 3) {
+            plane = 2;
+        }
+        const float pos = (float)p.positions[(size_t)plane * p.pos_plane_stride + tok];
+        const float angle = pos * s_inv_freq[i];
+        sin_a = __half2float(__float2half_rn(__nv_sinf(angle)));
+        cos_a = __half2float(__float2half_rn(__nv_cosf(angle)));
+    };
+    // The four rows of a warp are usually the kv heads of one token: the angles are then the same in all
+    // four, and row group g computes those of registers g, g + 4, ... for the others (a quarter of the calls).
+    const int g = lane_base >> 3;
+    const bool shared = ((regs & 3) == 0) && __all_sync(0xffffffffu, tok == __shfl_sync(0xffffffffu, tok, 0));
+    float s_own[4] = {0.f, 0.f, 0.f, 0.f}, c_own[4] = {0.f, 0.f, 0.f, 0.f};
+    if (shared) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            if (4 * k < regs) sincos_of(sub + 8 * (g + 4 * k), s_own[k], c_own[k]);
+        }
+    }
 #pragma unroll
     for (int r = 0; r < 16; ++r) {
         if (r < regs) {
-            const int i = sub + 8 * r;
-            int plane = 0;
-            if ((i % 3) == 1 && i < p.mrope_s1 * 3) {
-                plane = 1;
-            } else if ((i % 3) == 2 && i < p.mrope_s2 * 3) {
-                plane = 2;
+            float sin_a, cos_a;
+            if (shared) {
+                sin_a = __shfl_sync(0xffffffffu, s_own[r >> 2], sub + 8 * (r & 3));
+                cos_a = __shfl_sync(0xffffffffu, c_own[r >> 2], sub + 8 * (r & 3));
+            } else {
+                sincos_of(sub + 8 * r, sin_a, cos_a);
             }
-            const float pos = (float)p.positions[(size_t)plane * p.pos_plane_stride + tok];
-            const float angle = pos * s_inv_freq[i];
-            float sin_a = __nv_sinf(angle);
-            float cos_a = __nv_cosf(angle);
-            sin_a = __half2float(__float2half_rn(sin_a));
-            cos_a = __half2float(__float2half_rn(cos_a));
             const float x1 = x[r];
             const float x2 = x[r + regs];
             x[r] = __half2float(__float2half(x1 * cos_a - x2 * sin_a));
@@ -188,15 +207,17 @@ __device__ __forceinline__ void k_producer(float (&x)[32], int sub, int lane_bas
 }
 
 constexpr int kAppendBlocksPerSm = 5;   // 4, 6 and 8 measured within 3 % of it on a 32 768-token append
+constexpr int kProducerBlocksPerSm = 4;   // with the K producer in front: 128 registers (5 blocks of 96 registers measured the same, 3 of 168 slower)
 
 // IN_BF16: activations are bf16 instead of fp16.  Values that both types can hold encode to the
 // same bytes; bf16 values beyond the fp16 range are simply larger fp32 inputs.
 // PRODUCER: K rows go through k_producer() first (fp16 activations only).
 template <bool IN_BF16, bool PRODUCER>
-__global__ void __launch_bounds__(128, PRODUCER ? 3 : kAppendBlocksPerSm) tq4_append_kernel(const AppendParams p) {
+__global__ void __launch_bounds__(128, PRODUCER ? kProducerBlocksPerSm : kAppendBlocksPerSm) tq4_append_kernel(const AppendParams p) {
     __shared__ float s_centroid[16];
     __shared__ float s_w1[PRODUCER ? kHeadDim : 1];
     __shared__ float s_inv_freq[PRODUCER ? kHeadDim / 2 : 1];
+    __shared__ float s_rows[PRODUCER ? 4 * 4 * 257 : 1];   // one line per row of each of the four warps
     if (threadIdx.x < 16) s_centroid[threadIdx.x] = tq4_centroid(threadIdx.x);
     if (PRODUCER) {
         for (int i = threadIdx.x; i < kHeadDim; i += blockDim.x) {
@@ -226,15 +247,19 @@ __global__ void __launch_bounds__(128, PRODUCER ? 3 : kAppendBlocksPerSm) tq4_ap
 
     const int heads = p.layout.local_kv_heads;
     const int warps_total = gridDim.x * 4;
-    const int quads = (p.total_rows + 3) >> 2;
+    // A warp takes four rows at a time.  Plain append: rows 4 q .. 4 q + 3 of the list (token, head, K | V).
+    // With the producer in front, a group holds four K rows or four V rows (groups alternate), so that the
+    // norm and the rotation run for K groups only and not for the V rows that would share a warp with them.
+    const int pairs = p.total_rows >> 1;                      // (token, head) pairs
+    const int quads = PRODUCER ? 2 * ((pairs + 3) >> 2) : (p.total_rows + 3) >> 2;
 #pragma unroll 1
     for (int quad = blockIdx.x * 4 + (threadIdx.x >> 5); quad < quads; quad += warps_total) {
     const int row_id = quad * 4 + (lane >> 3);
 
     // ---- resolve the row: (token, head, K or V), masks, destination ------------------
-    bool active = row_id < p.total_rows;
-    const int which = row_id & 1;
-    const int th = row_id >> 1;
+    const int which = PRODUCER ? (quad & 1) : (row_id & 1);
+    const int th = PRODUCER ? ((quad >> 1) * 4 + (lane >> 3)) : (row_id >> 1);
+    bool active = PRODUCER ? (th < pairs) : (row_id < p.total_rows);
     const int tok = active ? th / heads : 0;
     const int head = th - tok * heads;
     int slot = -1;
@@ -276,15 +301,9 @@ __global__ void __launch_bounds__(128, PRODUCER ? 3 : kAppendBlocksPerSm) tq4_ap
         v[r] = PRODUCER ? x : __uint_as_float(__float_as_uint(x) ^ ((sign_word << (31 - r)) & 0x80000000u));
     }
     if (PRODUCER) {
-        float kx[32];
+        if (which == 0) k_producer(v, sub, lane_base, tok, p, s_w1, s_inv_freq, s_rows + (threadIdx.x >> 5) * (4 * 257));   // warp-uniform: a group is all K or all V
 #pragma unroll
-        for (int r = 0; r < 32; ++r) kx[r] = v[r];
-        k_producer(kx, sub, lane_base, tok, p, s_w1, s_inv_freq);
-#pragma unroll
-        for (int r = 0; r < 32; ++r) {
-            const float x = (which == 0) ? kx[r] : v[r];
-            v[r] = __uint_as_float(__float_as_uint(x) ^ ((sign_word << (31 - r)) & 0x80000000u));
-        }
+        for (int r = 0; r < 32; ++r) v[r] = __uint_as_float(__float_as_uint(v[r]) ^ ((sign_word << (31 - r)) & 0x80000000u));
     }
 
     // ---- WHT-256: stages 1,2,4 across lanes, 8..128 in registers ----------------------
@@ -518,7 +537,7 @@ static int launch_append(const warp34_exec* ex, const warp34_kv_layer_layout* la
         }
         if (sm_count_cache[dev] > 0) sms = sm_count_cache[dev];
     }
-    const long long resident = (long long)sms * (producer != nullptr ? 3 : kAppendBlocksPerSm);
+    const long long resident = (long long)sms * (producer != nullptr ? kProducerBlocksPerSm : kAppendBlocksPerSm);
     const unsigned blocks = (unsigned)(blocks_needed < resident ? blocks_needed : resident);
     p.k_norm_w = nullptr;
     p.positions = nullptr;
