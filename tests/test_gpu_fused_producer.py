@@ -28,7 +28,11 @@ def env(native_libs):
 
 
 @pytest.mark.parametrize("hq,hkv,rotary_dim,sections", [(24, 4, 64, (11, 11, 10)), (16, 4, 64, (8, 12, 12)),
-                                                       (8, 2, 128, (24, 20, 20)), (8, 2, 256, (44, 42, 42))])
+                                                       (8, 2, 128, (24, 20, 20)), (8, 2, 256, (44, 42, 42)),
+                                                       # a token's heads share their sines only when four rows of a warp
+                                                       # are one token's and rotary_dim / 16 is a multiple of 4
+                                                       (8, 8, 128, (22, 21, 21)), (3, 3, 64, (12, 10, 10)),
+                                                       (4, 1, 32, (6, 5, 5)), (8, 4, 96, (16, 16, 16))])
 def test_fused_producer_append_is_bit_identical_to_the_two_kernel_sequence(env, hq, hkv, rotary_dim, sections):
     ffi, kv, synth, lib, ref = env["ffi"], env["kv"], env["synth"], env["lib"], env["ref"]
     ctx = [37, 300, 1, 16]
