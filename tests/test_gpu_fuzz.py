@@ -241,7 +241,7 @@ def _append_case(env, ref_lib, fmt_name, seed):
     T = int(rng.integers(1, 200))
     num_pages = 40
     g = torch.Generator().manual_seed(seed)
-    pad = int(rng.choice([0, 8, 64]))
+    pad = int(rng.choice([0, 4, 8, 64]))        # 4 halves: every other row starts off a 16-byte boundary
     width = hkv * 256 + pad
     kbuf = torch.randn(T, width, generator=g)
     vbuf = torch.randn(T, width, generator=g)

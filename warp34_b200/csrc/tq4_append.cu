@@ -467,7 +467,7 @@ static int launch_append_kv8(const warp34_exec* ex, const warp34_kv_layer_layout
     const long long rows = 2ll * batch->total_tokens * layout->local_kv_heads;
     if (rows > 0x7fffffffll) return (int)cudaErrorInvalidValue;
     p.total_rows = (int)rows;
-    kv8_append_kernel<<<(unsigned)((rows + 3) / 4), 128, 0, (cudaStream_t)ex->stream>>>(p);
+    kv8_append_kernel<<<(unsigned)((rows / 2 + 3) / 4), 128, 0, (cudaStream_t)ex->stream>>>(p);   // a warp per (token, head)
     return (int)cudaGetLastError();
 }
 
