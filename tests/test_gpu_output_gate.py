@@ -121,8 +121,8 @@ def test_stand_alone_gate_steps(env, hadamard, total_dim):
     assert (d2 <= 2e-3 + 2.0 ** -10 * np.abs(want[live])).all()
     if hadamard:
         assert fn(C.byref(env["ex"].ex), a_dev.data_ptr(), g_dev.data_ptr(), out.data_ptr(), None, t, 100) == 1
-    # the reference's own kernels on the same inputs (when its unit was built into oracle/_ref): equal
-    # up to the last place of fp16 (it divides and exponentiates with the fast-math variants)
+    # the reference's own kernels on the same inputs (when its unit was built into oracle/_ref): the same bits
+    # (the sigmoid is ex2.approx and rcp.approx, as its -use_fast_math build lowers expf and the division)
     import oracle
     path = oracle.ref_lib_path()
     ref = C.CDLL(path) if path else None
@@ -139,6 +139,4 @@ def test_stand_alone_gate_steps(env, hadamard, total_dim):
     torch.cuda.synchronize()
     rb = out_r.cpu().numpy().view(np.uint16)
     assert (rb[5] == 0x5500).all()
-    mine, theirs = f16(bits)[live], f16(rb)[live]
-    assert np.abs(mine - theirs).max() <= 2.0 ** -10 * np.abs(theirs).max() + 1e-6
-    assert (bits[live] == rb[live]).mean() > 0.98
+    assert (bits[live] == rb[live]).all(), int((bits[live] != rb[live]).sum())

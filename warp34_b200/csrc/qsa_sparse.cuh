@@ -98,7 +98,7 @@ __device__ __forceinline__ void qsa_finish_row(const QsaParams& p, float* row_sm
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             const float g = __half2float(__ushort_as_half(p.gate[row_base + lane + 32 * j]));
-            t[j] *= 1.0f / (1.0f + __expf(-g));
+            t[j] *= sigmoid_gate(g);
         }
     }
     if (p.hadamard) hadamard64_row(t, lane, 0);

@@ -94,6 +94,14 @@ struct OutputGate {
                         // epilogue, op_qsa.cu:1040-1067) and may be absent (gate == nullptr)
 };
 
+// 1 / (1 + e^-g) as the reference's kernels compute it under -use_fast_math: ex2.approx of -g log2 e, then
+// rcp.approx (op_norms_rope_act.cu:756, :841), not an IEEE division.
+__device__ __forceinline__ float sigmoid_gate(float g) {
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + __expf(-g)));
+    return r;
+}
+
 __device__ __forceinline__ float round_act(float x, int bf16) {
     return bf16 ? __bfloat162float(__float2bfloat16_rn(x)) : __half2float(__float2half_rn(x));
 }
@@ -125,7 +133,7 @@ __device__ __forceinline__ void apply_output_gate(float (&v)[8], const OutputGat
         for (int j = 0; j < 8; ++j) {
             const float g = load_act(og.gate, row_base + lane + 32 * j, io_bf16);
             const float a = (og.mode & 4) ? v[j] : round_act(v[j], io_bf16);
-            v[j] = a * (1.0f / (1.0f + __expf(-g)));
+            v[j] = a * sigmoid_gate(g);
         }
     }
     if ((og.mode & 3) != 2) return;
@@ -145,17 +153,77 @@ __device__ __forceinline__ void store_output_row(void* out, size_t row_base, flo
 
 // The two steps on their own (for layers whose attention kernel has no fused epilogue): one warp per
 // 256 columns, in place or out of place.
+template <int MODE, bool BF16>
 __global__ void __launch_bounds__(128) attn_output_gate_kernel(const void* __restrict__ attn, const void* gate,
                                                                void* out, const uint8_t* __restrict__ valid_token_mask,
-                                                               int num_tokens, int total_dim, int mode, int io_bf16) {
+                                                               int num_tokens, int total_dim) {
+    constexpr int mode = MODE;
+    constexpr int io_bf16 = BF16 ? 1 : 0;
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int chunks = (total_dim + 255) / 256;
-    const long long w = (long long)blockIdx.x * 4 + wid;
-    if (w >= (long long)num_tokens * chunks) return;
-    const int tok = (int)(w / chunks), c = (int)(w % chunks);
+    const int tok = (int)blockIdx.x, c = (int)blockIdx.y * 4 + wid;   // grid: (tokens, chunks / 4)
+    if (tok >= num_tokens || c >= chunks) return;
     if (valid_token_mask != nullptr && valid_token_mask[tok] == 0) return;
     const size_t base = (size_t)tok * total_dim + (size_t)c * 256;
     const int cols = min(256, total_dim - c * 256);    // a multiple of 64 when mode == 2 (checked by the caller)
+    // A full chunk whose three rows start on 16-byte boundaries: lane holds columns [8 lane, 8 lane + 8), one
+    // 128-bit access per row; a 64-column Hadamard block is eight lanes (three levels in registers, three
+    // across lanes: the transform is the same whatever the order of its levels).  (A grid-stride loop with
+    // the next chunk's loads in flight measured slower than one chunk per warp.)
+    const uintptr_t pa = reinterpret_cast<uintptr_t>(attn) + 2 * base, pg = reinterpret_cast<uintptr_t>(gate) + 2 * base;
+    const uintptr_t po = reinterpret_cast<uintptr_t>(out) + 2 * base;
+    if (cols == 256 && ((pa | pg | po) & 15u) == 0u) {
+        const uint4 ra = reinterpret_cast<const uint4*>(pa)[lane];   // in place is fine: a lane writes the 16 bytes it read
+        const uint4 rg = reinterpret_cast<const uint4*>(pg)[lane];
+        const uint32_t wa[4] = {ra.x, ra.y, ra.z, ra.w}, wg[4] = {rg.x, rg.y, rg.z, rg.w};
+        float x[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t ha = (wa[i >> 1] >> (16 * (i & 1))) & 0xffffu, hg = (wg[i >> 1] >> (16 * (i & 1))) & 0xffffu;
+            const float a = io_bf16 ? __uint_as_float(ha << 16) : __half2float(__ushort_as_half((unsigned short)ha));
+            const float g = io_bf16 ? __uint_as_float(hg << 16) : __half2float(__ushort_as_half((unsigned short)hg));
+            x[i] = a * sigmoid_gate(g);   // `a` is already a value of the activation type
+        }
+        if (mode == 2) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) x[i] = round_act(x[i], io_bf16);
+#pragma unroll
+            for (int d = 1; d < 8; d <<= 1) {        // column bits 0-2: registers
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    if ((i & d) == 0) {
+                        const float lo = x[i], hi = x[i | d];
+                        x[i] = lo + hi;
+                        x[i | d] = lo - hi;
+                    }
+                }
+            }
+#pragma unroll
+            for (int d = 1; d < 8; d <<= 1) {        // column bits 3-5: lanes
+                const bool up = (lane & d) != 0;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float o = __shfl_xor_sync(0xffffffffu, x[i], d);
+                    x[i] = up ? (o - x[i]) : (x[i] + o);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) x[i] *= 0.125f;
+        }
+        uint32_t wo[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            if (io_bf16) {
+                const __nv_bfloat162 h = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
+                wo[i] = *reinterpret_cast<const uint32_t*>(&h);
+            } else {
+                const __half2 h = __floats2half2_rn(x[2 * i], x[2 * i + 1]);
+                wo[i] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+        }
+        reinterpret_cast<uint4*>(po)[lane] = make_uint4(wo[0], wo[1], wo[2], wo[3]);
+        return;
+    }
     float v[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) v[j] = (lane + 32 * j < cols) ? load_act(attn, base + lane + 32 * j, io_bf16) : 0.0f;
@@ -169,7 +237,7 @@ __global__ void __launch_bounds__(128) attn_output_gate_kernel(const void* __res
         for (int j = 0; j < 8; ++j) {
             if (lane + 32 * j < cols) {
                 const float g = load_act(gate, base + lane + 32 * j, io_bf16);
-                v[j] = round_act(v[j], io_bf16) * (1.0f / (1.0f + __expf(-g)));
+                v[j] = round_act(v[j], io_bf16) * sigmoid_gate(g);
             }
         }
         if (mode == 2) {
@@ -2239,10 +2307,18 @@ static int w34::launch_output_gate(const warp34_exec* ex, const void* attn, cons
     if (mode == 2 && (total_dim & 63) != 0) return (int)cudaErrorInvalidValue;
     if ((((uintptr_t)attn | (uintptr_t)gate | (uintptr_t)out) & 1u) != 0u) return (int)cudaErrorInvalidValue;
     if (num_tokens <= 0 || total_dim <= 0) return 0;
-    const long long warps = (long long)num_tokens * ((total_dim + 255) / 256);
-    if ((warps + 3) / 4 > 0x7fffffffll) return (int)cudaErrorInvalidValue;
-    w34::attn_output_gate_kernel<<<(unsigned)((warps + 3) / 4), 128, 0, (cudaStream_t)ex->stream>>>(
-        attn, gate, out, valid_token_mask, num_tokens, total_dim, mode, io_bf16);
+    const int chunk_blocks = ((total_dim + 255) / 256 + 3) / 4;
+    if (chunk_blocks > 65535) return (int)cudaErrorInvalidValue;
+    const dim3 grid((unsigned)num_tokens, (unsigned)chunk_blocks);
+    cudaStream_t st = (cudaStream_t)ex->stream;
+    if (mode != 1 && mode != 2) return (int)cudaErrorInvalidValue;
+    if (mode == 2) {
+        if (io_bf16) w34::attn_output_gate_kernel<2, true><<<grid, 128, 0, st>>>(attn, gate, out, valid_token_mask, num_tokens, total_dim);
+        else w34::attn_output_gate_kernel<2, false><<<grid, 128, 0, st>>>(attn, gate, out, valid_token_mask, num_tokens, total_dim);
+    } else {
+        if (io_bf16) w34::attn_output_gate_kernel<1, true><<<grid, 128, 0, st>>>(attn, gate, out, valid_token_mask, num_tokens, total_dim);
+        else w34::attn_output_gate_kernel<1, false><<<grid, 128, 0, st>>>(attn, gate, out, valid_token_mask, num_tokens, total_dim);
+    }
     return (int)cudaGetLastError();
 }
 
