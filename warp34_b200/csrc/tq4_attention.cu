@@ -116,9 +116,9 @@ __device__ __forceinline__ void hadamard64_row(float (&v)[8], int lane, int io_b
 #pragma unroll
         for (int d = 1; d < 32; d <<= 1) {
             const float o0 = __shfl_xor_sync(0xffffffffu, a0, d), o1 = __shfl_xor_sync(0xffffffffu, a1, d);
-            const bool up = (lane & d) != 0;
-            a0 = up ? (o0 - a0) : (a0 + o0);
-            a1 = up ? (o1 - a1) : (a1 + o1);
+            const float dir = (lane & d) ? -1.0f : 1.0f;   // upper lane: o - a, lower: a + o, one rounding either way
+            a0 = __fmaf_rn(dir, a0, o0);
+            a1 = __fmaf_rn(dir, a1, o1);
         }
         v[2 * b] = a0 * 0.125f;
         v[2 * b + 1] = a1 * 0.125f;
@@ -178,15 +178,31 @@ __global__ void __launch_bounds__(128) attn_output_gate_kernel(const void* __res
         const uint32_t wa[4] = {ra.x, ra.y, ra.z, ra.w}, wg[4] = {rg.x, rg.y, rg.z, rg.w};
         float x[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const uint32_t ha = (wa[i >> 1] >> (16 * (i & 1))) & 0xffffu, hg = (wg[i >> 1] >> (16 * (i & 1))) & 0xffffu;
-            const float a = io_bf16 ? __uint_as_float(ha << 16) : __half2float(__ushort_as_half((unsigned short)ha));
-            const float g = io_bf16 ? __uint_as_float(hg << 16) : __half2float(__ushort_as_half((unsigned short)hg));
-            x[i] = a * sigmoid_gate(g);   // `a` is already a value of the activation type
+        for (int i = 0; i < 4; ++i) {   // two columns per 32-bit word
+            float2 a, g;
+            if (io_bf16) {
+                a = make_float2(__uint_as_float(wa[i] << 16), __uint_as_float(wa[i] & 0xffff0000u));
+                g = make_float2(__uint_as_float(wg[i] << 16), __uint_as_float(wg[i] & 0xffff0000u));
+            } else {
+                a = __half22float2(*reinterpret_cast<const __half2*>(&wa[i]));
+                g = __half22float2(*reinterpret_cast<const __half2*>(&wg[i]));
+            }
+            x[2 * i] = a.x * sigmoid_gate(g.x);   // `a` is already a value of the activation type
+            x[2 * i + 1] = a.y * sigmoid_gate(g.y);
         }
         if (mode == 2) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) x[i] = round_act(x[i], io_bf16);
+            for (int i = 0; i < 4; ++i) {   // the gated values rounded to the activation type, pairwise
+                if (io_bf16) {
+                    const float2 r = __bfloat1622float2(__floats2bfloat162_rn(x[2 * i], x[2 * i + 1]));
+                    x[2 * i] = r.x;
+                    x[2 * i + 1] = r.y;
+                } else {
+                    const float2 r = __half22float2(__floats2half2_rn(x[2 * i], x[2 * i + 1]));
+                    x[2 * i] = r.x;
+                    x[2 * i + 1] = r.y;
+                }
+            }
 #pragma unroll
             for (int d = 1; d < 8; d <<= 1) {        // column bits 0-2: registers
 #pragma unroll
@@ -199,12 +215,12 @@ __global__ void __launch_bounds__(128) attn_output_gate_kernel(const void* __res
                 }
             }
 #pragma unroll
-            for (int d = 1; d < 8; d <<= 1) {        // column bits 3-5: lanes
-                const bool up = (lane & d) != 0;
+            for (int d = 1; d < 8; d <<= 1) {        // column bits 3-5: lanes (upper lane: o - x, lower: x + o)
+                const float dir = (lane & d) ? -1.0f : 1.0f;
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     const float o = __shfl_xor_sync(0xffffffffu, x[i], d);
-                    x[i] = up ? (o - x[i]) : (x[i] + o);
+                    x[i] = __fmaf_rn(dir, x[i], o);   // one rounding, like the add or the subtraction
                 }
             }
 #pragma unroll
