@@ -2184,7 +2184,13 @@ static DeviceInfo* device_info(int* rc) {
                                         cudaFuncAttributeMaxDynamicSharedMemorySize, optin);
         if (*rc != 0) return nullptr;
         if ((size_t)optin < prefill_exact_smem_min_bytes()) { *rc = (int)cudaErrorNotSupported; return nullptr; }
-        *rc = (int)cudaFuncSetAttribute(tq4_attention_prefill_exact_kernel,
+        *rc = (int)cudaFuncSetAttribute(tq4_attention_prefill_exact_kernel<kPxWarps>,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, optin);
+        if (*rc != 0) return nullptr;
+        *rc = (int)cudaFuncSetAttribute(tq4_attention_prefill_exact_kernel<kPxWarps / 2>,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, optin);
+        if (*rc != 0) return nullptr;
+        *rc = (int)cudaFuncSetAttribute(tq4_attention_prefill_exact_kernel<kPxWarps / 4>,
                                         cudaFuncAttributeMaxDynamicSharedMemorySize, optin);
         if (*rc != 0) return nullptr;
         *rc = (int)cudaFuncSetAttribute(tq4_attention_prefill_tc_kernel,
@@ -2464,15 +2470,34 @@ static int launch_attention(const warp34_exec* ex, const warp34_kv_layer_layout*
         pp.io_bf16 = io_bf16;
         pp.num_q_heads = num_q_heads;
         pp.gqa = gqa;
-        pp.tok_per_tile = kPxRows / gqa;
         pp.q_scale = batch->sm_scale * 1.4426950408889634f / kLutScale;
         pp.status = status;
         pp.smem_bytes = (uint32_t)dev->smem_optin;
         pp.og = og;
-        const long long tiles = (long long)batch->total_tokens / pp.tok_per_tile + batch->num_reqs;
+        // 128-row CTAs, or 64- / 32-row CTAs when that is faster for this call (a short chunk whose 128-row tiles
+        // would leave SMs without a CTA).  One CTA fits an SM; a CTA of 4 (2) warps takes about 0.69 (0.55) of the
+        // time of one of 8 warps over the same keys (measured: fewer warps share the SM's tensor pipe), so the
+        // estimate is waves x that factor.
+        int warps = kPxWarps;
+        long long tiles = 0;
+        {
+            const float factor[3] = {1.0f, 0.69f, 0.55f};
+            float best = 0.0f;
+            for (int k = 0, w = kPxWarps; k < 3 && gqa <= 16 * w; ++k, w /= 2) {
+                const int tpt = (16 * w) / gqa;
+                const long long t = (long long)batch->total_tokens / tpt + batch->num_reqs;
+                const long long waves = (t * layout->local_kv_heads + dev->sm_count - 1) / dev->sm_count;
+                const float est = (float)waves * factor[k];
+                if (k == 0 || est < best) { best = est; warps = w; tiles = t; pp.tok_per_tile = tpt; }
+            }
+        }
         if (tiles > 0x7fffffffll) return (int)cudaErrorInvalidValue;
         const dim3 grid((unsigned)tiles, (unsigned)layout->local_kv_heads);
-        tq4_attention_prefill_exact_kernel<<<grid, kPxWarps * 32, (size_t)dev->smem_optin, (cudaStream_t)ex->stream>>>(pp);
+        const size_t smem_px = (size_t)dev->smem_optin;
+        cudaStream_t st_px = (cudaStream_t)ex->stream;
+        if (warps == kPxWarps) tq4_attention_prefill_exact_kernel<kPxWarps><<<grid, kPxWarps * 32, smem_px, st_px>>>(pp);
+        else if (warps == kPxWarps / 2) tq4_attention_prefill_exact_kernel<kPxWarps / 2><<<grid, (kPxWarps / 2) * 32, smem_px, st_px>>>(pp);
+        else tq4_attention_prefill_exact_kernel<kPxWarps / 4><<<grid, (kPxWarps / 4) * 32, smem_px, st_px>>>(pp);
         return (int)cudaGetLastError();
     }
 

@@ -39,7 +39,7 @@ struct PrefillExactParams {
     int io_bf16;
     int num_q_heads;
     int gqa;
-    int tok_per_tile;      // 128 / gqa
+    int tok_per_tile;      // rows of a CTA (128 or 64) / gqa
     float q_scale;         // sm_scale * log2(e) / kLutScale
     int32_t* status;       // may be null; bit 0: a wait gave up, bit 1: shared-memory window too small
     uint32_t smem_bytes;
@@ -66,7 +66,11 @@ __device__ __forceinline__ void mma16816_a4(float (&c)[4], const uint32_t (&a)[4
     mma16816(c, a[0], a[1], a[2], a[3], b0, b1);
 }
 
-__global__ void __launch_bounds__(kPxWarps * 32, 1) tq4_attention_prefill_exact_kernel(const PrefillExactParams p) {
+// WARPS = 8: 128 query rows per CTA.  WARPS = 4: 64 rows, for launches whose 128-row tiles would leave SMs empty (a short
+// chunk): twice the CTAs, and half as many warps share an SM's tensor pipe.
+template <int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, 1) tq4_attention_prefill_exact_kernel(const PrefillExactParams p) {
+    constexpr int kRows = 16 * WARPS;
     extern __shared__ __align__(1024) uint8_t smem[];
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
     const int gid = lane >> 2, tig = lane & 3;
@@ -76,13 +80,13 @@ __global__ void __launch_bounds__(kPxWarps * 32, 1) tq4_attention_prefill_exact_
 
     SmemCarver carve(win_lo, lut_addr, win_hi);
     uint32_t qhi = 0, ring = 0, bars = 0;
-    for (int w = 0; w < kPxWarps; ++w) {
+    for (int w = 0; w < WARPS; ++w) {
         const uint32_t a = carve.take(kPxQHiBytes + kPxQLoBytes, 16);
         if (w == wid) qhi = a;
     }
     ring = carve.take(kPxStages * kStageStride, 128);
     bars = carve.take(2 * kPxStages * 8, 8);        // full[stage], then empty[stage]
-    const uint32_t red = carve.take((4 * kPxWarps + 1) * 4 + kPxRows * 4, 4);   // per-warp key ranges, abort flag, row steps
+    const uint32_t red = carve.take((4 * WARPS + 1) * 4 + kRows * 4, 4);   // per-warp key ranges, abort flag, row steps
     if (!carve.ok) {
         if (tid == 0 && p.status != nullptr) atomicOr(p.status, 2);
         return;
@@ -90,10 +94,10 @@ __global__ void __launch_bounds__(kPxWarps * 32, 1) tq4_attention_prefill_exact_
     const uint32_t qlo = qhi + kPxQHiBytes;
     uint8_t* qhi_gen = smem + (qhi - win_lo);
     int* s_lo = reinterpret_cast<int*>(smem + (red - win_lo));
-    int* s_hi = s_lo + kPxWarps;
-    int* s_slo = s_hi + kPxWarps;
-    int* s_shi = s_slo + kPxWarps;
-    int* s_failed = s_shi + kPxWarps;
+    int* s_hi = s_lo + WARPS;
+    int* s_slo = s_hi + WARPS;
+    int* s_shi = s_slo + WARPS;
+    int* s_failed = s_shi + WARPS;
     float* s_qstep = reinterpret_cast<float*>(s_failed + 1);   // [128 rows]: step of the row's Q' residual bytes
 
     // Tables as in the exact streaming kernel: (value pair, residual pair) in 16
@@ -113,7 +117,7 @@ __global__ void __launch_bounds__(kPxWarps * 32, 1) tq4_attention_prefill_exact_
     if (tid == 0) {
         for (int s = 0; s < kPxStages; ++s) {
             mbar_init(bars + 8u * s, 1u);
-            mbar_init(bars + 8u * (kPxStages + s), (uint32_t)kPxWarps);
+            mbar_init(bars + 8u * (kPxStages + s), (uint32_t)WARPS);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         *s_failed = 0;
@@ -221,7 +225,7 @@ __global__ void __launch_bounds__(kPxWarps * 32, 1) tq4_attention_prefill_exact_
 
     int kv_lo = 0x7fffffff, kv_hi = -1, safe_lo = 0, safe_hi = 0x7fffffff;
 #pragma unroll
-    for (int w = 0; w < kPxWarps; ++w) {
+    for (int w = 0; w < WARPS; ++w) {
         kv_lo = min(kv_lo, s_lo[w]); kv_hi = max(kv_hi, s_hi[w]);
         safe_lo = max(safe_lo, s_slo[w]); safe_hi = min(safe_hi, s_shi[w]);
     }
