@@ -280,17 +280,19 @@ __global__ void __launch_bounds__(128) attn_output_gate_kernel(const void* __res
 }
 
 // ---------------------------------------------------------------------------------------
-// Scalar dequant-then-attend: one warp per (token, q head), fp32, any strides.
+// Scalar dequant-then-attend: one block of four warps per (token, q head), fp32, any strides.
 // ---------------------------------------------------------------------------------------
+// One block of four warps per (token, q head): warp w takes the keys min_kv + w, + 4, ... (two per step, so
+// that two rows are in flight), and the four online-softmax states are merged through shared memory.
 __global__ void __launch_bounds__(128) tq4_attention_scalar_kernel(
     const warp34_kv_layer_layout layout, const warp34_attention_batch batch,
     const void* __restrict__ q_in, void* __restrict__ attn_out, int num_q_heads, int io_bf16, const OutputGate og) {
     __shared__ float s_x[4][kHeadDim];
+    __shared__ float s_m[4], s_l[4];
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-    const long long row = (long long)blockIdx.x * 4 + wid;
-    if (row >= (long long)batch.total_tokens * num_q_heads) return;
+    const long long row = blockIdx.x;
     const int tok = (int)(row / num_q_heads), q_head = (int)(row % num_q_heads);
-    if (batch.valid_token_mask != nullptr && batch.valid_token_mask[tok] == 0) return;
+    if (batch.valid_token_mask != nullptr && batch.valid_token_mask[tok] == 0) return;   // block-uniform exits
     const int req = find_request(batch.query_start_loc, batch.num_reqs, tok);
     if (req < 0) return;
     const ReqGeom g = load_req(batch, req);
@@ -303,7 +305,7 @@ __global__ void __launch_bounds__(128) tq4_attention_scalar_kernel(
 
     const size_t row_base = ((size_t)tok * num_q_heads + q_head) * kHeadDim;
 
-    // Q' = WHT(sign * q); then re-distribute so that lane L owns rotated columns [8 L, 8 L + 8).
+    // Q' = WHT(sign * q) (every warp computes it); then lane L owns rotated columns [8 L, 8 L + 8).
     float t[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) t[j] = apply_sign(load_act(q_in, row_base + lane + 32 * j, io_bf16), lane + 32 * j);
@@ -319,37 +321,85 @@ __global__ void __launch_bounds__(128) tq4_attention_scalar_kernel(
     const int blk = lane >> 4;                       // which 128-half this lane reads
     const int byte_off = kTq4BlockBytes * blk + 2 + 4 * (lane & 15);
     const int32_t* blocks = batch.block_tables + (size_t)req * batch.max_blocks_per_req;
+    const uint8_t* k_head = (const uint8_t*)(uintptr_t)layout.k_base + (size_t)kv_head * layout.k_head_stride_bytes;
+    const uint8_t* v_head = (const uint8_t*)(uintptr_t)layout.v_base + (size_t)kv_head * layout.v_head_stride_bytes;
     float m_i = -1e30f, l_i = 0.0f;
-    for (int pos = min_kv; pos <= max_kv; ++pos) {
-        const int page = block_table_page(blocks, pos >> 4, batch.max_blocks_per_req, kInScalar), off = pos & 15;
-        const uint8_t* kp = (const uint8_t*)(uintptr_t)layout.k_base + (size_t)page * layout.k_page_stride_bytes +
-                            (size_t)kv_head * layout.k_head_stride_bytes + (size_t)off * layout.k_token_stride_bytes;
-        const uint8_t* vp = (const uint8_t*)(uintptr_t)layout.v_base + (size_t)page * layout.v_page_stride_bytes +
-                            (size_t)kv_head * layout.v_head_stride_bytes + (size_t)off * layout.v_token_stride_bytes;
-        const float dk = __half2float(*reinterpret_cast<const __half*>(kp + kTq4BlockBytes * blk));
-        const uint32_t kw = (uint32_t)*reinterpret_cast<const uint16_t*>(kp + byte_off) |
-                            ((uint32_t)*reinterpret_cast<const uint16_t*>(kp + byte_off + 2) << 16);
-        float dot = 0.0f;
+    for (int pos0 = min_kv + wid; pos0 <= max_kv; pos0 += 8) {
+        // keys pos0 and pos0 + 4 of this warp; the second may lie past the row's last key
+        const int pos1 = pos0 + 4;
+        const bool two = pos1 <= max_kv;
+        const uint8_t* kp[2];
+        const uint8_t* vp[2];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) dot += qv[e] * tq4_centroid((kw >> (4 * e)) & 15u);
-        const float score = warp_sum(dot * dk) * batch.sm_scale;
-        const float m_new = fmaxf(m_i, score);
+        for (int x = 0; x < 2; ++x) {
+            const int pos = (x == 0 || two) ? pos0 + 4 * x : pos0;
+            const int page = block_table_page(blocks, pos >> 4, batch.max_blocks_per_req, kInScalar), off = pos & 15;
+            kp[x] = k_head + (size_t)page * layout.k_page_stride_bytes + (size_t)off * layout.k_token_stride_bytes;
+            vp[x] = v_head + (size_t)page * layout.v_page_stride_bytes + (size_t)off * layout.v_token_stride_bytes;
+        }
+        float dk[2], dv[2];
+        uint32_t kw[2], vw[2];
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+            dk[x] = __half2float(*reinterpret_cast<const __half*>(kp[x] + kTq4BlockBytes * blk));
+            kw[x] = (uint32_t)*reinterpret_cast<const uint16_t*>(kp[x] + byte_off) |
+                    ((uint32_t)*reinterpret_cast<const uint16_t*>(kp[x] + byte_off + 2) << 16);
+            dv[x] = __half2float(*reinterpret_cast<const __half*>(vp[x] + kTq4BlockBytes * blk));
+            vw[x] = (uint32_t)*reinterpret_cast<const uint16_t*>(vp[x] + byte_off) |
+                    ((uint32_t)*reinterpret_cast<const uint16_t*>(vp[x] + byte_off + 2) << 16);
+        }
+        float dot[2] = {0.0f, 0.0f};
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            dot[0] += qv[e] * tq4_centroid((kw[0] >> (4 * e)) & 15u);
+            dot[1] += qv[e] * tq4_centroid((kw[1] >> (4 * e)) & 15u);
+        }
+        dot[0] *= dk[0];
+        dot[1] *= dk[1];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            dot[0] += __shfl_xor_sync(0xffffffffu, dot[0], off);
+            dot[1] += __shfl_xor_sync(0xffffffffu, dot[1], off);
+        }
+        const float s0 = dot[0] * batch.sm_scale;
+        const float s1 = two ? dot[1] * batch.sm_scale : -1e30f;
+        const float m_new = fmaxf(m_i, fmaxf(s0, s1));
         const float alpha = __expf(m_i - m_new);
-        const float pr = __expf(score - m_new);
-        l_i = l_i * alpha + pr;
+        const float p0 = __expf(s0 - m_new);
+        const float p1 = two ? __expf(s1 - m_new) : 0.0f;
+        l_i = l_i * alpha + p0 + p1;
         m_i = m_new;
-        const float pd = pr * __half2float(*reinterpret_cast<const __half*>(vp + kTq4BlockBytes * blk));
-        const uint32_t vw = (uint32_t)*reinterpret_cast<const uint16_t*>(vp + byte_off) |
-                            ((uint32_t)*reinterpret_cast<const uint16_t*>(vp + byte_off + 2) << 16);
+        const float pd0 = p0 * dv[0], pd1 = p1 * dv[1];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) acc[e] = acc[e] * alpha + pd * tq4_centroid((vw >> (4 * e)) & 15u);
+        for (int e = 0; e < 8; ++e) {
+            acc[e] = acc[e] * alpha + pd0 * tq4_centroid((vw[0] >> (4 * e)) & 15u) +
+                     pd1 * tq4_centroid((vw[1] >> (4 * e)) & 15u);
+        }
     }
-    const float inv_l = (l_i > 0.0f) ? (1.0f / l_i) : 0.0f;
+    // ---- merge the four warps' states: warp 0 keeps the result ---------------------------------------
 #pragma unroll
-    for (int e = 0; e < 8; ++e) s_x[wid][8 * lane + e] = acc[e] * inv_l;
+    for (int e = 0; e < 8; ++e) s_x[wid][8 * lane + e] = acc[e];
+    if (lane == 0) { s_m[wid] = m_i; s_l[wid] = l_i; }
+    __syncthreads();
+    if (wid != 0) return;
+    float m_tot = fmaxf(fmaxf(s_m[0], s_m[1]), fmaxf(s_m[2], s_m[3]));
+    float l_tot = 0.0f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+        const float wgt = (s_l[w] > 0.0f) ? __expf(s_m[w] - m_tot) : 0.0f;
+        l_tot += s_l[w] * wgt;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] += s_x[w][8 * lane + e] * wgt;
+    }
+    __syncwarp();
+    const float inv_l = (l_tot > 0.0f) ? (1.0f / l_tot) : 0.0f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) s_x[0][8 * lane + e] = acc[e] * inv_l;
     __syncwarp();
 #pragma unroll
-    for (int j = 0; j < 8; ++j) t[j] = s_x[wid][lane + 32 * j];
+    for (int j = 0; j < 8; ++j) t[j] = s_x[0][lane + 32 * j];
     wht256_lanes(t, lane);
     store_output_row(attn_out, row_base, t, lane, io_bf16, og);
 }
@@ -2361,7 +2411,8 @@ static int w34::launch_scalar(const warp34_exec* ex, const warp34_kv_layer_layou
     if (!w34::tq4_layout_ok(layout)) return (int)cudaErrorNotSupported;
     if (num_q_heads % layout->local_kv_heads != 0 || batch->num_reqs <= 0) return (int)cudaErrorInvalidValue;
     const long long rows = (long long)batch->total_tokens * num_q_heads;
-    const unsigned blocks = (unsigned)((rows + 3) / 4);
+    if (rows > 0x7fffffffll) return (int)cudaErrorInvalidValue;
+    const unsigned blocks = (unsigned)rows;   // one block of four warps per row
     w34::tq4_attention_scalar_kernel<<<blocks, 128, 0, (cudaStream_t)ex->stream>>>(
         *layout, *batch, q_in, attn_out, num_q_heads, io_bf16, og != nullptr ? *og : none);
     return (int)cudaGetLastError();
