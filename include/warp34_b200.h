@@ -219,7 +219,7 @@ int warp34_paged_attention_f16(const warp34_exec* ex, const warp34_kv_layer_layo
                                int num_q_heads);
 
 /*
- * The literal dequant-then-attend kernel (one warp per query row, fp32
+ * The literal dequant-then-attend kernel (four warps per query row, fp32
  * throughout, no scratch).  Replaces warp34_paged_attention_scalar_f16
  * (op_kv_cache.cu:1244), which the reference keeps as its fallback and test
  * selector; accepts any strides in the layout.
@@ -267,7 +267,9 @@ int warp34_paged_attention_gated_f16(const warp34_exec* ex, const warp34_kv_laye
  * warp34_apply_attn_output_gate_hadamard_f16 (warp34_cuda.h:945-947,
  * op_norms_rope_act.cu:805-851, :2032-2056): out = fp16(attn_out * sigmoid(gate)), the second
  * followed by the Hadamard-64; rows with valid_token_mask == 0 are skipped; out may alias
- * attn_out.  total_dim must be a multiple of 64 for the Hadamard variant.
+ * attn_out.  total_dim must be a multiple of 64 for the Hadamard variant.  The sigmoid is
+ * ex2.approx and rcp.approx, as the reference's -use_fast_math build lowers it: the results are
+ * the reference kernels' bit for bit.
  */
 int warp34_apply_attn_output_gate_f16(const warp34_exec* ex, const void* attn_out, const void* gate, void* out,
                                       const uint8_t* valid_token_mask, int num_tokens, int total_dim);
