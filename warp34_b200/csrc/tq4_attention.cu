@@ -151,6 +151,92 @@ __device__ __forceinline__ void store_output_row(void* out, size_t row_base, flo
     for (int j = 0; j < 8; ++j) store_act(out, row_base + lane + 32 * j, t[j], io_bf16);
 }
 
+// One 256-column chunk whose three rows start on 16-byte boundaries: lane holds columns [8 lane, 8 lane + 8).
+template <int MODE, bool BF16>
+__device__ __forceinline__ void gate_chunk_vec(uintptr_t pa, uintptr_t pg, uintptr_t po, int lane) {
+    constexpr int mode = MODE;
+    constexpr int io_bf16 = BF16 ? 1 : 0;
+    const uint4 ra = reinterpret_cast<const uint4*>(pa)[lane];   // in place is fine: a lane writes the 16 bytes it read
+    const uint4 rg = reinterpret_cast<const uint4*>(pg)[lane];
+    const uint32_t wa[4] = {ra.x, ra.y, ra.z, ra.w}, wg[4] = {rg.x, rg.y, rg.z, rg.w};
+    float x[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {   // two columns per 32-bit word
+        float2 a, g;
+        if (io_bf16) {
+            a = make_float2(__uint_as_float(wa[i] << 16), __uint_as_float(wa[i] & 0xffff0000u));
+            g = make_float2(__uint_as_float(wg[i] << 16), __uint_as_float(wg[i] & 0xffff0000u));
+        } else {
+            a = __half22float2(*reinterpret_cast<const __half2*>(&wa[i]));
+            g = __half22float2(*reinterpret_cast<const __half2*>(&wg[i]));
+        }
+        x[2 * i] = a.x * sigmoid_gate(g.x);   // `a` is already a value of the activation type
+        x[2 * i + 1] = a.y * sigmoid_gate(g.y);
+    }
+    if (mode == 2) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {   // the gated values rounded to the activation type, pairwise
+            if (io_bf16) {
+                const float2 r = __bfloat1622float2(__floats2bfloat162_rn(x[2 * i], x[2 * i + 1]));
+                x[2 * i] = r.x;
+                x[2 * i + 1] = r.y;
+            } else {
+                const float2 r = __half22float2(__floats2half2_rn(x[2 * i], x[2 * i + 1]));
+                x[2 * i] = r.x;
+                x[2 * i + 1] = r.y;
+            }
+        }
+#pragma unroll
+        for (int d = 1; d < 8; d <<= 1) {        // column bits 0-2: registers
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                if ((i & d) == 0) {
+                    const float lo = x[i], hi = x[i | d];
+                    x[i] = lo + hi;
+                    x[i | d] = lo - hi;
+                }
+            }
+        }
+#pragma unroll
+        for (int d = 1; d < 8; d <<= 1) {        // column bits 3-5: lanes (upper lane: o - x, lower: x + o)
+            const float dir = (lane & d) ? -1.0f : 1.0f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float o = __shfl_xor_sync(0xffffffffu, x[i], d);
+                x[i] = __fmaf_rn(dir, x[i], o);   // one rounding, like the add or the subtraction
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] *= 0.125f;
+    }
+    uint32_t wo[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        if (io_bf16) {
+            const __nv_bfloat162 h = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
+            wo[i] = *reinterpret_cast<const uint32_t*>(&h);
+        } else {
+            const __half2 h = __floats2half2_rn(x[2 * i], x[2 * i + 1]);
+            wo[i] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+    }
+    reinterpret_cast<uint4*>(po)[lane] = make_uint4(wo[0], wo[1], wo[2], wo[3]);
+}
+
+// The whole matrix in full, aligned chunks (known on the host): nothing but the vector path.
+template <int MODE, bool BF16>
+__global__ void __launch_bounds__(128) attn_output_gate_vec_kernel(const void* __restrict__ attn, const void* gate, void* out,
+                                                                   const uint8_t* __restrict__ valid_token_mask, int num_tokens,
+                                                                   int total_dim) {
+    const int lane = threadIdx.x & 31;
+    const int tok = (int)blockIdx.x, c = (int)blockIdx.y * 4 + (int)(threadIdx.x >> 5);
+    if (tok >= num_tokens || c * 256 >= total_dim) return;
+    if (valid_token_mask != nullptr && valid_token_mask[tok] == 0) return;
+    const size_t off = 2 * ((size_t)tok * total_dim + (size_t)c * 256);
+    gate_chunk_vec<MODE, BF16>(reinterpret_cast<uintptr_t>(attn) + off, reinterpret_cast<uintptr_t>(gate) + off,
+                               reinterpret_cast<uintptr_t>(out) + off, lane);
+}
+
 // The two steps on their own (for layers whose attention kernel has no fused epilogue): one warp per
 // 256 columns, in place or out of place.
 template <int MODE, bool BF16>
@@ -173,71 +259,7 @@ __global__ void __launch_bounds__(128) attn_output_gate_kernel(const void* __res
     const uintptr_t pa = reinterpret_cast<uintptr_t>(attn) + 2 * base, pg = reinterpret_cast<uintptr_t>(gate) + 2 * base;
     const uintptr_t po = reinterpret_cast<uintptr_t>(out) + 2 * base;
     if (cols == 256 && ((pa | pg | po) & 15u) == 0u) {
-        const uint4 ra = reinterpret_cast<const uint4*>(pa)[lane];   // in place is fine: a lane writes the 16 bytes it read
-        const uint4 rg = reinterpret_cast<const uint4*>(pg)[lane];
-        const uint32_t wa[4] = {ra.x, ra.y, ra.z, ra.w}, wg[4] = {rg.x, rg.y, rg.z, rg.w};
-        float x[8];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {   // two columns per 32-bit word
-            float2 a, g;
-            if (io_bf16) {
-                a = make_float2(__uint_as_float(wa[i] << 16), __uint_as_float(wa[i] & 0xffff0000u));
-                g = make_float2(__uint_as_float(wg[i] << 16), __uint_as_float(wg[i] & 0xffff0000u));
-            } else {
-                a = __half22float2(*reinterpret_cast<const __half2*>(&wa[i]));
-                g = __half22float2(*reinterpret_cast<const __half2*>(&wg[i]));
-            }
-            x[2 * i] = a.x * sigmoid_gate(g.x);   // `a` is already a value of the activation type
-            x[2 * i + 1] = a.y * sigmoid_gate(g.y);
-        }
-        if (mode == 2) {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {   // the gated values rounded to the activation type, pairwise
-                if (io_bf16) {
-                    const float2 r = __bfloat1622float2(__floats2bfloat162_rn(x[2 * i], x[2 * i + 1]));
-                    x[2 * i] = r.x;
-                    x[2 * i + 1] = r.y;
-                } else {
-                    const float2 r = __half22float2(__floats2half2_rn(x[2 * i], x[2 * i + 1]));
-                    x[2 * i] = r.x;
-                    x[2 * i + 1] = r.y;
-                }
-            }
-#pragma unroll
-            for (int d = 1; d < 8; d <<= 1) {        // column bits 0-2: registers
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    if ((i & d) == 0) {
-                        const float lo = x[i], hi = x[i | d];
-                        x[i] = lo + hi;
-                        x[i | d] = lo - hi;
-                    }
-                }
-            }
-#pragma unroll
-            for (int d = 1; d < 8; d <<= 1) {        // column bits 3-5: lanes (upper lane: o - x, lower: x + o)
-                const float dir = (lane & d) ? -1.0f : 1.0f;
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const float o = __shfl_xor_sync(0xffffffffu, x[i], d);
-                    x[i] = __fmaf_rn(dir, x[i], o);   // one rounding, like the add or the subtraction
-                }
-            }
-#pragma unroll
-            for (int i = 0; i < 8; ++i) x[i] *= 0.125f;
-        }
-        uint32_t wo[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            if (io_bf16) {
-                const __nv_bfloat162 h = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
-                wo[i] = *reinterpret_cast<const uint32_t*>(&h);
-            } else {
-                const __half2 h = __floats2half2_rn(x[2 * i], x[2 * i + 1]);
-                wo[i] = *reinterpret_cast<const uint32_t*>(&h);
-            }
-        }
-        reinterpret_cast<uint4*>(po)[lane] = make_uint4(wo[0], wo[1], wo[2], wo[3]);
+        gate_chunk_vec<MODE, BF16>(pa, pg, po, lane);
         return;
     }
     float v[8];
@@ -2384,6 +2406,17 @@ static int w34::launch_output_gate(const warp34_exec* ex, const void* attn, cons
     const dim3 grid((unsigned)num_tokens, (unsigned)chunk_blocks);
     cudaStream_t st = (cudaStream_t)ex->stream;
     if (mode != 1 && mode != 2) return (int)cudaErrorInvalidValue;
+    const bool all_vec = (total_dim & 255) == 0 && ((((uintptr_t)attn | (uintptr_t)gate | (uintptr_t)out) & 15u) == 0u);
+    if (all_vec) {   // every chunk full and aligned: the kernel without the element-wise path
+        if (mode == 2) {
+            if (io_bf16) w34::attn_output_gate_vec_kernel<2, true><<<grid, 128, 0, st>>>(attn, gate, out, valid_token_mask, num_tokens, total_dim);
+            else w34::attn_output_gate_vec_kernel<2, false><<<grid, 128, 0, st>>>(attn, gate, out, valid_token_mask, num_tokens, total_dim);
+        } else {
+            if (io_bf16) w34::attn_output_gate_vec_kernel<1, true><<<grid, 128, 0, st>>>(attn, gate, out, valid_token_mask, num_tokens, total_dim);
+            else w34::attn_output_gate_vec_kernel<1, false><<<grid, 128, 0, st>>>(attn, gate, out, valid_token_mask, num_tokens, total_dim);
+        }
+        return (int)cudaGetLastError();
+    }
     if (mode == 2) {
         if (io_bf16) w34::attn_output_gate_kernel<2, true><<<grid, 128, 0, st>>>(attn, gate, out, valid_token_mask, num_tokens, total_dim);
         else w34::attn_output_gate_kernel<2, false><<<grid, 128, 0, st>>>(attn, gate, out, valid_token_mask, num_tokens, total_dim);
