@@ -126,6 +126,9 @@ __device__ __forceinline__ void kv8_encode_row_by_element(const __half* src_row,
 }
 
 // One warp per (token, kv head): its K row and its V row, both loads in flight before either is encoded.
+// ALIGNED: the host has checked that every source row starts on a 16-byte boundary (base pointers and row
+// strides), so the kernel holds the 128-bit path alone.
+template <bool ALIGNED>
 __global__ void __launch_bounds__(128) kv8_append_kernel(const AppendParams p) {
     const int lane = threadIdx.x & 31;
     const int heads = p.layout.local_kv_heads;
@@ -149,15 +152,17 @@ __global__ void __launch_bounds__(128) kv8_append_kernel(const AppendParams p) {
                     (size_t)head * p.layout.v_head_stride_bytes + (size_t)off * p.layout.v_token_stride_bytes;
     // Rows that start on a 16-byte boundary (the usual case: contiguous or packed activations) are read
     // with one 128-bit load per lane.
-    if (((reinterpret_cast<uintptr_t>(ksrc) | reinterpret_cast<uintptr_t>(vsrc)) & 15u) == 0u) {
+    if (ALIGNED || ((reinterpret_cast<uintptr_t>(ksrc) | reinterpret_cast<uintptr_t>(vsrc)) & 15u) == 0u) {
         const uint4 rk = *reinterpret_cast<const uint4*>(ksrc + 8 * lane);
         const uint4 rv = *reinterpret_cast<const uint4*>(vsrc + 8 * lane);
         kv8_encode_row_vec(rk, kdst, p.layout.k_format, lane);
         kv8_encode_row_vec(rv, vdst, p.layout.v_format, lane);
         return;
     }
-    kv8_encode_row_by_element(ksrc, kdst, p.layout.k_format, lane);
-    kv8_encode_row_by_element(vsrc, vdst, p.layout.v_format, lane);
+    if (!ALIGNED) {
+        kv8_encode_row_by_element(ksrc, kdst, p.layout.k_format, lane);
+        kv8_encode_row_by_element(vsrc, vdst, p.layout.v_format, lane);
+    }
 }
 
 // Formats this file handles: both sides 8-bit and unrotated.

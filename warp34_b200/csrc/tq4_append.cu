@@ -467,7 +467,10 @@ static int launch_append_kv8(const warp34_exec* ex, const warp34_kv_layer_layout
     const long long rows = 2ll * batch->total_tokens * layout->local_kv_heads;
     if (rows > 0x7fffffffll) return (int)cudaErrorInvalidValue;
     p.total_rows = (int)rows;
-    kv8_append_kernel<<<(unsigned)((rows / 2 + 3) / 4), 128, 0, (cudaStream_t)ex->stream>>>(p);   // a warp per (token, head)
+    const bool aligned = ((((uintptr_t)k_in | (uintptr_t)v_in) & 15u) == 0u) && (k_row_stride & 7) == 0 && (v_row_stride & 7) == 0;
+    const unsigned blocks8 = (unsigned)((rows / 2 + 3) / 4);   // a warp per (token, head)
+    if (aligned) kv8_append_kernel<true><<<blocks8, 128, 0, (cudaStream_t)ex->stream>>>(p);
+    else kv8_append_kernel<false><<<blocks8, 128, 0, (cudaStream_t)ex->stream>>>(p);
     return (int)cudaGetLastError();
 }
 
